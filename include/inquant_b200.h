@@ -1,0 +1,138 @@
+/*
+ * C ABI of libinquant_b200.so -- the B200 (sm_100a) implementation of the InQuant
+ * packed-KV hot path.  Plain pointers and sizes only; every pointer is a DEVICE pointer
+ * unless its comment says "host".  Every call enqueues work on `stream` and returns
+ * without synchronising; the return value is INQ_OK or a negative INQ_ERR_* code for
+ * arguments rejected on the host (nothing is launched in that case).  Data-dependent
+ * failures (non-finite input, a device-side wait that ran out) are reported through the
+ * caller's 32-bit device status word, which kernels only ever OR bits into.
+ *
+ * Each entry point names the reference interface (file:line in
+ * changzihan22/InQuant-open-source) whose work it performs.
+ */
+#ifndef INQUANT_B200_H
+#define INQUANT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* inq_stream_t; /* a cudaStream_t */
+
+enum {
+  INQ_OK = 0,
+  INQ_ERR_ARGUMENT = -1,    /* shape / stride / enum outside the supported set */
+  INQ_ERR_UNSUPPORTED = -2, /* valid for the reference, not built for this size */
+  INQ_ERR_CUDA = -3,        /* a CUDA runtime call failed; see inq_last_error() */
+  INQ_ERR_CAPACITY = -4     /* exceeds a fixed capacity stated by the entry point */
+};
+
+enum { INQ_F32 = 0, INQ_F16 = 1, INQ_BF16 = 2 };
+
+/* bits of the device status word */
+enum {
+  INQ_STATUS_NONFINITE = 1,       /* input (or a stored fp16 parameter) was not finite */
+  INQ_STATUS_BAD_INDEX = 2,       /* a table / page index was out of range and was skipped */
+  INQ_STATUS_WAIT_TIMEOUT = 4     /* a bounded device-side wait gave up */
+};
+
+/* Human-readable text of the last INQ_ERR_CUDA on this thread (host pointer, static). */
+const char* inq_last_error(void);
+int inq_version(void);
+
+/* ---------------------------------------------------------------- addressing helpers
+ * Inputs are 4-D logical tensors [outer, inner, tokens, channels] with unit channel
+ * stride; strides are in ELEMENTS.  This covers [batch, heads, T, C] tensors, a temporal
+ * block axis moved into `outer` (reference cache.py:104-107) and the token-major
+ * [tokens, heads, C] layout of the paged backend (reference backend.py:146-147).
+ *
+ * Outputs are addressed per row (outer index p, inner index h) as
+ *     base + slot(p) * outer_stride_bytes + h * inner_stride_bytes,
+ * slot(p) = page_ids ? page_ids[p] : p.  A compact tensor uses the obvious strides; a
+ * physical page pool uses outer_stride_bytes = page_bytes for every field.
+ */
+typedef struct {
+  void* base;            /* NULL = field not wanted */
+  int64_t outer_stride;  /* bytes */
+  int64_t inner_stride;  /* bytes */
+} inq_field_t;
+
+typedef struct {
+  const void* x;         /* input elements of type `dtype` */
+  int32_t dtype;         /* INQ_F32 / INQ_F16 / INQ_BF16 */
+  int64_t n_outer, n_inner;
+  int64_t stride_outer, stride_inner, stride_token; /* elements */
+  int32_t tokens, channels;
+  const void* page_ids;  /* optional [n_outer] physical slots; NULL = identity */
+  int32_t page_ids_i64;  /* 1 if page_ids is int64, 0 if int32 */
+} inq_input_t;
+
+/* ---------------------------------------------------------------- K4 encoder
+ * Fused sampled-saliency statistics, donor selection and mixed 4/8-bit key packing for
+ * every (outer, inner) row independently.
+ * Replaces: codec.py:181-243 `quantize` (statistics :202-210, `_reuse_map` :137-178,
+ * scales :218-221, codes/pack :223-233), triton_selection.py:11-60 `_select`/`reuse_map`,
+ * and the per-block export of cache.py:89-119 `_quantize_temporal_blocks`; with a page
+ * pool as destination also layout.py:103-115 `pack_pages_into` and packing.py:7-55.
+ *   count           floor(channels * salient_fraction), 0..channels/2
+ *   min_error       1 = donor pool restricted by full-block reconstruction error
+ *   payload         u8 [T, C/2] per row;  scales f32 [C];  padding f32 [count]
+ *   salient/donors  descriptor lists [count], u8 or i32 (`descriptor_i32`)
+ *   roles           optional per-channel role map [C], `role_bytes` = 1 (int8,
+ *                   triton_attention.py:301-309) or 2 (int16, layout.py:73-77)
+ * Requirements: channels even, <= 1024; tokens >= 1; sample_stride >= 1.
+ */
+typedef struct {
+  inq_input_t in;
+  int32_t sample_stride, count, min_error;
+  inq_field_t payload, scales, salient, donors, padding, roles;
+  int32_t descriptor_i32, role_bytes;
+} inq_k4_encode_args_t;
+int inq_k4_encode(const inq_k4_encode_args_t* args /* host */, int32_t* status, inq_stream_t stream);
+
+/* Stand-alone donor selection on precomputed statistics.
+ * Replaces: codec.py:137-178 `_reuse_map`, triton_selection.py:46-60 `reuse_map`.
+ * saliency / donor_error: f32 [rows, channels] (donor_error may be NULL);
+ * sources / donors: int64 [rows, count]. */
+int inq_select_donors(const float* saliency, const float* donor_error, int64_t rows, int32_t channels,
+                      int32_t count, int64_t* sources, int64_t* donors, inq_stream_t stream);
+
+/* Sampled statistics alone (used by stage-by-stage benchmarks and tests).
+ * Replaces: codec.py:202-210.  Outputs f32 [rows, C]; any may be NULL. */
+int inq_k4_statistics(const inq_input_t* in /* host */, int32_t sample_stride, float* saliency,
+                      float* sampled_mean, float* donor_error, float* absmax, inq_stream_t stream);
+
+/* Exact inverse of the K4 layout.  Replaces: codec.py:112-134 `PackedTensor.dequantize`.
+ * All tensors compact: payload [rows,T,C/2], scales [rows,C], lists [rows,count]. */
+int inq_k4_dequantize(const uint8_t* payload, const float* scales, const void* salient, const void* donors,
+                      int32_t descriptor_i32, const float* padding, int64_t rows, int32_t tokens,
+                      int32_t channels, int32_t count, void* out, int32_t out_dtype, inq_stream_t stream);
+
+/* ---------------------------------------------------------------- V encoder
+ * Per-token, per-group affine INT2/INT4 with fp16 scale and minimum.
+ * Replaces: value_codec.py:51-72 `quantize_values`, :75-88 `quantize_value_blocks`.
+ *   payload u8 [T, C*bits/8]; scales/offsets f16 [T, C/group] per row.
+ * Requirements: bits 2|4, group 32|64|128, channels % group == 0, channels <= 256. */
+typedef struct {
+  inq_input_t in;
+  int32_t bits, group;
+  inq_field_t payload, scales, offsets;
+} inq_v_encode_args_t;
+int inq_v_encode(const inq_v_encode_args_t* args /* host */, int32_t* status, inq_stream_t stream);
+
+/* Replaces: value_codec.py:38-48 `PackedValues.dequantize`. */
+int inq_v_dequantize(const uint8_t* payload, const void* scales, const void* offsets, int64_t rows,
+                     int32_t tokens, int32_t channels, int32_t bits, int32_t group, void* out,
+                     int32_t out_dtype, inq_stream_t stream);
+
+/* Role maps from descriptor lists.  Replaces: triton_attention.py:301-309 `_write_maps`
+ * and the map construction inside packing.py:24-29.  lists [rows,count] u8 or i32. */
+int inq_build_roles(const void* salient, const void* donors, int32_t descriptor_i32, int64_t rows,
+                    int32_t channels, int32_t count, void* roles, int32_t role_bytes, inq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INQUANT_B200_H */

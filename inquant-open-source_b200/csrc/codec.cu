@@ -1,0 +1,833 @@
+// K4 key encoder (sampled statistics + donor selection + mixed 4/8-bit packing), V2/V4
+// group-wise value encoder, their exact inverses and the role-map builder.
+//
+// Compile this translation unit with -fmad=false: the packed bytes must equal the
+// reference's bit for bit, and the reference performs separate IEEE multiplies, adds and
+// divisions.  The only fused operations are the explicit fma() calls of the division-by-
+// integer below, which is proven to return the correctly rounded quotient.
+#include "common.cuh"
+
+namespace inq {
+
+constexpr int kMaxChannels = 1024;
+constexpr int kMaxWords = kMaxChannels / 32;
+constexpr int kRcpTable = 512;  // tokens per row for which 1/(t+1) is tabulated in shared memory
+
+// ------------------------------------------------------------------------------------------
+// Sampled statistics in the summation order of the reference's CPU reduction: samples are
+// added one by one into a level-0 accumulator that is folded into level 1 every `step`
+// samples (level 1 into level 2 every step^2, ...), a remainder shorter than `step` stays in
+// level 0, and the levels are added lowest first at the end.
+struct CascadePair {
+  float abs_acc[4], sum_acc[4];
+  int i, full_end, mask, level_power;
+  __device__ void init(int n) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) abs_acc[k] = sum_acc[k] = 0.f;
+    int ceil_log2 = n <= 1 ? 0 : 32 - __clz(n - 1);
+    level_power = max(4, ceil_log2 / 4);
+    int step = 1 << level_power;
+    mask = step - 1;
+    full_end = (n / step) * step;
+    i = 0;
+  }
+  __device__ void add(float v) {
+    abs_acc[0] = abs_acc[0] + fabsf(v);
+    sum_acc[0] = sum_acc[0] + v;
+    ++i;
+    if (i <= full_end && (i & mask) == 0) {
+#pragma unroll
+      for (int level = 1; level < 4; ++level) {
+        abs_acc[level] = abs_acc[level] + abs_acc[level - 1];
+        sum_acc[level] = sum_acc[level] + sum_acc[level - 1];
+        abs_acc[level - 1] = 0.f;
+        sum_acc[level - 1] = 0.f;
+        if (i & (mask << (level * level_power))) break;
+      }
+    }
+  }
+  __device__ void finish(float& abs_total, float& sum_total) {
+#pragma unroll
+    for (int level = 1; level < 4; ++level) {
+      abs_acc[0] = abs_acc[0] + abs_acc[level];
+      sum_acc[0] = sum_acc[0] + sum_acc[level];
+    }
+    abs_total = abs_acc[0];
+    sum_total = sum_acc[0];
+  }
+};
+
+// d / n for a small positive integer n, given y = RN(1/n): one multiply and two fused
+// corrections return the correctly rounded IEEE quotient (Markstein's theorem).
+__device__ __forceinline__ double divide_by_count(double d, double n, double y) {
+  double q0 = d * y;
+  double r = fma(-q0, n, d);
+  return fma(r, y, q0);
+}
+
+struct ChannelStats {
+  float saliency, sampled_mean, donor_error, absmax;
+  bool finite;
+};
+
+// One thread walks one channel over all tokens of a row.
+template <typename T>
+__device__ ChannelStats channel_statistics(const T* column, long long s_token, int tokens, int sample_stride,
+                                           bool want_error, const double* rcp_table) {
+  ChannelStats out;
+  CascadePair cascade;
+  int samples = (tokens + sample_stride - 1) / sample_stride;
+  cascade.init(samples);
+  float absmax = 0.f;
+  bool finite = true;
+  double mean = 0.0, m2 = 0.0;
+  int next_sample = 0;
+  constexpr int kUnroll = 8;
+  for (int base = 0; base < tokens; base += kUnroll) {
+    float v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      int t = base + u;
+      v[u] = t < tokens ? to_float<T>(column[(long long)t * s_token]) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      int t = base + u;
+      if (t < tokens) {
+        float x = v[u];
+        finite = finite && finite_f32(x);
+        absmax = fmaxf(absmax, fabsf(x));
+        if (t == next_sample) {
+          cascade.add(x);
+          next_sample += sample_stride;
+        }
+        if (want_error) {
+          // Welford's update in float64, sequential over tokens (torch CPU var_mean).
+          double xd = (double)x;
+          double delta = xd - mean;
+          double q = rcp_table ? divide_by_count(delta, (double)(t + 1), rcp_table[t]) : delta / (double)(t + 1);
+          mean = mean + q;
+          m2 = m2 + delta * (xd - mean);
+        }
+      }
+    }
+  }
+  float abs_total, sum_total;
+  cascade.finish(abs_total, sum_total);
+  out.saliency = abs_total / (float)samples;
+  out.sampled_mean = sum_total / (float)samples;
+  out.absmax = absmax;
+  out.finite = finite;
+  out.donor_error = 0.f;
+  if (want_error) {
+    float variance = (float)(m2 / (double)tokens);
+    float diff = (float)mean - out.sampled_mean;
+    out.donor_error = variance + diff * diff;
+  }
+  return out;
+}
+
+// ------------------------------------------------------------------------------------------
+// Donor selection.  Called by every thread of a CTA whose blockDim.x >= channels.
+// Shared inputs: saliency[C], error[C] (if use_error).  Shared scratch: rank_key[C] (u32),
+// sel_mask / avail_mask [NW words].  Outputs in shared memory: sources[count] ascending,
+// donors[count].
+template <int NW>
+__device__ int highest_below(const unsigned (&mask)[NW], int pos) {  // largest set index < pos, or -1
+  int w = pos >> 5;
+  if (w < NW) {
+    unsigned m = (pos & 31) ? (mask[w] & ((1u << (pos & 31)) - 1u)) : 0u;
+    if (m) return (w << 5) + 31 - __clz(m);
+  }
+  for (int k = min(w, NW) - 1; k >= 0; --k)
+    if (mask[k]) return (k << 5) + 31 - __clz(mask[k]);
+  return -1;
+}
+template <int NW>
+__device__ int lowest_above(const unsigned (&mask)[NW], int pos, int limit) {  // smallest set index > pos, or limit
+  int start = pos + 1;
+  int w = start >> 5;
+  if (w < NW) {
+    unsigned m = mask[w] & (0xffffffffu << (start & 31));
+    if (m) return (w << 5) + __ffs(m) - 1;
+    for (int k = w + 1; k < NW; ++k)
+      if (mask[k]) return (k << 5) + __ffs(mask[k]) - 1;
+  }
+  return limit;
+}
+template <int NW>
+__device__ __forceinline__ bool test_bit(const unsigned (&mask)[NW], int pos) {
+  return pos >= 0 && (pos >> 5) < NW && ((mask[pos >> 5] >> (pos & 31)) & 1u);
+}
+
+template <int NW>
+__device__ void assign_donors_serial(const float* saliency, const unsigned* sel_words, const unsigned* avail_words,
+                                     int channels, int count, int* sources, int* donors) {
+  unsigned selected[NW], available[NW];
+#pragma unroll
+  for (int k = 0; k < NW; ++k) {
+    selected[k] = sel_words[k];
+    available[k] = avail_words[k];
+  }
+  int n = 0;
+#pragma unroll
+  for (int k = 0; k < NW; ++k) {
+    unsigned m = selected[k];
+    while (m && n < count) {
+      sources[n++] = (k << 5) + __ffs(m) - 1;
+      m &= m - 1;
+    }
+  }
+  for (int i = 0; i < count; ++i) {
+    int source = sources[i];
+    int low = test_bit<NW>(available, source - 1) ? source - 1 : -1;
+    int high = (source + 1 < channels && test_bit<NW>(available, source + 1)) ? source + 1 : -1;
+    if (low < 0 && high < 0) {
+      // Ends of the contiguous salient run that contains the source.
+      int left = source, right = source;
+      while (test_bit<NW>(selected, left - 1)) --left;
+      while (right + 1 < channels && test_bit<NW>(selected, right + 1)) ++right;
+      int below = highest_below<NW>(available, left);
+      int above = lowest_above<NW>(available, right, channels);
+      int d_below = below >= 0 ? left - below : 0x7fffffff;
+      int d_above = above < channels ? above - right : 0x7fffffff;
+      if (d_below <= d_above) low = below;
+      if (d_above <= d_below && above < channels) high = above;
+    }
+    int donor;
+    if (low >= 0 && high >= 0)
+      donor = saliency[low] <= saliency[high] ? low : high;  // ties: the lower channel
+    else
+      donor = low >= 0 ? low : high;
+    if (donor < 0) donor = 0;  // unreachable for count <= channels/2
+    donors[i] = donor;
+    available[donor >> 5] &= ~(1u << (donor & 31));
+  }
+}
+
+__device__ void select_donors_cta(const float* saliency, const float* error, bool use_error, int channels, int count,
+                                  unsigned* rank_key, unsigned* sel_mask, unsigned* avail_mask, int* sources,
+                                  int* donors) {
+  const int c = threadIdx.x;
+  const int words = (channels + 31) >> 5;
+  if (c < kMaxWords) {
+    sel_mask[c] = 0u;
+    avail_mask[c] = 0u;
+  }
+  __syncthreads();
+  bool selected = false;
+  if (c < channels && count > 0) {
+    // Non-negative floats order like their bit patterns; ties go to the lower channel.
+    unsigned mine = __float_as_uint(saliency[c]);
+    int rank = 0;
+    for (int o = 0; o < channels; ++o) {
+      unsigned other = __float_as_uint(saliency[o]);
+      rank += (other > mine) || (other == mine && o < c);
+    }
+    selected = rank < count;
+    if (selected) atomicOr(&sel_mask[c >> 5], 1u << (c & 31));
+    if (use_error) rank_key[c] = selected ? 0x7f800000u : __float_as_uint(error[c]);
+    if (!use_error && !selected) atomicOr(&avail_mask[c >> 5], 1u << (c & 31));
+  }
+  __syncthreads();
+  if (use_error && c < channels && count > 0 && !selected) {
+    unsigned mine = rank_key[c];
+    int rank = 0;
+    for (int o = 0; o < channels; ++o) {
+      unsigned other = rank_key[o];
+      rank += (other < mine) || (other == mine && o < c);
+    }
+    if (rank < count) atomicOr(&avail_mask[c >> 5], 1u << (c & 31));
+  }
+  __syncthreads();
+  if (c == 0 && count > 0) {
+    if (words <= 4)
+      assign_donors_serial<4>(saliency, sel_mask, avail_mask, channels, count, sources, donors);
+    else
+      assign_donors_serial<kMaxWords>(saliency, sel_mask, avail_mask, channels, count, sources, donors);
+  }
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------
+struct K4Params {
+  InputRef in;
+  int sample_stride, count, min_error;
+  FieldRef payload, scales, salient, donors, padding, roles;
+  int descriptor_i32, role_bytes;
+  int vector_path;  // 1: rows are 16-byte aligned and channels % 8 == 0
+  int* status;
+};
+
+struct K4Shared {
+  float* saliency;
+  float* error;
+  float* sampled_mean;
+  float* scale;      // divisor per slot (the source's scale for a donor slot)
+  int* read_from;    // channel whose value fills this slot
+  int* kind;         // 0 normal, 1 salient (high nibble), 2 donor slot (low nibble of its source)
+  unsigned* rank_key;
+  unsigned* sel_mask;
+  unsigned* avail_mask;
+  int* sources;
+  int* donors;
+  double* rcp;
+};
+
+__host__ __device__ inline size_t k4_shared_bytes(int channels, int count, int tokens, bool min_error) {
+  size_t bytes = 0;
+  bytes += (size_t)channels * 4 * 7;          // saliency, error, sampled_mean, scale, read_from, kind, rank_key
+  bytes += (size_t)kMaxWords * 4 * 2;         // masks
+  bytes += (size_t)(count > 0 ? count : 1) * 4 * 2;
+  bytes = (bytes + 7) & ~(size_t)7;
+  if (min_error && tokens <= kRcpTable) bytes += (size_t)tokens * 8;
+  return bytes;
+}
+
+__device__ inline K4Shared carve_k4_shared(unsigned char* raw, int channels, int count, int tokens, bool min_error) {
+  K4Shared s;
+  float* f = (float*)raw;
+  s.saliency = f; f += channels;
+  s.error = f; f += channels;
+  s.sampled_mean = f; f += channels;
+  s.scale = f; f += channels;
+  s.read_from = (int*)f; f += channels;
+  s.kind = (int*)f; f += channels;
+  s.rank_key = (unsigned*)f; f += channels;
+  s.sel_mask = (unsigned*)f; f += kMaxWords;
+  s.avail_mask = (unsigned*)f; f += kMaxWords;
+  s.sources = (int*)f; f += (count > 0 ? count : 1);
+  s.donors = (int*)f; f += (count > 0 ? count : 1);
+  size_t used = ((size_t)((unsigned char*)f - raw) + 7) & ~(size_t)7;
+  s.rcp = (min_error && tokens <= kRcpTable) ? (double*)(raw + used) : nullptr;
+  return s;
+}
+
+__device__ __forceinline__ unsigned encode_slot(float x, float scale, int kind) {
+  float q = rintf(x / scale);
+  if (kind == 0) return (unsigned)(int)(fminf(fmaxf(q, -7.f), 7.f) + 8.f);
+  unsigned code = (unsigned)(int)(fminf(fmaxf(q, -127.f), 127.f) + 128.f);
+  return kind == 1 ? (code >> 4) : (code & 15u);
+}
+
+template <typename T, int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads) k4_encode_kernel(K4Params p) {
+  extern __shared__ __align__(16) unsigned char raw[];
+  const int C = p.in.channels, tokens = p.in.tokens, count = p.count;
+  K4Shared s = carve_k4_shared(raw, C, count, tokens, p.min_error != 0);
+  const long long outer = blockIdx.x / p.in.n_inner, inner = blockIdx.x % p.in.n_inner;
+  const long long slot = p.in.slot(outer);
+  const T* row = (const T*)p.in.x + outer * p.in.s_outer + inner * p.in.s_inner;
+  const int c = threadIdx.x;
+
+  if (s.rcp)
+    for (int t = c; t < tokens; t += blockDim.x) s.rcp[t] = 1.0 / (double)(t + 1);
+  __syncthreads();
+
+  float absmax = 0.f;
+  if (c < C) {
+    ChannelStats st = channel_statistics<T>(row + c, p.in.s_token, tokens, p.sample_stride, p.min_error != 0, s.rcp);
+    s.saliency[c] = st.saliency;
+    s.sampled_mean[c] = st.sampled_mean;
+    s.error[c] = st.donor_error;
+    absmax = st.absmax;
+    if (!st.finite) atomicOr(p.status, INQ_STATUS_NONFINITE);
+    s.kind[c] = 0;
+    s.read_from[c] = c;
+  }
+  __syncthreads();
+  select_donors_cta(s.saliency, s.error, p.min_error != 0, C, count, s.rank_key, s.sel_mask, s.avail_mask,
+                    s.sources, s.donors);
+
+  if (c < C) {
+    bool selected = (s.sel_mask[c >> 5] >> (c & 31)) & 1u;
+    float own = fmaxf(absmax / (selected ? 127.0f : 7.0f), 1.17549435e-38f);
+    s.scale[c] = own;
+    ((float*)p.scales.at(slot, inner))[c] = own;
+    if (selected) s.kind[c] = 1;
+  }
+  __syncthreads();
+  if (c < count) {
+    int source = s.sources[c], donor = s.donors[c];
+    s.kind[donor] = 2;
+    s.read_from[donor] = source;
+    ((float*)p.padding.at(slot, inner))[c] = s.sampled_mean[donor];
+    if (p.salient.base) {
+      if (p.descriptor_i32) {
+        ((int*)p.salient.at(slot, inner))[c] = source;
+        ((int*)p.donors.at(slot, inner))[c] = donor;
+      } else {
+        ((unsigned char*)p.salient.at(slot, inner))[c] = (unsigned char)source;
+        ((unsigned char*)p.donors.at(slot, inner))[c] = (unsigned char)donor;
+      }
+    }
+  }
+  __syncthreads();
+  if (c < count) s.scale[s.donors[c]] = s.scale[s.sources[c]];  // a donor slot divides by its source's scale
+  if (p.roles.base) {
+    // role: donor channel of a salient channel, -1 for a normal one, -2-i for the i-th donor
+    if (c < C) {
+      int role = -1;
+      for (int i = 0; i < count; ++i) {
+        if (s.sources[i] == c) role = s.donors[i];
+        if (s.donors[i] == c) role = -2 - i;
+      }
+      if (p.role_bytes == 1)
+        ((signed char*)p.roles.at(slot, inner))[c] = (signed char)role;
+      else
+        ((short*)p.roles.at(slot, inner))[c] = (short)role;
+    }
+  }
+  __syncthreads();
+
+  unsigned char* payload = (unsigned char*)p.payload.at(slot, inner);
+  const int row_bytes = C / 2;
+  if (p.vector_path) {
+    // A thread owns 8 fixed channels (4 payload bytes) and strides over tokens.
+    const int chunks = C / 8;
+    const int lanes = (blockDim.x / chunks) * chunks;
+    if (c < lanes) {
+      const int chunk = c % chunks, t0 = c / chunks, t_step = lanes / chunks;
+      float scale[8];
+      int kind[8], from[8];
+      bool any_remote = false;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        int ch = chunk * 8 + j;
+        scale[j] = s.scale[ch];
+        kind[j] = s.kind[ch];
+        from[j] = s.read_from[ch];
+        any_remote |= (from[j] != ch);
+      }
+      for (int t = t0; t < tokens; t += t_step) {
+        const T* src = row + (long long)t * p.in.s_token;
+        float v[8];
+        if (sizeof(T) == 2) {
+          uint4 bits = *(const uint4*)(src + chunk * 8);
+          const T* h = (const T*)&bits;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = to_float<T>(h[j]);
+        } else {
+          float4 a = *(const float4*)(src + chunk * 8), b = *(const float4*)(src + chunk * 8 + 4);
+          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        }
+        if (any_remote) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (kind[j] == 2) v[j] = to_float<T>(src[from[j]]);
+        }
+        unsigned word = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) word |= encode_slot(v[j], scale[j], kind[j]) << (4 * j);
+        *(unsigned*)(payload + (long long)t * row_bytes + chunk * 4) = word;
+      }
+    }
+  } else {
+    for (long long idx = c; idx < (long long)tokens * row_bytes; idx += blockDim.x) {
+      int t = (int)(idx / row_bytes), b = (int)(idx % row_bytes);
+      const T* src = row + (long long)t * p.in.s_token;
+      unsigned lo = encode_slot(to_float<T>(src[s.read_from[2 * b]]), s.scale[2 * b], s.kind[2 * b]);
+      unsigned hi = encode_slot(to_float<T>(src[s.read_from[2 * b + 1]]), s.scale[2 * b + 1], s.kind[2 * b + 1]);
+      payload[idx] = (unsigned char)(lo | (hi << 4));
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024) k4_statistics_kernel(InputRef in, int sample_stride, float* saliency,
+                                                              float* sampled_mean, float* donor_error, float* absmax) {
+  extern __shared__ __align__(16) unsigned char raw[];
+  double* rcp = (donor_error && in.tokens <= kRcpTable) ? (double*)raw : nullptr;
+  const long long outer = blockIdx.x / in.n_inner, inner = blockIdx.x % in.n_inner;
+  const T* row = (const T*)in.x + outer * in.s_outer + inner * in.s_inner;
+  if (rcp)
+    for (int t = threadIdx.x; t < in.tokens; t += blockDim.x) rcp[t] = 1.0 / (double)(t + 1);
+  __syncthreads();
+  const int c = threadIdx.x;
+  if (c >= in.channels) return;
+  ChannelStats st = channel_statistics<T>(row + c, in.s_token, in.tokens, sample_stride, donor_error != nullptr, rcp);
+  long long o = (long long)blockIdx.x * in.channels + c;
+  if (saliency) saliency[o] = st.saliency;
+  if (sampled_mean) sampled_mean[o] = st.sampled_mean;
+  if (donor_error) donor_error[o] = st.donor_error;
+  if (absmax) absmax[o] = st.absmax;
+}
+
+__global__ void __launch_bounds__(1024) select_kernel(const float* saliency, const float* error, int channels, int count,
+                                                       long long* sources, long long* donors) {
+  extern __shared__ __align__(16) unsigned char raw[];
+  float* sal = (float*)raw;
+  float* err = sal + channels;
+  unsigned* rank_key = (unsigned*)(err + channels);
+  unsigned* sel_mask = rank_key + channels;
+  unsigned* avail_mask = sel_mask + kMaxWords;
+  int* src = (int*)(avail_mask + kMaxWords);
+  int* don = src + count;
+  const long long row = blockIdx.x;
+  const int c = threadIdx.x;
+  if (c < channels) {
+    sal[c] = saliency[row * channels + c];
+    err[c] = error ? error[row * channels + c] : 0.f;
+  }
+  __syncthreads();
+  select_donors_cta(sal, err, error != nullptr, channels, count, rank_key, sel_mask, avail_mask, src, don);
+  if (c < count) {
+    sources[row * count + c] = src[c];
+    donors[row * count + c] = don[c];
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void k4_dequantize_kernel(const unsigned char* payload, const float* scales, const void* salient,
+                                     const void* donors, int descriptor_i32, const float* padding, int tokens,
+                                     int channels, int count, T* out) {
+  extern __shared__ __align__(16) unsigned char raw[];
+  int* role = (int*)raw;  // >=0 partner slot of a salient channel, -1 normal, <=-2 donor
+  float* scale = (float*)(role + channels);
+  float* pad = scale + channels;
+  const long long row = blockIdx.x;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    role[c] = -1;
+    scale[c] = scales[row * channels + c];
+    pad[c] = 0.f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    int s = descriptor_i32 ? ((const int*)salient)[row * count + i] : ((const unsigned char*)salient)[row * count + i];
+    int d = descriptor_i32 ? ((const int*)donors)[row * count + i] : ((const unsigned char*)donors)[row * count + i];
+    role[s] = d;
+    role[d] = -2 - i;
+    pad[d] = padding[row * count + i];
+  }
+  __syncthreads();
+  const unsigned char* bytes = payload + row * (long long)tokens * (channels / 2);
+  T* dst = out + row * (long long)tokens * channels;
+  const int t_begin = blockIdx.y * 16, t_end = min(tokens, t_begin + 16);
+  for (int idx = t_begin * channels + threadIdx.x; idx < t_end * channels; idx += blockDim.x) {
+    int t = idx / channels, c = idx % channels;
+    const unsigned char* line = bytes + (long long)t * (channels / 2);
+    int slot = (line[c >> 1] >> ((c & 1) * 4)) & 15;
+    int r = role[c];
+    float value;
+    if (r >= 0) {
+      int partner = (line[r >> 1] >> ((r & 1) * 4)) & 15;
+      value = (float)(((slot << 4) | partner) - 128) * scale[c];
+    } else if (r == -1) {
+      value = (float)(slot - 8) * scale[c];
+    } else {
+      value = pad[c];
+    }
+    dst[idx] = from_float<T>(value);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+struct VParams {
+  InputRef in;
+  int bits, group;
+  FieldRef payload, scales, offsets;
+  int* status;
+};
+
+// One warp per token row; a lane owns channels / 32 consecutive channels.
+template <typename T, int CPL>
+__global__ void __launch_bounds__(256) v_encode_kernel(VParams p) {
+  const int warps_per_block = blockDim.x / 32, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const long long outer = blockIdx.x / p.in.n_inner, inner = blockIdx.x % p.in.n_inner;
+  const long long slot = p.in.slot(outer);
+  const int t = blockIdx.y * warps_per_block + warp;
+  if (t >= p.in.tokens) return;
+  const int C = p.in.channels, groups = C / p.group;
+  const T* src = (const T*)p.in.x + outer * p.in.s_outer + inner * p.in.s_inner + (long long)t * p.in.s_token + lane * CPL;
+  float v[CPL];
+#pragma unroll
+  for (int j = 0; j < CPL; ++j) v[j] = to_float<T>(src[j]);
+  float lo = v[0], hi = v[0];
+  bool finite = true;
+#pragma unroll
+  for (int j = 0; j < CPL; ++j) {
+    lo = fminf(lo, v[j]);
+    hi = fmaxf(hi, v[j]);
+    finite = finite && finite_f32(v[j]);
+  }
+  const int lanes_per_group = p.group / CPL;
+  for (int off = 1; off < lanes_per_group; off <<= 1) {
+    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+  }
+  const float levels = (float)((1 << p.bits) - 1);
+  __half offset16 = __float2half_rn(lo);
+  __half scale16 = __float2half_rn(fmaxf((hi - lo) / levels, 6.103515625e-05f));
+  float offset = __half2float(offset16), scale = __half2float(scale16);
+  finite = finite && finite_f32(offset) && finite_f32(scale);
+  if (!finite) atomicOr(p.status, INQ_STATUS_NONFINITE);
+  const int g = lane / lanes_per_group;
+  if (lane % lanes_per_group == 0) {
+    ((__half*)p.scales.at(slot, inner))[(long long)t * groups + g] = scale16;
+    ((__half*)p.offsets.at(slot, inner))[(long long)t * groups + g] = offset16;
+  }
+  // Pack this lane's codes, then OR together the lanes that share a 32-bit word.
+  const int bits = p.bits, lane_bits = CPL * bits;
+  unsigned char* dst = (unsigned char*)p.payload.at(slot, inner) + (long long)t * (C * bits / 8);
+  if (lane_bits >= 32) {
+    constexpr int kWords = (CPL * 4 + 31) / 32;  // upper bound for bits = 4
+    unsigned words[kWords];
+#pragma unroll
+    for (int w = 0; w < kWords; ++w) words[w] = 0u;
+#pragma unroll
+    for (int j = 0; j < CPL; ++j) {
+      unsigned code = (unsigned)(int)fminf(fmaxf(rintf((v[j] - offset) / scale), 0.f), levels);
+      words[(j * bits) >> 5] |= code << ((j * bits) & 31);
+    }
+    const int n_words = lane_bits / 32;
+    for (int w = 0; w < n_words; ++w) ((unsigned*)dst)[lane * n_words + w] = words[w];
+  } else {
+    unsigned word = 0u;
+    const int lanes_per_word = 32 / lane_bits;
+#pragma unroll
+    for (int j = 0; j < CPL; ++j) {
+      unsigned code = (unsigned)(int)fminf(fmaxf(rintf((v[j] - offset) / scale), 0.f), levels);
+      word |= code << (((lane % lanes_per_word) * CPL + j) * bits);
+    }
+    for (int off = 1; off < lanes_per_word; off <<= 1) word |= __shfl_xor_sync(0xffffffffu, word, off);
+    if (lane % lanes_per_word == 0) ((unsigned*)dst)[lane / lanes_per_word] = word;
+  }
+}
+
+template <typename T>
+__global__ void v_dequantize_kernel(const unsigned char* payload, const __half* scales, const __half* offsets,
+                                    long long total, int channels, int bits, int group, T* out) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  long long token = idx / channels;
+  int c = (int)(idx % channels);
+  int per_byte = 8 / bits;
+  unsigned byte = payload[token * (channels / per_byte) + c / per_byte];
+  float code = (float)((byte >> ((c % per_byte) * bits)) & ((1u << bits) - 1u));
+  long long param = token * (channels / group) + c / group;
+  float value = code * __half2float(scales[param]);
+  value = value + __half2float(offsets[param]);
+  out[idx] = from_float<T>(value);
+}
+
+__global__ void build_roles_kernel(const void* salient, const void* donors, int descriptor_i32, int channels, int count,
+                                   void* roles, int role_bytes) {
+  const long long row = blockIdx.x;
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    int role = -1;
+    for (int i = 0; i < count; ++i) {
+      int s = descriptor_i32 ? ((const int*)salient)[row * count + i] : ((const unsigned char*)salient)[row * count + i];
+      int d = descriptor_i32 ? ((const int*)donors)[row * count + i] : ((const unsigned char*)donors)[row * count + i];
+      if (s == c) role = d;
+      if (d == c) role = -2 - i;
+    }
+    if (role_bytes == 1)
+      ((signed char*)roles)[row * channels + c] = (signed char)role;
+    else
+      ((short*)roles)[row * channels + c] = (short)role;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+static bool input_ok(const inq_input_t& in) {
+  return in.x && valid_dtype(in.dtype) && in.n_outer >= 1 && in.n_inner >= 1 && in.tokens >= 1 && in.channels >= 1 &&
+         in.n_outer * in.n_inner < (1ll << 31);
+}
+
+static bool rows_vectorizable(const inq_input_t& in) {
+  long long es = dtype_size(in.dtype);
+  return in.channels % 8 == 0 && ((uintptr_t)in.x % 16 == 0) && (in.stride_outer * es) % 16 == 0 &&
+         (in.stride_inner * es) % 16 == 0 && (in.stride_token * es) % 16 == 0;
+}
+
+}  // namespace inq
+
+using namespace inq;
+
+extern "C" int inq_k4_encode(const inq_k4_encode_args_t* a, int32_t* status, inq_stream_t stream_) {
+  if (!a || !status || !input_ok(a->in)) return INQ_ERR_ARGUMENT;
+  const int C = a->in.channels;
+  if (C % 2 || a->count < 0 || a->count > C / 2 || a->sample_stride < 1) return INQ_ERR_ARGUMENT;
+  if (C > kMaxChannels) return INQ_ERR_UNSUPPORTED;
+  if (!a->payload.base || !a->scales.base || (a->count && !a->padding.base)) return INQ_ERR_ARGUMENT;
+  if ((a->salient.base == nullptr) != (a->donors.base == nullptr)) return INQ_ERR_ARGUMENT;
+  if (a->roles.base && a->role_bytes != 1 && a->role_bytes != 2) return INQ_ERR_ARGUMENT;
+  if (!a->descriptor_i32 && C > 256 && a->salient.base) return INQ_ERR_ARGUMENT;
+  K4Params p;
+  p.in = make_input(a->in);
+  p.sample_stride = a->sample_stride;
+  p.count = a->count;
+  p.min_error = a->min_error;
+  p.payload = make_field(a->payload);
+  p.scales = make_field(a->scales);
+  p.salient = make_field(a->salient);
+  p.donors = make_field(a->donors);
+  p.padding = make_field(a->padding);
+  p.roles = make_field(a->roles);
+  p.descriptor_i32 = a->descriptor_i32;
+  p.role_bytes = a->role_bytes;
+  p.status = status;
+  // 4-byte payload stores need 4-byte aligned rows; the payload row is C/2 bytes.
+  p.vector_path = rows_vectorizable(a->in) && ((uintptr_t)a->payload.base % 4 == 0) && a->payload.outer_stride % 4 == 0 &&
+                  a->payload.inner_stride % 4 == 0;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int threads = ((C + 31) / 32) * 32;
+  if (threads < 128 && C % 8 == 0) threads = 128;  // more tokens in flight while packing narrow rows
+  size_t shared = k4_shared_bytes(C, a->count, a->in.tokens, a->min_error != 0);
+  unsigned grid = (unsigned)(a->in.n_outer * a->in.n_inner);
+  if (threads <= 256) {
+    switch (a->in.dtype) {
+      case INQ_F32: k4_encode_kernel<float, 256><<<grid, threads, shared, stream>>>(p); break;
+      case INQ_F16: k4_encode_kernel<__half, 256><<<grid, threads, shared, stream>>>(p); break;
+      default: k4_encode_kernel<__nv_bfloat16, 256><<<grid, threads, shared, stream>>>(p); break;
+    }
+  } else {
+    switch (a->in.dtype) {
+      case INQ_F32: k4_encode_kernel<float, 1024><<<grid, threads, shared, stream>>>(p); break;
+      case INQ_F16: k4_encode_kernel<__half, 1024><<<grid, threads, shared, stream>>>(p); break;
+      default: k4_encode_kernel<__nv_bfloat16, 1024><<<grid, threads, shared, stream>>>(p); break;
+    }
+  }
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}
+
+extern "C" int inq_k4_statistics(const inq_input_t* in, int32_t sample_stride, float* saliency, float* sampled_mean,
+                                 float* donor_error, float* absmax, inq_stream_t stream_) {
+  if (!in || !input_ok(*in) || sample_stride < 1) return INQ_ERR_ARGUMENT;
+  if (in->channels > kMaxChannels) return INQ_ERR_UNSUPPORTED;
+  InputRef ref = make_input(*in);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int threads = ((in->channels + 31) / 32) * 32;
+  size_t shared = (donor_error && in->tokens <= kRcpTable) ? (size_t)in->tokens * 8 : 0;
+  unsigned grid = (unsigned)(in->n_outer * in->n_inner);
+  switch (in->dtype) {
+    case INQ_F32:
+      k4_statistics_kernel<float><<<grid, threads, shared, stream>>>(ref, sample_stride, saliency, sampled_mean, donor_error, absmax);
+      break;
+    case INQ_F16:
+      k4_statistics_kernel<__half><<<grid, threads, shared, stream>>>(ref, sample_stride, saliency, sampled_mean, donor_error, absmax);
+      break;
+    default:
+      k4_statistics_kernel<__nv_bfloat16><<<grid, threads, shared, stream>>>(ref, sample_stride, saliency, sampled_mean, donor_error, absmax);
+      break;
+  }
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}
+
+extern "C" int inq_select_donors(const float* saliency, const float* donor_error, int64_t rows, int32_t channels,
+                                 int32_t count, int64_t* sources, int64_t* donors, inq_stream_t stream_) {
+  if (!saliency || rows < 0 || channels < 1 || count < 0 || count > channels / 2 || rows >= (1ll << 31)) return INQ_ERR_ARGUMENT;
+  if (channels > kMaxChannels) return INQ_ERR_UNSUPPORTED;
+  if (rows == 0 || count == 0) return INQ_OK;
+  if (!sources || !donors) return INQ_ERR_ARGUMENT;
+  int threads = ((channels + 31) / 32) * 32;
+  size_t shared = (size_t)channels * 12 + kMaxWords * 8 + (size_t)count * 8;
+  select_kernel<<<(unsigned)rows, threads, shared, (cudaStream_t)stream_>>>(saliency, donor_error, channels, count,
+                                                                             (long long*)sources, (long long*)donors);
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}
+
+extern "C" int inq_k4_dequantize(const uint8_t* payload, const float* scales, const void* salient, const void* donors,
+                                 int32_t descriptor_i32, const float* padding, int64_t rows, int32_t tokens,
+                                 int32_t channels, int32_t count, void* out, int32_t out_dtype, inq_stream_t stream_) {
+  if (!payload || !scales || !out || rows < 1 || tokens < 1 || channels < 2 || channels % 2 || count < 0 ||
+      !valid_dtype(out_dtype) || rows >= (1ll << 31))
+    return INQ_ERR_ARGUMENT;
+  if (count && (!salient || !donors || !padding)) return INQ_ERR_ARGUMENT;
+  if (channels > 4096) return INQ_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)rows, (unsigned)((tokens + 15) / 16));
+  size_t shared = (size_t)channels * 12;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  switch (out_dtype) {
+    case INQ_F32:
+      k4_dequantize_kernel<float><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (float*)out);
+      break;
+    case INQ_F16:
+      k4_dequantize_kernel<__half><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (__half*)out);
+      break;
+    default:
+      k4_dequantize_kernel<__nv_bfloat16><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (__nv_bfloat16*)out);
+      break;
+  }
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}
+
+template <typename T>
+static int launch_v_encode(const VParams& p, int cpl, dim3 grid, cudaStream_t stream) {
+  switch (cpl) {
+    case 1: v_encode_kernel<T, 1><<<grid, 256, 0, stream>>>(p); break;
+    case 2: v_encode_kernel<T, 2><<<grid, 256, 0, stream>>>(p); break;
+    case 4: v_encode_kernel<T, 4><<<grid, 256, 0, stream>>>(p); break;
+    case 8: v_encode_kernel<T, 8><<<grid, 256, 0, stream>>>(p); break;
+    default: return INQ_ERR_UNSUPPORTED;
+  }
+  return INQ_OK;
+}
+
+extern "C" int inq_v_encode(const inq_v_encode_args_t* a, int32_t* status, inq_stream_t stream_) {
+  if (!a || !status || !input_ok(a->in)) return INQ_ERR_ARGUMENT;
+  if ((a->bits != 2 && a->bits != 4) || (a->group != 32 && a->group != 64 && a->group != 128)) return INQ_ERR_ARGUMENT;
+  const int C = a->in.channels;
+  if (C % a->group) return INQ_ERR_ARGUMENT;
+  if (!a->payload.base || !a->scales.base || !a->offsets.base) return INQ_ERR_ARGUMENT;
+  if (C % 32 || C > 256) return INQ_ERR_UNSUPPORTED;
+  VParams p;
+  p.in = make_input(a->in);
+  p.bits = a->bits;
+  p.group = a->group;
+  p.payload = make_field(a->payload);
+  p.scales = make_field(a->scales);
+  p.offsets = make_field(a->offsets);
+  p.status = status;
+  dim3 grid((unsigned)(a->in.n_outer * a->in.n_inner), (unsigned)((a->in.tokens + 7) / 8));
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc;
+  switch (a->in.dtype) {
+    case INQ_F32: rc = launch_v_encode<float>(p, C / 32, grid, stream); break;
+    case INQ_F16: rc = launch_v_encode<__half>(p, C / 32, grid, stream); break;
+    default: rc = launch_v_encode<__nv_bfloat16>(p, C / 32, grid, stream); break;
+  }
+  if (rc != INQ_OK) return rc;
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}
+
+extern "C" int inq_v_dequantize(const uint8_t* payload, const void* scales, const void* offsets, int64_t rows,
+                                int32_t tokens, int32_t channels, int32_t bits, int32_t group, void* out,
+                                int32_t out_dtype, inq_stream_t stream_) {
+  if (!payload || !scales || !offsets || !out || rows < 1 || tokens < 1 || (bits != 2 && bits != 4) ||
+      (group != 32 && group != 64 && group != 128) || channels % group || !valid_dtype(out_dtype))
+    return INQ_ERR_ARGUMENT;
+  long long total = rows * (long long)tokens * channels;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  switch (out_dtype) {
+    case INQ_F32:
+      v_dequantize_kernel<float><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (float*)out);
+      break;
+    case INQ_F16:
+      v_dequantize_kernel<__half><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (__half*)out);
+      break;
+    default:
+      v_dequantize_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (__nv_bfloat16*)out);
+      break;
+  }
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}
+
+extern "C" int inq_build_roles(const void* salient, const void* donors, int32_t descriptor_i32, int64_t rows,
+                               int32_t channels, int32_t count, void* roles, int32_t role_bytes, inq_stream_t stream_) {
+  if (!roles || rows < 0 || channels < 1 || count < 0 || (role_bytes != 1 && role_bytes != 2) || rows >= (1ll << 31))
+    return INQ_ERR_ARGUMENT;
+  if (count && (!salient || !donors)) return INQ_ERR_ARGUMENT;
+  if (rows == 0) return INQ_OK;
+  build_roles_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream_>>>(salient, donors, descriptor_i32, channels, count, roles, role_bytes);
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}

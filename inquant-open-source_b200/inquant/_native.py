@@ -1,0 +1,144 @@
+"""ctypes binding of libinquant_b200.so (declarations: include/inquant_b200.h)."""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_int32, c_int64, c_void_p
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_PATH = os.path.join(os.path.dirname(_HERE), "libinquant_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+STATUS_NONFINITE = 1
+STATUS_BAD_INDEX = 2
+STATUS_WAIT_TIMEOUT = 4
+
+OK, ERR_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_CAPACITY = 0, -1, -2, -3, -4
+
+
+class Field(ctypes.Structure):
+    _fields_ = [("base", c_void_p), ("outer_stride", c_int64), ("inner_stride", c_int64)]
+
+
+class Input(ctypes.Structure):
+    _fields_ = [("x", c_void_p), ("dtype", c_int32), ("n_outer", c_int64), ("n_inner", c_int64),
+                ("stride_outer", c_int64), ("stride_inner", c_int64), ("stride_token", c_int64),
+                ("tokens", c_int32), ("channels", c_int32), ("page_ids", c_void_p), ("page_ids_i64", c_int32)]
+
+
+class K4EncodeArgs(ctypes.Structure):
+    _fields_ = [("input", Input), ("sample_stride", c_int32), ("count", c_int32), ("min_error", c_int32),
+                ("payload", Field), ("scales", Field), ("salient", Field), ("donors", Field),
+                ("padding", Field), ("roles", Field), ("descriptor_i32", c_int32), ("role_bytes", c_int32)]
+
+
+class VEncodeArgs(ctypes.Structure):
+    _fields_ = [("input", Input), ("bits", c_int32), ("group", c_int32),
+                ("payload", Field), ("scales", Field), ("offsets", Field)]
+
+
+_lib = None
+
+
+def library() -> ctypes.CDLL:
+    """The shared library; raises loudly when it has not been built (there is no fallback)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIBRARY_PATH):
+            raise ImportError(
+                f"{LIBRARY_PATH} is missing: build it with `python inquant-open-source_b200/build.py` "
+                "(nvcc, sm_100a). The packed-KV path has no Triton, PyTorch or CPU fallback.")
+        lib = ctypes.CDLL(LIBRARY_PATH)
+        lib.inq_last_error.restype = ctypes.c_char_p
+        for name in EXPORTS:
+            function = getattr(lib, name)  # every declared entry point must resolve
+            if name in SIGNATURES:
+                function.argtypes = SIGNATURES[name]
+                function.restype = c_int32
+        _lib = lib
+    return _lib
+
+
+# Every symbol declared in include/inquant_b200.h.
+EXPORTS = (
+    "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
+    "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
+)
+
+
+_P, _I, _L = c_void_p, c_int32, c_int64
+SIGNATURES = {
+    "inq_k4_encode": [_P, _P, _P],
+    "inq_select_donors": [_P, _P, _L, _I, _I, _P, _P, _P],
+    "inq_k4_statistics": [_P, _I, _P, _P, _P, _P, _P],
+    "inq_k4_dequantize": [_P, _P, _P, _P, _I, _P, _L, _I, _I, _I, _P, _I, _P],
+    "inq_v_encode": [_P, _P, _P],
+    "inq_v_dequantize": [_P, _P, _P, _L, _I, _I, _I, _I, _P, _I, _P],
+    "inq_build_roles": [_P, _P, _I, _L, _I, _I, _P, _I, _P],
+}
+
+
+def check(rc: int, what: str) -> None:
+    if rc == OK:
+        return
+    if rc == ERR_CUDA:
+        raise RuntimeError(f"{what}: CUDA error: {library().inq_last_error().decode()}")
+    if rc == ERR_UNSUPPORTED:
+        raise NotImplementedError(f"{what}: size outside what the sm_100a kernels are built for")
+    if rc == ERR_CAPACITY:
+        raise ValueError(f"{what}: exceeds the fixed capacity of this entry point")
+    raise ValueError(f"{what}: invalid argument")
+
+
+def require_cuda(tensor: torch.Tensor, what: str) -> None:
+    if tensor.device.type != "cuda":
+        raise RuntimeError(f"{what} requires CUDA tensors: the B200 build has no CPU path")
+
+
+def stream_pointer(device: torch.device) -> c_void_p:
+    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+_status_words: dict[torch.device, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """One zero-initialised int32 per device that kernels OR failure bits into."""
+    word = _status_words.get(device)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[device] = word
+    return word
+
+
+def take_status(device: torch.device) -> int:
+    """Read and clear the status word (synchronises the current stream)."""
+    word = status_word(device)
+    value = int(word.item())
+    if value:
+        word.zero_()
+    return value
+
+
+def pointer(tensor: torch.Tensor | None) -> c_void_p:
+    return c_void_p(None if tensor is None or tensor.numel() == 0 else tensor.data_ptr())
+
+
+def compact_field(tensor: torch.Tensor | None, n_inner: int) -> Field:
+    """Field descriptor of a contiguous tensor whose two leading axes are (outer, inner)."""
+    if tensor is None or tensor.numel() == 0:
+        return Field(None, 0, 0)
+    row = tensor[0, 0].numel() * tensor.element_size()
+    return Field(tensor.data_ptr(), row * n_inner, row)
+
+
+def make_input(x: torch.Tensor, page_ids: torch.Tensor | None = None) -> Input:
+    """``x`` is [outer, inner, tokens, channels] with unit channel stride (any other strides)."""
+    assert x.ndim == 4 and x.stride(3) == 1
+    return Input(x.data_ptr(), DTYPE_CODE[x.dtype], x.shape[0], x.shape[1], x.stride(0), x.stride(1), x.stride(2),
+                 x.shape[2], x.shape[3], None if page_ids is None else page_ids.data_ptr(),
+                 0 if page_ids is None else int(page_ids.dtype == torch.int64))

@@ -1,0 +1,111 @@
+"""Per-token affine INT2/INT4 value codec: same interface as the reference
+``inquant/value_codec.py``, computed by the sm_100a kernel behind ``inq_v_encode``."""
+from dataclasses import dataclass
+
+import torch
+
+from . import _native as N
+
+
+def _logical_bytes(tensor):
+    return tensor.numel() * tensor.element_size()
+
+
+@dataclass(frozen=True)
+class PackedValues:
+    """Reference ``value_codec.py:12-48``; byte counts are logical (see ``PackedTensor``)."""
+
+    payload: torch.Tensor
+    scales: torch.Tensor
+    offsets: torch.Tensor
+    shape: tuple[int, int, int, int]
+    original_dtype: torch.dtype
+    bits: int
+    group_size: int
+
+    @property
+    def tensors(self):
+        return {"payload": self.payload, "scales": self.scales, "offsets": self.offsets}
+
+    @property
+    def payload_nbytes(self):
+        return _logical_bytes(self.payload)
+
+    @property
+    def nbytes(self):
+        return sum(_logical_bytes(t) for t in self.tensors.values())
+
+    @property
+    def metadata_nbytes(self):
+        return self.nbytes - self.payload_nbytes
+
+    @torch.no_grad()
+    def dequantize(self, dtype=None):
+        dtype = self.original_dtype if dtype is None else dtype
+        if not dtype.is_floating_point:
+            raise ValueError("dequantize dtype must be floating point")
+        if dtype not in N.DTYPE_CODE:
+            raise NotImplementedError("dequantize supports float32, float16 and bfloat16")
+        N.require_cuda(self.payload, "PackedValues.dequantize")
+        batch, heads, tokens, channels = self.shape
+        out = torch.empty(self.shape, dtype=dtype, device=self.payload.device)
+        payload, scales, offsets = self.payload.contiguous(), self.scales.contiguous(), self.offsets.contiguous()
+        rc = N.library().inq_v_dequantize(N.pointer(payload), N.pointer(scales), N.pointer(offsets),
+                                          batch * heads, tokens, channels, self.bits, self.group_size,
+                                          N.pointer(out), N.DTYPE_CODE[dtype], N.stream_pointer(out.device))
+        N.check(rc, "inq_v_dequantize")
+        return out
+
+
+def encode_values_into(x, bits, group_size, payload, scales, offsets, page_ids=None):
+    """Launch the value encoder on ``x`` = [outer, inner, tokens, channels]; no synchronisation."""
+    args = N.VEncodeArgs()
+    args.input = N.make_input(x, page_ids)
+    args.bits, args.group = bits, group_size
+    args.payload, args.scales, args.offsets = payload, scales, offsets
+    rc = N.library().inq_v_encode(N.ctypes.byref(args), N.pointer(N.status_word(x.device)),
+                                  N.stream_pointer(x.device))
+    N.check(rc, "inq_v_encode")
+
+
+@torch.no_grad()
+def quantize_values(x, bits=2, group_size=64):
+    """Reference ``value_codec.py:51-72``."""
+    if type(bits) is not int or bits not in (2, 4):
+        raise ValueError("Value bits must be 2 or 4")
+    if type(group_size) is not int or group_size not in (32, 64, 128):
+        raise ValueError("Value group size must be 32, 64 or 128")
+    if x.ndim != 4 or min(x.shape) < 1 or not x.is_floating_point() or x.shape[-1] % group_size:
+        raise ValueError("Expected nonempty floating [batch, heads, tokens, channels] divisible by group_size")
+    if x.dtype not in N.DTYPE_CODE:
+        raise NotImplementedError("quantize_values supports float32, float16 and bfloat16 inputs")
+    N.require_cuda(x, "quantize_values")
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    batch, heads, tokens, channels = x.shape
+    device = x.device
+    payload = torch.empty((batch, heads, tokens, channels * bits // 8), dtype=torch.uint8, device=device)
+    scales = torch.empty((batch, heads, tokens, channels // group_size), dtype=torch.float16, device=device)
+    offsets = torch.empty_like(scales)
+    encode_values_into(x.detach(), bits, group_size, N.compact_field(payload, heads),
+                       N.compact_field(scales, heads), N.compact_field(offsets, heads))
+    if N.take_status(device) & N.STATUS_NONFINITE:
+        raise ValueError("Values and stored FP16 quantization parameters must be finite")
+    return PackedValues(payload, scales, offsets, tuple(x.shape), x.dtype, bits, group_size)
+
+
+def quantize_value_blocks(tensor, block_count, block_size, bits, group_size):
+    """Reference ``value_codec.py:75-88``: the temporal block axis becomes the batch axis of
+    ONE kernel launch; the per-block results are views of that launch's output arena."""
+    if not block_count:
+        return []
+    if block_count == 1:
+        return [quantize_values(tensor[:, :, :block_size], bits, group_size)]
+    _, heads, _, channels = tensor.shape
+    blocked = tensor[0, :, :block_count * block_size].reshape(
+        heads, block_count, block_size, channels).permute(1, 0, 2, 3)
+    packed = quantize_values(blocked, bits, group_size)
+    return [PackedValues(
+        **{name: value[index:index + 1] for name, value in packed.tensors.items()},
+        shape=(1, heads, block_size, channels), original_dtype=tensor.dtype, bits=bits, group_size=group_size,
+    ) for index in range(block_count)]
