@@ -132,6 +132,80 @@ int inq_v_dequantize(const uint8_t* payload, const void* scales, const void* off
 int inq_build_roles(const void* salient, const void* donors, int32_t descriptor_i32, int64_t rows,
                     int32_t channels, int32_t count, void* roles, int32_t role_bytes, inq_stream_t stream);
 
+/* ---------------------------------------------------------------- decode attention
+ * One decode step of single-query grouped-query attention over packed K4/V2 history plus
+ * the exact sink and recent tail, for one sequence (a layer of a request) or a batch of
+ * them in ONE launch; split-KV partials are merged inside the same launch.
+ * Replaces: triton_attention.py:67-181 `_attention_partials` + `_reduce_partials` as
+ * launched by `PackedDecodeState.decode` (:317-388), and inquant_vllm/kernels.py:8-88
+ * `_paged_partials` / `paged_decode`.
+ *
+ * layout 0 ("table", triton_attention.py:277-295): block i is reached through six device
+ *   pointers table[i][0..5] = key payload, key scales, key padding, value payload, value
+ *   scales, value offsets, each a compact [kv_heads, ...] tensor; roles is the int8 map
+ *   [n_blocks, kv_heads, 128] of triton_attention.py:301-309.
+ * layout 1 ("paged", layout.py:18-42): block i is page page_table[i] of `pool`;
+ *   page_offsets = byte offsets of key_scales, key_map, key_padding, value_payload,
+ *   value_scales, value_offsets inside a page.
+ * Requirements: head_dim 128, V2 with group 64, query dtype fp16 or bf16 (the dense sink
+ * and tail share it), dense rows 16-byte aligned.  Masks: packed tokens whose position in
+ * the sequence (block*block_tokens + t) is below first_visible are skipped (the exact sink
+ * replaces them, kernels.py:41); the first tail_skip tail tokens are skipped (kernels.py:53).
+ */
+typedef struct {
+  const void* query;             /* [q_heads, 128], head stride query_head_stride elements */
+  void* output;                  /* [q_heads, 128] contiguous, query dtype */
+  int64_t query_head_stride;
+  const int64_t* table;          /* layout 0 */
+  const int8_t* roles;           /* layout 0 */
+  const uint8_t* pool;           /* layout 1 */
+  const int32_t* page_table;     /* layout 1 */
+  const void* sink_key; const void* sink_value; const void* tail_key; const void* tail_value;
+  int64_t sink_key_stride_h, sink_key_stride_t, sink_value_stride_h, sink_value_stride_t;   /* elements */
+  int64_t tail_key_stride_h, tail_key_stride_t, tail_value_stride_h, tail_value_stride_t;
+  int32_t n_blocks, sink_tokens, tail_tokens, first_visible, tail_skip;
+  const int32_t* tail_tokens_device; /* optional: overrides tail_tokens, read on the device */
+} inq_decode_seq_t;
+
+typedef struct {
+  int32_t n_seq;
+  const inq_decode_seq_t* seqs_device; /* [n_seq] in device memory, or NULL when n_seq == 1 */
+  const inq_decode_seq_t* seq_host;    /* host: the single sequence when seqs_device is NULL */
+  int32_t kv_heads, q_per_kv, block_tokens, n_pad; /* n_pad = salient channels per head */
+  int32_t layout, dtype;
+  float scale;
+  int64_t page_bytes;
+  int64_t page_offsets[6];
+  int32_t n_parts;   /* split of every (sequence, KV head): see inq_decode_plan_parts */
+  float* partials;   /* scratch: inq_decode_workspace_floats(...) floats, contents undefined */
+  int32_t* counters; /* scratch: n_seq * kv_heads * ceil(q_per_kv/8) ints, ZERO on entry, left zero */
+  int32_t* status;   /* device status word */
+} inq_decode_args_t;
+int inq_decode_attention(const inq_decode_args_t* args /* host */, inq_stream_t stream);
+/* Number of parts that fills the device for this batch (max_slices = 16-token slices of the
+ * longest sequence), and the scratch size that goes with it. */
+int inq_decode_plan_parts(int32_t n_seq, int32_t kv_heads, int32_t q_per_kv, int64_t max_slices);
+int64_t inq_decode_workspace_floats(int32_t n_seq, int32_t kv_heads, int32_t q_per_kv, int32_t n_parts);
+
+/* ---------------------------------------------------------------- incremental append
+ * Writes the key and value rows of ONE new token (all KV heads) at `tail_position` of the
+ * exact recent tail and, while the attention sink is still filling (sink_position >= 0),
+ * into the sink as well.  With `tail_counter` the position is read from that device int
+ * and incremented by the kernel, so a decode loop needs no host round trip.
+ * Replaces: the per-token `torch.cat` + `clone` of cache.py:256-259, 271-299 and the tail
+ * writes of backend.py:158-163.  Strides and row_bytes are BYTES, multiples of 16. */
+typedef struct {
+  const void* key; const void* value; int64_t src_stride_h;  /* new token rows, [heads, row] */
+  void* tail_key; void* tail_value; int64_t tail_stride_h, tail_stride_t;
+  int32_t tail_position, tail_capacity;
+  int32_t* tail_counter;          /* optional device position, overrides tail_position */
+  void* sink_key; void* sink_value; int64_t sink_stride_h, sink_stride_t;
+  int32_t sink_position;          /* < 0: sink already full */
+  int32_t heads, row_bytes;
+  int32_t* status;
+} inq_append_args_t;
+int inq_append_token(const inq_append_args_t* args /* host */, inq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -15,6 +15,8 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relax
 SOURCES = {
     "lib.cu": [],
     "codec.cu": ["-fmad=false"],
+    "decode.cu": [],
+    "append.cu": [],
 }
 
 

@@ -1,0 +1,729 @@
+// Single-query grouped-query attention over the packed K4/V2 history plus the exact
+// (bf16/fp16) sink and recent tail, with the split-KV partials merged by the last CTA of
+// every (sequence, KV head) -- one launch per decode step, for one layer or for a batch
+// of (request, layer) sequences.
+//
+// Work decomposition.  A (sequence, KV head) owns `slices` of 16 tokens: packed slices of
+// every sealed block first, then the dense sink and tail slices (weighted 4x, they carry
+// ~5x the bytes).  blockIdx.x cuts that list into `n_parts` contiguous ranges, a CTA's four
+// warps cut their range again, and every warp streams its slices on its own:
+//
+//   * staging: each lane issues 16-byte cp.async copies of the slice's K nibbles (1 KB),
+//     V codes (512 B) and V scale/offset pairs (128 B) into a per-warp ring in shared
+//     memory, four slices deep, so ~5 KB per warp are in flight without holding registers;
+//   * dequantisation never materialises K or V.  The descriptor-guided K decode is linear
+//     in the stored nibbles, so per block it is folded into the query:
+//         score = sum_c w_c * nibble_c + const,
+//     w_c = q_c s_c for a normal channel, 16 q_s s_s for a salient channel's own slot and
+//     q_s s_s for the donor slot that carries the salient channel's low nibble; const holds
+//     the -8 / -128 biases and the donors' padding values.  Nibbles are fed to the tensor
+//     cores as fp16 SUBNORMALS: a nibble masked in place at bit 0 or 4 of a 16-bit lane is
+//     the exact value nibble * 2^-24 (or * 2^-20), so unpacking costs one AND per two
+//     elements and no integer-to-float conversion.  V works the same way with 2-bit codes
+//     at bit 0..8, the per-token group scale folded into the probabilities and the group
+//     offsets accumulated on the side;
+//   * contractions use mma.sync.m16n8k16 with the 16 tokens as M and the (up to 8) query
+//     heads of the KV head as N, so one pass serves the whole GQA group.
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace inq {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 4;
+constexpr int kStageK = 1024, kStageV = 512, kStageP = 128;
+constexpr int kStageBytes = kStageK + kStageV + kStageP;
+constexpr int kRecordStride = 132;                  // floats per query head: acc[128], m, l, pad
+constexpr int kRecordFloats = 8 * kRecordStride;    // one partial record (8 query heads)
+constexpr int kQChunk = 36;                         // padded 32-float chunk of the staged query
+constexpr float kNegBig = -1.0e30f;
+
+struct SeqDesc {
+  const void* q;
+  void* out;
+  long long q_stride_h;
+  const long long* table;        // table layout: [n_blocks][6] device pointers
+  const signed char* roles;      // table layout: int8 [n_blocks][H][128]
+  const unsigned char* pool;     // paged layout
+  const int* page_table;         // paged layout: physical page of logical page i
+  const void* sink_k; const void* sink_v; const void* tail_k; const void* tail_v;
+  long long sink_k_sh, sink_k_st, sink_v_sh, sink_v_st;
+  long long tail_k_sh, tail_k_st, tail_v_sh, tail_v_st;
+  int n_blocks, sink_tokens, tail_tokens, first_visible, tail_skip;
+  const int* tail_tokens_dev;
+};
+static_assert(sizeof(SeqDesc) == sizeof(inq_decode_seq_t), "SeqDesc must mirror inq_decode_seq_t");
+
+struct DecodeParams {
+  const SeqDesc* seqs;
+  SeqDesc one;
+  int n_seq, H, G, T, n_pad, n_parts;
+  float scale_log2e;
+  long long page_bytes;
+  int off_ks, off_km, off_kp, off_vp, off_vs, off_vo;
+  float* partials;
+  int* counters;
+  int* status;
+};
+
+struct BlockPtrs {
+  const unsigned char *kp, *ks, *kr, *kpad, *vp, *vs, *vo;
+};
+
+// ------------------------------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ void mma_f16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                        unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                         unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <typename QT>
+__device__ __forceinline__ void mma_qt(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                       unsigned b1) {
+  if (sizeof(QT) == 2 && std::is_same<QT, __half>::value)
+    mma_f16(d, a0, a1, a2, a3, b0, b1);
+  else
+    mma_bf16(d, a0, a1, a2, a3, b0, b1);
+}
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned x) {
+  unsigned y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ unsigned pack_half2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&h);
+}
+template <typename QT>
+__device__ __forceinline__ unsigned pack_qt2(float lo, float hi) {
+  if (std::is_same<QT, __half>::value) return pack_half2(lo, hi);
+  __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&b);
+}
+__device__ __forceinline__ float2 half2_bits_to_float2(unsigned bits) {
+  return __half22float2(*reinterpret_cast<__half2*>(&bits));
+}
+
+// ------------------------------------------------------------------------------------------ block lookup
+template <int MODE>
+__device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const long long* table,
+                                                  const signed char* roles, const unsigned char* pool,
+                                                  const int* page_table, int b, int h) {
+  BlockPtrs out;
+  if (MODE == 0) {
+    const long long* row = table + (long long)b * 6;
+    const long long T = P.T;
+    out.kp = (const unsigned char*)row[0] + (long long)h * T * 64;
+    out.ks = (const unsigned char*)row[1] + (long long)h * 512;
+    out.kpad = (const unsigned char*)row[2] + (long long)h * P.n_pad * 4;
+    out.vp = (const unsigned char*)row[3] + (long long)h * T * 32;
+    out.vs = (const unsigned char*)row[4] + (long long)h * T * 4;
+    out.vo = (const unsigned char*)row[5] + (long long)h * T * 4;
+    out.kr = (const unsigned char*)roles + ((long long)b * P.H + h) * 128;
+  } else {
+    const unsigned char* page = pool + (long long)page_table[b] * P.page_bytes;
+    const long long T = P.T;
+    out.kp = page + (long long)h * T * 64;
+    out.ks = page + P.off_ks + (long long)h * 512;
+    out.kr = page + P.off_km + (long long)h * 256;
+    out.kpad = page + P.off_kp + (long long)h * 64;
+    out.vp = page + P.off_vp + (long long)h * T * 32;
+    out.vs = page + P.off_vs + (long long)h * T * 4;
+    out.vo = page + P.off_vo + (long long)h * T * 4;
+  }
+  return out;
+}
+
+// Issue the asynchronous copies of one packed slice (16 tokens from `tok0`) into a stage.
+__device__ __forceinline__ void stage_slice(unsigned char* stage, const BlockPtrs& B, int tok0, int T, int lane) {
+  const int r = lane >> 2, j = lane & 3;
+  const int last = T - 1;
+  const int t_lo = min(tok0 + r, last), t_hi = min(tok0 + r + 8, last);
+  cp_async16(stage + lane * 16, B.kp + (long long)t_lo * 64 + j * 16);
+  cp_async16(stage + 512 + lane * 16, B.kp + (long long)t_hi * 64 + j * 16);
+  {
+    const int t = lane >> 1, half = lane & 1;
+    const int tv = min(tok0 + t, last);
+    // swap the two 16-byte halves of tokens 4..7 and 12..15: the later word reads of tokens
+    // 2j, 2j+1, 2j+8, 2j+9 then fall into distinct banks
+    cp_async16(stage + kStageK + (t * 2 + (half ^ ((t >> 2) & 1))) * 16, B.vp + (long long)tv * 32 + half * 16);
+  }
+  {
+    const int t = lane & 15;
+    const int tp = min(tok0 + t, last);
+    const unsigned char* src = (lane < 16 ? B.vs : B.vo) + (long long)tp * 4;
+    cp_async4(stage + kStageK + kStageV + (lane < 16 ? 0 : 64) + t * 4, src);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ the kernel
+template <int MODE, typename QT>
+__global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams P) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  float* qs = (float*)smem;                                             // 8 heads x 4 chunks x kQChunk
+  unsigned char* warp_base = smem + 8 * 4 * kQChunk * 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = lane >> 2, j = lane & 3;
+  float* wf = (float*)(warp_base + warp * 1152);                        // slot factor per channel
+  float* wk0 = wf + 128;                                                // additive constant per channel
+  unsigned char* wqi = (unsigned char*)(wk0 + 128);                     // query channel multiplying each slot
+  unsigned char* ring = warp_base + kWarps * 1152 + warp * (kStages * kStageBytes);
+  __shared__ int s_is_last;
+
+  const int gtiles = (P.G + 7) >> 3;
+  const int h = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
+  const int seq = blockIdx.z;
+  // Descriptor fields are fetched where they are used: from kernel parameters for a single
+  // sequence, from the device array for a batch.
+  const SeqDesc* const Dp = P.seqs ? P.seqs + seq : nullptr;
+#define SEQ(field) (Dp ? Dp->field : P.one.field)
+  const long long* const d_table = SEQ(table);
+  const signed char* const d_roles = SEQ(roles);
+  const unsigned char* const d_pool = SEQ(pool);
+  const int* const d_pages = SEQ(page_table);
+  const int first_visible = SEQ(first_visible);
+  const int g_valid = min(8, P.G - gt * 8);
+  const long long q_head0 = (long long)h * P.G + gt * 8;
+  const QT* qptr = (const QT*)SEQ(q);
+  const long long q_stride = SEQ(q_stride_h);
+
+  // query, pre-multiplied by softmax_scale * log2(e), chunked so that lanes (head, chunk)
+  // read distinct banks
+  for (int idx = threadIdx.x; idx < 8 * 128; idx += kThreads) {
+    int g = idx >> 7, c = idx & 127;
+    float v = g < g_valid ? to_float<QT>(qptr[(q_head0 + g) * q_stride + c]) * P.scale_log2e : 0.f;
+    qs[(g * 4 + (c >> 5)) * kQChunk + (c & 31)] = v;
+  }
+  __syncthreads();
+
+  const int T = P.T;
+  const int spb = (T + 15) >> 4;
+  const int n_blocks = SEQ(n_blocks);
+  const int sink_tokens = SEQ(sink_tokens);
+  const int* const tail_dev = SEQ(tail_tokens_dev);
+  const int tail_tokens = tail_dev ? *tail_dev : SEQ(tail_tokens);
+  const long long n_packed = (long long)n_blocks * spb;
+  const int sink_slices = (sink_tokens + 15) >> 4, tail_slices = (tail_tokens + 15) >> 4;
+  const long long total = n_packed + 4ll * (sink_slices + tail_slices);
+  const long long cta_a = total * blockIdx.x / P.n_parts, cta_b = total * (blockIdx.x + 1) / P.n_parts;
+  const long long a = cta_a + (cta_b - cta_a) * warp / kWarps, b = cta_a + (cta_b - cta_a) * (warp + 1) / kWarps;
+  const long long pa = min(a, n_packed), pb = min(b, n_packed);
+  const int da = (int)((max(a, n_packed) - n_packed + 3) >> 2), db = (int)((max(b, n_packed) - n_packed + 3) >> 2);
+
+  float m_run[2] = {kNegBig, kNegBig}, l_run[2] = {0.f, 0.f};
+  float acc[8][4];
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[mt][k] = 0.f;
+  float oacc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+
+  // ---------------------------------------------------------------- packed history
+  if (pb > pa) {
+    const int n_my = (int)(pb - pa);
+    int pf_block = (int)(pa / spb), pf_slice = (int)(pa % spb);   // prefetch cursor
+    BlockPtrs pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
+    int issued = 0;
+    auto issue = [&]() {
+      if (issued < n_my) {
+        stage_slice(ring + (issued % kStages) * kStageBytes, pf_ptrs, pf_slice * 16, T, lane);
+        ++issued;
+        if (++pf_slice == spb) {
+          pf_slice = 0;
+          ++pf_block;
+          if (issued < n_my) pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
+        }
+      }
+      cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) issue();
+
+    int cur_block = (int)(pa / spb), cur_slice = (int)(pa % spb);
+    bool need_weights = true;
+    unsigned wfrag[8][2];
+    float alpha[2] = {0.f, 0.f}, beta[2] = {0.f, 0.f};
+    const unsigned vsel = (r & 1) ? 0x7632u : 0x5410u;
+
+    for (int it = 0; it < n_my; ++it) {
+      cp_async_wait<kStages - 2>();
+      __syncwarp();
+      issue();
+
+      if (need_weights) {
+        // ---- fold this block's descriptor, scales and padding into the query
+        BlockPtrs cb = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, cur_block, h);
+        const float4 sc = *(const float4*)(cb.ks + lane * 16);
+        int role[4];
+        if (MODE == 0) {
+          unsigned bits = *(const unsigned*)(cb.kr + lane * 4);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) role[i] = (int)(signed char)((bits >> (8 * i)) & 0xff);
+        } else {
+          uint2 bits = *(const uint2*)(cb.kr + lane * 8);
+          role[0] = (int)(short)(bits.x & 0xffff);
+          role[1] = (int)(short)(bits.x >> 16);
+          role[2] = (int)(short)(bits.y & 0xffff);
+          role[3] = (int)(short)(bits.y >> 16);
+        }
+        const float scv[4] = {sc.x, sc.y, sc.z, sc.w};
+        bool bad = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = lane * 4 + i;
+          int ro = role[i];
+          if (ro > 127 || ro < -2 - (P.n_pad - 1) || (ro <= -2 && P.n_pad == 0)) {
+            bad = true;
+            ro = -1;
+          }
+          if (ro == -1) {
+            wf[c] = scv[i];
+            wqi[c] = (unsigned char)c;
+            wk0[c] = -8.f * scv[i];
+          } else if (ro >= 0) {
+            wf[c] = 16.f * scv[i];
+            wqi[c] = (unsigned char)c;
+            wk0[c] = -128.f * scv[i];
+            wf[ro] = scv[i];              // the donor slot carries this channel's low nibble
+            wqi[ro] = (unsigned char)c;
+          } else {
+            wk0[c] = ((const float*)cb.kpad)[-ro - 2];
+          }
+        }
+        if (bad) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
+        __syncwarp();
+        // thread (head r, chunk j) owns the 32 channels 32j..32j+31 of query head r
+        float w[32];
+        float cpart = 0.f, wmax = 0.f;
+        const float* qown = qs + (r * 4 + j) * kQChunk;
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 f4 = *(const float4*)(wf + 32 * j + 4 * i4);
+          const float4 k4 = *(const float4*)(wk0 + 32 * j + 4 * i4);
+          const float4 q4 = *(const float4*)(qown + 4 * i4);
+          const unsigned qi4 = *(const unsigned*)(wqi + 32 * j + 4 * i4);
+          const float fv[4] = {f4.x, f4.y, f4.z, f4.w};
+          const float kv[4] = {k4.x, k4.y, k4.z, k4.w};
+          const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = 32 * j + 4 * i4 + e;
+            const int qc = (qi4 >> (8 * e)) & 0xff;
+            const float qsel = qc == c ? qv[e] : qs[(r * 4 + (qc >> 5)) * kQChunk + (qc & 31)];
+            w[4 * i4 + e] = qsel * fv[e];
+            wmax = fmaxf(wmax, fabsf(w[4 * i4 + e]));
+            cpart = fmaf(qv[e], kv[e], cpart);
+          }
+        }
+        cpart += __shfl_xor_sync(0xffffffffu, cpart, 1);
+        cpart += __shfl_xor_sync(0xffffffffu, cpart, 2);
+        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 1));
+        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 2));
+        // scale the row into [2^13, 2^14) so that fp16 neither overflows nor loses small weights
+        int ex = (int)((__float_as_uint(wmax) >> 23) & 0xff) - 127;
+        ex = max(-100, min(100, ex));
+        if (wmax == 0.f) ex = 13;
+        const float up = __uint_as_float((unsigned)(127 + 13 - ex) << 23);
+        const float inv = __uint_as_float((unsigned)(127 + ex + 11) << 23);   // 2^24 / up
+        const float up16 = up * 0.0625f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          const int base = 8 * (s >> 1) + 2 * (s & 1);
+          wfrag[s][0] = pack_half2(w[base] * up, w[base + 4] * up);
+          wfrag[s][1] = pack_half2(w[base + 1] * up16, w[base + 5] * up16);
+        }
+        // score columns of this thread are query heads 2j and 2j+1
+        alpha[0] = __shfl_sync(0xffffffffu, inv, (2 * j) * 4);
+        alpha[1] = __shfl_sync(0xffffffffu, inv, (2 * j + 1) * 4);
+        beta[0] = __shfl_sync(0xffffffffu, cpart, (2 * j) * 4);
+        beta[1] = __shfl_sync(0xffffffffu, cpart, (2 * j + 1) * 4);
+        need_weights = false;
+      }
+
+      const unsigned char* stage = ring + (it % kStages) * kStageBytes;
+      // ---- scores = K tile (16 tokens x 128 slots) * folded query
+      float S[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const uint4 kx = *(const uint4*)(stage + lane * 16);
+        const uint4 ky = *(const uint4*)(stage + 512 + lane * 16);
+        const unsigned xs[4] = {kx.x, kx.y, kx.z, kx.w}, ys[4] = {ky.x, ky.y, ky.z, ky.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          unsigned x = xs[i], y = ys[i];
+          mma_f16(S, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, wfrag[2 * i][0], wfrag[2 * i][1]);
+          x >>= 8;
+          y >>= 8;
+          mma_f16(S, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, wfrag[2 * i + 1][0],
+                  wfrag[2 * i + 1][1]);
+        }
+      }
+      float s2[4] = {fmaf(S[0], alpha[0], beta[0]), fmaf(S[1], alpha[1], beta[1]), fmaf(S[2], alpha[0], beta[0]),
+                     fmaf(S[3], alpha[1], beta[1])};
+      {
+        const int tok0 = cur_slice * 16;
+        const long long g0 = (long long)cur_block * T + tok0;
+        if (tok0 + 16 > T || g0 < first_visible) {
+          const bool lo_ok = tok0 + r < T && g0 + r >= first_visible;
+          const bool hi_ok = tok0 + r + 8 < T && g0 + r + 8 >= first_visible;
+          if (!lo_ok) s2[0] = s2[1] = -INFINITY;
+          if (!hi_ok) s2[2] = s2[3] = -INFINITY;
+        }
+      }
+      // ---- online softmax (base 2)
+      float mx0 = fmaxf(s2[0], s2[2]), mx1 = fmaxf(s2[1], s2[3]);
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+      }
+      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+      if (__any_sync(0xffffffffu, mn0 > m_run[0] || mn1 > m_run[1])) {
+        const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
+        l_run[0] *= a0;
+        l_run[1] *= a1;
+        oacc[0][0] *= a0; oacc[1][0] *= a0;
+        oacc[0][1] *= a1; oacc[1][1] *= a1;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+          acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
+        }
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+      }
+      const float p0 = fast_exp2(s2[0] - m_run[0]), p1 = fast_exp2(s2[1] - m_run[1]);
+      const float p2 = fast_exp2(s2[2] - m_run[0]), p3 = fast_exp2(s2[3] - m_run[1]);
+      l_run[0] += p0 + p2;
+      l_run[1] += p1 + p3;
+      // ---- values: probabilities times the per-token group scale, codes as fp16 subnormals
+      const unsigned char* sp = stage + kStageK + kStageV;
+      const float2 vs_lo = half2_bits_to_float2(*(const unsigned*)(sp + 4 * r));
+      const float2 vs_hi = half2_bits_to_float2(*(const unsigned*)(sp + 4 * (r + 8)));
+      const float2 vo_lo = half2_bits_to_float2(*(const unsigned*)(sp + 64 + 4 * r));
+      const float2 vo_hi = half2_bits_to_float2(*(const unsigned*)(sp + 64 + 4 * (r + 8)));
+      oacc[0][0] += p0 * vo_lo.x + p2 * vo_hi.x;
+      oacc[0][1] += p1 * vo_lo.x + p3 * vo_hi.x;
+      oacc[1][0] += p0 * vo_lo.y + p2 * vo_hi.y;
+      oacc[1][1] += p1 * vo_lo.y + p3 * vo_hi.y;
+      const unsigned char* sv = stage + kStageK;
+      const int tA = 2 * j, tB = 2 * j + 1, tC = 2 * j + 8, tD = 2 * j + 9;
+#pragma unroll
+      for (int gr = 0; gr < 2; ++gr) {
+        const float sl = gr ? vs_lo.y : vs_lo.x, sh = gr ? vs_hi.y : vs_hi.x;
+        const unsigned b0 = movmatrix_trans(pack_half2(p0 * sl, p1 * sl));
+        const unsigned b1 = movmatrix_trans(pack_half2(p2 * sh, p3 * sh));
+        const int word = (r >> 1) * 4;
+        const unsigned wA = *(const unsigned*)(sv + (tA * 2 + (gr ^ ((tA >> 2) & 1))) * 16 + word);
+        const unsigned wB = *(const unsigned*)(sv + (tB * 2 + (gr ^ ((tB >> 2) & 1))) * 16 + word);
+        const unsigned wC = *(const unsigned*)(sv + (tC * 2 + (gr ^ ((tC >> 2) & 1))) * 16 + word);
+        const unsigned wD = *(const unsigned*)(sv + (tD * 2 + (gr ^ ((tD >> 2) & 1))) * 16 + word);
+        const unsigned M0 = __byte_perm(wA, wB, vsel), M1 = __byte_perm(wC, wD, vsel);
+        const unsigned N0 = M0 >> 10, N1 = M1 >> 10;
+        mma_f16(acc[gr * 4 + 0], M0 & 0x00030003u, M0 & 0x000C000Cu, M1 & 0x00030003u, M1 & 0x000C000Cu, b0, b1);
+        mma_f16(acc[gr * 4 + 1], M0 & 0x00300030u, M0 & 0x00C000C0u, M1 & 0x00300030u, M1 & 0x00C000C0u, b0, b1);
+        mma_f16(acc[gr * 4 + 2], M0 & 0x03000300u, N0 & 0x00030003u, M1 & 0x03000300u, N1 & 0x00030003u, b0, b1);
+        mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1);
+      }
+      if (++cur_slice == spb) {
+        cur_slice = 0;
+        ++cur_block;
+        need_weights = true;
+      }
+    }
+    cp_async_wait<0>();
+    // a code at bit offset o of its 16-bit lane was multiplied as code * 2^(o-24)
+    const float fx[4] = {16777216.f, 1048576.f, 65536.f, 4194304.f};   // offsets 0, 4, 8, 2
+    const float fy[4] = {4194304.f, 262144.f, 16777216.f, 1048576.f};  // offsets 2, 6, 0, 4
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      acc[mt][0] *= fx[mt & 3];
+      acc[mt][1] *= fx[mt & 3];
+      acc[mt][2] *= fy[mt & 3];
+      acc[mt][3] *= fy[mt & 3];
+    }
+  }
+
+  // ---------------------------------------------------------------- exact sink and tail
+  if (db > da) {
+    unsigned qf[16];
+    {
+      const bool live = r < g_valid;
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (live) v = *(const uint4*)(qptr + (q_head0 + r) * q_stride + (4 * m + j) * 8);
+        qf[4 * m + 0] = v.x; qf[4 * m + 1] = v.y; qf[4 * m + 2] = v.z; qf[4 * m + 3] = v.w;
+      }
+    }
+    for (int ds = da; ds < db; ++ds) {
+      const bool is_sink = ds < sink_slices;
+      const int tok0 = (is_sink ? ds : ds - sink_slices) * 16;
+      const int count = is_sink ? sink_tokens : tail_tokens;
+      const int skip = is_sink ? 0 : SEQ(tail_skip);
+      const QT* kb = (const QT*)(is_sink ? SEQ(sink_k) : SEQ(tail_k)) + (long long)h * (is_sink ? SEQ(sink_k_sh) : SEQ(tail_k_sh));
+      const QT* vb = (const QT*)(is_sink ? SEQ(sink_v) : SEQ(tail_v)) + (long long)h * (is_sink ? SEQ(sink_v_sh) : SEQ(tail_v_sh));
+      const long long kst = is_sink ? SEQ(sink_k_st) : SEQ(tail_k_st), vst = is_sink ? SEQ(sink_v_st) : SEQ(tail_v_st);
+      const int last = count - 1;
+      float S[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const QT* k_lo = kb + (long long)min(tok0 + r, last) * kst;
+        const QT* k_hi = kb + (long long)min(tok0 + r + 8, last) * kst;
+        uint4 x[4], y[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          x[m] = *(const uint4*)(k_lo + (4 * m + j) * 8);
+          y[m] = *(const uint4*)(k_hi + (4 * m + j) * 8);
+        }
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          mma_qt<QT>(S, x[m].x, y[m].x, x[m].y, y[m].y, qf[4 * m + 0], qf[4 * m + 1]);
+          mma_qt<QT>(S, x[m].z, y[m].z, x[m].w, y[m].w, qf[4 * m + 2], qf[4 * m + 3]);
+        }
+      }
+      float s2[4] = {S[0] * P.scale_log2e, S[1] * P.scale_log2e, S[2] * P.scale_log2e, S[3] * P.scale_log2e};
+      {
+        const bool lo_ok = tok0 + r < count && tok0 + r >= skip;
+        const bool hi_ok = tok0 + r + 8 < count && tok0 + r + 8 >= skip;
+        if (!lo_ok) s2[0] = s2[1] = -INFINITY;
+        if (!hi_ok) s2[2] = s2[3] = -INFINITY;
+      }
+      float mx0 = fmaxf(s2[0], s2[2]), mx1 = fmaxf(s2[1], s2[3]);
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+      }
+      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+      if (__any_sync(0xffffffffu, mn0 > m_run[0] || mn1 > m_run[1])) {
+        const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
+        l_run[0] *= a0;
+        l_run[1] *= a1;
+        oacc[0][0] *= a0; oacc[1][0] *= a0;
+        oacc[0][1] *= a1; oacc[1][1] *= a1;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+          acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
+        }
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+      }
+      const float p0 = fast_exp2(s2[0] - m_run[0]), p1 = fast_exp2(s2[1] - m_run[1]);
+      const float p2 = fast_exp2(s2[2] - m_run[0]), p3 = fast_exp2(s2[3] - m_run[1]);
+      l_run[0] += p0 + p2;
+      l_run[1] += p1 + p3;
+      const unsigned b0 = movmatrix_trans(pack_qt2<QT>(p0, p1));
+      const unsigned b1 = movmatrix_trans(pack_qt2<QT>(p2, p3));
+      const QT* vA = vb + (long long)min(tok0 + 2 * j, last) * vst;
+      const QT* vB = vb + (long long)min(tok0 + 2 * j + 1, last) * vst;
+      const QT* vC = vb + (long long)min(tok0 + 2 * j + 8, last) * vst;
+      const QT* vD = vb + (long long)min(tok0 + 2 * j + 9, last) * vst;
+#pragma unroll
+      for (int gr = 0; gr < 2; ++gr) {
+        const int ch = 64 * gr + 8 * r;
+        const uint4 A = *(const uint4*)(vA + ch), Bv = *(const uint4*)(vB + ch);
+        const uint4 C = *(const uint4*)(vC + ch), Dv = *(const uint4*)(vD + ch);
+        const unsigned av[4] = {A.x, A.y, A.z, A.w}, bv[4] = {Bv.x, Bv.y, Bv.z, Bv.w};
+        const unsigned cv[4] = {C.x, C.y, C.z, C.w}, dv[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          mma_qt<QT>(acc[gr * 4 + q], __byte_perm(av[q], bv[q], 0x5410u), __byte_perm(av[q], bv[q], 0x7632u),
+                     __byte_perm(cv[q], dv[q], 0x5410u), __byte_perm(cv[q], dv[q], 0x7632u), b0, b1);
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- warp -> CTA -> global partial
+#pragma unroll
+  for (int off = 4; off < 32; off <<= 1) {
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], off);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], off);
+#pragma unroll
+    for (int gr = 0; gr < 2; ++gr) {
+      oacc[gr][0] += __shfl_xor_sync(0xffffffffu, oacc[gr][0], off);
+      oacc[gr][1] += __shfl_xor_sync(0xffffffffu, oacc[gr][1], off);
+    }
+  }
+  __syncthreads();   // every warp is done with its ring and weight scratch
+  float* wout = (float*)(warp_base + kWarps * 1152 + warp * (kStages * kStageBytes));   // [8][132]
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt) {
+    const int gr = mt >> 2, q = mt & 3;
+    const int ch = 64 * gr + 8 * r + 2 * q;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int g = 2 * j + e;
+      *(float2*)(wout + g * kRecordStride + ch) = make_float2(acc[mt][e] + oacc[gr][e], acc[mt][2 + e] + oacc[gr][e]);
+    }
+  }
+  if (r == 0) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      wout[(2 * j + e) * kRecordStride + 128] = m_run[e];
+      wout[(2 * j + e) * kRecordStride + 129] = l_run[e];
+    }
+  }
+  __syncthreads();
+  const long long slot = ((long long)seq * gridDim.y + blockIdx.y);
+  float* record = P.partials + (slot * P.n_parts + blockIdx.x) * kRecordFloats;
+  {
+    const int c = threadIdx.x;   // one channel per thread
+    const float* w0 = (const float*)(warp_base + kWarps * 1152);
+    const int wstride = kStages * kStageBytes / 4;
+    for (int g = 0; g < g_valid; ++g) {
+      float mw[kWarps], top = kNegBig;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        mw[w] = w0[w * wstride + g * kRecordStride + 128];
+        top = fmaxf(top, mw[w]);
+      }
+      float o = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float wt = fast_exp2(mw[w] - top);
+        o = fmaf(w0[w * wstride + g * kRecordStride + c], wt, o);
+        l = fmaf(w0[w * wstride + g * kRecordStride + 129], wt, l);
+      }
+      record[g * kRecordStride + c] = o;
+      if (c == 0) {
+        record[g * kRecordStride + 128] = top;
+        record[g * kRecordStride + 129] = l;
+      }
+    }
+  }
+  // ---------------------------------------------------------------- last CTA merges
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(P.counters + slot, 1);
+    s_is_last = (old == P.n_parts - 1);
+    if (s_is_last) P.counters[slot] = 0;   // scratch is left zeroed for the next launch
+  }
+  __syncthreads();
+  if (!s_is_last) return;
+  __threadfence();
+  {
+    const int c = threadIdx.x;
+    const float* base = P.partials + slot * P.n_parts * kRecordFloats;
+    QT* out = (QT*)SEQ(out);
+    for (int g = 0; g < g_valid; ++g) {
+      float top = kNegBig;
+      for (int p = 0; p < P.n_parts; ++p) top = fmaxf(top, __ldcg(base + (long long)p * kRecordFloats + g * kRecordStride + 128));
+      float o = 0.f, l = 0.f;
+      for (int p = 0; p < P.n_parts; ++p) {
+        const float* rec = base + (long long)p * kRecordFloats + g * kRecordStride;
+        const float wt = fast_exp2(__ldcg(rec + 128) - top);
+        o = fmaf(__ldcg(rec + c), wt, o);
+        l = fmaf(__ldcg(rec + 129), wt, l);
+      }
+      out[(q_head0 + g) * 128 + c] = from_float<QT>(o / l);
+    }
+  }
+}
+
+#undef SEQ
+static int smem_bytes() { return 8 * 4 * kQChunk * 4 + kWarps * 1152 + kWarps * kStages * kStageBytes; }
+
+}  // namespace inq
+
+using namespace inq;
+
+static int g_sm_count = 0;
+static int sm_count() {
+  if (!g_sm_count) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      g_sm_count = n;
+    else
+      return 148;
+  }
+  return g_sm_count;
+}
+
+extern "C" int inq_decode_plan_parts(int32_t n_seq, int32_t kv_heads, int32_t q_per_kv, int64_t max_slices) {
+  if (n_seq < 1 || kv_heads < 1 || q_per_kv < 1) return INQ_ERR_ARGUMENT;
+  const long long groups = (long long)n_seq * kv_heads * ((q_per_kv + 7) / 8);
+  const long long target = (long long)sm_count() * 4 * 3;            // three waves of four CTAs per SM
+  long long parts = (target + groups - 1) / groups;
+  const long long most = max_slices / 32 > 1 ? max_slices / 32 : 1;  // at least 8 slices per warp
+  if (parts > most) parts = most;
+  if (parts < 1) parts = 1;
+  if (parts > 1024) parts = 1024;
+  return (int)parts;
+}
+
+extern "C" int64_t inq_decode_workspace_floats(int32_t n_seq, int32_t kv_heads, int32_t q_per_kv, int32_t n_parts) {
+  return (int64_t)n_seq * kv_heads * ((q_per_kv + 7) / 8) * n_parts * kRecordFloats;
+}
+
+extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t stream_) {
+  if (!a || a->n_seq < 1 || a->kv_heads < 1 || a->q_per_kv < 1 || a->block_tokens < 1 || a->n_parts < 1) return INQ_ERR_ARGUMENT;
+  if (!a->partials || !a->counters || !a->status) return INQ_ERR_ARGUMENT;
+  if (a->n_seq > 1 && !a->seqs_device) return INQ_ERR_ARGUMENT;
+  if (a->n_seq == 1 && !a->seqs_device && !a->seq_host) return INQ_ERR_ARGUMENT;
+  if (a->dtype != INQ_F16 && a->dtype != INQ_BF16) return INQ_ERR_UNSUPPORTED;
+  if (a->layout != 0 && a->layout != 1) return INQ_ERR_ARGUMENT;
+  if (!(a->scale > 0.f) || a->n_pad < 0 || a->n_pad > 64) return INQ_ERR_ARGUMENT;
+  if (a->n_seq > 65535 || (long long)a->kv_heads * ((a->q_per_kv + 7) / 8) > 65535) return INQ_ERR_UNSUPPORTED;
+  DecodeParams P;
+  P.seqs = (const SeqDesc*)a->seqs_device;
+  if (!a->seqs_device) P.one = *(const SeqDesc*)a->seq_host;
+  P.n_seq = a->n_seq;
+  P.H = a->kv_heads;
+  P.G = a->q_per_kv;
+  P.T = a->block_tokens;
+  P.n_pad = a->n_pad;
+  P.n_parts = a->n_parts;
+  P.scale_log2e = a->scale * 1.4426950408889634f;
+  P.page_bytes = a->page_bytes;
+  P.off_ks = (int)a->page_offsets[0];
+  P.off_km = (int)a->page_offsets[1];
+  P.off_kp = (int)a->page_offsets[2];
+  P.off_vp = (int)a->page_offsets[3];
+  P.off_vs = (int)a->page_offsets[4];
+  P.off_vo = (int)a->page_offsets[5];
+  P.partials = a->partials;
+  P.counters = a->counters;
+  P.status = a->status;
+  dim3 grid((unsigned)a->n_parts, (unsigned)(a->kv_heads * ((a->q_per_kv + 7) / 8)), (unsigned)a->n_seq);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int shared = smem_bytes();
+  if (a->layout == 0) {
+    if (a->dtype == INQ_F16)
+      decode_kernel<0, __half><<<grid, kThreads, shared, stream>>>(P);
+    else
+      decode_kernel<0, __nv_bfloat16><<<grid, kThreads, shared, stream>>>(P);
+  } else {
+    if (a->dtype == INQ_F16)
+      decode_kernel<1, __half><<<grid, kThreads, shared, stream>>>(P);
+    else
+      decode_kernel<1, __nv_bfloat16><<<grid, kThreads, shared, stream>>>(P);
+  }
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}

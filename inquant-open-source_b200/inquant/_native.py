@@ -41,6 +41,36 @@ class VEncodeArgs(ctypes.Structure):
                 ("payload", Field), ("scales", Field), ("offsets", Field)]
 
 
+class DecodeSeq(ctypes.Structure):
+    _fields_ = [("query", c_void_p), ("output", c_void_p), ("query_head_stride", c_int64),
+                ("table", c_void_p), ("roles", c_void_p), ("pool", c_void_p), ("page_table", c_void_p),
+                ("sink_key", c_void_p), ("sink_value", c_void_p), ("tail_key", c_void_p), ("tail_value", c_void_p),
+                ("sink_key_stride_h", c_int64), ("sink_key_stride_t", c_int64),
+                ("sink_value_stride_h", c_int64), ("sink_value_stride_t", c_int64),
+                ("tail_key_stride_h", c_int64), ("tail_key_stride_t", c_int64),
+                ("tail_value_stride_h", c_int64), ("tail_value_stride_t", c_int64),
+                ("n_blocks", c_int32), ("sink_tokens", c_int32), ("tail_tokens", c_int32),
+                ("first_visible", c_int32), ("tail_skip", c_int32), ("tail_tokens_device", c_void_p)]
+
+
+class DecodeArgs(ctypes.Structure):
+    _fields_ = [("n_seq", c_int32), ("seqs_device", c_void_p), ("seq_host", ctypes.POINTER(DecodeSeq)),
+                ("kv_heads", c_int32), ("q_per_kv", c_int32), ("block_tokens", c_int32), ("n_pad", c_int32),
+                ("layout", c_int32), ("dtype", c_int32), ("scale", ctypes.c_float),
+                ("page_bytes", c_int64), ("page_offsets", c_int64 * 6), ("n_parts", c_int32),
+                ("partials", c_void_p), ("counters", c_void_p), ("status", c_void_p)]
+
+
+class AppendArgs(ctypes.Structure):
+    _fields_ = [("key", c_void_p), ("value", c_void_p), ("src_stride_h", c_int64),
+                ("tail_key", c_void_p), ("tail_value", c_void_p), ("tail_stride_h", c_int64), ("tail_stride_t", c_int64),
+                ("tail_position", c_int32), ("tail_capacity", c_int32), ("tail_counter", c_void_p),
+                ("sink_key", c_void_p), ("sink_value", c_void_p), ("sink_stride_h", c_int64), ("sink_stride_t", c_int64),
+                ("sink_position", c_int32), ("heads", c_int32), ("row_bytes", c_int32), ("status", c_void_p)]
+
+
+RECORD_FLOATS = 8 * 132  # one split-KV partial: 8 query heads x (acc[128], m, l, pad)
+
 _lib = None
 
 
@@ -54,6 +84,8 @@ def library() -> ctypes.CDLL:
                 "(nvcc, sm_100a). The packed-KV path has no Triton, PyTorch or CPU fallback.")
         lib = ctypes.CDLL(LIBRARY_PATH)
         lib.inq_last_error.restype = ctypes.c_char_p
+        lib.inq_decode_workspace_floats.restype = c_int64
+        lib.inq_decode_workspace_floats.argtypes = [c_int32, c_int32, c_int32, c_int32]
         for name in EXPORTS:
             function = getattr(lib, name)  # every declared entry point must resolve
             if name in SIGNATURES:
@@ -67,6 +99,7 @@ def library() -> ctypes.CDLL:
 EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
     "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
+    "inq_decode_attention", "inq_decode_plan_parts", "inq_decode_workspace_floats", "inq_append_token",
 )
 
 
@@ -79,6 +112,9 @@ SIGNATURES = {
     "inq_v_encode": [_P, _P, _P],
     "inq_v_dequantize": [_P, _P, _P, _L, _I, _I, _I, _I, _P, _I, _P],
     "inq_build_roles": [_P, _P, _I, _L, _I, _I, _P, _I, _P],
+    "inq_decode_attention": [_P, _P],
+    "inq_append_token": [_P, _P],
+    "inq_decode_plan_parts": [_I, _I, _I, _L],
 }
 
 
@@ -142,3 +178,23 @@ def make_input(x: torch.Tensor, page_ids: torch.Tensor | None = None) -> Input:
     return Input(x.data_ptr(), DTYPE_CODE[x.dtype], x.shape[0], x.shape[1], x.stride(0), x.stride(1), x.stride(2),
                  x.shape[2], x.shape[3], None if page_ids is None else page_ids.data_ptr(),
                  0 if page_ids is None else int(page_ids.dtype == torch.int64))
+
+
+_counters: dict[tuple, torch.Tensor] = {}
+
+
+def decode_counters(device: torch.device, count: int) -> torch.Tensor:
+    """Zero-initialised arrival counters of the fused split-KV merge, one array per
+    (device, stream); the kernel leaves them zero, so they are reused launch after launch."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    tensor = _counters.get(key)
+    if tensor is None or tensor.numel() < count:
+        tensor = torch.zeros(max(count, 1024), dtype=torch.int32, device=device)
+        _counters[key] = tensor
+    return tensor
+
+
+def dense_rows_aligned(tensor: torch.Tensor) -> bool:
+    """16-byte aligned rows of a [1, heads, tokens, 128] 16-bit tensor."""
+    return (tensor.data_ptr() % 16 == 0 and tensor.stride(-1) == 1 and tensor.stride(1) % 8 == 0
+            and tensor.stride(2) % 8 == 0)

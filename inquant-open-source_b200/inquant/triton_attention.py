@@ -1,0 +1,261 @@
+"""Single-query GQA attention directly over the packed layout, with the reference's
+``inquant.triton_attention`` interface (the module name is kept for drop-in use; nothing
+here uses Triton).
+
+``PackedDecodeState`` owns the per-block pointer table and the int8 channel-role maps and
+launches ONE sm_100a kernel per decode (C ABI ``inq_decode_attention``): partial softmax
+over the packed K4/V2 blocks, the exact sink and the exact tail, and the log-sum-exp merge
+by the last CTA of each KV head (reference: two Triton kernels,
+``triton_attention.py:67-181``).
+
+Limitations of this build: CUDA, batch 1, head_dim 128, one query token, fp16/bf16 query,
+uniform packed block length, values stored as 2-bit ``PackedValues`` with group 64.  Other
+variants raise ``NotImplementedError``; there is no fallback.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _native as N
+from .codec import PackedTensor
+from .value_codec import PackedValues
+
+
+class SharedDecodeWorkspace:
+    """One scratch allocation per request, usable only on one CUDA stream
+    (reference ``triton_attention.py:184-208``)."""
+
+    def __init__(self):
+        self.tensor = None
+        self._stream_identity = None
+
+    @property
+    def nbytes(self):
+        return 0 if self.tensor is None else self.tensor.numel() * self.tensor.element_size()
+
+    def acquire(self, shape, device):
+        stream = torch.cuda.current_stream(device)
+        identity = (stream.device, stream.cuda_stream)
+        if self._stream_identity is not None and identity != self._stream_identity:
+            raise RuntimeError("Shared decode workspace requires one CUDA stream per cache")
+        self._stream_identity = identity
+        required = math.prod(shape)
+        if self.tensor is None or self.tensor.numel() < required:
+            self.tensor = torch.empty(required, dtype=torch.float32, device=device)
+        return self.tensor[:required].view(shape)
+
+
+def plan_parts(kv_heads: int, q_per_kv: int, slices: int, n_seq: int = 1) -> int:
+    parts = N.library().inq_decode_plan_parts(n_seq, kv_heads, q_per_kv, max(1, slices))
+    if parts < 1:
+        raise ValueError("invalid decode geometry")
+    return parts
+
+
+class PackedDecodeState:
+    """Reusable descriptors for immutable blocks; exact tails are per-call inputs
+    (reference ``triton_attention.py:211-388``)."""
+
+    def __init__(self, key_blocks, value_blocks, *, workspace_pool=None):
+        if len(key_blocks) != len(value_blocks):
+            raise ValueError("Key and value block counts must match")
+        self.key_blocks = ()
+        self.value_blocks = ()
+        self._workspace = None
+        self._workspace_pool = workspace_pool
+        self._tables = None
+        self._key_map = None
+        self._value_map = None
+        self._device = None
+        self._kv_heads = None
+        self._packed_tokens = 256
+        self._salient = 0
+        self._value_bits = 0
+        self._value_group = 64
+        self._capacity = 0
+        self._stream_identity = None
+        self.extend(key_blocks, value_blocks)
+
+    def extend(self, key_blocks, value_blocks):
+        """Append immutable blocks, building descriptors only for the new suffix."""
+        if len(key_blocks) != len(value_blocks):
+            raise ValueError("Key and value block counts must match")
+        old_count = len(self.key_blocks)
+        if len(key_blocks) < old_count or any(a is not b for a, b in zip(self.key_blocks, key_blocks)) or any(
+                a is not b for a, b in zip(self.value_blocks, value_blocks)):
+            raise ValueError("PackedDecodeState.extend requires an immutable append-only prefix")
+        if len(key_blocks) == old_count:
+            return
+        first = key_blocks[0]
+        if first.shape[0] != 1 or first.shape[-1] != 128 or first.payload.device.type != "cuda":
+            raise ValueError("Packed decode requires CUDA blocks with batch=1 and head_dim=128")
+        stream = torch.cuda.current_stream(first.payload.device)
+        identity = (stream.device, stream.cuda_stream)
+        if self._stream_identity is not None and self._stream_identity != identity:
+            raise RuntimeError("Descriptor updates require one CUDA stream per state")
+        self._stream_identity = identity
+        self._device = first.payload.device
+        self._kv_heads = first.shape[1]
+        self._packed_tokens = first.shape[2]
+        self._salient = first.salient_channels.shape[-1]
+        for block in key_blocks:
+            if not isinstance(block, PackedTensor) or block.shape != first.shape or block.salient_channels.shape[-1] != self._salient:
+                raise ValueError("All packed K/V blocks must share shape and salient-channel count")
+        if not isinstance(value_blocks[0], PackedValues):
+            raise NotImplementedError("This build decodes values stored as PackedValues (value_bits=2); "
+                                      "InQuant-coded values are not built")
+        self._value_bits = value_blocks[0].bits
+        self._value_group = value_blocks[0].group_size
+        if (self._value_bits, self._value_group) != (2, 64):
+            raise NotImplementedError("This build decodes 2-bit values with group size 64 only")
+        for block in value_blocks:
+            if block.shape != first.shape:
+                raise ValueError("All packed blocks must share shape")
+            if not isinstance(block, PackedValues) or (block.bits, block.group_size) != (self._value_bits, self._value_group):
+                raise ValueError("All V blocks must share the same quantizer")
+        for block in (*key_blocks, *value_blocks):
+            if any(t.device != self._device for t in block.tensors.values()):
+                raise ValueError("All packed tensors must share the same CUDA device")
+        new_keys, new_values = key_blocks[old_count:], value_blocks[old_count:]
+        for k, v in zip(new_keys, new_values):
+            for t in (*k.tensors.values(), *v.tensors.values()):
+                if not t.is_contiguous():
+                    raise ValueError("Packed block tensors must be contiguous")
+        pointers = [[k.payload.data_ptr(), k.scales.data_ptr(), k.padding.data_ptr(),
+                     v.payload.data_ptr(), v.scales.data_ptr(), v.offsets.data_ptr()]
+                    for k, v in zip(new_keys, new_values)]
+        count = len(key_blocks)
+        if count > self._capacity:
+            capacity = count if not self._capacity else max(count, min(self._capacity * 2, count + 7))
+            tables = torch.empty((capacity, 6), dtype=torch.int64, device=self._device)
+            key_map = torch.empty((capacity, self._kv_heads, 128), dtype=torch.int8, device=self._device)
+            value_map = torch.empty((0,), dtype=torch.int8, device=self._device)
+            if old_count:
+                tables[:old_count].copy_(self._tables[:old_count])
+                key_map[:old_count].copy_(self._key_map[:old_count])
+            self._tables, self._key_map, self._value_map = tables, key_map, value_map
+            self._capacity = capacity
+        self._tables[old_count:count].copy_(torch.tensor(pointers, dtype=torch.int64).to(self._device, non_blocking=False))
+        self._write_maps(self._key_map[old_count:count], new_keys)
+        self.key_blocks, self.value_blocks = tuple(key_blocks), tuple(value_blocks)
+
+    def _write_maps(self, result, blocks):
+        """Roles: donor channel 0..127 for a salient channel, -1 normal, -2-i for the i-th donor
+        (C ABI ``inq_build_roles``; reference ``triton_attention.py:301-309``)."""
+        sources = torch.cat([block.salient_channels for block in blocks], dim=0).contiguous()
+        donors = torch.cat([block.donor_channels for block in blocks], dim=0).contiguous()
+        rows = len(blocks) * self._kv_heads
+        rc = N.library().inq_build_roles(N.pointer(sources), N.pointer(donors), 0, rows, 128, self._salient,
+                                         N.pointer(result), 1, N.stream_pointer(self._device))
+        N.check(rc, "inq_build_roles")
+        return result
+
+    @property
+    def nbytes(self) -> int:
+        """Auxiliary live GPU allocations; input packed blocks are counted elsewhere."""
+        return sum(t.numel() * t.element_size() for t in
+                   (self._tables, self._key_map, self._value_map, self._workspace) if t is not None)
+
+    @torch.no_grad()
+    def decode(self, query, *, sink_key=None, sink_value=None, residual_key=None, residual_value=None, scale=None):
+        if query.ndim != 4 or query.shape[0] != 1 or query.shape[1] < 1 or query.shape[-2:] != (1, 128):
+            raise ValueError("query must have shape [1, query_heads, 1, 128]")
+        if query.device.type != "cuda" or query.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+            raise ValueError("query must be a CUDA FP16, BF16 or FP32 tensor")
+        if query.dtype == torch.float32:
+            raise NotImplementedError("This build decodes fp16 and bf16 queries; fp32 queries are not built")
+        if query.stride(-1) != 1:
+            raise ValueError("query head dimension must be contiguous")
+        if self._device is not None and query.device != self._device:
+            raise ValueError("query and packed blocks must share a device")
+        kv_heads = self._kv_heads
+        dense = []
+        for name, key, value in (("sink", sink_key, sink_value), ("residual", residual_key, residual_value)):
+            if (key is None) != (value is None):
+                raise ValueError(f"{name} key/value must both be provided")
+            if key is None:
+                dense.append((None, None, 0))
+                continue
+            if key.ndim != 4 or key.shape != value.shape or key.shape[0] != 1 or key.shape[-1] != 128:
+                raise ValueError(f"{name} K/V must have matching [1, KV_heads, tokens, 128] shapes")
+            if key.dtype != query.dtype or value.dtype != query.dtype or key.device != query.device or value.device != query.device:
+                raise ValueError(f"{name} K/V must match query dtype and device")
+            if key.stride(-1) != 1 or value.stride(-1) != 1:
+                raise ValueError(f"{name} head dimension must be contiguous")
+            kv_heads = key.shape[1] if kv_heads is None else kv_heads
+            if key.shape[1] != kv_heads:
+                raise ValueError("All inputs must share their KV head count")
+            if not N.dense_rows_aligned(key):
+                key = key.contiguous()
+            if not N.dense_rows_aligned(value):
+                value = value.contiguous()
+            dense.append((key, value, key.shape[2]))
+        if kv_heads is None or query.shape[1] % kv_heads:
+            raise ValueError("query_heads must be divisible by the nonempty KV head count")
+        (sink_key, sink_value, sink_t), (residual_key, residual_value, residual_t) = dense
+        n_blocks = len(self.key_blocks)
+        if not (n_blocks + sink_t + residual_t):
+            raise ValueError("Attention requires at least one key/value token")
+        if scale is None:
+            scale = 128 ** -0.5
+        if not math.isfinite(scale) or scale <= 0:
+            raise ValueError("attention scale must be positive and finite")
+        stream = torch.cuda.current_stream(query.device)
+        identity = (stream.device, stream.cuda_stream)
+        if self._stream_identity is not None and self._stream_identity != identity:
+            raise RuntimeError("Packed decode state requires one CUDA stream per state")
+        q_per_kv = query.shape[1] // kv_heads
+        tiles = (q_per_kv + 7) // 8
+        slices = n_blocks * ((self._packed_tokens + 15) // 16) + 4 * ((sink_t + 15) // 16 + (residual_t + 15) // 16)
+        parts = plan_parts(kv_heads, q_per_kv, slices)
+        workspace_shape = (kv_heads * tiles, parts, N.RECORD_FLOATS)
+        if self._workspace_pool is not None:
+            workspace = self._workspace_pool.acquire(workspace_shape, query.device)
+        else:
+            if self._workspace is None or self._workspace.shape != workspace_shape or self._workspace.device != query.device:
+                self._workspace = torch.empty(workspace_shape, dtype=torch.float32, device=query.device)
+            workspace = self._workspace
+        if not N.dense_rows_aligned(query.squeeze(2).unsqueeze(0)):
+            query = query.contiguous()
+        output = torch.empty(query.shape, dtype=query.dtype, device=query.device)
+        if self._tables is None:
+            self._tables = torch.empty((0, 6), dtype=torch.int64, device=query.device)
+            self._key_map = torch.empty((0, kv_heads, 128), dtype=torch.int8, device=query.device)
+            self._value_map = torch.empty((0,), dtype=torch.int8, device=query.device)
+            self._device = query.device
+        seq = N.DecodeSeq()
+        seq.query, seq.output, seq.query_head_stride = query.data_ptr(), output.data_ptr(), query.stride(1)
+        seq.table = self._tables.data_ptr() if n_blocks else None
+        seq.roles = self._key_map.data_ptr() if n_blocks else None
+        if sink_t:
+            seq.sink_key, seq.sink_value = sink_key.data_ptr(), sink_value.data_ptr()
+            seq.sink_key_stride_h, seq.sink_key_stride_t = sink_key.stride(1), sink_key.stride(2)
+            seq.sink_value_stride_h, seq.sink_value_stride_t = sink_value.stride(1), sink_value.stride(2)
+        if residual_t:
+            seq.tail_key, seq.tail_value = residual_key.data_ptr(), residual_value.data_ptr()
+            seq.tail_key_stride_h, seq.tail_key_stride_t = residual_key.stride(1), residual_key.stride(2)
+            seq.tail_value_stride_h, seq.tail_value_stride_t = residual_value.stride(1), residual_value.stride(2)
+        seq.n_blocks, seq.sink_tokens, seq.tail_tokens = n_blocks, sink_t, residual_t
+        args = N.DecodeArgs()
+        args.n_seq, args.seq_host = 1, N.ctypes.pointer(seq)
+        args.kv_heads, args.q_per_kv = kv_heads, q_per_kv
+        args.block_tokens, args.n_pad = self._packed_tokens, self._salient
+        args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[query.dtype], scale
+        args.n_parts = parts
+        args.partials = workspace.data_ptr()
+        args.counters = N.decode_counters(query.device, kv_heads * tiles).data_ptr()
+        args.status = N.status_word(query.device).data_ptr()
+        rc = N.library().inq_decode_attention(N.ctypes.byref(args), N.stream_pointer(query.device))
+        N.check(rc, "inq_decode_attention")
+        return output
+
+
+def packed_decode(query, key_blocks, value_blocks, sink_key=None, sink_value=None,
+                  residual_key=None, residual_value=None, *, scale=None):
+    """One-shot convenience wrapper; reuse PackedDecodeState for repeated decoding."""
+    return PackedDecodeState(key_blocks, value_blocks).decode(
+        query, sink_key=sink_key, sink_value=sink_value,
+        residual_key=residual_key, residual_value=residual_value, scale=scale,
+    )

@@ -1,0 +1,226 @@
+"""Packed decode attention (table layout) vs the CPU oracle: dequantise everything with the
+oracle, run float64 attention, compare within max-abs 2e-2 and cosine >= 0.9999 (the bound
+stated for bf16 attention outputs); most cases also hold the reference tests' atol 1e-3 /
+rtol 2e-2.  Mirrors the reference's tests/test_triton_attention.py and
+tests/test_incremental_state.py."""
+import numpy as np
+import pytest
+import torch
+
+import inquant_oracle as oracle
+import workloads
+from cases import DECODE_CASES, k4_input
+from helpers import TORCH_DTYPE, attention_close, to_device, to_numpy
+
+pytestmark = pytest.mark.gpu
+
+
+def _mods():
+    from inquant.codec import CodecConfig, quantize
+    from inquant.value_codec import quantize_values
+    from inquant.triton_attention import PackedDecodeState, SharedDecodeWorkspace, packed_decode
+    return CodecConfig, quantize, quantize_values, PackedDecodeState, SharedDecodeWorkspace, packed_decode
+
+
+def _random(seed, shape, dtype):
+    x = np.random.default_rng(seed).standard_normal(shape, dtype=np.float32)
+    return oracle.round_to_dtype(x, dtype)
+
+
+def _expected(q, pieces_k, pieces_v, scale=128 ** -0.5):
+    keys = np.concatenate(pieces_k, axis=1)
+    vals = np.concatenate(pieces_v, axis=1)
+    return oracle.attention_decode(q, keys, vals, scale)
+
+
+def _check(actual, expected, atol=1e-3, rtol=0.02):
+    actual = to_numpy(actual.float()).reshape(expected.shape)
+    attention_close(actual, expected)
+    assert np.all(np.abs(actual - expected) <= atol + rtol * np.abs(expected) + 4e-3 * np.abs(expected).max()), \
+        np.abs(actual - expected).max()
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("fraction", [0.0, 0.125, 0.5])
+@pytest.mark.parametrize("policy", ["neighbors", "min_error"])
+def test_packed_gqa_with_sink_and_unsealed_tail(dtype, fraction, policy):
+    CodecConfig, quantize, quantize_values, PackedDecodeState, _, _ = _mods()
+    cfg = CodecConfig(salient_fraction=fraction, donor_policy=policy)
+    ks = [_random(921 + i, (1, 4, 256, 128), dtype) for i in range(3)]
+    vs = [_random(1921 + i, (1, 4, 256, 128), dtype) for i in range(3)]
+    for k in ks:
+        k[..., 5:8] *= 12
+    keys = [quantize(to_device(k, dtype), cfg) for k in ks]
+    values = [quantize_values(to_device(v, dtype)) for v in vs]
+    sink_k, sink_v = _random(1, (1, 4, 4, 128), dtype), _random(2, (1, 4, 4, 128), dtype)
+    tail_k, tail_v = _random(3, (1, 4, 281, 128), dtype), _random(4, (1, 4, 281, 128), dtype)
+    q = _random(5, (28, 128), dtype)
+    state = PackedDecodeState(keys, values)
+    descriptor_bytes = state.nbytes
+    args = dict(sink_key=to_device(sink_k, dtype), sink_value=to_device(sink_v, dtype),
+                residual_key=to_device(tail_k, dtype), residual_value=to_device(tail_v, dtype))
+    query = to_device(q, dtype).view(1, 28, 1, 128)
+    actual = state.decode(query, **args)
+    ok = [oracle.quantize_k4(k, dtype, 8, fraction, policy) for k in ks]
+    ov = [oracle.quantize_values(v, dtype) for v in vs]
+    expected = _expected(q, [sink_k[0]] + [oracle.dequantize_k4(b)[0] for b in ok] + [tail_k[0]],
+                         [sink_v[0]] + [oracle.dequantize_values(b)[0] for b in ov] + [tail_v[0]])
+    _check(actual, expected)
+    assert actual.shape == query.shape and actual.dtype == TORCH_DTYPE[dtype]
+    assert state.nbytes == descriptor_bytes + state._workspace.numel() * 4
+    pointer = state._workspace.data_ptr()
+    again = state.decode(query, **args)
+    assert state._workspace.data_ptr() == pointer
+    assert torch.equal(actual, again)
+
+
+@pytest.mark.parametrize("tokens", [1, 4, 15, 16, 17, 257])
+def test_dense_only_before_any_block_is_sealed(tokens):
+    *_, packed_decode = _mods()
+    q = _random(7, (14, 128), "bfloat16")
+    key, value = _random(8, (1, 2, tokens, 128), "bfloat16"), _random(9, (1, 2, tokens, 128), "bfloat16")
+    actual = packed_decode(to_device(q).view(1, 14, 1, 128), [], [], residual_key=to_device(key), residual_value=to_device(value))
+    _check(actual, _expected(q, [key[0]], [value[0]]), atol=5e-3)
+
+
+@pytest.mark.parametrize("tokens,heads,q_heads", [(41, 1, 3), (16, 2, 16), (200, 1, 1), (64, 2, 32)])
+def test_no_dense_tensors_and_nondefault_packed_block_length(tokens, heads, q_heads):
+    CodecConfig, quantize, quantize_values, _, _, packed_decode = _mods()
+    k, v = _random(10, (1, heads, tokens, 128), "float16"), _random(11, (1, heads, tokens, 128), "float16")
+    k[..., 100] *= 9
+    q = _random(12, (q_heads, 128), "float16")
+    actual = packed_decode(to_device(q, "float16").view(1, q_heads, 1, 128),
+                           [quantize(to_device(k, "float16"), CodecConfig(salient_fraction=0.125))],
+                           [quantize_values(to_device(v, "float16"))])
+    expected = _expected(q, [oracle.dequantize_k4(oracle.quantize_k4(k, "float16"))[0]],
+                         [oracle.dequantize_values(oracle.quantize_values(v, "float16"))[0]])
+    _check(actual, expected)
+
+
+def test_extreme_softmax_and_zero_blocks_remain_finite():
+    CodecConfig, quantize, quantize_values, _, _, packed_decode = _mods()
+    key = np.zeros((1, 1, 256, 128), np.float32)
+    key[..., 0, :] = 30
+    value = _random(13, key.shape, "bfloat16")
+    q = np.full((7, 128), 20, np.float32)
+    actual = packed_decode(to_device(q).view(1, 7, 1, 128), [quantize(to_device(key))], [quantize_values(to_device(value))])
+    expected = _expected(q, [oracle.dequantize_k4(oracle.quantize_k4(key))[0]],
+                         [oracle.dequantize_values(oracle.quantize_values(value))[0]])
+    assert torch.isfinite(actual).all()
+    _check(actual, expected)
+
+
+def test_growing_state_matches_fresh_state_and_rejects_replacement():
+    CodecConfig, quantize, quantize_values, PackedDecodeState, _, _ = _mods()
+    keys, values, raw = [], [], []
+    state = PackedDecodeState([], [])
+    q = _random(831, (8, 128), "bfloat16")
+    query = to_device(q).view(1, 8, 1, 128)
+    for i in range(11):
+        k = _random(100 + i, (1, 2, 32, 128), "bfloat16")
+        k[..., 127] *= 20   # source / donor indices at the signed-byte boundary
+        v = _random(200 + i, (1, 2, 32, 128), "bfloat16")
+        raw.append((k, v))
+        keys.append(quantize(to_device(k), CodecConfig(donor_policy="min_error")))
+        values.append(quantize_values(to_device(v)))
+        state.extend(keys, values)
+        fresh = PackedDecodeState(keys, values)
+        assert torch.equal(state.decode(query), fresh.decode(query))
+        assert state._key_map.dtype == torch.int8
+        assert torch.equal(state._key_map[:i + 1], fresh._key_map[:i + 1])
+        ok = oracle.quantize_k4(k, "bfloat16", 8, 0.125, "min_error")
+        assert np.array_equal(to_numpy(state._key_map[i]),
+                              oracle.role_map(ok.salient_channels, ok.donor_channels, 128)[0])
+    expected = _expected(q, [oracle.dequantize_k4(oracle.quantize_k4(k, "bfloat16", 8, 0.125, "min_error"))[0] for k, _ in raw],
+                         [oracle.dequantize_values(oracle.quantize_values(v))[0] for _, v in raw])
+    _check(state.decode(query), expected)
+    with pytest.raises(ValueError, match="append-only"):
+        state.extend(keys[:-1], values[:-1])
+    with pytest.raises(ValueError, match="append-only"):
+        state.extend(list(reversed(keys)), values)
+    state.extend(keys, values)
+    assert torch.equal(state.decode(query), fresh.decode(query))
+
+
+def test_growing_tail_lengths_and_strided_tail_views():
+    CodecConfig, quantize, quantize_values, PackedDecodeState, _, _ = _mods()
+    k, v = _random(20, (1, 4, 256, 128), "bfloat16"), _random(21, (1, 4, 256, 128), "bfloat16")
+    state = PackedDecodeState([quantize(to_device(k))], [quantize_values(to_device(v))])
+    tail_k, tail_v = _random(22, (1, 4, 192, 128), "bfloat16"), _random(23, (1, 4, 192, 128), "bfloat16")
+    tk, tv = to_device(tail_k), to_device(tail_v)
+    q = _random(24, (28, 128), "bfloat16")
+    query = to_device(q).view(1, 28, 1, 128)
+    dk = oracle.dequantize_k4(oracle.quantize_k4(k))[0]
+    dv = oracle.dequantize_values(oracle.quantize_values(v))[0]
+    for length in (129, 130, 143, 144, 145, 192):
+        compact = state.decode(query, residual_key=tk[:, :, :length].contiguous(), residual_value=tv[:, :, :length].contiguous())
+        strided = state.decode(query, residual_key=tk[:, :, :length], residual_value=tv[:, :, :length])
+        assert torch.equal(compact, strided)
+        _check(compact, _expected(q, [dk, tail_k[0, :, :length]], [dv, tail_v[0, :, :length]]))
+
+
+def test_workspace_pool_is_shared_and_rejects_other_stream():
+    CodecConfig, quantize, quantize_values, PackedDecodeState, SharedDecodeWorkspace, _ = _mods()
+    pool = SharedDecodeWorkspace()
+    q = _random(30, (28, 128), "bfloat16")
+    k, v = _random(31, (1, 4, 19, 128), "bfloat16"), _random(32, (1, 4, 19, 128), "bfloat16")
+    query = to_device(q).view(1, 28, 1, 128)
+    states = [PackedDecodeState([], [], workspace_pool=pool) for _ in range(3)]
+    for i, state in enumerate(states):
+        actual = state.decode(query, residual_key=to_device(k), residual_value=to_device(v + i))
+        _check(actual, _expected(q, [k[0]], [v[0] + i]), atol=8e-3)
+        assert state._workspace is None and state.nbytes == 0
+    first_pointer = pool.tensor.data_ptr()
+    states[0].decode(query, residual_key=to_device(k), residual_value=to_device(v))
+    assert first_pointer == pool.tensor.data_ptr()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(torch.cuda.Stream()):
+        with pytest.raises(RuntimeError, match="one CUDA stream"):
+            states[0].decode(query, residual_key=to_device(k), residual_value=to_device(v))
+
+
+def test_argument_validation():
+    CodecConfig, quantize, quantize_values, PackedDecodeState, _, packed_decode = _mods()
+    q = torch.zeros(1, 4, 1, 128, device="cuda", dtype=torch.bfloat16)
+    kv = torch.zeros(1, 2, 8, 128, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="at least one"):
+        packed_decode(q, [], [])
+    with pytest.raises(ValueError, match="both"):
+        packed_decode(q, [], [], residual_key=kv)
+    with pytest.raises(ValueError, match="divisible"):
+        packed_decode(torch.zeros(1, 3, 1, 128, device="cuda", dtype=torch.bfloat16), [], [], residual_key=kv, residual_value=kv)
+    with pytest.raises(ValueError, match="dtype"):
+        packed_decode(q.half(), [], [], residual_key=kv, residual_value=kv)
+    with pytest.raises(ValueError, match="scale"):
+        packed_decode(q, [], [], residual_key=kv, residual_value=kv, scale=0.0)
+    with pytest.raises(NotImplementedError):
+        packed_decode(q.float(), [], [], residual_key=kv.float(), residual_value=kv.float())
+    with pytest.raises(ValueError, match="counts"):
+        PackedDecodeState([quantize(kv)], [])
+    with pytest.raises(NotImplementedError):
+        PackedDecodeState([quantize(kv)], [quantize(kv)])
+
+
+@pytest.mark.parametrize("name", sorted(DECODE_CASES))
+def test_single_layer_roundtrip_matches_reference_output(golden, name):
+    """Config 0 of the benchmark definition (and a short-block variant): encode on the GPU,
+    decode on the GPU, compare with the reference's own attention output."""
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.triton_attention import PackedDecodeState
+    case = DECODE_CASES[name]
+    k, v = workloads.make_kv(case["seed"], case["kv_heads"], case["tokens"], outliers=6, adjacent=3,
+                             scale_range=case["scale_range"])
+    q = workloads.make_query(case["seed"], case["q_heads"])
+    cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=case["block"],
+                                     residual_length=case["residual"], sink_tokens=case["sink"], value_bits=2,
+                                     value_group_size=64, validate_positions=False))
+    kt, vt = to_device(k), to_device(v)
+    n = case["tokens"] - 1
+    cache.update(kt[:, :, :n], vt[:, :, :n], 0)
+    view = cache.append_for_attention(kt[:, :, n:], vt[:, :, n:], 0)
+    assert [len(view.key_blocks), view.sink_key.shape[2], view.residual_key.shape[2]] == list(golden[f"decode/{name}/layout"])
+    state = PackedDecodeState(view.key_blocks, view.value_blocks)
+    out = state.decode(to_device(q).view(1, case["q_heads"], 1, 128), sink_key=view.sink_key, sink_value=view.sink_value,
+                       residual_key=view.residual_key, residual_value=view.residual_value, scale=128 ** -0.5)
+    attention_close(to_numpy(out.float()).reshape(case["q_heads"], 128), golden[f"decode/{name}/output"])
