@@ -39,6 +39,11 @@ constexpr int kRecordStride = 132;                  // floats per query head: ac
 constexpr int kRecordFloats = 8 * kRecordStride;    // one partial record (8 query heads)
 constexpr int kQChunk = 36;                         // padded 32-float chunk of the staged query
 constexpr float kNegBig = -1.0e30f;
+constexpr int kWarpFixed = 512 + 512 + 256 + 256 + 64 + 64;   // per-warp scratch before the per-group parts
+
+__host__ __device__ constexpr int warp_smem_bytes(int groups) {
+  return kWarpFixed + groups * (256 + 4096) + kStages * kStageBytes;
+}
 
 struct SeqDesc {
   const void* q;
@@ -190,10 +195,18 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
   unsigned char* warp_base = smem + 8 * 4 * kQChunk * 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
-  float* wf = (float*)(warp_base + warp * 1152);                        // slot factor per channel
+  const int groups = (P.n_pad + 15) >> 4;                               // salient channels in groups of 16
+  const int warp_bytes = warp_smem_bytes(groups);
+  unsigned char* const wb = warp_base + warp * warp_bytes;
+  float* wf = (float*)wb;                                               // slot weight per channel
   float* wk0 = wf + 128;                                                // additive constant per channel
-  unsigned char* wqi = (unsigned char*)(wk0 + 128);                     // query channel multiplying each slot
-  unsigned char* ring = warp_base + kWarps * 1152 + warp * (kStages * kStageBytes);
+  short* wroles = (short*)(wk0 + 128);                                  // role map of the current block
+  float* wssc = (float*)(wroles + 128);                                 // scale of salient channel i
+  unsigned char* wsrc = (unsigned char*)(wssc + 64);                    // channel of salient i
+  unsigned char* wdon = wsrc + 64;                                      // its donor slot
+  unsigned char* wqsal = wdon + 64;                                     // B fragments: query at salient channels
+  unsigned char* wsel = wqsal + groups * 256;                           // B fragments: nibble selection
+  unsigned char* ring = wsel + groups * 4096;
   __shared__ int s_is_last;
 
   const int gtiles = (P.G + 7) >> 3;
@@ -296,27 +309,80 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
         bool bad = false;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int c = lane * 4 + i;
-          int ro = role[i];
-          if (ro > 127 || ro < -2 - (P.n_pad - 1) || (ro <= -2 && P.n_pad == 0)) {
+          if (role[i] > 127 || role[i] < -1 - P.n_pad) {
             bad = true;
-            ro = -1;
+            role[i] = -1;
           }
+          wroles[lane * 4 + i] = (short)role[i];
+        }
+        // clear the nibble-selection fragments of the salient path
+        for (int v = lane; v < groups * 256; v += 32) ((uint4*)wsel)[v] = make_uint4(0u, 0u, 0u, 0u);
+        if (lane < groups * 16) {
+          wsrc[lane] = 0;
+          wdon[lane] = 0;
+          wssc[lane] = 0.f;
+        }
+        if (groups > 2 && lane + 32 < groups * 16) {
+          wsrc[lane + 32] = 0;
+          wdon[lane + 32] = 0;
+          wssc[lane + 32] = 0.f;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = lane * 4 + i;
+          const int ro = role[i];
           if (ro == -1) {
             wf[c] = scv[i];
-            wqi[c] = (unsigned char)c;
             wk0[c] = -8.f * scv[i];
           } else if (ro >= 0) {
-            wf[c] = 16.f * scv[i];
-            wqi[c] = (unsigned char)c;
-            wk0[c] = -128.f * scv[i];
-            wf[ro] = scv[i];              // the donor slot carries this channel's low nibble
-            wqi[ro] = (unsigned char)c;
+            // salient: both of its slots leave the linear fold; its exact, dtype-rounded value
+            // is rebuilt per token by the salient path below
+            wf[c] = 0.f;
+            wk0[c] = 0.f;
+            wf[ro] = 0.f;
+            const int idx = -(int)wroles[ro] - 2;
+            if (idx >= 0 && idx < P.n_pad) {
+              wsrc[idx] = (unsigned char)c;
+              wdon[idx] = (unsigned char)ro;
+              wssc[idx] = scv[i];
+            } else {
+              bad = true;
+            }
           } else {
-            wk0[c] = ((const float*)cb.kpad)[-ro - 2];
+            // donor: the reference stores the sampled mean and rounds it to the model dtype
+            wk0[c] = to_float<QT>(from_float<QT>(((const float*)cb.kpad)[-ro - 2]));
           }
         }
         if (bad) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
+        __syncwarp();
+        // selection matrix: column i picks 16 * (high nibble of source i) + (low nibble in its
+        // donor slot), scaled by 2^11 so that every entry and every partial sum is exact
+        for (int i = lane; i < P.n_pad; i += 32) {
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const int c = which ? wdon[i] : wsrc[i];
+            const int jj = c >> 5, u = c & 31;
+            const int ks = 2 * (u >> 3) + ((u >> 1) & 1), half = u & 1, e = (u >> 2) & 1;
+            const int target = ((i & 7) << 2) | jj;
+            float value = which ? 2048.f : 32768.f;
+            if (half) value *= 0.0625f;
+            __half* cell = (__half*)(wsel + ((((i >> 4) * 8 + ks) * 32 + target) * 16) + (((i >> 3) & 1) * 2 + half) * 4 + e * 2);
+            *cell = __float2half_rn(value);
+          }
+        }
+        // query at the salient channels, as B fragments of the salient step
+        for (int gsel = 0; gsel < groups; ++gsel) {
+          unsigned short qv[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = gsel * 16 + 2 * j + (k & 1) + (k >> 1) * 8;
+            const bool live = r < g_valid && i < P.n_pad;
+            qv[k] = live ? *(const unsigned short*)(qptr + (q_head0 + r) * q_stride + wsrc[i]) : (unsigned short)0;
+          }
+          *(uint2*)(wqsal + (gsel * 32 + lane) * 8) = make_uint2((unsigned)qv[0] | ((unsigned)qv[1] << 16),
+                                                                 (unsigned)qv[2] | ((unsigned)qv[3] << 16));
+        }
         __syncwarp();
         // thread (head r, chunk j) owns the 32 channels 32j..32j+31 of query head r
         float w[32];
@@ -327,16 +393,12 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
           const float4 f4 = *(const float4*)(wf + 32 * j + 4 * i4);
           const float4 k4 = *(const float4*)(wk0 + 32 * j + 4 * i4);
           const float4 q4 = *(const float4*)(qown + 4 * i4);
-          const unsigned qi4 = *(const unsigned*)(wqi + 32 * j + 4 * i4);
           const float fv[4] = {f4.x, f4.y, f4.z, f4.w};
           const float kv[4] = {k4.x, k4.y, k4.z, k4.w};
           const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int c = 32 * j + 4 * i4 + e;
-            const int qc = (qi4 >> (8 * e)) & 0xff;
-            const float qsel = qc == c ? qv[e] : qs[(r * 4 + (qc >> 5)) * kQChunk + (qc & 31)];
-            w[4 * i4 + e] = qsel * fv[e];
+            w[4 * i4 + e] = qv[e] * fv[e];
             wmax = fmaxf(wmax, fabsf(w[4 * i4 + e]));
             cpart = fmaf(qv[e], kv[e], cpart);
           }
@@ -367,8 +429,9 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
       }
 
       const unsigned char* stage = ring + (it % kStages) * kStageBytes;
-      // ---- scores = K tile (16 tokens x 128 slots) * folded query
+      // ---- scores = K tile (16 tokens x 128 slots) * folded query, plus the salient channels
       float S[4] = {0.f, 0.f, 0.f, 0.f};
+      float S2[4] = {0.f, 0.f, 0.f, 0.f};
       {
         const uint4 kx = *(const uint4*)(stage + lane * 16);
         const uint4 ky = *(const uint4*)(stage + 512 + lane * 16);
@@ -382,9 +445,40 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
           mma_f16(S, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, wfrag[2 * i + 1][0],
                   wfrag[2 * i + 1][1]);
         }
+        for (int gsel = 0; gsel < groups; ++gsel) {
+          // gather code' = 16*hi + lo of 16 salient channels with the tensor cores (exact)
+          float C0[4] = {0.f, 0.f, 0.f, 0.f}, C1[4] = {0.f, 0.f, 0.f, 0.f};
+          const uint4* sel = (const uint4*)wsel + gsel * 256 + lane;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            unsigned x = xs[i], y = ys[i];
+            uint4 f = sel[(2 * i) * 32];
+            mma_f16(C0, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, f.x, f.y);
+            mma_f16(C1, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, f.z, f.w);
+            x >>= 8;
+            y >>= 8;
+            f = sel[(2 * i + 1) * 32];
+            mma_f16(C0, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, f.x, f.y);
+            mma_f16(C1, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, f.z, f.w);
+          }
+          // value = fl32((code' - 128) * scale) rounded to the model dtype, as the reference's
+          // dequantised tensor holds it
+          const float2 sc0 = *(const float2*)(wssc + gsel * 16 + 2 * j);
+          const float2 sc1 = *(const float2*)(wssc + gsel * 16 + 8 + 2 * j);
+          const unsigned a0 = pack_qt2<QT>(fmaf(C0[0], 8192.f, -128.f) * sc0.x, fmaf(C0[1], 8192.f, -128.f) * sc0.y);
+          const unsigned a1 = pack_qt2<QT>(fmaf(C0[2], 8192.f, -128.f) * sc0.x, fmaf(C0[3], 8192.f, -128.f) * sc0.y);
+          const unsigned a2 = pack_qt2<QT>(fmaf(C1[0], 8192.f, -128.f) * sc1.x, fmaf(C1[1], 8192.f, -128.f) * sc1.y);
+          const unsigned a3 = pack_qt2<QT>(fmaf(C1[2], 8192.f, -128.f) * sc1.x, fmaf(C1[3], 8192.f, -128.f) * sc1.y);
+          const uint2 qb = *(const uint2*)(wqsal + (gsel * 32 + lane) * 8);
+          mma_qt<QT>(S2, a0, a1, a2, a3, qb.x, qb.y);
+        }
       }
       float s2[4] = {fmaf(S[0], alpha[0], beta[0]), fmaf(S[1], alpha[1], beta[1]), fmaf(S[2], alpha[0], beta[0]),
                      fmaf(S[3], alpha[1], beta[1])};
+      if (groups) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s2[k] = fmaf(S2[k], P.scale_log2e, s2[k]);
+      }
       {
         const int tok0 = cur_slice * 16;
         const long long g0 = (long long)cur_block * T + tok0;
@@ -570,7 +664,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
     }
   }
   __syncthreads();   // every warp is done with its ring and weight scratch
-  float* wout = (float*)(warp_base + kWarps * 1152 + warp * (kStages * kStageBytes));   // [8][132]
+  float* wout = (float*)ring;   // [8][132]
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
     const int gr = mt >> 2, q = mt & 3;
@@ -593,8 +687,8 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
   float* record = P.partials + (slot * P.n_parts + blockIdx.x) * kRecordFloats;
   {
     const int c = threadIdx.x;   // one channel per thread
-    const float* w0 = (const float*)(warp_base + kWarps * 1152);
-    const int wstride = kStages * kStageBytes / 4;
+    const float* w0 = (const float*)(warp_base + (ring - wb));
+    const int wstride = warp_bytes / 4;
     for (int g = 0; g < g_valid; ++g) {
       float mw[kWarps], top = kNegBig;
 #pragma unroll
@@ -647,7 +741,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
 }
 
 #undef SEQ
-static int smem_bytes() { return 8 * 4 * kQChunk * 4 + kWarps * 1152 + kWarps * kStages * kStageBytes; }
+static int smem_bytes(int groups) { return 8 * 4 * kQChunk * 4 + kWarps * warp_smem_bytes(groups); }
 
 }  // namespace inq
 
@@ -712,18 +806,17 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   P.status = a->status;
   dim3 grid((unsigned)a->n_parts, (unsigned)(a->kv_heads * ((a->q_per_kv + 7) / 8)), (unsigned)a->n_seq);
   cudaStream_t stream = (cudaStream_t)stream_;
-  const int shared = smem_bytes();
-  if (a->layout == 0) {
-    if (a->dtype == INQ_F16)
-      decode_kernel<0, __half><<<grid, kThreads, shared, stream>>>(P);
-    else
-      decode_kernel<0, __nv_bfloat16><<<grid, kThreads, shared, stream>>>(P);
-  } else {
-    if (a->dtype == INQ_F16)
-      decode_kernel<1, __half><<<grid, kThreads, shared, stream>>>(P);
-    else
-      decode_kernel<1, __nv_bfloat16><<<grid, kThreads, shared, stream>>>(P);
+  const int shared = smem_bytes((a->n_pad + 15) / 16);
+  void (*kernel)(const DecodeParams) =
+      a->layout == 0 ? (a->dtype == INQ_F16 ? decode_kernel<0, __half> : decode_kernel<0, __nv_bfloat16>)
+                     : (a->dtype == INQ_F16 ? decode_kernel<1, __half> : decode_kernel<1, __nv_bfloat16>);
+  static bool raised[4] = {false, false, false, false};
+  const int which = a->layout * 2 + (a->dtype == INQ_F16 ? 0 : 1);
+  if (shared > 48 * 1024 && !raised[which]) {
+    INQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4)));
+    raised[which] = true;
   }
+  kernel<<<grid, kThreads, shared, stream>>>(P);
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
 }

@@ -48,8 +48,8 @@ def test_packed_gqa_with_sink_and_unsealed_tail(dtype, fraction, policy):
     cfg = CodecConfig(salient_fraction=fraction, donor_policy=policy)
     ks = [_random(921 + i, (1, 4, 256, 128), dtype) for i in range(3)]
     vs = [_random(1921 + i, (1, 4, 256, 128), dtype) for i in range(3)]
-    for k in ks:
-        k[..., 5:8] *= 12
+    ks = [oracle.round_to_dtype(k * np.where((np.arange(128) >= 5) & (np.arange(128) < 8), 12, 1).astype(np.float32), dtype)
+          for k in ks]
     keys = [quantize(to_device(k, dtype), cfg) for k in ks]
     values = [quantize_values(to_device(v, dtype)) for v in vs]
     sink_k, sink_v = _random(1, (1, 4, 4, 128), dtype), _random(2, (1, 4, 4, 128), dtype)
@@ -87,7 +87,7 @@ def test_dense_only_before_any_block_is_sealed(tokens):
 def test_no_dense_tensors_and_nondefault_packed_block_length(tokens, heads, q_heads):
     CodecConfig, quantize, quantize_values, _, _, packed_decode = _mods()
     k, v = _random(10, (1, heads, tokens, 128), "float16"), _random(11, (1, heads, tokens, 128), "float16")
-    k[..., 100] *= 9
+    k[..., 100] *= 8   # power of two: stays exactly representable
     q = _random(12, (q_heads, 128), "float16")
     actual = packed_decode(to_device(q, "float16").view(1, q_heads, 1, 128),
                            [quantize(to_device(k, "float16"), CodecConfig(salient_fraction=0.125))],
@@ -118,7 +118,7 @@ def test_growing_state_matches_fresh_state_and_rejects_replacement():
     query = to_device(q).view(1, 8, 1, 128)
     for i in range(11):
         k = _random(100 + i, (1, 2, 32, 128), "bfloat16")
-        k[..., 127] *= 20   # source / donor indices at the signed-byte boundary
+        k[..., 127] *= 16   # source / donor indices at the signed-byte boundary
         v = _random(200 + i, (1, 2, 32, 128), "bfloat16")
         raw.append((k, v))
         keys.append(quantize(to_device(k), CodecConfig(donor_policy="min_error")))
@@ -183,7 +183,7 @@ def test_argument_validation():
     CodecConfig, quantize, quantize_values, PackedDecodeState, _, packed_decode = _mods()
     q = torch.zeros(1, 4, 1, 128, device="cuda", dtype=torch.bfloat16)
     kv = torch.zeros(1, 2, 8, 128, device="cuda", dtype=torch.bfloat16)
-    with pytest.raises(ValueError, match="at least one"):
+    with pytest.raises(ValueError, match="nonempty KV head count"):
         packed_decode(q, [], [])
     with pytest.raises(ValueError, match="both"):
         packed_decode(q, [], [], residual_key=kv)
