@@ -1,0 +1,382 @@
+#!/usr/bin/env python
+"""Benchmark of the packed-KV hot path on B200.
+
+Workload (N=1): Qwen2.5-7B-shaped single-request decode -- 28 layers x 4 KV heads x 128
+head_dim, 28 query heads, 32768 history tokens packed K4/V2 (127 sealed blocks of 256 per
+layer), bf16 attention sink (4) and recent tail (252, growing by one per step).  A "step"
+is one decode step over ALL layers: the new token's K/V is appended to every layer's tail
+and single-query GQA attention runs over every layer's packed history, sink and tail.
+Inputs are seeded synthetic tensors with the reference workload's shapes and outlier
+statistics (no model weights or datasets are used).
+
+  python bench.py --gpus N --steps K --warmup W            this repository's CUDA path
+  python bench.py --impl reference ...                     the CPU restatement of the reference
+                                                           path, timed on the host cores
+
+With N > 1 (torchrun, one rank per GPU) every rank serves its own request of the same shape
+(requests shard across GPUs with no collective): weak scaling, value = sum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "inquant-open-source_b200"))
+
+LAYERS, KV_HEADS, Q_HEADS, DIM = 28, 4, 28, 128
+CONTEXT = 32768
+BLOCK, RESIDUAL, SINK = 256, 128, 4
+METRIC = "packed-KV decode attn HBM GB/s at 32K ctx (all 28 layers per step)"
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples the SM clock and the throttle reasons through NVML (read-only queries) from a
+    background thread while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.max_mhz, self._stop, self._thread, self._nvml = None, threading.Event(), None, None
+
+    def __enter__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = int(visible.split(",")[self.index]) if visible and visible.split(",")[self.index].isdigit() else self.index
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._nvml = pynvml
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        except Exception:
+            self._nvml = None
+        return self
+
+    def _run(self):
+        nv = self._nvml
+        names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            time.sleep(self.period)
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+
+    def summary(self):
+        clocks = sorted(self.samples)
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(clocks)}
+
+
+# --------------------------------------------------------------------------- CUDA arm
+def build_request(torch, device, seed_base):
+    """Prefill all layers through the public cache API; returns the cache and encode timings."""
+    import workloads
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error", donor_backend="triton"), block_size=BLOCK,
+                                     residual_length=RESIDUAL, sink_tokens=SINK, value_bits=2, value_group_size=64,
+                                     validate_positions=False))
+    encode_ms = 0.0
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for layer in range(LAYERS):
+        k, v = workloads.make_kv_torch(seed_base + layer, KV_HEADS, CONTEXT, device)
+        if layer == 0:  # warm the encoder kernels on a throw-away cache
+            warm = InQuantCache(cache.config)
+            warm.update(k, v, 0)
+            del warm
+        torch.cuda.synchronize()
+        start.record()
+        cache.update(k, v, layer)
+        stop.record()
+        torch.cuda.synchronize()
+        encode_ms += start.elapsed_time(stop)
+        del k, v
+    return cache, encode_ms
+
+
+def run_cuda(args):
+    import torch
+    import torch.distributed as dist
+    from inquant import _native
+    from inquant.batched import DecodeBatch, SequenceState
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the packed-KV path has no CPU fallback")
+    _native.library()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    cache, encode_ms = build_request(torch, device, seed_base=1000 * rank)
+    batch = DecodeBatch([SequenceState.from_cache_layer(cache, i) for i in range(LAYERS)], Q_HEADS, torch.bfloat16)
+    total_steps = args.warmup + args.steps
+    gen = torch.Generator(device=device).manual_seed(7 + rank)
+    # per step and layer: 28 query heads, then the new token's 4 key heads and 4 value heads
+    inputs = torch.randn((total_steps, LAYERS, Q_HEADS + 2 * KV_HEADS, DIM), device=device, generator=gen).bfloat16()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing (inputs already in HBM): per step one staging copy, then the
+    # CUDA graph of {append kernel, decode kernel}
+    for i in range(args.warmup):
+        batch.inputs.copy_(inputs[i])
+        batch.step()
+    torch.cuda.synchronize()
+    use_graph = not args.no_graph
+    if use_graph:
+        batch.capture()
+    run_step = batch.replay if use_graph else batch.step
+    for i in range(args.warmup):
+        if batch.capacity_left < 1:
+            batch.rewind()
+        batch.inputs.copy_(inputs[i])
+        run_step()
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    byte_samples = []
+    launches_before = batch.launches
+    with ClockSampler(local) as clocks:
+        t0.record()
+        for i in range(args.steps):
+            if batch.capacity_left < 1:
+                batch.rewind()
+            batch.inputs.copy_(inputs[args.warmup + i])
+            run_step()
+            byte_samples.append(batch._appended)
+        t1.record()
+        barrier()
+        # ---- the decode kernel alone, back to back, for the roofline figure
+        reps = max(args.steps, 20)
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            batch.attend()
+        torch.cuda.synchronize()
+        k0.record()
+        for _ in range(reps):
+            batch._launch_attend()
+        k1.record()
+        torch.cuda.synchronize()
+    elapsed_ms = t0.elapsed_time(t1)
+    launches = batch.launches - launches_before - 3
+    kernel_ms = k0.elapsed_time(k1) / reps
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    base = batch.algorithmic_bytes()
+    per_token = KV_HEADS * DIM * 2 * 2 * LAYERS
+    mean_appended = sum(byte_samples) / len(byte_samples) - batch._appended
+    mean_bytes = dict(base)
+    mean_bytes["dense"] = base["dense"] + mean_appended * per_token
+    mean_bytes["total"] = base["total"] + mean_appended * per_token
+    kernel_bytes = base["total"]
+    ms_per_step = elapsed_ms / args.steps
+    value = world * mean_bytes["total"] / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public API with host buffers
+    batch.rewind()
+    h_in = inputs.cpu().pin_memory()
+    h_out = torch.empty((LAYERS, Q_HEADS, DIM), dtype=torch.bfloat16).pin_memory()
+
+    def host_step(i):
+        if batch.capacity_left < 1:
+            batch.rewind()
+        batch.inputs.copy_(h_in[i], non_blocking=True)
+        out = run_step()
+        h_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the next token depends on this result
+
+    for i in range(args.warmup):
+        host_step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.perf_counter()
+    e0.record()
+    for i in range(args.steps):
+        host_step(args.warmup + i)
+    e1.record()
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - wall0) * 1e3) / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = h_in[0].numel() * 2
+    d2h = h_out.numel() * 2
+    status = _native.take_status(device)
+
+    peak, peak_kind = measured_peak_gbs()
+    achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 query/sink/tail; u4 keys and u2 values dequantised to fp16 operands, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "config 1: Qwen2.5-7B-shaped single-request decode, 28 layers x 4 KV heads x 128, 28 query heads, "
+                               "32768-token history packed K4/V2 (127 blocks of 256), bf16 sink 4 + tail 252 growing by 1/step",
+                   "requests_per_gpu": 1, "launch": "CUDA graph of append + decode kernels" if use_graph else "eager", "l2": "inputs larger than L2 (402 MB read per step vs 126 MB L2)",
+                   "sharding": "one request per GPU, no collective" if world > 1 else "single GPU"},
+        "us_per_step": round(ms_per_step * 1e3, 2),
+        "packed_gbs": round(world * (mean_bytes["packed"] + mean_bytes["metadata"]) / (ms_per_step * 1e-3) / 1e9, 1),
+        "algorithmic_bytes_per_step": {k: int(v) for k, v in mean_bytes.items()},
+        "encode_tokens_per_s": round(world * CONTEXT / (encode_ms * 1e-3), 1),
+        "encode_ms_all_layers": round(encode_ms, 3),
+        "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": round(achieved, 1), "peak": peak,
+                     "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_source": peak_kind,
+                     "us_per_launch": round(kernel_ms * 1e3, 2), "traffic": DECODE_TRAFFIC_BYTES},
+        "e2e": {"value": round(world * mean_bytes["total"] / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+                "us_per_step": round(e2e_ms * 1e3, 2), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,   # append + decode kernels of this library (torch's staging copy not counted)
+        "clocks": clocks.summary(),
+        "device_status": status,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(sample_layers=1)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one decode_kernel launch of this workload from an ncu capture;
+# see profiles/decode_kernel_cfg1.md.  None until a capture of the current kernel exists.
+DECODE_TRAFFIC_BYTES = None
+
+
+# --------------------------------------------------------------------------- CPU arm (oracle port)
+def cpu_layer(seed):
+    """Encode one layer of the workload with the CPU oracle; returns what its decode needs."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import inquant_oracle as oracle
+    import workloads
+    k, v = workloads.make_kv(seed, KV_HEADS, CONTEXT, outliers=6, adjacent=3)
+    take, blocks, tail = oracle.seal_plan(0, 0, CONTEXT, sink_tokens=SINK, residual_length=RESIDUAL, block_size=BLOCK)
+    body = slice(take, take + blocks * BLOCK)
+    shape = (KV_HEADS, blocks, BLOCK, DIM)
+    kb = np.ascontiguousarray(k[0][:, body].reshape(shape).transpose(1, 0, 2, 3))
+    vb = np.ascontiguousarray(v[0][:, body].reshape(shape).transpose(1, 0, 2, 3))
+    t0 = time.perf_counter()
+    pk = oracle.quantize_k4(kb, "bfloat16", 8, 0.125, "min_error")
+    pv = oracle.quantize_values(vb, "bfloat16", 2, 64)
+    encode_s = time.perf_counter() - t0
+    dense = (k[0][:, :take], v[0][:, :take], k[0][:, take + blocks * BLOCK:], v[0][:, take + blocks * BLOCK:])
+    return oracle, pk, pv, dense, blocks, encode_s
+
+
+def cpu_decode_once(oracle, pk, pv, dense, q):
+    import numpy as np
+    sk, sv, tk, tv = dense
+    keys = oracle.dequantize_k4(pk).transpose(1, 0, 2, 3).reshape(KV_HEADS, -1, DIM)
+    vals = oracle.dequantize_values(pv).transpose(1, 0, 2, 3).reshape(KV_HEADS, -1, DIM)
+    keys = np.concatenate([sk, keys, tk], 1)
+    vals = np.concatenate([sv, vals, tv], 1)
+    return oracle.attention_decode(q, keys, vals, DIM ** -0.5)
+
+
+def layer_bytes(blocks, tail):
+    return (KV_HEADS * blocks * BLOCK * 104 + KV_HEADS * blocks * 608 + (SINK + tail) * KV_HEADS * DIM * 2 * 2
+            + Q_HEADS * DIM * 2 * 2)
+
+
+def cpu_baseline(sample_layers=1, repeats=3):
+    import workloads
+    oracle, pk, pv, dense, blocks, encode_s = cpu_layer(0)
+    q = workloads.make_query(0, Q_HEADS)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        cpu_decode_once(oracle, pk, pv, dense, q)
+        times.append(time.perf_counter() - t0)
+    best = sorted(times)[len(times) // 2]
+    nbytes = layer_bytes(blocks, dense[2].shape[1])
+    return {"value": round(nbytes / best / 1e9, 4), "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": f"{sample_layers} of {LAYERS} layers of the same workload (32768 tokens, 4 KV heads): dequantise every "
+                      f"block + float64 attention with the numpy oracle, median of {repeats}; throughput is per byte so the "
+                      "sample is not scaled",
+            "us_per_step_extrapolated": round(best * LAYERS * 1e6, 1),
+            "encode_tokens_per_s": round(CONTEXT / (encode_s * LAYERS), 1)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    import workloads
+    oracle, pk, pv, dense, blocks, encode_s = cpu_layer(0)
+    q = workloads.make_query(0, Q_HEADS)
+    for _ in range(min(args.warmup, 1)):
+        cpu_decode_once(oracle, pk, pv, dense, q)
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_decode_once(oracle, pk, pv, dense, q)
+    per = (time.perf_counter() - t0) / steps
+    nbytes = layer_bytes(blocks, dense[2].shape[1])
+    value = round(nbytes / per / 1e9, 4)
+    sample = ("each step = ONE of the 28 layers (32768 tokens, 4 KV heads): numpy restatement of the reference's torch CPU "
+              f"path (dequantise all blocks + attention), {steps} timed steps; GB/s is per byte, so not scaled")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": round(per * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64 attention over bf16-rounded dequantised K/V", "data": "synthetic",
+        "config": {"workload": "config 1 (one layer per step on the host cores)"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "encode_tokens_per_s": round(CONTEXT / (encode_s * LAYERS), 1),
+    }))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="cuda", choices=("cuda", "reference"))
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-graph", action="store_true", help="launch the two kernels eagerly instead of replaying a CUDA graph")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_cuda(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -205,6 +205,11 @@ typedef struct {
   int32_t* status;
 } inq_append_args_t;
 int inq_append_token(const inq_append_args_t* args /* host */, inq_stream_t stream);
+/* The same for `count` independent sequences (one layer of one request each) in one launch;
+ * the records live in DEVICE memory and must satisfy the alignment rules above (they are
+ * not re-checked); their `status` field is ignored in favour of the argument. */
+int inq_append_token_batch(const inq_append_args_t* records_device, int32_t count, int32_t* status,
+                           inq_stream_t stream);
 
 #ifdef __cplusplus
 }

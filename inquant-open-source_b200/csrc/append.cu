@@ -24,7 +24,7 @@ struct AppendParams {
 
 // One CTA moves the whole token (heads * row bytes * 2 is a couple of KB), so the device-side
 // position can be read, used and advanced without a grid-wide ordering problem.
-__global__ void __launch_bounds__(256) append_token_kernel(AppendParams p) {
+__device__ __forceinline__ void append_one(const AppendParams& p) {
   __shared__ int s_position;
   if (threadIdx.x == 0) s_position = p.tail_counter ? *p.tail_counter : p.tail_position;
   __syncthreads();
@@ -45,6 +45,34 @@ __global__ void __launch_bounds__(256) append_token_kernel(AppendParams p) {
     }
   }
   if (p.tail_counter && threadIdx.x == 0) *p.tail_counter = position + 1;
+}
+
+__global__ void __launch_bounds__(256) append_token_kernel(AppendParams p) { append_one(p); }
+
+// Batched form: CTA i appends the token described by the i-th record of a device array
+// (byte strides, as in inq_append_args_t).
+__global__ void __launch_bounds__(256) append_batch_kernel(const inq_append_args_t* records, int* status) {
+  const inq_append_args_t& a = records[blockIdx.x];
+  AppendParams p;
+  p.key = (const uint4*)a.key;
+  p.value = (const uint4*)a.value;
+  p.src_stride_h = a.src_stride_h / 16;
+  p.tail_key = (uint4*)a.tail_key;
+  p.tail_value = (uint4*)a.tail_value;
+  p.tail_stride_h = a.tail_stride_h / 16;
+  p.tail_stride_t = a.tail_stride_t / 16;
+  p.tail_position = a.tail_position;
+  p.tail_counter = a.tail_counter;
+  p.tail_capacity = a.tail_capacity;
+  p.sink_key = (uint4*)a.sink_key;
+  p.sink_value = (uint4*)a.sink_value;
+  p.sink_stride_h = a.sink_stride_h / 16;
+  p.sink_stride_t = a.sink_stride_t / 16;
+  p.sink_position = a.sink_position;
+  p.heads = a.heads;
+  p.row_vectors = a.row_bytes / 16;
+  p.status = status;
+  append_one(p);
 }
 
 }  // namespace inq
@@ -82,6 +110,14 @@ extern "C" int inq_append_token(const inq_append_args_t* a, inq_stream_t stream)
   p.row_vectors = a->row_bytes / 16;
   p.status = a->status;
   append_token_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(p);
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}
+
+extern "C" int inq_append_token_batch(const inq_append_args_t* records_device, int32_t count, int32_t* status,
+                                      inq_stream_t stream) {
+  if (!records_device || count < 1 || !status) return INQ_ERR_ARGUMENT;
+  append_batch_kernel<<<(unsigned)count, 256, 0, (cudaStream_t)stream>>>(records_device, status);
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
 }

@@ -99,7 +99,7 @@ def library() -> ctypes.CDLL:
 EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
     "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
-    "inq_decode_attention", "inq_decode_plan_parts", "inq_decode_workspace_floats", "inq_append_token",
+    "inq_decode_attention", "inq_decode_plan_parts", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
 )
 
 
@@ -114,6 +114,7 @@ SIGNATURES = {
     "inq_build_roles": [_P, _P, _I, _L, _I, _I, _P, _I, _P],
     "inq_decode_attention": [_P, _P],
     "inq_append_token": [_P, _P],
+    "inq_append_token_batch": [_P, _I, _P, _P],
     "inq_decode_plan_parts": [_I, _I, _I, _L],
 }
 

@@ -1,0 +1,234 @@
+"""One-launch decode step for many (request, layer) sequences.
+
+The reference decodes layer by layer (``qwen_fused.py:138-158``), two Triton launches per
+layer.  A layer of a 32K-token request is only ~14 MB of packed cache, i.e. ~2 microseconds
+of HBM time on a B200, so per-layer launches are latency-bound.  ``DecodeBatch`` keeps a
+device-resident array of sequence descriptors (C ABI ``inq_decode_seq_t``) and runs
+
+    step():  1 launch  inq_append_token_batch   (new K/V token of every sequence -> its tail)
+             1 launch  inq_decode_attention     (all sequences, fused split-KV merge)
+
+with tail lengths held in device counters, so a decode loop makes no host round trip and
+can be captured in a CUDA graph.  Sequences are independent: this is also the collective-
+free batched-serving path (requests sharded across GPUs simply build one batch per rank).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _native as N
+from .triton_attention import PackedDecodeState, plan_parts
+
+
+@dataclass
+class SequenceState:
+    """One (request, layer): packed blocks plus exact sink and tail buffers."""
+
+    decode_state: PackedDecodeState          # pointer table + role maps of the sealed blocks
+    sink_key: torch.Tensor | None            # [1, H, sink, 128] (views allowed)
+    sink_value: torch.Tensor | None
+    tail_key_buffer: torch.Tensor            # [1, H, capacity, 128]
+    tail_value_buffer: torch.Tensor
+    tail_count: int
+
+    @classmethod
+    def from_cache_layer(cls, cache, layer_idx: int) -> "SequenceState":
+        layer = cache._layers[layer_idx]
+        state = PackedDecodeState(layer.key_blocks, layer.value_blocks)
+        if layer.tail_key_buffer is None:
+            raise ValueError("the layer has no tail buffer yet")
+        return cls(state, layer.sink_key, layer.sink_value, layer.tail_key_buffer, layer.tail_value_buffer,
+                   layer.tail_count)
+
+
+def _struct_array_to_device(array, device) -> torch.Tensor:
+    raw = bytes(array)
+    return torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
+
+
+class DecodeBatch:
+    """Device-resident descriptors, queries, outputs and scratch for a fixed set of sequences."""
+
+    def __init__(self, sequences: list[SequenceState], q_heads: int, dtype: torch.dtype = torch.bfloat16,
+                 scale: float | None = None, n_parts: int | None = None):
+        if not sequences:
+            raise ValueError("at least one sequence is required")
+        first = sequences[0].decode_state
+        self.sequences = sequences
+        self.device = sequences[0].tail_key_buffer.device
+        self.kv_heads = sequences[0].tail_key_buffer.shape[1]
+        if q_heads % self.kv_heads:
+            raise ValueError("query_heads must be divisible by the KV head count")
+        if dtype not in (torch.float16, torch.bfloat16):
+            raise NotImplementedError("batched decode supports fp16 and bf16")
+        self.q_heads, self.dtype = q_heads, dtype
+        self.q_per_kv = q_heads // self.kv_heads
+        self.scale = 128 ** -0.5 if scale is None else float(scale)
+        self.block_tokens = first._packed_tokens
+        self.n_pad = first._salient
+        n = len(sequences)
+        # one staging tensor per step: [query heads | new key heads | new value heads] x 128
+        self.inputs = torch.zeros((n, q_heads + 2 * self.kv_heads, 128), dtype=dtype, device=self.device)
+        self.queries = self.inputs[:, :q_heads]
+        self.new_keys = self.inputs[:, q_heads:q_heads + self.kv_heads]
+        self.new_values = self.inputs[:, q_heads + self.kv_heads:]
+        self.outputs = torch.empty((n, q_heads, 128), dtype=dtype, device=self.device)
+        self.tail_counters = torch.tensor([s.tail_count for s in sequences], dtype=torch.int32).to(self.device)
+        self._build_descriptors()
+        slices = max(len(s.decode_state.key_blocks) * ((self.block_tokens + 15) // 16)
+                     + 4 * (1 + (s.tail_key_buffer.shape[2] + 15) // 16) for s in sequences)
+        self.n_parts = n_parts or plan_parts(self.kv_heads, self.q_per_kv, slices, n)
+        tiles = (self.q_per_kv + 7) // 8
+        floats = N.library().inq_decode_workspace_floats(n, self.kv_heads, self.q_per_kv, self.n_parts)
+        self.partials = torch.empty(floats, dtype=torch.float32, device=self.device)
+        self.counters = torch.zeros(n * self.kv_heads * tiles, dtype=torch.int32, device=self.device)
+        self.launches = 0
+        self._initial_counters = self.tail_counters.clone()
+        self._prepare_launch_arguments()
+
+    def _build_descriptors(self) -> None:
+        n = len(self.sequences)
+        es = self.queries.element_size()
+        seqs = (N.DecodeSeq * n)()
+        apps = (N.AppendArgs * n)()
+        for i, s in enumerate(self.sequences):
+            st = s.decode_state
+            if st._packed_tokens != self.block_tokens or st._salient != self.n_pad:
+                raise ValueError("all sequences must share block length and salient-channel count")
+            d = seqs[i]
+            d.query = self.queries[i].data_ptr()
+            d.output = self.outputs[i].data_ptr()
+            d.query_head_stride = 128
+            n_blocks = len(st.key_blocks)
+            d.table = st._tables.data_ptr() if n_blocks else None
+            d.roles = st._key_map.data_ptr() if n_blocks else None
+            d.n_blocks = n_blocks
+            if s.sink_key is not None and s.sink_key.shape[2]:
+                for t in (s.sink_key, s.sink_value):
+                    if not N.dense_rows_aligned(t):
+                        raise ValueError("sink rows must be 16-byte aligned")
+                d.sink_key, d.sink_value = s.sink_key.data_ptr(), s.sink_value.data_ptr()
+                d.sink_key_stride_h, d.sink_key_stride_t = s.sink_key.stride(1), s.sink_key.stride(2)
+                d.sink_value_stride_h, d.sink_value_stride_t = s.sink_value.stride(1), s.sink_value.stride(2)
+                d.sink_tokens = s.sink_key.shape[2]
+            tk, tv = s.tail_key_buffer, s.tail_value_buffer
+            for t in (tk, tv):
+                if not N.dense_rows_aligned(t) or t.dtype != self.dtype:
+                    raise ValueError("tail buffers must match the batch dtype with 16-byte aligned rows")
+            d.tail_key, d.tail_value = tk.data_ptr(), tv.data_ptr()
+            d.tail_key_stride_h, d.tail_key_stride_t = tk.stride(1), tk.stride(2)
+            d.tail_value_stride_h, d.tail_value_stride_t = tv.stride(1), tv.stride(2)
+            d.tail_tokens = s.tail_count
+            d.tail_tokens_device = self.tail_counters[i:].data_ptr()
+            a = apps[i]
+            a.key, a.value, a.src_stride_h = self.new_keys[i].data_ptr(), self.new_values[i].data_ptr(), 128 * es
+            a.tail_key, a.tail_value = tk.data_ptr(), tv.data_ptr()
+            a.tail_stride_h, a.tail_stride_t = tk.stride(1) * es, tk.stride(2) * es
+            a.tail_position, a.tail_capacity = s.tail_count, tk.shape[2]
+            a.tail_counter = self.tail_counters[i:].data_ptr()
+            a.sink_position = -1
+            a.heads, a.row_bytes = self.kv_heads, 128 * es
+        self._seq_records = _struct_array_to_device(seqs, self.device)
+        self._append_records = _struct_array_to_device(apps, self.device)
+
+    @property
+    def capacity_left(self) -> int:
+        """Appends that still fit every tail buffer (host-side bookkeeping)."""
+        return self._capacity - self._appended
+
+    def _prepare_launch_arguments(self) -> None:
+        n = len(self.sequences)
+        self._capacity = min(s.tail_key_buffer.shape[2] - s.tail_count for s in self.sequences)
+        self._appended = 0
+        args = N.DecodeArgs()
+        args.n_seq, args.seqs_device = n, self._seq_records.data_ptr()
+        args.kv_heads, args.q_per_kv = self.kv_heads, self.q_per_kv
+        args.block_tokens, args.n_pad = self.block_tokens, self.n_pad
+        args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[self.dtype], self.scale
+        args.n_parts = self.n_parts
+        args.partials, args.counters = self.partials.data_ptr(), self.counters.data_ptr()
+        args.status = N.status_word(self.device).data_ptr()
+        self._decode_args = args
+        self._decode_args_ref = ctypes.byref(args)
+        self._status_pointer = N.status_word(self.device).data_ptr()
+        self._graph = None
+
+    def _launch_append(self) -> None:
+        rc = N.library().inq_append_token_batch(self._append_records.data_ptr(), len(self.sequences),
+                                                self._status_pointer, N.stream_pointer(self.device))
+        if rc:
+            N.check(rc, "inq_append_token_batch")
+
+    def _launch_attend(self) -> None:
+        rc = N.library().inq_decode_attention(self._decode_args_ref, N.stream_pointer(self.device))
+        if rc:
+            N.check(rc, "inq_decode_attention")
+
+    def append(self) -> None:
+        """Write ``new_keys`` / ``new_values`` at the end of every tail and advance the device counters."""
+        if self.capacity_left < 1:
+            raise RuntimeError("a tail buffer is full: seal a block before appending")
+        self._launch_append()
+        self._appended += 1
+        self.launches += 1
+
+    def attend(self) -> torch.Tensor:
+        """Attention of ``queries`` over every sequence; returns ``outputs`` ([n, q_heads, 128])."""
+        self._launch_attend()
+        self.launches += 1
+        return self.outputs
+
+    def step(self) -> torch.Tensor:
+        """One decode step: append the new token of every sequence, then attend."""
+        self.append()
+        return self.attend()
+
+    def capture(self) -> None:
+        """Record append + attend into a CUDA graph; ``replay`` then costs one graph launch.
+        Run at least one eager ``step`` first (the first launch sets kernel attributes)."""
+        graph = torch.cuda.CUDAGraph()
+        counters = self.tail_counters.clone()
+        with torch.cuda.graph(graph):
+            self._launch_append()
+            self._launch_attend()
+        self.tail_counters.copy_(counters)  # capture does not execute, but keep the state explicit
+        self._graph = graph
+
+    def replay(self) -> torch.Tensor:
+        if self._graph is None:
+            raise RuntimeError("call capture() first")
+        if self.capacity_left < 1:
+            raise RuntimeError("a tail buffer is full: seal a block before appending")
+        self._graph.replay()
+        self._appended += 1
+        self.launches += 2
+        return self.outputs
+
+    def rewind(self, appended: int = 0) -> None:
+        """Reset every tail to its length at construction plus ``appended`` tokens (benchmarks
+        re-use the same tail slots instead of sealing)."""
+        self.tail_counters.copy_(self._initial_counters + appended)
+        self._appended = appended
+
+    @property
+    def tail_tokens(self) -> list[int]:
+        return [s.tail_count + self._appended for s in self.sequences]
+
+    def algorithmic_bytes(self) -> dict[str, int]:
+        """Bytes one ``attend`` must read/write: packed blocks, their metadata, exact sink and
+        tail, queries and outputs (the model used for the roofline figures)."""
+        h, t = self.kv_heads, self.block_tokens
+        es = self.queries.element_size()
+        packed = meta = dense = 0
+        for s in self.sequences:
+            nb = len(s.decode_state.key_blocks)
+            packed += h * nb * t * (64 + 32 + 8)
+            meta += h * nb * (512 + self.n_pad * 2 + self.n_pad * 4)
+            sink = 0 if s.sink_key is None else s.sink_key.shape[2]
+            dense += (sink + s.tail_count + self._appended) * h * 128 * es * 2
+        qo = len(self.sequences) * self.q_heads * 128 * es * 2
+        return {"packed": packed, "metadata": meta, "dense": dense, "query_output": qo,
+                "total": packed + meta + dense + qo}
