@@ -208,6 +208,12 @@ def run_cuda(args):
     value = world * mean_bytes["total"] / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end through the public API with host buffers
+    if args.skip_e2e:
+        if rank == 0:
+            print(json.dumps({"layers": LAYERS, "us_per_step": round(ms_per_step * 1e3, 2),
+                              "decode_us_per_launch": round(kernel_ms * 1e3, 2), "kernel_bytes": kernel_bytes,
+                              "encode_ms": round(encode_ms, 3)}))
+        return
     batch.rewind()
     h_in = inputs.cpu().pin_memory()
     h_out = torch.empty((LAYERS, Q_HEADS, DIM), dtype=torch.bfloat16).pin_memory()
@@ -370,7 +376,10 @@ def main():
     parser.add_argument("--impl", default="cuda", choices=("cuda", "reference"))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-graph", action="store_true", help="launch the two kernels eagerly instead of replaying a CUDA graph")
+    parser.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for profiler captures (default: the full 28)")
+    parser.add_argument("--skip-e2e", action="store_true", help="profiler captures: skip the host-buffer leg")
     args = parser.parse_args()
+    globals()["LAYERS"] = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -176,16 +176,26 @@ typedef struct {
   float scale;
   int64_t page_bytes;
   int64_t page_offsets[6];
-  int32_t n_parts;   /* split of every (sequence, KV head): see inq_decode_plan_parts */
-  float* partials;   /* scratch: inq_decode_workspace_floats(...) floats, contents undefined */
-  int32_t* counters; /* scratch: n_seq * kv_heads * ceil(q_per_kv/8) ints, ZERO on entry, left zero */
-  int32_t* status;   /* device status word */
+  /* Work is balanced over the whole batch: the packed slices of all pairs
+   * (sequence, KV head, tile of 8 query heads), in that order, form one list that is cut into
+   * equal ranges, one per resident CTA.  pair_starts[p] = sum of inq_decode_units(n_blocks of
+   * the pair's sequence, block_tokens) over pairs before p; [n_pairs + 1] int64 in DEVICE
+   * memory.  NULL is allowed when every sequence holds `uniform_blocks` blocks (with
+   * seq_host the count is taken from the descriptor). */
+  const int64_t* pair_starts;
+  int64_t total_units;      /* pair_starts[n_pairs]; ignored without pair_starts */
+  int32_t uniform_blocks;
+  float* partials;          /* scratch, contents undefined on entry and exit */
+  int64_t partials_floats;  /* its size: at least inq_decode_workspace_floats(n_pairs, total_units) */
+  int32_t* counters;        /* scratch: n_pairs ints, ZERO on entry, left zero on exit */
+  int32_t* status;          /* device status word */
 } inq_decode_args_t;
 int inq_decode_attention(const inq_decode_args_t* args /* host */, inq_stream_t stream);
-/* Number of parts that fills the device for this batch (max_slices = 16-token slices of the
- * longest sequence), and the scratch size that goes with it. */
-int inq_decode_plan_parts(int32_t n_seq, int32_t kv_heads, int32_t q_per_kv, int64_t max_slices);
-int64_t inq_decode_workspace_floats(int32_t n_seq, int32_t kv_heads, int32_t q_per_kv, int32_t n_parts);
+/* Work units (32-token slices, at least 1) of one pair whose sequence holds n_blocks blocks. */
+int64_t inq_decode_units(int32_t n_blocks, int32_t block_tokens);
+/* Scratch floats that suffice for a launch with n_pairs pairs and total_units work units on
+ * the current device. */
+int64_t inq_decode_workspace_floats(int32_t n_pairs, int64_t total_units);
 
 /* ---------------------------------------------------------------- incremental append
  * Writes the key and value rows of ONE new token (all KV heads) at `tail_position` of the

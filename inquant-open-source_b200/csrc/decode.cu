@@ -32,14 +32,15 @@ namespace inq {
 
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 4;
-constexpr int kStageK = 1024, kStageV = 512, kStageP = 128;
+constexpr int kStages = 3;
+constexpr int kSliceTokens = 32;                    // tokens staged and processed per loop iteration
+constexpr int kStageK = 2048, kStageV = 1024, kStageP = 256;
 constexpr int kStageBytes = kStageK + kStageV + kStageP;
 constexpr int kRecordStride = 132;                  // floats per query head: acc[128], m, l, pad
 constexpr int kRecordFloats = 8 * kRecordStride;    // one partial record (8 query heads)
 constexpr int kQChunk = 36;                         // padded 32-float chunk of the staged query
 constexpr float kNegBig = -1.0e30f;
-constexpr int kWarpFixed = 512 + 512 + 256 + 256 + 64 + 64;   // per-warp scratch before the per-group parts
+constexpr int kWarpFixed = 2048 + 256 + 256 + 64 + 64;   // per-warp scratch before the per-group parts
 
 __host__ __device__ constexpr int warp_smem_bytes(int groups) {
   return kWarpFixed + groups * (256 + 4096) + kStages * kStageBytes;
@@ -64,7 +65,10 @@ static_assert(sizeof(SeqDesc) == sizeof(inq_decode_seq_t), "SeqDesc must mirror 
 struct DecodeParams {
   const SeqDesc* seqs;
   SeqDesc one;
-  int n_seq, H, G, T, n_pad, n_parts;
+  int n_seq, H, G, T, n_pad;
+  int n_ctas, n_pairs;
+  long long per_cta, total_units, uniform_units;   // flat work decomposition
+  const long long* pair_starts;                    // [n_pairs + 1] or nullptr when every pair has uniform_units
   float scale_log2e;
   long long page_bytes;
   int off_ks, off_km, off_kp, off_vp, off_vs, off_vo;
@@ -116,6 +120,33 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N));
 }
+// Shared-memory loads through 32-bit shared addresses with compile-time byte offsets.
+template <int OFF>
+__device__ __forceinline__ uint4 lds128(unsigned addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 lds64(unsigned addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ unsigned lds32(unsigned addr) {
+  unsigned v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+// D = A*B with a zero accumulator (first step of a chain: nothing to keep live or to clear)
+__device__ __forceinline__ void mma_f16_first(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                              unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%10,%10,%10,%10};"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -165,31 +196,41 @@ __device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const l
   return out;
 }
 
-// Issue the asynchronous copies of one packed slice (16 tokens from `tok0`) into a stage.
-__device__ __forceinline__ void stage_slice(unsigned char* stage, const BlockPtrs& B, int tok0, int T, int lane) {
-  const int r = lane >> 2, j = lane & 3;
-  const int last = T - 1;
-  const int t_lo = min(tok0 + r, last), t_hi = min(tok0 + r + 8, last);
-  cp_async16(stage + lane * 16, B.kp + (long long)t_lo * 64 + j * 16);
-  cp_async16(stage + 512 + lane * 16, B.kp + (long long)t_hi * 64 + j * 16);
-  {
-    const int t = lane >> 1, half = lane & 1;
-    const int tv = min(tok0 + t, last);
-    // swap the two 16-byte halves of tokens 4..7 and 12..15: the later word reads of tokens
-    // 2j, 2j+1, 2j+8, 2j+9 then fall into distinct banks
-    cp_async16(stage + kStageK + (t * 2 + (half ^ ((t >> 2) & 1))) * 16, B.vp + (long long)tv * 32 + half * 16);
-  }
-  {
-    const int t = lane & 15;
-    const int tp = min(tok0 + t, last);
-    const unsigned char* src = (lane < 16 ? B.vs : B.vo) + (long long)tp * 4;
-    cp_async4(stage + kStageK + kStageV + (lane < 16 ? 0 : 64) + t * 4, src);
+// Issue the asynchronous copies of one packed slice (32 tokens from `tok0`) into a stage.
+// Stage layout: K nibbles [32 tokens][64 B]; V codes [32 tokens][2 x 16 B] with the two halves
+// of tokens 4..7 (mod 8) swapped so that the later word reads of tokens 2j, 2j+1, 2j+8, 2j+9
+// fall into distinct banks; V scale pairs [32] and V offset pairs [32] (4 B each).
+__device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned char* kp, const unsigned char* vp,
+                                            const unsigned char* vs, const unsigned char* vo, int tok0, int T, int lane) {
+  const int v_dst = kStageK + (((lane >> 1) * 2 + ((lane & 1) ^ ((lane >> 3) & 1))) << 4);
+  if (tok0 + kSliceTokens <= T) {
+    // all 32 tokens exist: K tile, V tile and parameter vectors are contiguous in global memory
+    const unsigned char* ksrc = kp + tok0 * 64 + lane * 16;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) cp_async16(stage + lane * 16 + k * 512, ksrc + k * 512);
+    const unsigned char* vsrc = vp + tok0 * 32 + lane * 16;
+    cp_async16(stage + v_dst, vsrc);
+    cp_async16(stage + v_dst + 512, vsrc + 512);
+    cp_async4(stage + kStageK + kStageV + lane * 4, vs + (tok0 + lane) * 4);
+    cp_async4(stage + kStageK + kStageV + 128 + lane * 4, vo + (tok0 + lane) * 4);
+  } else {
+    const int last = T - 1;
+    const int r = lane >> 2, j = lane & 3;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      cp_async16(stage + lane * 16 + k * 512, kp + min(tok0 + r + 8 * k, last) * 64 + j * 16);
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      cp_async16(stage + v_dst + k * 512, vp + min(tok0 + (lane >> 1) + 16 * k, last) * 32 + (lane & 1) * 16);
+    const int tp = min(tok0 + lane, last);
+    cp_async4(stage + kStageK + kStageV + lane * 4, vs + tp * 4);
+    cp_async4(stage + kStageK + kStageV + 128 + lane * 4, vo + tp * 4);
   }
 }
 
 // ------------------------------------------------------------------------------------------ the kernel
-template <int MODE, typename QT>
-__global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams P) {
+template <int MODE, typename QT, bool SAL>
+__global__ void __launch_bounds__(kThreads, 3) decode_kernel(const DecodeParams P) {
   extern __shared__ __align__(16) unsigned char smem[];
   float* qs = (float*)smem;                                             // 8 heads x 4 chunks x kQChunk
   unsigned char* warp_base = smem + 8 * 4 * kQChunk * 4;
@@ -198,9 +239,12 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
   const int groups = (P.n_pad + 15) >> 4;                               // salient channels in groups of 16
   const int warp_bytes = warp_smem_bytes(groups);
   unsigned char* const wb = warp_base + warp * warp_bytes;
+  // folded-query B fragments of the 8 K steps ([step][lane] x 8 bytes); while a block's weights
+  // are being derived the same 2 KB hold the per-channel slot weights and additive constants
+  unsigned char* wW = wb;
   float* wf = (float*)wb;                                               // slot weight per channel
   float* wk0 = wf + 128;                                                // additive constant per channel
-  short* wroles = (short*)(wk0 + 128);                                  // role map of the current block
+  short* wroles = (short*)(wb + 2048);                                  // role map of the current block
   float* wssc = (float*)(wroles + 128);                                 // scale of salient channel i
   unsigned char* wsrc = (unsigned char*)(wssc + 64);                    // channel of salient i
   unsigned char* wdon = wsrc + 64;                                      // its donor slot
@@ -209,9 +253,32 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
   unsigned char* ring = wsel + groups * 4096;
   __shared__ int s_is_last;
 
+  // Flat decomposition: the packed slices of all (sequence, KV head, head tile) pairs form one
+  // list that is cut into gridDim.x equal ranges; a CTA walks its range pair by pair.
   const int gtiles = (P.G + 7) >> 3;
-  const int h = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
-  const int seq = blockIdx.z;
+  const long long c_begin = (long long)blockIdx.x * P.per_cta;
+  const long long c_end = min(c_begin + P.per_cta, P.total_units);
+  long long pos = c_begin;
+  int pair;
+  if (P.pair_starts) {
+    int lo = 0, hi = P.n_pairs - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (P.pair_starts[mid] <= pos) lo = mid; else hi = mid - 1;
+    }
+    pair = lo;
+  } else {
+    pair = (int)(pos / P.uniform_units);
+  }
+  for (; pos < c_end; ++pair) {
+  const long long pair_lo = P.pair_starts ? P.pair_starts[pair] : (long long)pair * P.uniform_units;
+  const long long pair_hi = P.pair_starts ? P.pair_starts[pair + 1] : pair_lo + P.uniform_units;
+  const long long seg_lo = pos - pair_lo, seg_hi = min(c_end, pair_hi) - pair_lo;
+  pos = pair_lo + seg_hi;
+  const int first_cta = (int)(pair_lo / P.per_cta), last_cta = (int)((pair_hi - 1) / P.per_cta);
+  const int n_cta_pair = last_cta - first_cta + 1;
+  const int seq = pair / (P.H * gtiles);
+  const int h = (pair / gtiles) % P.H, gt = pair % gtiles;
   // Descriptor fields are fetched where they are used: from kernel parameters for a single
   // sequence, from the device array for a batch.
   const SeqDesc* const Dp = P.seqs ? P.seqs + seq : nullptr;
@@ -236,18 +303,19 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
   __syncthreads();
 
   const int T = P.T;
-  const int spb = (T + 15) >> 4;
+  const int spb = (T + kSliceTokens - 1) / kSliceTokens;   // packed slices per block
   const int n_blocks = SEQ(n_blocks);
   const int sink_tokens = SEQ(sink_tokens);
   const int* const tail_dev = SEQ(tail_tokens_dev);
   const int tail_tokens = tail_dev ? *tail_dev : SEQ(tail_tokens);
   const long long n_packed = (long long)n_blocks * spb;
   const int sink_slices = (sink_tokens + 15) >> 4, tail_slices = (tail_tokens + 15) >> 4;
-  const long long total = n_packed + 4ll * (sink_slices + tail_slices);
-  const long long cta_a = total * blockIdx.x / P.n_parts, cta_b = total * (blockIdx.x + 1) / P.n_parts;
-  const long long a = cta_a + (cta_b - cta_a) * warp / kWarps, b = cta_a + (cta_b - cta_a) * (warp + 1) / kWarps;
-  const long long pa = min(a, n_packed), pb = min(b, n_packed);
-  const int da = (int)((max(a, n_packed) - n_packed + 3) >> 2), db = (int)((max(b, n_packed) - n_packed + 3) >> 2);
+  // packed slices are cut evenly over all warps of this (sequence, KV head); the few dense
+  // slices are dealt round-robin so that no warp ends with a long exposed-latency tail
+  const int n_workers = n_cta_pair * kWarps, worker = ((int)blockIdx.x - first_cta) * kWarps + warp;
+  const long long pa = min(n_packed, seg_lo + (seg_hi - seg_lo) * warp / kWarps);
+  const long long pb = min(n_packed, seg_lo + (seg_hi - seg_lo) * (warp + 1) / kWarps);
+  const int n_dense = sink_slices + tail_slices;
 
   float m_run[2] = {kNegBig, kNegBig}, l_run[2] = {0.f, 0.f};
   float acc[8][4];
@@ -262,15 +330,17 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
     const int n_my = (int)(pb - pa);
     int pf_block = (int)(pa / spb), pf_slice = (int)(pa % spb);   // prefetch cursor
     BlockPtrs pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
-    int issued = 0;
+    int to_issue = n_my, issue_stage = 0;
     auto issue = [&]() {
-      if (issued < n_my) {
-        stage_slice(ring + (issued % kStages) * kStageBytes, pf_ptrs, pf_slice * 16, T, lane);
-        ++issued;
+      if (to_issue > 0) {
+        stage_slice(ring + issue_stage * kStageBytes, pf_ptrs.kp, pf_ptrs.vp, pf_ptrs.vs, pf_ptrs.vo,
+                    pf_slice * kSliceTokens, T, lane);
+        --to_issue;
+        if (++issue_stage == kStages) issue_stage = 0;
         if (++pf_slice == spb) {
           pf_slice = 0;
           ++pf_block;
-          if (issued < n_my) pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
+          if (to_issue > 0) pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
         }
       }
       cp_async_commit();
@@ -280,9 +350,15 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
 
     int cur_block = (int)(pa / spb), cur_slice = (int)(pa % spb);
     bool need_weights = true;
-    unsigned wfrag[8][2];
     float alpha[2] = {0.f, 0.f}, beta[2] = {0.f, 0.f};
     const unsigned vsel = (r & 1) ? 0x7632u : 0x5410u;
+    // byte offset (inside a stage's V area) of this lane's word of token 2j for value group 0
+    // and group 1; tokens 2j+1, 2j+8, 2j+9 follow at +32, +256, +288
+    const unsigned v_base0 = (unsigned)((((2 * j) * 2 + (((2 * j) >> 2) & 1)) << 4) + (r >> 1) * 4);
+    const unsigned v_base1 = v_base0 ^ 16u;
+    const unsigned ring_addr = smem_addr(ring), lane16 = lane * 16;
+    const unsigned ww_addr = smem_addr(wW) + lane * 8, sel_addr = smem_addr(wsel) + lane * 16;
+    int stage_index = 0;
 
     for (int it = 0; it < n_my; ++it) {
       cp_async_wait<kStages - 2>();
@@ -414,11 +490,12 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
         const float up = __uint_as_float((unsigned)(127 + 13 - ex) << 23);
         const float inv = __uint_as_float((unsigned)(127 + ex + 11) << 23);   // 2^24 / up
         const float up16 = up * 0.0625f;
+        __syncwarp();   // every lane has read the per-channel weights that wW overwrites
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
           const int base = 8 * (s >> 1) + 2 * (s & 1);
-          wfrag[s][0] = pack_half2(w[base] * up, w[base + 4] * up);
-          wfrag[s][1] = pack_half2(w[base + 1] * up16, w[base + 5] * up16);
+          *(uint2*)(wW + (s * 32 + lane) * 8) = make_uint2(pack_half2(w[base] * up, w[base + 4] * up),
+                                                            pack_half2(w[base + 1] * up16, w[base + 5] * up16));
         }
         // score columns of this thread are query heads 2j and 2j+1
         alpha[0] = __shfl_sync(0xffffffffu, inv, (2 * j) * 4);
@@ -428,69 +505,127 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
         need_weights = false;
       }
 
-      const unsigned char* stage = ring + (it % kStages) * kStageBytes;
-      // ---- scores = K tile (16 tokens x 128 slots) * folded query, plus the salient channels
-      float S[4] = {0.f, 0.f, 0.f, 0.f};
-      float S2[4] = {0.f, 0.f, 0.f, 0.f};
+      const unsigned stage = ring_addr + stage_index * kStageBytes;
+      if (++stage_index == kStages) stage_index = 0;
+      // ---- scores of two 16-token sub-slices (tokens 0..15 and 16..31 of the stage): K nibbles
+      //      times the folded query, plus the exactly rebuilt salient channels
+      float S[2][4], S2[2][4];
       {
-        const uint4 kx = *(const uint4*)(stage + lane * 16);
-        const uint4 ky = *(const uint4*)(stage + 512 + lane * 16);
-        const unsigned xs[4] = {kx.x, kx.y, kx.z, kx.w}, ys[4] = {ky.x, ky.y, ky.z, ky.w};
+        float C[2][2][4];   // [sub-slice][n-tile][frag]: code' = 16*hi + lo of salient group 0
+        // One sub-slice at a time keeps the live register set small: this lane's 16 bytes
+        // (channels 32j..32j+31) of tokens r and r+8 of the sub-slice.
+#define INQ_KSTEP(U, KS, X, Y, FIRST)                                                                     \
+  {                                                                                                       \
+    const unsigned a0 = (X) & 0x000F000Fu, a1 = (Y) & 0x000F000Fu, a2 = (X) & 0x00F000F0u, a3 = (Y) & 0x00F000F0u; \
+    const uint2 wq = lds64<(KS) * 256>(ww_addr);                                                          \
+    if (FIRST) mma_f16_first(S[U], a0, a1, a2, a3, wq.x, wq.y);                                           \
+    else mma_f16(S[U], a0, a1, a2, a3, wq.x, wq.y);                                                       \
+    if (SAL) {                                                                                            \
+      const uint4 f = lds128<(KS) * 512>(sel_addr);                                                       \
+      if (FIRST) {                                                                                        \
+        mma_f16_first(C[U][0], a0, a1, a2, a3, f.x, f.y);                                                 \
+        mma_f16_first(C[U][1], a0, a1, a2, a3, f.z, f.w);                                                 \
+      } else {                                                                                            \
+        mma_f16(C[U][0], a0, a1, a2, a3, f.x, f.y);                                                       \
+        mma_f16(C[U][1], a0, a1, a2, a3, f.z, f.w);                                                       \
+      }                                                                                                   \
+    }                                                                                                     \
+  }
+#define INQ_KSUB(U)                                                                                       \
+  {                                                                                                       \
+    const uint4 kx = lds128<1024 * (U)>(stage + lane16), ky = lds128<1024 * (U) + 512>(stage + lane16);   \
+    INQ_KSTEP(U, 0, kx.x, ky.x, true)                                                                     \
+    INQ_KSTEP(U, 1, kx.x >> 8, ky.x >> 8, false)                                                          \
+    INQ_KSTEP(U, 2, kx.y, ky.y, false)                                                                    \
+    INQ_KSTEP(U, 3, kx.y >> 8, ky.y >> 8, false)                                                          \
+    INQ_KSTEP(U, 4, kx.z, ky.z, false)                                                                    \
+    INQ_KSTEP(U, 5, kx.z >> 8, ky.z >> 8, false)                                                          \
+    INQ_KSTEP(U, 6, kx.w, ky.w, false)                                                                    \
+    INQ_KSTEP(U, 7, kx.w >> 8, ky.w >> 8, false)                                                          \
+  }
+        INQ_KSUB(0)
+        INQ_KSUB(1)
+#undef INQ_KSUB
+#undef INQ_KSTEP
+        if (SAL) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          unsigned x = xs[i], y = ys[i];
-          mma_f16(S, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, wfrag[2 * i][0], wfrag[2 * i][1]);
-          x >>= 8;
-          y >>= 8;
-          mma_f16(S, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, wfrag[2 * i + 1][0],
-                  wfrag[2 * i + 1][1]);
-        }
-        for (int gsel = 0; gsel < groups; ++gsel) {
-          // gather code' = 16*hi + lo of 16 salient channels with the tensor cores (exact)
-          float C0[4] = {0.f, 0.f, 0.f, 0.f}, C1[4] = {0.f, 0.f, 0.f, 0.f};
-          const uint4* sel = (const uint4*)wsel + gsel * 256 + lane;
+          for (int u = 0; u < 2; ++u)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            unsigned x = xs[i], y = ys[i];
-            uint4 f = sel[(2 * i) * 32];
-            mma_f16(C0, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, f.x, f.y);
-            mma_f16(C1, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, f.z, f.w);
-            x >>= 8;
-            y >>= 8;
-            f = sel[(2 * i + 1) * 32];
-            mma_f16(C0, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, f.x, f.y);
-            mma_f16(C1, x & 0x000F000Fu, y & 0x000F000Fu, x & 0x00F000F0u, y & 0x00F000F0u, f.z, f.w);
+            for (int k = 0; k < 4; ++k) S2[u][k] = 0.f;
+          for (int gsel = 0; gsel < groups; ++gsel) {
+            if (gsel) {
+              // further groups of 16 salient channels (salient fractions above 1/8)
+              const uint4 k0 = lds128<0>(stage + lane16), k1 = lds128<512>(stage + lane16);
+              const uint4 k2 = lds128<1024>(stage + lane16), k3 = lds128<1536>(stage + lane16);
+              const unsigned kw[4][4] = {{k0.x, k0.y, k0.z, k0.w}, {k1.x, k1.y, k1.z, k1.w},
+                                         {k2.x, k2.y, k2.z, k2.w}, {k3.x, k3.y, k3.z, k3.w}};
+#pragma unroll
+              for (int u = 0; u < 2; ++u)
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) C[u][n][k] = 0.f;
+              const uint4* selg = (const uint4*)wsel + gsel * 256 + lane;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                unsigned x0 = kw[0][i], y0 = kw[1][i], x1 = kw[2][i], y1 = kw[3][i];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                  const uint4 f = selg[(2 * i + hh) * 32];
+                  const unsigned a0 = x0 & 0x000F000Fu, a1 = y0 & 0x000F000Fu, a2 = x0 & 0x00F000F0u, a3 = y0 & 0x00F000F0u;
+                  const unsigned b0 = x1 & 0x000F000Fu, b1 = y1 & 0x000F000Fu, b2 = x1 & 0x00F000F0u, b3 = y1 & 0x00F000F0u;
+                  mma_f16(C[0][0], a0, a1, a2, a3, f.x, f.y);
+                  mma_f16(C[1][0], b0, b1, b2, b3, f.x, f.y);
+                  mma_f16(C[0][1], a0, a1, a2, a3, f.z, f.w);
+                  mma_f16(C[1][1], b0, b1, b2, b3, f.z, f.w);
+                  x0 >>= 8; y0 >>= 8; x1 >>= 8; y1 >>= 8;
+                }
+              }
+            }
+            // value = fl32((code' - 128) * scale) rounded to the model dtype, as the reference's
+            // dequantised tensor holds it
+            const float2 sc0 = *(const float2*)(wssc + gsel * 16 + 2 * j);
+            const float2 sc1 = *(const float2*)(wssc + gsel * 16 + 8 + 2 * j);
+            const uint2 qb = *(const uint2*)(wqsal + (gsel * 32 + lane) * 8);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const unsigned a0 = pack_qt2<QT>(fmaf(C[u][0][0], 8192.f, -128.f) * sc0.x, fmaf(C[u][0][1], 8192.f, -128.f) * sc0.y);
+              const unsigned a1 = pack_qt2<QT>(fmaf(C[u][0][2], 8192.f, -128.f) * sc0.x, fmaf(C[u][0][3], 8192.f, -128.f) * sc0.y);
+              const unsigned a2 = pack_qt2<QT>(fmaf(C[u][1][0], 8192.f, -128.f) * sc1.x, fmaf(C[u][1][1], 8192.f, -128.f) * sc1.y);
+              const unsigned a3 = pack_qt2<QT>(fmaf(C[u][1][2], 8192.f, -128.f) * sc1.x, fmaf(C[u][1][3], 8192.f, -128.f) * sc1.y);
+              mma_qt<QT>(S2[u], a0, a1, a2, a3, qb.x, qb.y);
+            }
           }
-          // value = fl32((code' - 128) * scale) rounded to the model dtype, as the reference's
-          // dequantised tensor holds it
-          const float2 sc0 = *(const float2*)(wssc + gsel * 16 + 2 * j);
-          const float2 sc1 = *(const float2*)(wssc + gsel * 16 + 8 + 2 * j);
-          const unsigned a0 = pack_qt2<QT>(fmaf(C0[0], 8192.f, -128.f) * sc0.x, fmaf(C0[1], 8192.f, -128.f) * sc0.y);
-          const unsigned a1 = pack_qt2<QT>(fmaf(C0[2], 8192.f, -128.f) * sc0.x, fmaf(C0[3], 8192.f, -128.f) * sc0.y);
-          const unsigned a2 = pack_qt2<QT>(fmaf(C1[0], 8192.f, -128.f) * sc1.x, fmaf(C1[1], 8192.f, -128.f) * sc1.y);
-          const unsigned a3 = pack_qt2<QT>(fmaf(C1[2], 8192.f, -128.f) * sc1.x, fmaf(C1[3], 8192.f, -128.f) * sc1.y);
-          const uint2 qb = *(const uint2*)(wqsal + (gsel * 32 + lane) * 8);
-          mma_qt<QT>(S2, a0, a1, a2, a3, qb.x, qb.y);
         }
       }
-      float s2[4] = {fmaf(S[0], alpha[0], beta[0]), fmaf(S[1], alpha[1], beta[1]), fmaf(S[2], alpha[0], beta[0]),
-                     fmaf(S[3], alpha[1], beta[1])};
-      if (groups) {
+      // s2[u][k]: sub-slice u; k = 0,1 -> token r (+16u), heads 2j, 2j+1; k = 2,3 -> token r+8 (+16u)
+      float s2[2][4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) s2[k] = fmaf(S2[k], P.scale_log2e, s2[k]);
+      for (int u = 0; u < 2; ++u) {
+        s2[u][0] = fmaf(S[u][0], alpha[0], beta[0]);
+        s2[u][1] = fmaf(S[u][1], alpha[1], beta[1]);
+        s2[u][2] = fmaf(S[u][2], alpha[0], beta[0]);
+        s2[u][3] = fmaf(S[u][3], alpha[1], beta[1]);
+        if (SAL) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) s2[u][k] = fmaf(S2[u][k], P.scale_log2e, s2[u][k]);
+        }
       }
       {
-        const int tok0 = cur_slice * 16;
+        const int tok0 = cur_slice * kSliceTokens;
         const long long g0 = (long long)cur_block * T + tok0;
-        if (tok0 + 16 > T || g0 < first_visible) {
-          const bool lo_ok = tok0 + r < T && g0 + r >= first_visible;
-          const bool hi_ok = tok0 + r + 8 < T && g0 + r + 8 >= first_visible;
-          if (!lo_ok) s2[0] = s2[1] = -INFINITY;
-          if (!hi_ok) s2[2] = s2[3] = -INFINITY;
+        if (tok0 + kSliceTokens > T || g0 < first_visible) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int t_lo = tok0 + 16 * u + r, t_hi = t_lo + 8;
+            if (!(t_lo < T && g0 + 16 * u + r >= first_visible)) s2[u][0] = s2[u][1] = -INFINITY;
+            if (!(t_hi < T && g0 + 16 * u + r + 8 >= first_visible)) s2[u][2] = s2[u][3] = -INFINITY;
+          }
         }
       }
-      // ---- online softmax (base 2)
-      float mx0 = fmaxf(s2[0], s2[2]), mx1 = fmaxf(s2[1], s2[3]);
+      // ---- online softmax (base 2) over the 32 tokens
+      float mx0 = fmaxf(fmaxf(s2[0][0], s2[0][2]), fmaxf(s2[1][0], s2[1][2]));
+      float mx1 = fmaxf(fmaxf(s2[0][1], s2[0][3]), fmaxf(s2[1][1], s2[1][3]));
 #pragma unroll
       for (int off = 4; off < 32; off <<= 1) {
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
@@ -510,39 +645,44 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
         m_run[0] = mn0;
         m_run[1] = mn1;
       }
-      const float p0 = fast_exp2(s2[0] - m_run[0]), p1 = fast_exp2(s2[1] - m_run[1]);
-      const float p2 = fast_exp2(s2[2] - m_run[0]), p3 = fast_exp2(s2[3] - m_run[1]);
-      l_run[0] += p0 + p2;
-      l_run[1] += p1 + p3;
-      // ---- values: probabilities times the per-token group scale, codes as fp16 subnormals
-      const unsigned char* sp = stage + kStageK + kStageV;
-      const float2 vs_lo = half2_bits_to_float2(*(const unsigned*)(sp + 4 * r));
-      const float2 vs_hi = half2_bits_to_float2(*(const unsigned*)(sp + 4 * (r + 8)));
-      const float2 vo_lo = half2_bits_to_float2(*(const unsigned*)(sp + 64 + 4 * r));
-      const float2 vo_hi = half2_bits_to_float2(*(const unsigned*)(sp + 64 + 4 * (r + 8)));
-      oacc[0][0] += p0 * vo_lo.x + p2 * vo_hi.x;
-      oacc[0][1] += p1 * vo_lo.x + p3 * vo_hi.x;
-      oacc[1][0] += p0 * vo_lo.y + p2 * vo_hi.y;
-      oacc[1][1] += p1 * vo_lo.y + p3 * vo_hi.y;
-      const unsigned char* sv = stage + kStageK;
-      const int tA = 2 * j, tB = 2 * j + 1, tC = 2 * j + 8, tD = 2 * j + 9;
+      float pr[2][4];
 #pragma unroll
-      for (int gr = 0; gr < 2; ++gr) {
-        const float sl = gr ? vs_lo.y : vs_lo.x, sh = gr ? vs_hi.y : vs_hi.x;
-        const unsigned b0 = movmatrix_trans(pack_half2(p0 * sl, p1 * sl));
-        const unsigned b1 = movmatrix_trans(pack_half2(p2 * sh, p3 * sh));
-        const int word = (r >> 1) * 4;
-        const unsigned wA = *(const unsigned*)(sv + (tA * 2 + (gr ^ ((tA >> 2) & 1))) * 16 + word);
-        const unsigned wB = *(const unsigned*)(sv + (tB * 2 + (gr ^ ((tB >> 2) & 1))) * 16 + word);
-        const unsigned wC = *(const unsigned*)(sv + (tC * 2 + (gr ^ ((tC >> 2) & 1))) * 16 + word);
-        const unsigned wD = *(const unsigned*)(sv + (tD * 2 + (gr ^ ((tD >> 2) & 1))) * 16 + word);
-        const unsigned M0 = __byte_perm(wA, wB, vsel), M1 = __byte_perm(wC, wD, vsel);
-        const unsigned N0 = M0 >> 10, N1 = M1 >> 10;
-        mma_f16(acc[gr * 4 + 0], M0 & 0x00030003u, M0 & 0x000C000Cu, M1 & 0x00030003u, M1 & 0x000C000Cu, b0, b1);
-        mma_f16(acc[gr * 4 + 1], M0 & 0x00300030u, M0 & 0x00C000C0u, M1 & 0x00300030u, M1 & 0x00C000C0u, b0, b1);
-        mma_f16(acc[gr * 4 + 2], M0 & 0x03000300u, N0 & 0x00030003u, M1 & 0x03000300u, N1 & 0x00030003u, b0, b1);
-        mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1);
+      for (int u = 0; u < 2; ++u) {
+        pr[u][0] = fast_exp2(s2[u][0] - m_run[0]);
+        pr[u][1] = fast_exp2(s2[u][1] - m_run[1]);
+        pr[u][2] = fast_exp2(s2[u][2] - m_run[0]);
+        pr[u][3] = fast_exp2(s2[u][3] - m_run[1]);
+        l_run[0] += pr[u][0] + pr[u][2];
+        l_run[1] += pr[u][1] + pr[u][3];
       }
+      // ---- values: probabilities times the per-token group scale, codes as fp16 subnormals
+#define INQ_PV(U)                                                                                          \
+  {                                                                                                        \
+    const unsigned sp = stage + kStageK + kStageV + 4 * r;                                                 \
+    const float2 vs_lo = half2_bits_to_float2(lds32<64 * (U)>(sp)), vs_hi = half2_bits_to_float2(lds32<64 * (U) + 32>(sp)); \
+    const float2 vo_lo = half2_bits_to_float2(lds32<128 + 64 * (U)>(sp)), vo_hi = half2_bits_to_float2(lds32<128 + 64 * (U) + 32>(sp)); \
+    oacc[0][0] += pr[U][0] * vo_lo.x + pr[U][2] * vo_hi.x;                                                 \
+    oacc[0][1] += pr[U][1] * vo_lo.x + pr[U][3] * vo_hi.x;                                                 \
+    oacc[1][0] += pr[U][0] * vo_lo.y + pr[U][2] * vo_hi.y;                                                 \
+    oacc[1][1] += pr[U][1] * vo_lo.y + pr[U][3] * vo_hi.y;                                                 \
+    _Pragma("unroll") for (int gr = 0; gr < 2; ++gr) {                                                     \
+      const float sl = gr ? vs_lo.y : vs_lo.x, sh = gr ? vs_hi.y : vs_hi.x;                                \
+      const unsigned b0 = movmatrix_trans(pack_half2(pr[U][0] * sl, pr[U][1] * sl));                       \
+      const unsigned b1 = movmatrix_trans(pack_half2(pr[U][2] * sh, pr[U][3] * sh));                       \
+      const unsigned vb = stage + (gr ? v_base1 : v_base0);                                                \
+      const unsigned wA = lds32<kStageK + 512 * (U)>(vb), wB = lds32<kStageK + 512 * (U) + 32>(vb);        \
+      const unsigned wC = lds32<kStageK + 512 * (U) + 256>(vb), wD = lds32<kStageK + 512 * (U) + 288>(vb); \
+      const unsigned M0 = __byte_perm(wA, wB, vsel), M1 = __byte_perm(wC, wD, vsel);                       \
+      const unsigned N0 = M0 >> 10, N1 = M1 >> 10;                                                         \
+      mma_f16(acc[gr * 4 + 0], M0 & 0x00030003u, M0 & 0x000C000Cu, M1 & 0x00030003u, M1 & 0x000C000Cu, b0, b1); \
+      mma_f16(acc[gr * 4 + 1], M0 & 0x00300030u, M0 & 0x00C000C0u, M1 & 0x00300030u, M1 & 0x00C000C0u, b0, b1); \
+      mma_f16(acc[gr * 4 + 2], M0 & 0x03000300u, N0 & 0x00030003u, M1 & 0x03000300u, N1 & 0x00030003u, b0, b1); \
+      mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1); \
+    }                                                                                                      \
+  }
+      INQ_PV(0)
+      INQ_PV(1)
+#undef INQ_PV
       if (++cur_slice == spb) {
         cur_slice = 0;
         ++cur_block;
@@ -563,7 +703,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
   }
 
   // ---------------------------------------------------------------- exact sink and tail
-  if (db > da) {
+  if (worker < n_dense) {
     unsigned qf[16];
     {
       const bool live = r < g_valid;
@@ -574,7 +714,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
         qf[4 * m + 0] = v.x; qf[4 * m + 1] = v.y; qf[4 * m + 2] = v.z; qf[4 * m + 3] = v.w;
       }
     }
-    for (int ds = da; ds < db; ++ds) {
+    for (int ds = worker; ds < n_dense; ds += n_workers) {
       const bool is_sink = ds < sink_slices;
       const int tok0 = (is_sink ? ds : ds - sink_slices) * 16;
       const int count = is_sink ? sink_tokens : tail_tokens;
@@ -683,8 +823,7 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
     }
   }
   __syncthreads();
-  const long long slot = ((long long)seq * gridDim.y + blockIdx.y);
-  float* record = P.partials + (slot * P.n_parts + blockIdx.x) * kRecordFloats;
+  float* record = P.partials + ((long long)blockIdx.x + pair) * kRecordFloats;
   {
     const int c = threadIdx.x;   // one channel per thread
     const float* w0 = (const float*)(warp_base + (ring - wb));
@@ -714,30 +853,56 @@ __global__ void __launch_bounds__(kThreads, 4) decode_kernel(const DecodeParams 
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const int old = atomicAdd(P.counters + slot, 1);
-    s_is_last = (old == P.n_parts - 1);
-    if (s_is_last) P.counters[slot] = 0;   // scratch is left zeroed for the next launch
+    const int old = atomicAdd(P.counters + pair, 1);
+    s_is_last = (old == n_cta_pair - 1);
+    if (s_is_last) P.counters[pair] = 0;   // scratch is left zeroed for the next launch
   }
   __syncthreads();
-  if (!s_is_last) return;
+  if (s_is_last) {
   __threadfence();
-  {
-    const int c = threadIdx.x;
-    const float* base = P.partials + slot * P.n_parts * kRecordFloats;
-    QT* out = (QT*)SEQ(out);
-    for (int g = 0; g < g_valid; ++g) {
+    // weights of all (query head, part) pairs first, in parallel, then one pass over the records
+    float* mw = (float*)warp_base;                 // [8][np] weights, then [8] normalisers
+    const float* base = P.partials + ((long long)first_cta + pair) * kRecordFloats;
+    const int np = n_cta_pair;
+    float* norm = mw + 8 * np;
+    if (threadIdx.x < 8) norm[threadIdx.x] = 0.f;
+    for (int g = warp; g < g_valid; g += kWarps) {
       float top = kNegBig;
-      for (int p = 0; p < P.n_parts; ++p) top = fmaxf(top, __ldcg(base + (long long)p * kRecordFloats + g * kRecordStride + 128));
-      float o = 0.f, l = 0.f;
-      for (int p = 0; p < P.n_parts; ++p) {
+      for (int p = lane; p < np; p += 32) top = fmaxf(top, __ldcg(base + (long long)p * kRecordFloats + g * kRecordStride + 128));
+#pragma unroll
+      for (int off = 16; off; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+      float l = 0.f;
+      for (int p = lane; p < np; p += 32) {
         const float* rec = base + (long long)p * kRecordFloats + g * kRecordStride;
         const float wt = fast_exp2(__ldcg(rec + 128) - top);
-        o = fmaf(__ldcg(rec + c), wt, o);
+        mw[g * np + p] = wt;
         l = fmaf(__ldcg(rec + 129), wt, l);
       }
-      out[(q_head0 + g) * 128 + c] = from_float<QT>(o / l);
+#pragma unroll
+      for (int off = 16; off; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+      if (lane == 0) norm[g] = l;
+    }
+    __syncthreads();
+    const int c = threadIdx.x;
+    QT* out = (QT*)SEQ(out);
+    for (int g = 0; g < g_valid; ++g) {
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      const float* rec = base + g * kRecordStride + c;
+      int p = 0;
+      for (; p + 4 <= np; p += 4) {
+        const float v0 = __ldcg(rec + (long long)(p + 0) * kRecordFloats), v1 = __ldcg(rec + (long long)(p + 1) * kRecordFloats);
+        const float v2 = __ldcg(rec + (long long)(p + 2) * kRecordFloats), v3 = __ldcg(rec + (long long)(p + 3) * kRecordFloats);
+        o0 = fmaf(v0, mw[g * np + p], o0);
+        o1 = fmaf(v1, mw[g * np + p + 1], o1);
+        o2 = fmaf(v2, mw[g * np + p + 2], o2);
+        o3 = fmaf(v3, mw[g * np + p + 3], o3);
+      }
+      for (; p < np; ++p) o0 = fmaf(__ldcg(rec + (long long)p * kRecordFloats), mw[g * np + p], o0);
+      out[(q_head0 + g) * 128 + c] = from_float<QT>(((o0 + o1) + (o2 + o3)) / norm[g]);
     }
   }
+  __syncthreads();   // shared scratch is reused by the next pair of this CTA
+  }  // pairs of this CTA
 }
 
 #undef SEQ
@@ -759,31 +924,82 @@ static int sm_count() {
   return g_sm_count;
 }
 
-extern "C" int inq_decode_plan_parts(int32_t n_seq, int32_t kv_heads, int32_t q_per_kv, int64_t max_slices) {
-  if (n_seq < 1 || kv_heads < 1 || q_per_kv < 1) return INQ_ERR_ARGUMENT;
-  const long long groups = (long long)n_seq * kv_heads * ((q_per_kv + 7) / 8);
-  const long long target = (long long)sm_count() * 4 * 3;            // three waves of four CTAs per SM
-  long long parts = (target + groups - 1) / groups;
-  const long long most = max_slices / 32 > 1 ? max_slices / 32 : 1;  // at least 8 slices per warp
-  if (parts > most) parts = most;
-  if (parts < 1) parts = 1;
-  if (parts > 1024) parts = 1024;
-  return (int)parts;
+// Flat decomposition shared by the planner and the launcher.
+struct Plan {
+  int n_ctas;
+  long long per_cta, total, uniform_units;
+  int n_pairs;
+};
+
+static int spb_of(int block_tokens) { return (block_tokens + kSliceTokens - 1) / kSliceTokens; }
+
+static Plan make_plan(long long total_units, int n_pairs, long long uniform_units, int ctas_per_sm) {
+  Plan p;
+  p.total = total_units;
+  p.n_pairs = n_pairs;
+  p.uniform_units = uniform_units;
+  long long slots = (long long)sm_count() * ctas_per_sm;
+  long long by_work = total_units / 8 > 1 ? total_units / 8 : 1;   // at least 2 slices per warp
+  long long n = slots < by_work ? slots : by_work;
+  p.per_cta = (total_units + n - 1) / n;
+  p.n_ctas = (int)((total_units + p.per_cta - 1) / p.per_cta);
+  return p;
 }
 
-extern "C" int64_t inq_decode_workspace_floats(int32_t n_seq, int32_t kv_heads, int32_t q_per_kv, int32_t n_parts) {
-  return (int64_t)n_seq * kv_heads * ((q_per_kv + 7) / 8) * n_parts * kRecordFloats;
+extern "C" int64_t inq_decode_units(int32_t n_blocks, int32_t block_tokens) {
+  const long long u = (long long)n_blocks * spb_of(block_tokens);
+  return u > 0 ? u : 1;
+}
+
+extern "C" int64_t inq_decode_workspace_floats(int32_t n_pairs, int64_t total_units) {
+  const Plan p = make_plan(total_units > n_pairs ? total_units : n_pairs, n_pairs, 0, 8);
+  return ((int64_t)p.n_ctas + n_pairs) * kRecordFloats;
 }
 
 extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t stream_) {
-  if (!a || a->n_seq < 1 || a->kv_heads < 1 || a->q_per_kv < 1 || a->block_tokens < 1 || a->n_parts < 1) return INQ_ERR_ARGUMENT;
+  if (!a || a->n_seq < 1 || a->kv_heads < 1 || a->q_per_kv < 1 || a->block_tokens < 1) return INQ_ERR_ARGUMENT;
   if (!a->partials || !a->counters || !a->status) return INQ_ERR_ARGUMENT;
   if (a->n_seq > 1 && !a->seqs_device) return INQ_ERR_ARGUMENT;
-  if (a->n_seq == 1 && !a->seqs_device && !a->seq_host) return INQ_ERR_ARGUMENT;
+  if (!a->seqs_device && !a->seq_host) return INQ_ERR_ARGUMENT;
   if (a->dtype != INQ_F16 && a->dtype != INQ_BF16) return INQ_ERR_UNSUPPORTED;
   if (a->layout != 0 && a->layout != 1) return INQ_ERR_ARGUMENT;
   if (!(a->scale > 0.f) || a->n_pad < 0 || a->n_pad > 64) return INQ_ERR_ARGUMENT;
-  if (a->n_seq > 65535 || (long long)a->kv_heads * ((a->q_per_kv + 7) / 8) > 65535) return INQ_ERR_UNSUPPORTED;
+  const int gtiles = (a->q_per_kv + 7) / 8;
+  const long long n_pairs = (long long)a->n_seq * a->kv_heads * gtiles;
+  if (n_pairs > (1 << 30)) return INQ_ERR_UNSUPPORTED;
+  long long uniform = 0, total = 0;
+  if (a->pair_starts) {
+    if (a->total_units < n_pairs) return INQ_ERR_ARGUMENT;
+    total = a->total_units;
+  } else {
+    const int blocks = a->seqs_device ? a->uniform_blocks : ((const SeqDesc*)a->seq_host)->n_blocks;
+    if (blocks < 0) return INQ_ERR_ARGUMENT;
+    uniform = inq_decode_units(blocks, a->block_tokens);
+    total = uniform * n_pairs;
+  }
+  const int groups = (a->n_pad + 15) / 16;
+  const int shared = smem_bytes(groups);
+  typedef void (*kernel_t)(const DecodeParams);
+  static const kernel_t kernels[8] = {
+      decode_kernel<0, __half, false>, decode_kernel<0, __half, true>,
+      decode_kernel<0, __nv_bfloat16, false>, decode_kernel<0, __nv_bfloat16, true>,
+      decode_kernel<1, __half, false>, decode_kernel<1, __half, true>,
+      decode_kernel<1, __nv_bfloat16, false>, decode_kernel<1, __nv_bfloat16, true>};
+  static bool raised[8] = {};
+  static int per_sm[8][5] = {};
+  const int which = a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);
+  const kernel_t kernel = kernels[which];
+  if (!raised[which]) {
+    INQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4)));
+    raised[which] = true;
+  }
+  if (!per_sm[which][groups]) {
+    int n = 0;
+    INQ_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, shared));
+    per_sm[which][groups] = n > 0 ? n : 1;
+  }
+  const Plan plan = make_plan(total, (int)n_pairs, uniform, per_sm[which][groups]);
+  if (((long long)plan.n_ctas + n_pairs) * kRecordFloats > a->partials_floats) return INQ_ERR_CAPACITY;
   DecodeParams P;
   P.seqs = (const SeqDesc*)a->seqs_device;
   if (!a->seqs_device) P.one = *(const SeqDesc*)a->seq_host;
@@ -792,7 +1008,12 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   P.G = a->q_per_kv;
   P.T = a->block_tokens;
   P.n_pad = a->n_pad;
-  P.n_parts = a->n_parts;
+  P.n_ctas = plan.n_ctas;
+  P.n_pairs = plan.n_pairs;
+  P.per_cta = plan.per_cta;
+  P.total_units = plan.total;
+  P.uniform_units = plan.uniform_units;
+  P.pair_starts = (const long long*)a->pair_starts;
   P.scale_log2e = a->scale * 1.4426950408889634f;
   P.page_bytes = a->page_bytes;
   P.off_ks = (int)a->page_offsets[0];
@@ -804,19 +1025,7 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   P.partials = a->partials;
   P.counters = a->counters;
   P.status = a->status;
-  dim3 grid((unsigned)a->n_parts, (unsigned)(a->kv_heads * ((a->q_per_kv + 7) / 8)), (unsigned)a->n_seq);
-  cudaStream_t stream = (cudaStream_t)stream_;
-  const int shared = smem_bytes((a->n_pad + 15) / 16);
-  void (*kernel)(const DecodeParams) =
-      a->layout == 0 ? (a->dtype == INQ_F16 ? decode_kernel<0, __half> : decode_kernel<0, __nv_bfloat16>)
-                     : (a->dtype == INQ_F16 ? decode_kernel<1, __half> : decode_kernel<1, __nv_bfloat16>);
-  static bool raised[4] = {false, false, false, false};
-  const int which = a->layout * 2 + (a->dtype == INQ_F16 ? 0 : 1);
-  if (shared > 48 * 1024 && !raised[which]) {
-    INQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4)));
-    raised[which] = true;
-  }
-  kernel<<<grid, kThreads, shared, stream>>>(P);
+  kernel<<<(unsigned)plan.n_ctas, kThreads, shared, (cudaStream_t)stream_>>>(P);
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
 }

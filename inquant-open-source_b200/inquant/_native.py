@@ -57,8 +57,9 @@ class DecodeArgs(ctypes.Structure):
     _fields_ = [("n_seq", c_int32), ("seqs_device", c_void_p), ("seq_host", ctypes.POINTER(DecodeSeq)),
                 ("kv_heads", c_int32), ("q_per_kv", c_int32), ("block_tokens", c_int32), ("n_pad", c_int32),
                 ("layout", c_int32), ("dtype", c_int32), ("scale", ctypes.c_float),
-                ("page_bytes", c_int64), ("page_offsets", c_int64 * 6), ("n_parts", c_int32),
-                ("partials", c_void_p), ("counters", c_void_p), ("status", c_void_p)]
+                ("page_bytes", c_int64), ("page_offsets", c_int64 * 6),
+                ("pair_starts", c_void_p), ("total_units", c_int64), ("uniform_blocks", c_int32),
+                ("partials", c_void_p), ("partials_floats", c_int64), ("counters", c_void_p), ("status", c_void_p)]
 
 
 class AppendArgs(ctypes.Structure):
@@ -85,7 +86,9 @@ def library() -> ctypes.CDLL:
         lib = ctypes.CDLL(LIBRARY_PATH)
         lib.inq_last_error.restype = ctypes.c_char_p
         lib.inq_decode_workspace_floats.restype = c_int64
-        lib.inq_decode_workspace_floats.argtypes = [c_int32, c_int32, c_int32, c_int32]
+        lib.inq_decode_workspace_floats.argtypes = [c_int32, c_int64]
+        lib.inq_decode_units.restype = c_int64
+        lib.inq_decode_units.argtypes = [c_int32, c_int32]
         for name in EXPORTS:
             function = getattr(lib, name)  # every declared entry point must resolve
             if name in SIGNATURES:
@@ -99,7 +102,7 @@ def library() -> ctypes.CDLL:
 EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
     "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
-    "inq_decode_attention", "inq_decode_plan_parts", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
+    "inq_decode_attention", "inq_decode_units", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
 )
 
 
@@ -115,7 +118,6 @@ SIGNATURES = {
     "inq_decode_attention": [_P, _P],
     "inq_append_token": [_P, _P],
     "inq_append_token_batch": [_P, _I, _P, _P],
-    "inq_decode_plan_parts": [_I, _I, _I, _L],
 }
 
 

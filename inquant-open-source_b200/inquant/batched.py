@@ -20,7 +20,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _native as N
-from .triton_attention import PackedDecodeState, plan_parts
+from .triton_attention import PackedDecodeState, workspace_floats
 
 
 @dataclass
@@ -53,7 +53,7 @@ class DecodeBatch:
     """Device-resident descriptors, queries, outputs and scratch for a fixed set of sequences."""
 
     def __init__(self, sequences: list[SequenceState], q_heads: int, dtype: torch.dtype = torch.bfloat16,
-                 scale: float | None = None, n_parts: int | None = None):
+                 scale: float | None = None):
         if not sequences:
             raise ValueError("at least one sequence is required")
         first = sequences[0].decode_state
@@ -78,13 +78,16 @@ class DecodeBatch:
         self.outputs = torch.empty((n, q_heads, 128), dtype=dtype, device=self.device)
         self.tail_counters = torch.tensor([s.tail_count for s in sequences], dtype=torch.int32).to(self.device)
         self._build_descriptors()
-        slices = max(len(s.decode_state.key_blocks) * ((self.block_tokens + 15) // 16)
-                     + 4 * (1 + (s.tail_key_buffer.shape[2] + 15) // 16) for s in sequences)
-        self.n_parts = n_parts or plan_parts(self.kv_heads, self.q_per_kv, slices, n)
         tiles = (self.q_per_kv + 7) // 8
-        floats = N.library().inq_decode_workspace_floats(n, self.kv_heads, self.q_per_kv, self.n_parts)
-        self.partials = torch.empty(floats, dtype=torch.float32, device=self.device)
-        self.counters = torch.zeros(n * self.kv_heads * tiles, dtype=torch.int32, device=self.device)
+        n_pairs = n * self.kv_heads * tiles
+        # prefix sums of the work units of every (sequence, KV head, head tile) pair
+        units = [int(N.library().inq_decode_units(len(s.decode_state.key_blocks), self.block_tokens))
+                 for s in sequences for _ in range(self.kv_heads * tiles)]
+        starts = torch.tensor([0] + units, dtype=torch.int64).cumsum(0)
+        self.total_units = int(starts[-1])
+        self.pair_starts = starts.to(self.device)
+        self.partials = torch.empty(workspace_floats(n_pairs, self.total_units), dtype=torch.float32, device=self.device)
+        self.counters = torch.zeros(n_pairs, dtype=torch.int32, device=self.device)
         self.launches = 0
         self._initial_counters = self.tail_counters.clone()
         self._prepare_launch_arguments()
@@ -148,8 +151,9 @@ class DecodeBatch:
         args.kv_heads, args.q_per_kv = self.kv_heads, self.q_per_kv
         args.block_tokens, args.n_pad = self.block_tokens, self.n_pad
         args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[self.dtype], self.scale
-        args.n_parts = self.n_parts
-        args.partials, args.counters = self.partials.data_ptr(), self.counters.data_ptr()
+        args.pair_starts, args.total_units = self.pair_starts.data_ptr(), self.total_units
+        args.partials, args.partials_floats = self.partials.data_ptr(), self.partials.numel()
+        args.counters = self.counters.data_ptr()
         args.status = N.status_word(self.device).data_ptr()
         self._decode_args = args
         self._decode_args_ref = ctypes.byref(args)

@@ -47,11 +47,14 @@ class SharedDecodeWorkspace:
         return self.tensor[:required].view(shape)
 
 
-def plan_parts(kv_heads: int, q_per_kv: int, slices: int, n_seq: int = 1) -> int:
-    parts = N.library().inq_decode_plan_parts(n_seq, kv_heads, q_per_kv, max(1, slices))
-    if parts < 1:
-        raise ValueError("invalid decode geometry")
-    return parts
+def workspace_floats(n_pairs: int, total_units: int) -> int:
+    """Scratch floats for the split-KV partial records of ``n_pairs`` (sequence, KV head,
+    8-query-head tile) pairs holding ``total_units`` 32-token slices on the current device."""
+    return int(N.library().inq_decode_workspace_floats(n_pairs, total_units))
+
+
+def pair_units(n_blocks: int, block_tokens: int) -> int:
+    return int(N.library().inq_decode_units(n_blocks, block_tokens))
 
 
 class PackedDecodeState:
@@ -208,9 +211,9 @@ class PackedDecodeState:
             raise RuntimeError("Packed decode state requires one CUDA stream per state")
         q_per_kv = query.shape[1] // kv_heads
         tiles = (q_per_kv + 7) // 8
-        slices = n_blocks * ((self._packed_tokens + 15) // 16) + 4 * ((sink_t + 15) // 16 + (residual_t + 15) // 16)
-        parts = plan_parts(kv_heads, q_per_kv, slices)
-        workspace_shape = (kv_heads * tiles, parts, N.RECORD_FLOATS)
+        pairs = kv_heads * tiles
+        records = workspace_floats(pairs, pairs * pair_units(n_blocks, self._packed_tokens)) // N.RECORD_FLOATS
+        workspace_shape = (records, N.RECORD_FLOATS)
         if self._workspace_pool is not None:
             workspace = self._workspace_pool.acquire(workspace_shape, query.device)
         else:
@@ -243,8 +246,7 @@ class PackedDecodeState:
         args.kv_heads, args.q_per_kv = kv_heads, q_per_kv
         args.block_tokens, args.n_pad = self._packed_tokens, self._salient
         args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[query.dtype], scale
-        args.n_parts = parts
-        args.partials = workspace.data_ptr()
+        args.partials, args.partials_floats = workspace.data_ptr(), workspace.numel()
         args.counters = N.decode_counters(query.device, kv_heads * tiles).data_ptr()
         args.status = N.status_word(query.device).data_ptr()
         rc = N.library().inq_decode_attention(N.ctypes.byref(args), N.stream_pointer(query.device))
