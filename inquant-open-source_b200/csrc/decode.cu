@@ -33,14 +33,20 @@ namespace inq {
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;
-constexpr int kSliceTokens = 32;                    // tokens staged and processed per loop iteration
-constexpr int kStageK = 2048, kStageV = 1024, kStageP = 256;
+#ifndef INQ_DECODE_SUB
+#define INQ_DECODE_SUB 2                             // 16-token sub-slices per loop iteration (1 or 2)
+#endif
+constexpr int kSub = INQ_DECODE_SUB;
+constexpr int kSliceTokens = 16 * kSub;             // tokens staged and processed per loop iteration
+constexpr int kCtasPerSm = kSub == 1 ? 4 : 3;       // register budget: 128 vs 168 per thread
+constexpr int kStageK = 1024 * kSub, kStageV = 512 * kSub, kStageP = 128 * kSub;
 constexpr int kStageBytes = kStageK + kStageV + kStageP;
 constexpr int kRecordStride = 132;                  // floats per query head: acc[128], m, l, pad
 constexpr int kRecordFloats = 8 * kRecordStride;    // one partial record (8 query heads)
 constexpr int kQChunk = 36;                         // padded 32-float chunk of the staged query
 constexpr float kNegBig = -1.0e30f;
-constexpr int kWarpFixed = 2048 + 256 + 256 + 64 + 64;   // per-warp scratch before the per-group parts
+constexpr int kWarpFixed = 2048 + 256 + 64 + 64 + 1024;  // per-warp scratch before the per-group parts
+constexpr float kRescaleSlack = 4.f;   // the running reference maximum may lag the true one by 2^4
 
 __host__ __device__ constexpr int warp_smem_bytes(int groups) {
   return kWarpFixed + groups * (256 + 4096) + kStages * kStageBytes;
@@ -84,13 +90,13 @@ struct BlockPtrs {
 // ------------------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ void mma_f16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                         unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                          unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -104,7 +110,7 @@ __device__ __forceinline__ void mma_qt(float (&d)[4], unsigned a0, unsigned a1, 
 }
 __device__ __forceinline__ unsigned movmatrix_trans(unsigned x) {
   unsigned y;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
   return y;
 }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -120,7 +126,14 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N));
 }
-// Shared-memory loads through 32-bit shared addresses with compile-time byte offsets.
+// Shared-memory loads through 32-bit shared addresses with compile-time byte offsets.  They are
+// pure asm statements so that the compiler may schedule them freely among the MMAs; an address
+// passed through launder() after a synchronisation point cannot be read before that point, nor
+// can its loads be merged with those of an earlier loop iteration.
+__device__ __forceinline__ unsigned launder(unsigned addr) {
+  asm volatile("" : "+r"(addr));
+  return addr;
+}
 template <int OFF>
 __device__ __forceinline__ uint4 lds128(unsigned addr) {
   uint4 v;
@@ -143,7 +156,7 @@ __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)
 // D = A*B with a zero accumulator (first step of a chain: nothing to keep live or to clear)
 __device__ __forceinline__ void mma_f16_first(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                               unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%10,%10,%10,%10};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%10,%10,%10,%10};"
                : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
@@ -203,34 +216,46 @@ __device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const l
 __device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned char* kp, const unsigned char* vp,
                                             const unsigned char* vs, const unsigned char* vo, int tok0, int T, int lane) {
   const int v_dst = kStageK + (((lane >> 1) * 2 + ((lane & 1) ^ ((lane >> 3) & 1))) << 4);
+  // parameter vectors: 4 bytes (two fp16 group values) per token; with 16-token slices the lower
+  // half-warp copies the scales and the upper half-warp the offsets
+  const int p_tok = kSub == 1 ? (lane & 15) : lane;
+  const bool p_both = kSub > 1;
   if (tok0 + kSliceTokens <= T) {
-    // all 32 tokens exist: K tile, V tile and parameter vectors are contiguous in global memory
+    // every token exists: K tile, V tile and parameter vectors are contiguous in global memory
     const unsigned char* ksrc = kp + tok0 * 64 + lane * 16;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) cp_async16(stage + lane * 16 + k * 512, ksrc + k * 512);
+    for (int k = 0; k < 2 * kSub; ++k) cp_async16(stage + lane * 16 + k * 512, ksrc + k * 512);
     const unsigned char* vsrc = vp + tok0 * 32 + lane * 16;
-    cp_async16(stage + v_dst, vsrc);
-    cp_async16(stage + v_dst + 512, vsrc + 512);
-    cp_async4(stage + kStageK + kStageV + lane * 4, vs + (tok0 + lane) * 4);
-    cp_async4(stage + kStageK + kStageV + 128 + lane * 4, vo + (tok0 + lane) * 4);
+#pragma unroll
+    for (int k = 0; k < kSub; ++k) cp_async16(stage + v_dst + k * 512, vsrc + k * 512);
+    if (p_both) {
+      cp_async4(stage + kStageK + kStageV + lane * 4, vs + (tok0 + lane) * 4);
+      cp_async4(stage + kStageK + kStageV + kStageP / 2 + lane * 4, vo + (tok0 + lane) * 4);
+    } else {
+      cp_async4(stage + kStageK + kStageV + (lane < 16 ? 0 : kStageP / 2) + p_tok * 4, (lane < 16 ? vs : vo) + (tok0 + p_tok) * 4);
+    }
   } else {
     const int last = T - 1;
     const int r = lane >> 2, j = lane & 3;
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
+    for (int k = 0; k < 2 * kSub; ++k)
       cp_async16(stage + lane * 16 + k * 512, kp + min(tok0 + r + 8 * k, last) * 64 + j * 16);
 #pragma unroll
-    for (int k = 0; k < 2; ++k)
+    for (int k = 0; k < kSub; ++k)
       cp_async16(stage + v_dst + k * 512, vp + min(tok0 + (lane >> 1) + 16 * k, last) * 32 + (lane & 1) * 16);
-    const int tp = min(tok0 + lane, last);
-    cp_async4(stage + kStageK + kStageV + lane * 4, vs + tp * 4);
-    cp_async4(stage + kStageK + kStageV + 128 + lane * 4, vo + tp * 4);
+    const int tp = min(tok0 + p_tok, last);
+    if (p_both) {
+      cp_async4(stage + kStageK + kStageV + lane * 4, vs + tp * 4);
+      cp_async4(stage + kStageK + kStageV + kStageP / 2 + lane * 4, vo + tp * 4);
+    } else {
+      cp_async4(stage + kStageK + kStageV + (lane < 16 ? 0 : kStageP / 2) + p_tok * 4, (lane < 16 ? vs : vo) + tp * 4);
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------------ the kernel
 template <int MODE, typename QT, bool SAL>
-__global__ void __launch_bounds__(kThreads, 3) decode_kernel(const DecodeParams P) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const DecodeParams P) {
   extern __shared__ __align__(16) unsigned char smem[];
   float* qs = (float*)smem;                                             // 8 heads x 4 chunks x kQChunk
   unsigned char* warp_base = smem + 8 * 4 * kQChunk * 4;
@@ -244,11 +269,11 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const DecodeParams 
   unsigned char* wW = wb;
   float* wf = (float*)wb;                                               // slot weight per channel
   float* wk0 = wf + 128;                                                // additive constant per channel
-  short* wroles = (short*)(wb + 2048);                                  // role map of the current block
-  float* wssc = (float*)(wroles + 128);                                 // scale of salient channel i
+  float* wssc = (float*)(wb + 2048);                                    // scale of salient channel i
   unsigned char* wsrc = (unsigned char*)(wssc + 64);                    // channel of salient i
   unsigned char* wdon = wsrc + 64;                                      // its donor slot
-  unsigned char* wqsal = wdon + 64;                                     // B fragments: query at salient channels
+  unsigned char* wmeta = wdon + 64;       // staged block metadata: K scales 512 B | role map 256 B | padding 256 B
+  unsigned char* wqsal = wb + kWarpFixed;                               // B fragments: query at salient channels
   unsigned char* wsel = wqsal + groups * 256;                           // B fragments: nibble selection
   unsigned char* ring = wsel + groups * 4096;
   __shared__ int s_is_last;
@@ -325,384 +350,9 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const DecodeParams 
     for (int k = 0; k < 4; ++k) acc[mt][k] = 0.f;
   float oacc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
 
-  // ---------------------------------------------------------------- packed history
-  if (pb > pa) {
-    const int n_my = (int)(pb - pa);
-    int pf_block = (int)(pa / spb), pf_slice = (int)(pa % spb);   // prefetch cursor
-    BlockPtrs pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
-    int to_issue = n_my, issue_stage = 0;
-    auto issue = [&]() {
-      if (to_issue > 0) {
-        stage_slice(ring + issue_stage * kStageBytes, pf_ptrs.kp, pf_ptrs.vp, pf_ptrs.vs, pf_ptrs.vo,
-                    pf_slice * kSliceTokens, T, lane);
-        --to_issue;
-        if (++issue_stage == kStages) issue_stage = 0;
-        if (++pf_slice == spb) {
-          pf_slice = 0;
-          ++pf_block;
-          if (to_issue > 0) pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
-        }
-      }
-      cp_async_commit();
-    };
-#pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) issue();
-
-    int cur_block = (int)(pa / spb), cur_slice = (int)(pa % spb);
-    bool need_weights = true;
-    float alpha[2] = {0.f, 0.f}, beta[2] = {0.f, 0.f};
-    const unsigned vsel = (r & 1) ? 0x7632u : 0x5410u;
-    // byte offset (inside a stage's V area) of this lane's word of token 2j for value group 0
-    // and group 1; tokens 2j+1, 2j+8, 2j+9 follow at +32, +256, +288
-    const unsigned v_base0 = (unsigned)((((2 * j) * 2 + (((2 * j) >> 2) & 1)) << 4) + (r >> 1) * 4);
-    const unsigned v_base1 = v_base0 ^ 16u;
-    const unsigned ring_addr = smem_addr(ring), lane16 = lane * 16;
-    const unsigned ww_addr = smem_addr(wW) + lane * 8, sel_addr = smem_addr(wsel) + lane * 16;
-    int stage_index = 0;
-
-    for (int it = 0; it < n_my; ++it) {
-      cp_async_wait<kStages - 2>();
-      __syncwarp();
-      issue();
-
-      if (need_weights) {
-        // ---- fold this block's descriptor, scales and padding into the query
-        BlockPtrs cb = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, cur_block, h);
-        const float4 sc = *(const float4*)(cb.ks + lane * 16);
-        int role[4];
-        if (MODE == 0) {
-          unsigned bits = *(const unsigned*)(cb.kr + lane * 4);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) role[i] = (int)(signed char)((bits >> (8 * i)) & 0xff);
-        } else {
-          uint2 bits = *(const uint2*)(cb.kr + lane * 8);
-          role[0] = (int)(short)(bits.x & 0xffff);
-          role[1] = (int)(short)(bits.x >> 16);
-          role[2] = (int)(short)(bits.y & 0xffff);
-          role[3] = (int)(short)(bits.y >> 16);
-        }
-        const float scv[4] = {sc.x, sc.y, sc.z, sc.w};
-        bool bad = false;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          if (role[i] > 127 || role[i] < -1 - P.n_pad) {
-            bad = true;
-            role[i] = -1;
-          }
-          wroles[lane * 4 + i] = (short)role[i];
-        }
-        // clear the nibble-selection fragments of the salient path
-        for (int v = lane; v < groups * 256; v += 32) ((uint4*)wsel)[v] = make_uint4(0u, 0u, 0u, 0u);
-        if (lane < groups * 16) {
-          wsrc[lane] = 0;
-          wdon[lane] = 0;
-          wssc[lane] = 0.f;
-        }
-        if (groups > 2 && lane + 32 < groups * 16) {
-          wsrc[lane + 32] = 0;
-          wdon[lane + 32] = 0;
-          wssc[lane + 32] = 0.f;
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = lane * 4 + i;
-          const int ro = role[i];
-          if (ro == -1) {
-            wf[c] = scv[i];
-            wk0[c] = -8.f * scv[i];
-          } else if (ro >= 0) {
-            // salient: both of its slots leave the linear fold; its exact, dtype-rounded value
-            // is rebuilt per token by the salient path below
-            wf[c] = 0.f;
-            wk0[c] = 0.f;
-            wf[ro] = 0.f;
-            const int idx = -(int)wroles[ro] - 2;
-            if (idx >= 0 && idx < P.n_pad) {
-              wsrc[idx] = (unsigned char)c;
-              wdon[idx] = (unsigned char)ro;
-              wssc[idx] = scv[i];
-            } else {
-              bad = true;
-            }
-          } else {
-            // donor: the reference stores the sampled mean and rounds it to the model dtype
-            wk0[c] = to_float<QT>(from_float<QT>(((const float*)cb.kpad)[-ro - 2]));
-          }
-        }
-        if (bad) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
-        __syncwarp();
-        // selection matrix: column i picks 16 * (high nibble of source i) + (low nibble in its
-        // donor slot), scaled by 2^11 so that every entry and every partial sum is exact
-        for (int i = lane; i < P.n_pad; i += 32) {
-#pragma unroll
-          for (int which = 0; which < 2; ++which) {
-            const int c = which ? wdon[i] : wsrc[i];
-            const int jj = c >> 5, u = c & 31;
-            const int ks = 2 * (u >> 3) + ((u >> 1) & 1), half = u & 1, e = (u >> 2) & 1;
-            const int target = ((i & 7) << 2) | jj;
-            float value = which ? 2048.f : 32768.f;
-            if (half) value *= 0.0625f;
-            __half* cell = (__half*)(wsel + ((((i >> 4) * 8 + ks) * 32 + target) * 16) + (((i >> 3) & 1) * 2 + half) * 4 + e * 2);
-            *cell = __float2half_rn(value);
-          }
-        }
-        // query at the salient channels, as B fragments of the salient step
-        for (int gsel = 0; gsel < groups; ++gsel) {
-          unsigned short qv[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int i = gsel * 16 + 2 * j + (k & 1) + (k >> 1) * 8;
-            const bool live = r < g_valid && i < P.n_pad;
-            qv[k] = live ? *(const unsigned short*)(qptr + (q_head0 + r) * q_stride + wsrc[i]) : (unsigned short)0;
-          }
-          *(uint2*)(wqsal + (gsel * 32 + lane) * 8) = make_uint2((unsigned)qv[0] | ((unsigned)qv[1] << 16),
-                                                                 (unsigned)qv[2] | ((unsigned)qv[3] << 16));
-        }
-        __syncwarp();
-        // thread (head r, chunk j) owns the 32 channels 32j..32j+31 of query head r
-        float w[32];
-        float cpart = 0.f, wmax = 0.f;
-        const float* qown = qs + (r * 4 + j) * kQChunk;
-#pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const float4 f4 = *(const float4*)(wf + 32 * j + 4 * i4);
-          const float4 k4 = *(const float4*)(wk0 + 32 * j + 4 * i4);
-          const float4 q4 = *(const float4*)(qown + 4 * i4);
-          const float fv[4] = {f4.x, f4.y, f4.z, f4.w};
-          const float kv[4] = {k4.x, k4.y, k4.z, k4.w};
-          const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            w[4 * i4 + e] = qv[e] * fv[e];
-            wmax = fmaxf(wmax, fabsf(w[4 * i4 + e]));
-            cpart = fmaf(qv[e], kv[e], cpart);
-          }
-        }
-        cpart += __shfl_xor_sync(0xffffffffu, cpart, 1);
-        cpart += __shfl_xor_sync(0xffffffffu, cpart, 2);
-        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 1));
-        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 2));
-        // scale the row into [2^13, 2^14) so that fp16 neither overflows nor loses small weights
-        int ex = (int)((__float_as_uint(wmax) >> 23) & 0xff) - 127;
-        ex = max(-100, min(100, ex));
-        if (wmax == 0.f) ex = 13;
-        const float up = __uint_as_float((unsigned)(127 + 13 - ex) << 23);
-        const float inv = __uint_as_float((unsigned)(127 + ex + 11) << 23);   // 2^24 / up
-        const float up16 = up * 0.0625f;
-        __syncwarp();   // every lane has read the per-channel weights that wW overwrites
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          const int base = 8 * (s >> 1) + 2 * (s & 1);
-          *(uint2*)(wW + (s * 32 + lane) * 8) = make_uint2(pack_half2(w[base] * up, w[base + 4] * up),
-                                                            pack_half2(w[base + 1] * up16, w[base + 5] * up16));
-        }
-        // score columns of this thread are query heads 2j and 2j+1
-        alpha[0] = __shfl_sync(0xffffffffu, inv, (2 * j) * 4);
-        alpha[1] = __shfl_sync(0xffffffffu, inv, (2 * j + 1) * 4);
-        beta[0] = __shfl_sync(0xffffffffu, cpart, (2 * j) * 4);
-        beta[1] = __shfl_sync(0xffffffffu, cpart, (2 * j + 1) * 4);
-        need_weights = false;
-      }
-
-      const unsigned stage = ring_addr + stage_index * kStageBytes;
-      if (++stage_index == kStages) stage_index = 0;
-      // ---- scores of two 16-token sub-slices (tokens 0..15 and 16..31 of the stage): K nibbles
-      //      times the folded query, plus the exactly rebuilt salient channels
-      float S[2][4], S2[2][4];
-      {
-        float C[2][2][4];   // [sub-slice][n-tile][frag]: code' = 16*hi + lo of salient group 0
-        // One sub-slice at a time keeps the live register set small: this lane's 16 bytes
-        // (channels 32j..32j+31) of tokens r and r+8 of the sub-slice.
-#define INQ_KSTEP(U, KS, X, Y, FIRST)                                                                     \
-  {                                                                                                       \
-    const unsigned a0 = (X) & 0x000F000Fu, a1 = (Y) & 0x000F000Fu, a2 = (X) & 0x00F000F0u, a3 = (Y) & 0x00F000F0u; \
-    const uint2 wq = lds64<(KS) * 256>(ww_addr);                                                          \
-    if (FIRST) mma_f16_first(S[U], a0, a1, a2, a3, wq.x, wq.y);                                           \
-    else mma_f16(S[U], a0, a1, a2, a3, wq.x, wq.y);                                                       \
-    if (SAL) {                                                                                            \
-      const uint4 f = lds128<(KS) * 512>(sel_addr);                                                       \
-      if (FIRST) {                                                                                        \
-        mma_f16_first(C[U][0], a0, a1, a2, a3, f.x, f.y);                                                 \
-        mma_f16_first(C[U][1], a0, a1, a2, a3, f.z, f.w);                                                 \
-      } else {                                                                                            \
-        mma_f16(C[U][0], a0, a1, a2, a3, f.x, f.y);                                                       \
-        mma_f16(C[U][1], a0, a1, a2, a3, f.z, f.w);                                                       \
-      }                                                                                                   \
-    }                                                                                                     \
-  }
-#define INQ_KSUB(U)                                                                                       \
-  {                                                                                                       \
-    const uint4 kx = lds128<1024 * (U)>(stage + lane16), ky = lds128<1024 * (U) + 512>(stage + lane16);   \
-    INQ_KSTEP(U, 0, kx.x, ky.x, true)                                                                     \
-    INQ_KSTEP(U, 1, kx.x >> 8, ky.x >> 8, false)                                                          \
-    INQ_KSTEP(U, 2, kx.y, ky.y, false)                                                                    \
-    INQ_KSTEP(U, 3, kx.y >> 8, ky.y >> 8, false)                                                          \
-    INQ_KSTEP(U, 4, kx.z, ky.z, false)                                                                    \
-    INQ_KSTEP(U, 5, kx.z >> 8, ky.z >> 8, false)                                                          \
-    INQ_KSTEP(U, 6, kx.w, ky.w, false)                                                                    \
-    INQ_KSTEP(U, 7, kx.w >> 8, ky.w >> 8, false)                                                          \
-  }
-        INQ_KSUB(0)
-        INQ_KSUB(1)
-#undef INQ_KSUB
-#undef INQ_KSTEP
-        if (SAL) {
-#pragma unroll
-          for (int u = 0; u < 2; ++u)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) S2[u][k] = 0.f;
-          for (int gsel = 0; gsel < groups; ++gsel) {
-            if (gsel) {
-              // further groups of 16 salient channels (salient fractions above 1/8)
-              const uint4 k0 = lds128<0>(stage + lane16), k1 = lds128<512>(stage + lane16);
-              const uint4 k2 = lds128<1024>(stage + lane16), k3 = lds128<1536>(stage + lane16);
-              const unsigned kw[4][4] = {{k0.x, k0.y, k0.z, k0.w}, {k1.x, k1.y, k1.z, k1.w},
-                                         {k2.x, k2.y, k2.z, k2.w}, {k3.x, k3.y, k3.z, k3.w}};
-#pragma unroll
-              for (int u = 0; u < 2; ++u)
-#pragma unroll
-                for (int n = 0; n < 2; ++n)
-#pragma unroll
-                  for (int k = 0; k < 4; ++k) C[u][n][k] = 0.f;
-              const uint4* selg = (const uint4*)wsel + gsel * 256 + lane;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                unsigned x0 = kw[0][i], y0 = kw[1][i], x1 = kw[2][i], y1 = kw[3][i];
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                  const uint4 f = selg[(2 * i + hh) * 32];
-                  const unsigned a0 = x0 & 0x000F000Fu, a1 = y0 & 0x000F000Fu, a2 = x0 & 0x00F000F0u, a3 = y0 & 0x00F000F0u;
-                  const unsigned b0 = x1 & 0x000F000Fu, b1 = y1 & 0x000F000Fu, b2 = x1 & 0x00F000F0u, b3 = y1 & 0x00F000F0u;
-                  mma_f16(C[0][0], a0, a1, a2, a3, f.x, f.y);
-                  mma_f16(C[1][0], b0, b1, b2, b3, f.x, f.y);
-                  mma_f16(C[0][1], a0, a1, a2, a3, f.z, f.w);
-                  mma_f16(C[1][1], b0, b1, b2, b3, f.z, f.w);
-                  x0 >>= 8; y0 >>= 8; x1 >>= 8; y1 >>= 8;
-                }
-              }
-            }
-            // value = fl32((code' - 128) * scale) rounded to the model dtype, as the reference's
-            // dequantised tensor holds it
-            const float2 sc0 = *(const float2*)(wssc + gsel * 16 + 2 * j);
-            const float2 sc1 = *(const float2*)(wssc + gsel * 16 + 8 + 2 * j);
-            const uint2 qb = *(const uint2*)(wqsal + (gsel * 32 + lane) * 8);
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const unsigned a0 = pack_qt2<QT>(fmaf(C[u][0][0], 8192.f, -128.f) * sc0.x, fmaf(C[u][0][1], 8192.f, -128.f) * sc0.y);
-              const unsigned a1 = pack_qt2<QT>(fmaf(C[u][0][2], 8192.f, -128.f) * sc0.x, fmaf(C[u][0][3], 8192.f, -128.f) * sc0.y);
-              const unsigned a2 = pack_qt2<QT>(fmaf(C[u][1][0], 8192.f, -128.f) * sc1.x, fmaf(C[u][1][1], 8192.f, -128.f) * sc1.y);
-              const unsigned a3 = pack_qt2<QT>(fmaf(C[u][1][2], 8192.f, -128.f) * sc1.x, fmaf(C[u][1][3], 8192.f, -128.f) * sc1.y);
-              mma_qt<QT>(S2[u], a0, a1, a2, a3, qb.x, qb.y);
-            }
-          }
-        }
-      }
-      // s2[u][k]: sub-slice u; k = 0,1 -> token r (+16u), heads 2j, 2j+1; k = 2,3 -> token r+8 (+16u)
-      float s2[2][4];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        s2[u][0] = fmaf(S[u][0], alpha[0], beta[0]);
-        s2[u][1] = fmaf(S[u][1], alpha[1], beta[1]);
-        s2[u][2] = fmaf(S[u][2], alpha[0], beta[0]);
-        s2[u][3] = fmaf(S[u][3], alpha[1], beta[1]);
-        if (SAL) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k) s2[u][k] = fmaf(S2[u][k], P.scale_log2e, s2[u][k]);
-        }
-      }
-      {
-        const int tok0 = cur_slice * kSliceTokens;
-        const long long g0 = (long long)cur_block * T + tok0;
-        if (tok0 + kSliceTokens > T || g0 < first_visible) {
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int t_lo = tok0 + 16 * u + r, t_hi = t_lo + 8;
-            if (!(t_lo < T && g0 + 16 * u + r >= first_visible)) s2[u][0] = s2[u][1] = -INFINITY;
-            if (!(t_hi < T && g0 + 16 * u + r + 8 >= first_visible)) s2[u][2] = s2[u][3] = -INFINITY;
-          }
-        }
-      }
-      // ---- online softmax (base 2) over the 32 tokens
-      float mx0 = fmaxf(fmaxf(s2[0][0], s2[0][2]), fmaxf(s2[1][0], s2[1][2]));
-      float mx1 = fmaxf(fmaxf(s2[0][1], s2[0][3]), fmaxf(s2[1][1], s2[1][3]));
-#pragma unroll
-      for (int off = 4; off < 32; off <<= 1) {
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-      }
-      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-      if (__any_sync(0xffffffffu, mn0 > m_run[0] || mn1 > m_run[1])) {
-        const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
-        l_run[0] *= a0;
-        l_run[1] *= a1;
-        oacc[0][0] *= a0; oacc[1][0] *= a0;
-        oacc[0][1] *= a1; oacc[1][1] *= a1;
-#pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-          acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
-        }
-        m_run[0] = mn0;
-        m_run[1] = mn1;
-      }
-      float pr[2][4];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        pr[u][0] = fast_exp2(s2[u][0] - m_run[0]);
-        pr[u][1] = fast_exp2(s2[u][1] - m_run[1]);
-        pr[u][2] = fast_exp2(s2[u][2] - m_run[0]);
-        pr[u][3] = fast_exp2(s2[u][3] - m_run[1]);
-        l_run[0] += pr[u][0] + pr[u][2];
-        l_run[1] += pr[u][1] + pr[u][3];
-      }
-      // ---- values: probabilities times the per-token group scale, codes as fp16 subnormals
-#define INQ_PV(U)                                                                                          \
-  {                                                                                                        \
-    const unsigned sp = stage + kStageK + kStageV + 4 * r;                                                 \
-    const float2 vs_lo = half2_bits_to_float2(lds32<64 * (U)>(sp)), vs_hi = half2_bits_to_float2(lds32<64 * (U) + 32>(sp)); \
-    const float2 vo_lo = half2_bits_to_float2(lds32<128 + 64 * (U)>(sp)), vo_hi = half2_bits_to_float2(lds32<128 + 64 * (U) + 32>(sp)); \
-    oacc[0][0] += pr[U][0] * vo_lo.x + pr[U][2] * vo_hi.x;                                                 \
-    oacc[0][1] += pr[U][1] * vo_lo.x + pr[U][3] * vo_hi.x;                                                 \
-    oacc[1][0] += pr[U][0] * vo_lo.y + pr[U][2] * vo_hi.y;                                                 \
-    oacc[1][1] += pr[U][1] * vo_lo.y + pr[U][3] * vo_hi.y;                                                 \
-    _Pragma("unroll") for (int gr = 0; gr < 2; ++gr) {                                                     \
-      const float sl = gr ? vs_lo.y : vs_lo.x, sh = gr ? vs_hi.y : vs_hi.x;                                \
-      const unsigned b0 = movmatrix_trans(pack_half2(pr[U][0] * sl, pr[U][1] * sl));                       \
-      const unsigned b1 = movmatrix_trans(pack_half2(pr[U][2] * sh, pr[U][3] * sh));                       \
-      const unsigned vb = stage + (gr ? v_base1 : v_base0);                                                \
-      const unsigned wA = lds32<kStageK + 512 * (U)>(vb), wB = lds32<kStageK + 512 * (U) + 32>(vb);        \
-      const unsigned wC = lds32<kStageK + 512 * (U) + 256>(vb), wD = lds32<kStageK + 512 * (U) + 288>(vb); \
-      const unsigned M0 = __byte_perm(wA, wB, vsel), M1 = __byte_perm(wC, wD, vsel);                       \
-      const unsigned N0 = M0 >> 10, N1 = M1 >> 10;                                                         \
-      mma_f16(acc[gr * 4 + 0], M0 & 0x00030003u, M0 & 0x000C000Cu, M1 & 0x00030003u, M1 & 0x000C000Cu, b0, b1); \
-      mma_f16(acc[gr * 4 + 1], M0 & 0x00300030u, M0 & 0x00C000C0u, M1 & 0x00300030u, M1 & 0x00C000C0u, b0, b1); \
-      mma_f16(acc[gr * 4 + 2], M0 & 0x03000300u, N0 & 0x00030003u, M1 & 0x03000300u, N1 & 0x00030003u, b0, b1); \
-      mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1); \
-    }                                                                                                      \
-  }
-      INQ_PV(0)
-      INQ_PV(1)
-#undef INQ_PV
-      if (++cur_slice == spb) {
-        cur_slice = 0;
-        ++cur_block;
-        need_weights = true;
-      }
-    }
-    cp_async_wait<0>();
-    // a code at bit offset o of its 16-bit lane was multiplied as code * 2^(o-24)
-    const float fx[4] = {16777216.f, 1048576.f, 65536.f, 4194304.f};   // offsets 0, 4, 8, 2
-    const float fy[4] = {4194304.f, 262144.f, 16777216.f, 1048576.f};  // offsets 2, 6, 0, 4
-#pragma unroll
-    for (int mt = 0; mt < 8; ++mt) {
-      acc[mt][0] *= fx[mt & 3];
-      acc[mt][1] *= fx[mt & 3];
-      acc[mt][2] *= fy[mt & 3];
-      acc[mt][3] *= fy[mt & 3];
-    }
-  }
-
   // ---------------------------------------------------------------- exact sink and tail
+  // (run while the first packed slices are still in flight, see below)
+  auto dense_part = [&]() {
   if (worker < n_dense) {
     unsigned qf[16];
     {
@@ -790,6 +440,442 @@ __global__ void __launch_bounds__(kThreads, 3) decode_kernel(const DecodeParams 
         }
       }
     }
+  }
+
+  };
+
+  // ---------------------------------------------------------------- packed history
+  if (pb > pa) {
+    const int n_my = (int)(pb - pa);
+    int pf_block = (int)(pa / spb), pf_slice = (int)(pa % spb);   // prefetch cursor
+    BlockPtrs pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
+    int to_issue = n_my, issue_stage = 0;
+    int meta_block = -1;        // block whose metadata is staged (or in flight) in wmeta
+    int folded_block = -2;      // last block whose weights were derived from wmeta
+    auto stage_meta = [&](const BlockPtrs& bp) {
+      cp_async16(wmeta + lane * 16, bp.ks + lane * 16);
+      if (lane < (MODE == 0 ? 8 : 16)) cp_async16(wmeta + 512 + lane * 16, bp.kr + lane * 16);
+      for (int i = lane; i < P.n_pad; i += 32) cp_async4(wmeta + 768 + i * 4, bp.kpad + i * 4);
+    };
+    auto issue = [&]() {
+      if (to_issue > 0) {
+        // a new block's metadata rides in the same group as its first slice, provided the
+        // staging area is no longer needed by an earlier block
+        const bool first_of_block = to_issue == n_my || pf_slice == 0;
+        if (first_of_block && (meta_block < 0 || folded_block == meta_block)) {
+          stage_meta(pf_ptrs);
+          meta_block = pf_block;
+        }
+        stage_slice(ring + issue_stage * kStageBytes, pf_ptrs.kp, pf_ptrs.vp, pf_ptrs.vs, pf_ptrs.vo,
+                    pf_slice * kSliceTokens, T, lane);
+        --to_issue;
+        if (++issue_stage == kStages) issue_stage = 0;
+        if (++pf_slice == spb) {
+          pf_slice = 0;
+          ++pf_block;
+          if (to_issue > 0) pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
+        }
+      }
+      cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) issue();
+    // the dense slices of this warp hide behind the DRAM latency of the first packed slices;
+    // their contribution is brought into the packed loop's per-row units (powers of two)
+    dense_part();
+    {
+      const float ix[4] = {1.f / 16777216.f, 1.f / 1048576.f, 1.f / 65536.f, 1.f / 4194304.f};
+      const float iy[4] = {1.f / 4194304.f, 1.f / 262144.f, 1.f / 16777216.f, 1.f / 1048576.f};
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        acc[mt][0] *= ix[mt & 3];
+        acc[mt][1] *= ix[mt & 3];
+        acc[mt][2] *= iy[mt & 3];
+        acc[mt][3] *= iy[mt & 3];
+      }
+    }
+
+    int cur_block = (int)(pa / spb), cur_slice = (int)(pa % spb);
+    bool need_weights = true;
+    float alpha[2] = {0.f, 0.f}, beta[2] = {0.f, 0.f};
+    const unsigned vsel = (r & 1) ? 0x7632u : 0x5410u;
+    // byte offset (inside a stage's V area) of this lane's word of token 2j for value group 0
+    // and group 1; tokens 2j+1, 2j+8, 2j+9 follow at +32, +256, +288
+    const unsigned v_base0 = (unsigned)((((2 * j) * 2 + (((2 * j) >> 2) & 1)) << 4) + (r >> 1) * 4);
+    const unsigned v_base1 = v_base0 ^ 16u;
+    const unsigned ring_addr = smem_addr(ring), lane16 = lane * 16;
+    const unsigned ww_addr = smem_addr(wW) + lane * 8, sel_addr = smem_addr(wsel) + lane * 16;
+    int stage_index = 0;
+
+    for (int it = 0; it < n_my; ++it) {
+      cp_async_wait<kStages - 2>();
+      __syncwarp();
+      issue();
+
+      if (need_weights) {
+        // ---- fold this block's descriptor, scales and padding into the query
+        if (meta_block != cur_block) {
+          // not prefetched (very short blocks): fetch now and wait for it alone
+          BlockPtrs cb = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, cur_block, h);
+          __syncwarp();
+          stage_meta(cb);
+          cp_async_commit();
+          cp_async_wait<0>();
+          meta_block = cur_block;
+          __syncwarp();
+        }
+        folded_block = cur_block;
+        const float4 sc = *(const float4*)(wmeta + lane * 16);
+        const unsigned char* meta_roles = wmeta + 512;
+        const float* meta_pad = (const float*)(wmeta + 768);
+        int role[4];
+        if (MODE == 0) {
+          unsigned bits = *(const unsigned*)(meta_roles + lane * 4);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) role[i] = (int)(signed char)((bits >> (8 * i)) & 0xff);
+        } else {
+          uint2 bits = *(const uint2*)(meta_roles + lane * 8);
+          role[0] = (int)(short)(bits.x & 0xffff);
+          role[1] = (int)(short)(bits.x >> 16);
+          role[2] = (int)(short)(bits.y & 0xffff);
+          role[3] = (int)(short)(bits.y >> 16);
+        }
+        const float scv[4] = {sc.x, sc.y, sc.z, sc.w};
+        bool bad = false;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (role[i] > 127 || role[i] < -1 - P.n_pad) {
+            bad = true;
+            role[i] = -1;
+          }
+        }
+        // clear the nibble-selection fragments of the salient path
+        for (int v = lane; v < groups * 256; v += 32) ((uint4*)wsel)[v] = make_uint4(0u, 0u, 0u, 0u);
+        if (lane < groups * 16) {
+          wsrc[lane] = 0;
+          wdon[lane] = 0;
+          wssc[lane] = 0.f;
+        }
+        if (groups > 2 && lane + 32 < groups * 16) {
+          wsrc[lane + 32] = 0;
+          wdon[lane + 32] = 0;
+          wssc[lane + 32] = 0.f;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = lane * 4 + i;
+          const int ro = role[i];
+          if (ro == -1) {
+            wf[c] = scv[i];
+            wk0[c] = -8.f * scv[i];
+          } else if (ro >= 0) {
+            // salient: both of its slots leave the linear fold; its exact, dtype-rounded value
+            // is rebuilt per token by the salient path below
+            wf[c] = 0.f;
+            wk0[c] = 0.f;
+            wf[ro] = 0.f;
+            const int idx = -(MODE == 0 ? (int)((const signed char*)meta_roles)[ro] : (int)((const short*)meta_roles)[ro]) - 2;
+            if (idx >= 0 && idx < P.n_pad) {
+              wsrc[idx] = (unsigned char)c;
+              wdon[idx] = (unsigned char)ro;
+              wssc[idx] = scv[i];
+            } else {
+              bad = true;
+            }
+          } else {
+            // donor: the reference stores the sampled mean and rounds it to the model dtype
+            wk0[c] = to_float<QT>(from_float<QT>(meta_pad[-ro - 2]));
+          }
+        }
+        if (bad) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
+        __syncwarp();
+        // selection matrix: column i picks 16 * (high nibble of source i) + (low nibble in its
+        // donor slot), scaled by 2^11 so that every entry and every partial sum is exact
+        for (int i = lane; i < P.n_pad; i += 32) {
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const int c = which ? wdon[i] : wsrc[i];
+            const int jj = c >> 5, u = c & 31;
+            const int ks = 2 * (u >> 3) + ((u >> 1) & 1), half = u & 1, e = (u >> 2) & 1;
+            const int target = ((i & 7) << 2) | jj;
+            float value = which ? 2048.f : 32768.f;
+            if (half) value *= 0.0625f;
+            __half* cell = (__half*)(wsel + ((((i >> 4) * 8 + ks) * 32 + target) * 16) + (((i >> 3) & 1) * 2 + half) * 4 + e * 2);
+            *cell = __float2half_rn(value);
+          }
+        }
+        // query at the salient channels, as B fragments of the salient step
+        for (int gsel = 0; gsel < groups; ++gsel) {
+          unsigned short qv[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = gsel * 16 + 2 * j + (k & 1) + (k >> 1) * 8;
+            const bool live = r < g_valid && i < P.n_pad;
+            qv[k] = live ? *(const unsigned short*)(qptr + (q_head0 + r) * q_stride + wsrc[i]) : (unsigned short)0;
+          }
+          *(uint2*)(wqsal + (gsel * 32 + lane) * 8) = make_uint2((unsigned)qv[0] | ((unsigned)qv[1] << 16),
+                                                                 (unsigned)qv[2] | ((unsigned)qv[3] << 16));
+        }
+        __syncwarp();
+        // thread (head r, chunk j) owns the 32 channels 32j..32j+31 of query head r
+        float w[32];
+        float cpart = 0.f, wmax = 0.f;
+        const float* qown = qs + (r * 4 + j) * kQChunk;
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 f4 = *(const float4*)(wf + 32 * j + 4 * i4);
+          const float4 k4 = *(const float4*)(wk0 + 32 * j + 4 * i4);
+          const float4 q4 = *(const float4*)(qown + 4 * i4);
+          const float fv[4] = {f4.x, f4.y, f4.z, f4.w};
+          const float kv[4] = {k4.x, k4.y, k4.z, k4.w};
+          const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            w[4 * i4 + e] = qv[e] * fv[e];
+            wmax = fmaxf(wmax, fabsf(w[4 * i4 + e]));
+            cpart = fmaf(qv[e], kv[e], cpart);
+          }
+        }
+        cpart += __shfl_xor_sync(0xffffffffu, cpart, 1);
+        cpart += __shfl_xor_sync(0xffffffffu, cpart, 2);
+        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 1));
+        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 2));
+        // scale the row into [2^13, 2^14) so that fp16 neither overflows nor loses small weights
+        int ex = (int)((__float_as_uint(wmax) >> 23) & 0xff) - 127;
+        ex = max(-100, min(100, ex));
+        if (wmax == 0.f) ex = 13;
+        const float up = __uint_as_float((unsigned)(127 + 13 - ex) << 23);
+        const float inv = __uint_as_float((unsigned)(127 + ex + 11) << 23);   // 2^24 / up
+        const float up16 = up * 0.0625f;
+        __syncwarp();   // every lane has read the per-channel weights that wW overwrites
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          const int base = 8 * (s >> 1) + 2 * (s & 1);
+          *(uint2*)(wW + (s * 32 + lane) * 8) = make_uint2(pack_half2(w[base] * up, w[base + 4] * up),
+                                                            pack_half2(w[base + 1] * up16, w[base + 5] * up16));
+        }
+        // score columns of this thread are query heads 2j and 2j+1
+        alpha[0] = __shfl_sync(0xffffffffu, inv, (2 * j) * 4);
+        alpha[1] = __shfl_sync(0xffffffffu, inv, (2 * j + 1) * 4);
+        beta[0] = __shfl_sync(0xffffffffu, cpart, (2 * j) * 4);
+        beta[1] = __shfl_sync(0xffffffffu, cpart, (2 * j + 1) * 4);
+        need_weights = false;
+      }
+
+      const unsigned stage = launder(ring_addr + stage_index * kStageBytes);
+      const unsigned ww_it = launder(ww_addr), sel_it = launder(sel_addr);
+      if (++stage_index == kStages) stage_index = 0;
+      // ---- scores of two 16-token sub-slices (tokens 0..15 and 16..31 of the stage): K nibbles
+      //      times the folded query, plus the exactly rebuilt salient channels
+      float S[2][4], S2[2][4];
+      {
+        float C[2][2][4];   // [sub-slice][n-tile][frag]: code' = 16*hi + lo of salient group 0
+        // One sub-slice at a time keeps the live register set small: this lane's 16 bytes
+        // (channels 32j..32j+31) of tokens r and r+8 of the sub-slice.
+// One K step: the fragments of the NEXT step are fetched before this step's MMAs are issued,
+// so no MMA waits on a shared-memory load that was issued just before it.
+#define INQ_KSTEP(U, KS, X, Y, FIRST, WQ, F, WQN, FN)                                                     \
+  {                                                                                                       \
+    const unsigned a0 = (X) & 0x000F000Fu, a1 = (Y) & 0x000F000Fu, a2 = (X) & 0x00F000F0u, a3 = (Y) & 0x00F000F0u; \
+    if ((KS) < 7) {                                                                                       \
+      WQN = lds64<(((KS) + 1) & 7) * 256>(ww_it);                                                         \
+      if (SAL) FN = lds128<(((KS) + 1) & 7) * 512>(sel_it);                                               \
+    }                                                                                                     \
+    if (FIRST) mma_f16_first(S[U], a0, a1, a2, a3, WQ.x, WQ.y);                                           \
+    else mma_f16(S[U], a0, a1, a2, a3, WQ.x, WQ.y);                                                       \
+    if (SAL) {                                                                                            \
+      if (FIRST) {                                                                                        \
+        mma_f16_first(C[U][0], a0, a1, a2, a3, F.x, F.y);                                                 \
+        mma_f16_first(C[U][1], a0, a1, a2, a3, F.z, F.w);                                                 \
+      } else {                                                                                            \
+        mma_f16(C[U][0], a0, a1, a2, a3, F.x, F.y);                                                       \
+        mma_f16(C[U][1], a0, a1, a2, a3, F.z, F.w);                                                       \
+      }                                                                                                   \
+    }                                                                                                     \
+  }
+#define INQ_KSUB(U)                                                                                       \
+  {                                                                                                       \
+    const uint4 kx = lds128<1024 * (U)>(stage + lane16), ky = lds128<1024 * (U) + 512>(stage + lane16);   \
+    uint2 wa = lds64<0>(ww_it), wb_;                                                                      \
+    uint4 fa = make_uint4(0u, 0u, 0u, 0u), fb = fa;                                                       \
+    if (SAL) fa = lds128<0>(sel_it);                                                                      \
+    INQ_KSTEP(U, 0, kx.x, ky.x, true, wa, fa, wb_, fb)                                                    \
+    INQ_KSTEP(U, 1, kx.x >> 8, ky.x >> 8, false, wb_, fb, wa, fa)                                         \
+    INQ_KSTEP(U, 2, kx.y, ky.y, false, wa, fa, wb_, fb)                                                   \
+    INQ_KSTEP(U, 3, kx.y >> 8, ky.y >> 8, false, wb_, fb, wa, fa)                                         \
+    INQ_KSTEP(U, 4, kx.z, ky.z, false, wa, fa, wb_, fb)                                                   \
+    INQ_KSTEP(U, 5, kx.z >> 8, ky.z >> 8, false, wb_, fb, wa, fa)                                         \
+    INQ_KSTEP(U, 6, kx.w, ky.w, false, wa, fa, wb_, fb)                                                   \
+    INQ_KSTEP(U, 7, kx.w >> 8, ky.w >> 8, false, wb_, fb, wa, fa)                                         \
+  }
+        INQ_KSUB(0)
+        if (kSub > 1) INQ_KSUB(1)
+#undef INQ_KSUB
+#undef INQ_KSTEP
+        if (SAL) {
+#pragma unroll
+          for (int u = 0; u < kSub; ++u)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) S2[u][k] = 0.f;
+          for (int gsel = 0; gsel < groups; ++gsel) {
+            if (gsel) {
+              // further groups of 16 salient channels (salient fractions above 1/8)
+              const uint4 k0 = lds128<0>(stage + lane16), k1 = lds128<512>(stage + lane16);
+              const uint4 k2 = lds128<(kSub > 1 ? 1024 : 0)>(stage + lane16), k3 = lds128<(kSub > 1 ? 1536 : 512)>(stage + lane16);
+              const unsigned kw[4][4] = {{k0.x, k0.y, k0.z, k0.w}, {k1.x, k1.y, k1.z, k1.w},
+                                         {k2.x, k2.y, k2.z, k2.w}, {k3.x, k3.y, k3.z, k3.w}};
+#pragma unroll
+              for (int u = 0; u < kSub; ++u)
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) C[u][n][k] = 0.f;
+              const uint4* selg = (const uint4*)wsel + gsel * 256 + lane;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                unsigned x0 = kw[0][i], y0 = kw[1][i], x1 = kw[2][i], y1 = kw[3][i];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                  const uint4 f = selg[(2 * i + hh) * 32];
+                  const unsigned a0 = x0 & 0x000F000Fu, a1 = y0 & 0x000F000Fu, a2 = x0 & 0x00F000F0u, a3 = y0 & 0x00F000F0u;
+                  const unsigned b0 = x1 & 0x000F000Fu, b1 = y1 & 0x000F000Fu, b2 = x1 & 0x00F000F0u, b3 = y1 & 0x00F000F0u;
+                  mma_f16(C[0][0], a0, a1, a2, a3, f.x, f.y);
+                  mma_f16(C[1][0], b0, b1, b2, b3, f.x, f.y);
+                  mma_f16(C[0][1], a0, a1, a2, a3, f.z, f.w);
+                  mma_f16(C[1][1], b0, b1, b2, b3, f.z, f.w);
+                  x0 >>= 8; y0 >>= 8; x1 >>= 8; y1 >>= 8;
+                }
+              }
+            }
+            // value = fl32((code' - 128) * scale) rounded to the model dtype, as the reference's
+            // dequantised tensor holds it
+            const float2 sc0 = *(const float2*)(wssc + gsel * 16 + 2 * j);
+            const float2 sc1 = *(const float2*)(wssc + gsel * 16 + 8 + 2 * j);
+            const uint2 qb = *(const uint2*)(wqsal + (gsel * 32 + lane) * 8);
+#pragma unroll
+            for (int u = 0; u < kSub; ++u) {
+              const unsigned a0 = pack_qt2<QT>(fmaf(C[u][0][0], 8192.f, -128.f) * sc0.x, fmaf(C[u][0][1], 8192.f, -128.f) * sc0.y);
+              const unsigned a1 = pack_qt2<QT>(fmaf(C[u][0][2], 8192.f, -128.f) * sc0.x, fmaf(C[u][0][3], 8192.f, -128.f) * sc0.y);
+              const unsigned a2 = pack_qt2<QT>(fmaf(C[u][1][0], 8192.f, -128.f) * sc1.x, fmaf(C[u][1][1], 8192.f, -128.f) * sc1.y);
+              const unsigned a3 = pack_qt2<QT>(fmaf(C[u][1][2], 8192.f, -128.f) * sc1.x, fmaf(C[u][1][3], 8192.f, -128.f) * sc1.y);
+              mma_qt<QT>(S2[u], a0, a1, a2, a3, qb.x, qb.y);
+            }
+          }
+        }
+      }
+      // s2[u][k]: sub-slice u; k = 0,1 -> token r (+16u), heads 2j, 2j+1; k = 2,3 -> token r+8 (+16u)
+      float s2[2][4];
+#pragma unroll
+      for (int u = 0; u < kSub; ++u) {
+        s2[u][0] = fmaf(S[u][0], alpha[0], beta[0]);
+        s2[u][1] = fmaf(S[u][1], alpha[1], beta[1]);
+        s2[u][2] = fmaf(S[u][2], alpha[0], beta[0]);
+        s2[u][3] = fmaf(S[u][3], alpha[1], beta[1]);
+        if (SAL) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) s2[u][k] = fmaf(S2[u][k], P.scale_log2e, s2[u][k]);
+        }
+      }
+      {
+        const int tok0 = cur_slice * kSliceTokens;
+        const long long g0 = (long long)cur_block * T + tok0;
+        if (tok0 + kSliceTokens > T || g0 < first_visible) {
+#pragma unroll
+          for (int u = 0; u < kSub; ++u) {
+            const int t_lo = tok0 + 16 * u + r, t_hi = t_lo + 8;
+            if (!(t_lo < T && g0 + 16 * u + r >= first_visible)) s2[u][0] = s2[u][1] = -INFINITY;
+            if (!(t_hi < T && g0 + 16 * u + r + 8 >= first_visible)) s2[u][2] = s2[u][3] = -INFINITY;
+          }
+        }
+      }
+      // ---- online softmax (base 2) over the 32 tokens
+      float mx0 = fmaxf(s2[0][0], s2[0][2]), mx1 = fmaxf(s2[0][1], s2[0][3]);
+      if (kSub > 1) {
+        mx0 = fmaxf(mx0, fmaxf(s2[kSub - 1][0], s2[kSub - 1][2]));
+        mx1 = fmaxf(mx1, fmaxf(s2[kSub - 1][1], s2[kSub - 1][3]));
+      }
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+      }
+      // the reference maximum is raised only when a score exceeds it by more than the slack, so
+      // the accumulators are rescaled rarely; probabilities stay below 2^slack
+      if (__any_sync(0xffffffffu, mx0 > m_run[0] + kRescaleSlack || mx1 > m_run[1] + kRescaleSlack)) {
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
+        l_run[0] *= a0;
+        l_run[1] *= a1;
+        oacc[0][0] *= a0; oacc[1][0] *= a0;
+        oacc[0][1] *= a1; oacc[1][1] *= a1;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+          acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
+        }
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+      }
+      float pr[2][4];
+#pragma unroll
+      for (int u = 0; u < kSub; ++u) {
+        pr[u][0] = fast_exp2(s2[u][0] - m_run[0]);
+        pr[u][1] = fast_exp2(s2[u][1] - m_run[1]);
+        pr[u][2] = fast_exp2(s2[u][2] - m_run[0]);
+        pr[u][3] = fast_exp2(s2[u][3] - m_run[1]);
+        l_run[0] += pr[u][0] + pr[u][2];
+        l_run[1] += pr[u][1] + pr[u][3];
+      }
+      // ---- values: probabilities times the per-token group scale, codes as fp16 subnormals
+#define INQ_PV(U)                                                                                          \
+  {                                                                                                        \
+    const unsigned sp = stage + kStageK + kStageV + 4 * r;                                                 \
+    const float2 vs_lo = half2_bits_to_float2(lds32<64 * (U)>(sp)), vs_hi = half2_bits_to_float2(lds32<64 * (U) + 32>(sp)); \
+    const float2 vo_lo = half2_bits_to_float2(lds32<kStageP / 2 + 64 * (U)>(sp)), vo_hi = half2_bits_to_float2(lds32<kStageP / 2 + 64 * (U) + 32>(sp)); \
+    oacc[0][0] += pr[U][0] * vo_lo.x + pr[U][2] * vo_hi.x;                                                 \
+    oacc[0][1] += pr[U][1] * vo_lo.x + pr[U][3] * vo_hi.x;                                                 \
+    oacc[1][0] += pr[U][0] * vo_lo.y + pr[U][2] * vo_hi.y;                                                 \
+    oacc[1][1] += pr[U][1] * vo_lo.y + pr[U][3] * vo_hi.y;                                                 \
+    const unsigned va = stage + v_base0, vb1 = stage + v_base1;                                            \
+    const unsigned wA0 = lds32<kStageK + 512 * (U)>(va), wB0 = lds32<kStageK + 512 * (U) + 32>(va);        \
+    const unsigned wC0 = lds32<kStageK + 512 * (U) + 256>(va), wD0 = lds32<kStageK + 512 * (U) + 288>(va); \
+    const unsigned wA1 = lds32<kStageK + 512 * (U)>(vb1), wB1 = lds32<kStageK + 512 * (U) + 32>(vb1);      \
+    const unsigned wC1 = lds32<kStageK + 512 * (U) + 256>(vb1), wD1 = lds32<kStageK + 512 * (U) + 288>(vb1); \
+    _Pragma("unroll") for (int gr = 0; gr < 2; ++gr) {                                                     \
+      const float sl = gr ? vs_lo.y : vs_lo.x, sh = gr ? vs_hi.y : vs_hi.x;                                \
+      const unsigned b0 = movmatrix_trans(pack_half2(pr[U][0] * sl, pr[U][1] * sl));                       \
+      const unsigned b1 = movmatrix_trans(pack_half2(pr[U][2] * sh, pr[U][3] * sh));                       \
+      const unsigned M0 = __byte_perm(gr ? wA1 : wA0, gr ? wB1 : wB0, vsel);                               \
+      const unsigned M1 = __byte_perm(gr ? wC1 : wC0, gr ? wD1 : wD0, vsel);                               \
+      const unsigned N0 = M0 >> 10, N1 = M1 >> 10;                                                         \
+      mma_f16(acc[gr * 4 + 0], M0 & 0x00030003u, M0 & 0x000C000Cu, M1 & 0x00030003u, M1 & 0x000C000Cu, b0, b1); \
+      mma_f16(acc[gr * 4 + 1], M0 & 0x00300030u, M0 & 0x00C000C0u, M1 & 0x00300030u, M1 & 0x00C000C0u, b0, b1); \
+      mma_f16(acc[gr * 4 + 2], M0 & 0x03000300u, N0 & 0x00030003u, M1 & 0x03000300u, N1 & 0x00030003u, b0, b1); \
+      mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1); \
+    }                                                                                                      \
+  }
+      INQ_PV(0)
+      if (kSub > 1) INQ_PV(1)
+#undef INQ_PV
+      if (++cur_slice == spb) {
+        cur_slice = 0;
+        ++cur_block;
+        need_weights = true;
+      }
+    }
+    cp_async_wait<0>();
+    // a code at bit offset o of its 16-bit lane was multiplied as code * 2^(o-24)
+    const float fx[4] = {16777216.f, 1048576.f, 65536.f, 4194304.f};   // offsets 0, 4, 8, 2
+    const float fy[4] = {4194304.f, 262144.f, 16777216.f, 1048576.f};  // offsets 2, 6, 0, 4
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      acc[mt][0] *= fx[mt & 3];
+      acc[mt][1] *= fx[mt & 3];
+      acc[mt][2] *= fy[mt & 3];
+      acc[mt][3] *= fy[mt & 3];
+    }
+  } else {
+    dense_part();
   }
 
   // ---------------------------------------------------------------- warp -> CTA -> global partial
