@@ -1115,3 +1115,46 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Serving stacks commonly hand (almost) all device memory to their own page pool at start-up
+// and forbid any later cudaMalloc from inside an attention backend: it may fail outright, it
+// may fragment the pool, and it is illegal inside a CUDA-graph capture.  A foreign-language
+// host (Go, Java, Rust over FFI) that owns device memory through its own allocator is in the
+// same position.  For those callers the split-KV partial records and arrival counters live in
+// this fixed array instead of caller-provided scratch.  Every process that loads the library
+// holds it on every device it uses until exit.
+namespace inq {
+constexpr int kStaticRecords = 1024;   // (resident CTAs + pairs) of one launch must fit
+constexpr int kStaticPairs = 256;      // (sequence, KV head, head tile) pairs of one launch
+constexpr size_t kStaticCounterBytes = kStaticPairs * sizeof(int);
+constexpr size_t kStaticBytes = kStaticCounterBytes + (size_t)kStaticRecords * kRecordFloats * sizeof(float);
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticBytes];
+}  // namespace inq
+
+extern "C" int inq_decode_attention_noalloc(const inq_decode_args_t* a, inq_stream_t stream_) {
+  if (!a) return INQ_ERR_ARGUMENT;
+  const long long n_pairs = (long long)a->n_seq * a->kv_heads * ((a->q_per_kv + 7) / 8);
+  if (a->n_seq < 1 || a->kv_heads < 1 || a->q_per_kv < 1) return INQ_ERR_ARGUMENT;
+  if (n_pairs > kStaticPairs) return INQ_ERR_CAPACITY;
+  // The array's name is a host-side stand-in, not a device address: resolve it once per device,
+  // with that device current, and hand the resolved pointer to the kernel.
+  static void* resolved[64] = {};
+  int device = -1;
+  INQ_CUDA_CHECK(cudaGetDevice(&device));
+  if (device < 0 || device >= 64) return INQ_ERR_UNSUPPORTED;
+  if (!resolved[device]) {
+    void* ptr = nullptr;
+    INQ_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
+    // counters must start at zero (the kernel leaves them zero afterwards)
+    INQ_CUDA_CHECK(cudaMemsetAsync(ptr, 0, kStaticCounterBytes, (cudaStream_t)stream_));
+    resolved[device] = ptr;
+  }
+  inq_decode_args_t local = *a;
+  local.counters = (int32_t*)resolved[device];
+  local.partials = (float*)((unsigned char*)resolved[device] + kStaticCounterBytes);
+  local.partials_floats = (int64_t)kStaticRecords * kRecordFloats;
+  return inq_decode_attention(&local, stream_);   // INQ_ERR_CAPACITY when the launch needs more records
+}

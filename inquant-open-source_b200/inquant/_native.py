@@ -102,7 +102,7 @@ def library() -> ctypes.CDLL:
 EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
     "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
-    "inq_decode_attention", "inq_decode_units", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
+    "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
 )
 
 
@@ -116,6 +116,7 @@ SIGNATURES = {
     "inq_v_dequantize": [_P, _P, _P, _L, _I, _I, _I, _I, _P, _I, _P],
     "inq_build_roles": [_P, _P, _I, _L, _I, _I, _P, _I, _P],
     "inq_decode_attention": [_P, _P],
+    "inq_decode_attention_noalloc": [_P, _P],
     "inq_append_token": [_P, _P],
     "inq_append_token_batch": [_P, _I, _P, _P],
 }
