@@ -44,6 +44,21 @@ class SequenceState:
                    layer.tail_count)
 
 
+@dataclass
+class PagedSequenceState:
+    """One (request, layer) in the paged layout: physical pages of a pool reached through a
+    page table, plus the ``[2,H,B+4,128]`` dense tensor holding the exact sink (tokens 0..3) and
+    the unsealed tail (from token 4), as the reference's serving backend keeps them."""
+
+    pool: torch.Tensor               # [num_pages, page_bytes] uint8
+    page_table: torch.Tensor         # int32 physical page of logical page i
+    num_pages: int
+    dense: torch.Tensor              # [2, H, B + 4, 128]
+    tail_count: int
+    sink_count: int
+    layout: object                   # inquant_vllm.layout.PageLayout
+
+
 def _struct_array_to_device(array, device) -> torch.Tensor:
     raw = bytes(array)
     return torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
@@ -56,10 +71,19 @@ class DecodeBatch:
                  scale: float | None = None):
         if not sequences:
             raise ValueError("at least one sequence is required")
-        first = sequences[0].decode_state
+        self.paged = isinstance(sequences[0], PagedSequenceState)
+        if any(isinstance(s, PagedSequenceState) != self.paged for s in sequences):
+            raise ValueError("a batch holds either table-layout or paged sequences")
         self.sequences = sequences
-        self.device = sequences[0].tail_key_buffer.device
-        self.kv_heads = sequences[0].tail_key_buffer.shape[1]
+        if self.paged:
+            self.layout = sequences[0].layout
+            self.device = sequences[0].pool.device
+            self.kv_heads = self.layout.heads
+        else:
+            with_blocks = [s.decode_state for s in sequences if s.decode_state.key_blocks]
+            first = with_blocks[0] if with_blocks else sequences[0].decode_state
+            self.device = sequences[0].tail_key_buffer.device
+            self.kv_heads = sequences[0].tail_key_buffer.shape[1]
         if q_heads % self.kv_heads:
             raise ValueError("query_heads must be divisible by the KV head count")
         if dtype not in (torch.float16, torch.bfloat16):
@@ -67,8 +91,8 @@ class DecodeBatch:
         self.q_heads, self.dtype = q_heads, dtype
         self.q_per_kv = q_heads // self.kv_heads
         self.scale = 128 ** -0.5 if scale is None else float(scale)
-        self.block_tokens = first._packed_tokens
-        self.n_pad = first._salient
+        self.block_tokens = self.layout.block_size if self.paged else first._packed_tokens
+        self.n_pad = 16 if self.paged else first._salient
         n = len(sequences)
         # one staging tensor per step: [query heads | new key heads | new value heads] x 128
         self.inputs = torch.zeros((n, q_heads + 2 * self.kv_heads, 128), dtype=dtype, device=self.device)
@@ -81,7 +105,7 @@ class DecodeBatch:
         tiles = (self.q_per_kv + 7) // 8
         n_pairs = n * self.kv_heads * tiles
         # prefix sums of the work units of every (sequence, KV head, head tile) pair
-        units = [int(N.library().inq_decode_units(len(s.decode_state.key_blocks), self.block_tokens))
+        units = [int(N.library().inq_decode_units(self._blocks_of(s), self.block_tokens))
                  for s in sequences for _ in range(self.kv_heads * tiles)]
         starts = torch.tensor([0] + units, dtype=torch.int64).cumsum(0)
         self.total_units = int(starts[-1])
@@ -92,14 +116,47 @@ class DecodeBatch:
         self._initial_counters = self.tail_counters.clone()
         self._prepare_launch_arguments()
 
+    def _blocks_of(self, s) -> int:
+        return s.num_pages if self.paged else len(s.decode_state.key_blocks)
+
+    def _tail_capacity_of(self, s) -> int:
+        return self.layout.block_size if self.paged else s.tail_key_buffer.shape[2]
+
+    def _build_paged_descriptors(self) -> None:
+        from inquant_vllm.kernels import fill_paged_sequence
+        n = len(self.sequences)
+        es = self.queries.element_size()
+        seqs = (N.DecodeSeq * n)()
+        apps = (N.AppendArgs * n)()
+        for i, s in enumerate(self.sequences):
+            if s.layout != self.layout or s.dense.dtype != self.dtype or not s.dense.is_contiguous():
+                raise ValueError("all paged sequences must share the layout and hold contiguous dense tensors of the batch dtype")
+            table = s.page_table if s.page_table.dtype == torch.int32 else s.page_table.to(torch.int32)
+            s.page_table = table
+            fill_paged_sequence(seqs[i], self.queries[i], self.outputs[i], s.pool, table, s.dense, s.num_pages,
+                                s.tail_count, s.sink_count, self.layout)
+            seqs[i].tail_tokens_device = self.tail_counters[i:].data_ptr()
+            a = apps[i]
+            a.key, a.value, a.src_stride_h = self.new_keys[i].data_ptr(), self.new_values[i].data_ptr(), 128 * es
+            a.tail_key, a.tail_value = seqs[i].tail_key, seqs[i].tail_value
+            a.tail_stride_h, a.tail_stride_t = s.dense.stride(1) * es, s.dense.stride(2) * es
+            a.tail_position, a.tail_capacity = s.tail_count, self.layout.block_size
+            a.tail_counter = self.tail_counters[i:].data_ptr()
+            a.sink_position = -1
+            a.heads, a.row_bytes = self.kv_heads, 128 * es
+        self._seq_records = _struct_array_to_device(seqs, self.device)
+        self._append_records = _struct_array_to_device(apps, self.device)
+
     def _build_descriptors(self) -> None:
+        if self.paged:
+            return self._build_paged_descriptors()
         n = len(self.sequences)
         es = self.queries.element_size()
         seqs = (N.DecodeSeq * n)()
         apps = (N.AppendArgs * n)()
         for i, s in enumerate(self.sequences):
             st = s.decode_state
-            if st._packed_tokens != self.block_tokens or st._salient != self.n_pad:
+            if st.key_blocks and (st._packed_tokens != self.block_tokens or st._salient != self.n_pad):
                 raise ValueError("all sequences must share block length and salient-channel count")
             d = seqs[i]
             d.query = self.queries[i].data_ptr()
@@ -144,13 +201,16 @@ class DecodeBatch:
 
     def _prepare_launch_arguments(self) -> None:
         n = len(self.sequences)
-        self._capacity = min(s.tail_key_buffer.shape[2] - s.tail_count for s in self.sequences)
+        self._capacity = min(self._tail_capacity_of(s) - s.tail_count for s in self.sequences)
         self._appended = 0
         args = N.DecodeArgs()
         args.n_seq, args.seqs_device = n, self._seq_records.data_ptr()
         args.kv_heads, args.q_per_kv = self.kv_heads, self.q_per_kv
         args.block_tokens, args.n_pad = self.block_tokens, self.n_pad
-        args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[self.dtype], self.scale
+        args.layout, args.dtype, args.scale = int(self.paged), N.DTYPE_CODE[self.dtype], self.scale
+        if self.paged:
+            from inquant_vllm.kernels import page_offsets_array
+            args.page_bytes, args.page_offsets = self.layout.page_bytes, page_offsets_array(self.layout)
         args.pair_starts, args.total_units = self.pair_starts.data_ptr(), self.total_units
         args.partials, args.partials_floats = self.partials.data_ptr(), self.partials.numel()
         args.counters = self.counters.data_ptr()
@@ -228,10 +288,10 @@ class DecodeBatch:
         es = self.queries.element_size()
         packed = meta = dense = 0
         for s in self.sequences:
-            nb = len(s.decode_state.key_blocks)
+            nb = self._blocks_of(s)
             packed += h * nb * t * (64 + 32 + 8)
-            meta += h * nb * (512 + self.n_pad * 2 + self.n_pad * 4)
-            sink = 0 if s.sink_key is None else s.sink_key.shape[2]
+            meta += h * nb * (832 if self.paged else 512 + self.n_pad * 2 + self.n_pad * 4)
+            sink = s.sink_count if self.paged else (0 if s.sink_key is None else s.sink_key.shape[2])
             dense += (sink + s.tail_count + self._appended) * h * 128 * es * 2
         qo = len(self.sequences) * self.q_heads * 128 * es * 2
         return {"packed": packed, "metadata": meta, "dense": dense, "query_output": qo,
