@@ -270,12 +270,77 @@ def run_cuda(args):
         "clocks": clocks.summary(),
         "device_status": status,
     }
+    if args.split_context:
+        del batch, cache
+        torch.cuda.empty_cache()
+        line["split_kv"] = run_split_kv(args, torch, dist, device, world, rank)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sample_layers=1)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_split_kv(args, torch, dist, device, world, rank):
+    """Config 4: one 131072-token request, sealed blocks partitioned by sequence over the ranks,
+    partial (acc, m, l) records exchanged by ONE all-gather per step and merged locally."""
+    import workloads
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.batched import SequenceState
+    from inquant.split_kv import SplitKVDecode, shard_blocks
+    context = args.split_context
+    total_blocks = (context - SINK - RESIDUAL) // BLOCK
+    start, end = shard_blocks(total_blocks, world, rank)
+    first, last = rank == 0, rank == world - 1
+    tail = context - SINK - total_blocks * BLOCK
+    tokens = (SINK if first else 0) + (end - start) * BLOCK + (tail if last else 0)
+    cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=BLOCK,
+                                     residual_length=RESIDUAL if last else 0, sink_tokens=SINK if first else 0,
+                                     value_bits=2, value_group_size=64, validate_positions=False))
+    for layer in range(LAYERS):
+        k, v = workloads.make_kv_torch(50000 + 1000 * rank + layer, KV_HEADS, tokens, device)
+        cache.update(k, v, layer)
+        del k, v
+    seqs = [SequenceState.from_cache_layer(cache, i) for i in range(LAYERS)]
+    assert all(len(s.decode_state.key_blocks) == end - start for s in seqs)
+    split = SplitKVDecode(seqs, Q_HEADS, owns_tail=last)
+    gen = torch.Generator(device=device).manual_seed(99)   # the same queries on every rank
+    steps = min(args.steps, 40)
+    inputs = torch.randn((args.warmup + steps, LAYERS, Q_HEADS + 2 * KV_HEADS, DIM), device=device, generator=gen).bfloat16()
+    for i in range(args.warmup):
+        split.inputs.copy_(inputs[i])
+        split.step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        split.inputs.copy_(inputs[args.warmup + i])
+        split.step()
+    t1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    local_bytes = split.batch.algorithmic_bytes()["total"]
+    stats = torch.tensor([ms, float(local_bytes)], device=device, dtype=torch.float64)
+    if world > 1:
+        worst = stats.clone()
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        total = stats.clone()
+        dist.all_reduce(total, op=dist.ReduceOp.SUM)
+        ms, total_bytes = float(worst[0]), float(total[1])
+    else:
+        total_bytes = float(local_bytes)
+    peak, _ = measured_peak_gbs()
+    return {"context": context, "blocks_per_rank": end - start, "us_per_step": round(ms * 1e3, 2),
+            "aggregate_gbs": round(total_bytes / (ms * 1e-3) / 1e9, 1),
+            "per_gpu_hbm_frac": round(total_bytes / world / (ms * 1e-3) / 1e9 / peak, 4),
+            "exchange": f"one all-gather of {LAYERS * Q_HEADS * 130 * 4} B per rank per step, then a local log-sum-exp merge",
+            "steps": steps}
 
 
 # DRAM bytes (read + write) of one decode_kernel launch of this workload from an ncu capture;
@@ -376,6 +441,8 @@ def main():
     parser.add_argument("--impl", default="cuda", choices=("cuda", "reference"))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-graph", action="store_true", help="launch the two kernels eagerly instead of replaying a CUDA graph")
+    parser.add_argument("--split-context", type=int, default=131072,
+                        help="also time config 4: one request of this many tokens split by sequence over the ranks (0 = skip)")
     parser.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for profiler captures (default: the full 28)")
     parser.add_argument("--skip-e2e", action="store_true", help="profiler captures: skip the host-buffer leg")
     args = parser.parse_args()

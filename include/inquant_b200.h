@@ -165,6 +165,10 @@ typedef struct {
   int64_t tail_key_stride_h, tail_key_stride_t, tail_value_stride_h, tail_value_stride_t;
   int32_t n_blocks, sink_tokens, tail_tokens, first_visible, tail_skip;
   const int32_t* tail_tokens_device; /* optional: overrides tail_tokens, read on the device */
+  float* partial_output;  /* optional [q_heads][130] fp32: when set, `output` is not written; the
+                           * un-normalised record (acc[128], m in base-2 units, l) of each query
+                           * head is stored instead -- the reference's partial format
+                           * (triton_attention.py:162-165) -- for a cross-GPU merge */
 } inq_decode_seq_t;
 
 typedef struct {
@@ -203,6 +207,12 @@ int inq_decode_attention(const inq_decode_args_t* args /* host */, inq_stream_t 
  * All calls on a device share the array: launches that may overlap on the GPU (different
  * streams) race on it; calls on one stream do not. */
 int inq_decode_attention_noalloc(const inq_decode_args_t* args /* host */, inq_stream_t stream);
+/* Log-sum-exp merge of partial records from n_parts ranks (split-KV of one long sequence over
+ * GPUs): records [n_parts][n_rows][130] fp32 as written through `partial_output`, out
+ * [n_rows][128] fp16/bf16.  Replaces: triton_attention.py:168-181 `_reduce_partials` applied
+ * across ranks after an all-gather. */
+int inq_merge_partials(const float* records, int32_t n_parts, int64_t n_rows, void* out, int32_t out_dtype,
+                       inq_stream_t stream);
 /* Work units (32-token slices, at least 1) of one pair whose sequence holds n_blocks blocks. */
 int64_t inq_decode_units(int32_t n_blocks, int32_t block_tokens);
 /* Scratch floats that suffice for a launch with n_pairs pairs and total_units work units on

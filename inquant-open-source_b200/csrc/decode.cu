@@ -65,6 +65,7 @@ struct SeqDesc {
   long long tail_k_sh, tail_k_st, tail_v_sh, tail_v_st;
   int n_blocks, sink_tokens, tail_tokens, first_visible, tail_skip;
   const int* tail_tokens_dev;
+  float* partial_out;            // optional: un-normalised (acc[128], m, l) per query head instead of `out`
 };
 static_assert(sizeof(SeqDesc) == sizeof(inq_decode_seq_t), "SeqDesc must mirror inq_decode_seq_t");
 
@@ -951,6 +952,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     const float* base = P.partials + ((long long)first_cta + pair) * kRecordFloats;
     const int np = n_cta_pair;
     float* norm = mw + 8 * np;
+    float* mtop = norm + 8;
+    float* const partial = SEQ(partial_out);
     if (threadIdx.x < 8) norm[threadIdx.x] = 0.f;
     for (int g = warp; g < g_valid; g += kWarps) {
       float top = kNegBig;
@@ -966,7 +969,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       }
 #pragma unroll
       for (int off = 16; off; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
-      if (lane == 0) norm[g] = l;
+      if (lane == 0) {
+        norm[g] = l;
+        mtop[g] = top;
+      }
     }
     __syncthreads();
     const int c = threadIdx.x;
@@ -984,7 +990,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         o3 = fmaf(v3, mw[g * np + p + 3], o3);
       }
       for (; p < np; ++p) o0 = fmaf(__ldcg(rec + (long long)p * kRecordFloats), mw[g * np + p], o0);
-      out[(q_head0 + g) * 128 + c] = from_float<QT>(((o0 + o1) + (o2 + o3)) / norm[g]);
+      const float o = (o0 + o1) + (o2 + o3);
+      if (partial) {
+        // this rank's share of a sequence split across GPUs: keep the record un-normalised
+        float* rec_out = partial + (q_head0 + g) * 130;
+        rec_out[c] = o;
+        if (c == 0) {
+          rec_out[128] = mtop[g];
+          rec_out[129] = norm[g];
+        }
+      } else {
+        out[(q_head0 + g) * 128 + c] = from_float<QT>(o / norm[g]);
+      }
     }
   }
   __syncthreads();   // shared scratch is reused by the next pair of this CTA
@@ -1157,4 +1174,39 @@ extern "C" int inq_decode_attention_noalloc(const inq_decode_args_t* a, inq_stre
   local.partials = (float*)((unsigned char*)resolved[device] + kStaticCounterBytes);
   local.partials_floats = (int64_t)kStaticRecords * kRecordFloats;
   return inq_decode_attention(&local, stream_);   // INQ_ERR_CAPACITY when the launch needs more records
+}
+
+
+// ------------------------------------------------------------------------------------------
+// Log-sum-exp merge of the un-normalised partial records of several ranks (split-KV across
+// GPUs): records [n_parts][n_rows][130] fp32 -> out [n_rows][128].  m is in base-2 units.
+namespace inq {
+template <typename QT>
+__global__ void __launch_bounds__(128) merge_partials_kernel(const float* records, int n_parts, long long n_rows, QT* out) {
+  const long long row = blockIdx.x;
+  const int c = threadIdx.x;
+  float top = kNegBig;
+  for (int p = 0; p < n_parts; ++p) top = fmaxf(top, records[((long long)p * n_rows + row) * 130 + 128]);
+  float o = 0.f, l = 0.f;
+  for (int p = 0; p < n_parts; ++p) {
+    const float* rec = records + ((long long)p * n_rows + row) * 130;
+    const float w = fast_exp2(rec[128] - top);
+    o = fmaf(rec[c], w, o);
+    l = fmaf(rec[129], w, l);
+  }
+  out[row * 128 + c] = from_float<QT>(o / l);
+}
+}  // namespace inq
+
+extern "C" int inq_merge_partials(const float* records, int32_t n_parts, int64_t n_rows, void* out, int32_t out_dtype,
+                                  inq_stream_t stream_) {
+  if (!records || !out || n_parts < 1 || n_rows < 1 || n_rows >= (1ll << 31)) return INQ_ERR_ARGUMENT;
+  if (out_dtype != INQ_F16 && out_dtype != INQ_BF16) return INQ_ERR_UNSUPPORTED;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (out_dtype == INQ_F16)
+    inq::merge_partials_kernel<__half><<<(unsigned)n_rows, 128, 0, stream>>>(records, n_parts, n_rows, (__half*)out);
+  else
+    inq::merge_partials_kernel<__nv_bfloat16><<<(unsigned)n_rows, 128, 0, stream>>>(records, n_parts, n_rows, (__nv_bfloat16*)out);
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
 }

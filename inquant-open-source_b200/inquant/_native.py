@@ -50,7 +50,8 @@ class DecodeSeq(ctypes.Structure):
                 ("tail_key_stride_h", c_int64), ("tail_key_stride_t", c_int64),
                 ("tail_value_stride_h", c_int64), ("tail_value_stride_t", c_int64),
                 ("n_blocks", c_int32), ("sink_tokens", c_int32), ("tail_tokens", c_int32),
-                ("first_visible", c_int32), ("tail_skip", c_int32), ("tail_tokens_device", c_void_p)]
+                ("first_visible", c_int32), ("tail_skip", c_int32), ("tail_tokens_device", c_void_p),
+                ("partial_output", c_void_p)]
 
 
 class DecodeArgs(ctypes.Structure):
@@ -102,7 +103,7 @@ def library() -> ctypes.CDLL:
 EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
     "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
-    "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
+    "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
 )
 
 
@@ -117,6 +118,7 @@ SIGNATURES = {
     "inq_build_roles": [_P, _P, _I, _L, _I, _I, _P, _I, _P],
     "inq_decode_attention": [_P, _P],
     "inq_decode_attention_noalloc": [_P, _P],
+    "inq_merge_partials": [_P, _I, _L, _P, _I, _P],
     "inq_append_token": [_P, _P],
     "inq_append_token_batch": [_P, _I, _P, _P],
 }

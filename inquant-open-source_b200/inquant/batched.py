@@ -68,7 +68,7 @@ class DecodeBatch:
     """Device-resident descriptors, queries, outputs and scratch for a fixed set of sequences."""
 
     def __init__(self, sequences: list[SequenceState], q_heads: int, dtype: torch.dtype = torch.bfloat16,
-                 scale: float | None = None):
+                 scale: float | None = None, partials_only: bool = False):
         if not sequences:
             raise ValueError("at least one sequence is required")
         self.paged = isinstance(sequences[0], PagedSequenceState)
@@ -100,6 +100,9 @@ class DecodeBatch:
         self.new_keys = self.inputs[:, q_heads:q_heads + self.kv_heads]
         self.new_values = self.inputs[:, q_heads + self.kv_heads:]
         self.outputs = torch.empty((n, q_heads, 128), dtype=dtype, device=self.device)
+        # split-KV across GPUs: keep un-normalised (acc[128], m, l) records instead of outputs
+        self.partial_records = (torch.zeros((n, q_heads, 130), dtype=torch.float32, device=self.device)
+                                if partials_only else None)
         self.tail_counters = torch.tensor([s.tail_count for s in sequences], dtype=torch.int32).to(self.device)
         self._build_descriptors()
         tiles = (self.q_per_kv + 7) // 8
@@ -144,6 +147,12 @@ class DecodeBatch:
             a.tail_counter = self.tail_counters[i:].data_ptr()
             a.sink_position = -1
             a.heads, a.row_bytes = self.kv_heads, 128 * es
+        self._finish_descriptors(seqs, apps)
+
+    def _finish_descriptors(self, seqs, apps) -> None:
+        if self.partial_records is not None:
+            for i in range(len(self.sequences)):
+                seqs[i].partial_output = self.partial_records[i].data_ptr()
         self._seq_records = _struct_array_to_device(seqs, self.device)
         self._append_records = _struct_array_to_device(apps, self.device)
 
@@ -191,8 +200,7 @@ class DecodeBatch:
             a.tail_counter = self.tail_counters[i:].data_ptr()
             a.sink_position = -1
             a.heads, a.row_bytes = self.kv_heads, 128 * es
-        self._seq_records = _struct_array_to_device(seqs, self.device)
-        self._append_records = _struct_array_to_device(apps, self.device)
+        self._finish_descriptors(seqs, apps)
 
     @property
     def capacity_left(self) -> int:
