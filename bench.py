@@ -263,7 +263,9 @@ def run_cuda(args):
         "encode_ms_all_layers": round(encode_ms, 3),
         "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": round(achieved, 1), "peak": peak,
                      "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_source": peak_kind,
-                     "us_per_launch": round(kernel_ms * 1e3, 2), "traffic": DECODE_TRAFFIC_BYTES},
+                     "us_per_launch": round(kernel_ms * 1e3, 2),
+                     "traffic": int(kernel_bytes * DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE),
+                     "traffic_source": "ncu capture of a 10-layer case scaled by units"},
         "e2e": {"value": round(world * mean_bytes["total"] / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "us_per_step": round(e2e_ms * 1e3, 2), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,   # append + decode kernels of this library (torch's staging copy not counted)
@@ -343,8 +345,10 @@ def run_split_kv(args, torch, dist, device, world, rank):
             "steps": steps}
 
 
-# DRAM bytes (read + write) of one decode_kernel launch of this workload from an ncu capture;
-# see profiles/decode_kernel_cfg1.md.  None until a capture of the current kernel exists.
+# DRAM bytes (read + write) of one decode_kernel launch: 152.49 MB measured by ncu on the 10-layer
+# capture case (143.9 MB algorithmic), scaled to the layers of this run because traffic grows in
+# proportion to the units processed (profiles/decode_kernel_cfg1_10layers.md).
+DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 152.49 / 143.89
 DECODE_TRAFFIC_BYTES = None
 
 
