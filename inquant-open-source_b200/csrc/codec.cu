@@ -433,6 +433,331 @@ __global__ void __launch_bounds__(kMaxThreads) k4_encode_kernel(K4Params p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// 128-channel fast path (every decode-capable layout): same arithmetic as k4_encode_kernel,
+// fewer instructions per element.
+//   * |x| maximum and the finite check come from one unsigned maximum of the fp32 bit patterns
+//     (NaN and Inf sort above every finite value);
+//   * x / s uses a correctly rounded reciprocal and two fused corrections, which returns the
+//     IEEE quotient (Markstein); scales below 2^-100 keep the plain division;
+//   * the selected / available sets are two 64-bit masks in registers.
+struct Mask128 {
+  unsigned long long lo, hi;
+  __device__ __forceinline__ bool test(int i) const { return i >= 0 && i < 128 && (((i < 64 ? lo : hi) >> (i & 63)) & 1ull); }
+  __device__ __forceinline__ void clear(int i) {
+    if (i < 64) lo &= ~(1ull << i); else hi &= ~(1ull << (i - 64));
+  }
+  __device__ __forceinline__ int below(int pos) const {   // largest member < pos, or -1
+    if (pos > 64) {
+      unsigned long long m = pos >= 128 ? hi : (hi & ((1ull << (pos - 64)) - 1ull));
+      if (m) return 127 - __clzll((long long)m);
+      pos = 64;
+    }
+    unsigned long long m = pos >= 64 ? lo : (lo & ((1ull << pos) - 1ull));
+    return m ? 63 - __clzll((long long)m) : -1;
+  }
+  __device__ __forceinline__ int above(int pos) const {   // smallest member > pos, or 128
+    int start = pos + 1;
+    if (start < 64) {
+      unsigned long long m = lo & (~0ull << start);
+      if (m) return __ffsll((long long)m) - 1;
+      start = 64;
+    }
+    if (start >= 128) return 128;
+    unsigned long long m = hi & (~0ull << (start - 64));
+    return m ? 63 + __ffsll((long long)m) : 128;
+  }
+};
+
+__device__ __forceinline__ float exact_quotient(float x, float s, float r, bool plain) {
+  if (plain) return x / s;
+  const float q0 = x * r;
+  const float rem = fmaf(-q0, s, x);
+  return fmaf(rem, r, q0);
+}
+
+__device__ __forceinline__ unsigned encode_slot_fast(float x, float scale, float rcp, bool plain, int kind) {
+  const float q = rintf(exact_quotient(x, scale, rcp, plain));
+  if (kind == 0) return (unsigned)(int)(fminf(fmaxf(q, -7.f), 7.f) + 8.f);
+  const unsigned code = (unsigned)(int)(fminf(fmaxf(q, -127.f), 127.f) + 128.f);
+  return kind == 1 ? (code >> 4) : (code & 15u);
+}
+
+template <typename T>
+__device__ __forceinline__ unsigned f32_bits_of(T v) { return __float_as_uint(to_float<T>(v)); }
+
+template <typename T, bool REGULAR>   // REGULAR: tokens % 8 == 0 and sample_stride == 8
+__global__ void __launch_bounds__(128, 7) k4_encode128_kernel(K4Params p) {
+  constexpr int C = 128;
+  __shared__ float s_sal[C], s_err[C], s_mean[C], s_scale[C], s_rcp[C];
+  __shared__ unsigned s_key[C];
+  __shared__ unsigned char s_kind[C], s_from[C], s_plain[C];
+  __shared__ int s_src[64], s_don[64];
+  __shared__ unsigned s_sel[4], s_avail[4];
+  __shared__ double s_inv[kRcpTable];
+  const int tokens = p.in.tokens, count = p.count;
+  const bool want_error = p.min_error != 0;
+  const long long outer = blockIdx.x / p.in.n_inner, inner = blockIdx.x % p.in.n_inner;
+  const long long slot = p.in.slot(outer);
+  const T* row = (const T*)p.in.x + outer * p.in.s_outer + inner * p.in.s_inner;
+  const int c = threadIdx.x;
+  if (want_error)
+    for (int t = c; t < tokens; t += C) s_inv[t] = 1.0 / (double)(t + 1);
+  if (c < 4) s_sel[c] = s_avail[c] = 0u;
+  __syncthreads();
+
+  // ---- statistics: one thread per channel, sequential over tokens
+  unsigned top_bits = 0u;
+  CascadePair cascade;
+  const int samples = (tokens + p.sample_stride - 1) / p.sample_stride;
+  cascade.init(samples);
+  double mean = 0.0, m2 = 0.0, count_d = 0.0;
+  int next_sample = 0;
+  {
+    const T* column = row + c;
+    constexpr int kUnroll = 8;
+    const long long step = p.in.s_token;
+    // the next batch of tokens is requested before the current one is consumed, so the
+    // sequential (Welford) chain never waits on a freshly issued load
+    T ahead[kUnroll];
+    if (REGULAR) {
+      const T* cursor = column;
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) ahead[u] = cursor[u * step];
+      const double* inv = s_inv;
+      for (int base = 0; base < tokens; base += kUnroll) {
+        float v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) v[u] = to_float<T>(ahead[u]);
+        cursor += kUnroll * step;
+        if (base + kUnroll < tokens) {
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) ahead[u] = cursor[u * step];
+        }
+        cascade.add(v[0]);   // every eighth token is a sample
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const float x = v[u];
+          top_bits = max(top_bits, __float_as_uint(x) & 0x7fffffffu);
+          if (want_error) {
+            const double xd = (double)x;
+            const double delta = xd - mean;
+            count_d = count_d + 1.0;
+            mean = mean + divide_by_count(delta, count_d, inv[u]);
+            m2 = m2 + delta * (xd - mean);
+          }
+        }
+        inv += kUnroll;
+      }
+    } else {
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) ahead[u] = u < tokens ? column[(long long)u * p.in.s_token] : T();
+    for (int base = 0; base < tokens; base += kUnroll) {
+      float v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[u] = to_float<T>(ahead[u]);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int t = base + kUnroll + u;
+        if (t < tokens) ahead[u] = column[(long long)t * p.in.s_token];
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int t = base + u;
+        if (t < tokens) {
+          const float x = v[u];
+          top_bits = max(top_bits, __float_as_uint(x) & 0x7fffffffu);
+          if (t == next_sample) {
+            cascade.add(x);
+            next_sample += p.sample_stride;
+          }
+          if (want_error) {
+            const double xd = (double)x;
+            const double delta = xd - mean;
+            count_d = count_d + 1.0;
+            mean = mean + divide_by_count(delta, count_d, s_inv[t]);
+            m2 = m2 + delta * (xd - mean);
+          }
+        }
+      }
+    }
+    }
+  }
+  float abs_total, sum_total;
+  cascade.finish(abs_total, sum_total);
+  const float saliency = abs_total / (float)samples, sampled_mean = sum_total / (float)samples;
+  float donor_error = 0.f;
+  if (want_error) {
+    const float variance = (float)(m2 / (double)tokens);
+    const float diff = (float)mean - sampled_mean;
+    donor_error = variance + diff * diff;
+  }
+  if (top_bits >= 0x7f800000u) atomicOr(p.status, INQ_STATUS_NONFINITE);
+  const float absmax = __uint_as_float(top_bits);
+  s_sal[c] = saliency;
+  s_mean[c] = sampled_mean;
+  s_err[c] = donor_error;
+  __syncthreads();
+
+  // ---- top-`count` channels by saliency (ties: lower channel), optional least-error pool
+  bool selected = false;
+  if (count > 0) {
+    const unsigned mine = __float_as_uint(saliency);
+    int rank = 0;
+#pragma unroll 4
+    for (int o4 = 0; o4 < C / 4; ++o4) {
+      const float4 f = *(const float4*)(s_sal + 4 * o4);
+      const unsigned k0 = __float_as_uint(f.x), k1 = __float_as_uint(f.y), k2 = __float_as_uint(f.z), k3 = __float_as_uint(f.w);
+      rank += (k0 > mine) || (k0 == mine && 4 * o4 + 0 < c);
+      rank += (k1 > mine) || (k1 == mine && 4 * o4 + 1 < c);
+      rank += (k2 > mine) || (k2 == mine && 4 * o4 + 2 < c);
+      rank += (k3 > mine) || (k3 == mine && 4 * o4 + 3 < c);
+    }
+    selected = rank < count;
+    if (selected) atomicOr(&s_sel[c >> 5], 1u << (c & 31));
+    s_key[c] = selected ? 0x7f800000u : __float_as_uint(donor_error);
+    if (!want_error && !selected) atomicOr(&s_avail[c >> 5], 1u << (c & 31));
+  }
+  __syncthreads();
+  if (want_error && count > 0 && !selected) {
+    const unsigned mine = s_key[c];
+    int rank = 0;
+#pragma unroll 4
+    for (int o4 = 0; o4 < C / 4; ++o4) {
+      const uint4 k = *(const uint4*)(s_key + 4 * o4);
+      rank += (k.x < mine) || (k.x == mine && 4 * o4 + 0 < c);
+      rank += (k.y < mine) || (k.y == mine && 4 * o4 + 1 < c);
+      rank += (k.z < mine) || (k.z == mine && 4 * o4 + 2 < c);
+      rank += (k.w < mine) || (k.w == mine && 4 * o4 + 3 < c);
+    }
+    if (rank < count) atomicOr(&s_avail[c >> 5], 1u << (c & 31));
+  }
+  __syncthreads();
+  if (c == 0 && count > 0) {
+    Mask128 sel{(unsigned long long)s_sel[0] | ((unsigned long long)s_sel[1] << 32),
+                (unsigned long long)s_sel[2] | ((unsigned long long)s_sel[3] << 32)};
+    Mask128 avail{(unsigned long long)s_avail[0] | ((unsigned long long)s_avail[1] << 32),
+                  (unsigned long long)s_avail[2] | ((unsigned long long)s_avail[3] << 32)};
+    int n = 0;
+    for (unsigned long long m = sel.lo; m && n < count; m &= m - 1) s_src[n++] = __ffsll((long long)m) - 1;
+    for (unsigned long long m = sel.hi; m && n < count; m &= m - 1) s_src[n++] = 63 + __ffsll((long long)m);
+    for (int i = 0; i < count; ++i) {
+      const int source = s_src[i];
+      int low = avail.test(source - 1) ? source - 1 : -1;
+      int high = avail.test(source + 1) ? source + 1 : -1;
+      if (low < 0 && high < 0) {
+        int left = source, right = source;
+        while (sel.test(left - 1)) --left;
+        while (sel.test(right + 1)) ++right;
+        const int below = avail.below(left), above = avail.above(right);
+        const int d_below = below >= 0 ? left - below : 0x7fffffff;
+        const int d_above = above < 128 ? above - right : 0x7fffffff;
+        if (d_below <= d_above) low = below;
+        if (d_above <= d_below && above < 128) high = above;
+      }
+      int donor;
+      if (low >= 0 && high >= 0)
+        donor = s_sal[low] <= s_sal[high] ? low : high;
+      else
+        donor = low >= 0 ? low : high;
+      if (donor < 0) donor = 0;
+      s_don[i] = donor;
+      avail.clear(donor);
+    }
+  }
+  // ---- scales and per-slot encoding parameters
+  const float own_scale = fmaxf(absmax / (selected ? 127.0f : 7.0f), 1.17549435e-38f);
+  s_scale[c] = own_scale;
+  s_rcp[c] = __frcp_rn(own_scale);
+  s_plain[c] = own_scale < 7.8886091e-31f;   // 2^-100: remainders would underflow
+  s_kind[c] = selected ? 1 : 0;
+  s_from[c] = (unsigned char)c;
+  ((float*)p.scales.at(slot, inner))[c] = own_scale;
+  __syncthreads();
+  if (c < count) {
+    const int source = s_src[c], donor = s_don[c];
+    s_kind[donor] = 2;
+    s_from[donor] = (unsigned char)source;
+    ((float*)p.padding.at(slot, inner))[c] = s_mean[donor];
+    if (p.salient.base) {
+      ((unsigned char*)p.salient.at(slot, inner))[c] = (unsigned char)source;
+      ((unsigned char*)p.donors.at(slot, inner))[c] = (unsigned char)donor;
+    }
+  }
+  __syncthreads();
+  if (p.roles.base) {
+    int role = -1;
+    for (int i = 0; i < count; ++i) {
+      if (s_src[i] == c) role = s_don[i];
+      if (s_don[i] == c) role = -2 - i;
+    }
+    if (p.role_bytes == 1)
+      ((signed char*)p.roles.at(slot, inner))[c] = (signed char)role;
+    else
+      ((short*)p.roles.at(slot, inner))[c] = (short)role;
+  }
+  // ---- packing: a thread owns 8 fixed slots (4 payload bytes) and strides over tokens
+  unsigned char* payload = (unsigned char*)p.payload.at(slot, inner);
+  const int chunk = c & 15, t0 = c >> 4;
+  // per slot: divisor, clamp limit, bias and which nibble of the code is stored -- a normal slot
+  // keeps clamp(q, +-7) + 8, a salient slot the high nibble of clamp(q, +-127) + 128, a donor slot
+  // the low nibble of its source's code; all three are (code >> shift) & 15
+  float scale[8], rcp[8], limit[8], bias[8];
+  int shift[8], from[8], kind[8];
+  bool any_plain = false, any_remote = false;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int ch = chunk * 8 + j;
+    kind[j] = s_kind[ch];
+    from[j] = s_from[ch];
+    const int src_ch = from[j];       // a donor slot divides its source's value by its source's scale
+    scale[j] = s_scale[src_ch];
+    rcp[j] = s_rcp[src_ch];
+    any_plain |= s_plain[src_ch] != 0;
+    limit[j] = kind[j] ? 127.f : 7.f;
+    bias[j] = kind[j] ? 128.f : 8.f;
+    shift[j] = kind[j] == 1 ? 4 : 0;
+    any_remote |= (from[j] != ch);
+  }
+  constexpr int kVec = sizeof(T) == 2 ? 1 : 2;   // 16-byte vectors per 8 elements
+  uint4 next[kVec];
+  if (t0 < tokens) {
+#pragma unroll
+    for (int q = 0; q < kVec; ++q) next[q] = ((const uint4*)(row + (long long)t0 * p.in.s_token + chunk * 8))[q];
+  }
+  const long long pack_step = 8 * p.in.s_token;
+  const T* src = row + (long long)t0 * p.in.s_token - pack_step;
+  unsigned char* dst = payload + (long long)t0 * 64 + chunk * 4 - 512;
+  for (int t = t0; t < tokens; t += 8) {
+    src += pack_step;
+    dst += 512;
+    uint4 cur[kVec];
+#pragma unroll
+    for (int q = 0; q < kVec; ++q) cur[q] = next[q];
+    if (t + 8 < tokens) {
+#pragma unroll
+      for (int q = 0; q < kVec; ++q) next[q] = ((const uint4*)(src + pack_step + chunk * 8))[q];
+    }
+    float v[8];
+    const T* hv = (const T*)cur;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = to_float<T>(hv[j]);
+    if (any_remote) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (kind[j] == 2) v[j] = to_float<T>(src[from[j]]);
+    }
+    unsigned word = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float q = rintf(exact_quotient(v[j], scale[j], rcp[j], any_plain));
+      const unsigned code = (unsigned)(int)(fminf(fmaxf(q, -limit[j]), limit[j]) + bias[j]);
+      word |= ((code >> shift[j]) & 15u) << (4 * j);
+    }
+    *(unsigned*)dst = word;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(1024) k4_statistics_kernel(InputRef in, int sample_stride, float* saliency,
                                                               float* sampled_mean, float* donor_error, float* absmax) {
@@ -595,6 +920,85 @@ __global__ void __launch_bounds__(256) v_encode_kernel(VParams p) {
   }
 }
 
+// 128-channel fast path of the value encoder: a warp owns 8 consecutive tokens, issues all its
+// loads first (2 KB in flight per warp), then quantises token by token.  A lane owns 4 channels.
+template <typename T, int BITS, int GROUP>
+__global__ void __launch_bounds__(256) v_encode128_kernel(VParams p) {
+  constexpr int kRows = 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long outer = blockIdx.x / p.in.n_inner, inner = blockIdx.x % p.in.n_inner;
+  const long long slot = p.in.slot(outer);
+  const int t0 = (blockIdx.y * 8 + warp) * kRows;
+  if (t0 >= p.in.tokens) return;
+  const T* base = (const T*)p.in.x + outer * p.in.s_outer + inner * p.in.s_inner + lane * 4;
+  float v[kRows][4];
+#pragma unroll
+  for (int k = 0; k < kRows; ++k) {
+    const int t = min(t0 + k, p.in.tokens - 1);
+    const T* src = base + (long long)t * p.in.s_token;
+    if (sizeof(T) == 2) {
+      const uint2 bits = *(const uint2*)src;
+      const T* hv = (const T*)&bits;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[k][j] = to_float<T>(hv[j]);
+    } else {
+      const float4 f = *(const float4*)src;
+      v[k][0] = f.x; v[k][1] = f.y; v[k][2] = f.z; v[k][3] = f.w;
+    }
+  }
+  constexpr int lanes_per_group = GROUP / 4, groups = 128 / GROUP, bits = BITS;
+  constexpr float levels = (float)((1 << BITS) - 1);
+  unsigned nonfinite = 0u;
+  unsigned char* payload = (unsigned char*)p.payload.at(slot, inner);
+  __half* scales = (__half*)p.scales.at(slot, inner);
+  __half* offsets = (__half*)p.offsets.at(slot, inner);
+#pragma unroll
+  for (int k = 0; k < kRows; ++k) {
+    const int t = t0 + k;
+    if (t >= p.in.tokens) break;
+    float lo = fminf(fminf(v[k][0], v[k][1]), fminf(v[k][2], v[k][3]));
+    float hi = fmaxf(fmaxf(v[k][0], v[k][1]), fmaxf(v[k][2], v[k][3]));
+    unsigned top = max(max(__float_as_uint(v[k][0]) & 0x7fffffffu, __float_as_uint(v[k][1]) & 0x7fffffffu),
+                       max(__float_as_uint(v[k][2]) & 0x7fffffffu, __float_as_uint(v[k][3]) & 0x7fffffffu));
+#pragma unroll
+    for (int off = 1; off < lanes_per_group; off <<= 1) {
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+    }
+    const __half offset16 = __float2half_rn(lo);
+    const __half scale16 = __float2half_rn(fmaxf((hi - lo) / levels, 6.103515625e-05f));
+    const float offset = __half2float(offset16), scale = __half2float(scale16);
+    top = max(top, max(__float_as_uint(offset) & 0x7fffffffu, __float_as_uint(scale) & 0x7fffffffu));
+    nonfinite |= top >= 0x7f800000u;
+    if (lane % lanes_per_group == 0) {
+      const int g = lane / lanes_per_group;
+      scales[(long long)t * groups + g] = scale16;
+      offsets[(long long)t * groups + g] = offset16;
+    }
+    // stored scales are >= 2^-14, so the fused-correction quotient is the IEEE quotient
+    const float rcp = __frcp_rn(scale);
+    unsigned word = 0u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float q = exact_quotient(v[k][j] - offset, scale, rcp, false);
+      const unsigned code = (unsigned)(int)fminf(fmaxf(rintf(q), 0.f), levels);
+      word |= code << (j * bits);
+    }
+    if (bits == 2) {
+      // 8 bits per lane, four lanes per 32-bit word
+      word <<= 8 * (lane & 3);
+      word |= __shfl_xor_sync(0xffffffffu, word, 1);
+      word |= __shfl_xor_sync(0xffffffffu, word, 2);
+      if ((lane & 3) == 0) ((unsigned*)(payload + (long long)t * 32))[lane >> 2] = word;
+    } else {
+      word <<= 16 * (lane & 1);
+      word |= __shfl_xor_sync(0xffffffffu, word, 1);
+      if ((lane & 1) == 0) ((unsigned*)(payload + (long long)t * 64))[lane >> 1] = word;
+    }
+  }
+  if (nonfinite) atomicOr(p.status, INQ_STATUS_NONFINITE);
+}
+
 template <typename T>
 __global__ void v_dequantize_kernel(const unsigned char* payload, const __half* scales, const __half* offsets,
                                     long long total, int channels, int bits, int group, T* out) {
@@ -676,7 +1080,23 @@ extern "C" int inq_k4_encode(const inq_k4_encode_args_t* a, int32_t* status, inq
   if (threads < 128 && C % 8 == 0) threads = 128;  // more tokens in flight while packing narrow rows
   size_t shared = k4_shared_bytes(C, a->count, a->in.tokens, a->min_error != 0);
   unsigned grid = (unsigned)(a->in.n_outer * a->in.n_inner);
-  if (threads <= 256) {
+  if (C == 128 && p.vector_path && a->in.tokens <= kRcpTable && !a->descriptor_i32) {
+    const bool regular = a->in.tokens % 8 == 0 && a->sample_stride == 8;
+    switch (a->in.dtype) {
+      case INQ_F32:
+        if (regular) k4_encode128_kernel<float, true><<<grid, 128, 0, stream>>>(p);
+        else k4_encode128_kernel<float, false><<<grid, 128, 0, stream>>>(p);
+        break;
+      case INQ_F16:
+        if (regular) k4_encode128_kernel<__half, true><<<grid, 128, 0, stream>>>(p);
+        else k4_encode128_kernel<__half, false><<<grid, 128, 0, stream>>>(p);
+        break;
+      default:
+        if (regular) k4_encode128_kernel<__nv_bfloat16, true><<<grid, 128, 0, stream>>>(p);
+        else k4_encode128_kernel<__nv_bfloat16, false><<<grid, 128, 0, stream>>>(p);
+        break;
+    }
+  } else if (threads <= 256) {
     switch (a->in.dtype) {
       case INQ_F32: k4_encode_kernel<float, 256><<<grid, threads, shared, stream>>>(p); break;
       case INQ_F16: k4_encode_kernel<__half, 256><<<grid, threads, shared, stream>>>(p); break;
@@ -786,6 +1206,31 @@ extern "C" int inq_v_encode(const inq_v_encode_args_t* a, int32_t* status, inq_s
   p.status = status;
   dim3 grid((unsigned)(a->in.n_outer * a->in.n_inner), (unsigned)((a->in.tokens + 7) / 8));
   cudaStream_t stream = (cudaStream_t)stream_;
+  const long long es = dtype_size(a->in.dtype);
+  const bool aligned8 = ((uintptr_t)a->in.x % 16 == 0) && (a->in.stride_outer * es) % 16 == 0 &&
+                        (a->in.stride_inner * es) % 16 == 0 && (a->in.stride_token * es) % 16 == 0 &&
+                        ((uintptr_t)a->payload.base % 4 == 0) && a->payload.outer_stride % 4 == 0 && a->payload.inner_stride % 4 == 0;
+  if (C == 128 && aligned8) {
+    dim3 fast((unsigned)(a->in.n_outer * a->in.n_inner), (unsigned)((a->in.tokens + 63) / 64));
+#define INQ_V128(T)                                                                         \
+  if (a->bits == 2) {                                                                       \
+    if (a->group == 32) v_encode128_kernel<T, 2, 32><<<fast, 256, 0, stream>>>(p);          \
+    else if (a->group == 64) v_encode128_kernel<T, 2, 64><<<fast, 256, 0, stream>>>(p);     \
+    else v_encode128_kernel<T, 2, 128><<<fast, 256, 0, stream>>>(p);                        \
+  } else {                                                                                  \
+    if (a->group == 32) v_encode128_kernel<T, 4, 32><<<fast, 256, 0, stream>>>(p);          \
+    else if (a->group == 64) v_encode128_kernel<T, 4, 64><<<fast, 256, 0, stream>>>(p);     \
+    else v_encode128_kernel<T, 4, 128><<<fast, 256, 0, stream>>>(p);                        \
+  }
+    switch (a->in.dtype) {
+      case INQ_F32: INQ_V128(float) break;
+      case INQ_F16: INQ_V128(__half) break;
+      default: INQ_V128(__nv_bfloat16) break;
+    }
+#undef INQ_V128
+    INQ_CUDA_CHECK(cudaGetLastError());
+    return INQ_OK;
+  }
   int rc;
   switch (a->in.dtype) {
     case INQ_F32: rc = launch_v_encode<float>(p, C / 32, grid, stream); break;
