@@ -153,6 +153,19 @@ __device__ __forceinline__ unsigned lds32(unsigned addr) {
   asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
   return v;
 }
+// four transposed 8x8 b16 matrices: register i of lane (r, j) holds elements (2j, r) and (2j+1, r) of matrix i
+template <int OFF>
+__device__ __forceinline__ uint4 ldsm4_trans(unsigned addr) {
+  uint4 v;
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
+  return v;
+}
+__device__ __forceinline__ unsigned hmul2_bits(unsigned a, unsigned b) {
+  unsigned d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 // D = A*B with a zero accumulator (first step of a chain: nothing to keep live or to clear)
 __device__ __forceinline__ void mma_f16_first(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
@@ -260,7 +273,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   extern __shared__ __align__(16) unsigned char smem[];
   float* qs = (float*)smem;                                             // 8 heads x 4 chunks x kQChunk
   unsigned char* warp_base = smem + 8 * 4 * kQChunk * 4;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
   const int groups = (P.n_pad + 15) >> 4;                               // salient channels in groups of 16
   const int warp_bytes = warp_smem_bytes(groups);
@@ -349,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   for (int mt = 0; mt < 8; ++mt)
 #pragma unroll
     for (int k = 0; k < 4; ++k) acc[mt][k] = 0.f;
-  float oacc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  float oacc[4] = {0.f, 0.f, 0.f, 0.f};   // value offsets: row = value group (lanes r < 2), columns = heads 2j, 2j+1
 
   // ---------------------------------------------------------------- exact sink and tail
   // (run while the first packed slices are still in flight, see below)
@@ -408,8 +421,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
         l_run[0] *= a0;
         l_run[1] *= a1;
-        oacc[0][0] *= a0; oacc[1][0] *= a0;
-        oacc[0][1] *= a1; oacc[1][1] *= a1;
+        oacc[0] *= a0;
+        oacc[1] *= a1;
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
           acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
@@ -500,10 +513,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     bool need_weights = true;
     float alpha[2] = {0.f, 0.f}, beta[2] = {0.f, 0.f};
     const unsigned vsel = (r & 1) ? 0x7632u : 0x5410u;
-    // byte offset (inside a stage's V area) of this lane's word of token 2j for value group 0
-    // and group 1; tokens 2j+1, 2j+8, 2j+9 follow at +32, +256, +288
-    const unsigned v_base0 = (unsigned)((((2 * j) * 2 + (((2 * j) >> 2) & 1)) << 4) + (r >> 1) * 4);
-    const unsigned v_base1 = v_base0 ^ 16u;
+    // ldmatrix row address of this lane inside a stage's V area: lanes 0-7 / 8-15 name tokens 0-7 /
+    // 8-15 of value group 0, lanes 16-31 the same tokens of group 1 (halves of tokens 4..7 swapped)
+    const int v_tok = (lane & 7) + 8 * ((lane >> 3) & 1);
+    const unsigned v_ldsm = (unsigned)((2 * v_tok + ((lane >> 4) ^ ((v_tok >> 2) & 1))) << 4);
     const unsigned ring_addr = smem_addr(ring), lane16 = lane * 16;
     const unsigned ww_addr = smem_addr(wW) + lane * 8, sel_addr = smem_addr(wsel) + lane * 16;
     int stage_index = 0;
@@ -676,13 +689,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         // (channels 32j..32j+31) of tokens r and r+8 of the sub-slice.
 // One K step: the fragments of the NEXT step are fetched before this step's MMAs are issued,
 // so no MMA waits on a shared-memory load that was issued just before it.
-#define INQ_KSTEP(U, KS, X, Y, FIRST, WQ, F, WQN, FN)                                                     \
+#define INQ_KMMA(U, X, Y, FIRST, WQ, F)                                                                   \
   {                                                                                                       \
     const unsigned a0 = (X) & 0x000F000Fu, a1 = (Y) & 0x000F000Fu, a2 = (X) & 0x00F000F0u, a3 = (Y) & 0x00F000F0u; \
-    if ((KS) < 7) {                                                                                       \
-      WQN = lds64<(((KS) + 1) & 7) * 256>(ww_it);                                                         \
-      if (SAL) FN = lds128<(((KS) + 1) & 7) * 512>(sel_it);                                               \
-    }                                                                                                     \
     if (FIRST) mma_f16_first(S[U], a0, a1, a2, a3, WQ.x, WQ.y);                                           \
     else mma_f16(S[U], a0, a1, a2, a3, WQ.x, WQ.y);                                                       \
     if (SAL) {                                                                                            \
@@ -695,23 +704,31 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       }                                                                                                   \
     }                                                                                                     \
   }
-#define INQ_KSUB(U)                                                                                       \
+#define INQ_KSTEP(KS, M, SH, FIRST, WQ, F, WQN, FN)                                                       \
   {                                                                                                       \
-    const uint4 kx = lds128<1024 * (U)>(stage + lane16), ky = lds128<1024 * (U) + 512>(stage + lane16);   \
-    uint2 wa = lds64<0>(ww_it), wb_;                                                                      \
-    uint4 fa = make_uint4(0u, 0u, 0u, 0u), fb = fa;                                                       \
-    if (SAL) fa = lds128<0>(sel_it);                                                                      \
-    INQ_KSTEP(U, 0, kx.x, ky.x, true, wa, fa, wb_, fb)                                                    \
-    INQ_KSTEP(U, 1, kx.x >> 8, ky.x >> 8, false, wb_, fb, wa, fa)                                         \
-    INQ_KSTEP(U, 2, kx.y, ky.y, false, wa, fa, wb_, fb)                                                   \
-    INQ_KSTEP(U, 3, kx.y >> 8, ky.y >> 8, false, wb_, fb, wa, fa)                                         \
-    INQ_KSTEP(U, 4, kx.z, ky.z, false, wa, fa, wb_, fb)                                                   \
-    INQ_KSTEP(U, 5, kx.z >> 8, ky.z >> 8, false, wb_, fb, wa, fa)                                         \
-    INQ_KSTEP(U, 6, kx.w, ky.w, false, wa, fa, wb_, fb)                                                   \
-    INQ_KSTEP(U, 7, kx.w >> 8, ky.w >> 8, false, wb_, fb, wa, fa)                                         \
+    if ((KS) < 7) {                                                                                       \
+      WQN = lds64<(((KS) + 1) & 7) * 256>(ww_it);                                                         \
+      if (SAL) FN = lds128<(((KS) + 1) & 7) * 512>(sel_it);                                               \
+    }                                                                                                     \
+    INQ_KMMA(0, kx0.M >> SH, ky0.M >> SH, FIRST, WQ, F)                                                   \
+    if (kSub > 1) INQ_KMMA(kSub - 1, kx1.M >> SH, ky1.M >> SH, FIRST, WQ, F)                              \
   }
-        INQ_KSUB(0)
-        if (kSub > 1) INQ_KSUB(1)
+        {
+          const uint4 kx0 = lds128<0>(stage + lane16), ky0 = lds128<512>(stage + lane16);
+          const uint4 kx1 = lds128<(kSub > 1 ? 1024 : 0)>(stage + lane16), ky1 = lds128<(kSub > 1 ? 1536 : 512)>(stage + lane16);
+          uint2 wa = lds64<0>(ww_it), wb_;
+          uint4 fa = make_uint4(0u, 0u, 0u, 0u), fb = fa;
+          if (SAL) fa = lds128<0>(sel_it);
+          INQ_KSTEP(0, x, 0, true, wa, fa, wb_, fb)
+          INQ_KSTEP(1, x, 8, false, wb_, fb, wa, fa)
+          INQ_KSTEP(2, y, 0, false, wa, fa, wb_, fb)
+          INQ_KSTEP(3, y, 8, false, wb_, fb, wa, fa)
+          INQ_KSTEP(4, z, 0, false, wa, fa, wb_, fb)
+          INQ_KSTEP(5, z, 8, false, wb_, fb, wa, fa)
+          INQ_KSTEP(6, w, 0, false, wa, fa, wb_, fb)
+          INQ_KSTEP(7, w, 8, false, wb_, fb, wa, fa)
+        }
+#undef INQ_KMMA
 #undef INQ_KSUB
 #undef INQ_KSTEP
         if (SAL) {
@@ -808,8 +825,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
         l_run[0] *= a0;
         l_run[1] *= a1;
-        oacc[0][0] *= a0; oacc[1][0] *= a0;
-        oacc[0][1] *= a1; oacc[1][1] *= a1;
+        oacc[0] *= a0;
+        oacc[1] *= a1;
 #pragma unroll
         for (int mt = 0; mt < 8; ++mt) {
           acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
@@ -830,24 +847,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       // ---- values: probabilities times the per-token group scale, codes as fp16 subnormals
 #define INQ_PV(U)                                                                                          \
   {                                                                                                        \
-    const unsigned sp = stage + kStageK + kStageV + 4 * r;                                                 \
-    const float2 vs_lo = half2_bits_to_float2(lds32<64 * (U)>(sp)), vs_hi = half2_bits_to_float2(lds32<64 * (U) + 32>(sp)); \
-    const float2 vo_lo = half2_bits_to_float2(lds32<kStageP / 2 + 64 * (U)>(sp)), vo_hi = half2_bits_to_float2(lds32<kStageP / 2 + 64 * (U) + 32>(sp)); \
-    oacc[0][0] += pr[U][0] * vo_lo.x + pr[U][2] * vo_hi.x;                                                 \
-    oacc[0][1] += pr[U][1] * vo_lo.x + pr[U][3] * vo_hi.x;                                                 \
-    oacc[1][0] += pr[U][0] * vo_lo.y + pr[U][2] * vo_hi.y;                                                 \
-    oacc[1][1] += pr[U][1] * vo_lo.y + pr[U][3] * vo_hi.y;                                                 \
-    const unsigned va = stage + v_base0, vb1 = stage + v_base1;                                            \
-    const unsigned wA0 = lds32<kStageK + 512 * (U)>(va), wB0 = lds32<kStageK + 512 * (U) + 32>(va);        \
-    const unsigned wC0 = lds32<kStageK + 512 * (U) + 256>(va), wD0 = lds32<kStageK + 512 * (U) + 288>(va); \
-    const unsigned wA1 = lds32<kStageK + 512 * (U)>(vb1), wB1 = lds32<kStageK + 512 * (U) + 32>(vb1);      \
-    const unsigned wC1 = lds32<kStageK + 512 * (U) + 256>(vb1), wD1 = lds32<kStageK + 512 * (U) + 288>(vb1); \
+    /* probabilities as fp16, transposed into B fragments: tokens (2j, 2j+1) and (2j+8, 2j+9) of head r */ \
+    const unsigned t0 = movmatrix_trans(pack_half2(pr[U][0], pr[U][1]));                                   \
+    const unsigned t1 = movmatrix_trans(pack_half2(pr[U][2], pr[U][3]));                                   \
+    const unsigned sp = stage + kStageK + kStageV + 8 * j;                                                 \
+    const uint2 s_lo = lds64<64 * (U)>(sp), s_hi = lds64<64 * (U) + 32>(sp);                               \
+    const uint2 o_lo = lds64<kStageP / 2 + 64 * (U)>(sp), o_hi = lds64<kStageP / 2 + 64 * (U) + 32>(sp);   \
+    /* offsets: rows 0 and 1 of a 16-row MMA are the two value groups */                                   \
+    mma_f16(oacc, __byte_perm(o_lo.x, o_lo.y, vsel), 0u, __byte_perm(o_hi.x, o_hi.y, vsel), 0u, t0, t1);   \
+    const uint4 M = ldsm4_trans<kStageK + 512 * (U)>(stage + v_ldsm);                                      \
     _Pragma("unroll") for (int gr = 0; gr < 2; ++gr) {                                                     \
-      const float sl = gr ? vs_lo.y : vs_lo.x, sh = gr ? vs_hi.y : vs_hi.x;                                \
-      const unsigned b0 = movmatrix_trans(pack_half2(pr[U][0] * sl, pr[U][1] * sl));                       \
-      const unsigned b1 = movmatrix_trans(pack_half2(pr[U][2] * sh, pr[U][3] * sh));                       \
-      const unsigned M0 = __byte_perm(gr ? wA1 : wA0, gr ? wB1 : wB0, vsel);                               \
-      const unsigned M1 = __byte_perm(gr ? wC1 : wC0, gr ? wD1 : wD0, vsel);                               \
+      const unsigned gsel2 = gr ? 0x7632u : 0x5410u;                                                       \
+      const unsigned b0 = hmul2_bits(t0, __byte_perm(s_lo.x, s_lo.y, gsel2));                              \
+      const unsigned b1 = hmul2_bits(t1, __byte_perm(s_hi.x, s_hi.y, gsel2));                              \
+      const unsigned M0 = gr ? M.z : M.x, M1 = gr ? M.w : M.y;                                             \
       const unsigned N0 = M0 >> 10, N1 = M1 >> 10;                                                         \
       mma_f16(acc[gr * 4 + 0], M0 & 0x00030003u, M0 & 0x000C000Cu, M1 & 0x00030003u, M1 & 0x000C000Cu, b0, b1); \
       mma_f16(acc[gr * 4 + 1], M0 & 0x00300030u, M0 & 0x00C000C0u, M1 & 0x00300030u, M1 & 0x00C000C0u, b0, b1); \
@@ -884,11 +897,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   for (int off = 4; off < 32; off <<= 1) {
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], off);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], off);
+  }
+  // the offset sums of value group gr, heads 2j and 2j+1, sit in lane (r = gr, j)
+  float osum[2][2];
 #pragma unroll
-    for (int gr = 0; gr < 2; ++gr) {
-      oacc[gr][0] += __shfl_xor_sync(0xffffffffu, oacc[gr][0], off);
-      oacc[gr][1] += __shfl_xor_sync(0xffffffffu, oacc[gr][1], off);
-    }
+  for (int gr = 0; gr < 2; ++gr) {
+    osum[gr][0] = __shfl_sync(0xffffffffu, oacc[0], gr * 4 + j);
+    osum[gr][1] = __shfl_sync(0xffffffffu, oacc[1], gr * 4 + j);
   }
   __syncthreads();   // every warp is done with its ring and weight scratch
   float* wout = (float*)ring;   // [8][132]
@@ -899,7 +914,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int g = 2 * j + e;
-      *(float2*)(wout + g * kRecordStride + ch) = make_float2(acc[mt][e] + oacc[gr][e], acc[mt][2 + e] + oacc[gr][e]);
+      *(float2*)(wout + g * kRecordStride + ch) = make_float2(acc[mt][e] + osum[gr][e], acc[mt][2 + e] + osum[gr][e]);
     }
   }
   if (r == 0) {

@@ -8,7 +8,8 @@ from ctypes import c_int32, c_int64, c_void_p
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIBRARY_PATH = os.path.join(os.path.dirname(_HERE), "libinquant_b200.so")
+# INQUANT_B200_LIBRARY names a library built elsewhere (a deployment's install location)
+LIBRARY_PATH = os.environ.get("INQUANT_B200_LIBRARY") or os.path.join(os.path.dirname(_HERE), "libinquant_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
