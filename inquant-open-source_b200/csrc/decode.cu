@@ -44,12 +44,13 @@ constexpr int kStageBytes = kStageK + kStageV + kStageP;
 constexpr int kRecordStride = 132;                  // floats per query head: acc[128], m, l, pad
 constexpr int kRecordFloats = 8 * kRecordStride;    // one partial record (8 query heads)
 constexpr int kQChunk = 36;                         // padded 32-float chunk of the staged query
+constexpr int kQBytes = 8 * 4 * kQChunk * 4 + 64;   // staged query and two factors per head
 constexpr float kNegBig = -1.0e30f;
 constexpr int kWarpFixed = 2048 + 256 + 64 + 64 + 1024;  // per-warp scratch before the per-group parts
 constexpr float kRescaleSlack = 4.f;   // the running reference maximum may lag the true one by 2^4
 
 __host__ __device__ constexpr int warp_smem_bytes(int groups) {
-  return kWarpFixed + groups * (256 + 4096) + kStages * kStageBytes;
+  return kWarpFixed + groups * (256 + 4096 + 64) + kStages * kStageBytes;
 }
 
 struct SeqDesc {
@@ -272,7 +273,9 @@ template <int MODE, typename QT, bool SAL>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const DecodeParams P) {
   extern __shared__ __align__(16) unsigned char smem[];
   float* qs = (float*)smem;                                             // 8 heads x 4 chunks x kQChunk
-  unsigned char* warp_base = smem + 8 * 4 * kQChunk * 4;
+  float* qinv = qs + 8 * 4 * kQChunk;   // per head: softmax scale * log2(e) * 2^(exponent of max|q| - 12)
+  float* qunscale = qinv + 8;           // per head: the power of two that restores the staged query
+  unsigned char* warp_base = smem + kQBytes;
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
   const int groups = (P.n_pad + 15) >> 4;                               // salient channels in groups of 16
@@ -281,15 +284,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   // folded-query B fragments of the 8 K steps ([step][lane] x 8 bytes); while a block's weights
   // are being derived the same 2 KB hold the per-channel slot weights and additive constants
   unsigned char* wW = wb;
-  float* wf = (float*)wb;                                               // slot weight per channel
-  float* wk0 = wf + 128;                                                // additive constant per channel
   float* wssc = (float*)(wb + 2048);                                    // scale of salient channel i
   unsigned char* wsrc = (unsigned char*)(wssc + 64);                    // channel of salient i
   unsigned char* wdon = wsrc + 64;                                      // its donor slot
   unsigned char* wmeta = wdon + 64;       // staged block metadata: K scales 512 B | role map 256 B | padding 256 B
+  float* ff = (float*)wmeta;              // during a fold: slot weight per channel, over the staged K scales
+  float* fk0 = ff + 128;                  // during a fold: additive constant per channel, over role map and padding
   unsigned char* wqsal = wb + kWarpFixed;                               // B fragments: query at salient channels
   unsigned char* wsel = wqsal + groups * 256;                           // B fragments: nibble selection
-  unsigned char* ring = wsel + groups * 4096;
+  unsigned short* wcell = (unsigned short*)(wsel + groups * 4096);      // selection cells written by the last fold (offsets into wsel)
+  unsigned char* ring = (unsigned char*)wcell + groups * 64;
   __shared__ int s_is_last;
 
   // Flat decomposition: the packed slices of all (sequence, KV head, head tile) pairs form one
@@ -332,12 +336,34 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   const QT* qptr = (const QT*)SEQ(q);
   const long long q_stride = SEQ(q_stride_h);
 
-  // query, pre-multiplied by softmax_scale * log2(e), chunked so that lanes (head, chunk)
-  // read distinct banks
+  // the merge of the previous pair may have used this scratch: start from an empty selection
+  // matrix and an empty list of written cells
+  for (int v = lane; v < groups * 256; v += 32) ((uint4*)wsel)[v] = make_uint4(0u, 0u, 0u, 0u);
+  for (int v = lane; v < groups * 32; v += 32) wcell[v] = 0;
+  // query as fp32, chunked so that lanes (head, chunk) read distinct banks, then scaled per head by
+  // a power of two that brings its largest magnitude into [2^12, 2^13): every folded weight is
+  // then a product below 2^14 that fp16 holds without overflow and with full precision
   for (int idx = threadIdx.x; idx < 8 * 128; idx += kThreads) {
     int g = idx >> 7, c = idx & 127;
-    float v = g < g_valid ? to_float<QT>(qptr[(q_head0 + g) * q_stride + c]) * P.scale_log2e : 0.f;
+    float v = g < g_valid ? to_float<QT>(qptr[(q_head0 + g) * q_stride + c]) : 0.f;
     qs[(g * 4 + (c >> 5)) * kQChunk + (c & 31)] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int hh = 0; hh < 8 / kWarps; ++hh) {
+    const int head = warp * (8 / kWarps) + hh;
+    float* row = qs + head * 4 * kQChunk + lane;
+    const float v0 = row[0], v1 = row[kQChunk], v2 = row[2 * kQChunk], v3 = row[3 * kQChunk];
+    unsigned top = __float_as_uint(fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3))));
+    top = __reduce_max_sync(0xffffffffu, top);
+    int ex = (int)(top >> 23) - 127;
+    ex = top == 0u ? 0 : max(-60, min(60, ex));
+    const float mul = __uint_as_float((unsigned)(127 + 12 - ex) << 23);
+    row[0] = v0 * mul; row[kQChunk] = v1 * mul; row[2 * kQChunk] = v2 * mul; row[3 * kQChunk] = v3 * mul;
+    if (lane == 0) {
+      qunscale[head] = __uint_as_float((unsigned)(127 + ex - 12) << 23);
+      qinv[head] = P.scale_log2e * qunscale[head];
+    }
   }
   __syncthreads();
 
@@ -539,22 +565,30 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           __syncwarp();
         }
         folded_block = cur_block;
-        const float4 sc = *(const float4*)(wmeta + lane * 16);
+        // step 1: this lane owns channels 4*lane .. 4*lane+3
         const unsigned char* meta_roles = wmeta + 512;
-        const float* meta_pad = (const float*)(wmeta + 768);
-        int role[4];
-        if (MODE == 0) {
-          unsigned bits = *(const unsigned*)(meta_roles + lane * 4);
+        int role[4], sidx[4];
+        float scv[4], fv[4], kv[4];
+        {
+          const float4 sc = *(const float4*)(wmeta + lane * 16);
+          scv[0] = sc.x; scv[1] = sc.y; scv[2] = sc.z; scv[3] = sc.w;
+          if (MODE == 0) {
+            const unsigned bits = *(const unsigned*)(meta_roles + lane * 4);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) role[i] = (int)(signed char)((bits >> (8 * i)) & 0xff);
-        } else {
-          uint2 bits = *(const uint2*)(meta_roles + lane * 8);
-          role[0] = (int)(short)(bits.x & 0xffff);
-          role[1] = (int)(short)(bits.x >> 16);
-          role[2] = (int)(short)(bits.y & 0xffff);
-          role[3] = (int)(short)(bits.y >> 16);
+            for (int i = 0; i < 4; ++i) role[i] = (int)(signed char)((bits >> (8 * i)) & 0xff);
+          } else {
+            const uint2 bits = *(const uint2*)(meta_roles + lane * 8);
+            role[0] = (int)(short)(bits.x & 0xffff);
+            role[1] = (int)(short)(bits.x >> 16);
+            role[2] = (int)(short)(bits.y & 0xffff);
+            role[3] = (int)(short)(bits.y >> 16);
+          }
         }
-        const float scv[4] = {sc.x, sc.y, sc.z, sc.w};
+        // the block's scales are brought into [0, 2) by a power of two
+        unsigned top = __float_as_uint(fmaxf(fmaxf(fabsf(scv[0]), fabsf(scv[1])), fmaxf(fabsf(scv[2]), fabsf(scv[3]))));
+        top = __reduce_max_sync(0xffffffffu, top);
+        const int ex_f = max(-60, min(60, (int)(top >> 23) - 127));
+        const float down = __uint_as_float((unsigned)(127 - ex_f) << 23);
         bool bad = false;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -562,113 +596,95 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
             bad = true;
             role[i] = -1;
           }
-        }
-        // clear the nibble-selection fragments of the salient path
-        for (int v = lane; v < groups * 256; v += 32) ((uint4*)wsel)[v] = make_uint4(0u, 0u, 0u, 0u);
-        if (lane < groups * 16) {
-          wsrc[lane] = 0;
-          wdon[lane] = 0;
-          wssc[lane] = 0.f;
-        }
-        if (groups > 2 && lane + 32 < groups * 16) {
-          wsrc[lane + 32] = 0;
-          wdon[lane + 32] = 0;
-          wssc[lane + 32] = 0.f;
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = lane * 4 + i;
-          const int ro = role[i];
-          if (ro == -1) {
-            wf[c] = scv[i];
-            wk0[c] = -8.f * scv[i];
-          } else if (ro >= 0) {
-            // salient: both of its slots leave the linear fold; its exact, dtype-rounded value
-            // is rebuilt per token by the salient path below
-            wf[c] = 0.f;
-            wk0[c] = 0.f;
-            wf[ro] = 0.f;
-            const int idx = -(MODE == 0 ? (int)((const signed char*)meta_roles)[ro] : (int)((const short*)meta_roles)[ro]) - 2;
-            if (idx >= 0 && idx < P.n_pad) {
-              wsrc[idx] = (unsigned char)c;
-              wdon[idx] = (unsigned char)ro;
-              wssc[idx] = scv[i];
-            } else {
-              bad = true;
-            }
-          } else {
-            // donor: the reference stores the sampled mean and rounds it to the model dtype
-            wk0[c] = to_float<QT>(from_float<QT>(meta_pad[-ro - 2]));
+          sidx[i] = -1;
+          // the odd channel of a byte is its high nibble: 16 times the code as an fp16 subnormal
+          fv[i] = scv[i] * ((i & 1) ? 0.0625f * down : down);
+          kv[i] = -8.f * scv[i];
+          if (role[i] >= 0) {
+            // salient: both of its slots leave the linear fold (its exact, dtype-rounded value is
+            // rebuilt per token); its index in the padding list is recorded in its donor's role
+            fv[i] = 0.f;
+            kv[i] = 0.f;
+            const int idx = -(MODE == 0 ? (int)((const signed char*)meta_roles)[role[i]] : (int)((const short*)meta_roles)[role[i]]) - 2;
+            if (idx >= 0 && idx < P.n_pad) sidx[i] = idx; else bad = true;
+          } else if (role[i] < -1) {
+            // donor: its slot holds the low nibble of a salient code; the reference stores the
+            // sampled mean as the channel's own value and rounds it to the model dtype
+            fv[i] = 0.f;
+            kv[i] = to_float<QT>(from_float<QT>(((const float*)(wmeta + 768))[-role[i] - 2]));
           }
         }
         if (bad) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
-        __syncwarp();
-        // selection matrix: column i picks 16 * (high nibble of source i) + (low nibble in its
-        // donor slot), scaled by 2^11 so that every entry and every partial sum is exact
-        for (int i = lane; i < P.n_pad; i += 32) {
+        // the selection cells of the last block are cleared through their recorded offsets
+        for (int v = lane; v < 2 * P.n_pad; v += 32) *(unsigned short*)(wsel + wcell[v]) = 0;
+        __syncwarp();   // the staged metadata has been read: its area now takes the per-channel terms
+        *(float4*)(ff + 4 * lane) = make_float4(fv[0], fv[1], fv[2], fv[3]);
+        *(float4*)(fk0 + 4 * lane) = make_float4(kv[0], kv[1], kv[2], kv[3]);
 #pragma unroll
-          for (int which = 0; which < 2; ++which) {
-            const int c = which ? wdon[i] : wsrc[i];
-            const int jj = c >> 5, u = c & 31;
-            const int ks = 2 * (u >> 3) + ((u >> 1) & 1), half = u & 1, e = (u >> 2) & 1;
-            const int target = ((i & 7) << 2) | jj;
-            float value = which ? 2048.f : 32768.f;
-            if (half) value *= 0.0625f;
-            __half* cell = (__half*)(wsel + ((((i >> 4) * 8 + ks) * 32 + target) * 16) + (((i >> 3) & 1) * 2 + half) * 4 + e * 2);
-            *cell = __float2half_rn(value);
+        for (int i = 0; i < 4; ++i) {
+          if (sidx[i] >= 0) {
+            const int idx = sidx[i];
+            wsrc[idx] = (unsigned char)(4 * lane + i);
+            wdon[idx] = (unsigned char)role[i];
+            wssc[idx] = scv[i];
+            // selection matrix: column idx picks 16 * (high nibble of the source) + (low nibble in
+            // the donor slot), scaled by 2^11 so that every entry and every partial sum is exact
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+              const int c = which ? role[i] : 4 * lane + i;
+              const int jj = c >> 5, u = c & 31;
+              const int ks = 2 * (u >> 3) + ((u >> 1) & 1), half = u & 1, e = (u >> 2) & 1;
+              const int target = ((idx & 7) << 2) | jj;
+              float value = which ? 2048.f : 32768.f;
+              if (half) value *= 0.0625f;
+              const int cell = ((((idx >> 4) * 8 + ks) * 32 + target) * 16) + (((idx >> 3) & 1) * 2 + half) * 4 + e * 2;
+              *(__half*)(wsel + cell) = __float2half_rn(value);
+              wcell[2 * idx + which] = (unsigned short)cell;
+            }
           }
         }
-        // query at the salient channels, as B fragments of the salient step
-        for (int gsel = 0; gsel < groups; ++gsel) {
-          unsigned short qv[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int i = gsel * 16 + 2 * j + (k & 1) + (k >> 1) * 8;
-            const bool live = r < g_valid && i < P.n_pad;
-            qv[k] = live ? *(const unsigned short*)(qptr + (q_head0 + r) * q_stride + wsrc[i]) : (unsigned short)0;
-          }
-          *(uint2*)(wqsal + (gsel * 32 + lane) * 8) = make_uint2((unsigned)qv[0] | ((unsigned)qv[1] << 16),
-                                                                 (unsigned)qv[2] | ((unsigned)qv[3] << 16));
-        }
         __syncwarp();
-        // thread (head r, chunk j) owns the 32 channels 32j..32j+31 of query head r
-        float w[32];
-        float cpart = 0.f, wmax = 0.f;
+        // query at the salient channels, as B fragments of the salient step: the staged copy,
+        // scaled back by its power of two, converts to the model dtype exactly
+        {
+          const float back = qunscale[r];
+          for (int gsel = 0; gsel < groups; ++gsel) {
+            unsigned short qv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int i = gsel * 16 + 2 * j + (k & 1) + (k >> 1) * 8;
+              const int c = wsrc[min(i, 63)];
+              const QT qt = from_float<QT>(qs[(r * 4 + (c >> 5)) * kQChunk + (c & 31)] * back);
+              qv[k] = i < P.n_pad ? *(const unsigned short*)&qt : (unsigned short)0;
+            }
+            *(uint2*)(wqsal + (gsel * 32 + lane) * 8) = make_uint2((unsigned)qv[0] | ((unsigned)qv[1] << 16),
+                                                                   (unsigned)qv[2] | ((unsigned)qv[3] << 16));
+          }
+        }
+        // step 2: thread (head r, chunk j) owns the 32 channels 32j..32j+31 of query head r
         const float* qown = qs + (r * 4 + j) * kQChunk;
+        const float* fown = ff + 32 * j;
+        const float* kown = fk0 + 32 * j;
+        float cp0 = 0.f, cp1 = 0.f, cp2 = 0.f, cp3 = 0.f;
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const float4 f4 = *(const float4*)(wf + 32 * j + 4 * i4);
-          const float4 k4 = *(const float4*)(wk0 + 32 * j + 4 * i4);
-          const float4 q4 = *(const float4*)(qown + 4 * i4);
-          const float fv[4] = {f4.x, f4.y, f4.z, f4.w};
-          const float kv[4] = {k4.x, k4.y, k4.z, k4.w};
-          const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            w[4 * i4 + e] = qv[e] * fv[e];
-            wmax = fmaxf(wmax, fabsf(w[4 * i4 + e]));
-            cpart = fmaf(qv[e], kv[e], cpart);
-          }
+        for (int k8 = 0; k8 < 4; ++k8) {
+          const float4 fa4 = *(const float4*)(fown + 8 * k8), fb4 = *(const float4*)(fown + 8 * k8 + 4);
+          const float4 ka4 = *(const float4*)(kown + 8 * k8), kb4 = *(const float4*)(kown + 8 * k8 + 4);
+          const float4 qa4 = *(const float4*)(qown + 8 * k8), qb4 = *(const float4*)(qown + 8 * k8 + 4);
+          cp0 = fmaf(qa4.x, ka4.x, cp0); cp1 = fmaf(qa4.y, ka4.y, cp1); cp2 = fmaf(qa4.z, ka4.z, cp2); cp3 = fmaf(qa4.w, ka4.w, cp3);
+          cp0 = fmaf(qb4.x, kb4.x, cp0); cp1 = fmaf(qb4.y, kb4.y, cp1); cp2 = fmaf(qb4.z, kb4.z, cp2); cp3 = fmaf(qb4.w, kb4.w, cp3);
+          // K steps 2*k8 and 2*k8+1: channels (0,4 | 1,5) and (2,6 | 3,7) of this group of eight
+          *(uint2*)(wW + ((2 * k8) * 32 + lane) * 8) = make_uint2(pack_half2(qa4.x * fa4.x, qb4.x * fb4.x), pack_half2(qa4.y * fa4.y, qb4.y * fb4.y));
+          *(uint2*)(wW + ((2 * k8 + 1) * 32 + lane) * 8) = make_uint2(pack_half2(qa4.z * fa4.z, qb4.z * fb4.z), pack_half2(qa4.w * fa4.w, qb4.w * fb4.w));
         }
+        float cpart = (cp0 + cp1) + (cp2 + cp3);
         cpart += __shfl_xor_sync(0xffffffffu, cpart, 1);
         cpart += __shfl_xor_sync(0xffffffffu, cpart, 2);
-        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 1));
-        wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, 2));
-        // scale the row into [2^13, 2^14) so that fp16 neither overflows nor loses small weights
-        int ex = (int)((__float_as_uint(wmax) >> 23) & 0xff) - 127;
-        ex = max(-100, min(100, ex));
-        if (wmax == 0.f) ex = 13;
-        const float up = __uint_as_float((unsigned)(127 + 13 - ex) << 23);
-        const float inv = __uint_as_float((unsigned)(127 + ex + 11) << 23);   // 2^24 / up
-        const float up16 = up * 0.0625f;
-        __syncwarp();   // every lane has read the per-channel weights that wW overwrites
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          const int base = 8 * (s >> 1) + 2 * (s & 1);
-          *(uint2*)(wW + (s * 32 + lane) * 8) = make_uint2(pack_half2(w[base] * up, w[base + 4] * up),
-                                                            pack_half2(w[base + 1] * up16, w[base + 5] * up16));
-        }
+        // raw score -> base-2 score of head r: undo 2^-24 (subnormal nibbles), the scale exponent
+        // and the query factor
+        const float qf = qinv[r];
+        const float inv = qf * __uint_as_float((unsigned)(127 + 24 + ex_f) << 23);
+        cpart *= qf;
         // score columns of this thread are query heads 2j and 2j+1
         alpha[0] = __shfl_sync(0xffffffffu, inv, (2 * j) * 4);
         alpha[1] = __shfl_sync(0xffffffffu, inv, (2 * j + 1) * 4);
@@ -807,32 +823,34 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           }
         }
       }
-      // ---- online softmax (base 2) over the 32 tokens
-      float mx0 = fmaxf(s2[0][0], s2[0][2]), mx1 = fmaxf(s2[0][1], s2[0][3]);
-      if (kSub > 1) {
-        mx0 = fmaxf(mx0, fmaxf(s2[kSub - 1][0], s2[kSub - 1][2]));
-        mx1 = fmaxf(mx1, fmaxf(s2[kSub - 1][1], s2[kSub - 1][3]));
-      }
-#pragma unroll
-      for (int off = 4; off < 32; off <<= 1) {
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-      }
-      // the reference maximum is raised only when a score exceeds it by more than the slack, so
-      // the accumulators are rescaled rarely; probabilities stay below 2^slack
-      if (__any_sync(0xffffffffu, mx0 > m_run[0] + kRescaleSlack || mx1 > m_run[1] + kRescaleSlack)) {
-        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-        const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
-        l_run[0] *= a0;
-        l_run[1] *= a1;
-        oacc[0] *= a0;
-        oacc[1] *= a1;
-#pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-          acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
+      // ---- online softmax (base 2) over the 32 tokens.  The reference maximum is raised only when
+      //      a score exceeds it by more than the slack, so the accumulators are rescaled rarely and
+      //      probabilities stay below 2^slack; the common case costs one vote
+      {
+        float mx0 = fmaxf(s2[0][0], s2[0][2]), mx1 = fmaxf(s2[0][1], s2[0][3]);
+        if (kSub > 1) {
+          mx0 = fmaxf(mx0, fmaxf(s2[kSub - 1][0], s2[kSub - 1][2]));
+          mx1 = fmaxf(mx1, fmaxf(s2[kSub - 1][1], s2[kSub - 1][3]));
         }
-        m_run[0] = mn0;
-        m_run[1] = mn1;
+        if (__any_sync(0xffffffffu, mx0 > m_run[0] + kRescaleSlack || mx1 > m_run[1] + kRescaleSlack)) {
+#pragma unroll
+          for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+          }
+          const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+          const float a0 = fast_exp2(m_run[0] - mn0), a1 = fast_exp2(m_run[1] - mn1);
+          l_run[0] *= a0;
+          l_run[1] *= a1;
+          oacc[0] *= a0;
+          oacc[1] *= a1;
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
+          }
+          m_run[0] = mn0;
+          m_run[1] = mn1;
+        }
       }
       float pr[2][4];
 #pragma unroll
@@ -1024,7 +1042,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
 }
 
 #undef SEQ
-static int smem_bytes(int groups) { return 8 * 4 * kQChunk * 4 + kWarps * warp_smem_bytes(groups); }
+static int smem_bytes(int groups) { return kQBytes + kWarps * warp_smem_bytes(groups); }
 
 }  // namespace inq
 
