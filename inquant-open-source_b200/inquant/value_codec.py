@@ -105,7 +105,7 @@ def quantize_value_blocks(tensor, block_count, block_size, bits, group_size):
     blocked = tensor[0, :, :block_count * block_size].reshape(
         heads, block_count, block_size, channels).permute(1, 0, 2, 3)
     packed = quantize_values(blocked, bits, group_size)
-    return [PackedValues(
-        **{name: value[index:index + 1] for name, value in packed.tensors.items()},
-        shape=(1, heads, block_size, channels), original_dtype=tensor.dtype, bits=bits, group_size=group_size,
-    ) for index in range(block_count)]
+    shape = (1, heads, block_size, channels)
+    fields = [packed.payload.split(1), packed.scales.split(1), packed.offsets.split(1)]
+    return [PackedValues(*views, shape=shape, original_dtype=tensor.dtype, bits=bits, group_size=group_size)
+            for views in zip(*fields)]
