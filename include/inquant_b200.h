@@ -213,6 +213,27 @@ int inq_decode_attention_noalloc(const inq_decode_args_t* args /* host */, inq_s
  * across ranks after an all-gather. */
 int inq_merge_partials(const float* records, int32_t n_parts, int64_t n_rows, void* out, int32_t out_dtype,
                        inq_stream_t stream);
+/* Chunked-prefill attention on tcgen05 tensor cores with TMEM accumulators: causal attention of
+ * `q_tokens` new query tokens over `kv_tokens` keys and values, where the last `q_tokens` rows of
+ * k/v are the chunk's own tokens and the rows before them the history (for a packed cache: the
+ * exact sink, the dequantised blocks written by inq_k4_dequantize / inq_v_dequantize, and the
+ * exact tail).  Query i attends to rows 0 .. kv_tokens - q_tokens + i.  Layouts: q/out
+ * [q_heads][q_tokens][128], k/v [kv_heads][kv_tokens][128], fp16 or bf16, element strides below
+ * (multiples of 8, bases 16-byte aligned); head dimension 128; q_heads a multiple of kv_heads.
+ * Replaces: cache.py:179-200 `update` returning the materialised history to the model's SDPA call
+ * (qwen_fused.py:112-121, the original forward) for query chunks after the first. */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  int64_t q_stride_h, q_stride_t, k_stride_h, k_stride_t, v_stride_h, v_stride_t, o_stride_h, o_stride_t;
+  int32_t q_heads, kv_heads, q_tokens, kv_tokens;
+  int32_t dtype;              /* INQ_F16 or INQ_BF16 */
+  float scale;                /* softmax scale */
+  int32_t* status;            /* device status word (INQ_STATUS_WAIT_TIMEOUT on a stuck barrier) */
+} inq_prefill_args_t;
+int inq_prefill_attention(const inq_prefill_args_t* args /* host */, inq_stream_t stream);
 /* Work units (32-token slices, at least 1) of one pair whose sequence holds n_blocks blocks. */
 int64_t inq_decode_units(int32_t n_blocks, int32_t block_tokens);
 /* Scratch floats that suffice for a launch with n_pairs pairs and total_units work units on

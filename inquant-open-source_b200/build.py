@@ -17,6 +17,7 @@ SOURCES = {
     "codec.cu": ["-fmad=false"],
     "decode.cu": ["-DINQ_DECODE_SUB=" + os.environ.get("INQ_DECODE_SUB", "2")],
     "append.cu": [],
+    "prefill.cu": [],
 }
 
 

@@ -1,0 +1,331 @@
+// Chunked-prefill attention on the 5th-generation tensor cores (tcgen05, accumulators in TMEM).
+//
+// One CTA owns 128 query tokens of one query head.  It walks the visible keys and values in
+// tiles of 128 tokens: S = Q K^T (tcgen05.mma, 128 x 128 x 128, fp32 in TMEM), base-2 online
+// softmax with one thread per query row reading its row of S with tcgen05.ld, P written to
+// shared memory in the model dtype, O += P V (tcgen05.mma with V as an MN-major operand, fp32
+// in TMEM).  Keys and values are dense tensors in the model dtype: the dequantised packed
+// history followed by the chunk's own tokens; query i sees positions <= history + i.
+//
+// Shared-memory operand tiles are 128 rows x 128 columns of 2-byte elements as two slabs of 64
+// columns; inside a slab a row is 128 bytes and its 16-byte chunks are XOR-swizzled with the
+// row index modulo 8 (the 128-byte swizzle of the tensor-core descriptors).
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace inq {
+
+constexpr int kPfThreads = 128;
+constexpr int kPfTile = 128;                 // query rows / KV tokens per tile; also the head dimension
+constexpr int kPfSlab = 16384;               // 128 rows x 128 bytes
+constexpr int kPfTileBytes = 2 * kPfSlab;    // one operand tile
+constexpr int kPfSmem = 3 * kPfTileBytes + 1024;   // Q, K (reused for P), V, alignment slack
+constexpr int kPfTmemCols = 256;             // S in columns 0..127, O in columns 128..255
+constexpr float kPfNegBig = -1.0e30f;
+constexpr float kPfSlack = 4.f;              // the reference maximum may lag the true one by 2^4
+constexpr int kPfSpinLimit = 1 << 22;
+
+struct PrefillParams {
+  const void *q, *k, *v;
+  void* out;
+  long long q_sh, q_st, k_sh, k_st, v_sh, v_st, o_sh, o_st;   // strides in elements
+  int q_heads, kv_heads, q_tokens, kv_tokens, n_qtiles;
+  float scale_log2e;
+  int* status;
+};
+
+__device__ __forceinline__ unsigned pf_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+// 64-bit shared-memory matrix descriptor, 128-byte swizzle: start address, leading and stride
+// byte offsets in 16-byte units, descriptor version 1, layout type 2.
+__device__ __forceinline__ unsigned long long pf_desc(unsigned saddr, unsigned lbo_bytes, unsigned sbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((saddr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)(lbo_bytes >> 4) << 16;
+  d |= (unsigned long long)(sbo_bytes >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+__device__ __forceinline__ void pf_mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
+                                       unsigned accumulate) {
+  asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void pf_commit(unsigned mbar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ bool pf_wait(unsigned mbar, unsigned parity) {
+  for (int it = 0; it < kPfSpinLimit; ++it) {
+    unsigned done;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void pf_tmem_ld32(unsigned taddr, unsigned (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+      "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void pf_tmem_st32(unsigned taddr, const unsigned (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+      "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ float pf_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <typename QT>
+__device__ __forceinline__ unsigned pf_pack2(float lo, float hi) {
+  if (std::is_same<QT, __half>::value) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&h);
+  }
+  __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&b);
+}
+
+// Copies rows [row0, row0 + 128) of a [rows][128] tensor into a swizzled operand tile; rows at or
+// beyond `limit` are zero-filled.
+template <typename QT>
+__device__ __forceinline__ void pf_fill_tile(unsigned tile, const QT* base, long long row_stride, int row0, int limit,
+                                             int tid) {
+#pragma unroll 4
+  for (int idx = tid; idx < kPfTile * 16; idx += kPfThreads) {
+    const int row = idx >> 4, chunk = idx & 15, slab = chunk >> 3, c = chunk & 7;
+    const unsigned dst = tile + slab * kPfSlab + (row >> 3) * 1024 + (row & 7) * 128 + ((c ^ (row & 7)) << 4);
+    const bool valid = row0 + row < limit;
+    const QT* src = base + (long long)(valid ? row0 + row : 0) * row_stride + chunk * 8;
+    const unsigned bytes = valid ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+  }
+}
+
+template <typename QT>
+__global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillParams P) {
+  extern __shared__ unsigned char pf_raw[];
+  const unsigned smem0 = (pf_smem(pf_raw) + 1023u) & ~1023u;
+  const unsigned sQ = smem0, sK = smem0 + kPfTileBytes, sV = smem0 + 2 * kPfTileBytes;   // P reuses the K tile
+  __shared__ unsigned tmem_base_s;
+  __shared__ __align__(8) unsigned long long bars[2];
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const unsigned bar_s = pf_smem(&bars[0]), bar_o = pf_smem(&bars[1]);
+
+  // late query tiles see the most keys: they are scheduled first
+  const int qt = P.n_qtiles - 1 - (int)(blockIdx.x / P.q_heads);
+  const int head = (int)(blockIdx.x % P.q_heads);
+  const int kvh = head / (P.q_heads / P.kv_heads);
+  const int q0 = qt * kPfTile;
+  const int hist = P.kv_tokens - P.q_tokens;
+  const int kv_end = min(P.kv_tokens, hist + q0 + kPfTile);
+  const int n_tiles = (kv_end + kPfTile - 1) / kPfTile;
+  const QT* qbase = (const QT*)P.q + (long long)head * P.q_sh;
+  const QT* kbase = (const QT*)P.k + (long long)kvh * P.k_sh;
+  const QT* vbase = (const QT*)P.v + (long long)kvh * P.v_sh;
+
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_o) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(pf_smem(&tmem_base_s)), "r"(kPfTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pf_fill_tile<QT>(sQ, qbase, P.q_st, q0, P.q_tokens, tid);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem = tmem_base_s;
+  const unsigned lane_field = (unsigned)(warp * 32) << 16;
+  const unsigned tS = tmem + lane_field, tO = tmem + lane_field + kPfTile;
+
+  // instruction descriptors: fp32 accumulate, A/B in the model dtype, M = N = 128; the value
+  // tile is an MN-major B operand (tokens are its K dimension, stored row by row)
+  const unsigned fmt = std::is_same<QT, __half>::value ? 0u : 1u;
+  const unsigned idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+  const unsigned idesc_o = idesc_s | (1u << 16);
+
+  const int row = tid;                          // this thread's query row = its TMEM lane
+  const int q_pos = hist + q0 + row;            // keys at positions <= q_pos are visible
+  float m_ref = kPfNegBig, l_sum = 0.f;
+  bool failed = false;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int kv0 = t * kPfTile;
+    if (t > 0 && !failed && !pf_wait(bar_o, (unsigned)(t - 1) & 1u)) failed = true;   // P and V tiles are free again
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    pf_fill_tile<QT>(sK, kbase, P.k_st, kv0, P.kv_tokens, tid);
+    pf_fill_tile<QT>(sV, vbase, P.v_st, kv0, P.kv_tokens, tid);
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const unsigned off = (kk >> 2) * kPfSlab + (kk & 3) * 32;
+        pf_mma(tmem, pf_desc(sQ + off, 16, 1024), pf_desc(sK + off, 16, 1024), idesc_s, kk > 0);
+      }
+      pf_commit(bar_s);
+    }
+    if (!failed && !pf_wait(bar_s, (unsigned)t & 1u)) failed = true;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // ---- softmax of this thread's row: maximum first, then probabilities
+    const bool masked = kv0 + kPfTile - 1 > hist + q0;    // some row of this tile crosses its diagonal
+    float mx = kPfNegBig;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+      unsigned v[32];
+      pf_tmem_ld32(tS + c0, v);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float s = __uint_as_float(v[c]);
+        if (!masked || kv0 + c0 + c <= q_pos) mx = fmaxf(mx, s);
+      }
+    }
+    mx *= P.scale_log2e;
+    const bool raise = mx > m_ref + kPfSlack;
+    if (__any_sync(0xffffffffu, raise)) {
+      // rare: bring the running sums and the output accumulator to the new reference maximum
+      const float m_new = raise ? mx : m_ref;
+      const float factor = pf_exp2(m_ref - m_new);
+      l_sum *= factor;
+      m_ref = m_new;
+      if (t > 0) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+          unsigned v[32];
+          pf_tmem_ld32(tO + c0, v);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * factor);
+          pf_tmem_st32(tO + c0, v);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+    }
+    {
+      const unsigned prow = sK + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+        unsigned v[32];
+        pf_tmem_ld32(tS + c0, v);
+        float p[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float e = pf_exp2(fmaf(__uint_as_float(v[c]), P.scale_log2e, -m_ref));
+          p[c] = (!masked || kv0 + c0 + c <= q_pos) ? e : 0.f;
+          l_sum += p[c];
+        }
+        // 32 tokens = 4 chunks of 8 inside slab c0 / 64
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = ((c0 & 63) >> 3) + q4;
+          const unsigned dst = prow + (c0 >> 6) * kPfSlab + ((chunk ^ (row & 7)) << 4);
+          const unsigned w0 = pf_pack2<QT>(p[8 * q4 + 0], p[8 * q4 + 1]), w1 = pf_pack2<QT>(p[8 * q4 + 2], p[8 * q4 + 3]);
+          const unsigned w2 = pf_pack2<QT>(p[8 * q4 + 4], p[8 * q4 + 5]), w3 = pf_pack2<QT>(p[8 * q4 + 6], p[8 * q4 + 7]);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+        }
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        // A: 16 tokens of P (K-major); B: the same 16 tokens of V, 128 bytes per token and slab
+        const unsigned a_off = (kk >> 2) * kPfSlab + (kk & 3) * 32;
+        pf_mma(tmem + kPfTile, pf_desc(sK + a_off, 16, 1024), pf_desc(sV + kk * 2048, kPfSlab, 1024), idesc_o,
+               (t > 0 || kk > 0) ? 1u : 0u);
+      }
+      pf_commit(bar_o);
+    }
+  }
+  if (!failed && !pf_wait(bar_o, (unsigned)(n_tiles - 1) & 1u)) failed = true;
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (failed && (tid & 31) == 0) atomicOr(P.status, INQ_STATUS_WAIT_TIMEOUT);
+
+  // ---- normalise and store this thread's row
+  {
+    const float inv = 1.f / l_sum;
+    const bool live = q0 + row < P.q_tokens;
+    QT* orow = (QT*)P.out + (long long)head * P.o_sh + (long long)(q0 + row) * P.o_st;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+      unsigned v[32];
+      pf_tmem_ld32(tO + c0, v);
+      if (live) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 0]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
+          w.y = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
+          w.z = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
+          w.w = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
+          *(uint4*)(orow + c0 + 8 * q4) = w;
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPfTmemCols) : "memory");
+}
+
+}  // namespace inq
+
+using namespace inq;
+
+extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t stream_) {
+  if (!a || !a->q || !a->k || !a->v || !a->out || !a->status) return INQ_ERR_ARGUMENT;
+  if (a->q_heads < 1 || a->kv_heads < 1 || a->q_heads % a->kv_heads) return INQ_ERR_ARGUMENT;
+  if (a->q_tokens < 1 || a->kv_tokens < a->q_tokens || !(a->scale > 0.f)) return INQ_ERR_ARGUMENT;
+  if (a->dtype != INQ_F16 && a->dtype != INQ_BF16) return INQ_ERR_UNSUPPORTED;
+  // rows are read and written as 16-byte vectors
+  if ((a->q_stride_t | a->k_stride_t | a->v_stride_t | a->o_stride_t | a->q_stride_h | a->k_stride_h | a->v_stride_h |
+       a->o_stride_h) & 7)
+    return INQ_ERR_ARGUMENT;
+  if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->out) & 15) return INQ_ERR_ARGUMENT;
+  PrefillParams P;
+  P.q = a->q; P.k = a->k; P.v = a->v; P.out = a->out;
+  P.q_sh = a->q_stride_h; P.q_st = a->q_stride_t; P.k_sh = a->k_stride_h; P.k_st = a->k_stride_t;
+  P.v_sh = a->v_stride_h; P.v_st = a->v_stride_t; P.o_sh = a->o_stride_h; P.o_st = a->o_stride_t;
+  P.q_heads = a->q_heads; P.kv_heads = a->kv_heads; P.q_tokens = a->q_tokens; P.kv_tokens = a->kv_tokens;
+  P.n_qtiles = (a->q_tokens + kPfTile - 1) / kPfTile;
+  P.scale_log2e = a->scale * 1.4426950408889634f;
+  P.status = a->status;
+  const long long ctas = (long long)P.n_qtiles * P.q_heads;
+  if (ctas > 0x7fffffffLL) return INQ_ERR_CAPACITY;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (a->dtype == INQ_F16) {
+    INQ_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+    prefill_kernel<__half><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P);
+  } else {
+    INQ_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+    prefill_kernel<__nv_bfloat16><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P);
+  }
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}

@@ -72,6 +72,14 @@ class AppendArgs(ctypes.Structure):
                 ("sink_position", c_int32), ("heads", c_int32), ("row_bytes", c_int32), ("status", c_void_p)]
 
 
+class PrefillArgs(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p),
+                ("q_stride_h", c_int64), ("q_stride_t", c_int64), ("k_stride_h", c_int64), ("k_stride_t", c_int64),
+                ("v_stride_h", c_int64), ("v_stride_t", c_int64), ("o_stride_h", c_int64), ("o_stride_t", c_int64),
+                ("q_heads", c_int32), ("kv_heads", c_int32), ("q_tokens", c_int32), ("kv_tokens", c_int32),
+                ("dtype", c_int32), ("scale", ctypes.c_float), ("status", c_void_p)]
+
+
 RECORD_FLOATS = 8 * 132  # one split-KV partial: 8 query heads x (acc[128], m, l, pad)
 
 _lib = None
@@ -105,6 +113,7 @@ EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
     "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
     "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
+    "inq_prefill_attention",
 )
 
 
@@ -120,6 +129,7 @@ SIGNATURES = {
     "inq_decode_attention": [_P, _P],
     "inq_decode_attention_noalloc": [_P, _P],
     "inq_merge_partials": [_P, _I, _L, _P, _I, _P],
+    "inq_prefill_attention": [_P, _P],
     "inq_append_token": [_P, _P],
     "inq_append_token_batch": [_P, _I, _P, _P],
 }

@@ -1,0 +1,86 @@
+"""Chunked-prefill attention (tcgen05 kernel) against float32 causal attention computed by torch
+from the same bf16/fp16 tensors, and against the cache's materialising semantics."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import attention_close, to_numpy
+
+pytestmark = pytest.mark.gpu
+
+
+def _reference(q, k, v, scale):
+    """fp32 causal attention; query i sees keys 0 .. L - Tq + i."""
+    q32, k32, v32 = q.float(), k.float(), v.float()
+    groups = q.shape[1] // k.shape[1]
+    k32 = k32.repeat_interleave(groups, dim=1)
+    v32 = v32.repeat_interleave(groups, dim=1)
+    tq, tk = q.shape[2], k.shape[2]
+    s = torch.einsum("bhqd,bhkd->bhqk", q32, k32) * scale
+    pos = torch.arange(tq, device=q.device)[:, None] + (tk - tq)
+    s = s.masked_fill(torch.arange(tk, device=q.device)[None, :] > pos, float("-inf"))
+    return torch.einsum("bhqk,bhkd->bhqd", torch.softmax(s, dim=-1), v32)
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,q_tokens,history,dtype", [
+    (2, 1, 128, 0, torch.bfloat16),        # one tile, pure causal
+    (4, 2, 256, 128, torch.bfloat16),      # full tiles with history
+    (7, 1, 200, 77, torch.bfloat16),       # ragged query and history lengths, GQA 7
+    (4, 4, 1, 300, torch.bfloat16),        # a single query token
+    (8, 2, 384, 1000, torch.float16),      # fp16, several KV tiles
+    (28, 4, 512, 2048, torch.bfloat16),    # Qwen2.5-7B head counts
+])
+def test_prefill_attention_matches_fp32_causal_attention(q_heads, kv_heads, q_tokens, history, dtype):
+    from inquant.prefill import prefill_attention
+    gen = torch.Generator(device="cuda").manual_seed(11 + q_tokens + history)
+    q = torch.randn((1, q_heads, q_tokens, 128), device="cuda", generator=gen).to(dtype)
+    k = torch.randn((1, kv_heads, history + q_tokens, 128), device="cuda", generator=gen).to(dtype)
+    v = torch.randn((1, kv_heads, history + q_tokens, 128), device="cuda", generator=gen).to(dtype)
+    k[:, :, :, 5] *= 6.0   # an outlier channel sharpens the softmax
+    scale = 128 ** -0.5
+    out = prefill_attention(q, k, v, scale)
+    from inquant import _native
+    assert _native.take_status(q.device) == 0
+    expected = _reference(q, k, v, scale)
+    attention_close(to_numpy(out.float())[0], to_numpy(expected)[0])
+
+
+def test_prefill_attention_accepts_strided_views_and_rejects_bad_arguments():
+    from inquant.prefill import prefill_attention
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    # [1, T, H, D] projections viewed as [1, H, T, D], as a model produces them
+    q = torch.randn((1, 160, 4, 128), device="cuda", generator=gen).bfloat16().transpose(1, 2)
+    k = torch.randn((1, 400, 2, 128), device="cuda", generator=gen).bfloat16().transpose(1, 2)
+    v = torch.randn((1, 400, 2, 128), device="cuda", generator=gen).bfloat16().transpose(1, 2)
+    out = prefill_attention(q, k, v, 0.1)
+    attention_close(to_numpy(out.float())[0], to_numpy(_reference(q, k, v, 0.1))[0])
+    with pytest.raises(ValueError):
+        prefill_attention(q, k[:, :, :100], v[:, :, :100])          # fewer keys than queries
+    with pytest.raises(NotImplementedError):
+        prefill_attention(q.float(), k.float(), v.float())
+    with pytest.raises(ValueError):
+        prefill_attention(q[:, :3], k, v)                            # 3 query heads over 2 KV heads
+
+
+def test_prefill_chunks_through_the_cache_match_one_shot_attention_over_materialised_history():
+    """16 chunks... here 3 chunks of 256: every chunk attends to the cache's dequantised history
+    plus itself, exactly what `InQuantCache.update` hands to the model's attention."""
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.prefill import prefill_chunk
+    gen = torch.Generator(device="cuda").manual_seed(19)
+    heads, q_heads, chunk, chunks = 2, 14, 256, 3
+    cfg = CacheConfig(CodecConfig(donor_policy="min_error"), block_size=64, residual_length=16, sink_tokens=4,
+                      value_bits=2, value_group_size=64)
+    cache, shadow = InQuantCache(cfg), InQuantCache(cfg)
+    scale = 128 ** -0.5
+    for c in range(chunks):
+        q = torch.randn((1, q_heads, chunk, 128), device="cuda", generator=gen).bfloat16()
+        k = torch.randn((1, heads, chunk, 128), device="cuda", generator=gen).bfloat16()
+        v = torch.randn((1, heads, chunk, 128), device="cuda", generator=gen).bfloat16()
+        out = prefill_chunk(cache, q, k, v, 0, scale)
+        full_k, full_v = shadow.update(k, v, 0)
+        assert full_k.shape[2] == (c + 1) * chunk
+        attention_close(to_numpy(out.float())[0], to_numpy(_reference(q, full_k, full_v, scale))[0])
+    for a, b in zip(cache.materialize(0), shadow.materialize(0)):
+        assert torch.equal(a, b)
