@@ -1,13 +1,14 @@
 // Chunked-prefill attention on the 5th-generation tensor cores (tcgen05, accumulators in TMEM).
 //
 // One CTA owns 128 query tokens of one query head.  It walks the visible keys and values in
-// tiles of 128 tokens: S = Q K^T (tcgen05.mma, 128 x 128 x 128, fp32 in TMEM), base-2 online
+// tiles of 64 tokens: S = Q K^T (tcgen05.mma, 128 x 64 x 128, fp32 in TMEM), base-2 online
 // softmax with one thread per query row reading its row of S with tcgen05.ld, P written to
-// shared memory in the model dtype, O += P V (tcgen05.mma with V as an MN-major operand, fp32
-// in TMEM).  Keys and values are dense tensors in the model dtype: the dequantised packed
-// history followed by the chunk's own tokens; query i sees positions <= history + i.
+// shared memory in the model dtype, O += P V (tcgen05.mma 128 x 128 x 64 with V as an MN-major
+// operand, fp32 in TMEM).  K and V tiles are double-buffered: the copies of tile t+1 run under
+// the softmax and the second contraction of tile t; two CTAs share an SM.  Keys and values are dense tensors in
+// the model dtype: the dequantised packed history followed by the chunk's own tokens; query i sees positions <= history + i.
 //
-// Shared-memory operand tiles are 128 rows x 128 columns of 2-byte elements as two slabs of 64
+// Shared-memory operand tiles hold rows of 128 (Q, K, V) or 64 (P) 2-byte elements as slabs of 64
 // columns; inside a slab a row is 128 bytes and its 16-byte chunks are XOR-swizzled with the
 // row index modulo 8 (the 128-byte swizzle of the tensor-core descriptors).
 #include <type_traits>
@@ -17,11 +18,16 @@
 namespace inq {
 
 constexpr int kPfThreads = 128;
-constexpr int kPfTile = 128;                 // query rows / KV tokens per tile; also the head dimension
-constexpr int kPfSlab = 16384;               // 128 rows x 128 bytes
-constexpr int kPfTileBytes = 2 * kPfSlab;    // one operand tile
-constexpr int kPfSmem = 3 * kPfTileBytes + 1024;   // Q, K (reused for P), V, alignment slack
-constexpr int kPfTmemCols = 256;             // S in columns 0..127, O in columns 128..255
+constexpr int kPfTile = 128;                 // query rows per CTA; also the head dimension
+constexpr int kPfKv = 64;                    // KV tokens per tile
+constexpr int kPfQSlab = kPfTile * 128;      // 128 rows x 128 bytes
+constexpr int kPfKvSlab = kPfKv * 128;       // 64 rows x 128 bytes
+constexpr int kPfQBytes = 2 * kPfQSlab;      // Q tile: two slabs (head dimension halves)
+constexpr int kPfKvBytes = 2 * kPfKvSlab;    // K or V tile
+constexpr int kPfPBytes = kPfQSlab;          // P tile: 128 rows x 64 tokens, one slab
+constexpr int kPfTiles = kPfQBytes + 4 * kPfKvBytes + kPfPBytes;   // Q, K x2, V x2, P
+constexpr int kPfSmem = kPfTiles + 64;       // then the TMEM base address and two mbarriers; two CTAs fit an SM
+constexpr int kPfTmemCols = 256;             // S in columns 0..63, O in columns 64..191
 constexpr float kPfNegBig = -1.0e30f;
 constexpr float kPfSlack = 4.f;              // the reference maximum may lag the true one by 2^4
 constexpr int kPfSpinLimit = 1 << 22;
@@ -102,15 +108,15 @@ __device__ __forceinline__ unsigned pf_pack2(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&b);
 }
 
-// Copies rows [row0, row0 + 128) of a [rows][128] tensor into a swizzled operand tile; rows at or
+// Copies rows [row0, row0 + ROWS) of a [rows][128] tensor into a swizzled operand tile; rows at or
 // beyond `limit` are zero-filled.
-template <typename QT>
+template <typename QT, int ROWS>
 __device__ __forceinline__ void pf_fill_tile(unsigned tile, const QT* base, long long row_stride, int row0, int limit,
                                              int tid) {
 #pragma unroll 4
-  for (int idx = tid; idx < kPfTile * 16; idx += kPfThreads) {
+  for (int idx = tid; idx < ROWS * 16; idx += kPfThreads) {
     const int row = idx >> 4, chunk = idx & 15, slab = chunk >> 3, c = chunk & 7;
-    const unsigned dst = tile + slab * kPfSlab + (row >> 3) * 1024 + (row & 7) * 128 + ((c ^ (row & 7)) << 4);
+    const unsigned dst = tile + slab * (ROWS * 128) + (row >> 3) * 1024 + (row & 7) * 128 + ((c ^ (row & 7)) << 4);
     const bool valid = row0 + row < limit;
     const QT* src = base + (long long)(valid ? row0 + row : 0) * row_stride + chunk * 8;
     const unsigned bytes = valid ? 16u : 0u;
@@ -120,13 +126,19 @@ __device__ __forceinline__ void pf_fill_tile(unsigned tile, const QT* base, long
 
 template <typename QT>
 __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillParams P) {
-  extern __shared__ unsigned char pf_raw[];
-  const unsigned smem0 = (pf_smem(pf_raw) + 1023u) & ~1023u;
-  const unsigned sQ = smem0, sK = smem0 + kPfTileBytes, sV = smem0 + 2 * kPfTileBytes;   // P reuses the K tile
-  __shared__ unsigned tmem_base_s;
-  __shared__ __align__(8) unsigned long long bars[2];
+  // no static shared memory: the dynamic region starts the CTA's window, 1024-byte aligned as the
+  // 128-byte swizzle needs (checked below)
+  extern __shared__ __align__(1024) unsigned char pf_raw[];
+  const unsigned smem0 = pf_smem(pf_raw);
+  const unsigned sQ = smem0, sKV = smem0 + kPfQBytes, sP = sKV + 4 * kPfKvBytes;
+  // tile t uses K buffer sKV + (t & 1) * kPfKvBytes and V buffer sKV + (2 + (t & 1)) * kPfKvBytes
+  unsigned* const tmem_base_p = (unsigned*)(pf_raw + kPfTiles);
+  const unsigned bar_s = smem0 + kPfTiles + 16, bar_o = bar_s + 8;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const unsigned bar_s = pf_smem(&bars[0]), bar_o = pf_smem(&bars[1]);
+  if (smem0 & 1023u) {
+    if (tid == 0) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
+    return;
+  }
 
   // late query tiles see the most keys: they are scheduled first
   const int qt = P.n_qtiles - 1 - (int)(blockIdx.x / P.q_heads);
@@ -135,7 +147,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
   const int q0 = qt * kPfTile;
   const int hist = P.kv_tokens - P.q_tokens;
   const int kv_end = min(P.kv_tokens, hist + q0 + kPfTile);
-  const int n_tiles = (kv_end + kPfTile - 1) / kPfTile;
+  const int n_tiles = (kv_end + kPfKv - 1) / kPfKv;
   const QT* qbase = (const QT*)P.q + (long long)head * P.q_sh;
   const QT* kbase = (const QT*)P.k + (long long)kvh * P.k_sh;
   const QT* vbase = (const QT*)P.v + (long long)kvh * P.v_sh;
@@ -147,22 +159,25 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(pf_smem(&tmem_base_s)), "r"(kPfTmemCols) : "memory");
+                 ::"r"(pf_smem(tmem_base_p)), "r"(kPfTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  pf_fill_tile<QT>(sQ, qbase, P.q_st, q0, P.q_tokens, tid);
+  pf_fill_tile<QT, kPfTile>(sQ, qbase, P.q_st, q0, P.q_tokens, tid);
+  pf_fill_tile<QT, kPfKv>(sKV, kbase, P.k_st, 0, P.kv_tokens, tid);
+  pf_fill_tile<QT, kPfKv>(sKV + 2 * kPfKvBytes, vbase, P.v_st, 0, P.kv_tokens, tid);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const unsigned tmem = tmem_base_s;
+  const unsigned tmem = *tmem_base_p;
   const unsigned lane_field = (unsigned)(warp * 32) << 16;
-  const unsigned tS = tmem + lane_field, tO = tmem + lane_field + kPfTile;
+  const unsigned tS = tmem + lane_field, tO = tmem + lane_field + kPfKv;
 
-  // instruction descriptors: fp32 accumulate, A/B in the model dtype, M = N = 128; the value
-  // tile is an MN-major B operand (tokens are its K dimension, stored row by row)
+  // instruction descriptors: fp32 accumulate, A/B in the model dtype, M = 128; N = 64 tokens for
+  // the scores, N = 128 channels for the output, whose value tile is an MN-major B operand
+  // (tokens are its K dimension, stored row by row)
   const unsigned fmt = std::is_same<QT, __half>::value ? 0u : 1u;
-  const unsigned idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-  const unsigned idesc_o = idesc_s | (1u << 16);
+  const unsigned idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((unsigned)(kPfKv >> 3) << 17) | ((128u >> 4) << 24);
+  const unsigned idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
   const int row = tid;                          // this thread's query row = its TMEM lane
   const int q_pos = hist + q0 + row;            // keys at positions <= q_pos are visible
@@ -170,11 +185,8 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
   bool failed = false;
 
   for (int t = 0; t < n_tiles; ++t) {
-    const int kv0 = t * kPfTile;
-    if (t > 0 && !failed && !pf_wait(bar_o, (unsigned)(t - 1) & 1u)) failed = true;   // P and V tiles are free again
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    pf_fill_tile<QT>(sK, kbase, P.k_st, kv0, P.kv_tokens, tid);
-    pf_fill_tile<QT>(sV, vbase, P.v_st, kv0, P.kv_tokens, tid);
+    const int kv0 = t * kPfKv;
+    const unsigned sK = sKV + (t & 1) * kPfKvBytes, sV = sKV + (2 + (t & 1)) * kPfKvBytes;
     asm volatile("cp.async.wait_all;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
@@ -182,32 +194,62 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        const unsigned off = (kk >> 2) * kPfSlab + (kk & 3) * 32;
-        pf_mma(tmem, pf_desc(sQ + off, 16, 1024), pf_desc(sK + off, 16, 1024), idesc_s, kk > 0);
+        pf_mma(tmem, pf_desc(sQ + (kk >> 2) * kPfQSlab + (kk & 3) * 32, 16, 1024),
+               pf_desc(sK + (kk >> 2) * kPfKvSlab + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
       }
       pf_commit(bar_s);
+    }
+    // the second contraction of tile t-1 has to finish before its P, its V buffer and the K buffer
+    // of tile t-1 are reused; then tile t+1 is requested into those buffers
+    if (t > 0 && !failed && !pf_wait(bar_o, (unsigned)(t - 1) & 1u)) failed = true;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (t + 1 < n_tiles) {
+      pf_fill_tile<QT, kPfKv>(sKV + ((t + 1) & 1) * kPfKvBytes, kbase, P.k_st, kv0 + kPfKv, P.kv_tokens, tid);
+      pf_fill_tile<QT, kPfKv>(sKV + (2 + ((t + 1) & 1)) * kPfKvBytes, vbase, P.v_st, kv0 + kPfKv, P.kv_tokens, tid);
     }
     if (!failed && !pf_wait(bar_s, (unsigned)t & 1u)) failed = true;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // ---- softmax of this thread's row: maximum first, then probabilities
-    const bool masked = kv0 + kPfTile - 1 > hist + q0;    // some row of this tile crosses its diagonal
-    float mx = kPfNegBig;
+    // ---- softmax of this thread's row in one pass over S: probabilities are taken against the
+    //      running reference maximum; only when a score exceeds it by more than the slack (rare
+    //      after the first tile) is the maximum raised, the accumulator rescaled and the pass redone
+    const bool masked = kv0 + kPfKv - 1 > hist + q0;    // some row of this tile crosses its diagonal
+    const unsigned prow = sP + (row >> 3) * 1024 + (row & 7) * 128;
+    float smax, l_tile;
+    auto pass = [&](auto masked_tag) {
+      constexpr bool kMasked = decltype(masked_tag)::value;
+      smax = kPfNegBig;
+      l_tile = 0.f;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kPfTile; c0 += 32) {
-      unsigned v[32];
-      pf_tmem_ld32(tS + c0, v);
+      for (int c0 = 0; c0 < kPfKv; c0 += 32) {
+        unsigned v[32];
+        pf_tmem_ld32(tS + c0, v);
+        float p[32];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const float s = __uint_as_float(v[c]);
-        if (!masked || kv0 + c0 + c <= q_pos) mx = fmaxf(mx, s);
+        for (int c = 0; c < 32; ++c) {
+          const float sv = __uint_as_float(v[c]);
+          const bool visible = !kMasked || kv0 + c0 + c <= q_pos;
+          if (visible) smax = fmaxf(smax, sv);
+          const float e = pf_exp2(fmaf(sv, P.scale_log2e, -m_ref));
+          p[c] = visible ? e : 0.f;
+          l_tile += p[c];
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = (c0 >> 3) + q4;
+          const unsigned dst = prow + ((chunk ^ (row & 7)) << 4);
+          const unsigned w0 = pf_pack2<QT>(p[8 * q4 + 0], p[8 * q4 + 1]), w1 = pf_pack2<QT>(p[8 * q4 + 2], p[8 * q4 + 3]);
+          const unsigned w2 = pf_pack2<QT>(p[8 * q4 + 4], p[8 * q4 + 5]), w3 = pf_pack2<QT>(p[8 * q4 + 6], p[8 * q4 + 7]);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+        }
       }
-    }
-    mx *= P.scale_log2e;
-    const bool raise = mx > m_ref + kPfSlack;
+    };
+    if (masked) pass(std::true_type{}); else pass(std::false_type{});
+    const bool raise = smax * P.scale_log2e > m_ref + kPfSlack;
     if (__any_sync(0xffffffffu, raise)) {
-      // rare: bring the running sums and the output accumulator to the new reference maximum
-      const float m_new = raise ? mx : m_ref;
+      // bring the running sum and the output accumulator to the new reference maximum, then
+      // take the probabilities again
+      const float m_new = raise ? smax * P.scale_log2e : m_ref;
       const float factor = pf_exp2(m_ref - m_new);
       l_sum *= factor;
       m_ref = m_new;
@@ -222,41 +264,18 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
+      if (masked) pass(std::true_type{}); else pass(std::false_type{});
     }
-    {
-      const unsigned prow = sK + (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kPfTile; c0 += 32) {
-        unsigned v[32];
-        pf_tmem_ld32(tS + c0, v);
-        float p[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float e = pf_exp2(fmaf(__uint_as_float(v[c]), P.scale_log2e, -m_ref));
-          p[c] = (!masked || kv0 + c0 + c <= q_pos) ? e : 0.f;
-          l_sum += p[c];
-        }
-        // 32 tokens = 4 chunks of 8 inside slab c0 / 64
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((c0 & 63) >> 3) + q4;
-          const unsigned dst = prow + (c0 >> 6) * kPfSlab + ((chunk ^ (row & 7)) << 4);
-          const unsigned w0 = pf_pack2<QT>(p[8 * q4 + 0], p[8 * q4 + 1]), w1 = pf_pack2<QT>(p[8 * q4 + 2], p[8 * q4 + 3]);
-          const unsigned w2 = pf_pack2<QT>(p[8 * q4 + 4], p[8 * q4 + 5]), w3 = pf_pack2<QT>(p[8 * q4 + 6], p[8 * q4 + 7]);
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-        }
-      }
-    }
+    l_sum += l_tile;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
+      for (int kk = 0; kk < 4; ++kk) {
         // A: 16 tokens of P (K-major); B: the same 16 tokens of V, 128 bytes per token and slab
-        const unsigned a_off = (kk >> 2) * kPfSlab + (kk & 3) * 32;
-        pf_mma(tmem + kPfTile, pf_desc(sK + a_off, 16, 1024), pf_desc(sV + kk * 2048, kPfSlab, 1024), idesc_o,
+        pf_mma(tmem + kPfKv, pf_desc(sP + kk * 32, 16, 1024), pf_desc(sV + kk * 2048, kPfKvSlab, 1024), idesc_o,
                (t > 0 || kk > 0) ? 1u : 0u);
       }
       pf_commit(bar_o);
