@@ -4,13 +4,16 @@
 // tiles of 64 tokens: S = Q K^T (tcgen05.mma, 128 x 64 x 128, fp32 in TMEM), base-2 online
 // softmax with one thread per query row reading its row of S with tcgen05.ld, P written to
 // shared memory in the model dtype, O += P V (tcgen05.mma 128 x 128 x 64 with V as an MN-major
-// operand, fp32 in TMEM).  K and V tiles are double-buffered: the copies of tile t+1 run under
-// the softmax and the second contraction of tile t; two CTAs share an SM.  Keys and values are dense tensors in
+// operand, fp32 in TMEM).  Q, K and V tiles arrive by TMA (cp.async.bulk.tensor with the 128-byte
+// swizzle, completion on mbarriers, no multicast); K and V are double-buffered: the copies of
+// tile t+1 run under the softmax and the second contraction of tile t; two CTAs share an SM.  Keys and values are dense tensors in
 // the model dtype: the dequantised packed history followed by the chunk's own tokens; query i sees positions <= history + i.
 //
 // Shared-memory operand tiles hold rows of 128 (Q, K, V) or 64 (P) 2-byte elements as slabs of 64
 // columns; inside a slab a row is 128 bytes and its 16-byte chunks are XOR-swizzled with the
 // row index modulo 8 (the 128-byte swizzle of the tensor-core descriptors).
+#include <cuda.h>
+
 #include <type_traits>
 
 #include "common.cuh"
@@ -26,7 +29,7 @@ constexpr int kPfQBytes = 2 * kPfQSlab;      // Q tile: two slabs (head dimensio
 constexpr int kPfKvBytes = 2 * kPfKvSlab;    // K or V tile
 constexpr int kPfPBytes = kPfQSlab;          // P tile: 128 rows x 64 tokens, one slab
 constexpr int kPfTiles = kPfQBytes + 4 * kPfKvBytes + kPfPBytes;   // Q, K x2, V x2, P
-constexpr int kPfSmem = kPfTiles + 64;       // then the TMEM base address and two mbarriers; two CTAs fit an SM
+constexpr int kPfSmem = kPfTiles + 64;       // then the TMEM base address and five mbarriers; two CTAs fit an SM
 constexpr int kPfTmemCols = 256;             // S in columns 0..63, O in columns 64..191
 constexpr float kPfNegBig = -1.0e30f;
 constexpr float kPfSlack = 4.f;              // the reference maximum may lag the true one by 2^4
@@ -108,24 +111,20 @@ __device__ __forceinline__ unsigned pf_pack2(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&b);
 }
 
-// Copies rows [row0, row0 + ROWS) of a [rows][128] tensor into a swizzled operand tile; rows at or
-// beyond `limit` are zero-filled.
-template <typename QT, int ROWS>
-__device__ __forceinline__ void pf_fill_tile(unsigned tile, const QT* base, long long row_stride, int row0, int limit,
-                                             int tid) {
-#pragma unroll 4
-  for (int idx = tid; idx < ROWS * 16; idx += kPfThreads) {
-    const int row = idx >> 4, chunk = idx & 15, slab = chunk >> 3, c = chunk & 7;
-    const unsigned dst = tile + slab * (ROWS * 128) + (row >> 3) * 1024 + (row & 7) * 128 + ((c ^ (row & 7)) << 4);
-    const bool valid = row0 + row < limit;
-    const QT* src = base + (long long)(valid ? row0 + row : 0) * row_stride + chunk * 8;
-    const unsigned bytes = valid ? 16u : 0u;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-  }
+// One TMA box: 64 columns (128 bytes) x `rows` rows of head `z`, starting at column x and row y, into
+// a swizzled slab; rows beyond the tensor are zero-filled by the hardware.
+__device__ __forceinline__ void pf_tma(unsigned dst, const CUtensorMap* map, int x, int y, int z, unsigned mbar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ void pf_expect(unsigned mbar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
 }
 
 template <typename QT>
-__global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillParams P) {
+__global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillParams P, const __grid_constant__ CUtensorMap map_q,
+                                                                const __grid_constant__ CUtensorMap map_k,
+                                                                const __grid_constant__ CUtensorMap map_v) {
   // no static shared memory: the dynamic region starts the CTA's window, 1024-byte aligned as the
   // 128-byte swizzle needs (checked below)
   extern __shared__ __align__(1024) unsigned char pf_raw[];
@@ -133,7 +132,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
   const unsigned sQ = smem0, sKV = smem0 + kPfQBytes, sP = sKV + 4 * kPfKvBytes;
   // tile t uses K buffer sKV + (t & 1) * kPfKvBytes and V buffer sKV + (2 + (t & 1)) * kPfKvBytes
   unsigned* const tmem_base_p = (unsigned*)(pf_raw + kPfTiles);
-  const unsigned bar_s = smem0 + kPfTiles + 16, bar_o = bar_s + 8;
+  const unsigned bar_s = smem0 + kPfTiles + 16, bar_o = bar_s + 8, bar_q = bar_s + 16, bar_kv = bar_s + 24;   // bar_kv: two
   const int tid = threadIdx.x, warp = tid >> 5;
   if (smem0 & 1023u) {
     if (tid == 0) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
@@ -148,23 +147,34 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
   const int hist = P.kv_tokens - P.q_tokens;
   const int kv_end = min(P.kv_tokens, hist + q0 + kPfTile);
   const int n_tiles = (kv_end + kPfKv - 1) / kPfKv;
-  const QT* qbase = (const QT*)P.q + (long long)head * P.q_sh;
-  const QT* kbase = (const QT*)P.k + (long long)kvh * P.k_sh;
-  const QT* vbase = (const QT*)P.v + (long long)kvh * P.v_sh;
+  // tile t: K into sKV + (t & 1) * kPfKvBytes, V into sKV + (2 + (t & 1)) * kPfKvBytes, two boxes each
+  auto request_tile = [&](int t) {
+    const unsigned bar = bar_kv + 8 * (t & 1);
+    const unsigned dk = sKV + (t & 1) * kPfKvBytes, dv = sKV + (2 + (t & 1)) * kPfKvBytes;
+    pf_expect(bar, 2 * kPfKvBytes);
+    pf_tma(dk, &map_k, 0, t * kPfKv, kvh, bar);
+    pf_tma(dk + kPfKvSlab, &map_k, 64, t * kPfKv, kvh, bar);
+    pf_tma(dv, &map_v, 0, t * kPfKv, kvh, bar);
+    pf_tma(dv + kPfKvSlab, &map_v, 64, t * kPfKv, kvh, bar);
+  };
 
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s) : "memory");
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_o) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_q) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_kv) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_kv + 8) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    pf_expect(bar_q, kPfQBytes);
+    pf_tma(sQ, &map_q, 0, q0, head, bar_q);
+    pf_tma(sQ + kPfQSlab, &map_q, 64, q0, head, bar_q);
+    request_tile(0);
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(pf_smem(tmem_base_p)), "r"(kPfTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  pf_fill_tile<QT, kPfTile>(sQ, qbase, P.q_st, q0, P.q_tokens, tid);
-  pf_fill_tile<QT, kPfKv>(sKV, kbase, P.k_st, 0, P.kv_tokens, tid);
-  pf_fill_tile<QT, kPfKv>(sKV + 2 * kPfKvBytes, vbase, P.v_st, 0, P.kv_tokens, tid);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -187,10 +197,11 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
   for (int t = 0; t < n_tiles; ++t) {
     const int kv0 = t * kPfKv;
     const unsigned sK = sKV + (t & 1) * kPfKvBytes, sV = sKV + (2 + (t & 1)) * kPfKvBytes;
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
     if (tid == 0) {
+      // the tile has landed (TMA and the tensor core share the asynchronous proxy); every thread
+      // finished reading the previous S before the barrier that preceded the last PV issue
+      if (t == 0 && !pf_wait(bar_q, 0)) failed = true;
+      if (!pf_wait(bar_kv + 8 * (t & 1), (unsigned)(t >> 1) & 1u)) failed = true;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
@@ -203,10 +214,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
     // of tile t-1 are reused; then tile t+1 is requested into those buffers
     if (t > 0 && !failed && !pf_wait(bar_o, (unsigned)(t - 1) & 1u)) failed = true;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (t + 1 < n_tiles) {
-      pf_fill_tile<QT, kPfKv>(sKV + ((t + 1) & 1) * kPfKvBytes, kbase, P.k_st, kv0 + kPfKv, P.kv_tokens, tid);
-      pf_fill_tile<QT, kPfKv>(sKV + (2 + ((t + 1) & 1)) * kPfKvBytes, vbase, P.v_st, kv0 + kPfKv, P.kv_tokens, tid);
-    }
+    if (tid == 0 && t + 1 < n_tiles) request_tile(t + 1);
     if (!failed && !pf_wait(bar_s, (unsigned)t & 1u)) failed = true;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
@@ -317,6 +325,38 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
 
 using namespace inq;
 
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+// [heads][tokens][128] tensor of 2-byte elements, boxes of 64 columns x `box_rows` rows, 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* base, int dtype, long long tokens, long long heads, long long stride_t,
+              long long stride_h, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return false;
+  if (heads == 1) stride_h = tokens * stride_t;   // unused, but must be a valid stride
+  const cuuint64_t dims[3] = {128, (cuuint64_t)tokens, (cuuint64_t)heads};
+  const cuuint64_t strides[2] = {(cuuint64_t)stride_t * 2, (cuuint64_t)stride_h * 2};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return fn(map, dtype == INQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)base, dims,
+            strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+
 extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->out || !a->status) return INQ_ERR_ARGUMENT;
   if (a->q_heads < 1 || a->kv_heads < 1 || a->q_heads % a->kv_heads) return INQ_ERR_ARGUMENT;
@@ -338,12 +378,20 @@ extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t s
   const long long ctas = (long long)P.n_qtiles * P.q_heads;
   if (ctas > 0x7fffffffLL) return INQ_ERR_CAPACITY;
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (a->q_stride_h <= 0 || a->k_stride_h <= 0 || a->v_stride_h <= 0 || a->q_stride_t < 128 || a->k_stride_t < 128 ||
+      a->v_stride_t < 128)
+    return INQ_ERR_ARGUMENT;
+  CUtensorMap map_q, map_k, map_v;
+  if (!make_map(&map_q, a->q, a->dtype, a->q_tokens, a->q_heads, a->q_stride_t, a->q_stride_h, kPfTile) ||
+      !make_map(&map_k, a->k, a->dtype, a->kv_tokens, a->kv_heads, a->k_stride_t, a->k_stride_h, kPfKv) ||
+      !make_map(&map_v, a->v, a->dtype, a->kv_tokens, a->kv_heads, a->v_stride_t, a->v_stride_h, kPfKv))
+    return INQ_ERR_ARGUMENT;
   if (a->dtype == INQ_F16) {
     INQ_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
-    prefill_kernel<__half><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P);
+    prefill_kernel<__half><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P, map_q, map_k, map_v);
   } else {
     INQ_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
-    prefill_kernel<__nv_bfloat16><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P);
+    prefill_kernel<__nv_bfloat16><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P, map_q, map_k, map_v);
   }
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
