@@ -1,13 +1,21 @@
 // Chunked-prefill attention on the 5th-generation tensor cores (tcgen05, accumulators in TMEM).
 //
-// One CTA owns 128 query tokens of one query head.  It walks the visible keys and values in
-// tiles of 64 tokens: S = Q K^T (tcgen05.mma, 128 x 64 x 128, fp32 in TMEM), base-2 online
-// softmax with one thread per query row reading its row of S with tcgen05.ld, P written to
-// shared memory in the model dtype, O += P V (tcgen05.mma 128 x 128 x 64 with V as an MN-major
-// operand, fp32 in TMEM).  Q, K and V tiles arrive by TMA (cp.async.bulk.tensor with the 128-byte
-// swizzle, completion on mbarriers, no multicast); K and V are double-buffered: the copies of
-// tile t+1 run under the softmax and the second contraction of tile t; two CTAs share an SM.  Keys and values are dense tensors in
-// the model dtype: the dequantised packed history followed by the chunk's own tokens; query i sees positions <= history + i.
+// One CTA owns 256 query tokens of one query head as two tiles of 128 rows (A and B) and walks
+// the visible keys and values in tiles of 64 tokens.  Ten warps, three roles:
+//   * warps 0-3 / 4-7: softmax of tile A / tile B, one thread per query row.  A thread reads its
+//     row of S from tensor memory (tcgen05.ld), takes base-2 probabilities against a lazily
+//     raised reference maximum in one pass, and writes P in the model dtype to shared memory.
+//   * warp 8 (one lane): issues the contractions.  S = Q K^T (tcgen05.mma 128 x 64 x 128) and
+//     O += P V (128 x 128 x 64, V as an MN-major operand), fp32 accumulators in tensor memory.
+//     The order S_A, S_B, PV_A, S_A', PV_B, S_B', ... keeps the tensor core busy with one tile
+//     while the other tile's softmax runs.
+//   * warp 9 (one lane): TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) for Q once and
+//     for the K and V tiles, four of each in flight.
+// All hand-overs are mbarriers; every wait is bounded and a wait that gives up raises an abort
+// flag that ends the other loops.  One CTA per SM (tensor-memory kernels are scheduled that way),
+// 224 KB of shared memory, 384 of the 512 TMEM columns.  Keys and values are dense tensors in
+// the model dtype: the dequantised packed history followed by the chunk's own tokens; query i
+// sees positions <= history + i.
 //
 // Shared-memory operand tiles hold rows of 128 (Q, K, V) or 64 (P) 2-byte elements as slabs of 64
 // columns; inside a slab a row is 128 bytes and its 16-byte chunks are XOR-swizzled with the
@@ -20,17 +28,19 @@
 
 namespace inq {
 
-constexpr int kPfThreads = 128;
-constexpr int kPfTile = 128;                 // query rows per CTA; also the head dimension
+constexpr int kPfThreads = 320;              // 8 softmax warps, the MMA warp, the TMA warp
+constexpr int kPfTile = 128;                 // query rows per tile; also the head dimension
+constexpr int kPfRows = 2 * kPfTile;         // query rows per CTA (tiles A and B)
 constexpr int kPfKv = 64;                    // KV tokens per tile
 constexpr int kPfQSlab = kPfTile * 128;      // 128 rows x 128 bytes
 constexpr int kPfKvSlab = kPfKv * 128;       // 64 rows x 128 bytes
-constexpr int kPfQBytes = 2 * kPfQSlab;      // Q tile: two slabs (head dimension halves)
+constexpr int kPfQBytes = 2 * kPfQSlab;      // one Q tile: two slabs (head dimension halves)
 constexpr int kPfKvBytes = 2 * kPfKvSlab;    // K or V tile
 constexpr int kPfPBytes = kPfQSlab;          // P tile: 128 rows x 64 tokens, one slab
-constexpr int kPfTiles = kPfQBytes + 4 * kPfKvBytes + kPfPBytes;   // Q, K x2, V x2, P
-constexpr int kPfSmem = kPfTiles + 64;       // then the TMEM base address and five mbarriers; two CTAs fit an SM
-constexpr int kPfTmemCols = 256;             // S in columns 0..63, O in columns 64..191
+constexpr int kPfStages = 4;                 // K and V tiles in flight: the TMA latency spans several tiles
+constexpr int kPfTiles = 2 * kPfQBytes + 2 * kPfStages * kPfKvBytes + 2 * kPfPBytes;   // Q x2, K and V stages, P x2
+constexpr int kPfSmem = kPfTiles + 160;      // then the TMEM base address, the abort flag and 15 mbarriers
+constexpr int kPfTmemCols = 512;             // S_A 0..63, S_B 64..127, O_A 128..255, O_B 256..383
 constexpr float kPfNegBig = -1.0e30f;
 constexpr float kPfSlack = 4.f;              // the reference maximum may lag the true one by 2^4
 constexpr int kPfSpinLimit = 1 << 22;
@@ -39,7 +49,7 @@ struct PrefillParams {
   const void *q, *k, *v;
   void* out;
   long long q_sh, q_st, k_sh, k_st, v_sh, v_st, o_sh, o_st;   // strides in elements
-  int q_heads, kv_heads, q_tokens, kv_tokens, n_qtiles;
+  int q_heads, kv_heads, q_tokens, kv_tokens, n_qpairs;
   float scale_log2e;
   int* status;
 };
@@ -66,14 +76,20 @@ __device__ __forceinline__ void pf_mma(unsigned tmem_d, unsigned long long da, u
 __device__ __forceinline__ void pf_commit(unsigned mbar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
 }
-__device__ __forceinline__ bool pf_wait(unsigned mbar, unsigned parity) {
+// Bounded wait; gives up early when another role has raised the abort flag.
+__device__ __forceinline__ bool pf_wait(unsigned mbar, unsigned parity, volatile int* abort_flag) {
   for (int it = 0; it < kPfSpinLimit; ++it) {
     unsigned done;
     asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                  : "=r"(done) : "r"(mbar), "r"(parity) : "memory");
     if (done) return true;
+    if ((it & 255) == 255 && *abort_flag) return false;
   }
+  *abort_flag = 1;
   return false;
+}
+__device__ __forceinline__ void pf_arrive(unsigned mbar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
 }
 __device__ __forceinline__ void pf_tmem_ld32(unsigned taddr, unsigned (&v)[32]) {
   asm volatile(
@@ -122,55 +138,55 @@ __device__ __forceinline__ void pf_expect(unsigned mbar, unsigned bytes) {
 }
 
 template <typename QT>
-__global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillParams P, const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillParams P, const __grid_constant__ CUtensorMap map_q,
                                                                 const __grid_constant__ CUtensorMap map_k,
                                                                 const __grid_constant__ CUtensorMap map_v) {
   // no static shared memory: the dynamic region starts the CTA's window, 1024-byte aligned as the
   // 128-byte swizzle needs (checked below)
   extern __shared__ __align__(1024) unsigned char pf_raw[];
   const unsigned smem0 = pf_smem(pf_raw);
-  const unsigned sQ = smem0, sKV = smem0 + kPfQBytes, sP = sKV + 4 * kPfKvBytes;
-  // tile t uses K buffer sKV + (t & 1) * kPfKvBytes and V buffer sKV + (2 + (t & 1)) * kPfKvBytes
+  const unsigned sQ = smem0;                                  // tile A, then tile B
+  const unsigned sKb = smem0 + 2 * kPfQBytes;                 // K stages
+  const unsigned sVb = sKb + kPfStages * kPfKvBytes;          // V stages
+  const unsigned sPb = sVb + kPfStages * kPfKvBytes;          // P of tile A, then of tile B
   unsigned* const tmem_base_p = (unsigned*)(pf_raw + kPfTiles);
-  const unsigned bar_s = smem0 + kPfTiles + 16, bar_o = bar_s + 8, bar_q = bar_s + 16, bar_kv = bar_s + 24;   // bar_kv: two
-  const int tid = threadIdx.x, warp = tid >> 5;
+  volatile int* const abort_flag = (volatile int*)(pf_raw + kPfTiles + 4);
+  const unsigned bars = smem0 + kPfTiles + 16;
+  const unsigned bar_q = bars, bar_k = bars + 8 /* per stage */, bar_v = bar_k + 8 * kPfStages /* per stage */;
+  const unsigned bar_s = bar_v + 8 * kPfStages /* A, B */, bar_p = bar_s + 16 /* A, B */, bar_o = bar_p + 16 /* A, B */;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (smem0 & 1023u) {
     if (tid == 0) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
     return;
   }
 
-  // late query tiles see the most keys: they are scheduled first
-  const int qt = P.n_qtiles - 1 - (int)(blockIdx.x / P.q_heads);
+  // late query rows see the most keys: they are scheduled first
+  const int qp = P.n_qpairs - 1 - (int)(blockIdx.x / P.q_heads);
   const int head = (int)(blockIdx.x % P.q_heads);
   const int kvh = head / (P.q_heads / P.kv_heads);
-  const int q0 = qt * kPfTile;
+  const int q0 = qp * kPfRows;
   const int hist = P.kv_tokens - P.q_tokens;
-  const int kv_end = min(P.kv_tokens, hist + q0 + kPfTile);
-  const int n_tiles = (kv_end + kPfKv - 1) / kPfKv;
-  // tile t: K into sKV + (t & 1) * kPfKvBytes, V into sKV + (2 + (t & 1)) * kPfKvBytes, two boxes each
-  auto request_tile = [&](int t) {
-    const unsigned bar = bar_kv + 8 * (t & 1);
-    const unsigned dk = sKV + (t & 1) * kPfKvBytes, dv = sKV + (2 + (t & 1)) * kPfKvBytes;
-    pf_expect(bar, 2 * kPfKvBytes);
-    pf_tma(dk, &map_k, 0, t * kPfKv, kvh, bar);
-    pf_tma(dk + kPfKvSlab, &map_k, 64, t * kPfKv, kvh, bar);
-    pf_tma(dv, &map_v, 0, t * kPfKv, kvh, bar);
-    pf_tma(dv + kPfKvSlab, &map_v, 64, t * kPfKv, kvh, bar);
-  };
+  // tiles each query tile needs: A ends at its last row's diagonal, B 128 tokens later
+  const int n_a = (min(P.kv_tokens, hist + q0 + kPfTile) + kPfKv - 1) / kPfKv;
+  const int n_b = (min(P.kv_tokens, hist + q0 + kPfRows) + kPfKv - 1) / kPfKv;
 
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s) : "memory");
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_o) : "memory");
+    *abort_flag = 0;
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_q) : "memory");
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_kv) : "memory");
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_kv + 8) : "memory");
+#pragma unroll
+    for (int i = 0; i < kPfStages; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_k + 8 * i) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_v + 8 * i) : "memory");
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_s + 8 * i) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_p + 8 * i), "r"(kPfTile) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_o + 8 * i) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    pf_expect(bar_q, kPfQBytes);
-    pf_tma(sQ, &map_q, 0, q0, head, bar_q);
-    pf_tma(sQ + kPfQSlab, &map_q, 64, q0, head, bar_q);
-    request_tile(0);
   }
-  if (warp == 0) {
+  if (warp == 8) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(pf_smem(tmem_base_p)), "r"(kPfTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -179,125 +195,176 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem = *tmem_base_p;
-  const unsigned lane_field = (unsigned)(warp * 32) << 16;
-  const unsigned tS = tmem + lane_field, tO = tmem + lane_field + kPfKv;
 
-  // instruction descriptors: fp32 accumulate, A/B in the model dtype, M = 128; N = 64 tokens for
-  // the scores, N = 128 channels for the output, whose value tile is an MN-major B operand
-  // (tokens are its K dimension, stored row by row)
-  const unsigned fmt = std::is_same<QT, __half>::value ? 0u : 1u;
-  const unsigned idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((unsigned)(kPfKv >> 3) << 17) | ((128u >> 4) << 24);
-  const unsigned idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-
-  const int row = tid;                          // this thread's query row = its TMEM lane
-  const int q_pos = hist + q0 + row;            // keys at positions <= q_pos are visible
-  float m_ref = kPfNegBig, l_sum = 0.f;
-  bool failed = false;
-
-  for (int t = 0; t < n_tiles; ++t) {
-    const int kv0 = t * kPfKv;
-    const unsigned sK = sKV + (t & 1) * kPfKvBytes, sV = sKV + (2 + (t & 1)) * kPfKvBytes;
-    if (tid == 0) {
-      // the tile has landed (TMA and the tensor core share the asynchronous proxy); every thread
-      // finished reading the previous S before the barrier that preceded the last PV issue
-      if (t == 0 && !pf_wait(bar_q, 0)) failed = true;
-      if (!pf_wait(bar_kv + 8 * (t & 1), (unsigned)(t >> 1) & 1u)) failed = true;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (warp == 9) {
+    // ================================================================ TMA warp
+    if (lane == 0) {
+      auto request_k = [&](int t) {
+        const unsigned bar = bar_k + 8 * (t % kPfStages), dst = sKb + (t % kPfStages) * kPfKvBytes;
+        pf_expect(bar, kPfKvBytes);
+        pf_tma(dst, &map_k, 0, t * kPfKv, kvh, bar);
+        pf_tma(dst + kPfKvSlab, &map_k, 64, t * kPfKv, kvh, bar);
+      };
+      auto request_v = [&](int t) {
+        const unsigned bar = bar_v + 8 * (t % kPfStages), dst = sVb + (t % kPfStages) * kPfKvBytes;
+        pf_expect(bar, kPfKvBytes);
+        pf_tma(dst, &map_v, 0, t * kPfKv, kvh, bar);
+        pf_tma(dst + kPfKvSlab, &map_v, 64, t * kPfKv, kvh, bar);
+      };
+      pf_expect(bar_q, 2 * kPfQBytes);
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {
-        pf_mma(tmem, pf_desc(sQ + (kk >> 2) * kPfQSlab + (kk & 3) * 32, 16, 1024),
-               pf_desc(sK + (kk >> 2) * kPfKvSlab + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
+      for (int x = 0; x < 2; ++x) {
+        pf_tma(sQ + x * kPfQBytes, &map_q, 0, q0 + x * kPfTile, head, bar_q);
+        pf_tma(sQ + x * kPfQBytes + kPfQSlab, &map_q, 64, q0 + x * kPfTile, head, bar_q);
       }
-      pf_commit(bar_s);
+      for (int t = 0; t < kPfStages && t < n_b; ++t) {
+        request_k(t);
+        request_v(t);
+      }
+      for (int t = 0; t + kPfStages < n_b; ++t) {
+        // K(t) is free once both score contractions of tile t are done, V(t) once both output
+        // contractions are (the commits are ordered, so tile B's barrier covers tile A's)
+        if (!pf_wait(bar_s + 8, (unsigned)t & 1u, abort_flag)) break;
+        request_k(t + kPfStages);
+        if (!pf_wait(bar_o + 8, (unsigned)t & 1u, abort_flag)) break;
+        request_v(t + kPfStages);
+      }
     }
-    // the second contraction of tile t-1 has to finish before its P, its V buffer and the K buffer
-    // of tile t-1 are reused; then tile t+1 is requested into those buffers
-    if (t > 0 && !failed && !pf_wait(bar_o, (unsigned)(t - 1) & 1u)) failed = true;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (tid == 0 && t + 1 < n_tiles) request_tile(t + 1);
-    if (!failed && !pf_wait(bar_s, (unsigned)t & 1u)) failed = true;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-    // ---- softmax of this thread's row in one pass over S: probabilities are taken against the
-    //      running reference maximum; only when a score exceeds it by more than the slack (rare
-    //      after the first tile) is the maximum raised, the accumulator rescaled and the pass redone
-    const bool masked = kv0 + kPfKv - 1 > hist + q0;    // some row of this tile crosses its diagonal
-    const unsigned prow = sP + (row >> 3) * 1024 + (row & 7) * 128;
-    float smax, l_tile;
-    auto pass = [&](auto masked_tag) {
-      constexpr bool kMasked = decltype(masked_tag)::value;
-      smax = kPfNegBig;
-      l_tile = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kPfKv; c0 += 32) {
-        unsigned v[32];
-        pf_tmem_ld32(tS + c0, v);
-        float p[32];
+  } else if (warp == 8) {
+    // ================================================================ MMA warp
+    if (lane == 0) {
+      // instruction descriptors: fp32 accumulate, A/B in the model dtype, M = 128; N = 64 tokens
+      // for the scores, N = 128 channels for the output, whose value tile is an MN-major B operand
+      const unsigned fmt = std::is_same<QT, __half>::value ? 0u : 1u;
+      const unsigned idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((unsigned)(kPfKv >> 3) << 17) | ((128u >> 4) << 24);
+      const unsigned idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+      auto issue_s = [&](int x, int t) {      // S_x = Q_x K(t)^T
+        const unsigned q = sQ + x * kPfQBytes, k = sKb + (t % kPfStages) * kPfKvBytes;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float sv = __uint_as_float(v[c]);
-          const bool visible = !kMasked || kv0 + c0 + c <= q_pos;
-          if (visible) smax = fmaxf(smax, sv);
-          const float e = pf_exp2(fmaf(sv, P.scale_log2e, -m_ref));
-          p[c] = visible ? e : 0.f;
-          l_tile += p[c];
-        }
+        for (int kk = 0; kk < 8; ++kk)
+          pf_mma(tmem + x * kPfKv, pf_desc(q + (kk >> 2) * kPfQSlab + (kk & 3) * 32, 16, 1024),
+                 pf_desc(k + (kk >> 2) * kPfKvSlab + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
+        pf_commit(bar_s + 8 * x);
+      };
+      auto issue_o = [&](int x, int t) {      // O_x += P_x V(t)
+        const unsigned pp = sPb + x * kPfPBytes, v = sVb + (t % kPfStages) * kPfKvBytes;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (c0 >> 3) + q4;
-          const unsigned dst = prow + ((chunk ^ (row & 7)) << 4);
-          const unsigned w0 = pf_pack2<QT>(p[8 * q4 + 0], p[8 * q4 + 1]), w1 = pf_pack2<QT>(p[8 * q4 + 2], p[8 * q4 + 3]);
-          const unsigned w2 = pf_pack2<QT>(p[8 * q4 + 4], p[8 * q4 + 5]), w3 = pf_pack2<QT>(p[8 * q4 + 6], p[8 * q4 + 7]);
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-        }
+        for (int kk = 0; kk < 4; ++kk)
+          pf_mma(tmem + 2 * kPfKv + x * kPfTile, pf_desc(pp + kk * 32, 16, 1024), pf_desc(v + kk * 2048, kPfKvSlab, 1024),
+                 idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+        pf_commit(bar_o + 8 * x);
+      };
+      bool ok = pf_wait(bar_q, 0, abort_flag) && pf_wait(bar_k, 0, abort_flag);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_s(0, 0);
+        issue_s(1, 0);
       }
-    };
-    if (masked) pass(std::true_type{}); else pass(std::false_type{});
-    const bool raise = smax * P.scale_log2e > m_ref + kPfSlack;
-    if (__any_sync(0xffffffffu, raise)) {
-      // bring the running sum and the output accumulator to the new reference maximum, then
-      // take the probabilities again
-      const float m_new = raise ? smax * P.scale_log2e : m_ref;
-      const float factor = pf_exp2(m_ref - m_new);
-      l_sum *= factor;
-      m_ref = m_new;
-      if (t > 0) {
+      for (int t = 0; ok && t < n_b; ++t) {
+        const bool a_live = t < n_a;
+        if (a_live) ok = ok && pf_wait(bar_p, (unsigned)t & 1u, abort_flag);       // P_A(t) written, S_A(t) read
+        ok = ok && pf_wait(bar_v + 8 * (t % kPfStages), (unsigned)(t / kPfStages) & 1u, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (a_live) issue_o(0, t);
+        if (t + 1 < n_b) {
+          ok = pf_wait(bar_k + 8 * ((t + 1) % kPfStages), (unsigned)((t + 1) / kPfStages) & 1u, abort_flag);
+          if (!ok) break;
+          if (t + 1 < n_a) issue_s(0, t + 1);
+        }
+        ok = pf_wait(bar_p + 8, (unsigned)t & 1u, abort_flag);                     // P_B(t) written, S_B(t) read
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_o(1, t);
+        if (t + 1 < n_b) issue_s(1, t + 1);
+      }
+    }
+  } else {
+    // ================================================================ softmax warps
+    const int x = warp >> 2;                       // 0: tile A, 1: tile B
+    const int row = tid & (kPfTile - 1);           // query row inside the tile = TMEM lane
+    const int n_x = x ? n_b : n_a;
+    const int q_row = q0 + x * kPfTile + row;
+    const int q_pos = hist + q_row;                // keys at positions <= q_pos are visible
+    const int diag0 = hist + q0 + x * kPfTile;     // first row's diagonal: tiles reaching beyond it need masks
+    const unsigned lane_field = (unsigned)((warp & 3) * 32) << 16;
+    const unsigned tS = tmem + lane_field + x * kPfKv, tO = tmem + lane_field + 2 * kPfKv + x * kPfTile;
+    const unsigned prow = sPb + x * kPfPBytes + (row >> 3) * 1024 + (row & 7) * 128;
+    const unsigned my_s = bar_s + 8 * x, my_p = bar_p + 8 * x, my_o = bar_o + 8 * x;
+    float m_ref = kPfNegBig, l_sum = 0.f;
+    bool ok = true;
+
+    for (int t = 0; t < n_x; ++t) {
+      const int kv0 = t * kPfKv;
+      // S(t) is complete; the contractions run in issue order, so PV(t-1) is complete as well:
+      // P may be overwritten and O may be rescaled
+      if (!pf_wait(my_s, (unsigned)t & 1u, abort_flag)) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool masked = kv0 + kPfKv - 1 > diag0;
+      float smax, l_tile;
+      auto pass = [&](auto masked_tag) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
+        smax = kPfNegBig;
+        l_tile = 0.f;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+        for (int c0 = 0; c0 < kPfKv; c0 += 32) {
           unsigned v[32];
-          pf_tmem_ld32(tO + c0, v);
+          pf_tmem_ld32(tS + c0, v);
+          float p[32];
 #pragma unroll
-          for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * factor);
-          pf_tmem_st32(tO + c0, v);
+          for (int c = 0; c < 32; ++c) {
+            const float sv = __uint_as_float(v[c]);
+            const bool visible = !kMasked || kv0 + c0 + c <= q_pos;
+            if (visible) smax = fmaxf(smax, sv);
+            const float e = pf_exp2(fmaf(sv, P.scale_log2e, -m_ref));
+            p[c] = visible ? e : 0.f;
+            l_tile += p[c];
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int chunk = (c0 >> 3) + q4;
+            const unsigned dst = prow + ((chunk ^ (row & 7)) << 4);
+            const unsigned w0 = pf_pack2<QT>(p[8 * q4 + 0], p[8 * q4 + 1]), w1 = pf_pack2<QT>(p[8 * q4 + 2], p[8 * q4 + 3]);
+            const unsigned w2 = pf_pack2<QT>(p[8 * q4 + 4], p[8 * q4 + 5]), w3 = pf_pack2<QT>(p[8 * q4 + 6], p[8 * q4 + 7]);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+          }
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      }
+      };
       if (masked) pass(std::true_type{}); else pass(std::false_type{});
-    }
-    l_sum += l_tile;
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool raise = smax * P.scale_log2e > m_ref + kPfSlack;
+      if (__any_sync(0xffffffffu, raise)) {
+        // rare after the first tile: bring the running sum and the output accumulator to the new
+        // reference maximum, then take the probabilities again
+        const float m_new = raise ? smax * P.scale_log2e : m_ref;
+        const float factor = pf_exp2(m_ref - m_new);
+        l_sum *= factor;
+        m_ref = m_new;
+        if (t > 0) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+            unsigned v[32];
+            pf_tmem_ld32(tO + c0, v);
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        // A: 16 tokens of P (K-major); B: the same 16 tokens of V, 128 bytes per token and slab
-        pf_mma(tmem + kPfKv, pf_desc(sP + kk * 32, 16, 1024), pf_desc(sV + kk * 2048, kPfKvSlab, 1024), idesc_o,
-               (t > 0 || kk > 0) ? 1u : 0u);
+            for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * factor);
+            pf_tmem_st32(tO + c0, v);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+        if (masked) pass(std::true_type{}); else pass(std::false_type{});
       }
-      pf_commit(bar_o);
+      l_sum += l_tile;
+      // P is visible to the tensor core's proxy, S has been read: hand both to the MMA warp
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      pf_arrive(my_p);
     }
-  }
-  if (!failed && !pf_wait(bar_o, (unsigned)(n_tiles - 1) & 1u)) failed = true;
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  if (failed && (tid & 31) == 0) atomicOr(P.status, INQ_STATUS_WAIT_TIMEOUT);
+    ok = ok && pf_wait(my_o, (unsigned)(n_x - 1) & 1u, abort_flag);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-  // ---- normalise and store this thread's row
-  {
+    // ---- normalise and store this thread's row
     const float inv = 1.f / l_sum;
-    const bool live = q0 + row < P.q_tokens;
-    QT* orow = (QT*)P.out + (long long)head * P.o_sh + (long long)(q0 + row) * P.o_st;
+    const bool live = ok && q_row < P.q_tokens;
+    QT* orow = (QT*)P.out + (long long)head * P.o_sh + (long long)q_row * P.o_st;
 #pragma unroll 1
     for (int c0 = 0; c0 < kPfTile; c0 += 32) {
       unsigned v[32];
@@ -317,7 +384,8 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_kernel(const PrefillPar
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0)
+  if (tid == 0 && *abort_flag) atomicOr(P.status, INQ_STATUS_WAIT_TIMEOUT);
+  if (warp == 8)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPfTmemCols) : "memory");
 }
 
@@ -372,10 +440,10 @@ extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t s
   P.q_sh = a->q_stride_h; P.q_st = a->q_stride_t; P.k_sh = a->k_stride_h; P.k_st = a->k_stride_t;
   P.v_sh = a->v_stride_h; P.v_st = a->v_stride_t; P.o_sh = a->o_stride_h; P.o_st = a->o_stride_t;
   P.q_heads = a->q_heads; P.kv_heads = a->kv_heads; P.q_tokens = a->q_tokens; P.kv_tokens = a->kv_tokens;
-  P.n_qtiles = (a->q_tokens + kPfTile - 1) / kPfTile;
+  P.n_qpairs = (a->q_tokens + kPfRows - 1) / kPfRows;
   P.scale_log2e = a->scale * 1.4426950408889634f;
   P.status = a->status;
-  const long long ctas = (long long)P.n_qtiles * P.q_heads;
+  const long long ctas = (long long)P.n_qpairs * P.q_heads;
   if (ctas > 0x7fffffffLL) return INQ_ERR_CAPACITY;
   cudaStream_t stream = (cudaStream_t)stream_;
   if (a->q_stride_h <= 0 || a->k_stride_h <= 0 || a->v_stride_h <= 0 || a->q_stride_t < 128 || a->k_stride_t < 128 ||
