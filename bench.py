@@ -278,12 +278,78 @@ def run_cuda(args):
         del batch, cache
         torch.cuda.empty_cache()
         line["split_kv"] = run_split_kv(args, torch, dist, device, world, rank)
+    if world == 1 and not args.no_prefill:
+        line["prefill"] = run_prefill(torch, device)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sample_layers=1)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_prefill(torch, device):
+    """Config 2, one of the 28 layers: the 32768-token prompt arrives as 16 chunks of 2048; every
+    chunk attends to the cache's history (dequantised by this library's kernels into dense
+    tensors) plus itself with the tcgen05 kernel, then is sealed into the packed cache.  Reports
+    the whole chunk loop through the public API and the attention kernel alone."""
+    import workloads
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.prefill import prefill_attention, prefill_chunk
+    chunk = 2048
+    k, v = workloads.make_kv_torch(4242, KV_HEADS, CONTEXT, device)
+    gen = torch.Generator(device=device).manual_seed(99)
+    q = torch.randn((1, Q_HEADS, CONTEXT, DIM), device=device, generator=gen).bfloat16()
+    cfg = CacheConfig(CodecConfig(donor_policy="min_error", donor_backend="triton"), block_size=BLOCK,
+                      residual_length=RESIDUAL, sink_tokens=SINK, value_bits=2, value_group_size=64, validate_positions=False)
+    scale = DIM ** -0.5
+    flops = sum(4 * Q_HEADS * DIM * (chunk * c0 + chunk * (chunk + 1) // 2) for c0 in range(0, CONTEXT, chunk))
+
+    def whole_layer():
+        cache = InQuantCache(cfg)
+        for c0 in range(0, CONTEXT, chunk):
+            prefill_chunk(cache, q[:, :, c0:c0 + chunk], k[:, :, c0:c0 + chunk], v[:, :, c0:c0 + chunk], 0, scale)
+    for _ in range(2):
+        whole_layer()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        whole_layer()
+    e1.record()
+    torch.cuda.synchronize()
+    layer_ms = e0.elapsed_time(e1) / 3
+    # the attention kernel alone on the last (largest) chunk: 2048 queries over 32768 keys
+    out = torch.empty((1, Q_HEADS, chunk, DIM), dtype=torch.bfloat16, device=device)
+    last_q = q[:, :, CONTEXT - chunk:]
+    for _ in range(3):
+        prefill_attention(last_q, k, v, scale, out=out)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(10):
+        prefill_attention(last_q, k, v, scale, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    kernel_ms = e0.elapsed_time(e1) / 10
+    kernel_flops = 4 * Q_HEADS * DIM * (chunk * (CONTEXT - chunk) + chunk * (chunk + 1) // 2)
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            peaks = json.load(fh)
+        burst, sustained, source = float(peaks["bf16_tflops"]), float(peaks["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        burst, sustained, source = 1590.0, 1400.0, "fallback"
+    kernel_tflops = kernel_flops / (kernel_ms * 1e-3) / 1e12
+    return {
+        "workload": "config 2, one layer: 16 chunks of 2048 tokens over the packed history (K4/V2), 28 query heads, bf16",
+        "layer_ms": round(layer_ms, 3), "layer_tflops": round(flops / (layer_ms * 1e-3) / 1e12, 1),
+        "layer_includes": "dequantising the history per chunk, the attention kernel, sealing the chunk",
+        "tokens_per_s_all_layers": round(CONTEXT / (layer_ms * 1e-3 * LAYERS), 1),
+        "roofline": {"bound": "tensor", "kernel": "prefill_kernel (2048 queries over 32768 keys)", "achieved": round(kernel_tflops, 1),
+                     "peak": burst, "unit": "TFLOP/s", "frac": round(kernel_tflops / burst, 4),
+                     "frac_of_sustained": round(kernel_tflops / sustained, 4), "peak_source": source,
+                     "us_per_launch": round(kernel_ms * 1e3, 1)},
+    }
 
 
 def run_split_kv(args, torch, dist, device, world, rank):
@@ -451,6 +517,7 @@ def main():
                         help="also time config 4: one request of this many tokens split by sequence over the ranks (0 = skip)")
     parser.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for profiler captures (default: the full 28)")
     parser.add_argument("--skip-e2e", action="store_true", help="profiler captures: skip the host-buffer leg")
+    parser.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill leg (config 2, one layer)")
     args = parser.parse_args()
     globals()["LAYERS"] = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup

@@ -1,25 +1,27 @@
 // Chunked-prefill attention on the 5th-generation tensor cores (tcgen05, accumulators in TMEM).
 //
 // One CTA owns 256 query tokens of one query head as two tiles of 128 rows (A and B) and walks
-// the visible keys and values in tiles of 64 tokens.  Ten warps, three roles:
+// the visible keys and values in tiles of 128 tokens.  Ten warps, three roles:
 //   * warps 0-3 / 4-7: softmax of tile A / tile B, one thread per query row.  A thread reads its
 //     row of S from tensor memory (tcgen05.ld), takes base-2 probabilities against a lazily
-//     raised reference maximum in one pass, and writes P in the model dtype to shared memory.
-//   * warp 8 (one lane): issues the contractions.  S = Q K^T (tcgen05.mma 128 x 64 x 128) and
-//     O += P V (128 x 128 x 64, V as an MN-major operand), fp32 accumulators in tensor memory.
-//     The order S_A, S_B, PV_A, S_A', PV_B, S_B', ... keeps the tensor core busy with one tile
-//     while the other tile's softmax runs.
+//     raised reference maximum and writes P in the model dtype back to tensor memory
+//     (tcgen05.st) over the columns of S it has consumed.
+//   * warp 8 (one lane): issues the contractions.  S = Q K^T (tcgen05.mma 128 x 128 x 128, both
+//     operands in shared memory) and O += P V (128 x 128 x 128, P from tensor memory, V as an
+//     MN-major shared-memory operand), fp32 accumulators in tensor memory.  The order S_A, S_B,
+//     PV_A, S_A', PV_B, S_B', ... keeps the tensor core busy with one tile while the other
+//     tile's softmax runs.
 //   * warp 9 (one lane): TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) for Q once and
-//     for the K and V tiles, four of each in flight.
+//     for the double-buffered K and V tiles.
 // All hand-overs are mbarriers; every wait is bounded and a wait that gives up raises an abort
 // flag that ends the other loops.  One CTA per SM (tensor-memory kernels are scheduled that way),
-// 224 KB of shared memory, 384 of the 512 TMEM columns.  Keys and values are dense tensors in
-// the model dtype: the dequantised packed history followed by the chunk's own tokens; query i
-// sees positions <= history + i.
+// 192 KB of shared memory, all 512 TMEM columns.  Keys and values are dense tensors in the model
+// dtype: the dequantised packed history followed by the chunk's own tokens; query i sees
+// positions <= history + i.
 //
-// Shared-memory operand tiles hold rows of 128 (Q, K, V) or 64 (P) 2-byte elements as slabs of 64
-// columns; inside a slab a row is 128 bytes and its 16-byte chunks are XOR-swizzled with the
-// row index modulo 8 (the 128-byte swizzle of the tensor-core descriptors).
+// Shared-memory operand tiles hold 128 rows of 128 2-byte elements as two slabs of 64 columns;
+// inside a slab a row is 128 bytes and its 16-byte chunks are XOR-swizzled with the row index
+// modulo 8 (the 128-byte swizzle of the tensor-core descriptors).
 #include <cuda.h>
 
 #include <type_traits>
@@ -29,18 +31,14 @@
 namespace inq {
 
 constexpr int kPfThreads = 320;              // 8 softmax warps, the MMA warp, the TMA warp
-constexpr int kPfTile = 128;                 // query rows per tile; also the head dimension
+constexpr int kPfTile = 128;                 // query rows per tile, KV tokens per tile, head dimension
 constexpr int kPfRows = 2 * kPfTile;         // query rows per CTA (tiles A and B)
-constexpr int kPfKv = 64;                    // KV tokens per tile
-constexpr int kPfQSlab = kPfTile * 128;      // 128 rows x 128 bytes
-constexpr int kPfKvSlab = kPfKv * 128;       // 64 rows x 128 bytes
-constexpr int kPfQBytes = 2 * kPfQSlab;      // one Q tile: two slabs (head dimension halves)
-constexpr int kPfKvBytes = 2 * kPfKvSlab;    // K or V tile
-constexpr int kPfPBytes = kPfQSlab;          // P tile: 128 rows x 64 tokens, one slab
-constexpr int kPfStages = 4;                 // K and V tiles in flight: the TMA latency spans several tiles
-constexpr int kPfTiles = 2 * kPfQBytes + 2 * kPfStages * kPfKvBytes + 2 * kPfPBytes;   // Q x2, K and V stages, P x2
-constexpr int kPfSmem = kPfTiles + 160;      // then the TMEM base address, the abort flag and 15 mbarriers
-constexpr int kPfTmemCols = 512;             // S_A 0..63, S_B 64..127, O_A 128..255, O_B 256..383
+constexpr int kPfSlab = kPfTile * 128;       // 128 rows x 128 bytes
+constexpr int kPfTileBytes = 2 * kPfSlab;    // one operand tile: two slabs (64-column halves)
+constexpr int kPfStages = 2;                 // K and V tiles in flight
+constexpr int kPfTiles = (2 + 2 * kPfStages) * kPfTileBytes;   // Q x2, K and V stages
+constexpr int kPfSmem = kPfTiles + 160;      // then the TMEM base address, the abort flag and 11 mbarriers
+constexpr int kPfTmemCols = 512;             // S_A 0..127, S_B 128..255 (P over their first 64), O_A 256..383, O_B 384..511
 constexpr float kPfNegBig = -1.0e30f;
 constexpr float kPfSlack = 4.f;              // the reference maximum may lag the true one by 2^4
 constexpr int kPfSpinLimit = 1 << 22;
@@ -72,6 +70,11 @@ __device__ __forceinline__ void pf_mma(unsigned tmem_d, unsigned long long da, u
                                        unsigned accumulate) {
   asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
                ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void pf_mma_ta(unsigned tmem_d, unsigned tmem_a, unsigned long long db, unsigned idesc,
+                                          unsigned accumulate) {
+  asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void pf_commit(unsigned mbar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
@@ -146,9 +149,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
   extern __shared__ __align__(1024) unsigned char pf_raw[];
   const unsigned smem0 = pf_smem(pf_raw);
   const unsigned sQ = smem0;                                  // tile A, then tile B
-  const unsigned sKb = smem0 + 2 * kPfQBytes;                 // K stages
-  const unsigned sVb = sKb + kPfStages * kPfKvBytes;          // V stages
-  const unsigned sPb = sVb + kPfStages * kPfKvBytes;          // P of tile A, then of tile B
+  const unsigned sKb = smem0 + 2 * kPfTileBytes;              // K stages
+  const unsigned sVb = sKb + kPfStages * kPfTileBytes;        // V stages
   unsigned* const tmem_base_p = (unsigned*)(pf_raw + kPfTiles);
   volatile int* const abort_flag = (volatile int*)(pf_raw + kPfTiles + 4);
   const unsigned bars = smem0 + kPfTiles + 16;
@@ -167,8 +169,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
   const int q0 = qp * kPfRows;
   const int hist = P.kv_tokens - P.q_tokens;
   // tiles each query tile needs: A ends at its last row's diagonal, B 128 tokens later
-  const int n_a = (min(P.kv_tokens, hist + q0 + kPfTile) + kPfKv - 1) / kPfKv;
-  const int n_b = (min(P.kv_tokens, hist + q0 + kPfRows) + kPfKv - 1) / kPfKv;
+  const int n_a = (min(P.kv_tokens, hist + q0 + kPfTile) + kPfTile - 1) / kPfTile;
+  const int n_b = (min(P.kv_tokens, hist + q0 + kPfRows) + kPfTile - 1) / kPfTile;
 
   if (tid == 0) {
     *abort_flag = 0;
@@ -200,22 +202,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
     // ================================================================ TMA warp
     if (lane == 0) {
       auto request_k = [&](int t) {
-        const unsigned bar = bar_k + 8 * (t % kPfStages), dst = sKb + (t % kPfStages) * kPfKvBytes;
-        pf_expect(bar, kPfKvBytes);
-        pf_tma(dst, &map_k, 0, t * kPfKv, kvh, bar);
-        pf_tma(dst + kPfKvSlab, &map_k, 64, t * kPfKv, kvh, bar);
+        const unsigned bar = bar_k + 8 * (t % kPfStages), dst = sKb + (t % kPfStages) * kPfTileBytes;
+        pf_expect(bar, kPfTileBytes);
+        pf_tma(dst, &map_k, 0, t * kPfTile, kvh, bar);
+        pf_tma(dst + kPfSlab, &map_k, 64, t * kPfTile, kvh, bar);
       };
       auto request_v = [&](int t) {
-        const unsigned bar = bar_v + 8 * (t % kPfStages), dst = sVb + (t % kPfStages) * kPfKvBytes;
-        pf_expect(bar, kPfKvBytes);
-        pf_tma(dst, &map_v, 0, t * kPfKv, kvh, bar);
-        pf_tma(dst + kPfKvSlab, &map_v, 64, t * kPfKv, kvh, bar);
+        const unsigned bar = bar_v + 8 * (t % kPfStages), dst = sVb + (t % kPfStages) * kPfTileBytes;
+        pf_expect(bar, kPfTileBytes);
+        pf_tma(dst, &map_v, 0, t * kPfTile, kvh, bar);
+        pf_tma(dst + kPfSlab, &map_v, 64, t * kPfTile, kvh, bar);
       };
-      pf_expect(bar_q, 2 * kPfQBytes);
+      pf_expect(bar_q, 2 * kPfTileBytes);
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
-        pf_tma(sQ + x * kPfQBytes, &map_q, 0, q0 + x * kPfTile, head, bar_q);
-        pf_tma(sQ + x * kPfQBytes + kPfQSlab, &map_q, 64, q0 + x * kPfTile, head, bar_q);
+        pf_tma(sQ + x * kPfTileBytes, &map_q, 0, q0 + x * kPfTile, head, bar_q);
+        pf_tma(sQ + x * kPfTileBytes + kPfSlab, &map_q, 64, q0 + x * kPfTile, head, bar_q);
       }
       for (int t = 0; t < kPfStages && t < n_b; ++t) {
         request_k(t);
@@ -233,25 +235,26 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
   } else if (warp == 8) {
     // ================================================================ MMA warp
     if (lane == 0) {
-      // instruction descriptors: fp32 accumulate, A/B in the model dtype, M = 128; N = 64 tokens
-      // for the scores, N = 128 channels for the output, whose value tile is an MN-major B operand
+      // instruction descriptors: fp32 accumulate, A/B in the model dtype, M = N = 128; the value
+      // tile is an MN-major B operand (tokens are its K dimension, stored row by row)
       const unsigned fmt = std::is_same<QT, __half>::value ? 0u : 1u;
-      const unsigned idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((unsigned)(kPfKv >> 3) << 17) | ((128u >> 4) << 24);
-      const unsigned idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+      const unsigned idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+      const unsigned idesc_o = idesc_s | (1u << 16);
       auto issue_s = [&](int x, int t) {      // S_x = Q_x K(t)^T
-        const unsigned q = sQ + x * kPfQBytes, k = sKb + (t % kPfStages) * kPfKvBytes;
+        const unsigned q = sQ + x * kPfTileBytes, k = sKb + (t % kPfStages) * kPfTileBytes;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          pf_mma(tmem + x * kPfKv, pf_desc(q + (kk >> 2) * kPfQSlab + (kk & 3) * 32, 16, 1024),
-                 pf_desc(k + (kk >> 2) * kPfKvSlab + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0);
+        for (int kk = 0; kk < 8; ++kk) {
+          const unsigned off = (kk >> 2) * kPfSlab + (kk & 3) * 32;
+          pf_mma(tmem + x * kPfTile, pf_desc(q + off, 16, 1024), pf_desc(k + off, 16, 1024), idesc_s, kk > 0);
+        }
         pf_commit(bar_s + 8 * x);
       };
-      auto issue_o = [&](int x, int t) {      // O_x += P_x V(t)
-        const unsigned pp = sPb + x * kPfPBytes, v = sVb + (t % kPfStages) * kPfKvBytes;
+      auto issue_o = [&](int x, int t) {      // O_x += P_x V(t): 16 tokens per step = 8 columns of packed P
+        const unsigned v = sVb + (t % kPfStages) * kPfTileBytes;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          pf_mma(tmem + 2 * kPfKv + x * kPfTile, pf_desc(pp + kk * 32, 16, 1024), pf_desc(v + kk * 2048, kPfKvSlab, 1024),
-                 idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk)
+          pf_mma_ta(tmem + 2 * kPfTile + x * kPfTile, tmem + x * kPfTile + kk * 8, pf_desc(v + kk * 2048, kPfSlab, 1024), idesc_o,
+                    (t > 0 || kk > 0) ? 1u : 0u);
         pf_commit(bar_o + 8 * x);
       };
       bool ok = pf_wait(bar_q, 0, abort_flag) && pf_wait(bar_k, 0, abort_flag);
@@ -288,53 +291,37 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
     const int q_pos = hist + q_row;                // keys at positions <= q_pos are visible
     const int diag0 = hist + q0 + x * kPfTile;     // first row's diagonal: tiles reaching beyond it need masks
     const unsigned lane_field = (unsigned)((warp & 3) * 32) << 16;
-    const unsigned tS = tmem + lane_field + x * kPfKv, tO = tmem + lane_field + 2 * kPfKv + x * kPfTile;
-    const unsigned prow = sPb + x * kPfPBytes + (row >> 3) * 1024 + (row & 7) * 128;
+    const unsigned tS = tmem + lane_field + x * kPfTile, tO = tmem + lane_field + 2 * kPfTile + x * kPfTile;
     const unsigned my_s = bar_s + 8 * x, my_p = bar_p + 8 * x, my_o = bar_o + 8 * x;
     float m_ref = kPfNegBig, l_sum = 0.f;
     bool ok = true;
 
     for (int t = 0; t < n_x; ++t) {
-      const int kv0 = t * kPfKv;
+      const int kv0 = t * kPfTile;
       // S(t) is complete; the contractions run in issue order, so PV(t-1) is complete as well:
-      // P may be overwritten and O may be rescaled
+      // the columns of P may be overwritten by S and O may be rescaled
       if (!pf_wait(my_s, (unsigned)t & 1u, abort_flag)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool masked = kv0 + kPfKv - 1 > diag0;
-      float smax, l_tile;
-      auto pass = [&](auto masked_tag) {
-        constexpr bool kMasked = decltype(masked_tag)::value;
-        smax = kPfNegBig;
-        l_tile = 0.f;
+      const bool masked = kv0 + kPfTile - 1 > diag0;
+      // ---- row maximum
+      float smax = kPfNegBig;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kPfKv; c0 += 32) {
-          unsigned v[32];
-          pf_tmem_ld32(tS + c0, v);
-          float p[32];
+      for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+        unsigned v[32];
+        pf_tmem_ld32(tS + c0, v);
+        if (masked) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const float sv = __uint_as_float(v[c]);
-            const bool visible = !kMasked || kv0 + c0 + c <= q_pos;
-            if (visible) smax = fmaxf(smax, sv);
-            const float e = pf_exp2(fmaf(sv, P.scale_log2e, -m_ref));
-            p[c] = visible ? e : 0.f;
-            l_tile += p[c];
-          }
+          for (int c = 0; c < 32; ++c)
+            if (kv0 + c0 + c <= q_pos) smax = fmaxf(smax, __uint_as_float(v[c]));
+        } else {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const int chunk = (c0 >> 3) + q4;
-            const unsigned dst = prow + ((chunk ^ (row & 7)) << 4);
-            const unsigned w0 = pf_pack2<QT>(p[8 * q4 + 0], p[8 * q4 + 1]), w1 = pf_pack2<QT>(p[8 * q4 + 2], p[8 * q4 + 3]);
-            const unsigned w2 = pf_pack2<QT>(p[8 * q4 + 4], p[8 * q4 + 5]), w3 = pf_pack2<QT>(p[8 * q4 + 6], p[8 * q4 + 7]);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-          }
+          for (int c = 0; c < 32; ++c) smax = fmaxf(smax, __uint_as_float(v[c]));
         }
-      };
-      if (masked) pass(std::true_type{}); else pass(std::false_type{});
+      }
       const bool raise = smax * P.scale_log2e > m_ref + kPfSlack;
       if (__any_sync(0xffffffffu, raise)) {
         // rare after the first tile: bring the running sum and the output accumulator to the new
-        // reference maximum, then take the probabilities again
+        // reference maximum
         const float m_new = raise ? smax * P.scale_log2e : m_ref;
         const float factor = pf_exp2(m_ref - m_new);
         l_sum *= factor;
@@ -348,13 +335,34 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
             for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * factor);
             pf_tmem_st32(tO + c0, v);
           }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
-        if (masked) pass(std::true_type{}); else pass(std::false_type{});
       }
-      l_sum += l_tile;
-      // P is visible to the tensor core's proxy, S has been read: hand both to the MMA warp
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // ---- probabilities, 64 tokens at a time: two loads of S, one store of packed P over the
+      //      columns of S that have been consumed
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        unsigned packed[32];
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          const int c0 = half * 64 + sub * 32;
+          unsigned v[32];
+          pf_tmem_ld32(tS + c0, v);
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            float e0 = pf_exp2(fmaf(__uint_as_float(v[c]), P.scale_log2e, -m_ref));
+            float e1 = pf_exp2(fmaf(__uint_as_float(v[c + 1]), P.scale_log2e, -m_ref));
+            if (masked) {
+              if (kv0 + c0 + c > q_pos) e0 = 0.f;
+              if (kv0 + c0 + c + 1 > q_pos) e1 = 0.f;
+            }
+            l_sum += e0 + e1;
+            packed[sub * 16 + (c >> 1)] = pf_pack2<QT>(e0, e1);
+          }
+        }
+        pf_tmem_st32(tS + half * 32, packed);
+      }
+      // P is in tensor memory, S has been read: hand both to the MMA warp
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       pf_arrive(my_p);
     }
@@ -451,8 +459,8 @@ extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t s
     return INQ_ERR_ARGUMENT;
   CUtensorMap map_q, map_k, map_v;
   if (!make_map(&map_q, a->q, a->dtype, a->q_tokens, a->q_heads, a->q_stride_t, a->q_stride_h, kPfTile) ||
-      !make_map(&map_k, a->k, a->dtype, a->kv_tokens, a->kv_heads, a->k_stride_t, a->k_stride_h, kPfKv) ||
-      !make_map(&map_v, a->v, a->dtype, a->kv_tokens, a->kv_heads, a->v_stride_t, a->v_stride_h, kPfKv))
+      !make_map(&map_k, a->k, a->dtype, a->kv_tokens, a->kv_heads, a->k_stride_t, a->k_stride_h, kPfTile) ||
+      !make_map(&map_v, a->v, a->dtype, a->kv_tokens, a->kv_heads, a->v_stride_t, a->v_stride_h, kPfTile))
     return INQ_ERR_ARGUMENT;
   if (a->dtype == INQ_F16) {
     INQ_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
