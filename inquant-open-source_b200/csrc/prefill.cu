@@ -3,9 +3,9 @@
 // One CTA owns 256 query tokens of one query head as two tiles of 128 rows (A and B) and walks
 // the visible keys and values in tiles of 128 tokens.  Ten warps, three roles:
 //   * warps 0-3 / 4-7: softmax of tile A / tile B, one thread per query row.  A thread reads its
-//     row of S from tensor memory (tcgen05.ld), takes base-2 probabilities against a lazily
-//     raised reference maximum and writes P in the model dtype back to tensor memory
-//     (tcgen05.st) over the columns of S it has consumed.
+//     row of S from tensor memory (tcgen05.ld) once, takes base-2 probabilities against a lazily
+//     raised reference maximum (the pass is repeated in the rare case that the maximum has to
+//     rise) and writes P in the model dtype back to tensor memory (tcgen05.st) over S.
 //   * warp 8 (one lane): issues the contractions.  S = Q K^T (tcgen05.mma 128 x 128 x 128, both
 //     operands in shared memory) and O += P V (128 x 128 x 128, P from tensor memory, V as an
 //     MN-major shared-memory operand), fp32 accumulators in tensor memory.  The order S_A, S_B,
@@ -303,25 +303,41 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
       if (!pf_wait(my_s, (unsigned)t & 1u, abort_flag)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool masked = kv0 + kPfTile - 1 > diag0;
-      // ---- row maximum
-      float smax = kPfNegBig;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kPfTile; c0 += 32) {
-        unsigned v[32];
-        pf_tmem_ld32(tS + c0, v);
-        if (masked) {
+      // ---- one pass over S: probabilities against the running reference maximum are packed
+      //      into registers while the row maximum is tracked; P is stored over S only afterwards,
+      //      so the rare case of a maximum that has to be raised can simply take the pass again
+      unsigned packed[64];
+      float smax, l_tile;
+      auto pass = [&](auto masked_tag) {
+        constexpr bool kMasked = decltype(masked_tag)::value;
+        smax = kPfNegBig;
+        l_tile = 0.f;
 #pragma unroll
-          for (int c = 0; c < 32; ++c)
-            if (kv0 + c0 + c <= q_pos) smax = fmaxf(smax, __uint_as_float(v[c]));
-        } else {
+        for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+          unsigned v[32];
+          pf_tmem_ld32(tS + c0, v);
 #pragma unroll
-          for (int c = 0; c < 32; ++c) smax = fmaxf(smax, __uint_as_float(v[c]));
+          for (int c = 0; c < 32; c += 2) {
+            const float s0 = __uint_as_float(v[c]), s1 = __uint_as_float(v[c + 1]);
+            float e0 = pf_exp2(fmaf(s0, P.scale_log2e, -m_ref));
+            float e1 = pf_exp2(fmaf(s1, P.scale_log2e, -m_ref));
+            if (kMasked) {
+              const bool vis0 = kv0 + c0 + c <= q_pos, vis1 = kv0 + c0 + c + 1 <= q_pos;
+              if (vis0) smax = fmaxf(smax, s0); else e0 = 0.f;
+              if (vis1) smax = fmaxf(smax, s1); else e1 = 0.f;
+            } else {
+              smax = fmaxf(smax, fmaxf(s0, s1));
+            }
+            l_tile += e0 + e1;
+            packed[(c0 + c) >> 1] = pf_pack2<QT>(e0, e1);
+          }
         }
-      }
+      };
+      if (masked) pass(std::true_type{}); else pass(std::false_type{});
       const bool raise = smax * P.scale_log2e > m_ref + kPfSlack;
       if (__any_sync(0xffffffffu, raise)) {
         // rare after the first tile: bring the running sum and the output accumulator to the new
-        // reference maximum
+        // reference maximum, then take the probabilities again
         const float m_new = raise ? smax * P.scale_log2e : m_ref;
         const float factor = pf_exp2(m_ref - m_new);
         l_sum *= factor;
@@ -336,30 +352,18 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
             pf_tmem_st32(tO + c0, v);
           }
         }
+        if (masked) pass(std::true_type{}); else pass(std::false_type{});
       }
-      // ---- probabilities, 64 tokens at a time: two loads of S, one store of packed P over the
-      //      columns of S that have been consumed
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        unsigned packed[32];
+      l_sum += l_tile;
+      {
+        unsigned lo[32], hi[32];
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-          const int c0 = half * 64 + sub * 32;
-          unsigned v[32];
-          pf_tmem_ld32(tS + c0, v);
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            float e0 = pf_exp2(fmaf(__uint_as_float(v[c]), P.scale_log2e, -m_ref));
-            float e1 = pf_exp2(fmaf(__uint_as_float(v[c + 1]), P.scale_log2e, -m_ref));
-            if (masked) {
-              if (kv0 + c0 + c > q_pos) e0 = 0.f;
-              if (kv0 + c0 + c + 1 > q_pos) e1 = 0.f;
-            }
-            l_sum += e0 + e1;
-            packed[sub * 16 + (c >> 1)] = pf_pack2<QT>(e0, e1);
-          }
+        for (int c = 0; c < 32; ++c) {
+          lo[c] = packed[c];
+          hi[c] = packed[32 + c];
         }
-        pf_tmem_st32(tS + half * 32, packed);
+        pf_tmem_st32(tS, lo);
+        pf_tmem_st32(tS + 32, hi);
       }
       // P is in tensor memory, S has been read: hand both to the MMA warp
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
