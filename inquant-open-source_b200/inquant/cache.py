@@ -132,7 +132,10 @@ def _quantize_temporal_blocks(tensor, block_count, block_size, config):
     # x 5 fields would cost more host time than the encoder launch itself)
     fields = [packed.payload.split(1), packed.scales.split(1), packed.salient_channels.split(1),
               packed.donor_channels.split(1), packed.padding.split(1)]
-    return [PackedTensor(*views, shape=shape, original_dtype=tensor.dtype) for views in zip(*fields)]
+    blocks = [PackedTensor(*views, shape=shape, original_dtype=tensor.dtype) for views in zip(*fields)]
+    for index, block in enumerate(blocks):
+        object.__setattr__(block, "_arena", (packed, index))   # lets materialize() dequantise the whole launch at once
+    return blocks
 
 
 class InQuantCache(_HFCache):
@@ -390,11 +393,39 @@ class InQuantCache(_HFCache):
         layer = self._layers[layer_idx]
 
         def restore(sink, blocks, tail):
-            pieces = [] if sink is None else [sink]
-            pieces.extend(block.dequantize(dtype=layer.dtype) for block in blocks)
-            if tail is not None and tail.shape[2]:
-                pieces.append(tail)
-            return torch.cat(pieces, dim=2)
+            # blocks sealed by one call share an encoder arena: each arena is dequantised by one
+            # launch straight into its place in the output instead of block by block
+            _, heads, _, channels = layer.shape
+            sink_tokens = 0 if sink is None else sink.shape[2]
+            tail_tokens = 0 if tail is None else tail.shape[2]
+            packed_tokens = sum(block.shape[2] for block in blocks)
+            out = torch.empty((1, heads, sink_tokens + packed_tokens + tail_tokens, channels),
+                              dtype=layer.dtype, device=layer.device)
+            if sink_tokens:
+                out[:, :, :sink_tokens].copy_(sink)
+            position, index = sink_tokens, 0
+            while index < len(blocks):
+                arena = getattr(blocks[index], "_arena", None)
+                run = 1
+                if arena is not None and arena[1] == 0:
+                    while index + run < len(blocks):
+                        other = getattr(blocks[index + run], "_arena", None)
+                        if other is None or other[0] is not arena[0] or other[1] != run:
+                            break
+                        run += 1
+                tokens = blocks[index].shape[2]
+                if run > 1 and run == arena[0].shape[0]:
+                    dense = arena[0].dequantize(dtype=layer.dtype)            # [run, heads, tokens, channels]
+                    out[0, :, position:position + run * tokens].view(heads, run, tokens, channels).copy_(
+                        dense.permute(1, 0, 2, 3))
+                else:
+                    run = 1
+                    out[:, :, position:position + tokens].copy_(blocks[index].dequantize(dtype=layer.dtype))
+                position += run * tokens
+                index += run
+            if tail_tokens:
+                out[:, :, position:].copy_(tail)
+            return out
 
         return (
             restore(layer.sink_key, layer.key_blocks, layer.residual_key),

@@ -107,5 +107,8 @@ def quantize_value_blocks(tensor, block_count, block_size, bits, group_size):
     packed = quantize_values(blocked, bits, group_size)
     shape = (1, heads, block_size, channels)
     fields = [packed.payload.split(1), packed.scales.split(1), packed.offsets.split(1)]
-    return [PackedValues(*views, shape=shape, original_dtype=tensor.dtype, bits=bits, group_size=group_size)
-            for views in zip(*fields)]
+    blocks = [PackedValues(*views, shape=shape, original_dtype=tensor.dtype, bits=bits, group_size=group_size)
+              for views in zip(*fields)]
+    for index, block in enumerate(blocks):
+        object.__setattr__(block, "_arena", (packed, index))   # lets InQuantCache.materialize dequantise the whole launch at once
+    return blocks
