@@ -280,6 +280,9 @@ def run_cuda(args):
         line["split_kv"] = run_split_kv(args, torch, dist, device, world, rank)
     if world == 1 and not args.no_prefill:
         line["prefill"] = run_prefill(torch, device)
+    if not args.no_paged_batch:
+        torch.cuda.empty_cache()
+        line["paged_batch"] = run_paged_batch(torch, dist, device, world, rank)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sample_layers=1)
     if rank == 0:
@@ -350,6 +353,79 @@ def run_prefill(torch, device):
                      "frac_of_sustained": round(kernel_tflops / sustained, 4), "peak_source": source,
                      "us_per_launch": round(kernel_ms * 1e3, 1)},
     }
+
+
+def run_paged_batch(torch, dist, device, world, rank):
+    """Config 3: Mistral-7B-shaped batched paged decode (vLLM-extension page layout, block 16):
+    32 layers x 8 KV heads x 128, 32 query heads, 16 requests with seeded context lengths uniform
+    in 4096..32768, pages at shuffled physical ids, requests dealt round-robin to the ranks with no
+    collective.  One step = every layer of every local request in one decode launch.  A request's
+    pages are sealed once by the page-packing kernels and copied to the other layers' (distinct)
+    physical pages, so every layer still streams its own memory."""
+    import numpy as np
+    import workloads
+    from inquant.batched import DecodeBatch, PagedSequenceState
+    from inquant_vllm.layout import PageLayout, pack_pages_into
+    layers, heads, q_heads, block, requests = 32, 8, 32, 16, 16
+    layout = PageLayout(block, heads)
+    lengths = [int(x) for x in np.random.default_rng(2024).integers(4096, 32769, size=requests)]
+    mine = [i for i in range(requests) if i % world == rank]
+    pages_of = {i: lengths[i] // block for i in mine}
+    total_pages = layers * sum(pages_of.values())
+    pool = torch.empty((total_pages + 8, layout.page_bytes), dtype=torch.uint8, device=device)
+    order = torch.randperm(total_pages + 8, generator=torch.Generator().manual_seed(7 + rank)).to(device=device, dtype=torch.int32)
+    cursor, seqs = 0, []
+    for i in mine:
+        n, pages = lengths[i], pages_of[i]
+        k, v = workloads.make_kv_torch(9000 + i, heads, n, device)
+        tail, sink = n % block, min(4, n)
+        dense = torch.zeros((2, heads, block + 4, DIM), dtype=torch.bfloat16, device=device)
+        dense[0, :, :sink], dense[1, :, :sink] = k[0, :, :sink], v[0, :, :sink]
+        if tail:
+            dense[0, :, 4:4 + tail], dense[1, :, 4:4 + tail] = k[0, :, n - tail:], v[0, :, n - tail:]
+        kt = k[0, :, :pages * block].reshape(heads, pages, block, DIM).permute(1, 0, 2, 3).contiguous()
+        vt = v[0, :, :pages * block].reshape(heads, pages, block, DIM).permute(1, 0, 2, 3).contiguous()
+        first = order[cursor:cursor + pages].contiguous()
+        pack_pages_into(kt, vt, layout, pool, first)
+        for layer in range(layers):
+            ids = order[cursor:cursor + pages].contiguous()
+            cursor += pages
+            if layer:
+                pool[ids.long()] = pool[first.long()]
+            seqs.append(PagedSequenceState(pool, ids, pages, dense.clone(), tail, sink, layout))
+        del k, v, kt, vt
+    batch = DecodeBatch(seqs, q_heads, torch.bfloat16)
+    gen = torch.Generator(device=device).manual_seed(31 + rank)
+    batch.queries.copy_(torch.randn(batch.queries.shape, device=device, generator=gen).to(torch.bfloat16))
+    for _ in range(3):
+        batch.attend()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    steps = 20
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        batch._launch_attend()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    total_bytes = batch.algorithmic_bytes()["total"]
+    if world > 1:
+        t = torch.tensor([ms, float(total_bytes)], device=device, dtype=torch.float64)
+        worst = t.clone()
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, total_bytes = float(worst[0].item()), float(t[1].item())
+    peak, _ = measured_peak_gbs()
+    gbs = total_bytes / (ms * 1e-3) / 1e9
+    return {"workload": "config 3: 16 requests x 32 layers, 8 KV heads, 32 query heads, contexts 4096..32768, pages of 16 tokens",
+            "requests": requests, "context_tokens": sum(lengths), "us_per_step": round(ms * 1e3, 1),
+            "decode_tokens_per_s": round(requests / (ms * 1e-3), 1), "aggregate_gbs": round(gbs, 1),
+            "per_gpu_hbm_frac": round(gbs / world / peak, 4), "algorithmic_bytes_per_step": int(total_bytes),
+            "sharding": "requests round-robin over ranks, no collective", "steps": steps}
 
 
 def run_split_kv(args, torch, dist, device, world, rank):
@@ -518,6 +594,7 @@ def main():
     parser.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for profiler captures (default: the full 28)")
     parser.add_argument("--skip-e2e", action="store_true", help="profiler captures: skip the host-buffer leg")
     parser.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill leg (config 2, one layer)")
+    parser.add_argument("--no-paged-batch", action="store_true", help="skip the batched paged decode leg (config 3)")
     args = parser.parse_args()
     globals()["LAYERS"] = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup
