@@ -213,6 +213,36 @@ int inq_decode_attention_noalloc(const inq_decode_args_t* args /* host */, inq_s
  * across ranks after an all-gather. */
 int inq_merge_partials(const float* records, int32_t n_parts, int64_t n_rows, void* out, int32_t out_dtype,
                        inq_stream_t stream);
+/* Packed decode attention for codec variants outside the K4/V2 preset (slower, general): values
+ * stored as InQuant packed tensors (value_kind 1: table columns 3..5 are payload, f32 scales, f32
+ * padding, with an int8 role map like the keys') or as 2/4-bit groups of `value_group` channels
+ * (value_kind 0: payload, f16 scales, f16 offsets); fp32, fp16 or bf16 queries with sink/tail in
+ * the same dtype; even head dimensions up to 256.  One sequence, table layout as in
+ * inq_decode_seq_t.  `partials` is scratch of inq_decode_generic_workspace_floats floats.
+ * Replaces: triton_attention.py:67-181 for `value_bits=None`, V4, value groups of 32/128 and
+ * fp32 queries (triton_attention.py:122-124, tests/test_triton_attention.py:23-25). */
+typedef struct {
+  const void* q;              /* [kv_heads * q_per_kv][head_dim] rows, `q_stride_h` elements apart */
+  void* out;                  /* [kv_heads * q_per_kv][head_dim], contiguous */
+  int64_t q_stride_h;
+  const int64_t* table;       /* device: [n_blocks][6] pointers */
+  const int8_t* key_roles;    /* device: [n_blocks][kv_heads][head_dim] */
+  const int8_t* value_roles;  /* device, value_kind 1 only */
+  const void *sink_key, *sink_value, *tail_key, *tail_value;
+  int64_t sink_key_stride_h, sink_key_stride_t, sink_value_stride_h, sink_value_stride_t;
+  int64_t tail_key_stride_h, tail_key_stride_t, tail_value_stride_h, tail_value_stride_t;
+  int32_t n_blocks, sink_tokens, tail_tokens;
+  int32_t kv_heads, q_per_kv, block_tokens, head_dim, key_pad, value_pad;
+  int32_t value_kind, value_bits, value_group;
+  int32_t dtype;              /* INQ_F32 / INQ_F16 / INQ_BF16: query, output, sink and tail */
+  float scale;
+  float* partials;
+  int64_t partials_floats;
+} inq_decode_generic_args_t;
+int inq_decode_generic(const inq_decode_generic_args_t* args /* host */, inq_stream_t stream);
+int64_t inq_decode_generic_workspace_floats(int32_t q_heads, int32_t n_blocks, int32_t sink_tokens,
+                                            int32_t tail_tokens, int32_t head_dim);
+
 /* Chunked-prefill attention on tcgen05 tensor cores with TMEM accumulators: causal attention of
  * `q_tokens` new query tokens over `kv_tokens` keys and values, where the last `q_tokens` rows of
  * k/v are the chunk's own tokens and the rows before them the history (for a packed cache: the

@@ -18,6 +18,7 @@ SOURCES = {
     "decode.cu": ["-DINQ_DECODE_SUB=" + os.environ.get("INQ_DECODE_SUB", "2")],
     "append.cu": [],
     "prefill.cu": [],
+    "decode_generic.cu": [],
 }
 
 

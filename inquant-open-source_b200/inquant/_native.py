@@ -72,6 +72,21 @@ class AppendArgs(ctypes.Structure):
                 ("sink_position", c_int32), ("heads", c_int32), ("row_bytes", c_int32), ("status", c_void_p)]
 
 
+class GenericDecodeArgs(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("out", c_void_p), ("q_stride_h", c_int64), ("table", c_void_p),
+                ("key_roles", c_void_p), ("value_roles", c_void_p),
+                ("sink_key", c_void_p), ("sink_value", c_void_p), ("tail_key", c_void_p), ("tail_value", c_void_p),
+                ("sink_key_stride_h", c_int64), ("sink_key_stride_t", c_int64),
+                ("sink_value_stride_h", c_int64), ("sink_value_stride_t", c_int64),
+                ("tail_key_stride_h", c_int64), ("tail_key_stride_t", c_int64),
+                ("tail_value_stride_h", c_int64), ("tail_value_stride_t", c_int64),
+                ("n_blocks", c_int32), ("sink_tokens", c_int32), ("tail_tokens", c_int32),
+                ("kv_heads", c_int32), ("q_per_kv", c_int32), ("block_tokens", c_int32), ("head_dim", c_int32),
+                ("key_pad", c_int32), ("value_pad", c_int32),
+                ("value_kind", c_int32), ("value_bits", c_int32), ("value_group", c_int32),
+                ("dtype", c_int32), ("scale", ctypes.c_float), ("partials", c_void_p), ("partials_floats", c_int64)]
+
+
 class PrefillArgs(ctypes.Structure):
     _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p),
                 ("q_stride_h", c_int64), ("q_stride_t", c_int64), ("k_stride_h", c_int64), ("k_stride_t", c_int64),
@@ -97,6 +112,8 @@ def library() -> ctypes.CDLL:
         lib.inq_last_error.restype = ctypes.c_char_p
         lib.inq_decode_workspace_floats.restype = c_int64
         lib.inq_decode_workspace_floats.argtypes = [c_int32, c_int64]
+        lib.inq_decode_generic_workspace_floats.restype = c_int64
+        lib.inq_decode_generic_workspace_floats.argtypes = [c_int32, c_int32, c_int32, c_int32, c_int32]
         lib.inq_decode_units.restype = c_int64
         lib.inq_decode_units.argtypes = [c_int32, c_int32]
         for name in EXPORTS:
@@ -113,7 +130,7 @@ EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
     "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
     "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
-    "inq_prefill_attention",
+    "inq_prefill_attention", "inq_decode_generic", "inq_decode_generic_workspace_floats",
 )
 
 
@@ -130,6 +147,7 @@ SIGNATURES = {
     "inq_decode_attention_noalloc": [_P, _P],
     "inq_merge_partials": [_P, _I, _L, _P, _I, _P],
     "inq_prefill_attention": [_P, _P],
+    "inq_decode_generic": [_P, _P],
     "inq_append_token": [_P, _P],
     "inq_append_token_batch": [_P, _I, _P, _P],
 }

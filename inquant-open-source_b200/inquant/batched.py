@@ -81,6 +81,8 @@ class DecodeBatch:
             self.kv_heads = self.layout.heads
         else:
             with_blocks = [s.decode_state for s in sequences if s.decode_state.key_blocks]
+            if any(not state._preset for state in with_blocks):
+                raise NotImplementedError("batched decode runs the K4/V2 preset (2-bit values in groups of 64) only")
             first = with_blocks[0] if with_blocks else sequences[0].decode_state
             self.device = sequences[0].tail_key_buffer.device
             self.kv_heads = sequences[0].tail_key_buffer.shape[1]

@@ -77,6 +77,9 @@ class PackedDecodeState:
         self._salient = 0
         self._value_bits = 0
         self._value_group = 64
+        self._value_salient = 0
+        self._inquant_values = False
+        self._preset = True
         self._capacity = 0
         self._stream_identity = None
         self.extend(key_blocks, value_blocks)
@@ -106,17 +109,26 @@ class PackedDecodeState:
         for block in key_blocks:
             if not isinstance(block, PackedTensor) or block.shape != first.shape or block.salient_channels.shape[-1] != self._salient:
                 raise ValueError("All packed K/V blocks must share shape and salient-channel count")
-        if not isinstance(value_blocks[0], PackedValues):
-            raise NotImplementedError("This build decodes values stored as PackedValues (value_bits=2); "
-                                      "InQuant-coded values are not built")
-        self._value_bits = value_blocks[0].bits
-        self._value_group = value_blocks[0].group_size
-        if (self._value_bits, self._value_group) != (2, 64):
-            raise NotImplementedError("This build decodes 2-bit values with group size 64 only")
+        # the preset (2-bit values in groups of 64) runs the streaming kernel; every other value
+        # codec the reference accepts runs the general kernel
+        self._inquant_values = isinstance(value_blocks[0], PackedTensor)
+        if self._inquant_values:
+            self._value_bits, self._value_group = 0, 64
+            self._value_salient = value_blocks[0].salient_channels.shape[-1]
+        elif isinstance(value_blocks[0], PackedValues):
+            self._value_bits = value_blocks[0].bits
+            self._value_group = value_blocks[0].group_size
+            self._value_salient = 0
+        else:
+            raise ValueError("Value blocks must be PackedValues or PackedTensor")
+        self._preset = not self._inquant_values and (self._value_bits, self._value_group) == (2, 64)
         for block in value_blocks:
             if block.shape != first.shape:
                 raise ValueError("All packed blocks must share shape")
-            if not isinstance(block, PackedValues) or (block.bits, block.group_size) != (self._value_bits, self._value_group):
+            if self._inquant_values:
+                if not isinstance(block, PackedTensor) or block.salient_channels.shape[-1] != self._value_salient:
+                    raise ValueError("All V blocks must share the same quantizer")
+            elif not isinstance(block, PackedValues) or (block.bits, block.group_size) != (self._value_bits, self._value_group):
                 raise ValueError("All V blocks must share the same quantizer")
         for block in (*key_blocks, *value_blocks):
             if any(t.device != self._device for t in block.tensors.values()):
@@ -127,30 +139,36 @@ class PackedDecodeState:
                 if not t.is_contiguous():
                     raise ValueError("Packed block tensors must be contiguous")
         pointers = [[k.payload.data_ptr(), k.scales.data_ptr(), k.padding.data_ptr(),
-                     v.payload.data_ptr(), v.scales.data_ptr(), v.offsets.data_ptr()]
+                     v.payload.data_ptr(), v.scales.data_ptr(),
+                     (v.padding if self._inquant_values else v.offsets).data_ptr()]
                     for k, v in zip(new_keys, new_values)]
         count = len(key_blocks)
         if count > self._capacity:
             capacity = count if not self._capacity else max(count, min(self._capacity * 2, count + 7))
             tables = torch.empty((capacity, 6), dtype=torch.int64, device=self._device)
             key_map = torch.empty((capacity, self._kv_heads, 128), dtype=torch.int8, device=self._device)
-            value_map = torch.empty((0,), dtype=torch.int8, device=self._device)
+            value_map = torch.empty((capacity, self._kv_heads, 128) if self._inquant_values else (0,),
+                                    dtype=torch.int8, device=self._device)
             if old_count:
                 tables[:old_count].copy_(self._tables[:old_count])
                 key_map[:old_count].copy_(self._key_map[:old_count])
+                if self._inquant_values:
+                    value_map[:old_count].copy_(self._value_map[:old_count])
             self._tables, self._key_map, self._value_map = tables, key_map, value_map
             self._capacity = capacity
         self._tables[old_count:count].copy_(torch.tensor(pointers, dtype=torch.int64).to(self._device, non_blocking=False))
-        self._write_maps(self._key_map[old_count:count], new_keys)
+        self._write_maps(self._key_map[old_count:count], new_keys, self._salient)
+        if self._inquant_values:
+            self._write_maps(self._value_map[old_count:count], new_values, self._value_salient)
         self.key_blocks, self.value_blocks = tuple(key_blocks), tuple(value_blocks)
 
-    def _write_maps(self, result, blocks):
+    def _write_maps(self, result, blocks, count):
         """Roles: donor channel 0..127 for a salient channel, -1 normal, -2-i for the i-th donor
         (C ABI ``inq_build_roles``; reference ``triton_attention.py:301-309``)."""
         sources = torch.cat([block.salient_channels for block in blocks], dim=0).contiguous()
         donors = torch.cat([block.donor_channels for block in blocks], dim=0).contiguous()
         rows = len(blocks) * self._kv_heads
-        rc = N.library().inq_build_roles(N.pointer(sources), N.pointer(donors), 0, rows, 128, self._salient,
+        rc = N.library().inq_build_roles(N.pointer(sources), N.pointer(donors), 0, rows, 128, count,
                                          N.pointer(result), 1, N.stream_pointer(self._device))
         N.check(rc, "inq_build_roles")
         return result
@@ -167,8 +185,6 @@ class PackedDecodeState:
             raise ValueError("query must have shape [1, query_heads, 1, 128]")
         if query.device.type != "cuda" or query.dtype not in (torch.float16, torch.bfloat16, torch.float32):
             raise ValueError("query must be a CUDA FP16, BF16 or FP32 tensor")
-        if query.dtype == torch.float32:
-            raise NotImplementedError("This build decodes fp16 and bf16 queries; fp32 queries are not built")
         if query.stride(-1) != 1:
             raise ValueError("query head dimension must be contiguous")
         if self._device is not None and query.device != self._device:
@@ -210,6 +226,9 @@ class PackedDecodeState:
         if self._stream_identity is not None and self._stream_identity != identity:
             raise RuntimeError("Packed decode state requires one CUDA stream per state")
         q_per_kv = query.shape[1] // kv_heads
+        if query.dtype == torch.float32 or (n_blocks and not self._preset):
+            return self._decode_general(query, kv_heads, q_per_kv, n_blocks, sink_key, sink_value, sink_t,
+                                        residual_key, residual_value, residual_t, scale)
         tiles = (q_per_kv + 7) // 8
         pairs = kv_heads * tiles
         records = workspace_floats(pairs, pairs * pair_units(n_blocks, self._packed_tokens)) // N.RECORD_FLOATS
@@ -251,6 +270,44 @@ class PackedDecodeState:
         args.status = N.status_word(query.device).data_ptr()
         rc = N.library().inq_decode_attention(N.ctypes.byref(args), N.stream_pointer(query.device))
         N.check(rc, "inq_decode_attention")
+        return output
+
+
+    def _decode_general(self, query, kv_heads, q_per_kv, n_blocks, sink_key, sink_value, sink_t,
+                        residual_key, residual_value, residual_t, scale):
+        """Codec variants outside the K4/V2 preset and fp32 queries (C ABI ``inq_decode_generic``)."""
+        lib = N.library()
+        floats = lib.inq_decode_generic_workspace_floats(query.shape[1], n_blocks, sink_t, residual_t, 128)
+        shape = (floats,)
+        if self._workspace_pool is not None:
+            workspace = self._workspace_pool.acquire(shape, query.device)
+        else:
+            if self._workspace is None or self._workspace.numel() < floats or self._workspace.device != query.device:
+                self._workspace = torch.empty(shape, dtype=torch.float32, device=query.device)
+            workspace = self._workspace
+        rows = query.reshape(query.shape[1], 128) if query.is_contiguous() else query.contiguous().reshape(query.shape[1], 128)
+        output = torch.empty(query.shape, dtype=query.dtype, device=query.device)
+        a = N.GenericDecodeArgs()
+        a.q, a.out, a.q_stride_h = rows.data_ptr(), output.data_ptr(), rows.stride(0)
+        if n_blocks:
+            a.table, a.key_roles = self._tables.data_ptr(), self._key_map.data_ptr()
+            a.value_roles = self._value_map.data_ptr() if self._inquant_values else None
+            a.value_kind = 1 if self._inquant_values else 0
+            a.value_bits, a.value_group = self._value_bits, self._value_group
+            a.key_pad, a.value_pad = self._salient, self._value_salient
+        if sink_t:
+            a.sink_key, a.sink_value = sink_key.data_ptr(), sink_value.data_ptr()
+            a.sink_key_stride_h, a.sink_key_stride_t = sink_key.stride(1), sink_key.stride(2)
+            a.sink_value_stride_h, a.sink_value_stride_t = sink_value.stride(1), sink_value.stride(2)
+        if residual_t:
+            a.tail_key, a.tail_value = residual_key.data_ptr(), residual_value.data_ptr()
+            a.tail_key_stride_h, a.tail_key_stride_t = residual_key.stride(1), residual_key.stride(2)
+            a.tail_value_stride_h, a.tail_value_stride_t = residual_value.stride(1), residual_value.stride(2)
+        a.n_blocks, a.sink_tokens, a.tail_tokens = n_blocks, sink_t, residual_t
+        a.kv_heads, a.q_per_kv, a.block_tokens, a.head_dim = kv_heads, q_per_kv, self._packed_tokens, 128
+        a.dtype, a.scale = N.DTYPE_CODE[query.dtype], scale
+        a.partials, a.partials_floats = workspace.data_ptr(), workspace.numel()
+        N.check(lib.inq_decode_generic(N.ctypes.byref(a), N.stream_pointer(query.device)), "inq_decode_generic")
         return output
 
 

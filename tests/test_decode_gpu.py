@@ -193,12 +193,11 @@ def test_argument_validation():
         packed_decode(q.half(), [], [], residual_key=kv, residual_value=kv)
     with pytest.raises(ValueError, match="scale"):
         packed_decode(q, [], [], residual_key=kv, residual_value=kv, scale=0.0)
-    with pytest.raises(NotImplementedError):
-        packed_decode(q.float(), [], [], residual_key=kv.float(), residual_value=kv.float())
+    assert packed_decode(q.float(), [], [], residual_key=kv.float(), residual_value=kv.float()).dtype == torch.float32
     with pytest.raises(ValueError, match="counts"):
         PackedDecodeState([quantize(kv)], [])
-    with pytest.raises(NotImplementedError):
-        PackedDecodeState([quantize(kv)], [quantize(kv)])
+    with pytest.raises(ValueError, match="same quantizer"):
+        PackedDecodeState([quantize(kv), quantize(kv)], [quantize(kv), quantize_values(kv)])
 
 
 @pytest.mark.parametrize("name", sorted(DECODE_CASES))
@@ -224,3 +223,54 @@ def test_single_layer_roundtrip_matches_reference_output(golden, name):
     out = state.decode(to_device(q).view(1, case["q_heads"], 1, 128), sink_key=view.sink_key, sink_value=view.sink_value,
                        residual_key=view.residual_key, residual_value=view.residual_value, scale=128 ** -0.5)
     attention_close(to_numpy(out.float()).reshape(case["q_heads"], 128), golden[f"decode/{name}/output"])
+
+
+# ---------------------------------------------------------------------------------------------
+# Codec variants outside the K4/V2 preset and fp32 queries run the general kernel
+# (the reference's tests/test_triton_attention.py cover the same combinations).
+@pytest.mark.parametrize("value_codec,dtype,q_heads", [
+    ("inquant", "bfloat16", 8), ("inquant", "float16", 14), ((4, 64), "bfloat16", 8), ((2, 32), "bfloat16", 4),
+    ((2, 128), "float16", 8), ((4, 32), "bfloat16", 34), ((2, 64), "float32", 8), ("inquant", "float32", 4)])
+def test_general_kernel_covers_non_preset_value_codecs_and_fp32(value_codec, dtype, q_heads):
+    CodecConfig, quantize, quantize_values, PackedDecodeState, _, _ = _mods()
+    heads, blocks, block, tail, sink, fraction = 2, 3, 64, 37, 4, 0.125
+    cfg = CodecConfig(salient_fraction=fraction, donor_policy="min_error")
+    boost = np.where((np.arange(128) >= 5) & (np.arange(128) < 8), 12, 1).astype(np.float32)
+    ks = [oracle.round_to_dtype(_random(400 + i, (1, heads, block, 128), dtype) * boost, dtype) for i in range(blocks)]
+    vs = [_random(500 + i, (1, heads, block, 128), dtype) for i in range(blocks)]
+    keys = [quantize(to_device(k, dtype), cfg) for k in ks]
+    dense_k = [oracle.dequantize_k4(oracle.quantize_k4(k, dtype, 8, fraction, "min_error"))[0] for k in ks]
+    if value_codec == "inquant":
+        values = [quantize(to_device(v, dtype), cfg) for v in vs]
+        dense_v = [oracle.dequantize_k4(oracle.quantize_k4(v, dtype, 8, fraction, "min_error"))[0] for v in vs]
+    else:
+        bits, group = value_codec
+        values = [quantize_values(to_device(v, dtype), bits, group) for v in vs]
+        dense_v = [oracle.dequantize_values(oracle.quantize_values(v, dtype, bits, group))[0] for v in vs]
+    sink_k, sink_v = _random(1, (1, heads, sink, 128), dtype), _random(2, (1, heads, sink, 128), dtype)
+    tail_k, tail_v = _random(3, (1, heads, tail, 128), dtype), _random(4, (1, heads, tail, 128), dtype)
+    q = _random(5, (q_heads, 128), dtype)
+    state = PackedDecodeState(keys, values)
+    assert state._preset == (value_codec == (2, 64))
+    actual = state.decode(to_device(q, dtype).view(1, q_heads, 1, 128),
+                          sink_key=to_device(sink_k, dtype), sink_value=to_device(sink_v, dtype),
+                          residual_key=to_device(tail_k, dtype), residual_value=to_device(tail_v, dtype))
+    expected = _expected(q, [sink_k[0]] + dense_k + [tail_k[0]], [sink_v[0]] + dense_v + [tail_v[0]])
+    _check(actual, expected)
+    assert actual.dtype == TORCH_DTYPE[dtype]
+    # a growing state keeps working on the general path
+    grown = PackedDecodeState(keys[:1], values[:1])
+    grown.extend(keys, values)
+    again = grown.decode(to_device(q, dtype).view(1, q_heads, 1, 128),
+                         sink_key=to_device(sink_k, dtype), sink_value=to_device(sink_v, dtype),
+                         residual_key=to_device(tail_k, dtype), residual_value=to_device(tail_v, dtype))
+    assert torch.equal(actual, again)
+
+
+def test_general_kernel_dense_only_fp32():
+    _, _, _, _, _, packed_decode = _mods()
+    k, v, q = _random(7, (1, 2, 150, 128), "float32"), _random(8, (1, 2, 150, 128), "float32"), _random(9, (6, 128), "float32")
+    out = packed_decode(to_device(q, "float32").view(1, 6, 1, 128), [], [],
+                        residual_key=to_device(k, "float32"), residual_value=to_device(v, "float32"))
+    attention_close(to_numpy(out).reshape(6, 128), oracle.attention_decode(q, k[0], v[0], 128 ** -0.5),
+                    max_abs=1e-4, cosine=0.999999)
