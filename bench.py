@@ -282,7 +282,12 @@ def run_cuda(args):
         line["prefill"] = run_prefill(torch, device)
     if not args.no_paged_batch:
         torch.cuda.empty_cache()
-        line["paged_batch"] = run_paged_batch(torch, dist, device, world, rank)
+        line["paged_batch"] = run_paged_batch(torch, dist, device, world, rank, 16)
+        torch.cuda.empty_cache()
+        # the same requests with the reference's 64-token pages, for comparison
+        line["paged_batch"]["pages_of_64_tokens"] = {
+            k: v for k, v in run_paged_batch(torch, dist, device, world, rank, 64).items()
+            if k in ("us_per_step", "decode_tokens_per_s", "aggregate_gbs", "per_gpu_hbm_frac", "algorithmic_bytes_per_step")}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sample_layers=1)
     if rank == 0:
@@ -355,7 +360,7 @@ def run_prefill(torch, device):
     }
 
 
-def run_paged_batch(torch, dist, device, world, rank):
+def run_paged_batch(torch, dist, device, world, rank, block):
     """Config 3: Mistral-7B-shaped batched paged decode (vLLM-extension page layout, block 16):
     32 layers x 8 KV heads x 128, 32 query heads, 16 requests with seeded context lengths uniform
     in 4096..32768, pages at shuffled physical ids, requests dealt round-robin to the ranks with no
@@ -366,7 +371,7 @@ def run_paged_batch(torch, dist, device, world, rank):
     import workloads
     from inquant.batched import DecodeBatch, PagedSequenceState
     from inquant_vllm.layout import PageLayout, pack_pages_into
-    layers, heads, q_heads, block, requests = 32, 8, 32, 16, 16
+    layers, heads, q_heads, requests = 32, 8, 32, 16
     layout = PageLayout(block, heads)
     lengths = [int(x) for x in np.random.default_rng(2024).integers(4096, 32769, size=requests)]
     mine = [i for i in range(requests) if i % world == rank]
@@ -421,7 +426,7 @@ def run_paged_batch(torch, dist, device, world, rank):
         ms, total_bytes = float(worst[0].item()), float(t[1].item())
     peak, _ = measured_peak_gbs()
     gbs = total_bytes / (ms * 1e-3) / 1e9
-    return {"workload": "config 3: 16 requests x 32 layers, 8 KV heads, 32 query heads, contexts 4096..32768, pages of 16 tokens",
+    return {"workload": f"config 3: 16 requests x 32 layers, 8 KV heads, 32 query heads, contexts 4096..32768, pages of {block} tokens",
             "requests": requests, "context_tokens": sum(lengths), "us_per_step": round(ms * 1e3, 1),
             "decode_tokens_per_s": round(requests / (ms * 1e-3), 1), "aggregate_gbs": round(gbs, 1),
             "per_gpu_hbm_frac": round(gbs / world / peak, 4), "algorithmic_bytes_per_step": int(total_bytes),

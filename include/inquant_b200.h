@@ -262,8 +262,12 @@ typedef struct {
   int32_t dtype;              /* INQ_F16 or INQ_BF16 */
   float scale;                /* softmax scale */
   int32_t* status;            /* device status word (INQ_STATUS_WAIT_TIMEOUT on a stuck barrier) */
+  void* workspace;            /* optional device scratch: lets the kernel cut the KV range of every */
+  int64_t workspace_bytes;    /* (256 rows, head) item into segments that fill the SMs evenly      */
 } inq_prefill_args_t;
 int inq_prefill_attention(const inq_prefill_args_t* args /* host */, inq_stream_t stream);
+/* Scratch that allows every cut inq_prefill_attention may choose. */
+int64_t inq_prefill_workspace_bytes(int32_t q_heads, int32_t q_tokens);
 /* Work units (32-token slices, at least 1) of one pair whose sequence holds n_blocks blocks. */
 int64_t inq_decode_units(int32_t n_blocks, int32_t block_tokens);
 /* Scratch floats that suffice for a launch with n_pairs pairs and total_units work units on

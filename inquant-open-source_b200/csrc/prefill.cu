@@ -24,6 +24,7 @@
 // modulo 8 (the 128-byte swizzle of the tensor-core descriptors).
 #include <cuda.h>
 
+#include <algorithm>
 #include <type_traits>
 
 #include "common.cuh"
@@ -42,12 +43,15 @@ constexpr int kPfTmemCols = 512;             // S_A 0..127, S_B 128..255 (P over
 constexpr float kPfNegBig = -1.0e30f;
 constexpr float kPfSlack = 4.f;              // the reference maximum may lag the true one by 2^4
 constexpr int kPfSpinLimit = 1 << 22;
+constexpr int kPfMaxSplits = 8;              // KV segments per item at most
 
 struct PrefillParams {
   const void *q, *k, *v;
   void* out;
   long long q_sh, q_st, k_sh, k_st, v_sh, v_st, o_sh, o_st;   // strides in elements
   int q_heads, kv_heads, q_tokens, kv_tokens, n_qpairs;
+  int splits;         // KV segments per (query pair, head) item; > 1 writes partial records
+  float* records;     // [items][splits][256 rows][130]: unnormalised O, reference maximum, sum
   float scale_log2e;
   int* status;
 };
@@ -162,15 +166,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
     return;
   }
 
-  // late query rows see the most keys: they are scheduled first
-  const int qp = P.n_qpairs - 1 - (int)(blockIdx.x / P.q_heads);
-  const int head = (int)(blockIdx.x % P.q_heads);
+  // An item is (256 query rows, query head); late query rows see the most keys and are scheduled
+  // first.  With P.splits > 1 every item is cut into that many KV segments, one CTA each, so that
+  // the grid fills the SMs evenly; the segments' partial results are merged by a second kernel.
+  const int item = (int)(blockIdx.x / P.splits), seg = (int)(blockIdx.x % P.splits);
+  const int qp = P.n_qpairs - 1 - item / P.q_heads;
+  const int head = item % P.q_heads;
   const int kvh = head / (P.q_heads / P.kv_heads);
   const int q0 = qp * kPfRows;
   const int hist = P.kv_tokens - P.q_tokens;
-  // tiles each query tile needs: A ends at its last row's diagonal, B 128 tokens later
-  const int n_a = (min(P.kv_tokens, hist + q0 + kPfTile) + kPfTile - 1) / kPfTile;
-  const int n_b = (min(P.kv_tokens, hist + q0 + kPfRows) + kPfTile - 1) / kPfTile;
+  // tiles each query tile needs: A ends at its last row's diagonal, B 128 tokens later; this CTA
+  // walks tiles [t_lo, t_hi) and n_a / n_b count the tiles of its segment
+  const int all_a = (min(P.kv_tokens, hist + q0 + kPfTile) + kPfTile - 1) / kPfTile;
+  const int all_b = (min(P.kv_tokens, hist + q0 + kPfRows) + kPfTile - 1) / kPfTile;
+  const int t_lo = (int)((long long)all_b * seg / P.splits), t_hi = (int)((long long)all_b * (seg + 1) / P.splits);
+  const int n_b = t_hi - t_lo;
+  const int n_a = max(0, min(all_a, t_hi) - t_lo);
 
   if (tid == 0) {
     *abort_flag = 0;
@@ -200,18 +211,18 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
 
   if (warp == 9) {
     // ================================================================ TMA warp
-    if (lane == 0) {
+    if (lane == 0 && n_b > 0) {
       auto request_k = [&](int t) {
         const unsigned bar = bar_k + 8 * (t % kPfStages), dst = sKb + (t % kPfStages) * kPfTileBytes;
         pf_expect(bar, kPfTileBytes);
-        pf_tma(dst, &map_k, 0, t * kPfTile, kvh, bar);
-        pf_tma(dst + kPfSlab, &map_k, 64, t * kPfTile, kvh, bar);
+        pf_tma(dst, &map_k, 0, (t_lo + t) * kPfTile, kvh, bar);
+        pf_tma(dst + kPfSlab, &map_k, 64, (t_lo + t) * kPfTile, kvh, bar);
       };
       auto request_v = [&](int t) {
         const unsigned bar = bar_v + 8 * (t % kPfStages), dst = sVb + (t % kPfStages) * kPfTileBytes;
         pf_expect(bar, kPfTileBytes);
-        pf_tma(dst, &map_v, 0, t * kPfTile, kvh, bar);
-        pf_tma(dst + kPfSlab, &map_v, 64, t * kPfTile, kvh, bar);
+        pf_tma(dst, &map_v, 0, (t_lo + t) * kPfTile, kvh, bar);
+        pf_tma(dst + kPfSlab, &map_v, 64, (t_lo + t) * kPfTile, kvh, bar);
       };
       pf_expect(bar_q, 2 * kPfTileBytes);
 #pragma unroll
@@ -234,7 +245,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
     }
   } else if (warp == 8) {
     // ================================================================ MMA warp
-    if (lane == 0) {
+    if (lane == 0 && n_b > 0) {
       // instruction descriptors: fp32 accumulate, A/B in the model dtype, M = N = 128; the value
       // tile is an MN-major B operand (tokens are its K dimension, stored row by row)
       const unsigned fmt = std::is_same<QT, __half>::value ? 0u : 1u;
@@ -260,7 +271,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
       bool ok = pf_wait(bar_q, 0, abort_flag) && pf_wait(bar_k, 0, abort_flag);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        issue_s(0, 0);
+        if (n_a > 0) issue_s(0, 0);
         issue_s(1, 0);
       }
       for (int t = 0; ok && t < n_b; ++t) {
@@ -297,7 +308,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
     bool ok = true;
 
     for (int t = 0; t < n_x; ++t) {
-      const int kv0 = t * kPfTile;
+      const int kv0 = (t_lo + t) * kPfTile;
       // S(t) is complete; the contractions run in issue order, so PV(t-1) is complete as well:
       // the columns of P may be overwritten by S and O may be rescaled
       if (!pf_wait(my_s, (unsigned)t & 1u, abort_flag)) { ok = false; break; }
@@ -370,28 +381,51 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       pf_arrive(my_p);
     }
-    ok = ok && pf_wait(my_o, (unsigned)(n_x - 1) & 1u, abort_flag);
+    if (n_x > 0) ok = ok && pf_wait(my_o, (unsigned)(n_x - 1) & 1u, abort_flag);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
-    // ---- normalise and store this thread's row
-    const float inv = 1.f / l_sum;
-    const bool live = ok && q_row < P.q_tokens;
-    QT* orow = (QT*)P.out + (long long)head * P.o_sh + (long long)q_row * P.o_st;
+    if (P.splits == 1) {
+      // ---- normalise and store this thread's row
+      const float inv = 1.f / l_sum;
+      const bool live = ok && q_row < P.q_tokens;
+      QT* orow = (QT*)P.out + (long long)head * P.o_sh + (long long)q_row * P.o_st;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kPfTile; c0 += 32) {
-      unsigned v[32];
-      pf_tmem_ld32(tO + c0, v);
-      if (live) {
+      for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+        unsigned v[32];
+        pf_tmem_ld32(tO + c0, v);
+        if (live) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 w;
-          w.x = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 0]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
-          w.y = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
-          w.z = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
-          w.w = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
-          *(uint4*)(orow + c0 + 8 * q4) = w;
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 w;
+            w.x = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 0]) * inv, __uint_as_float(v[8 * q4 + 1]) * inv);
+            w.y = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 2]) * inv, __uint_as_float(v[8 * q4 + 3]) * inv);
+            w.z = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 4]) * inv, __uint_as_float(v[8 * q4 + 5]) * inv);
+            w.w = pf_pack2<QT>(__uint_as_float(v[8 * q4 + 6]) * inv, __uint_as_float(v[8 * q4 + 7]) * inv);
+            *(uint4*)(orow + c0 + 8 * q4) = w;
+          }
         }
       }
+    } else {
+      // ---- partial record of this row: unnormalised output, reference maximum, sum
+      float* rec = P.records + (((long long)item * P.splits + seg) * kPfRows + x * kPfTile + row) * 130;
+      const bool have = ok && n_x > 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+        unsigned v[32];
+        if (n_x > 0) {
+          pf_tmem_ld32(tO + c0, v);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (have) w = make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
+                                    __uint_as_float(v[4 * q4 + 3]));
+          *(float2*)(rec + c0 + 4 * q4) = make_float2(w.x, w.y);
+          *(float2*)(rec + c0 + 4 * q4 + 2) = make_float2(w.z, w.w);
+        }
+      }
+      rec[128] = have ? m_ref : kPfNegBig;
+      rec[129] = have ? l_sum : 0.f;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -399,6 +433,29 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
   if (tid == 0 && *abort_flag) atomicOr(P.status, INQ_STATUS_WAIT_TIMEOUT);
   if (warp == 8)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPfTmemCols) : "memory");
+}
+
+// Merges the KV segments of every item: out = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
+// One block per (item, 8 rows), one thread per channel.
+template <typename QT>
+__global__ void __launch_bounds__(kPfTile) prefill_merge_kernel(const PrefillParams P) {
+  const int item = blockIdx.x, c = threadIdx.x;
+  const int qp = P.n_qpairs - 1 - item / P.q_heads, head = item % P.q_heads;
+  for (int r = 0; r < 8; ++r) {
+    const int row = blockIdx.y * 8 + r, q_row = qp * kPfRows + row;
+    if (q_row >= P.q_tokens) continue;
+    const float* base = P.records + ((long long)item * P.splits * kPfRows + row) * 130;
+    float top = kPfNegBig;
+    for (int sgm = 0; sgm < P.splits; ++sgm) top = fmaxf(top, base[(long long)sgm * kPfRows * 130 + 128]);
+    float o = 0.f, l = 0.f;
+    for (int sgm = 0; sgm < P.splits; ++sgm) {
+      const float* rec = base + (long long)sgm * kPfRows * 130;
+      const float w = pf_exp2(rec[128] - top);
+      o = fmaf(rec[c], w, o);
+      l = fmaf(rec[129], w, l);
+    }
+    ((QT*)P.out)[(long long)head * P.o_sh + (long long)q_row * P.o_st + c] = from_float<QT>(o / l);
+  }
 }
 
 }  // namespace inq
@@ -437,6 +494,11 @@ bool make_map(CUtensorMap* map, const void* base, int dtype, long long tokens, l
 }  // namespace
 
 
+extern "C" int64_t inq_prefill_workspace_bytes(int32_t q_heads, int32_t q_tokens) {
+  const long long items = (long long)((q_tokens + kPfRows - 1) / kPfRows) * q_heads;
+  return items * kPfMaxSplits * kPfRows * 130 * (long long)sizeof(float);
+}
+
 extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t stream_) {
   if (!a || !a->q || !a->k || !a->v || !a->out || !a->status) return INQ_ERR_ARGUMENT;
   if (a->q_heads < 1 || a->kv_heads < 1 || a->q_heads % a->kv_heads) return INQ_ERR_ARGUMENT;
@@ -453,9 +515,39 @@ extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t s
   P.v_sh = a->v_stride_h; P.v_st = a->v_stride_t; P.o_sh = a->o_stride_h; P.o_st = a->o_stride_t;
   P.q_heads = a->q_heads; P.kv_heads = a->kv_heads; P.q_tokens = a->q_tokens; P.kv_tokens = a->kv_tokens;
   P.n_qpairs = (a->q_tokens + kPfRows - 1) / kPfRows;
+  P.splits = 1;
+  P.records = (float*)a->workspace;
+  {
+    // cut every item into `splits` KV segments when that fills the SMs more evenly: rounds of
+    // CTAs over the SMs, each round as long as one segment, a few per cent of overhead per cut
+    static int n_sm = 0;
+    if (!n_sm) {
+      int device = 0;
+      INQ_CUDA_CHECK(cudaGetDevice(&device));
+      INQ_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
+    }
+    const long long items = (long long)P.n_qpairs * a->q_heads;
+    const int lightest = (int)((std::min<long long>(a->kv_tokens, (long long)a->kv_tokens - a->q_tokens + kPfRows) + kPfTile - 1) / kPfTile);
+    // cost of a cut into sp segments, in KV-tile times: rounds of CTAs over the SMs, each as long
+    // as one segment plus, when cut, the fixed price of a segment (pipeline fill, writing and
+    // merging a 133 KB partial record), measured at about six tile times
+    const double tiles = ((double)a->kv_tokens - 0.5 * a->q_tokens) / kPfTile;
+    double best = 1e30;
+    for (int sp = 1; sp <= kPfMaxSplits; ++sp) {
+      if (sp > 1 && (lightest / sp < 2 || !a->workspace ||
+                     a->workspace_bytes < (long long)items * sp * kPfRows * 130 * (long long)sizeof(float)))
+        break;
+      const double rounds = (double)((items * sp + n_sm - 1) / n_sm);
+      const double cost = rounds * (tiles / sp + (sp > 1 ? 6.0 : 0.0));
+      if (cost < best - 1e-9) {
+        best = cost;
+        P.splits = sp;
+      }
+    }
+  }
   P.scale_log2e = a->scale * 1.4426950408889634f;
   P.status = a->status;
-  const long long ctas = (long long)P.n_qpairs * P.q_heads;
+  const long long ctas = (long long)P.n_qpairs * P.q_heads * P.splits;
   if (ctas > 0x7fffffffLL) return INQ_ERR_CAPACITY;
   cudaStream_t stream = (cudaStream_t)stream_;
   if (a->q_stride_h <= 0 || a->k_stride_h <= 0 || a->v_stride_h <= 0 || a->q_stride_t < 128 || a->k_stride_t < 128 ||
@@ -469,9 +561,11 @@ extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t s
   if (a->dtype == INQ_F16) {
     INQ_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
     prefill_kernel<__half><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P, map_q, map_k, map_v);
+    if (P.splits > 1) prefill_merge_kernel<__half><<<dim3((unsigned)(ctas / P.splits), kPfRows / 8), kPfTile, 0, stream>>>(P);
   } else {
     INQ_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
     prefill_kernel<__nv_bfloat16><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P, map_q, map_k, map_v);
+    if (P.splits > 1) prefill_merge_kernel<__nv_bfloat16><<<dim3((unsigned)(ctas / P.splits), kPfRows / 8), kPfTile, 0, stream>>>(P);
   }
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;

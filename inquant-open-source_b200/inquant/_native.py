@@ -92,7 +92,8 @@ class PrefillArgs(ctypes.Structure):
                 ("q_stride_h", c_int64), ("q_stride_t", c_int64), ("k_stride_h", c_int64), ("k_stride_t", c_int64),
                 ("v_stride_h", c_int64), ("v_stride_t", c_int64), ("o_stride_h", c_int64), ("o_stride_t", c_int64),
                 ("q_heads", c_int32), ("kv_heads", c_int32), ("q_tokens", c_int32), ("kv_tokens", c_int32),
-                ("dtype", c_int32), ("scale", ctypes.c_float), ("status", c_void_p)]
+                ("dtype", c_int32), ("scale", ctypes.c_float), ("status", c_void_p),
+                ("workspace", c_void_p), ("workspace_bytes", c_int64)]
 
 
 RECORD_FLOATS = 8 * 132  # one split-KV partial: 8 query heads x (acc[128], m, l, pad)
@@ -114,6 +115,8 @@ def library() -> ctypes.CDLL:
         lib.inq_decode_workspace_floats.argtypes = [c_int32, c_int64]
         lib.inq_decode_generic_workspace_floats.restype = c_int64
         lib.inq_decode_generic_workspace_floats.argtypes = [c_int32, c_int32, c_int32, c_int32, c_int32]
+        lib.inq_prefill_workspace_bytes.restype = c_int64
+        lib.inq_prefill_workspace_bytes.argtypes = [c_int32, c_int32]
         lib.inq_decode_units.restype = c_int64
         lib.inq_decode_units.argtypes = [c_int32, c_int32]
         for name in EXPORTS:
@@ -131,6 +134,7 @@ EXPORTS = (
     "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
     "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
     "inq_prefill_attention", "inq_decode_generic", "inq_decode_generic_workspace_floats",
+    "inq_prefill_workspace_bytes",
 )
 
 

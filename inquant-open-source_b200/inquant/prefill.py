@@ -17,6 +17,10 @@ import torch
 from . import _native as N
 
 
+# per-device scratch for the kernel's partial results (one stream at a time, like the decode workspace)
+_SCRATCH: dict = {}
+
+
 def prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, scale: float | None = None,
                       out: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of ``query`` [1, Hq, Tq, 128] over ``key``/``value`` [1, H, L, 128] whose
@@ -43,11 +47,16 @@ def prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
         out = torch.empty((1, q_heads, q_tokens, 128), dtype=query.dtype, device=query.device)
     elif out.shape != (1, q_heads, q_tokens, 128) or out.dtype != query.dtype or rows(out) is not out:
         raise ValueError("out must be a [1, Hq, Tq, 128] tensor of the query dtype with aligned rows")
+    need = N.library().inq_prefill_workspace_bytes(q_heads, q_tokens)
+    scratch = _SCRATCH.get(query.device)
+    if scratch is None or scratch.numel() < need:
+        scratch = _SCRATCH[query.device] = torch.empty(need, dtype=torch.uint8, device=query.device)
     args = N.PrefillArgs(
         query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(),
         query.stride(1), query.stride(2), key.stride(1), key.stride(2), value.stride(1), value.stride(2),
         out.stride(1), out.stride(2), q_heads, kv_heads, q_tokens, kv_tokens, N.DTYPE_CODE[query.dtype],
-        float(scale if scale is not None else 128 ** -0.5), N.status_word(query.device).data_ptr())
+        float(scale if scale is not None else 128 ** -0.5), N.status_word(query.device).data_ptr(),
+        scratch.data_ptr(), scratch.numel())
     N.check(N.library().inq_prefill_attention(ctypes.byref(args), N.stream_pointer(query.device)), "inq_prefill_attention")
     return out
 

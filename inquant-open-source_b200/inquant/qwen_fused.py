@@ -12,6 +12,11 @@ Differences from the reference, none visible through the call signatures:
 
 * the attention interface of both Transformers 4.53 (``past_key_value=``) and 5.x
   (``past_key_values=``) is accepted;
+* ``fused_prefill=True`` (not in the reference) also routes query chunks that FOLLOW earlier
+  tokens of an ``InQuantCache`` through this library's tcgen05 prefill kernel
+  (``inquant.prefill.prefill_chunk``) instead of the stock forward; the chunk is attended
+  causally and any mask the model built is ignored, so enable it only for unpadded batch-one
+  prompts;
 * there is no CPU path in this library: ``allow_cpu_reference`` is accepted for signature
   compatibility, but a non-CUDA decode step always raises (the reference would run its
   materialising oracle there), and ``cpu_reference_calls`` therefore stays 0.
@@ -63,6 +68,10 @@ class FusedQwen2Handle:
         return sum(getattr(module, "_inquant_fused_decode_calls", 0) for module, _ in self.originals)
 
     @property
+    def fused_prefill_calls(self) -> int:
+        return sum(getattr(module, "_inquant_fused_prefill_calls", 0) for module, _ in self.originals)
+
+    @property
     def cpu_reference_calls(self) -> int:
         return sum(getattr(module, "_inquant_cpu_reference_calls", 0) for module, _ in self.originals)
 
@@ -94,7 +103,8 @@ def _attention_class(model: Any):
     return Attention, apply_rotary_pos_emb
 
 
-def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False) -> FusedQwen2Handle:
+def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False,
+                           fused_prefill: bool = False) -> FusedQwen2Handle:
     """Patch this instantiated model only; retain its weights and prefill forward
     (reference ``qwen_fused.py:71-174``).
 
@@ -140,6 +150,29 @@ def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False) -> 
             and attention_mask is None
             and not kwargs.get("output_attentions", False)
         )
+        use_prefill = (
+            fused_prefill and not use_packed
+            and isinstance(cache, InQuantCache)
+            and hidden_states.shape[0] == 1 and hidden_states.shape[1] > 1
+            and hidden_states.device.type == "cuda"
+            and hidden_states.dtype in (torch.float16, torch.bfloat16)
+            and cache.get_seq_length(attention.layer_idx) > 0
+            and not kwargs.get("output_attentions", False)
+            and not torch.is_grad_enabled()
+        )
+        if use_prefill:
+            from .prefill import prefill_chunk
+            input_shape = hidden_states.shape[:-1]
+            hidden_shape = (*input_shape, -1, attention.head_dim)
+            query = attention.q_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+            key = attention.k_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+            value = attention.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+            cos, sin = position_embeddings
+            query, key = apply_rotary_pos_emb(query, key, cos, sin)
+            result = prefill_chunk(cache, query, key, value, attention.layer_idx, attention.scaling)
+            attention._inquant_fused_prefill_calls += 1
+            output = result.transpose(1, 2).reshape(*input_shape, -1).contiguous()
+            return attention.o_proj(output), None
         if not use_packed:
             extra = dict(kwargs)
             extra[attention._inquant_cache_name] = cache
@@ -195,6 +228,7 @@ def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False) -> 
         module._inquant_cache_name = cache_name
         module._inquant_fused_decode_calls = 0
         module._inquant_cpu_reference_calls = 0
+        module._inquant_fused_prefill_calls = 0
         module.forward = MethodType(forward, module)
     return FusedQwen2Handle(originals)
 

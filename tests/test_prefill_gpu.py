@@ -28,7 +28,9 @@ def _reference(q, k, v, scale):
     (7, 1, 200, 77, torch.bfloat16),       # ragged query and history lengths, GQA 7
     (4, 4, 1, 300, torch.bfloat16),        # a single query token
     (8, 2, 384, 1000, torch.float16),      # fp16, several KV tiles
-    (28, 4, 512, 2048, torch.bfloat16),    # Qwen2.5-7B head counts
+    (28, 4, 512, 2048, torch.bfloat16),    # Qwen2.5-7B head counts; items cut into 2 KV segments
+    (28, 4, 2048, 6144, torch.bfloat16),   # config 2's chunk shape: 224 items cut into 3 KV segments each
+    (3, 1, 300, 5000, torch.float16),      # few items over a long history: cut into 8 segments
 ])
 def test_prefill_attention_matches_fp32_causal_attention(q_heads, kv_heads, q_tokens, history, dtype):
     from inquant.prefill import prefill_attention

@@ -79,3 +79,32 @@ def test_generate_runs_through_the_packed_path():
                                    max_new_tokens=5, min_new_tokens=5)
     assert tuple(generated.shape) == (1, 55)
     assert handle.fused_decode_calls + handle.cpu_reference_calls >= 0
+
+
+def test_chunked_prefill_through_the_tensor_core_kernel_matches_the_stock_forward():
+    """A 300-token prompt fed as chunks of 100: with fused_prefill the later chunks run this
+    library's prefill kernel over the packed history; logits must agree with the stock forward,
+    which materialises the same history and calls SDPA with the model's causal mask."""
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.qwen_fused import enable_fused_attention
+    torch.manual_seed(41)
+    model = _model("qwen2", layers=1, heads=14, kv_heads=2)
+    twin = copy.deepcopy(model)
+    config = CacheConfig(CodecConfig(salient_fraction=.125), block_size=32, residual_length=4, sink_tokens=2, value_bits=2)
+    tokens = torch.randint(2, 90, (1, 300), device="cuda")
+    with enable_fused_attention(model, fused_prefill=True) as handle, torch.no_grad():
+        expected_cache, packed = InQuantCache(config), InQuantCache(config)
+        for start in range(0, 300, 100):
+            chunk = tokens[:, start:start + 100]
+            expected = twin(chunk, past_key_values=expected_cache).logits
+            actual = model(chunk, past_key_values=packed).logits
+            # two attention implementations in bf16: up to three bf16 steps of order-one logits
+            torch.testing.assert_close(actual.float(), expected.float(), rtol=.035, atol=.024)
+        assert handle.fused_prefill_calls == 2 and handle.fused_decode_calls == 0
+        token = torch.tensor([[7]], device="cuda")
+        torch.testing.assert_close(model(token, past_key_values=packed).logits.float(),
+                                   twin(token, past_key_values=expected_cache).logits.float(), rtol=.035, atol=.016)
+        assert handle.fused_decode_calls == 1
+        for a, b in zip(packed.materialize(0), expected_cache.materialize(0)):
+            assert torch.equal(a, b)
