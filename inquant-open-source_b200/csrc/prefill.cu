@@ -41,7 +41,7 @@ constexpr int kPfTiles = (2 + 2 * kPfStages) * kPfTileBytes;   // Q x2, K and V 
 constexpr int kPfSmem = kPfTiles + 160;      // then the TMEM base address, the abort flag and 11 mbarriers
 constexpr int kPfTmemCols = 512;             // S_A 0..127, S_B 128..255 (P over their first 64), O_A 256..383, O_B 384..511
 constexpr float kPfNegBig = -1.0e30f;
-constexpr float kPfSlack = 4.f;              // the reference maximum may lag the true one by 2^4
+constexpr float kPfSlack = 8.f;              // the reference maximum may lag the true one by 2^8 (P stays below 256)
 constexpr int kPfSpinLimit = 1 << 22;
 constexpr int kPfMaxSplits = 8;              // KV segments per item at most
 
