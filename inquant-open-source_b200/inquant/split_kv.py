@@ -85,3 +85,32 @@ class SplitKVDecode:
             self.gathered[0].copy_(local)
         merge_records(self.gathered, self.outputs.view(-1, 128))
         return self.outputs
+
+    def capture(self) -> None:
+        """Record one step (append on the tail owner, local decode, all-gather, merge) into a CUDA
+        graph; ``replay`` then costs one graph launch per step.  Run eager steps first: the first
+        launches set kernel attributes and NCCL builds its communicator outside a capture."""
+        graph = torch.cuda.CUDAGraph()
+        counters = self.batch.tail_counters.clone()
+        with torch.cuda.graph(graph):
+            if self.owns_tail:
+                self.batch._launch_append()
+            self.batch._launch_attend()
+            local = self.batch.partial_records.view(-1, 130)
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.gathered.view(-1, 130), local, group=self.group)
+            else:
+                self.gathered[0].copy_(local)
+            merge_records(self.gathered, self.outputs.view(-1, 128))
+        self.batch.tail_counters.copy_(counters)
+        self._graph = graph
+
+    def replay(self) -> torch.Tensor:
+        if getattr(self, "_graph", None) is None:
+            raise RuntimeError("call capture() first")
+        if self.owns_tail and self.batch.capacity_left < 1:
+            raise RuntimeError("a tail buffer is full: seal a block before appending")
+        self._graph.replay()
+        if self.owns_tail:
+            self.batch._appended += 1
+        return self.outputs
