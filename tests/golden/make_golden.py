@@ -105,4 +105,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("INQUANT_REFERENCE"):
+        raise SystemExit("usage: make_golden.py <path of the reference checkout>  (or set INQUANT_REFERENCE)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["INQUANT_REFERENCE"])
