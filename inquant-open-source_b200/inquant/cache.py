@@ -28,7 +28,7 @@ except ImportError:
         pass
 
 from . import _native as N
-from .codec import CodecConfig, PackedTensor, quantize
+from .codec import ArenaPackedTensor, CodecConfig, PackedTensor, quantize
 
 
 @dataclass(frozen=True)
@@ -128,14 +128,7 @@ def _quantize_temporal_blocks(tensor, block_count, block_size, config):
     ).permute(1, 0, 2, 3)
     packed = quantize(blocked, config)
     shape = (1, heads, block_size, channels)
-    # one split per field yields every block's view at once (the per-block slicing of 127 blocks
-    # x 5 fields would cost more host time than the encoder launch itself)
-    fields = [packed.payload.split(1), packed.scales.split(1), packed.salient_channels.split(1),
-              packed.donor_channels.split(1), packed.padding.split(1)]
-    blocks = [PackedTensor(*views, shape=shape, original_dtype=tensor.dtype) for views in zip(*fields)]
-    for index, block in enumerate(blocks):
-        object.__setattr__(block, "_arena", (packed, index))   # lets materialize() dequantise the whole launch at once
-    return blocks
+    return [ArenaPackedTensor(packed, index, shape, tensor.dtype) for index in range(block_count)]
 
 
 class InQuantCache(_HFCache):

@@ -120,6 +120,43 @@ class PackedTensor:
         return out
 
 
+class ArenaPackedTensor(PackedTensor):
+    """One block of a batch that a single encoder launch sealed.  Its field tensors are views of
+    that launch's output arena and are created on first access: a 32K-token prefill seals 127
+    blocks per layer, and building 5 views for each costs more host time than the launch."""
+
+    _FIELDS = ("payload", "scales", "salient_channels", "donor_channels", "padding")
+
+    def __init__(self, arena: PackedTensor, index: int, shape, original_dtype) -> None:
+        object.__setattr__(self, "_arena", (arena, index))
+        object.__setattr__(self, "shape", shape)
+        object.__setattr__(self, "original_dtype", original_dtype)
+
+    def __getattr__(self, name):   # reached only while a field has not been materialised yet
+        if name in ArenaPackedTensor._FIELDS:
+            arena, index = self.__dict__["_arena"]
+            view = getattr(arena, name)[index:index + 1]
+            object.__setattr__(self, name, view)
+            return view
+        raise AttributeError(name)
+
+    def field_pointer(self, name: str) -> int:
+        """Device address of a field without creating its view."""
+        arena, index = self.__dict__["_arena"]
+        tensor = getattr(arena, name)
+        return tensor.data_ptr() + index * tensor.stride(0) * tensor.element_size()
+
+    @property
+    def payload_nbytes(self) -> int:
+        arena, _ = self.__dict__["_arena"]
+        return _logical_bytes(arena.payload) // arena.payload.shape[0]
+
+    @property
+    def nbytes(self) -> int:
+        arena, _ = self.__dict__["_arena"]
+        return sum(_logical_bytes(t) // t.shape[0] for t in arena.tensors.values())
+
+
 def _reuse_map(saliency: torch.Tensor, count: int, donor_error: torch.Tensor | None = None):
     """Disjoint sources/donors (C ABI ``inq_select_donors``; reference ``codec.py:137-178``).
 

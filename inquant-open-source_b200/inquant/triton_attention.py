@@ -134,14 +134,19 @@ class PackedDecodeState:
             if any(t.device != self._device for t in block.tensors.values()):
                 raise ValueError("All packed tensors must share the same CUDA device")
         new_keys, new_values = key_blocks[old_count:], value_blocks[old_count:]
+        last_field = "padding" if self._inquant_values else "offsets"
+        pointers = []
         for k, v in zip(new_keys, new_values):
+            if hasattr(k, "field_pointer") and hasattr(v, "field_pointer"):
+                # blocks of one encoder launch: contiguous slices of its arena, addressed directly
+                pointers.append([k.field_pointer("payload"), k.field_pointer("scales"), k.field_pointer("padding"),
+                                 v.field_pointer("payload"), v.field_pointer("scales"), v.field_pointer(last_field)])
+                continue
             for t in (*k.tensors.values(), *v.tensors.values()):
                 if not t.is_contiguous():
                     raise ValueError("Packed block tensors must be contiguous")
-        pointers = [[k.payload.data_ptr(), k.scales.data_ptr(), k.padding.data_ptr(),
-                     v.payload.data_ptr(), v.scales.data_ptr(),
-                     (v.padding if self._inquant_values else v.offsets).data_ptr()]
-                    for k, v in zip(new_keys, new_values)]
+            pointers.append([k.payload.data_ptr(), k.scales.data_ptr(), k.padding.data_ptr(),
+                             v.payload.data_ptr(), v.scales.data_ptr(), getattr(v, last_field).data_ptr()])
         count = len(key_blocks)
         if count > self._capacity:
             capacity = count if not self._capacity else max(count, min(self._capacity * 2, count + 7))

@@ -57,6 +57,43 @@ class PackedValues:
         return out
 
 
+class ArenaPackedValues(PackedValues):
+    """One block of a batch sealed by a single value-encoder launch; field views are created on
+    first access (see ``codec.ArenaPackedTensor``)."""
+
+    _FIELDS = ("payload", "scales", "offsets")
+
+    def __init__(self, arena: PackedValues, index: int, shape, original_dtype) -> None:
+        object.__setattr__(self, "_arena", (arena, index))
+        object.__setattr__(self, "shape", shape)
+        object.__setattr__(self, "original_dtype", original_dtype)
+        object.__setattr__(self, "bits", arena.bits)
+        object.__setattr__(self, "group_size", arena.group_size)
+
+    def __getattr__(self, name):
+        if name in ArenaPackedValues._FIELDS:
+            arena, index = self.__dict__["_arena"]
+            view = getattr(arena, name)[index:index + 1]
+            object.__setattr__(self, name, view)
+            return view
+        raise AttributeError(name)
+
+    def field_pointer(self, name: str) -> int:
+        arena, index = self.__dict__["_arena"]
+        tensor = getattr(arena, name)
+        return tensor.data_ptr() + index * tensor.stride(0) * tensor.element_size()
+
+    @property
+    def payload_nbytes(self):
+        arena, _ = self.__dict__["_arena"]
+        return _logical_bytes(arena.payload) // arena.payload.shape[0]
+
+    @property
+    def nbytes(self):
+        arena, _ = self.__dict__["_arena"]
+        return sum(_logical_bytes(t) // t.shape[0] for t in arena.tensors.values())
+
+
 def encode_values_into(x, bits, group_size, payload, scales, offsets, page_ids=None):
     """Launch the value encoder on ``x`` = [outer, inner, tokens, channels]; no synchronisation."""
     args = N.VEncodeArgs()
@@ -106,9 +143,4 @@ def quantize_value_blocks(tensor, block_count, block_size, bits, group_size):
         heads, block_count, block_size, channels).permute(1, 0, 2, 3)
     packed = quantize_values(blocked, bits, group_size)
     shape = (1, heads, block_size, channels)
-    fields = [packed.payload.split(1), packed.scales.split(1), packed.offsets.split(1)]
-    blocks = [PackedValues(*views, shape=shape, original_dtype=tensor.dtype, bits=bits, group_size=group_size)
-              for views in zip(*fields)]
-    for index, block in enumerate(blocks):
-        object.__setattr__(block, "_arena", (packed, index))   # lets InQuantCache.materialize dequantise the whole launch at once
-    return blocks
+    return [ArenaPackedValues(packed, index, shape, tensor.dtype) for index in range(block_count)]
