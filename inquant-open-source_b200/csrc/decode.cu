@@ -1,29 +1,34 @@
 // Single-query grouped-query attention over the packed K4/V2 history plus the exact
 // (bf16/fp16) sink and recent tail, with the split-KV partials merged by the last CTA of
-// every (sequence, KV head) -- one launch per decode step, for one layer or for a batch
-// of (request, layer) sequences.
+// every (sequence, KV head, 8-query-head tile) pair -- one launch per decode step, for one
+// layer or for a batch of (request, layer) sequences.
 //
-// Work decomposition.  A (sequence, KV head) owns `slices` of 16 tokens: packed slices of
-// every sealed block first, then the dense sink and tail slices (weighted 4x, they carry
-// ~5x the bytes).  blockIdx.x cuts that list into `n_parts` contiguous ranges, a CTA's four
-// warps cut their range again, and every warp streams its slices on its own:
+// Work decomposition.  The 32-token packed slices of all pairs form one flat list that is cut
+// into gridDim.x equal ranges (the grid is SMs x resident CTAs); a CTA walks its range pair by
+// pair and its four warps cut each segment again.  The few dense sink/tail slices of a pair
+// (16 tokens each) are dealt round-robin to the warps that work on it.  Every warp streams its
+// slices on its own:
 //
-//   * staging: each lane issues 16-byte cp.async copies of the slice's K nibbles (1 KB),
-//     V codes (512 B) and V scale/offset pairs (128 B) into a per-warp ring in shared
-//     memory, four slices deep, so ~5 KB per warp are in flight without holding registers;
+//   * staging: each lane issues 16-byte cp.async copies of the slice's K nibbles (2 KB),
+//     V codes (1 KB) and V scale/offset pairs (256 B) into a per-warp ring of three stages in
+//     shared memory; a block's scales, role map and padding ride with its first slice;
 //   * dequantisation never materialises K or V.  The descriptor-guided K decode is linear
-//     in the stored nibbles, so per block it is folded into the query:
+//     in the stored nibbles, so once per block it is folded into the query:
 //         score = sum_c w_c * nibble_c + const,
-//     w_c = q_c s_c for a normal channel, 16 q_s s_s for a salient channel's own slot and
-//     q_s s_s for the donor slot that carries the salient channel's low nibble; const holds
-//     the -8 / -128 biases and the donors' padding values.  Nibbles are fed to the tensor
+//     w_c = q_c s_c for a normal channel and 0 for the two slots of a salient channel; const
+//     holds the -8 biases and the donors' padding values.  Nibbles are fed to the tensor
 //     cores as fp16 SUBNORMALS: a nibble masked in place at bit 0 or 4 of a 16-bit lane is
 //     the exact value nibble * 2^-24 (or * 2^-20), so unpacking costs one AND per two
 //     elements and no integer-to-float conversion.  V works the same way with 2-bit codes
-//     at bit 0..8, the per-token group scale folded into the probabilities and the group
-//     offsets accumulated on the side;
-//   * contractions use mma.sync.m16n8k16 with the 16 tokens as M and the (up to 8) query
-//     heads of the KV head as N, so one pass serves the whole GQA group.
+//     at bit 0..8 (ldmatrix.trans delivers token pairs per channel group), the per-token group
+//     scale multiplied into the transposed probabilities and the group offsets contracted by
+//     one more MMA;
+//   * salient channels are rebuilt exactly as the reference rounds them: a tensor-core gather
+//     (nibbles x selection matrix) yields 16*hi + lo, fl32((code - 128) * scale) is rounded to
+//     the model dtype and contracted with the query at those channels;
+//   * contractions use mma.sync.m16n8k16 with 16 tokens as M and the (up to 8) query heads
+//     of the KV head as N, so one pass serves the whole GQA group; base-2 online softmax with
+//     a lazily raised reference maximum.
 #include <type_traits>
 
 #include "common.cuh"
