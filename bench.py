@@ -132,6 +132,41 @@ def build_request(torch, device, seed_base):
     return cache, encode_ms, kernels_us
 
 
+def measure_append_and_seal(torch, batch, device):
+    """The append kernel alone (one launch writes the new token of all 28 layers into tail, and
+    sink while it fills) and the sealing of one 256-token block of one layer through the codec
+    API (K4 + V2 encoders on [1, 4, 256, 128], including the finite-check read-back): a block is
+    sealed once per 256 decoded tokens and layer."""
+    from inquant.codec import CodecConfig, quantize
+    from inquant.value_codec import quantize_values
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 20
+    batch.rewind()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        batch._launch_append()
+    e1.record()
+    torch.cuda.synchronize()
+    append_us = e0.elapsed_time(e1) / reps * 1e3
+    batch.rewind()
+    gen = torch.Generator(device=device).manual_seed(5)
+    block_k = torch.randn((1, KV_HEADS, BLOCK, DIM), device=device, generator=gen).bfloat16()
+    block_v = torch.randn((1, KV_HEADS, BLOCK, DIM), device=device, generator=gen).bfloat16()
+    cfg = CodecConfig(donor_policy="min_error", donor_backend="triton")
+    for _ in range(3):
+        quantize(block_k, cfg), quantize_values(block_v, 2, 64)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        quantize(block_k, cfg), quantize_values(block_v, 2, 64)
+    e1.record()
+    torch.cuda.synchronize()
+    seal_us = e0.elapsed_time(e1) / reps * 1e3
+    return {"append_us_all_layers": round(append_us, 2), "seal_us_per_block_and_layer": round(seal_us, 1),
+            "seal_us_per_token_amortised_all_layers": round(seal_us * LAYERS / BLOCK, 2)}
+
+
 def encoder_kernels_us(torch, k, v):
     """Device time of the two encoder launches that seal one layer (127 blocks x 4 heads of keys,
     then of values), launched back to back into preallocated outputs through the C ABI without
@@ -242,6 +277,7 @@ def run_cuda(args):
     elapsed_ms = t0.elapsed_time(t1)
     launches = batch.launches - launches_before - 3
     kernel_ms = k0.elapsed_time(k1) / reps
+    append_info = measure_append_and_seal(torch, batch, device)
     if world > 1:
         t = torch.tensor([elapsed_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -310,6 +346,7 @@ def run_cuda(args):
         "algorithmic_bytes_per_step": {k: int(v) for k, v in mean_bytes.items()},
         "encode_tokens_per_s": round(world * CONTEXT / (encode_ms * 1e-3), 1),
         "encode_ms_all_layers": round(encode_ms, 3),
+        "append": append_info,
         "encode_kernels": {"us_per_layer": round(encode_kernels_us, 1),
                            "tokens_per_s_all_layers": round(world * CONTEXT / (encode_kernels_us * 1e-6 * LAYERS), 1),
                            "hbm_frac": round((blocks_bytes_encode() / (encode_kernels_us * 1e-6) / 1e9) / measured_peak_gbs()[0], 4),
