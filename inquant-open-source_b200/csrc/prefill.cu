@@ -494,9 +494,16 @@ bool make_map(CUtensorMap* map, const void* base, int dtype, long long tokens, l
 }  // namespace
 
 
+// Cuts only pay while the items are few compared with the SMs: at most 2048 segments in all, which
+// also bounds the scratch at 2048 partial records (272 MB).
+static int max_splits(long long items) {
+  return (int)std::max<long long>(1, std::min<long long>(kPfMaxSplits, 2048 / std::max<long long>(items, 1)));
+}
+
 extern "C" int64_t inq_prefill_workspace_bytes(int32_t q_heads, int32_t q_tokens) {
   const long long items = (long long)((q_tokens + kPfRows - 1) / kPfRows) * q_heads;
-  return items * kPfMaxSplits * kPfRows * 130 * (long long)sizeof(float);
+  const int sp = max_splits(items);
+  return sp > 1 ? items * sp * kPfRows * 130 * (long long)sizeof(float) : 0;
 }
 
 extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t stream_) {
@@ -533,7 +540,7 @@ extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t s
     // merging a 133 KB partial record), measured at about six tile times
     const double tiles = ((double)a->kv_tokens - 0.5 * a->q_tokens) / kPfTile;
     double best = 1e30;
-    for (int sp = 1; sp <= kPfMaxSplits; ++sp) {
+    for (int sp = 1; sp <= max_splits(items); ++sp) {
       if (sp > 1 && (lightest / sp < 2 || !a->workspace ||
                      a->workspace_bytes < (long long)items * sp * kPfRows * 130 * (long long)sizeof(float)))
         break;

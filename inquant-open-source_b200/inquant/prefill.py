@@ -50,7 +50,7 @@ def prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tenso
     need = N.library().inq_prefill_workspace_bytes(q_heads, q_tokens)
     scratch = _SCRATCH.get(query.device)
     if scratch is None or scratch.numel() < need:
-        scratch = _SCRATCH[query.device] = torch.empty(need, dtype=torch.uint8, device=query.device)
+        scratch = _SCRATCH[query.device] = torch.empty(max(need, 16), dtype=torch.uint8, device=query.device)
     args = N.PrefillArgs(
         query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(),
         query.stride(1), query.stride(2), key.stride(1), key.stride(2), value.stride(1), value.stride(2),

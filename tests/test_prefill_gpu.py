@@ -31,6 +31,7 @@ def _reference(q, k, v, scale):
     (28, 4, 512, 2048, torch.bfloat16),    # Qwen2.5-7B head counts; items cut into 2 KV segments
     (28, 4, 2048, 6144, torch.bfloat16),   # config 2's chunk shape: 224 items cut into 3 KV segments each
     (3, 1, 300, 5000, torch.float16),      # few items over a long history: cut into 8 segments
+    (28, 4, 4224, 0, torch.bfloat16),      # a long unchunked prompt: many items, no cut, ragged last pair
 ])
 def test_prefill_attention_matches_fp32_causal_attention(q_heads, kv_heads, q_tokens, history, dtype):
     from inquant.prefill import prefill_attention
