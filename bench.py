@@ -523,11 +523,13 @@ def run_paged_batch(torch, dist, device, world, rank, block):
 
 def run_split_kv(args, torch, dist, device, world, rank):
     """Config 4: one 131072-token request, sealed blocks partitioned by sequence over the ranks,
-    partial (acc, m, l) records exchanged by ONE all-gather per step and merged locally."""
+    partial (acc, m, l) records exchanged once per step (peer-memory kernel when the ranks can
+    map one another's inbox, else an all-gather) and merged."""
     import workloads
     from inquant.cache import CacheConfig, InQuantCache
     from inquant.codec import CodecConfig
     from inquant.batched import SequenceState
+    from inquant import _native as N
     from inquant.split_kv import SplitKVDecode, shard_blocks
     context = args.split_context
     total_blocks = (context - SINK - RESIDUAL) // BLOCK
@@ -544,50 +546,62 @@ def run_split_kv(args, torch, dist, device, world, rank):
         del k, v
     seqs = [SequenceState.from_cache_layer(cache, i) for i in range(LAYERS)]
     assert all(len(s.decode_state.key_blocks) == end - start for s in seqs)
-    split = SplitKVDecode(seqs, Q_HEADS, owns_tail=last)
     gen = torch.Generator(device=device).manual_seed(99)   # the same queries on every rank
     steps = min(args.steps, 40)
     inputs = torch.randn((args.warmup + steps, LAYERS, Q_HEADS + 2 * KV_HEADS, DIM), device=device, generator=gen).bfloat16()
-    for i in range(args.warmup):
-        split.inputs.copy_(inputs[i])
-        split.step()
-    torch.cuda.synchronize()
     use_graph = not args.no_graph
-    if use_graph:
-        split.capture()
-        split.inputs.copy_(inputs[0])
-        split.replay()
-    run_step = split.replay if use_graph else split.step
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for i in range(steps):
-        split.inputs.copy_(inputs[args.warmup + i])
-        run_step()
-    t1.record()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ms = t0.elapsed_time(t1) / steps
-    local_bytes = split.batch.algorithmic_bytes()["total"]
-    stats = torch.tensor([ms, float(local_bytes)], device=device, dtype=torch.float64)
-    if world > 1:
-        worst = stats.clone()
-        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-        total = stats.clone()
-        dist.all_reduce(total, op=dist.ReduceOp.SUM)
-        ms, total_bytes = float(worst[0]), float(total[1])
+
+    def time_split(exchange):
+        split = SplitKVDecode(seqs, Q_HEADS, owns_tail=last, exchange=exchange)
+        for i in range(args.warmup):
+            split.inputs.copy_(inputs[i])
+            split.step()
+        torch.cuda.synchronize()
+        if use_graph:
+            split.capture()
+            split.inputs.copy_(inputs[0])
+            split.replay()
+        run_step = split.replay if use_graph else split.step
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(steps):
+            split.inputs.copy_(inputs[args.warmup + i])
+            run_step()
+        t1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / steps
+        local_bytes = split.batch.algorithmic_bytes()["total"]
+        stats = torch.tensor([ms, float(local_bytes)], device=device, dtype=torch.float64)
+        if world > 1:
+            worst = stats.clone()
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            total = stats.clone()
+            dist.all_reduce(total, op=dist.ReduceOp.SUM)
+            return float(worst[0]), float(total[1]), split.exchange
+        return ms, float(local_bytes), split.exchange
+
+    ms, total_bytes, exchange = time_split("auto")
+    record_bytes = LAYERS * Q_HEADS * 130 * 4
+    extra = {}
+    if exchange == "p2p":
+        how = (f"peer memory: one kernel per rank stores its {record_bytes} B of records into every peer's inbox over "
+               "NVLink, signals, waits (bounded) and merges")
+        extra["us_per_step_nccl_all_gather"] = round(time_split("nccl")[0] * 1e3, 2)
     else:
-        total_bytes = float(local_bytes)
+        how = f"one all-gather of {record_bytes} B per rank per step, then a local log-sum-exp merge"
+    if N.take_status(device):
+        raise RuntimeError("a split-KV kernel reported a failure in the status word")
     peak, _ = measured_peak_gbs()
     return {"context": context, "blocks_per_rank": end - start, "us_per_step": round(ms * 1e3, 2),
             "aggregate_gbs": round(total_bytes / (ms * 1e-3) / 1e9, 1),
             "per_gpu_hbm_frac": round(total_bytes / world / (ms * 1e-3) / 1e9 / peak, 4),
-            "exchange": f"one all-gather of {LAYERS * Q_HEADS * 130 * 4} B per rank per step, then a local log-sum-exp merge",
-            "launch": "CUDA graph of append + decode + all-gather + merge" if use_graph else "eager",
-            "steps": steps}
+            "exchange": how, "launch": "CUDA graph of append + decode + exchange + merge" if use_graph else "eager",
+            "steps": steps, **extra}
 
 
 # DRAM bytes (read + write) of one decode_kernel launch: 150.87 MB measured by ncu on the 10-layer

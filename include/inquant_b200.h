@@ -213,6 +213,44 @@ int inq_decode_attention_noalloc(const inq_decode_args_t* args /* host */, inq_s
  * across ranks after an all-gather. */
 int inq_merge_partials(const float* records, int32_t n_parts, int64_t n_rows, void* out, int32_t out_dtype,
                        inq_stream_t stream);
+/* Split-KV across the GPUs of ONE node without a library collective: exchange of the partial
+ * records over NVLink peer memory fused with their merge, one launch per rank and decode step.
+ * Every rank owns an inbox (inq_peer_buffer_create, inq_exchange_inbox_bytes bytes, zeroed) that
+ * every other process maps (inq_peer_buffer_open).  The kernel stores this rank's records into
+ * all peers' inboxes, publishes a per-chunk step flag with a release store, waits -- bounded --
+ * for the peers' flags in its own inbox and merges as inq_merge_partials does.  All ranks must
+ * launch it the same number of times; `epoch` (device int32[2], zeroed once, owned by the kernel)
+ * counts the steps.  A wait that runs out sets INQ_STATUS_WAIT_TIMEOUT in `status`, zeroes the
+ * affected output rows and returns.  At most 8 ranks; INQ_ERR_CAPACITY when the CTAs of a launch
+ * could not all be resident.  With n_local == world the entries of `ranks` are ALL ranks, emulated
+ * inside one cooperative grid on the current device (for tests on a single GPU).
+ * Replaces: nothing in the reference (it has no multi-GPU path); the merge is
+ * triton_attention.py:168-181 `_reduce_partials` applied across ranks. */
+typedef struct {
+  const float* local;     /* device: this rank's records [n_rows][130] fp32 (partial_output) */
+  void* const* inboxes;   /* HOST array [world]: the inbox of every rank as mapped here (own included) */
+  void* out;              /* device: [n_rows][128] fp16/bf16 */
+  int32_t* epoch;         /* device int32[2] */
+  int32_t* status;        /* device status word */
+  int32_t rank;
+} inq_exchange_rank_t;
+typedef struct {
+  const inq_exchange_rank_t* ranks;  /* host: 1 entry (this process), or `world` entries to emulate */
+  int32_t n_local;                   /* 1 or world */
+  int32_t world;
+  int64_t n_rows;
+  int32_t out_dtype;                 /* INQ_F16 or INQ_BF16 */
+  int32_t spin_limit;                /* polls (>= 100 ns each) before a wait gives up; 0 = default (~0.3 s) */
+} inq_exchange_args_t;
+int inq_exchange_merge(const inq_exchange_args_t* args /* host */, inq_stream_t stream);
+int64_t inq_exchange_inbox_bytes(int32_t world, int64_t n_rows);
+/* Device memory other processes of the node can map: create = cudaMalloc + zero fill + a 64-byte
+ * CUDA IPC handle to send to the peers; open maps a peer's buffer (enabling peer access);
+ * close / destroy undo open / create.  These four calls synchronise with the device. */
+int inq_peer_buffer_create(int64_t bytes, void** ptr, unsigned char* handle /* 64 bytes out */);
+int inq_peer_buffer_open(const unsigned char* handle /* 64 bytes */, void** ptr);
+int inq_peer_buffer_close(void* ptr);
+int inq_peer_buffer_destroy(void* ptr);
 /* Packed decode attention for codec variants outside the K4/V2 preset (slower, general): values
  * stored as InQuant packed tensors (value_kind 1: table columns 3..5 are payload, f32 scales, f32
  * padding, with an int8 role map like the keys') or as 2/4-bit groups of `value_group` channels

@@ -19,6 +19,7 @@ SOURCES = {
     "append.cu": [],
     "prefill.cu": [],
     "decode_generic.cu": [],
+    "exchange.cu": [],
 }
 
 

@@ -96,6 +96,16 @@ class PrefillArgs(ctypes.Structure):
                 ("workspace", c_void_p), ("workspace_bytes", c_int64)]
 
 
+class ExchangeRank(ctypes.Structure):
+    _fields_ = [("local", c_void_p), ("inboxes", ctypes.POINTER(c_void_p)), ("out", c_void_p),
+                ("epoch", c_void_p), ("status", c_void_p), ("rank", c_int32)]
+
+
+class ExchangeArgs(ctypes.Structure):
+    _fields_ = [("ranks", ctypes.POINTER(ExchangeRank)), ("n_local", c_int32), ("world", c_int32),
+                ("n_rows", c_int64), ("out_dtype", c_int32), ("spin_limit", c_int32)]
+
+
 RECORD_FLOATS = 8 * 132  # one split-KV partial: 8 query heads x (acc[128], m, l, pad)
 
 _lib = None
@@ -117,6 +127,8 @@ def library() -> ctypes.CDLL:
         lib.inq_decode_generic_workspace_floats.argtypes = [c_int32, c_int32, c_int32, c_int32, c_int32]
         lib.inq_prefill_workspace_bytes.restype = c_int64
         lib.inq_prefill_workspace_bytes.argtypes = [c_int32, c_int32]
+        lib.inq_exchange_inbox_bytes.restype = c_int64
+        lib.inq_exchange_inbox_bytes.argtypes = [c_int32, c_int64]
         lib.inq_decode_units.restype = c_int64
         lib.inq_decode_units.argtypes = [c_int32, c_int32]
         for name in EXPORTS:
@@ -135,6 +147,8 @@ EXPORTS = (
     "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
     "inq_prefill_attention", "inq_decode_generic", "inq_decode_generic_workspace_floats",
     "inq_prefill_workspace_bytes",
+    "inq_exchange_merge", "inq_exchange_inbox_bytes", "inq_peer_buffer_create", "inq_peer_buffer_open",
+    "inq_peer_buffer_close", "inq_peer_buffer_destroy",
 )
 
 
@@ -152,6 +166,11 @@ SIGNATURES = {
     "inq_merge_partials": [_P, _I, _L, _P, _I, _P],
     "inq_prefill_attention": [_P, _P],
     "inq_decode_generic": [_P, _P],
+    "inq_exchange_merge": [_P, _P],
+    "inq_peer_buffer_create": [_L, _P, _P],
+    "inq_peer_buffer_open": [_P, _P],
+    "inq_peer_buffer_close": [_P],
+    "inq_peer_buffer_destroy": [_P],
     "inq_append_token": [_P, _P],
     "inq_append_token_batch": [_P, _I, _P, _P],
 }

@@ -4,13 +4,23 @@ The sealed blocks of every layer are partitioned by sequence: rank r owns a cont
 of blocks (all layers, all KV heads), rank 0 also owns the exact sink and the last rank the
 exact tail.  Each rank runs the ordinary one-launch decode over its share but keeps the
 un-normalised ``(acc[128], m, l)`` record per (layer, query head) -- the reference's partial
-format (``triton_attention.py:162-165``).  ONE ``all_gather`` per decode step moves the records
-of all layers (``layers * q_heads * 130`` floats per rank, 408 KB for 28 x 28) over NVLink into
-local memory, and a small kernel applies the log-sum-exp merge (``inq_merge_partials``, the
-cross-rank form of ``triton_attention.py:168-181``).  Nothing else is exchanged: encode and
-append are block-local.  The reference has no multi-GPU path; this module is new.
+format (``triton_attention.py:162-165``).  The records of all layers (``layers * q_heads * 130``
+floats per rank, 408 KB for 28 x 28) are exchanged once per decode step and merged by the
+log-sum-exp rule (the cross-rank form of ``triton_attention.py:168-181``).  Two exchanges exist:
+
+``"p2p"``   ``PeerExchange``: ONE kernel of this library per rank stores the records straight into
+            every peer's inbox over NVLink peer memory (CUDA IPC mappings), signals per chunk,
+            waits (bounded) for the peers' chunks and merges them (``inq_exchange_merge``);
+``"nccl"``  one ``all_gather`` followed by the merge kernel ``inq_merge_partials``.
+
+``"auto"`` takes the first when every rank sits on the same host and the mappings can be made,
+else the second.  Nothing else is exchanged: encode and append are block-local.  The reference
+has no multi-GPU path; this module is new.
 """
 from __future__ import annotations
+
+import ctypes
+import socket
 
 import torch
 import torch.distributed as dist
@@ -54,11 +64,96 @@ def merge_records(records: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+class PeerExchange:
+    """This rank's inbox, mapped into every peer of the node, and the mappings of theirs.
+
+    Collective over ``group``: every rank constructs it with the same ``n_rows`` and calls ``run``
+    the same number of times.  ``run`` launches ONE kernel on the current stream (push to the
+    peers, signal, bounded wait, merge); a wait that runs out sets the wait-timeout bit of the
+    device status word (``_native.take_status``) instead of hanging.  Raises ``RuntimeError`` on
+    every rank when the ranks span hosts or a mapping cannot be made.
+    """
+
+    def __init__(self, n_rows: int, device: torch.device, group=None, spin_limit: int = 0):
+        if not dist.is_initialized():
+            raise RuntimeError("PeerExchange needs an initialised process group")
+        self.group, self.device, self.n_rows, self.spin_limit = group, device, int(n_rows), int(spin_limit)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        lib = N.library()
+        if not 1 <= self.world <= 8:
+            raise RuntimeError("PeerExchange serves at most 8 ranks")
+        self._own = ctypes.c_void_p()
+        self._opened: list[ctypes.c_void_p] = []
+        handle = (ctypes.c_ubyte * 64)()
+        error = None
+        with torch.cuda.device(device):
+            try:
+                N.check(lib.inq_peer_buffer_create(lib.inq_exchange_inbox_bytes(self.world, self.n_rows),
+                                                   ctypes.byref(self._own), handle), "inq_peer_buffer_create")
+            except (RuntimeError, ValueError) as exc:
+                error = str(exc)
+            offers = [None] * self.world
+            dist.all_gather_object(offers, (socket.gethostname(), bytes(handle), error), group=group)
+            pointers = [None] * self.world
+            if error is None and any(o[2] for o in offers):
+                error = "a peer could not create its inbox"
+            if error is None and len({o[0] for o in offers}) != 1:
+                error = "the ranks are not on one host"
+            if error is None:
+                for peer, (_, peer_handle, _) in enumerate(offers):
+                    if peer == self.rank:
+                        pointers[peer] = self._own.value
+                        continue
+                    mapped = ctypes.c_void_p()
+                    rc = lib.inq_peer_buffer_open((ctypes.c_ubyte * 64).from_buffer_copy(peer_handle), ctypes.byref(mapped))
+                    if rc != N.OK:
+                        error = f"mapping the inbox of rank {peer} failed: {lib.inq_last_error().decode()}"
+                        break
+                    self._opened.append(mapped)
+                    pointers[peer] = mapped.value
+            verdicts = [None] * self.world
+            dist.all_gather_object(verdicts, error, group=group)
+        if any(verdicts):
+            self.close()
+            raise RuntimeError("peer exchange unavailable: " + next(v for v in verdicts if v))
+        self._inboxes = (ctypes.c_void_p * self.world)(*pointers)
+        self._epoch = torch.zeros(2, dtype=torch.int32, device=device)
+
+    def run(self, local: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``local`` [n_rows, 130] fp32 (this rank's records) -> ``out`` [n_rows, 128] fp16/bf16, merged
+        over all ranks."""
+        if local.dtype != torch.float32 or local.shape != (self.n_rows, 130) or not local.is_contiguous():
+            raise ValueError("local must be a contiguous [n_rows, 130] float32 tensor")
+        if out.shape != (self.n_rows, 128) or not out.is_contiguous() or out.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("out must be a contiguous [n_rows, 128] fp16/bf16 tensor")
+        N.require_cuda(local, "PeerExchange.run")
+        entry = N.ExchangeRank(local.data_ptr(), self._inboxes, out.data_ptr(), self._epoch.data_ptr(),
+                               N.status_word(self.device).data_ptr(), self.rank)
+        args = N.ExchangeArgs(ctypes.pointer(entry), 1, self.world, self.n_rows, N.DTYPE_CODE[out.dtype], self.spin_limit)
+        N.check(N.library().inq_exchange_merge(ctypes.byref(args), N.stream_pointer(self.device)), "inq_exchange_merge")
+        return out
+
+    def close(self) -> None:
+        """Unmap the peers' inboxes and free this rank's.  Call it on every rank once no launch
+        that uses the exchange is still in flight anywhere (e.g. after a barrier)."""
+        lib = N.library()
+        with torch.cuda.device(self.device):
+            for mapped in self._opened:
+                lib.inq_peer_buffer_close(mapped)
+            self._opened = []
+            if self._own:
+                lib.inq_peer_buffer_destroy(self._own)
+                self._own = ctypes.c_void_p()
+
+
 class SplitKVDecode:
-    """Per-rank driver: local decode over this rank's blocks, one all-gather, local merge."""
+    """Per-rank driver: local decode over this rank's blocks, then the exchange and merge of the
+    partial records (``exchange``: "p2p", "nccl" or "auto", see the module text)."""
 
     def __init__(self, sequences: list[SequenceState], q_heads: int, group=None, dtype=torch.bfloat16,
-                 owns_tail: bool | None = None):
+                 owns_tail: bool | None = None, exchange: str = "auto"):
+        if exchange not in ("auto", "p2p", "nccl"):
+            raise ValueError("exchange must be 'auto', 'p2p' or 'nccl'")
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -67,6 +162,25 @@ class SplitKVDecode:
         n = len(sequences)
         self.gathered = torch.empty((self.world, n * q_heads, 130), dtype=torch.float32, device=self.batch.device)
         self.outputs = torch.empty((n, q_heads, 128), dtype=dtype, device=self.batch.device)
+        self.peers = None
+        if self.world > 1 and exchange != "nccl":
+            try:
+                self.peers = PeerExchange(n * q_heads, self.batch.device, group)
+            except RuntimeError:
+                if exchange == "p2p":
+                    raise
+        self.exchange = "p2p" if self.peers is not None else "nccl"
+
+    def _exchange_and_merge(self) -> None:
+        local = self.batch.partial_records.view(-1, 130)
+        if self.peers is not None:
+            self.peers.run(local, self.outputs.view(-1, 128))
+            return
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered.view(-1, 130), local, group=self.group)
+        else:
+            self.gathered[0].copy_(local)
+        merge_records(self.gathered, self.outputs.view(-1, 128))
 
     @property
     def inputs(self) -> torch.Tensor:
@@ -78,16 +192,11 @@ class SplitKVDecode:
         if append and self.owns_tail:
             self.batch.append()
         self.batch.attend()
-        local = self.batch.partial_records.view(-1, 130)
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.gathered.view(-1, 130), local, group=self.group)
-        else:
-            self.gathered[0].copy_(local)
-        merge_records(self.gathered, self.outputs.view(-1, 128))
+        self._exchange_and_merge()
         return self.outputs
 
     def capture(self) -> None:
-        """Record one step (append on the tail owner, local decode, all-gather, merge) into a CUDA
+        """Record one step (append on the tail owner, local decode, exchange, merge) into a CUDA
         graph; ``replay`` then costs one graph launch per step.  Run eager steps first: the first
         launches set kernel attributes and NCCL builds its communicator outside a capture."""
         graph = torch.cuda.CUDAGraph()
@@ -96,12 +205,7 @@ class SplitKVDecode:
             if self.owns_tail:
                 self.batch._launch_append()
             self.batch._launch_attend()
-            local = self.batch.partial_records.view(-1, 130)
-            if self.world > 1:
-                dist.all_gather_into_tensor(self.gathered.view(-1, 130), local, group=self.group)
-            else:
-                self.gathered[0].copy_(local)
-            merge_records(self.gathered, self.outputs.view(-1, 128))
+            self._exchange_and_merge()
         self.batch.tail_counters.copy_(counters)
         self._graph = graph
 

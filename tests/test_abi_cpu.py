@@ -43,3 +43,16 @@ def test_struct_mirrors_have_the_sizes_the_header_implies():
     assert ctypes.sizeof(N.DecodeSeq) == 192
     assert ctypes.sizeof(N.PrefillArgs) == 4 * 8 + 8 * 8 + 4 * 4 + 4 + 4 + 8 + 8 + 8
     assert ctypes.sizeof(N.GenericDecodeArgs) % 8 == 0
+    assert ctypes.sizeof(N.ExchangeRank) == 48 and ctypes.sizeof(N.ExchangeArgs) == 32
+
+
+def test_exchange_entry_points_check_their_arguments_without_a_gpu():
+    from inquant import _native as N
+    lib = N.library()
+    assert lib.inq_exchange_inbox_bytes(9, 10) == 0 and lib.inq_exchange_inbox_bytes(2, 0) == 0
+    assert lib.inq_exchange_inbox_bytes(2, 10) == 2 * 8 * 512 * 4 + 2 * 2 * 10 * 520
+    args = N.ExchangeArgs(None, 1, 2, 10, 2, 0)
+    assert lib.inq_exchange_merge(ctypes.byref(args), None) == N.ERR_ARGUMENT
+    assert lib.inq_peer_buffer_create(0, None, None) == N.ERR_ARGUMENT
+    assert lib.inq_peer_buffer_open(None, None) == N.ERR_ARGUMENT
+    assert lib.inq_peer_buffer_close(None) == N.ERR_ARGUMENT and lib.inq_peer_buffer_destroy(None) == N.ERR_ARGUMENT

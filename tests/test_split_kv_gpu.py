@@ -75,3 +75,56 @@ def test_single_rank_driver_graph_replay_matches_eager_steps():
         assert torch.equal(graphed.replay(), expected[i])
     with pytest.raises(RuntimeError, match="capture"):
         build().replay()
+
+
+def _emulated_exchange(records, steps=1, spin_limit=0, only_rank=None):
+    """All ranks of an exchange inside one cooperative launch on this GPU (or, with ``only_rank``,
+    that rank alone next to inboxes nobody writes).  ``records`` [world, rows, 130]."""
+    import ctypes
+    from inquant import _native as N
+    lib = N.library()
+    world, rows = records.shape[0], records.shape[1]
+    device = records.device
+    inboxes = [torch.zeros(lib.inq_exchange_inbox_bytes(world, rows), dtype=torch.uint8, device=device) for _ in range(world)]
+    table = (ctypes.c_void_p * world)(*[b.data_ptr() for b in inboxes])
+    epochs = torch.zeros((world, 2), dtype=torch.int32, device=device)
+    outs = torch.full((world, rows, 128), 7.0, dtype=torch.bfloat16, device=device)
+    ranks = range(world) if only_rank is None else [only_rank]
+    entries = (N.ExchangeRank * len(ranks))(*[
+        N.ExchangeRank(records[r].data_ptr(), table, outs[r].data_ptr(), epochs[r].data_ptr(),
+                       N.status_word(device).data_ptr(), r) for r in ranks])
+    args = N.ExchangeArgs(entries, len(ranks), world, rows, N.DTYPE_CODE[torch.bfloat16], spin_limit)
+    for _ in range(steps):
+        N.check(lib.inq_exchange_merge(ctypes.byref(args), N.stream_pointer(device)), "inq_exchange_merge")
+    torch.cuda.synchronize()
+    return outs, epochs
+
+
+@pytest.mark.parametrize("world,rows", [(2, 84), (3, 61), (8, 84), (2, 4500)])
+def test_peer_exchange_protocol_with_all_ranks_in_one_cooperative_launch(world, rows):
+    """Push, per-chunk flags, wait and merge of inq_exchange_merge: every emulated rank must end
+    with exactly what the all-gather + inq_merge_partials path computes, on odd and even steps."""
+    from inquant import _native as N
+    from inquant.split_kv import merge_records
+    gen = torch.Generator(device="cuda").manual_seed(world * 1000 + rows)
+    records = torch.randn((world, rows, 130), device="cuda", generator=gen)
+    records[:, :, 128] *= 8.0                       # running maxima, base-2 units
+    records[:, :, 129] = records[:, :, 129].abs() + 0.5
+    expected = merge_records(records.contiguous(), torch.empty((rows, 128), dtype=torch.bfloat16, device="cuda"))
+    for steps in (1, 2, 3):
+        outs, epochs = _emulated_exchange(records, steps=steps)
+        assert N.take_status(torch.device("cuda", 0)) == 0
+        assert epochs[:, 0].tolist() == [steps] * world and epochs[:, 1].tolist() == [0] * world
+        for r in range(world):
+            assert torch.equal(outs[r], expected)
+
+
+def test_peer_exchange_wait_gives_up_and_reports_when_a_peer_never_signals():
+    """Rank 0 of a two-rank exchange alone: the flag of rank 1 is never set, so the bounded wait
+    runs out, the status word carries the timeout bit and the rows are zeroed."""
+    from inquant import _native as N
+    records = torch.ones((2, 20, 130), device="cuda")
+    outs, epochs = _emulated_exchange(records, spin_limit=200, only_rank=0)
+    assert N.take_status(torch.device("cuda", 0)) == N.STATUS_WAIT_TIMEOUT
+    assert int(epochs[0, 0]) == 1
+    assert torch.count_nonzero(outs[0]) == 0
