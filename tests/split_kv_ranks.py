@@ -57,8 +57,8 @@ def main() -> None:
         assert N.take_status(device) == 0
         results[exchange] = outs
         for got, want in zip(outs, expected):
-            error = (got.float() - want.float()).abs().max().item()
-            assert error <= 8e-3, (exchange, error)
+            # the merge order differs from the unsplit kernel's: one bf16 ulp (2^-7 relative) of slack
+            assert torch.allclose(got.float(), want.float(), atol=4e-3, rtol=2.0 ** -7), exchange
     for a, b in zip(results["nccl"], results["p2p"]):
         assert torch.equal(a, b)
     dist.barrier()
