@@ -376,12 +376,84 @@ def run_cuda(args):
         line["paged_batch"]["pages_of_64_tokens"] = {
             k: v for k, v in run_paged_batch(torch, dist, device, world, rank, 64).items()
             if k in ("us_per_step", "decode_tokens_per_s", "aggregate_gbs", "per_gpu_hbm_frac", "algorithmic_bytes_per_step")}
+    if world == 1 and args.model_step:
+        torch.cuda.empty_cache()
+        line["model_step"] = run_model_step(args, torch, device)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sample_layers=1)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_model_step(args, torch, device):
+    """Opt-in leg: one decode token of a randomly initialised Qwen2.5-7B-shaped model (28 layers,
+    hidden 3584, 28/4 heads of 128, vocabulary 152064, bf16) over a 32768-token packed cache,
+    through the model adapter layer by layer (eager) and as one replayed CUDA graph."""
+    import time
+    import workloads
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.graph_decode import GraphedDecodeStep
+    from inquant.qwen_fused import enable_fused_attention
+    config = Qwen2Config(vocab_size=152064, hidden_size=Q_HEADS * DIM, intermediate_size=18944, head_dim=DIM,
+                         num_hidden_layers=LAYERS, num_attention_heads=Q_HEADS, num_key_value_heads=KV_HEADS,
+                         max_position_embeddings=131072, attn_implementation="sdpa")
+    previous = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(device):
+            model = Qwen2ForCausalLM(config).eval()
+    finally:
+        torch.set_default_dtype(previous)
+    weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
+    context = CONTEXT
+    cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=BLOCK, residual_length=RESIDUAL,
+                                     sink_tokens=SINK, value_bits=2, value_group_size=64, validate_positions=False))
+    for layer in range(LAYERS):   # the history is synthetic: the adapter only needs a filled cache
+        k, v = workloads.make_kv_torch(70000 + layer, KV_HEADS, context, device)
+        cache.update(k, v, layer)
+        del k, v
+    result = {"workload": f"config 1 shapes with the model around the attention: {LAYERS}-layer Qwen2.5-7B-shaped random-init "
+                          f"model, {context}-token packed history, batch 1, greedy decode",
+              "weights_gb": round(weight_bytes / 1e9, 2)}
+    with enable_fused_attention(model), torch.no_grad():
+        token = torch.tensor([[17]], device=device)
+        for _ in range(3):
+            model(token, past_key_values=cache)
+        torch.cuda.synchronize()
+        steps = 20
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            model(token, past_key_values=cache)
+        torch.cuda.synchronize()
+        result["eager_ms_per_token"] = round((time.perf_counter() - t0) / steps * 1e3, 3)
+        stepper = GraphedDecodeStep(model, cache)
+        stepper.step(17)
+        for _ in range(3):
+            stepper.step()
+        torch.cuda.synchronize()
+        steps = 60
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            stepper.step()
+        e1.record()
+        torch.cuda.synchronize()
+        result["graphed_ms_per_token"] = round((time.perf_counter() - t0) / steps * 1e3, 3)
+        result["graphed_device_ms_per_token"] = round(e0.elapsed_time(e1) / steps, 3)
+        result["graph_replays"], result["eager_seal_steps"] = stepper.replays, stepper.eager_steps
+        stepper.close()
+    peak, _ = measured_peak_gbs()
+    kv_bytes = LAYERS * KV_HEADS * ((CONTEXT - SINK - RESIDUAL) // BLOCK) * BLOCK * 104
+    result["hbm_floor_ms"] = round((weight_bytes + kv_bytes) / (peak * 1e9) * 1e3, 3)
+    result["hbm_frac_graphed"] = round(result["hbm_floor_ms"] / result["graphed_device_ms_per_token"], 4)
+    del model, cache
+    torch.cuda.empty_cache()
+    return result
 
 
 def run_prefill(torch, device):
@@ -776,6 +848,8 @@ def main():
     parser.add_argument("--skip-e2e", action="store_true", help="profiler captures: skip the host-buffer leg")
     parser.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill leg (config 2, one layer)")
     parser.add_argument("--no-paged-batch", action="store_true", help="skip the batched paged decode leg (config 3)")
+    parser.add_argument("--model-step", action="store_true",
+                        help="also time a whole-model decode token (random-init 7B-shaped model) eagerly and from one CUDA graph")
     args = parser.parse_args()
     globals()["LAYERS"] = args.layers
     args.warmup = max(args.warmup, 3) if args.impl == "cuda" else args.warmup

@@ -147,7 +147,10 @@ def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False,
             isinstance(cache, InQuantCache)
             and hidden_states.shape[1] == 1
             and cache.get_seq_length(attention.layer_idx) > 0
-            and attention_mask is None
+            # inside a graphed step (inquant.graph_decode) the model may hand over the all-true
+            # causal mask of a single query token, which Transformers materialises while a
+            # stream is capturing; batch one has no padding, so it carries no information
+            and (attention_mask is None or attention._inquant_graph_batch is not None)
             and not kwargs.get("output_attentions", False)
         )
         use_prefill = (
@@ -196,6 +199,17 @@ def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False,
         value = attention.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
         cos, sin = position_embeddings
         query, key = apply_rotary_pos_emb(query, key, cos, sin)
+        graph_batch = attention._inquant_graph_batch
+        if graph_batch is not None:
+            # graph-safe step (inquant.graph_decode): the tail length lives in a device counter and
+            # the cache's host bookkeeping is applied afterwards, so nothing here depends on the step
+            graph_batch.queries[0].copy_(query[0, :, 0])
+            graph_batch.new_keys[0].copy_(key[0, :, 0])
+            graph_batch.new_values[0].copy_(value[0, :, 0])
+            graph_batch._launch_append()
+            graph_batch._launch_attend()
+            attention._inquant_fused_decode_calls += 1
+            return attention.o_proj(graph_batch.outputs.reshape(*input_shape, -1)), None
         view = cache.append_for_attention(
             key, value, attention.layer_idx,
             {"sin": sin, "cos": cos, "cache_position": cache_position},
@@ -229,6 +243,7 @@ def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False,
         module._inquant_fused_decode_calls = 0
         module._inquant_cpu_reference_calls = 0
         module._inquant_fused_prefill_calls = 0
+        module._inquant_graph_batch = None
         module.forward = MethodType(forward, module)
     return FusedQwen2Handle(originals)
 
