@@ -985,25 +985,37 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   __syncthreads();
   if (s_is_last) {
   __threadfence();
-    // weights of all (query head, part) pairs first, in parallel, then one pass over the records
-    float* mw = (float*)warp_base;                 // [8][np] weights, then [8] normalisers
-    const float* base = P.partials + ((long long)first_cta + pair) * kRecordFloats;
+    // A sequence decoded alone is cut into a hundred parts per pair, so this merge is written for
+    // many loads in flight: (m, l) of every (query head, part) are staged first, the weights
+    // come from shared memory, and each thread then sums 8 channels of one head over the parts
+    // with 16 vector loads outstanding.
+    float* mw = (float*)warp_base;                 // [8][np] running maxima, then weights
     const int np = n_cta_pair;
-    float* norm = mw + 8 * np;
+    float* lw = mw + 8 * np;                       // [8][np] partial normalisers
+    float* norm = lw + 8 * np;
     float* mtop = norm + 8;
+    const float* base = P.partials + ((long long)first_cta + pair) * kRecordFloats;
     float* const partial = SEQ(partial_out);
-    if (threadIdx.x < 8) norm[threadIdx.x] = 0.f;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < 8 * np; i += kThreads) {
+      const int g = i & 7, p = i >> 3;
+      if (g < g_valid) {
+        const float2 ml = __ldcg((const float2*)(base + (long long)p * kRecordFloats + g * kRecordStride + 128));
+        mw[g * np + p] = ml.x;
+        lw[g * np + p] = ml.y;
+      }
+    }
+    __syncthreads();
     for (int g = warp; g < g_valid; g += kWarps) {
       float top = kNegBig;
-      for (int p = lane; p < np; p += 32) top = fmaxf(top, __ldcg(base + (long long)p * kRecordFloats + g * kRecordStride + 128));
+      for (int p = lane; p < np; p += 32) top = fmaxf(top, mw[g * np + p]);
 #pragma unroll
       for (int off = 16; off; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
       float l = 0.f;
       for (int p = lane; p < np; p += 32) {
-        const float* rec = base + (long long)p * kRecordFloats + g * kRecordStride;
-        const float wt = fast_exp2(__ldcg(rec + 128) - top);
+        const float wt = fast_exp2(mw[g * np + p] - top);
         mw[g * np + p] = wt;
-        l = fmaf(__ldcg(rec + 129), wt, l);
+        l = fmaf(lw[g * np + p], wt, l);
       }
 #pragma unroll
       for (int off = 16; off; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
@@ -1013,32 +1025,49 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       }
     }
     __syncthreads();
-    const int c = threadIdx.x;
-    QT* out = (QT*)SEQ(out);
-    for (int g = 0; g < g_valid; ++g) {
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-      const float* rec = base + g * kRecordStride + c;
+    const int g = threadIdx.x >> 4, c8 = (threadIdx.x & 15) * 8;   // kThreads = 128: 8 heads x 16 threads
+    if (g < g_valid) {
+      float o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = 0.f;
+      const float* rec = base + g * kRecordStride + c8;
+      const float* wg = mw + g * np;
       int p = 0;
-      for (; p + 4 <= np; p += 4) {
-        const float v0 = __ldcg(rec + (long long)(p + 0) * kRecordFloats), v1 = __ldcg(rec + (long long)(p + 1) * kRecordFloats);
-        const float v2 = __ldcg(rec + (long long)(p + 2) * kRecordFloats), v3 = __ldcg(rec + (long long)(p + 3) * kRecordFloats);
-        o0 = fmaf(v0, mw[g * np + p], o0);
-        o1 = fmaf(v1, mw[g * np + p + 1], o1);
-        o2 = fmaf(v2, mw[g * np + p + 2], o2);
-        o3 = fmaf(v3, mw[g * np + p + 3], o3);
+      for (; p + 8 <= np; p += 8) {
+        float4 va[8], vb[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          va[u] = __ldcg((const float4*)(rec + (long long)(p + u) * kRecordFloats));
+          vb[u] = __ldcg((const float4*)(rec + (long long)(p + u) * kRecordFloats) + 1);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float wt = wg[p + u];
+          o[0] = fmaf(va[u].x, wt, o[0]); o[1] = fmaf(va[u].y, wt, o[1]); o[2] = fmaf(va[u].z, wt, o[2]); o[3] = fmaf(va[u].w, wt, o[3]);
+          o[4] = fmaf(vb[u].x, wt, o[4]); o[5] = fmaf(vb[u].y, wt, o[5]); o[6] = fmaf(vb[u].z, wt, o[6]); o[7] = fmaf(vb[u].w, wt, o[7]);
+        }
       }
-      for (; p < np; ++p) o0 = fmaf(__ldcg(rec + (long long)p * kRecordFloats), mw[g * np + p], o0);
-      const float o = (o0 + o1) + (o2 + o3);
+      for (; p < np; ++p) {
+        const float4 va = __ldcg((const float4*)(rec + (long long)p * kRecordFloats));
+        const float4 vb = __ldcg((const float4*)(rec + (long long)p * kRecordFloats) + 1);
+        const float wt = wg[p];
+        o[0] = fmaf(va.x, wt, o[0]); o[1] = fmaf(va.y, wt, o[1]); o[2] = fmaf(va.z, wt, o[2]); o[3] = fmaf(va.w, wt, o[3]);
+        o[4] = fmaf(vb.x, wt, o[4]); o[5] = fmaf(vb.y, wt, o[5]); o[6] = fmaf(vb.z, wt, o[6]); o[7] = fmaf(vb.w, wt, o[7]);
+      }
       if (partial) {
         // this rank's share of a sequence split across GPUs: keep the record un-normalised
         float* rec_out = partial + (q_head0 + g) * 130;
-        rec_out[c] = o;
-        if (c == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) *(float2*)(rec_out + c8 + k) = make_float2(o[k], o[k + 1]);
+        if (c8 == 0) {
           rec_out[128] = mtop[g];
           rec_out[129] = norm[g];
         }
       } else {
-        out[(q_head0 + g) * 128 + c] = from_float<QT>(o / norm[g]);
+        QT* out = (QT*)SEQ(out) + (q_head0 + g) * 128 + c8;
+        const float inv = norm[g];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) out[k] = from_float<QT>(o[k] / inv);
       }
     }
   }
