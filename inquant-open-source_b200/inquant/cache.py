@@ -131,6 +131,34 @@ def _quantize_temporal_blocks(tensor, block_count, block_size, config):
     return [ArenaPackedTensor(packed, index, shape, tensor.dtype) for index in range(block_count)]
 
 
+def restore_blocks(blocks, out: torch.Tensor, position: int) -> int:
+    """Dequantise ``blocks`` into ``out`` [1, H, tokens, C] from token ``position`` on; returns the
+    position after the last block.  Blocks sealed by one call share an encoder arena: each arena is
+    dequantised by one launch instead of block by block."""
+    heads, channels = out.shape[1], out.shape[3]
+    index = 0
+    while index < len(blocks):
+        arena = getattr(blocks[index], "_arena", None)
+        run = 1
+        if arena is not None and arena[1] == 0:
+            while index + run < len(blocks):
+                other = getattr(blocks[index + run], "_arena", None)
+                if other is None or other[0] is not arena[0] or other[1] != run:
+                    break
+                run += 1
+        tokens = blocks[index].shape[2]
+        if run > 1 and run == arena[0].shape[0]:
+            dense = arena[0].dequantize(dtype=out.dtype)            # [run, heads, tokens, channels]
+            out[0, :, position:position + run * tokens].view(heads, run, tokens, channels).copy_(
+                dense.permute(1, 0, 2, 3))
+        else:
+            run = 1
+            out[:, :, position:position + tokens].copy_(blocks[index].dequantize(dtype=out.dtype))
+        position += run * tokens
+        index += run
+    return position
+
+
 class InQuantCache(_HFCache):
     """Immutable quantized history plus exact sink and a bounded recent tail
     (reference ``cache.py:122-419``)."""
@@ -203,6 +231,21 @@ class InQuantCache(_HFCache):
         if layer_idx == 0:
             self._seen_tokens = layer.seq_length
         return full_key, full_value
+
+    @torch.no_grad()
+    def extend(self, key_states, value_states, layer_idx, cache_kwargs=None) -> None:
+        """``update`` without its return value: the new states are appended and full blocks sealed
+        exactly as ``update`` does (reference ``cache.py:179-200``), but the dense history is
+        neither built nor returned.  Not in the reference; used by ``inquant.prefill``, which keeps
+        its own dense history across the chunks of a prompt."""
+        layer = self._validate_update(key_states, value_states, layer_idx, cache_kwargs)
+        if layer is None:
+            layer = _Layer(tuple(key_states.shape), key_states.dtype, key_states.device)
+        self._append(layer, key_states, value_states)
+        self._layers[layer_idx] = layer
+        self.record_peak(layer_idx)
+        if layer_idx == 0:
+            self._seen_tokens = layer.seq_length
 
     def _validate_update(self, key_states, value_states, layer_idx, cache_kwargs):
         if not isinstance(layer_idx, int) or layer_idx < 0:
@@ -386,8 +429,6 @@ class InQuantCache(_HFCache):
         layer = self._layers[layer_idx]
 
         def restore(sink, blocks, tail):
-            # blocks sealed by one call share an encoder arena: each arena is dequantised by one
-            # launch straight into its place in the output instead of block by block
             _, heads, _, channels = layer.shape
             sink_tokens = 0 if sink is None else sink.shape[2]
             tail_tokens = 0 if tail is None else tail.shape[2]
@@ -396,26 +437,7 @@ class InQuantCache(_HFCache):
                               dtype=layer.dtype, device=layer.device)
             if sink_tokens:
                 out[:, :, :sink_tokens].copy_(sink)
-            position, index = sink_tokens, 0
-            while index < len(blocks):
-                arena = getattr(blocks[index], "_arena", None)
-                run = 1
-                if arena is not None and arena[1] == 0:
-                    while index + run < len(blocks):
-                        other = getattr(blocks[index + run], "_arena", None)
-                        if other is None or other[0] is not arena[0] or other[1] != run:
-                            break
-                        run += 1
-                tokens = blocks[index].shape[2]
-                if run > 1 and run == arena[0].shape[0]:
-                    dense = arena[0].dequantize(dtype=layer.dtype)            # [run, heads, tokens, channels]
-                    out[0, :, position:position + run * tokens].view(heads, run, tokens, channels).copy_(
-                        dense.permute(1, 0, 2, 3))
-                else:
-                    run = 1
-                    out[:, :, position:position + tokens].copy_(blocks[index].dequantize(dtype=layer.dtype))
-                position += run * tokens
-                index += run
+            position = restore_blocks(blocks, out, sink_tokens)
             if tail_tokens:
                 out[:, :, position:].copy_(tail)
             return out

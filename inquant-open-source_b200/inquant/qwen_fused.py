@@ -16,7 +16,8 @@ Differences from the reference, none visible through the call signatures:
   tokens of an ``InQuantCache`` through this library's tcgen05 prefill kernel
   (``inquant.prefill.prefill_chunk``) instead of the stock forward; the chunk is attended
   causally and any mask the model built is ignored, so enable it only for unpadded batch-one
-  prompts;
+  prompts.  A ``PrefillHistory`` of the cache stored by the caller as ``cache._prefill_history``
+  is used (the dense history is then kept across chunks instead of being rebuilt per chunk);
 * there is no CPU path in this library: ``allow_cpu_reference`` is accepted for signature
   compatibility, but a non-CUDA decode step always raises (the reference would run its
   materialising oracle there), and ``cpu_reference_calls`` therefore stays 0.
@@ -172,7 +173,10 @@ def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False,
             value = attention.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
             cos, sin = position_embeddings
             query, key = apply_rotary_pos_emb(query, key, cos, sin)
-            result = prefill_chunk(cache, query, key, value, attention.layer_idx, attention.scaling)
+            history = getattr(cache, "_prefill_history", None)
+            if history is not None and history.cache is not cache:
+                history = None
+            result = prefill_chunk(cache, query, key, value, attention.layer_idx, attention.scaling, history=history)
             attention._inquant_fused_prefill_calls += 1
             output = result.transpose(1, 2).reshape(*input_shape, -1).contiguous()
             return attention.o_proj(output), None

@@ -87,3 +87,52 @@ def test_prefill_chunks_through_the_cache_match_one_shot_attention_over_material
         attention_close(to_numpy(out.float())[0], to_numpy(_reference(q, full_k, full_v, scale))[0])
     for a, b in zip(cache.materialize(0), shadow.materialize(0)):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("value_bits,chunk_sizes", [(2, (256, 256, 256, 100, 37)), (None, (300, 212)), (4, (64, 1, 500))])
+def test_prefill_history_holds_exactly_what_update_would_return(value_bits, chunk_sizes):
+    """The dense history kept across chunks is bit-identical to the tensors `InQuantCache.update`
+    rebuilds per chunk, so the two forms of `prefill_chunk` give the same attention, and both caches
+    end up with the same contents."""
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.prefill import PrefillHistory, prefill_chunk
+    gen = torch.Generator(device="cuda").manual_seed(23)
+    heads, q_heads = 2, 14
+    cfg = CacheConfig(CodecConfig(donor_policy="min_error"), block_size=64, residual_length=16, sink_tokens=4,
+                      value_bits=value_bits, value_group_size=64)
+    cache, shadow, plain = InQuantCache(cfg), InQuantCache(cfg), InQuantCache(cfg)
+    history = PrefillHistory(cache, capacity_tokens=128)      # forces the tensors to grow
+    scale, seen = 128 ** -0.5, 0
+    for tokens in chunk_sizes:
+        q = torch.randn((1, q_heads, tokens, 128), device="cuda", generator=gen).bfloat16()
+        k = torch.randn((1, heads, tokens, 128), device="cuda", generator=gen).bfloat16()
+        v = torch.randn((1, heads, tokens, 128), device="cuda", generator=gen).bfloat16()
+        out = prefill_chunk(cache, q, k, v, 0, scale, history=history)
+        full_k, full_v = shadow.update(k, v, 0)
+        seen += tokens
+        key, value = history._layers[0][0], history._layers[0][1]
+        assert history._layers[0][2] == seen == cache.get_seq_length(0)
+        assert torch.equal(out, prefill_chunk(plain, q, k, v, 0, scale))
+        attention_close(to_numpy(out.float())[0], to_numpy(_reference(q, full_k, full_v, scale))[0])
+        # after sealing, the history equals what the NEXT update would put before its new states
+        next_k, next_v = shadow.materialize(0)
+        assert torch.equal(key[:, :, :seen], next_k) and torch.equal(value[:, :, :seen], next_v)
+    for a, b in zip(cache.materialize(0), shadow.materialize(0)):
+        assert torch.equal(a, b)
+    assert history.nbytes > 0
+    # a history first used on a filled layer takes the dense state over from the cache
+    late = PrefillHistory(plain)
+    q = torch.randn((1, q_heads, 50, 128), device="cuda", generator=gen).bfloat16()
+    k = torch.randn((1, heads, 50, 128), device="cuda", generator=gen).bfloat16()
+    assert torch.equal(prefill_chunk(plain, q, k, k, 0, scale, history=late), prefill_chunk(cache, q, k, k, 0, scale, history=history))
+    seen += 50
+    # an update behind the history's back is detected
+    k = torch.randn((1, heads, 8, 128), device="cuda", generator=gen).bfloat16()
+    cache.update(k, k, 0)
+    with pytest.raises(RuntimeError, match="state mismatch"):
+        prefill_chunk(cache, torch.zeros((1, q_heads, 8, 128), device="cuda", dtype=torch.bfloat16), k, k, 0, scale, history=history)
+    with pytest.raises(ValueError, match="another cache"):
+        prefill_chunk(plain, torch.zeros((1, q_heads, 8, 128), device="cuda", dtype=torch.bfloat16), k, k, 0, scale, history=history)
+    history.release()
+    assert history.nbytes == 0

@@ -81,7 +81,8 @@ def test_generate_runs_through_the_packed_path():
     assert handle.fused_decode_calls + handle.cpu_reference_calls >= 0
 
 
-def test_chunked_prefill_through_the_tensor_core_kernel_matches_the_stock_forward():
+@pytest.mark.parametrize("keep_history", [False, True])
+def test_chunked_prefill_through_the_tensor_core_kernel_matches_the_stock_forward(keep_history):
     """A 300-token prompt fed as chunks of 100: with fused_prefill the later chunks run this
     library's prefill kernel over the packed history; logits must agree with the stock forward,
     which materialises the same history and calls SDPA with the model's causal mask."""
@@ -95,6 +96,9 @@ def test_chunked_prefill_through_the_tensor_core_kernel_matches_the_stock_forwar
     tokens = torch.randint(2, 90, (1, 300), device="cuda")
     with enable_fused_attention(model, fused_prefill=True) as handle, torch.no_grad():
         expected_cache, packed = InQuantCache(config), InQuantCache(config)
+        if keep_history:   # the dense history is kept across chunks instead of rebuilt per chunk
+            from inquant.prefill import PrefillHistory
+            packed._prefill_history = PrefillHistory(packed)
         for start in range(0, 300, 100):
             chunk = tokens[:, start:start + 100]
             expected = twin(chunk, past_key_values=expected_cache).logits
@@ -102,6 +106,8 @@ def test_chunked_prefill_through_the_tensor_core_kernel_matches_the_stock_forwar
             # two attention implementations in bf16: up to three bf16 steps of order-one logits
             torch.testing.assert_close(actual.float(), expected.float(), rtol=.035, atol=.024)
         assert handle.fused_prefill_calls == 2 and handle.fused_decode_calls == 0
+        if keep_history:
+            assert packed._prefill_history._layers[0][2] == 300
         token = torch.tensor([[7]], device="cuda")
         torch.testing.assert_close(model(token, past_key_values=packed).logits.float(),
                                    twin(token, past_key_values=expected_cache).logits.float(), rtol=.035, atol=.016)
