@@ -480,6 +480,7 @@ def run_prefill(torch, device):
         for c0 in range(0, CONTEXT, chunk):
             prefill_chunk(cache, q[:, :, c0:c0 + chunk], k[:, :, c0:c0 + chunk], v[:, :, c0:c0 + chunk], 0, scale,
                           history=history)
+        history.check()
     for _ in range(2):
         whole_layer()
     torch.cuda.synchronize()

@@ -436,26 +436,47 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_kernel(const PrefillPar
 }
 
 // Merges the KV segments of every item: out = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m).
-// One block per (item, 8 rows), one thread per channel.
+// One block per (item, 8 rows): a warp owns a row, a lane four channels, and the loads of all
+// segments are issued before the first is used.
+constexpr int kPfMergeRows = 8;
 template <typename QT>
-__global__ void __launch_bounds__(kPfTile) prefill_merge_kernel(const PrefillParams P) {
-  const int item = blockIdx.x, c = threadIdx.x;
+__global__ void __launch_bounds__(kPfMergeRows * 32) prefill_merge_kernel(const PrefillParams P) {
+  const int item = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qp = P.n_qpairs - 1 - item / P.q_heads, head = item % P.q_heads;
-  for (int r = 0; r < 8; ++r) {
-    const int row = blockIdx.y * 8 + r, q_row = qp * kPfRows + row;
-    if (q_row >= P.q_tokens) continue;
-    const float* base = P.records + ((long long)item * P.splits * kPfRows + row) * 130;
-    float top = kPfNegBig;
-    for (int sgm = 0; sgm < P.splits; ++sgm) top = fmaxf(top, base[(long long)sgm * kPfRows * 130 + 128]);
-    float o = 0.f, l = 0.f;
-    for (int sgm = 0; sgm < P.splits; ++sgm) {
-      const float* rec = base + (long long)sgm * kPfRows * 130;
-      const float w = pf_exp2(rec[128] - top);
-      o = fmaf(rec[c], w, o);
-      l = fmaf(rec[129], w, l);
+  const int row = blockIdx.y * kPfMergeRows + warp, q_row = qp * kPfRows + row;
+  if (q_row >= P.q_tokens) return;
+  const float* base = P.records + ((long long)item * P.splits * kPfRows + row) * 130;   // rows are 520 B apart: 8-byte aligned
+  float2 ml[kPfMaxSplits], va[kPfMaxSplits], vb[kPfMaxSplits];
+#pragma unroll
+  for (int sgm = 0; sgm < kPfMaxSplits; ++sgm) {
+    if (sgm < P.splits) {
+      const float2* rec = (const float2*)(base + (long long)sgm * kPfRows * 130);
+      ml[sgm] = __ldcg(rec + 64);
+      va[sgm] = __ldcg(rec + 2 * lane);
+      vb[sgm] = __ldcg(rec + 2 * lane + 1);
     }
-    ((QT*)P.out)[(long long)head * P.o_sh + (long long)q_row * P.o_st + c] = from_float<QT>(o / l);
   }
+  float top = kPfNegBig;
+#pragma unroll
+  for (int sgm = 0; sgm < kPfMaxSplits; ++sgm)
+    if (sgm < P.splits) top = fmaxf(top, ml[sgm].x);
+  float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f, l = 0.f;
+#pragma unroll
+  for (int sgm = 0; sgm < kPfMaxSplits; ++sgm) {
+    if (sgm < P.splits) {
+      const float w = pf_exp2(ml[sgm].x - top);
+      o0 = fmaf(va[sgm].x, w, o0);
+      o1 = fmaf(va[sgm].y, w, o1);
+      o2 = fmaf(vb[sgm].x, w, o2);
+      o3 = fmaf(vb[sgm].y, w, o3);
+      l = fmaf(ml[sgm].y, w, l);
+    }
+  }
+  QT* out = (QT*)P.out + (long long)head * P.o_sh + (long long)q_row * P.o_st + 4 * lane;
+  out[0] = from_float<QT>(o0 / l);
+  out[1] = from_float<QT>(o1 / l);
+  out[2] = from_float<QT>(o2 / l);
+  out[3] = from_float<QT>(o3 / l);
 }
 
 }  // namespace inq
@@ -568,11 +589,11 @@ extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t s
   if (a->dtype == INQ_F16) {
     INQ_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
     prefill_kernel<__half><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P, map_q, map_k, map_v);
-    if (P.splits > 1) prefill_merge_kernel<__half><<<dim3((unsigned)(ctas / P.splits), kPfRows / 8), kPfTile, 0, stream>>>(P);
+    if (P.splits > 1) prefill_merge_kernel<__half><<<dim3((unsigned)(ctas / P.splits), kPfRows / kPfMergeRows), kPfMergeRows * 32, 0, stream>>>(P);
   } else {
     INQ_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
     prefill_kernel<__nv_bfloat16><<<(unsigned)ctas, kPfThreads, kPfSmem, stream>>>(P, map_q, map_k, map_v);
-    if (P.splits > 1) prefill_merge_kernel<__nv_bfloat16><<<dim3((unsigned)(ctas / P.splits), kPfRows / 8), kPfTile, 0, stream>>>(P);
+    if (P.splits > 1) prefill_merge_kernel<__nv_bfloat16><<<dim3((unsigned)(ctas / P.splits), kPfRows / kPfMergeRows), kPfMergeRows * 32, 0, stream>>>(P);
   }
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;

@@ -218,6 +218,31 @@ def take_status(device: torch.device) -> int:
     return value
 
 
+_deferred_depth = 0
+
+
+class deferred_status:
+    """Inside this context the encoders do not read the status word after a launch (no stream
+    synchronisation); failure bits stay in the word until ``take_status`` is called."""
+
+    def __enter__(self):
+        global _deferred_depth
+        _deferred_depth += 1
+        return self
+
+    def __exit__(self, *_exc):
+        global _deferred_depth
+        _deferred_depth -= 1
+
+
+def nonfinite_reported(device: torch.device) -> bool:
+    """The encoders' finite check: reads and clears the status word (a synchronisation) unless
+    status reads are deferred."""
+    if _deferred_depth:
+        return False
+    return bool(take_status(device) & STATUS_NONFINITE)
+
+
 def pointer(tensor: torch.Tensor | None) -> c_void_p:
     return c_void_p(None if tensor is None or tensor.numel() == 0 else tensor.data_ptr())
 

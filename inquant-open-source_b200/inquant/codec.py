@@ -236,6 +236,6 @@ def quantize(x: torch.Tensor, config: CodecConfig = CodecConfig()) -> PackedTens
     padding = torch.empty((batch, heads, count), dtype=torch.float32, device=device)
     encode_into(x.detach(), config, N.compact_field(payload, heads), N.compact_field(scales, heads),
                 N.compact_field(salient, heads), N.compact_field(donors, heads), N.compact_field(padding, heads))
-    if N.take_status(device) & N.STATUS_NONFINITE:
+    if N.nonfinite_reported(device):
         raise ValueError("x must contain finite values representable in float32")
     return PackedTensor(payload, scales, salient, donors, padding, tuple(x.shape), x.dtype)

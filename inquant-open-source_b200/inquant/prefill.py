@@ -73,19 +73,35 @@ class PrefillHistory:
     reads the tensors in place, and after the cache has sealed blocks only those new blocks are
     dequantised over the exact rows they replace.  Every block is restored once.
 
+    With ``defer_checks`` (the default) the encoders' finite check does not synchronise after every
+    seal: a non-finite input sets a bit in the device status word instead of raising at once, and
+    ``check`` -- to be called when the prompt is done -- raises the ``ValueError`` then (the cache
+    contents are undefined after that; reset it).  ``defer_checks=False`` keeps the reference's
+    behaviour of raising inside the call, at one stream synchronisation per sealed tensor.
+
     The price is memory: 2 * layers * H * tokens * C elements of the model dtype while the prompt
     is being prefilled (1.9 GB for 32768 tokens of a 28-layer, 4-KV-head model); ``release`` frees
     it.  Tensors grow geometrically unless ``capacity_tokens`` covers the prompt.
     """
 
-    def __init__(self, cache, capacity_tokens: int = 4096):
+    def __init__(self, cache, capacity_tokens: int = 4096, defer_checks: bool = True):
         if capacity_tokens < 1:
             raise ValueError("capacity_tokens must be positive")
-        self.cache, self.capacity_tokens = cache, int(capacity_tokens)
+        self.cache, self.capacity_tokens, self.defer_checks = cache, int(capacity_tokens), bool(defer_checks)
         self._layers: dict[int, list] = {}    # layer -> [key, value, tokens, restored blocks]
 
     def release(self) -> None:
         self._layers.clear()
+
+    def check(self) -> None:
+        """Raise for failures recorded while checks were deferred (synchronises the stream)."""
+        devices = {state[0].device for state in self._layers.values() if state[0] is not None}
+        for device in devices:
+            status = N.take_status(device)
+            if status & N.STATUS_NONFINITE:
+                raise ValueError("K/V must contain finite values representable in float32 (reported by a deferred check)")
+            if status:
+                raise RuntimeError(f"a kernel reported status {status} during the prefill")
 
     @property
     def nbytes(self) -> int:
@@ -126,7 +142,11 @@ class PrefillHistory:
         state[0][:, :, seen:seen + tokens].copy_(key)
         state[1][:, :, seen:seen + tokens].copy_(value)
         out = prefill_attention(query, state[0][:, :, :seen + tokens], state[1][:, :, :seen + tokens], scale)
-        cache.extend(key, value, layer_idx, cache_kwargs)
+        if self.defer_checks:
+            with N.deferred_status():
+                cache.extend(key, value, layer_idx, cache_kwargs)
+        else:
+            cache.extend(key, value, layer_idx, cache_kwargs)
         layer = cache._layers[layer_idx]
         if len(layer.key_blocks) > state[3]:
             # blocks follow the sink; the block length is fixed per cache

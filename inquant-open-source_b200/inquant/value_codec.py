@@ -126,7 +126,7 @@ def quantize_values(x, bits=2, group_size=64):
     offsets = torch.empty_like(scales)
     encode_values_into(x.detach(), bits, group_size, N.compact_field(payload, heads),
                        N.compact_field(scales, heads), N.compact_field(offsets, heads))
-    if N.take_status(device) & N.STATUS_NONFINITE:
+    if N.nonfinite_reported(device):
         raise ValueError("Values and stored FP16 quantization parameters must be finite")
     return PackedValues(payload, scales, offsets, tuple(x.shape), x.dtype, bits, group_size)
 

@@ -136,3 +136,25 @@ def test_prefill_history_holds_exactly_what_update_would_return(value_bits, chun
         prefill_chunk(plain, torch.zeros((1, q_heads, 8, 128), device="cuda", dtype=torch.bfloat16), k, k, 0, scale, history=history)
     history.release()
     assert history.nbytes == 0
+
+
+def test_prefill_history_reports_non_finite_input_at_check_or_at_once():
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.prefill import PrefillHistory, prefill_chunk
+    cfg = CacheConfig(CodecConfig(donor_policy="min_error"), block_size=64, residual_length=16, sink_tokens=4, value_bits=2)
+    q = torch.zeros((1, 4, 200, 128), device="cuda", dtype=torch.bfloat16)
+    k = torch.randn((1, 2, 200, 128), device="cuda").bfloat16()
+    bad = k.clone()
+    bad[0, 1, 30, 7] = float("inf")
+    cache = InQuantCache(cfg)
+    history = PrefillHistory(cache)
+    prefill_chunk(cache, q, k, k, 0, history=history)
+    history.check()                                  # nothing to report
+    prefill_chunk(cache, q, bad, k, 0, history=history)   # deferred: no exception here
+    with pytest.raises(ValueError, match="finite"):
+        history.check()
+    history.check()                                  # the report clears the word
+    strict = InQuantCache(cfg)
+    with pytest.raises(ValueError, match="finite"):
+        prefill_chunk(strict, q, bad, k, 0, history=PrefillHistory(strict, defer_checks=False))
