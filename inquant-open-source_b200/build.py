@@ -15,7 +15,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relax
 SOURCES = {
     "lib.cu": [],
     "codec.cu": ["-fmad=false"],
-    "decode.cu": ["-DINQ_DECODE_SUB=" + os.environ.get("INQ_DECODE_SUB", "2")],
+    "decode.cu": [],
     "append.cu": [],
     "prefill.cu": [],
     "decode_generic.cu": [],

@@ -38,14 +38,18 @@ namespace inq {
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr int kStages = 3;
-#ifndef INQ_DECODE_SUB
-#define INQ_DECODE_SUB 2                             // 16-token sub-slices per loop iteration (1 or 2)
-#endif
-constexpr int kSub = INQ_DECODE_SUB;
-constexpr int kSliceTokens = 16 * kSub;             // tokens staged and processed per loop iteration
-constexpr int kCtasPerSm = kSub == 1 ? 4 : 3;       // register budget: 128 vs 168 per thread
-constexpr int kStageK = 1024 * kSub, kStageV = 512 * kSub, kStageP = 128 * kSub;
-constexpr int kStageBytes = kStageK + kStageV + kStageP;
+// Tokens per loop iteration are a template parameter of the kernel: SUB = 2 (32 tokens) for
+// blocks above 16 tokens, SUB = 1 (16 tokens) for smaller blocks (16-token pages), where every
+// slice is a whole block and its metadata rides inside the slice's own ring stage.
+template <int SUB>
+struct SliceCfg {
+  static constexpr int kSliceTokens = 16 * SUB;       // tokens staged and processed per loop iteration
+  static constexpr int kStageK = 1024 * SUB, kStageV = 512 * SUB, kStageP = 128 * SUB;
+  static constexpr int kStageMeta = SUB == 1 ? 1024 : 0;   // K scales 512 B | role map 256 B | padding 256 B
+  static constexpr int kStageBytes = kStageK + kStageV + kStageP + kStageMeta;
+};
+constexpr int kPlanSliceTokens = 32;                // the unit of the flat work list (equal for both SUB when a block has <= 16 tokens)
+constexpr int kCtasPerSm = 3;                       // register budget: 168 per thread
 constexpr int kRecordStride = 132;                  // floats per query head: acc[128], m, l, pad
 constexpr int kRecordFloats = 8 * kRecordStride;    // one partial record (8 query heads)
 constexpr int kQChunk = 36;                         // padded 32-float chunk of the staged query
@@ -54,8 +58,8 @@ constexpr float kNegBig = -1.0e30f;
 constexpr int kWarpFixed = 2048 + 256 + 64 + 64 + 1024;  // per-warp scratch before the per-group parts
 constexpr float kRescaleSlack = 4.f;   // the running reference maximum may lag the true one by 2^4
 
-__host__ __device__ constexpr int warp_smem_bytes(int groups) {
-  return kWarpFixed + groups * (256 + 4096 + 64) + kStages * kStageBytes;
+__host__ __device__ constexpr int warp_smem_bytes(int groups, int stage_bytes) {
+  return kWarpFixed + groups * (256 + 4096 + 64) + kStages * stage_bytes;
 }
 
 struct SeqDesc {
@@ -233,8 +237,11 @@ __device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const l
 // Stage layout: K nibbles [32 tokens][64 B]; V codes [32 tokens][2 x 16 B] with the two halves
 // of tokens 4..7 (mod 8) swapped so that the later word reads of tokens 2j, 2j+1, 2j+8, 2j+9
 // fall into distinct banks; V scale pairs [32] and V offset pairs [32] (4 B each).
+template <int kSub>
 __device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned char* kp, const unsigned char* vp,
                                             const unsigned char* vs, const unsigned char* vo, int tok0, int T, int lane) {
+  constexpr int kSliceTokens = SliceCfg<kSub>::kSliceTokens;
+  constexpr int kStageK = SliceCfg<kSub>::kStageK, kStageV = SliceCfg<kSub>::kStageV, kStageP = SliceCfg<kSub>::kStageP;
   const int v_dst = kStageK + (((lane >> 1) * 2 + ((lane & 1) ^ ((lane >> 3) & 1))) << 4);
   // parameter vectors: 4 bytes (two fp16 group values) per token; with 16-token slices the lower
   // half-warp copies the scales and the upper half-warp the offsets
@@ -274,8 +281,14 @@ __device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned
 }
 
 // ------------------------------------------------------------------------------------------ the kernel
-template <int MODE, typename QT, bool SAL>
+template <int MODE, typename QT, bool SAL, int SUB>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const DecodeParams P) {
+  constexpr int kSub = SUB;
+  constexpr int kSliceTokens = SliceCfg<SUB>::kSliceTokens;
+  constexpr int kStageK = SliceCfg<SUB>::kStageK, kStageV = SliceCfg<SUB>::kStageV, kStageP = SliceCfg<SUB>::kStageP;
+  constexpr int kStageBytes = SliceCfg<SUB>::kStageBytes;
+  constexpr bool kMetaInStage = SliceCfg<SUB>::kStageMeta > 0;   // host guarantees one slice per block
+  constexpr int kMetaOffset = kStageK + kStageV + kStageP;
   extern __shared__ __align__(16) unsigned char smem[];
   float* qs = (float*)smem;                                             // 8 heads x 4 chunks x kQChunk
   float* qinv = qs + 8 * 4 * kQChunk;   // per head: softmax scale * log2(e) * 2^(exponent of max|q| - 12)
@@ -284,7 +297,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
   const int groups = (P.n_pad + 15) >> 4;                               // salient channels in groups of 16
-  const int warp_bytes = warp_smem_bytes(groups);
+  const int warp_bytes = warp_smem_bytes(groups, kStageBytes);
   unsigned char* const wb = warp_base + warp * warp_bytes;
   // folded-query B fragments of the 8 K steps ([step][lane] x 8 bytes); while a block's weights
   // are being derived the same 2 KB hold the per-channel slot weights and additive constants
@@ -293,8 +306,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   unsigned char* wsrc = (unsigned char*)(wssc + 64);                    // channel of salient i
   unsigned char* wdon = wsrc + 64;                                      // its donor slot
   unsigned char* wmeta = wdon + 64;       // staged block metadata: K scales 512 B | role map 256 B | padding 256 B
-  float* ff = (float*)wmeta;              // during a fold: slot weight per channel, over the staged K scales
-  float* fk0 = ff + 128;                  // during a fold: additive constant per channel, over role map and padding
   unsigned char* wqsal = wb + kWarpFixed;                               // B fragments: query at salient channels
   unsigned char* wsel = wqsal + groups * 256;                           // B fragments: nibble selection
   unsigned short* wcell = (unsigned short*)(wsel + groups * 4096);      // selection cells written by the last fold (offsets into wsel)
@@ -497,22 +508,27 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     int to_issue = n_my, issue_stage = 0;
     int meta_block = -1;        // block whose metadata is staged (or in flight) in wmeta
     int folded_block = -2;      // last block whose weights were derived from wmeta
-    auto stage_meta = [&](const BlockPtrs& bp) {
-      cp_async16(wmeta + lane * 16, bp.ks + lane * 16);
-      if (lane < (MODE == 0 ? 8 : 16)) cp_async16(wmeta + 512 + lane * 16, bp.kr + lane * 16);
-      for (int i = lane; i < P.n_pad; i += 32) cp_async4(wmeta + 768 + i * 4, bp.kpad + i * 4);
+    auto stage_meta = [&](const BlockPtrs& bp, unsigned char* dst) {
+      cp_async16(dst + lane * 16, bp.ks + lane * 16);
+      if (lane < (MODE == 0 ? 8 : 16)) cp_async16(dst + 512 + lane * 16, bp.kr + lane * 16);
+      for (int i = lane; i < P.n_pad; i += 32) cp_async4(dst + 768 + i * 4, bp.kpad + i * 4);
     };
     auto issue = [&]() {
       if (to_issue > 0) {
-        // a new block's metadata rides in the same group as its first slice, provided the
-        // staging area is no longer needed by an earlier block
-        const bool first_of_block = to_issue == n_my || pf_slice == 0;
-        if (first_of_block && (meta_block < 0 || folded_block == meta_block)) {
-          stage_meta(pf_ptrs);
-          meta_block = pf_block;
+        unsigned char* const stage_ptr = ring + issue_stage * kStageBytes;
+        if (kMetaInStage) {
+          // every slice is a whole block: its metadata travels in the slice's own stage
+          stage_meta(pf_ptrs, stage_ptr + kMetaOffset);
+        } else {
+          // a new block's metadata rides in the same group as its first slice, provided the
+          // staging area is no longer needed by an earlier block
+          const bool first_of_block = to_issue == n_my || pf_slice == 0;
+          if (first_of_block && (meta_block < 0 || folded_block == meta_block)) {
+            stage_meta(pf_ptrs, wmeta);
+            meta_block = pf_block;
+          }
         }
-        stage_slice(ring + issue_stage * kStageBytes, pf_ptrs.kp, pf_ptrs.vp, pf_ptrs.vs, pf_ptrs.vo,
-                    pf_slice * kSliceTokens, T, lane);
+        stage_slice<kSub>(stage_ptr, pf_ptrs.kp, pf_ptrs.vp, pf_ptrs.vs, pf_ptrs.vo, pf_slice * kSliceTokens, T, lane);
         --to_issue;
         if (++issue_stage == kStages) issue_stage = 0;
         if (++pf_slice == spb) {
@@ -555,27 +571,36 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     for (int it = 0; it < n_my; ++it) {
       cp_async_wait<kStages - 2>();
       __syncwarp();
-      issue();
+      // With fewer than three slices per block the next block's metadata can only be staged once
+      // this block's fold has released the staging area: there the copies are issued after the
+      // fold.  Otherwise they go out first.
+      const bool issue_late = !kMetaInStage && spb < 3 && need_weights;
+      if (!issue_late) issue();
 
       if (need_weights) {
         // ---- fold this block's descriptor, scales and padding into the query
-        if (meta_block != cur_block) {
+        unsigned char* meta = wmeta;
+        if (kMetaInStage) {
+          meta = ring + stage_index * kStageBytes + kMetaOffset;
+        } else if (meta_block != cur_block) {
           // not prefetched (very short blocks): fetch now and wait for it alone
           BlockPtrs cb = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, cur_block, h);
           __syncwarp();
-          stage_meta(cb);
+          stage_meta(cb, wmeta);
           cp_async_commit();
           cp_async_wait<0>();
           meta_block = cur_block;
           __syncwarp();
         }
         folded_block = cur_block;
+        float* const ff = (float*)meta;     // during a fold: slot weight per channel, over the staged K scales
+        float* const fk0 = ff + 128;        // during a fold: additive constant per channel, over role map and padding
         // step 1: this lane owns channels 4*lane .. 4*lane+3
-        const unsigned char* meta_roles = wmeta + 512;
+        const unsigned char* meta_roles = meta + 512;
         int role[4], sidx[4];
         float scv[4], fv[4], kv[4];
         {
-          const float4 sc = *(const float4*)(wmeta + lane * 16);
+          const float4 sc = *(const float4*)(meta + lane * 16);
           scv[0] = sc.x; scv[1] = sc.y; scv[2] = sc.z; scv[3] = sc.w;
           if (MODE == 0) {
             const unsigned bits = *(const unsigned*)(meta_roles + lane * 4);
@@ -616,7 +641,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
             // donor: its slot holds the low nibble of a salient code; the reference stores the
             // sampled mean as the channel's own value and rounds it to the model dtype
             fv[i] = 0.f;
-            kv[i] = to_float<QT>(from_float<QT>(((const float*)(wmeta + 768))[-role[i] - 2]));
+            kv[i] = to_float<QT>(from_float<QT>(((const float*)(meta + 768))[-role[i] - 2]));
           }
         }
         if (bad) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
@@ -696,6 +721,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         beta[0] = __shfl_sync(0xffffffffu, cpart, (2 * j) * 4);
         beta[1] = __shfl_sync(0xffffffffu, cpart, (2 * j + 1) * 4);
         need_weights = false;
+        if (issue_late) {
+          __syncwarp();   // every lane has read the per-channel terms: the staging area is free
+          issue();
+        }
       }
 
       const unsigned stage = launder(ring_addr + stage_index * kStageBytes);
@@ -1076,7 +1105,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
 }
 
 #undef SEQ
-static int smem_bytes(int groups) { return kQBytes + kWarps * warp_smem_bytes(groups); }
+static int smem_bytes(int groups, int sub) {
+  return kQBytes + kWarps * warp_smem_bytes(groups, sub == 1 ? SliceCfg<1>::kStageBytes : SliceCfg<2>::kStageBytes);
+}
 
 }  // namespace inq
 
@@ -1101,7 +1132,7 @@ struct Plan {
   int n_pairs;
 };
 
-static int spb_of(int block_tokens) { return (block_tokens + kSliceTokens - 1) / kSliceTokens; }
+static int spb_of(int block_tokens) { return (block_tokens + kPlanSliceTokens - 1) / kPlanSliceTokens; }
 
 static Plan make_plan(long long total_units, int n_pairs, long long uniform_units, int ctas_per_sm) {
   Plan p;
@@ -1152,19 +1183,26 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
     total = uniform * n_pairs;
   }
   const int groups = (a->n_pad + 15) / 16;
-  const int shared = smem_bytes(groups);
+  // blocks of at most 16 tokens (16-token pages) take the 16-token-slice kernel: one slice per
+  // block either way, so the work list does not depend on the choice
+  const int sub = a->block_tokens <= 16 ? 1 : 2;
+  const int shared = smem_bytes(groups, sub);
   typedef void (*kernel_t)(const DecodeParams);
-  static const kernel_t kernels[8] = {
-      decode_kernel<0, __half, false>, decode_kernel<0, __half, true>,
-      decode_kernel<0, __nv_bfloat16, false>, decode_kernel<0, __nv_bfloat16, true>,
-      decode_kernel<1, __half, false>, decode_kernel<1, __half, true>,
-      decode_kernel<1, __nv_bfloat16, false>, decode_kernel<1, __nv_bfloat16, true>};
-  static bool raised[8] = {};
-  static int per_sm[8][5] = {};
-  const int which = a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);
+  static const kernel_t kernels[16] = {
+      decode_kernel<0, __half, false, 2>, decode_kernel<0, __half, true, 2>,
+      decode_kernel<0, __nv_bfloat16, false, 2>, decode_kernel<0, __nv_bfloat16, true, 2>,
+      decode_kernel<1, __half, false, 2>, decode_kernel<1, __half, true, 2>,
+      decode_kernel<1, __nv_bfloat16, false, 2>, decode_kernel<1, __nv_bfloat16, true, 2>,
+      decode_kernel<0, __half, false, 1>, decode_kernel<0, __half, true, 1>,
+      decode_kernel<0, __nv_bfloat16, false, 1>, decode_kernel<0, __nv_bfloat16, true, 1>,
+      decode_kernel<1, __half, false, 1>, decode_kernel<1, __half, true, 1>,
+      decode_kernel<1, __nv_bfloat16, false, 1>, decode_kernel<1, __nv_bfloat16, true, 1>};
+  static bool raised[16] = {};
+  static int per_sm[16][5] = {};
+  const int which = (sub == 1 ? 8 : 0) + a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);
   const kernel_t kernel = kernels[which];
   if (!raised[which]) {
-    INQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4)));
+    INQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4, sub)));
     raised[which] = true;
   }
   if (!per_sm[which][groups]) {

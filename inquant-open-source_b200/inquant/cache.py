@@ -128,7 +128,7 @@ def _quantize_temporal_blocks(tensor, block_count, block_size, config):
     ).permute(1, 0, 2, 3)
     packed = quantize(blocked, config)
     shape = (1, heads, block_size, channels)
-    return [ArenaPackedTensor(packed, index, shape, tensor.dtype) for index in range(block_count)]
+    return ArenaPackedTensor.split(packed, block_count, shape, tensor.dtype)
 
 
 def restore_blocks(blocks, out: torch.Tensor, position: int) -> int:
@@ -379,13 +379,17 @@ class InQuantCache(_HFCache):
             else:
                 pending_key = torch.cat((layer.residual_key, pending_key), dim=2)
                 pending_value = torch.cat((layer.residual_value, pending_value), dim=2)
-        new_keys = _quantize_temporal_blocks(pending_key, blocks, cfg.block_size, cfg.codec)
-        if cfg.value_bits is None:
-            new_values = _quantize_temporal_blocks(pending_value, blocks, cfg.block_size, cfg.codec)
-        else:
-            from .value_codec import quantize_value_blocks
-            new_values = quantize_value_blocks(pending_value, blocks, cfg.block_size, cfg.value_bits,
-                                               cfg.value_group_size)
+        # Both encoders are launched before either finite check is read: the key and value kernels
+        # run back to back while the host builds the block views and the new tail, and one read of
+        # the status word (one synchronisation instead of two) decides before any state changes.
+        with N.deferred_status():
+            new_keys = _quantize_temporal_blocks(pending_key, blocks, cfg.block_size, cfg.codec)
+            if cfg.value_bits is None:
+                new_values = _quantize_temporal_blocks(pending_value, blocks, cfg.block_size, cfg.codec)
+            else:
+                from .value_codec import quantize_value_blocks
+                new_values = quantize_value_blocks(pending_value, blocks, cfg.block_size, cfg.value_bits,
+                                                   cfg.value_group_size)
         offset = blocks * cfg.block_size
         remainder = pending_key.shape[2] - offset
         # a new tail buffer: views handed out earlier keep the old one alive and unchanged
@@ -393,6 +397,13 @@ class InQuantCache(_HFCache):
         if remainder:
             tail_key_buffer[:, :, :remainder].copy_(pending_key[:, :, offset:])
             tail_value_buffer[:, :, :remainder].copy_(pending_value[:, :, offset:])
+        if blocks and N.nonfinite_reported(layer.device):
+            # the failure path alone works out which tensor it was (same messages as the codecs)
+            if not bool(torch.isfinite(pending_key[:, :, :offset]).all()):
+                raise ValueError("x must contain finite values representable in float32")
+            if cfg.value_bits is None:
+                raise ValueError("x must contain finite values representable in float32")
+            raise ValueError("Values and stored FP16 quantization parameters must be finite")
         if take_sink:
             layer.sink_key_buffer[:, :, layer.sink_count:layer.sink_count + take_sink].copy_(keys[:, :, :take_sink])
             layer.sink_value_buffer[:, :, layer.sink_count:layer.sink_count + take_sink].copy_(values[:, :, :take_sink])

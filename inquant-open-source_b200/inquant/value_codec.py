@@ -70,6 +70,22 @@ class ArenaPackedValues(PackedValues):
         object.__setattr__(self, "bits", arena.bits)
         object.__setattr__(self, "group_size", arena.group_size)
 
+    @classmethod
+    def split(cls, arena: PackedValues, count: int, shape, original_dtype) -> list:
+        """The ``count`` blocks of ``arena`` as a list (see ``codec.ArenaPackedTensor.split``)."""
+        new, blocks = object.__new__, []
+        bits, group_size = arena.bits, arena.group_size
+        for index in range(count):
+            block = new(cls)
+            fields = block.__dict__
+            fields["_arena"] = (arena, index)
+            fields["shape"] = shape
+            fields["original_dtype"] = original_dtype
+            fields["bits"] = bits
+            fields["group_size"] = group_size
+            blocks.append(block)
+        return blocks
+
     def __getattr__(self, name):
         if name in ArenaPackedValues._FIELDS:
             arena, index = self.__dict__["_arena"]
@@ -143,4 +159,4 @@ def quantize_value_blocks(tensor, block_count, block_size, bits, group_size):
         heads, block_count, block_size, channels).permute(1, 0, 2, 3)
     packed = quantize_values(blocked, bits, group_size)
     shape = (1, heads, block_size, channels)
-    return [ArenaPackedValues(packed, index, shape, tensor.dtype) for index in range(block_count)]
+    return ArenaPackedValues.split(packed, block_count, shape, tensor.dtype)
