@@ -84,7 +84,8 @@ struct DecodeParams {
   SeqDesc one;
   int n_seq, H, G, T, n_pad;
   int n_ctas, n_pairs;
-  long long per_cta, total_units, uniform_units;   // flat work decomposition
+  long long per_cta, total_units, uniform_units;   // flat work decomposition (total_units counts the ramp units too)
+  long long ramp_units;                            // list positions every pair is charged for its fixed costs
   const long long* pair_starts;                    // [n_pairs + 1] or nullptr when every pair has uniform_units
   float scale_log2e;
   long long page_bytes;
@@ -280,6 +281,17 @@ __device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned
   }
 }
 
+// Optional phase stamps (build with -DINQ_DECODE_TIMING): per CTA, per visited pair (first two) and
+// per warp the SM clock at the phase boundaries, the global timer at both ends, the SM id and the
+// slices of the visit; read back through inq_debug_decode_phases.  Off in the shipped library.
+#ifdef INQ_DECODE_TIMING
+__device__ long long g_phase[512][2][4][12];
+#define INQ_STAMP(k) do { if (lane == 0 && blockIdx.x < 512 && visit < 2) g_phase[blockIdx.x][visit][warp][k] = clock64(); } while (0)
+#define INQ_GSTAMP(k) do { if (lane == 0 && blockIdx.x < 512 && visit < 2) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_phase[blockIdx.x][visit][warp][k] = t; } } while (0)
+#else
+#define INQ_STAMP(k)
+#define INQ_GSTAMP(k)
+#endif
 // ------------------------------------------------------------------------------------------ the kernel
 template <int MODE, typename QT, bool SAL, int SUB>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const DecodeParams P) {
@@ -315,6 +327,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   // Flat decomposition: the packed slices of all (sequence, KV head, head tile) pairs form one
   // list that is cut into gridDim.x equal ranges; a CTA walks its range pair by pair.
   const int gtiles = (P.G + 7) >> 3;
+  // Every pair starts with `ramp_units` list positions that hold no slices: they stand for the
+  // fixed cost a CTA pays per pair it touches (query staging, first copies, dense slices, record,
+  // merge), so a CTA whose range crosses into the next pair is given fewer slices.  A CTA that
+  // reaches only the ramp of a pair leaves that pair alone.
+  const long long R = P.ramp_units;
   const long long c_begin = (long long)blockIdx.x * P.per_cta;
   const long long c_end = min(c_begin + P.per_cta, P.total_units);
   long long pos = c_begin;
@@ -323,17 +340,25 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     int lo = 0, hi = P.n_pairs - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
-      if (P.pair_starts[mid] <= pos) lo = mid; else hi = mid - 1;
+      if (P.pair_starts[mid] + mid * R <= pos) lo = mid; else hi = mid - 1;
     }
     pair = lo;
   } else {
-    pair = (int)(pos / P.uniform_units);
+    pair = (int)(pos / (P.uniform_units + R));
   }
+  int visit = -1;   // read by the optional phase stamps only
+  (void)visit;
   for (; pos < c_end; ++pair) {
-  const long long pair_lo = P.pair_starts ? P.pair_starts[pair] : (long long)pair * P.uniform_units;
-  const long long pair_hi = P.pair_starts ? P.pair_starts[pair + 1] : pair_lo + P.uniform_units;
-  const long long seg_lo = pos - pair_lo, seg_hi = min(c_end, pair_hi) - pair_lo;
-  pos = pair_lo + seg_hi;
+  const long long pair_lo = (P.pair_starts ? P.pair_starts[pair] : (long long)pair * P.uniform_units) + (pair + 1) * R;   // first slice
+  const long long pair_hi = (P.pair_starts ? P.pair_starts[pair + 1] : (long long)(pair + 1) * P.uniform_units) + (pair + 1) * R;
+  const long long seg_lo = max(pos, pair_lo) - pair_lo, seg_hi = min(c_end, pair_hi) - pair_lo;
+  pos = min(c_end, pair_hi);
+  if (seg_hi <= seg_lo) continue;   // only ramp positions of this pair fall into the range
+  ++visit;
+  INQ_STAMP(0); INQ_GSTAMP(8);
+#ifdef INQ_DECODE_TIMING
+  if (lane == 0 && blockIdx.x < 512 && visit < 2) { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); g_phase[blockIdx.x][visit][warp][10] = smid; g_phase[blockIdx.x][visit][warp][11] = seg_hi - seg_lo; }
+#endif
   const int first_cta = (int)(pair_lo / P.per_cta), last_cta = (int)((pair_hi - 1) / P.per_cta);
   const int n_cta_pair = last_cta - first_cta + 1;
   const int seq = pair / (P.H * gtiles);
@@ -359,10 +384,21 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   // query as fp32, chunked so that lanes (head, chunk) read distinct banks, then scaled per head by
   // a power of two that brings its largest magnitude into [2^12, 2^13): every folded weight is
   // then a product below 2^14 that fp16 holds without overflow and with full precision
-  for (int idx = threadIdx.x; idx < 8 * 128; idx += kThreads) {
-    int g = idx >> 7, c = idx & 127;
-    float v = g < g_valid ? to_float<QT>(qptr[(q_head0 + g) * q_stride + c]) : 0.f;
-    qs[(g * 4 + (c >> 5)) * kQChunk + (c & 31)] = v;
+  if ((((unsigned long long)qptr | (unsigned long long)(q_stride * (long long)sizeof(QT))) & 15ull) == 0) {
+    // one 16-byte load per thread: head g = thread / 16, channels 8 * (thread % 16) .. + 7
+    const int g = threadIdx.x >> 4, c0 = (threadIdx.x & 15) * 8;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (g < g_valid) raw = *(const uint4*)(qptr + (q_head0 + g) * q_stride + c0);
+    const QT* e = (const QT*)&raw;
+    float* dst = qs + (g * 4 + (c0 >> 5)) * kQChunk + (c0 & 31);
+    *(float4*)dst = make_float4(to_float<QT>(e[0]), to_float<QT>(e[1]), to_float<QT>(e[2]), to_float<QT>(e[3]));
+    *(float4*)(dst + 4) = make_float4(to_float<QT>(e[4]), to_float<QT>(e[5]), to_float<QT>(e[6]), to_float<QT>(e[7]));
+  } else {
+    for (int idx = threadIdx.x; idx < 8 * 128; idx += kThreads) {
+      int g = idx >> 7, c = idx & 127;
+      float v = g < g_valid ? to_float<QT>(qptr[(q_head0 + g) * q_stride + c]) : 0.f;
+      qs[(g * 4 + (c >> 5)) * kQChunk + (c & 31)] = v;
+    }
   }
   __syncthreads();
 #pragma unroll
@@ -383,6 +419,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   }
   __syncthreads();
 
+  INQ_STAMP(1);
   const int T = P.T;
   const int spb = (T + kSliceTokens - 1) / kSliceTokens;   // packed slices per block
   const int n_blocks = SEQ(n_blocks);
@@ -430,6 +467,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       const long long kst = is_sink ? SEQ(sink_k_st) : SEQ(tail_k_st), vst = is_sink ? SEQ(sink_v_st) : SEQ(tail_v_st);
       const int last = count - 1;
       float S[4] = {0.f, 0.f, 0.f, 0.f};
+      // the value rows are requested together with the key rows: one exposed latency, not two
+      const QT* vA = vb + (long long)min(tok0 + 2 * j, last) * vst;
+      const QT* vB = vb + (long long)min(tok0 + 2 * j + 1, last) * vst;
+      const QT* vC = vb + (long long)min(tok0 + 2 * j + 8, last) * vst;
+      const QT* vD = vb + (long long)min(tok0 + 2 * j + 9, last) * vst;
+      uint4 vrow[2][4];
       {
         const QT* k_lo = kb + (long long)min(tok0 + r, last) * kst;
         const QT* k_hi = kb + (long long)min(tok0 + r + 8, last) * kst;
@@ -438,6 +481,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         for (int m = 0; m < 4; ++m) {
           x[m] = *(const uint4*)(k_lo + (4 * m + j) * 8);
           y[m] = *(const uint4*)(k_hi + (4 * m + j) * 8);
+        }
+#pragma unroll
+        for (int gr = 0; gr < 2; ++gr) {
+          const int ch = 64 * gr + 8 * r;
+          vrow[gr][0] = *(const uint4*)(vA + ch);
+          vrow[gr][1] = *(const uint4*)(vB + ch);
+          vrow[gr][2] = *(const uint4*)(vC + ch);
+          vrow[gr][3] = *(const uint4*)(vD + ch);
         }
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
@@ -478,15 +529,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       l_run[1] += p1 + p3;
       const unsigned b0 = movmatrix_trans(pack_qt2<QT>(p0, p1));
       const unsigned b1 = movmatrix_trans(pack_qt2<QT>(p2, p3));
-      const QT* vA = vb + (long long)min(tok0 + 2 * j, last) * vst;
-      const QT* vB = vb + (long long)min(tok0 + 2 * j + 1, last) * vst;
-      const QT* vC = vb + (long long)min(tok0 + 2 * j + 8, last) * vst;
-      const QT* vD = vb + (long long)min(tok0 + 2 * j + 9, last) * vst;
 #pragma unroll
       for (int gr = 0; gr < 2; ++gr) {
-        const int ch = 64 * gr + 8 * r;
-        const uint4 A = *(const uint4*)(vA + ch), Bv = *(const uint4*)(vB + ch);
-        const uint4 C = *(const uint4*)(vC + ch), Dv = *(const uint4*)(vD + ch);
+        const uint4 A = vrow[gr][0], Bv = vrow[gr][1], C = vrow[gr][2], Dv = vrow[gr][3];
         const unsigned av[4] = {A.x, A.y, A.z, A.w}, bv[4] = {Bv.x, Bv.y, Bv.z, Bv.w};
         const unsigned cv[4] = {C.x, C.y, C.z, C.w}, dv[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
 #pragma unroll
@@ -544,6 +589,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     // the dense slices of this warp hide behind the DRAM latency of the first packed slices;
     // their contribution is brought into the packed loop's per-row units (powers of two)
     dense_part();
+    INQ_STAMP(2);
     {
       const float ix[4] = {1.f / 16777216.f, 1.f / 1048576.f, 1.f / 65536.f, 1.f / 4194304.f};
       const float iy[4] = {1.f / 4194304.f, 1.f / 262144.f, 1.f / 16777216.f, 1.f / 1048576.f};
@@ -571,6 +617,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     for (int it = 0; it < n_my; ++it) {
       cp_async_wait<kStages - 2>();
       __syncwarp();
+#ifdef INQ_DECODE_TIMING
+      if (it == 0) INQ_STAMP(3);
+#endif
       // With fewer than three slices per block the next block's metadata can only be staged once
       // this block's fold has released the staging area: there the copies are issued after the
       // fold.  Otherwise they go out first.
@@ -929,6 +978,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         need_weights = true;
       }
     }
+    INQ_STAMP(4);
     cp_async_wait<0>();
     // a code at bit offset o of its 16-bit lane was multiplied as code * 2^(o-24)
     const float fx[4] = {16777216.f, 1048576.f, 65536.f, 4194304.f};   // offsets 0, 4, 8, 2
@@ -958,6 +1008,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     osum[gr][1] = __shfl_sync(0xffffffffu, oacc[1], gr * 4 + j);
   }
   __syncthreads();   // every warp is done with its ring and weight scratch
+  INQ_STAMP(5);
   float* wout = (float*)ring;   // [8][132]
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
@@ -1012,6 +1063,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     if (s_is_last) P.counters[pair] = 0;   // scratch is left zeroed for the next launch
   }
   __syncthreads();
+  INQ_STAMP(6);
   if (s_is_last) {
   __threadfence();
     // A sequence decoded alone is cut into a hundred parts per pair, so this merge is written for
@@ -1101,6 +1153,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     }
   }
   __syncthreads();   // shared scratch is reused by the next pair of this CTA
+  INQ_STAMP(7); INQ_GSTAMP(9);
   }  // pairs of this CTA
 }
 
@@ -1128,15 +1181,19 @@ static int sm_count() {
 // Flat decomposition shared by the planner and the launcher.
 struct Plan {
   int n_ctas;
-  long long per_cta, total, uniform_units;
+  long long per_cta, total, uniform_units, ramp_units;
   int n_pairs;
 };
 
 static int spb_of(int block_tokens) { return (block_tokens + kPlanSliceTokens - 1) / kPlanSliceTokens; }
 
+// List positions charged per pair for its fixed costs, in slices: a visit of a pair costs a CTA
+// 11-14 us (measured with the phase stamps) against ~0.45 us per 32-token slice of a 256-token
+// block; 12..36 all beat 0 on the 28-layer, 32768-token step (157.8 us at 24 against 163.1).
+constexpr long long kRampUnits = 24;
+
 static Plan make_plan(long long total_units, int n_pairs, long long uniform_units, int ctas_per_sm) {
   Plan p;
-  p.total = total_units;
   p.n_pairs = n_pairs;
   p.uniform_units = uniform_units;
   long long slots = (long long)sm_count() * ctas_per_sm;
@@ -1146,8 +1203,14 @@ static Plan make_plan(long long total_units, int n_pairs, long long uniform_unit
   const long long by_pairs = 64ll * n_pairs;
   long long n = slots < by_work ? slots : by_work;
   if (n > by_pairs) n = by_pairs;
-  p.per_cta = (total_units + n - 1) / n;
-  p.n_ctas = (int)((total_units + p.per_cta - 1) / p.per_cta);
+  // the ramp charge never exceeds half of an even share of slices
+  long long ramp = kRampUnits;
+  const long long share = total_units / n;
+  if (ramp > share / 2) ramp = share / 2;
+  p.ramp_units = ramp;
+  p.total = total_units + ramp * n_pairs;
+  p.per_cta = (p.total + n - 1) / n;
+  p.n_ctas = (int)((p.total + p.per_cta - 1) / p.per_cta);
   return p;
 }
 
@@ -1225,6 +1288,7 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   P.per_cta = plan.per_cta;
   P.total_units = plan.total;
   P.uniform_units = plan.uniform_units;
+  P.ramp_units = plan.ramp_units;
   P.pair_starts = (const long long*)a->pair_starts;
   P.scale_log2e = a->scale * 1.4426950408889634f;
   P.page_bytes = a->page_bytes;
@@ -1319,3 +1383,9 @@ extern "C" int inq_merge_partials(const float* records, int32_t n_parts, int64_t
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
 }
+
+#ifdef INQ_DECODE_TIMING
+extern "C" int inq_debug_decode_phases(void* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, inq::g_phase, sizeof(inq::g_phase));
+}
+#endif

@@ -251,7 +251,9 @@ def compact_field(tensor: torch.Tensor | None, n_inner: int) -> Field:
     """Field descriptor of a contiguous tensor whose two leading axes are (outer, inner)."""
     if tensor is None or tensor.numel() == 0:
         return Field(None, 0, 0)
-    row = tensor[0, 0].numel() * tensor.element_size()
+    row = tensor.element_size()
+    for size in tensor.shape[2:]:   # plain integers: indexing the tensor costs four times as much
+        row *= size
     return Field(tensor.data_ptr(), row * n_inner, row)
 
 
