@@ -486,9 +486,26 @@ __device__ __forceinline__ unsigned encode_slot_fast(float x, float scale, float
 template <typename T>
 __device__ __forceinline__ unsigned f32_bits_of(T v) { return __float_as_uint(to_float<T>(v)); }
 
-template <typename T, bool REGULAR>   // REGULAR: tokens % 8 == 0 and sample_stride == 8
-__global__ void __launch_bounds__(128, 7) k4_encode128_kernel(K4Params p) {
+__device__ __forceinline__ void stage_copy16(void* dst, const void* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void stage_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void stage_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// REGULAR: tokens % 8 == 0 and sample_stride == 8.
+// STAGED (16-bit inputs, contiguous rows, tokens % 32 == 0): the row's tokens stream twice -- once
+// for the statistics, once for the packing -- through a ring of four 8 KB shared-memory stages
+// filled by 16-byte asynchronous copies, three groups of 32 tokens in flight per CTA.  A thread
+// that fetches its own channel with 2-byte loads keeps only 16 bytes in flight, which left the
+// kernel waiting on memory latency at a tenth of the HBM rate.
+template <typename T, bool REGULAR, bool STAGED = false>
+__global__ void __launch_bounds__(128, STAGED ? 5 : 7) k4_encode128_kernel(K4Params p) {
   constexpr int C = 128;
+  constexpr int kGroupTokens = 32, kRing = 4;
+  constexpr int kGroupBytes = kGroupTokens * C * (int)sizeof(T);
+  __shared__ __align__(16) unsigned char s_ring[STAGED ? kRing * kGroupBytes : 16];
   __shared__ float s_sal[C], s_err[C], s_mean[C], s_scale[C], s_rcp[C];
   __shared__ unsigned s_key[C];
   __shared__ unsigned char s_kind[C], s_from[C], s_plain[C];
@@ -520,7 +537,52 @@ __global__ void __launch_bounds__(128, 7) k4_encode128_kernel(K4Params p) {
     // the next batch of tokens is requested before the current one is consumed, so the
     // sequential (Welford) chain never waits on a freshly issued load
     T ahead[kUnroll];
-    if (REGULAR) {
+    if constexpr (STAGED) {
+      const int n_groups = tokens / kGroupTokens;
+      const unsigned char* src_bytes = (const unsigned char*)row;
+      auto issue = [&](int step_index) {
+        if (step_index < 2 * n_groups) {
+          const int g = step_index >= n_groups ? step_index - n_groups : step_index;
+          unsigned char* dst = s_ring + (step_index & (kRing - 1)) * kGroupBytes;
+          const unsigned char* src = src_bytes + (long long)g * kGroupBytes;
+#pragma unroll
+          for (int k = 0; k < kGroupBytes / (16 * C); ++k) stage_copy16(dst + (k * C + c) * 16, src + (k * C + c) * 16);
+        }
+        stage_commit();
+      };
+      issue(0);
+      issue(1);
+      issue(2);
+      const double* inv = s_inv;
+      for (int g = 0; g < n_groups; ++g) {
+        stage_wait<kRing - 2>();
+        __syncthreads();   // group g has landed for every thread; the stage of group g - 1 is free
+        issue(g + 3);
+        const T* tile = (const T*)(s_ring + (g & (kRing - 1)) * kGroupBytes) + c;
+#pragma unroll
+        for (int b = 0; b < kGroupTokens / kUnroll; ++b) {
+          float v[kUnroll];
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) v[u] = to_float<T>(tile[(b * kUnroll + u) * C]);
+          cascade.add(v[0]);   // every eighth token is a sample
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            const float x = v[u];
+            top_bits = max(top_bits, __float_as_uint(x) & 0x7fffffffu);
+            if (want_error) {
+              const double xd = (double)x;
+              const double delta = xd - mean;
+              count_d = count_d + 1.0;
+              mean = mean + divide_by_count(delta, count_d, inv[u]);
+              m2 = m2 + delta * (xd - mean);
+            }
+          }
+          inv += kUnroll;
+        }
+      }
+      (void)step;
+      (void)ahead;
+    } else if (REGULAR) {
       const T* cursor = column;
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) ahead[u] = cursor[u * step];
@@ -718,6 +780,49 @@ __global__ void __launch_bounds__(128, 7) k4_encode128_kernel(K4Params p) {
     bias[j] = kind[j] ? 128.f : 8.f;
     shift[j] = kind[j] == 1 ? 4 : 0;
     any_remote |= (from[j] != ch);
+  }
+  if constexpr (STAGED) {
+    const int n_groups = tokens / kGroupTokens;
+    const unsigned char* src_bytes = (const unsigned char*)row;
+    for (int g = 0; g < n_groups; ++g) {
+      const int step_index = n_groups + g;
+      stage_wait<kRing - 2>();
+      __syncthreads();
+      if (step_index + 3 < 2 * n_groups) {
+        const int ahead_group = step_index + 3 - n_groups;
+        unsigned char* dst = s_ring + ((step_index + 3) & (kRing - 1)) * kGroupBytes;
+        const unsigned char* src = src_bytes + (long long)ahead_group * kGroupBytes;
+#pragma unroll
+        for (int k = 0; k < kGroupBytes / (16 * C); ++k) stage_copy16(dst + (k * C + c) * 16, src + (k * C + c) * 16);
+      }
+      stage_commit();
+      const T* tile = (const T*)(s_ring + (step_index & (kRing - 1)) * kGroupBytes);
+#pragma unroll
+      for (int i = 0; i < kGroupTokens / 8; ++i) {
+        const int tl = t0 + 8 * i;
+        const T* trow = tile + tl * C;
+        const uint4 cur = *(const uint4*)(trow + chunk * 8);
+        const T* hv = (const T*)&cur;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = to_float<T>(hv[j]);
+        if (any_remote) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (kind[j] == 2) v[j] = to_float<T>(trow[from[j]]);
+        }
+        unsigned word = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float q = rintf(exact_quotient(v[j], scale[j], rcp[j], any_plain));
+          const unsigned code = (unsigned)(int)(fminf(fmaxf(q, -limit[j]), limit[j]) + bias[j]);
+          word |= ((code >> shift[j]) & 15u) << (4 * j);
+        }
+        *(unsigned*)(payload + (long long)(g * kGroupTokens + tl) * 64 + chunk * 4) = word;
+      }
+    }
+    stage_wait<0>();
+    return;
   }
   constexpr int kVec = sizeof(T) == 2 ? 1 : 2;   // 16-byte vectors per 8 elements
   uint4 next[kVec];
@@ -1082,17 +1187,21 @@ extern "C" int inq_k4_encode(const inq_k4_encode_args_t* a, int32_t* status, inq
   unsigned grid = (unsigned)(a->in.n_outer * a->in.n_inner);
   if (C == 128 && p.vector_path && a->in.tokens <= kRcpTable && !a->descriptor_i32) {
     const bool regular = a->in.tokens % 8 == 0 && a->sample_stride == 8;
+    // whole rows contiguous in memory, in groups of 32 tokens: the shared-memory ring variant
+    const bool staged = regular && a->in.tokens % 32 == 0 && a->in.stride_token == C;
     switch (a->in.dtype) {
       case INQ_F32:
         if (regular) k4_encode128_kernel<float, true><<<grid, 128, 0, stream>>>(p);
         else k4_encode128_kernel<float, false><<<grid, 128, 0, stream>>>(p);
         break;
       case INQ_F16:
-        if (regular) k4_encode128_kernel<__half, true><<<grid, 128, 0, stream>>>(p);
+        if (staged) k4_encode128_kernel<__half, true, true><<<grid, 128, 0, stream>>>(p);
+        else if (regular) k4_encode128_kernel<__half, true><<<grid, 128, 0, stream>>>(p);
         else k4_encode128_kernel<__half, false><<<grid, 128, 0, stream>>>(p);
         break;
       default:
-        if (regular) k4_encode128_kernel<__nv_bfloat16, true><<<grid, 128, 0, stream>>>(p);
+        if (staged) k4_encode128_kernel<__nv_bfloat16, true, true><<<grid, 128, 0, stream>>>(p);
+        else if (regular) k4_encode128_kernel<__nv_bfloat16, true><<<grid, 128, 0, stream>>>(p);
         else k4_encode128_kernel<__nv_bfloat16, false><<<grid, 128, 0, stream>>>(p);
         break;
     }
