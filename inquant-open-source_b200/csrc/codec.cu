@@ -497,14 +497,17 @@ __device__ __forceinline__ void stage_wait() { asm volatile("cp.async.wait_group
 // REGULAR: tokens % 8 == 0 and sample_stride == 8.
 // STAGED (16-bit inputs, contiguous rows, tokens % 32 == 0): the row's tokens stream twice -- once
 // for the statistics, once for the packing -- through a ring of four 8 KB shared-memory stages
-// filled by 16-byte asynchronous copies, three groups of 32 tokens in flight per CTA.  A thread
+// filled by 16-byte asynchronous copies, three groups of 32 tokens in flight per CTA; every warp
+// stages exactly the bytes it reads, so the two passes run without CTA-wide barriers.  A thread
 // that fetches its own channel with 2-byte loads keeps only 16 bytes in flight, which left the
 // kernel waiting on memory latency at a tenth of the HBM rate.
 template <typename T, bool REGULAR, bool STAGED = false>
 __global__ void __launch_bounds__(128, STAGED ? 5 : 7) k4_encode128_kernel(K4Params p) {
   constexpr int C = 128;
   constexpr int kGroupTokens = 32, kRing = 4;
-  constexpr int kGroupBytes = kGroupTokens * C * (int)sizeof(T);
+  constexpr int kRowBytes = C * (int)sizeof(T);
+  constexpr int kGroupBytes = kGroupTokens * kRowBytes;
+  constexpr int kWarpStage = kGroupBytes / 4;   // a warp's share of a stage
   __shared__ __align__(16) unsigned char s_ring[STAGED ? kRing * kGroupBytes : 16];
   __shared__ float s_sal[C], s_err[C], s_mean[C], s_scale[C], s_rcp[C];
   __shared__ unsigned s_key[C];
@@ -538,15 +541,32 @@ __global__ void __launch_bounds__(128, STAGED ? 5 : 7) k4_encode128_kernel(K4Par
     // sequential (Welford) chain never waits on a freshly issued load
     T ahead[kUnroll];
     if constexpr (STAGED) {
+      // Every warp stages what it reads itself, so the passes need no CTA-wide barrier: for the
+      // statistics the 64 bytes of its 32 channels in each of the group's 32 token rows.
       const int n_groups = tokens / kGroupTokens;
+      const int warp_id = c >> 5, lane_id = c & 31;
+      unsigned char* const warp_ring = s_ring + warp_id * (kRing * kWarpStage);
       const unsigned char* src_bytes = (const unsigned char*)row;
       auto issue = [&](int step_index) {
         if (step_index < 2 * n_groups) {
-          const int g = step_index >= n_groups ? step_index - n_groups : step_index;
-          unsigned char* dst = s_ring + (step_index & (kRing - 1)) * kGroupBytes;
-          const unsigned char* src = src_bytes + (long long)g * kGroupBytes;
+          unsigned char* dst = warp_ring + (step_index & (kRing - 1)) * kWarpStage;
+          if (step_index < n_groups) {
+            const unsigned char* src = src_bytes + (long long)step_index * kGroupBytes + warp_id * 64;
 #pragma unroll
-          for (int k = 0; k < kGroupBytes / (16 * C); ++k) stage_copy16(dst + (k * C + c) * 16, src + (k * C + c) * 16);
+            for (int k = 0; k < 4; ++k) {
+              const int idx = k * 32 + lane_id, token = idx >> 2, part = idx & 3;
+              stage_copy16(dst + token * 64 + part * 16, src + token * kRowBytes + part * 16);
+            }
+          } else {
+            // packing: the thread's own 16 bytes of token rows 2 * warp + lane / 16 + 8k
+            const unsigned char* src = src_bytes + (long long)(step_index - n_groups) * kGroupBytes;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int token = 2 * warp_id + (lane_id >> 4) + 8 * k;
+              stage_copy16(dst + (2 * k + (lane_id >> 4)) * kRowBytes + (lane_id & 15) * 16,
+                           src + token * kRowBytes + (lane_id & 15) * 16);
+            }
+          }
         }
         stage_commit();
       };
@@ -556,14 +576,14 @@ __global__ void __launch_bounds__(128, STAGED ? 5 : 7) k4_encode128_kernel(K4Par
       const double* inv = s_inv;
       for (int g = 0; g < n_groups; ++g) {
         stage_wait<kRing - 2>();
-        __syncthreads();   // group g has landed for every thread; the stage of group g - 1 is free
+        __syncwarp();   // group g has landed for every lane; the stage of group g - 1 is free
         issue(g + 3);
-        const T* tile = (const T*)(s_ring + (g & (kRing - 1)) * kGroupBytes) + c;
+        const T* tile = (const T*)(warp_ring + (g & (kRing - 1)) * kWarpStage) + lane_id;
 #pragma unroll
         for (int b = 0; b < kGroupTokens / kUnroll; ++b) {
           float v[kUnroll];
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) v[u] = to_float<T>(tile[(b * kUnroll + u) * C]);
+          for (int u = 0; u < kUnroll; ++u) v[u] = to_float<T>(tile[(b * kUnroll + u) * 32]);
           cascade.add(v[0]);   // every eighth token is a sample
 #pragma unroll
           for (int u = 0; u < kUnroll; ++u) {
@@ -783,24 +803,29 @@ __global__ void __launch_bounds__(128, STAGED ? 5 : 7) k4_encode128_kernel(K4Par
   }
   if constexpr (STAGED) {
     const int n_groups = tokens / kGroupTokens;
+    const int warp_id = c >> 5, lane_id = c & 31;
+    unsigned char* const warp_ring = s_ring + warp_id * (kRing * kWarpStage);
     const unsigned char* src_bytes = (const unsigned char*)row;
     for (int g = 0; g < n_groups; ++g) {
       const int step_index = n_groups + g;
       stage_wait<kRing - 2>();
-      __syncthreads();
+      __syncwarp();
       if (step_index + 3 < 2 * n_groups) {
-        const int ahead_group = step_index + 3 - n_groups;
-        unsigned char* dst = s_ring + ((step_index + 3) & (kRing - 1)) * kGroupBytes;
-        const unsigned char* src = src_bytes + (long long)ahead_group * kGroupBytes;
+        unsigned char* dst = warp_ring + ((step_index + 3) & (kRing - 1)) * kWarpStage;
+        const unsigned char* src = src_bytes + (long long)(g + 3) * kGroupBytes;
 #pragma unroll
-        for (int k = 0; k < kGroupBytes / (16 * C); ++k) stage_copy16(dst + (k * C + c) * 16, src + (k * C + c) * 16);
+        for (int k = 0; k < 4; ++k) {
+          const int token = 2 * warp_id + (lane_id >> 4) + 8 * k;
+          stage_copy16(dst + (2 * k + (lane_id >> 4)) * kRowBytes + (lane_id & 15) * 16,
+                       src + token * kRowBytes + (lane_id & 15) * 16);
+        }
       }
       stage_commit();
-      const T* tile = (const T*)(s_ring + (step_index & (kRing - 1)) * kGroupBytes);
+      const unsigned char* tile = warp_ring + (step_index & (kRing - 1)) * kWarpStage;
 #pragma unroll
       for (int i = 0; i < kGroupTokens / 8; ++i) {
-        const int tl = t0 + 8 * i;
-        const T* trow = tile + tl * C;
+        const int tl = t0 + 8 * i;   // t0 = 2 * warp + lane / 16
+        const T* trow = (const T*)(tile + (2 * i + (lane_id >> 4)) * kRowBytes);
         const uint4 cur = *(const uint4*)(trow + chunk * 8);
         const T* hv = (const T*)&cur;
         float v[8];
