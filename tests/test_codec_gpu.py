@@ -48,6 +48,26 @@ def test_k4_matches_oracle_on_seeded_inputs(dtype, shape, policy):
         assert_same_bytes(packed.dequantize().float(), oracle.dequantize_k4(ref), "dequantize")
 
 
+@pytest.mark.parametrize("tokens", [32, 64, 96, 256, 512])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_k4_ring_staged_rows_match_strided_rows_and_oracle(tokens, dtype):
+    """Contiguous 16-bit rows in groups of 32 tokens take the shared-memory ring kernel, a
+    token-major view of the same values (token stride = heads x channels) the direct-load one:
+    both must give the oracle's bytes (1, 2, 3, 8 and 16 groups: shorter than, equal to and longer
+    than the ring)."""
+    CodecConfig, quantize, _ = _codec()
+    cfg = CodecConfig(donor_policy="min_error")
+    x32 = k4_input(dict(seed=40 + tokens, shape=(3, 4, tokens, 128), dtype=dtype))
+    x = to_device(x32, dtype)
+    token_major = x.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    assert x.is_contiguous() and not token_major.is_contiguous() and token_major.stride(2) == 4 * 128
+    staged, direct = quantize(x, cfg), quantize(token_major, cfg)
+    ref = oracle.quantize_k4(x32, dtype, 8, 0.125, "min_error")
+    for name in staged.tensors:
+        assert torch.equal(staged.tensors[name], direct.tensors[name]), name
+        assert_same_bytes(staged.tensors[name], ref.fields()[name], name)
+
+
 def test_block_axis_in_batch_and_token_major_strides_match_contiguous():
     CodecConfig, quantize, _ = _codec()
     cfg = CodecConfig(donor_policy="min_error")
