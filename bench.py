@@ -526,18 +526,18 @@ def run_prefill(torch, device):
 def run_paged_batch(torch, dist, device, world, rank, block):
     """Config 3: Mistral-7B-shaped batched paged decode (vLLM-extension page layout, block 16):
     32 layers x 8 KV heads x 128, 32 query heads, 16 requests with seeded context lengths uniform
-    in 4096..32768, pages at shuffled physical ids, requests dealt round-robin to the ranks with no
+    in 4096..32768, pages at shuffled physical ids, requests dealt to the ranks by context length with no
     collective.  One step = every layer of every local request in one decode launch.  A request's
     pages are sealed once by the page-packing kernels and copied to the other layers' (distinct)
     physical pages, so every layer still streams its own memory."""
     import numpy as np
     import workloads
-    from inquant.batched import DecodeBatch, PagedSequenceState
+    from inquant.batched import DecodeBatch, PagedSequenceState, shard_requests
     from inquant_vllm.layout import PageLayout, pack_pages_into
     layers, heads, q_heads, requests = 32, 8, 32, 16
     layout = PageLayout(block, heads)
     lengths = [int(x) for x in np.random.default_rng(2024).integers(4096, 32769, size=requests)]
-    mine = [i for i in range(requests) if i % world == rank]
+    mine = shard_requests(lengths, world)[rank]
     pages_of = {i: lengths[i] // block for i in mine}
     total_pages = layers * sum(pages_of.values())
     pool = torch.empty((total_pages + 8, layout.page_bytes), dtype=torch.uint8, device=device)
@@ -593,7 +593,7 @@ def run_paged_batch(torch, dist, device, world, rank, block):
             "requests": requests, "context_tokens": sum(lengths), "us_per_step": round(ms * 1e3, 1),
             "decode_tokens_per_s": round(requests / (ms * 1e-3), 1), "aggregate_gbs": round(gbs, 1),
             "per_gpu_hbm_frac": round(gbs / world / peak, 4), "algorithmic_bytes_per_step": int(total_bytes),
-            "sharding": "requests round-robin over ranks, no collective", "steps": steps}
+            "sharding": "requests dealt to the ranks by context length (longest first, to the least loaded rank), no collective", "steps": steps}
 
 
 def run_split_kv(args, torch, dist, device, world, rank):

@@ -59,6 +59,22 @@ class PagedSequenceState:
     layout: object                   # inquant_vllm.layout.PageLayout
 
 
+def shard_requests(lengths, world: int) -> list[list[int]]:
+    """Deal independent requests to ``world`` ranks so that the longest rank is as short as a
+    greedy pass gets it: requests in order of decreasing context length, each to the rank with
+    the fewest tokens so far (ties: fewer requests, then lower rank).  Every rank computes the same
+    assignment from the same lengths, so no collective is involved.  Returns the request indices
+    of every rank in increasing order."""
+    if world < 1:
+        raise ValueError("world must be positive")
+    load, shards = [0] * world, [[] for _ in range(world)]
+    for index in sorted(range(len(lengths)), key=lambda i: (-int(lengths[i]), i)):
+        rank = min(range(world), key=lambda r: (load[r], len(shards[r]), r))
+        load[rank] += int(lengths[index])
+        shards[rank].append(index)
+    return [sorted(shard) for shard in shards]
+
+
 def _struct_array_to_device(array, device) -> torch.Tensor:
     raw = bytes(array)
     return torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)

@@ -69,3 +69,26 @@ def test_block_sharding_is_a_contiguous_partition():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         shard_blocks(4, 2, 2)
+
+
+def test_requests_are_dealt_by_length_to_the_least_loaded_rank():
+    """Batched serving shards whole requests: every request lands on exactly one rank, the
+    assignment is the same wherever it is computed, and the longest rank stays within one request
+    of the mean for the bench's seeded lengths."""
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "inquant-open-source_b200"))
+    from inquant.batched import shard_requests
+    lengths = [int(x) for x in np.random.default_rng(2024).integers(4096, 32769, size=16)]
+    for world in (1, 2, 4, 8):
+        shards = shard_requests(lengths, world)
+        assert sorted(i for shard in shards for i in shard) == list(range(16))
+        assert shards == shard_requests(list(lengths), world)
+        loads = [sum(lengths[i] for i in shard) for shard in shards]
+        assert max(loads) - sum(loads) / world <= max(lengths)
+        if world == 8:
+            assert max(loads) <= 1.25 * sum(loads) / world
+    assert shard_requests([5, 5, 5], 2) == [[0, 2], [1]]
+    assert shard_requests([], 3) == [[], [], []]
+    with pytest.raises(ValueError):
+        shard_requests([1], 0)
