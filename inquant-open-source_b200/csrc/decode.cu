@@ -706,21 +706,22 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
             wsrc[idx] = (unsigned char)(4 * lane + i);
             wdon[idx] = (unsigned char)role[i];
             wssc[idx] = scv[i];
-            // selection matrix: column idx picks 16 * (high nibble of the source) + (low nibble in
-            // the donor slot), scaled by 2^11 so that every entry and every partial sum is exact
-#pragma unroll
-            for (int which = 0; which < 2; ++which) {
-              const int c = which ? role[i] : 4 * lane + i;
-              const int jj = c >> 5, u = c & 31;
-              const int ks = 2 * (u >> 3) + ((u >> 1) & 1), half = u & 1, e = (u >> 2) & 1;
-              const int target = ((idx & 7) << 2) | jj;
-              float value = which ? 2048.f : 32768.f;
-              if (half) value *= 0.0625f;
-              const int cell = ((((idx >> 4) * 8 + ks) * 32 + target) * 16) + (((idx >> 3) & 1) * 2 + half) * 4 + e * 2;
-              *(__half*)(wsel + cell) = __float2half_rn(value);
-              wcell[2 * idx + which] = (unsigned short)cell;
-            }
           }
+        }
+        __syncwarp();
+        // selection matrix: column idx picks 16 * (high nibble of the source) + (low nibble in the
+        // donor slot), scaled by 2^11 so that every entry and every partial sum is exact.  One
+        // cell per lane: entry v is the source (even v) or the donor slot (odd v) of salient v / 2.
+        for (int v = lane; v < 2 * P.n_pad; v += 32) {
+          const int idx = v >> 1, which = v & 1;
+          const int c = (which ? wdon[idx] : wsrc[idx]) & 127;
+          const int jj = c >> 5, u = c & 31;
+          const int ks = 2 * (u >> 3) + ((u >> 1) & 1), half = u & 1, e = (u >> 2) & 1;
+          const int target = ((idx & 7) << 2) | jj;
+          const int cell = ((((idx >> 4) * 8 + ks) * 32 + target) * 16) + (((idx >> 3) & 1) * 2 + half) * 4 + e * 2;
+          // fp16 bits of 32768 (source), 2048 (donor), each divided by 16 for the high nibble of a byte
+          *(unsigned short*)(wsel + cell) = (unsigned short)(0x7800 - (which + half) * 0x1000);
+          wcell[v] = (unsigned short)cell;
         }
         __syncwarp();
         // query at the salient channels, as B fragments of the salient step: the staged copy,
