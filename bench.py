@@ -679,10 +679,10 @@ def run_split_kv(args, torch, dist, device, world, rank):
             "steps": steps, **extra}
 
 
-# DRAM bytes (read + write) of one decode_kernel launch: 151.80 MB measured by ncu on the 10-layer
+# DRAM bytes (read + write) of one decode_kernel launch: 151.77 MB measured by ncu on the 10-layer
 # capture case (143.9 MB algorithmic), scaled to the layers of this run because traffic grows in
 # proportion to the units processed (profiles/decode_kernel_cfg1_10layers.md).
-DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 151.80 / 143.89
+DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 151.77 / 143.89
 DECODE_TRAFFIC_BYTES = None
 
 
