@@ -11,9 +11,10 @@ sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(
 import workloads  # noqa: E402
 
 
-def _k4(seed, shape, dtype="bfloat16", policy="min_error", fraction=0.125, stride=8, zero_row=False):
+def _k4(seed, shape, dtype="bfloat16", policy="min_error", fraction=0.125, stride=8, zero_row=False,
+        boundaries=False):
     return dict(seed=seed, shape=shape, dtype=dtype, policy=policy, fraction=fraction, stride=stride,
-                zero_row=zero_row)
+                zero_row=zero_row, boundaries=boundaries)
 
 
 K4_CASES = {
@@ -28,6 +29,10 @@ K4_CASES = {
     "fp32_min_error": _k4(71, (1, 2, 64, 128), dtype="float32"),
     "small_c16": _k4(915, (2, 3, 41, 16), policy="neighbors", fraction=0.25),
     "stride3_c16": _k4(811, (6, 3, 8, 16), fraction=0.25, stride=3),
+    # channels that put the float64 mean / variance update and the float32 roundings after it on
+    # their boundaries (constant, zero-mean, offset, all-zero)
+    "boundaries_bf16": _k4(5, (2, 2, 256, 128), boundaries=True),
+    "boundaries_fp16": _k4(6, (1, 2, 256, 128), dtype="float16", boundaries=True),
 }
 
 V_CASES = {
@@ -65,6 +70,14 @@ def k4_input(case) -> np.ndarray:
         x[..., 32:35] *= 15
     if case.get("zero_row"):
         x[0, 0] = 0
+    if case.get("boundaries"):
+        sign = np.where(np.arange(t) % 2 == 0, 1.0, -1.0).astype(np.float32)[:, None]
+        x[..., 0::8] = 0.5                                   # constant: variance exactly zero
+        x[..., 1::8] = 0.5 + sign * 2.0 ** -7                # constant plus a one-step ripple
+        x[..., 2::8] = sign * 1.25                           # mean exactly zero
+        x[..., 3::8] = 100.0 + 0.01 * x[..., 3::8]           # mean far above the spread
+        x[..., 4::8] = 0.0                                   # all zero
+        x[..., 5::8] = sign * 3.0 + 2.0 ** -8                # tiny mean, large swings
     if case["dtype"] == "bfloat16":
         return workloads.bf16_exact(x)
     if case["dtype"] == "float16":

@@ -68,31 +68,6 @@ def test_k4_ring_staged_rows_match_strided_rows_and_oracle(tokens, dtype):
         assert_same_bytes(staged.tensors[name], ref.fields()[name], name)
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
-def test_k4_statistics_on_constant_and_zero_mean_channels_match_oracle(dtype):
-    """Constant channels (variance exactly zero), channels whose mean is exactly zero, channels
-    with a mean far above their spread and all-zero channels put the float64 mean / variance
-    update and the float32 roundings after it on their boundaries: packed bytes, scales,
-    descriptors and padding must still equal the oracle's."""
-    CodecConfig, quantize, _ = _codec()
-    rng = np.random.default_rng(5)
-    tokens = 256
-    x32 = rng.standard_normal((2, 2, tokens, 128)).astype(np.float32)
-    sign = np.where(np.arange(tokens) % 2 == 0, 1.0, -1.0).astype(np.float32)[:, None]
-    x32[..., 0::8] = 0.5                                              # constant
-    x32[..., 1::8] = 0.5 + sign * 2.0 ** -7                           # constant plus a one-ulp ripple
-    x32[..., 2::8] = sign * 1.25                                      # mean exactly zero
-    x32[..., 3::8] = 100.0 + 0.01 * x32[..., 3::8]                    # mean far above the spread
-    x32[..., 4::8] = 0.0                                              # all zero
-    x32[..., 5::8] = sign * 3.0 + 2.0 ** -8                           # tiny mean, large swings
-    x32 = oracle.round_to_dtype(x32, dtype)                           # the oracle takes values the dtype holds exactly
-    cfg = CodecConfig(donor_policy="min_error")
-    packed = quantize(to_device(x32, dtype), cfg)
-    ref = oracle.quantize_k4(x32, dtype, 8, 0.125, "min_error")
-    for field, tensor in packed.tensors.items():
-        assert_same_bytes(tensor, ref.fields()[field], field)
-
-
 def test_block_axis_in_batch_and_token_major_strides_match_contiguous():
     CodecConfig, quantize, _ = _codec()
     cfg = CodecConfig(donor_policy="min_error")
