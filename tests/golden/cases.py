@@ -40,6 +40,11 @@ V_CASES = {
     "v4_g64": dict(seed=17, shape=(1, 2, 32, 128), dtype="bfloat16", bits=4, group=64, zero_row=False),
     "v2_g32": dict(seed=27, shape=(1, 2, 32, 128), dtype="float16", bits=2, group=32, zero_row=False),
     "v2_g128": dict(seed=31, shape=(1, 2, 16, 128), dtype="float32", bits=2, group=128, zero_row=False),
+    # groups of range zero (constant rows), groups dominated by one large channel, exact zeros
+    "v2_boundaries": dict(seed=41, shape=(2, 2, 64, 128), dtype="bfloat16", bits=2, group=64, zero_row=True,
+                          boundaries=True),
+    "v4_boundaries_fp16": dict(seed=43, shape=(1, 2, 32, 128), dtype="float16", bits=4, group=32, zero_row=False,
+                               boundaries=True),
 }
 
 SELECT_CASES = {f"{policy}_{count}": dict(seed=112, count=count, policy=policy)
@@ -78,6 +83,9 @@ def k4_input(case) -> np.ndarray:
         x[..., 3::8] = 100.0 + 0.01 * x[..., 3::8]           # mean far above the spread
         x[..., 4::8] = 0.0                                   # all zero
         x[..., 5::8] = sign * 3.0 + 2.0 ** -8                # tiny mean, large swings
+        if t > 7:
+            x[0, -1, 5] = 0.75                               # a token row that is constant: every value group has range zero
+            x[-1, 0, 7, : c // 2] = -2.5                     # one constant value group beside an ordinary one
     if case["dtype"] == "bfloat16":
         return workloads.bf16_exact(x)
     if case["dtype"] == "float16":
