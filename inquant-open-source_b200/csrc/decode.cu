@@ -5,7 +5,11 @@
 //
 // Work decomposition.  The 32-token packed slices of all pairs form one flat list that is cut
 // into gridDim.x equal ranges (the grid is SMs x resident CTAs); a CTA walks its range pair by
-// pair and its four warps cut each segment again.  The few dense sink/tail slices of a pair
+// pair and its four warps cut each segment again.  Every pair also occupies a few list positions
+// without slices (its ramp): they stand for the fixed cost of visiting a pair, so that a CTA
+// whose range crosses a pair boundary receives fewer slices.  Blocks of at most 16 tokens
+// (16-token pages) use a variant of the kernel with 16-token slices that carry their block's
+// metadata in the slice's own ring stage.  The few dense sink/tail slices of a pair
 // (16 tokens each) are dealt round-robin to the warps that work on it.  Every warp streams its
 // slices on its own:
 //
