@@ -101,6 +101,191 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(clocks)}
 
 
+
+# --------------------------------------------------------------------------- parity against the oracle
+# Every timed leg is followed, outside its timed region, by a comparison of a sample of the
+# outputs it produced with the CPU oracle (the checker, never the thing measured): attention
+# within max-abs 2e-2 and cosine >= 0.9999, packed bytes and descriptors bit for bit.  A failed
+# comparison ends the run with a non-zero exit code.
+PARITY_MAX_ABS, PARITY_MIN_COS = 2e-2, 0.9999
+
+
+class ParityError(SystemExit):
+    def __init__(self, what):
+        super().__init__(f"parity check failed: {what}")
+
+
+def _oracle():
+    path = os.path.join(ROOT, "oracle")
+    if path not in sys.path:
+        sys.path.insert(0, path)
+    import inquant_oracle
+    return inquant_oracle
+
+
+def _closeness(got, want):
+    import numpy as np
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    err = float(np.abs(got - want).max())
+    cos = (got * want).sum(-1) / np.sqrt((got * got).sum(-1) * (want * want).sum(-1) + 1e-300)
+    return err, float(cos.min()), bool(np.isfinite(got).all())
+
+
+def _host(t):
+    import torch
+    t = t.detach()
+    return (t.float() if t.dtype == torch.bfloat16 else t).cpu().numpy()
+
+
+def oracle_packed(oracle, key_blocks, value_blocks):
+    """The device's packed blocks (lists of [1, H, T, ...] fields) as the oracle's containers."""
+    import torch
+    cat = lambda blocks, name: _host(torch.cat([getattr(b, name) for b in blocks], 0))
+    n, heads, tokens = len(key_blocks), key_blocks[0].payload.shape[1], key_blocks[0].payload.shape[2]
+    shape = (n, heads, tokens, DIM)
+    pk = oracle.PackedK(cat(key_blocks, "payload"), cat(key_blocks, "scales"), cat(key_blocks, "salient_channels"),
+                        cat(key_blocks, "donor_channels"), cat(key_blocks, "padding"), shape, "bfloat16")
+    pv = oracle.PackedV(cat(value_blocks, "payload"), scales=cat(value_blocks, "scales"), offsets=cat(value_blocks, "offsets"),
+                        shape=shape, dtype="bfloat16", bits=2, group_size=64)
+    return pk, pv
+
+
+def oracle_dense_history(oracle, pk, pv, sink, tail):
+    """[H, tokens, 128] keys and values the reference's oracle attends to: exact sink, dequantised
+    blocks rounded to bf16, exact tail."""
+    import numpy as np
+    heads = pk.shape[1]
+    keys = oracle.dequantize_k4(pk).transpose(1, 0, 2, 3).reshape(heads, -1, DIM)
+    vals = oracle.dequantize_values(pv).transpose(1, 0, 2, 3).reshape(heads, -1, DIM)
+    return (np.concatenate([sink[0], keys, tail[0]], 1), np.concatenate([sink[1], vals, tail[1]], 1))
+
+
+def layer_dense_parts(cache, layer_idx, tail_tokens):
+    layer = cache._layers[layer_idx]
+    sink = (_host(layer.sink_key)[0], _host(layer.sink_value)[0])
+    tail = (_host(layer.tail_key_buffer[:, :, :tail_tokens])[0], _host(layer.tail_value_buffer[:, :, :tail_tokens])[0])
+    return sink, tail
+
+
+def check_decode_parity(torch, batch, cache, layers, seed_base, encode_layer=0):
+    """Config 1 at full size: the outputs of the 28-layer launch for `layers` against the oracle's
+    attention over the device's own packed bytes, and the packed fields of one whole layer
+    (127 blocks x 4 heads) bit for bit against the oracle's encoders on the same seeded tensors."""
+    import numpy as np
+    import workloads
+    oracle = _oracle()
+    torch.cuda.synchronize()
+    outputs = _host(batch.outputs)
+    queries = _host(batch.queries)
+    tails = batch.tail_tokens
+    worst, lowest = 0.0, 1.0
+    for index in layers:
+        state = batch.sequences[index].decode_state
+        pk, pv = oracle_packed(oracle, state.key_blocks, state.value_blocks)
+        sink, tail = layer_dense_parts(cache, index, tails[index])
+        keys, vals = oracle_dense_history(oracle, pk, pv, sink, tail)
+        want = oracle.attention_decode(queries[index], keys, vals, DIM ** -0.5)
+        err, cos, finite = _closeness(outputs[index], want)
+        worst, lowest = max(worst, err), min(lowest, cos)
+        if not finite or err >= PARITY_MAX_ABS or cos < PARITY_MIN_COS:
+            raise ParityError(f"config 1 decode, layer {index}: max abs {err:.3e}, min cosine {cos:.6f}")
+    # one layer's packed bytes and descriptors against the oracle's encoders
+    k, v = workloads.make_kv_torch(seed_base + encode_layer, KV_HEADS, CONTEXT, batch.device)
+    take, blocks, _ = oracle.seal_plan(0, 0, CONTEXT, sink_tokens=SINK, residual_length=RESIDUAL, block_size=BLOCK)
+    body = slice(take, take + blocks * BLOCK)
+    shape = (KV_HEADS, blocks, BLOCK, DIM)
+    kb = np.ascontiguousarray(_host(k)[0][:, body].reshape(shape).transpose(1, 0, 2, 3))
+    vb = np.ascontiguousarray(_host(v)[0][:, body].reshape(shape).transpose(1, 0, 2, 3))
+    del k, v
+    want_k = oracle.quantize_k4(kb, "bfloat16", 8, 0.125, "min_error")
+    want_v = oracle.quantize_values(vb, "bfloat16", 2, 64)
+    state = batch.sequences[encode_layer].decode_state
+    got_k, got_v = oracle_packed(oracle, state.key_blocks, state.value_blocks)
+    mismatches = 0
+    for got, want in ((got_k, want_k), (got_v, want_v)):
+        for name, array in want.fields().items():
+            have = getattr(got, name)
+            if have.shape != array.shape or have.dtype != array.dtype:
+                raise ParityError(f"config 1 encode, field {name}: {have.dtype}{have.shape} vs {array.dtype}{array.shape}")
+            mismatches += int(np.count_nonzero(np.ascontiguousarray(have).view(np.uint8) != np.ascontiguousarray(array).view(np.uint8)))
+    if mismatches:
+        raise ParityError(f"config 1 encode, layer {encode_layer}: {mismatches} packed bytes differ from the oracle")
+    return {"max_abs": round(worst, 6), "min_cos": round(lowest, 7), "layers_checked": list(layers),
+            "against": "oracle f64 attention over the device's packed bytes (exact sink and tail), all layers in one launch",
+            "encode_layer_checked": encode_layer, "encode_blocks_checked": blocks * KV_HEADS,
+            "encode_mismatched_bytes": mismatches}
+
+
+def check_split_parity(torch, dist, split, cache, run_step, step_inputs, world, rank, first, last, layer=0):
+    """Config 4: the merged output of one layer against the oracle's attention over the WHOLE
+    request.  Every rank computes the oracle's partial record (acc, m, l) over its own shard of
+    the history from the device's packed bytes; the records are gathered and merged as the
+    reference's reduce kernel merges them (at one rank that is the unsplit oracle)."""
+    import numpy as np
+    oracle = _oracle()
+    split.inputs.copy_(step_inputs)
+    run_step()
+    torch.cuda.synchronize()
+    batch = split.batch
+    state = batch.sequences[layer].decode_state
+    pk, pv = oracle_packed(oracle, state.key_blocks, state.value_blocks)
+    heads = pk.shape[1]
+    cache_layer = cache._layers[layer]
+    empty = np.zeros((heads, 0, DIM), np.float32)
+    sink = (_host(cache_layer.sink_key)[0], _host(cache_layer.sink_value)[0]) if first and cache_layer.sink_key is not None else (empty, empty)
+    tail_tokens = batch.tail_tokens[layer] if last else 0
+    tail = ((_host(cache_layer.tail_key_buffer[:, :, :tail_tokens])[0], _host(cache_layer.tail_value_buffer[:, :, :tail_tokens])[0])
+            if tail_tokens else (empty, empty))
+    keys, vals = oracle_dense_history(oracle, pk, pv, sink, tail)
+    query = _host(batch.queries)[layer]
+    record = oracle.attention_partial(query, keys, vals, DIM ** -0.5)
+    records = [record]
+    if world > 1:
+        records = [None] * world
+        dist.all_gather_object(records, record)
+    acc, m, l = (np.stack([r[i] for r in records]) for i in range(3))
+    want = oracle.merge_partials(acc, m, l)
+    err, cos, finite = _closeness(_host(split.outputs)[layer], want)
+    if not finite or err >= PARITY_MAX_ABS or cos < PARITY_MIN_COS:
+        raise ParityError(f"config 4 split-KV, layer {layer}, rank {rank}: max abs {err:.3e}, min cosine {cos:.6f}")
+    return {"max_abs": round(err, 6), "min_cos": round(cos, 7), "layers_checked": [layer],
+            "against": "oracle partial records of every rank's shard, merged; equal to the unsplit oracle"}
+
+
+def check_paged_parity(torch, batch, seqs, local_lengths, layers, block, heads, layer=1):
+    """Config 3: the shortest and the longest request of this rank, one layer each, against the
+    oracle: the pages' bytes are unpacked as the reference's `unpack_pages_reference` does, the
+    exact sink replaces the first packed tokens, the exact tail follows."""
+    import numpy as np
+    oracle = _oracle()
+    torch.cuda.synchronize()
+    outputs, queries = _host(batch.outputs), _host(batch.queries)
+    order = sorted(range(len(local_lengths)), key=lambda i: local_lengths[i])
+    picks = sorted({order[0], order[-1]})
+    worst, lowest = 0.0, 1.0
+    for pick in picks:
+        index = pick * layers + min(layer, layers - 1)
+        seq = seqs[index]
+        pages = seq.pool[seq.page_table.long()].cpu().numpy()
+        keys, vals = oracle.unpack_pages(pages, block, heads)
+        keys = keys.transpose(1, 0, 2, 3).reshape(heads, -1, DIM).copy()
+        vals = vals.transpose(1, 0, 2, 3).reshape(heads, -1, DIM).copy()
+        dense = _host(seq.dense)
+        sink, tail = seq.sink_count, seq.tail_count
+        keys[:, :sink], vals[:, :sink] = dense[0][:, :sink], dense[1][:, :sink]
+        keys = np.concatenate([keys, dense[0][:, 4:4 + tail]], 1)
+        vals = np.concatenate([vals, dense[1][:, 4:4 + tail]], 1)
+        want = oracle.attention_decode(queries[index], keys, vals, DIM ** -0.5)
+        err, cos, finite = _closeness(outputs[index], want)
+        worst, lowest = max(worst, err), min(lowest, cos)
+        if not finite or err >= PARITY_MAX_ABS or cos < PARITY_MIN_COS:
+            raise ParityError(f"config 3 paged decode, block {block}, request of {local_lengths[pick]} tokens: "
+                              f"max abs {err:.3e}, min cosine {cos:.6f}")
+    return {"max_abs": round(worst, 6), "min_cos": round(lowest, 7),
+            "requests_checked": [int(local_lengths[i]) for i in picks], "layer": min(layer, layers - 1),
+            "against": "oracle f64 attention over the unpacked page bytes (exact sink and tail)"}
+
+
 # --------------------------------------------------------------------------- CUDA arm
 def build_request(torch, device, seed_base):
     """Prefill all layers through the public cache API; returns the cache and encode timings."""
@@ -205,6 +390,32 @@ def encoder_kernels_us(torch, k, v):
     return e0.elapsed_time(e1) / 10 * 1e3
 
 
+def sustained_leg(torch, batch, run_step, device_index, seconds):
+    """The same step replayed back to back for `seconds` of device time: on this pool the SM clock
+    settles well below its boost value under seconds of load, and a kernel that is bound by
+    latency or issue rate slows down with it.  Clocks are sampled, never set."""
+    chunk = max(1, min(100, batch._capacity - 1))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = 0
+    with ClockSampler(device_index, period_s=0.005) as clocks:
+        wall = time.perf_counter()
+        e0.record()
+        while time.perf_counter() - wall < seconds:
+            batch.rewind()
+            for _ in range(chunk):
+                run_step()
+            steps += chunk
+        e1.record()
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / steps
+    summary = clocks.summary()
+    return {"what": "the same decode step replayed back to back; tails rewound every %d steps (one small copy)" % chunk,
+            "seconds": round(e0.elapsed_time(e1) / 1e3, 2), "steps": steps, "us_per_step": round(us, 2),
+            "sm_mhz_median": summary["sm_mhz"], "sm_max_mhz": summary["sm_max_mhz"], "clock_samples": summary["samples"],
+            "reasons": summary["reasons"],
+            "us_times_mhz": round(us * summary["sm_mhz"], 0) if summary["sm_mhz"] else None}
+
+
 def run_cuda(args):
     import torch
     import torch.distributed as dist
@@ -276,6 +487,7 @@ def run_cuda(args):
         torch.cuda.synchronize()
     elapsed_ms = t0.elapsed_time(t1)
     launches = batch.launches - launches_before - 3
+    sustained = sustained_leg(torch, batch, run_step, local, args.sustained_seconds) if args.sustained_seconds > 0 else None
     kernel_ms = k0.elapsed_time(k1) / reps
     append_info = measure_append_and_seal(torch, batch, device)
     if world > 1:
@@ -329,6 +541,11 @@ def run_cuda(args):
     h2d = h_in[0].numel() * 2
     d2h = h_out.numel() * 2
     status = _native.take_status(device)
+    # ---- parity of what was just timed (outside every timed region)
+    batch.rewind()
+    batch.inputs.copy_(inputs[0])
+    run_step()
+    parity = check_decode_parity(torch, batch, cache, sorted({0, LAYERS // 2, LAYERS - 1}), seed_base=1000 * rank)
 
     peak, peak_kind = measured_peak_gbs()
     achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
@@ -354,14 +571,22 @@ def run_cuda(args):
         "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": round(achieved, 1), "peak": peak,
                      "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_source": peak_kind,
                      "us_per_launch": round(kernel_ms * 1e3, 2),
-                     "traffic": int(kernel_bytes * DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE),
-                     "traffic_source": "ncu capture of a 10-layer case scaled by units"},
+                     "traffic": int(kernel_bytes * DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE) if DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE else None,
+                     "traffic_source": DECODE_TRAFFIC_SOURCE},
         "e2e": {"value": round(world * mean_bytes["total"] / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "us_per_step": round(e2e_ms * 1e3, 2), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,   # append + decode kernels of this library (torch's staging copy not counted)
         "clocks": clocks.summary(),
         "device_status": status,
+        "parity": parity,
     }
+    if sustained is not None:
+        peak_now = measured_peak_gbs()[0]
+        sustained["gbs"] = round(kernel_bytes / (sustained["us_per_step"] * 1e-6) / 1e9, 1)
+        sustained["frac"] = round(sustained["gbs"] / peak_now, 4)
+        burst_mhz = line["clocks"]["sm_mhz"] or line["clocks"]["sm_max_mhz"]
+        sustained["burst_us_times_mhz"] = round(ms_per_step * 1e3 * burst_mhz, 0) if burst_mhz else None
+        line["sustained"] = sustained
     if args.split_context:
         del batch, cache
         torch.cuda.empty_cache()
@@ -375,7 +600,7 @@ def run_cuda(args):
         # the same requests with the reference's 64-token pages, for comparison
         line["paged_batch"]["pages_of_64_tokens"] = {
             k: v for k, v in run_paged_batch(torch, dist, device, world, rank, 64).items()
-            if k in ("us_per_step", "decode_tokens_per_s", "aggregate_gbs", "per_gpu_hbm_frac", "algorithmic_bytes_per_step")}
+            if k in ("us_per_step", "decode_tokens_per_s", "aggregate_gbs", "per_gpu_hbm_frac", "algorithmic_bytes_per_step", "parity")}
     if world == 1 and args.model_step:
         torch.cuda.empty_cache()
         line["model_step"] = run_model_step(args, torch, device)
@@ -580,6 +805,7 @@ def run_paged_batch(torch, dist, device, world, rank, block):
         dist.barrier()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
+    parity = check_paged_parity(torch, batch, seqs, [lengths[i] for i in mine], layers, block, heads)
     total_bytes = batch.algorithmic_bytes()["total"]
     if world > 1:
         t = torch.tensor([ms, float(total_bytes)], device=device, dtype=torch.float64)
@@ -593,7 +819,8 @@ def run_paged_batch(torch, dist, device, world, rank, block):
             "requests": requests, "context_tokens": sum(lengths), "us_per_step": round(ms * 1e3, 1),
             "decode_tokens_per_s": round(requests / (ms * 1e-3), 1), "aggregate_gbs": round(gbs, 1),
             "per_gpu_hbm_frac": round(gbs / world / peak, 4), "algorithmic_bytes_per_step": int(total_bytes),
-            "sharding": "requests dealt to the ranks by context length (longest first, to the least loaded rank), no collective", "steps": steps}
+            "sharding": "requests dealt to the ranks by context length (longest first, to the least loaded rank), no collective", "steps": steps,
+            "parity": parity}
 
 
 def run_split_kv(args, torch, dist, device, world, rank):
@@ -626,7 +853,9 @@ def run_split_kv(args, torch, dist, device, world, rank):
     inputs = torch.randn((args.warmup + steps, LAYERS, Q_HEADS + 2 * KV_HEADS, DIM), device=device, generator=gen).bfloat16()
     use_graph = not args.no_graph
 
-    def time_split(exchange):
+    parity = {}
+
+    def time_split(exchange, check=False):
         split = SplitKVDecode(seqs, Q_HEADS, owns_tail=last, exchange=exchange)
         for i in range(args.warmup):
             split.inputs.copy_(inputs[i])
@@ -650,6 +879,8 @@ def run_split_kv(args, torch, dist, device, world, rank):
             dist.barrier()
         torch.cuda.synchronize()
         ms = t0.elapsed_time(t1) / steps
+        if check:
+            parity.update(check_split_parity(torch, dist, split, cache, run_step, inputs[0], world, rank, first, last))
         local_bytes = split.batch.algorithmic_bytes()["total"]
         stats = torch.tensor([ms, float(local_bytes)], device=device, dtype=torch.float64)
         if world > 1:
@@ -660,7 +891,7 @@ def run_split_kv(args, torch, dist, device, world, rank):
             return float(worst[0]), float(total[1]), split.exchange
         return ms, float(local_bytes), split.exchange
 
-    ms, total_bytes, exchange = time_split("auto")
+    ms, total_bytes, exchange = time_split("auto", check=True)
     record_bytes = LAYERS * Q_HEADS * 130 * 4
     extra = {}
     if exchange == "p2p":
@@ -676,7 +907,7 @@ def run_split_kv(args, torch, dist, device, world, rank):
             "aggregate_gbs": round(total_bytes / (ms * 1e-3) / 1e9, 1),
             "per_gpu_hbm_frac": round(total_bytes / world / (ms * 1e-3) / 1e9 / peak, 4),
             "exchange": how, "launch": "CUDA graph of append + decode + exchange + merge" if use_graph else "eager",
-            "steps": steps, **extra}
+            "steps": steps, "parity": parity, **extra}
 
 
 # DRAM bytes (read + write) of one decode_kernel launch: 151.77 MB measured by ncu on the 10-layer
@@ -851,6 +1082,8 @@ def main():
     parser.add_argument("--skip-e2e", action="store_true", help="profiler captures: skip the host-buffer leg")
     parser.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill leg (config 2, one layer)")
     parser.add_argument("--no-paged-batch", action="store_true", help="skip the batched paged decode leg (config 3)")
+    parser.add_argument("--sustained-seconds", type=float, default=2.5,
+                        help="length of the sustained-clock leg (0 = skip)")
     parser.add_argument("--model-step", action="store_true",
                         help="also time a whole-model decode token (random-init 7B-shaped model) eagerly and from one CUDA graph")
     args = parser.parse_args()

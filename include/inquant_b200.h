@@ -34,7 +34,8 @@ enum { INQ_F32 = 0, INQ_F16 = 1, INQ_BF16 = 2 };
 /* bits of the device status word */
 enum {
   INQ_STATUS_NONFINITE = 1,       /* input (or a stored fp16 parameter) was not finite */
-  INQ_STATUS_BAD_INDEX = 2,       /* a table / page index was out of range and was skipped */
+  INQ_STATUS_BAD_INDEX = 2,       /* a role-map entry, tail position or (when the caller passed the
+                                   * pool size) page id was out of range and was not used */
   INQ_STATUS_WAIT_TIMEOUT = 4     /* a bounded device-side wait gave up */
 };
 
@@ -67,6 +68,9 @@ typedef struct {
   int32_t tokens, channels;
   const void* page_ids;  /* optional [n_outer] physical slots; NULL = identity */
   int32_t page_ids_i64;  /* 1 if page_ids is int64, 0 if int32 */
+  int64_t num_slots;     /* slots the destination holds: a row whose page id lies outside
+                          * [0, num_slots) is not written and INQ_STATUS_BAD_INDEX is set;
+                          * 0 = the caller vouches for the ids (they are not checked) */
 } inq_input_t;
 
 /* ---------------------------------------------------------------- K4 encoder
@@ -164,6 +168,10 @@ typedef struct {
   int64_t sink_key_stride_h, sink_key_stride_t, sink_value_stride_h, sink_value_stride_t;   /* elements */
   int64_t tail_key_stride_h, tail_key_stride_t, tail_value_stride_h, tail_value_stride_t;
   int32_t n_blocks, sink_tokens, tail_tokens, first_visible, tail_skip;
+  int32_t pool_pages;     /* layout 1: pages in `pool`.  A page_table entry outside [0, pool_pages)
+                           * is never dereferenced: page 0 is read in its place and
+                           * INQ_STATUS_BAD_INDEX is set (the step's output is then meaningless);
+                           * 0 = the caller vouches for the table (entries are not checked) */
   const int32_t* tail_tokens_device; /* optional: overrides tail_tokens, read on the device */
   float* partial_output;  /* optional [q_heads][130] fp32: when set, `output` is not written; the
                            * un-normalised record (acc[128], m in base-2 units, l) of each query

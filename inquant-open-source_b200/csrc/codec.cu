@@ -317,6 +317,10 @@ __global__ void __launch_bounds__(kMaxThreads) k4_encode_kernel(K4Params p) {
   K4Shared s = carve_k4_shared(raw, C, count, tokens, p.min_error != 0);
   const long long outer = blockIdx.x / p.in.n_inner, inner = blockIdx.x % p.in.n_inner;
   const long long slot = p.in.slot(outer);
+  if (!p.in.slot_ok(slot)) {   // uniform over the CTA: nothing of this row is written
+    if (threadIdx.x == 0) atomicOr(p.status, INQ_STATUS_BAD_INDEX);
+    return;
+  }
   const T* row = (const T*)p.in.x + outer * p.in.s_outer + inner * p.in.s_inner;
   const int c = threadIdx.x;
 
@@ -519,6 +523,10 @@ __global__ void __launch_bounds__(128, STAGED ? 5 : 7) k4_encode128_kernel(K4Par
   const bool want_error = p.min_error != 0;
   const long long outer = blockIdx.x / p.in.n_inner, inner = blockIdx.x % p.in.n_inner;
   const long long slot = p.in.slot(outer);
+  if (!p.in.slot_ok(slot)) {   // uniform over the CTA: nothing of this row is written
+    if (threadIdx.x == 0) atomicOr(p.status, INQ_STATUS_BAD_INDEX);
+    return;
+  }
   const T* row = (const T*)p.in.x + outer * p.in.s_outer + inner * p.in.s_inner;
   const int c = threadIdx.x;
   if (want_error)
@@ -991,6 +999,10 @@ __global__ void __launch_bounds__(256) v_encode_kernel(VParams p) {
   const int warps_per_block = blockDim.x / 32, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const long long outer = blockIdx.x / p.in.n_inner, inner = blockIdx.x % p.in.n_inner;
   const long long slot = p.in.slot(outer);
+  if (!p.in.slot_ok(slot)) {   // uniform over the CTA: nothing of this row is written
+    if (threadIdx.x == 0) atomicOr(p.status, INQ_STATUS_BAD_INDEX);
+    return;
+  }
   const int t = blockIdx.y * warps_per_block + warp;
   if (t >= p.in.tokens) return;
   const int C = p.in.channels, groups = C / p.group;
@@ -1058,6 +1070,10 @@ __global__ void __launch_bounds__(256) v_encode128_kernel(VParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long outer = blockIdx.x / p.in.n_inner, inner = blockIdx.x % p.in.n_inner;
   const long long slot = p.in.slot(outer);
+  if (!p.in.slot_ok(slot)) {   // uniform over the CTA: nothing of this row is written
+    if (threadIdx.x == 0) atomicOr(p.status, INQ_STATUS_BAD_INDEX);
+    return;
+  }
   const int t0 = (blockIdx.y * 8 + warp) * kRows;
   if (t0 >= p.in.tokens) return;
   const T* base = (const T*)p.in.x + outer * p.in.s_outer + inner * p.in.s_inner + lane * 4;

@@ -54,6 +54,9 @@ struct InputRef {
   int tokens, channels;
   const void* page_ids;
   int page_ids_i64;
+  long long num_slots;
+  // false for a page id outside the destination the caller described (the row is then skipped)
+  __device__ bool slot_ok(long long slot) const { return num_slots <= 0 || (slot >= 0 && slot < num_slots); }
   __device__ long long slot(long long p) const {
     if (!page_ids) return p;
     return page_ids_i64 ? ((const long long*)page_ids)[p] : (long long)((const int*)page_ids)[p];
@@ -61,7 +64,7 @@ struct InputRef {
 };
 inline InputRef make_input(const inq_input_t& in) {
   return InputRef{in.x, in.n_outer, in.n_inner, in.stride_outer, in.stride_inner, in.stride_token,
-                  in.tokens, in.channels, in.page_ids, in.page_ids_i64};
+                  in.tokens, in.channels, in.page_ids, in.page_ids_i64, in.num_slots};
 }
 inline int dtype_size(int dtype) { return dtype == INQ_F32 ? 4 : 2; }
 inline bool valid_dtype(int dtype) { return dtype == INQ_F32 || dtype == INQ_F16 || dtype == INQ_BF16; }

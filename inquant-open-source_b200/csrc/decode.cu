@@ -33,6 +33,7 @@
 //   * contractions use mma.sync.m16n8k16 with 16 tokens as M and the (up to 8) query heads
 //     of the KV head as N, so one pass serves the whole GQA group; base-2 online softmax with
 //     a lazily raised reference maximum.
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -61,9 +62,13 @@ constexpr int kQBytes = 8 * 4 * kQChunk * 4 + 64;   // staged query and two fact
 constexpr float kNegBig = -1.0e30f;
 constexpr int kWarpFixed = 2048 + 256 + 64 + 64 + 1024;  // per-warp scratch before the per-group parts
 constexpr float kRescaleSlack = 4.f;   // the running reference maximum may lag the true one by 2^4
+// start value of a gather accumulator: -(128 + 128/512) in units of 2^-13, so that it ends as
+// (code'_n - 128) + (code'_{n+8} - 128) / 512 (the fraction stays within +-1/4 even for a column
+// whose second salient channel does not exist)
+constexpr float kGatherInit = -128.25f / 8192.f;
 
 __host__ __device__ constexpr int warp_smem_bytes(int groups, int stage_bytes) {
-  return kWarpFixed + groups * (256 + 4096 + 64) + kStages * stage_bytes;
+  return kWarpFixed + groups * (256 + 2048 + 64) + kStages * stage_bytes;
 }
 
 struct SeqDesc {
@@ -78,6 +83,7 @@ struct SeqDesc {
   long long sink_k_sh, sink_k_st, sink_v_sh, sink_v_st;
   long long tail_k_sh, tail_k_st, tail_v_sh, tail_v_st;
   int n_blocks, sink_tokens, tail_tokens, first_visible, tail_skip;
+  int pool_pages;
   const int* tail_tokens_dev;
   float* partial_out;            // optional: un-normalised (acc[128], m, l) per query head instead of `out`
 };
@@ -189,6 +195,13 @@ __device__ __forceinline__ void mma_f16_first(float (&d)[4], unsigned a0, unsign
                : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
+// D = A*B + c with the same constant c in all four accumulators (first step of a chain)
+__device__ __forceinline__ void mma_f16_init(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                             unsigned b1, float c) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3},{%4,%5,%6,%7},{%8,%9},{%10,%10,%10,%10};"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c));
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -212,7 +225,7 @@ __device__ __forceinline__ float2 half2_bits_to_float2(unsigned bits) {
 template <int MODE>
 __device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const long long* table,
                                                   const signed char* roles, const unsigned char* pool,
-                                                  const int* page_table, int b, int h) {
+                                                  const int* page_table, int pool_pages, int b, int h) {
   BlockPtrs out;
   if (MODE == 0) {
     const long long* row = table + (long long)b * 6;
@@ -225,7 +238,13 @@ __device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const l
     out.vo = (const unsigned char*)row[5] + (long long)h * T * 4;
     out.kr = (const unsigned char*)roles + ((long long)b * P.H + h) * 128;
   } else {
-    const unsigned char* page = pool + (long long)page_table[b] * P.page_bytes;
+    int id = page_table[b];
+    if (pool_pages > 0 && (unsigned)id >= (unsigned)pool_pages) {
+      // never dereferenced: the first page stands in and the caller learns of it from the status word
+      atomicOr(P.status, INQ_STATUS_BAD_INDEX);
+      id = 0;
+    }
+    const unsigned char* page = pool + (long long)id * P.page_bytes;
     const long long T = P.T;
     out.kp = page + (long long)h * T * 64;
     out.ks = page + P.off_ks + (long long)h * 512;
@@ -285,17 +304,6 @@ __device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned
   }
 }
 
-// Optional phase stamps (build with -DINQ_DECODE_TIMING): per CTA, per visited pair (first two) and
-// per warp the SM clock at the phase boundaries, the global timer at both ends, the SM id and the
-// slices of the visit; read back through inq_debug_decode_phases.  Off in the shipped library.
-#ifdef INQ_DECODE_TIMING
-__device__ long long g_phase[512][2][4][12];
-#define INQ_STAMP(k) do { if (lane == 0 && blockIdx.x < 512 && visit < 2) g_phase[blockIdx.x][visit][warp][k] = clock64(); } while (0)
-#define INQ_GSTAMP(k) do { if (lane == 0 && blockIdx.x < 512 && visit < 2) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_phase[blockIdx.x][visit][warp][k] = t; } } while (0)
-#else
-#define INQ_STAMP(k)
-#define INQ_GSTAMP(k)
-#endif
 // ------------------------------------------------------------------------------------------ the kernel
 template <int MODE, typename QT, bool SAL, int SUB>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const DecodeParams P) {
@@ -324,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   unsigned char* wmeta = wdon + 64;       // staged block metadata: K scales 512 B | role map 256 B | padding 256 B
   unsigned char* wqsal = wb + kWarpFixed;                               // B fragments: query at salient channels
   unsigned char* wsel = wqsal + groups * 256;                           // B fragments: nibble selection
-  unsigned short* wcell = (unsigned short*)(wsel + groups * 4096);      // selection cells written by the last fold (offsets into wsel)
+  unsigned short* wcell = (unsigned short*)(wsel + groups * 2048);      // selection cells written by the last fold (offsets into wsel)
   unsigned char* ring = (unsigned char*)wcell + groups * 64;
   __shared__ int s_is_last;
 
@@ -350,19 +358,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   } else {
     pair = (int)(pos / (P.uniform_units + R));
   }
-  int visit = -1;   // read by the optional phase stamps only
-  (void)visit;
   for (; pos < c_end; ++pair) {
   const long long pair_lo = (P.pair_starts ? P.pair_starts[pair] : (long long)pair * P.uniform_units) + (pair + 1) * R;   // first slice
   const long long pair_hi = (P.pair_starts ? P.pair_starts[pair + 1] : (long long)(pair + 1) * P.uniform_units) + (pair + 1) * R;
   const long long seg_lo = max(pos, pair_lo) - pair_lo, seg_hi = min(c_end, pair_hi) - pair_lo;
   pos = min(c_end, pair_hi);
   if (seg_hi <= seg_lo) continue;   // only ramp positions of this pair fall into the range
-  ++visit;
-  INQ_STAMP(0); INQ_GSTAMP(8);
-#ifdef INQ_DECODE_TIMING
-  if (lane == 0 && blockIdx.x < 512 && visit < 2) { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); g_phase[blockIdx.x][visit][warp][10] = smid; g_phase[blockIdx.x][visit][warp][11] = seg_hi - seg_lo; }
-#endif
   const int first_cta = (int)(pair_lo / P.per_cta), last_cta = (int)((pair_hi - 1) / P.per_cta);
   const int n_cta_pair = last_cta - first_cta + 1;
   const int seq = pair / (P.H * gtiles);
@@ -375,6 +376,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   const signed char* const d_roles = SEQ(roles);
   const unsigned char* const d_pool = SEQ(pool);
   const int* const d_pages = SEQ(page_table);
+  const int d_pool_pages = SEQ(pool_pages);
   const int first_visible = SEQ(first_visible);
   const int g_valid = min(8, P.G - gt * 8);
   const long long q_head0 = (long long)h * P.G + gt * 8;
@@ -383,7 +385,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
 
   // the merge of the previous pair may have used this scratch: start from an empty selection
   // matrix and an empty list of written cells
-  for (int v = lane; v < groups * 256; v += 32) ((uint4*)wsel)[v] = make_uint4(0u, 0u, 0u, 0u);
+  for (int v = lane; v < groups * 128; v += 32) ((uint4*)wsel)[v] = make_uint4(0u, 0u, 0u, 0u);
+  for (int v = lane; v < 64; v += 32) wssc[v] = 0.f;   // scales of unused salient slots must be finite
   for (int v = lane; v < groups * 32; v += 32) wcell[v] = 0;
   // query as fp32, chunked so that lanes (head, chunk) read distinct banks, then scaled per head by
   // a power of two that brings its largest magnitude into [2^12, 2^13): every folded weight is
@@ -422,8 +425,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     }
   }
   __syncthreads();
-
-  INQ_STAMP(1);
   const int T = P.T;
   const int spb = (T + kSliceTokens - 1) / kSliceTokens;   // packed slices per block
   const int n_blocks = SEQ(n_blocks);
@@ -553,7 +554,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   if (pb > pa) {
     const int n_my = (int)(pb - pa);
     int pf_block = (int)(pa / spb), pf_slice = (int)(pa % spb);   // prefetch cursor
-    BlockPtrs pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
+    BlockPtrs pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h);
     int to_issue = n_my, issue_stage = 0;
     int meta_block = -1;        // block whose metadata is staged (or in flight) in wmeta
     int folded_block = -2;      // last block whose weights were derived from wmeta
@@ -583,7 +584,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         if (++pf_slice == spb) {
           pf_slice = 0;
           ++pf_block;
-          if (to_issue > 0) pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, pf_block, h);
+          if (to_issue > 0) pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h);
         }
       }
       cp_async_commit();
@@ -593,7 +594,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     // the dense slices of this warp hide behind the DRAM latency of the first packed slices;
     // their contribution is brought into the packed loop's per-row units (powers of two)
     dense_part();
-    INQ_STAMP(2);
     {
       const float ix[4] = {1.f / 16777216.f, 1.f / 1048576.f, 1.f / 65536.f, 1.f / 4194304.f};
       const float iy[4] = {1.f / 4194304.f, 1.f / 262144.f, 1.f / 16777216.f, 1.f / 1048576.f};
@@ -615,15 +615,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     const int v_tok = (lane & 7) + 8 * ((lane >> 3) & 1);
     const unsigned v_ldsm = (unsigned)((2 * v_tok + ((lane >> 4) ^ ((v_tok >> 2) & 1))) << 4);
     const unsigned ring_addr = smem_addr(ring), lane16 = lane * 16;
-    const unsigned ww_addr = smem_addr(wW) + lane * 8, sel_addr = smem_addr(wsel) + lane * 16;
+    const unsigned ww_addr = smem_addr(wW) + lane * 8, sel_addr = smem_addr(wsel) + lane * 8;
     int stage_index = 0;
 
     for (int it = 0; it < n_my; ++it) {
       cp_async_wait<kStages - 2>();
       __syncwarp();
-#ifdef INQ_DECODE_TIMING
-      if (it == 0) INQ_STAMP(3);
-#endif
       // With fewer than three slices per block the next block's metadata can only be staged once
       // this block's fold has released the staging area: there the copies are issued after the
       // fold.  Otherwise they go out first.
@@ -637,7 +634,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           meta = ring + stage_index * kStageBytes + kMetaOffset;
         } else if (meta_block != cur_block) {
           // not prefetched (very short blocks): fetch now and wait for it alone
-          BlockPtrs cb = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, cur_block, h);
+          BlockPtrs cb = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, cur_block, h);
           __syncwarp();
           stage_meta(cb, wmeta);
           cp_async_commit();
@@ -713,18 +710,21 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           }
         }
         __syncwarp();
-        // selection matrix: column idx picks 16 * (high nibble of the source) + (low nibble in the
-        // donor slot), scaled by 2^11 so that every entry and every partial sum is exact.  One
-        // cell per lane: entry v is the source (even v) or the donor slot (odd v) of salient v / 2.
+        // selection matrix: column (idx & 7) gathers the codes of TWO salient channels into one fp32
+        // accumulator, code' = 16 * (high nibble of the source) + (low nibble in the donor slot) of
+        // salient idx with weight 2^-13 when idx & 8 is clear and with weight 2^-22 when it is set;
+        // every entry and every partial sum is exact.  One cell per lane: entry v is the source
+        // (even v) or the donor slot (odd v) of salient v / 2.
         for (int v = lane; v < 2 * P.n_pad; v += 32) {
           const int idx = v >> 1, which = v & 1;
           const int c = (which ? wdon[idx] : wsrc[idx]) & 127;
           const int jj = c >> 5, u = c & 31;
           const int ks = 2 * (u >> 3) + ((u >> 1) & 1), half = u & 1, e = (u >> 2) & 1;
           const int target = ((idx & 7) << 2) | jj;
-          const int cell = ((((idx >> 4) * 8 + ks) * 32 + target) * 16) + (((idx >> 3) & 1) * 2 + half) * 4 + e * 2;
-          // fp16 bits of 32768 (source), 2048 (donor), each divided by 16 for the high nibble of a byte
-          *(unsigned short*)(wsel + cell) = (unsigned short)(0x7800 - (which + half) * 0x1000);
+          const int cell = ((((idx >> 4) * 8 + ks) * 32 + target) * 8) + half * 4 + e * 2;
+          // fp16 bits of 32768 (source), 2048 (donor), each divided by 16 for the high nibble of a
+          // byte and by 512 for the second salient channel of the column
+          *(unsigned short*)(wsel + cell) = (unsigned short)(0x7800 - (which + half) * 0x1000 - ((idx >> 3) & 1) * 0x2400);
           wcell[v] = (unsigned short)cell;
         }
         __syncwarp();
@@ -788,7 +788,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       //      times the folded query, plus the exactly rebuilt salient channels
       float S[2][4], S2[2][4];
       {
-        float C[2][2][4];   // [sub-slice][n-tile][frag]: code' = 16*hi + lo of salient group 0
+        // C[sub-slice][frag]: column n of the gather holds the codes of salient n and n + 8 of the
+        // group as (code'_n - 128) + (code'_{n+8} - 128) / 512, in units of 2^-13
+        float C[2][4];
         // One sub-slice at a time keeps the live register set small: this lane's 16 bytes
         // (channels 32j..32j+31) of tokens r and r+8 of the sub-slice.
 // One K step: the fragments of the NEXT step are fetched before this step's MMAs are issued,
@@ -799,20 +801,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     if (FIRST) mma_f16_first(S[U], a0, a1, a2, a3, WQ.x, WQ.y);                                           \
     else mma_f16(S[U], a0, a1, a2, a3, WQ.x, WQ.y);                                                       \
     if (SAL) {                                                                                            \
-      if (FIRST) {                                                                                        \
-        mma_f16_first(C[U][0], a0, a1, a2, a3, F.x, F.y);                                                 \
-        mma_f16_first(C[U][1], a0, a1, a2, a3, F.z, F.w);                                                 \
-      } else {                                                                                            \
-        mma_f16(C[U][0], a0, a1, a2, a3, F.x, F.y);                                                       \
-        mma_f16(C[U][1], a0, a1, a2, a3, F.z, F.w);                                                       \
-      }                                                                                                   \
+      if (FIRST) mma_f16_init(C[U], a0, a1, a2, a3, F.x, F.y, kGatherInit);                               \
+      else mma_f16(C[U], a0, a1, a2, a3, F.x, F.y);                                                       \
     }                                                                                                     \
   }
 #define INQ_KSTEP(KS, M, SH, FIRST, WQ, F, WQN, FN)                                                       \
   {                                                                                                       \
     if ((KS) < 7) {                                                                                       \
       WQN = lds64<(((KS) + 1) & 7) * 256>(ww_it);                                                         \
-      if (SAL) FN = lds128<(((KS) + 1) & 7) * 512>(sel_it);                                               \
+      if (SAL) FN = lds64<(((KS) + 1) & 7) * 256>(sel_it);                                                \
     }                                                                                                     \
     INQ_KMMA(0, kx0.M >> SH, ky0.M >> SH, FIRST, WQ, F)                                                   \
     if (kSub > 1) INQ_KMMA(kSub - 1, kx1.M >> SH, ky1.M >> SH, FIRST, WQ, F)                              \
@@ -821,8 +818,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           const uint4 kx0 = lds128<0>(stage + lane16), ky0 = lds128<512>(stage + lane16);
           const uint4 kx1 = lds128<(kSub > 1 ? 1024 : 0)>(stage + lane16), ky1 = lds128<(kSub > 1 ? 1536 : 512)>(stage + lane16);
           uint2 wa = lds64<0>(ww_it), wb_;
-          uint4 fa = make_uint4(0u, 0u, 0u, 0u), fb = fa;
-          if (SAL) fa = lds128<0>(sel_it);
+          uint2 fa = make_uint2(0u, 0u), fb = fa;
+          if (SAL) fa = lds64<0>(sel_it);
           INQ_KSTEP(0, x, 0, true, wa, fa, wb_, fb)
           INQ_KSTEP(1, x, 8, false, wb_, fb, wa, fa)
           INQ_KSTEP(2, y, 0, false, wa, fa, wb_, fb)
@@ -833,7 +830,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           INQ_KSTEP(7, w, 8, false, wb_, fb, wa, fa)
         }
 #undef INQ_KMMA
-#undef INQ_KSUB
 #undef INQ_KSTEP
         if (SAL) {
 #pragma unroll
@@ -850,37 +846,42 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
 #pragma unroll
               for (int u = 0; u < kSub; ++u)
 #pragma unroll
-                for (int n = 0; n < 2; ++n)
-#pragma unroll
-                  for (int k = 0; k < 4; ++k) C[u][n][k] = 0.f;
-              const uint4* selg = (const uint4*)wsel + gsel * 256 + lane;
+                for (int k = 0; k < 4; ++k) C[u][k] = kGatherInit;
+              const uint2* selg = (const uint2*)wsel + gsel * 256 + lane;
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 unsigned x0 = kw[0][i], y0 = kw[1][i], x1 = kw[2][i], y1 = kw[3][i];
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                  const uint4 f = selg[(2 * i + hh) * 32];
-                  const unsigned a0 = x0 & 0x000F000Fu, a1 = y0 & 0x000F000Fu, a2 = x0 & 0x00F000F0u, a3 = y0 & 0x00F000F0u;
-                  const unsigned b0 = x1 & 0x000F000Fu, b1 = y1 & 0x000F000Fu, b2 = x1 & 0x00F000F0u, b3 = y1 & 0x00F000F0u;
-                  mma_f16(C[0][0], a0, a1, a2, a3, f.x, f.y);
-                  mma_f16(C[1][0], b0, b1, b2, b3, f.x, f.y);
-                  mma_f16(C[0][1], a0, a1, a2, a3, f.z, f.w);
-                  mma_f16(C[1][1], b0, b1, b2, b3, f.z, f.w);
+                  const uint2 f = selg[(2 * i + hh) * 32];
+                  mma_f16(C[0], x0 & 0x000F000Fu, y0 & 0x000F000Fu, x0 & 0x00F000F0u, y0 & 0x00F000F0u, f.x, f.y);
+                  if (kSub > 1)
+                    mma_f16(C[kSub - 1], x1 & 0x000F000Fu, y1 & 0x000F000Fu, x1 & 0x00F000F0u, y1 & 0x00F000F0u, f.x, f.y);
                   x0 >>= 8; y0 >>= 8; x1 >>= 8; y1 >>= 8;
                 }
               }
             }
             // value = fl32((code' - 128) * scale) rounded to the model dtype, as the reference's
-            // dequantised tensor holds it
+            // dequantised tensor holds it.  The two codes of an accumulator are separated exactly:
+            // adding 1.5 * 2^23 rounds to the integer part (the fraction stays within 1/4), the rest
+            // is the second code over 512.
             const float2 sc0 = *(const float2*)(wssc + gsel * 16 + 2 * j);
-            const float2 sc1 = *(const float2*)(wssc + gsel * 16 + 8 + 2 * j);
+            float2 sc1 = *(const float2*)(wssc + gsel * 16 + 8 + 2 * j);
+            sc1.x *= 512.f;
+            sc1.y *= 512.f;
             const uint2 qb = *(const uint2*)(wqsal + (gsel * 32 + lane) * 8);
 #pragma unroll
             for (int u = 0; u < kSub; ++u) {
-              const unsigned a0 = pack_qt2<QT>(fmaf(C[u][0][0], 8192.f, -128.f) * sc0.x, fmaf(C[u][0][1], 8192.f, -128.f) * sc0.y);
-              const unsigned a1 = pack_qt2<QT>(fmaf(C[u][0][2], 8192.f, -128.f) * sc0.x, fmaf(C[u][0][3], 8192.f, -128.f) * sc0.y);
-              const unsigned a2 = pack_qt2<QT>(fmaf(C[u][1][0], 8192.f, -128.f) * sc1.x, fmaf(C[u][1][1], 8192.f, -128.f) * sc1.y);
-              const unsigned a3 = pack_qt2<QT>(fmaf(C[u][1][2], 8192.f, -128.f) * sc1.x, fmaf(C[u][1][3], 8192.f, -128.f) * sc1.y);
+              float hi[4], lo[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                hi[k] = fmaf(C[u][k], 8192.f, 12582912.f) - 12582912.f;
+                lo[k] = fmaf(C[u][k], 8192.f, -hi[k]);
+              }
+              const unsigned a0 = pack_qt2<QT>(hi[0] * sc0.x, hi[1] * sc0.y);
+              const unsigned a1 = pack_qt2<QT>(hi[2] * sc0.x, hi[3] * sc0.y);
+              const unsigned a2 = pack_qt2<QT>(lo[0] * sc1.x, lo[1] * sc1.y);
+              const unsigned a3 = pack_qt2<QT>(lo[2] * sc1.x, lo[3] * sc1.y);
               mma_qt<QT>(S2[u], a0, a1, a2, a3, qb.x, qb.y);
             }
           }
@@ -983,7 +984,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         need_weights = true;
       }
     }
-    INQ_STAMP(4);
     cp_async_wait<0>();
     // a code at bit offset o of its 16-bit lane was multiplied as code * 2^(o-24)
     const float fx[4] = {16777216.f, 1048576.f, 65536.f, 4194304.f};   // offsets 0, 4, 8, 2
@@ -1013,7 +1013,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     osum[gr][1] = __shfl_sync(0xffffffffu, oacc[1], gr * 4 + j);
   }
   __syncthreads();   // every warp is done with its ring and weight scratch
-  INQ_STAMP(5);
   float* wout = (float*)ring;   // [8][132]
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
@@ -1068,7 +1067,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     if (s_is_last) P.counters[pair] = 0;   // scratch is left zeroed for the next launch
   }
   __syncthreads();
-  INQ_STAMP(6);
   if (s_is_last) {
   __threadfence();
     // A sequence decoded alone is cut into a hundred parts per pair, so this merge is written for
@@ -1158,7 +1156,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     }
   }
   __syncthreads();   // shared scratch is reused by the next pair of this CTA
-  INQ_STAMP(7); INQ_GSTAMP(9);
   }  // pairs of this CTA
 }
 
@@ -1171,16 +1168,40 @@ static int smem_bytes(int groups, int sub) {
 
 using namespace inq;
 
-static int g_sm_count = 0;
+// Per-device launch state.  Function attributes, occupancy answers and the SM count belong to a
+// device, not to the process: a process that drives several GPUs (or several host threads) gets
+// one record per device ordinal, filled under a mutex on first use.
+constexpr int kMaxDevices = 64;
+constexpr int kKernelVariants = 16;
+struct DeviceState {
+  int sm_count = 0;
+  bool raised[kKernelVariants] = {};
+  int per_sm[kKernelVariants][5] = {};
+  void* static_scratch = nullptr;   // resolved address of the allocation-free entry point's array
+  bool static_counters_stale = false;
+};
+static DeviceState g_devices[kMaxDevices];
+static std::mutex g_devices_mutex;
+
+static int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
 static int sm_count() {
-  if (!g_sm_count) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-      g_sm_count = n;
+  const int dev = current_device();
+  if (dev < 0) return 148;
+  std::lock_guard<std::mutex> guard(g_devices_mutex);
+  DeviceState& d = g_devices[dev];
+  if (!d.sm_count) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      d.sm_count = n;
     else
       return 148;
   }
-  return g_sm_count;
+  return d.sm_count;
 }
 
 // Flat decomposition shared by the planner and the launcher.
@@ -1265,20 +1286,26 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
       decode_kernel<0, __nv_bfloat16, false, 1>, decode_kernel<0, __nv_bfloat16, true, 1>,
       decode_kernel<1, __half, false, 1>, decode_kernel<1, __half, true, 1>,
       decode_kernel<1, __nv_bfloat16, false, 1>, decode_kernel<1, __nv_bfloat16, true, 1>};
-  static bool raised[16] = {};
-  static int per_sm[16][5] = {};
   const int which = (sub == 1 ? 8 : 0) + a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);
   const kernel_t kernel = kernels[which];
-  if (!raised[which]) {
-    INQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4, sub)));
-    raised[which] = true;
+  const int device = current_device();
+  if (device < 0) return INQ_ERR_UNSUPPORTED;   // device ordinals above 63 are not tracked
+  int resident = 0;
+  {
+    std::lock_guard<std::mutex> guard(g_devices_mutex);
+    DeviceState& d = g_devices[device];
+    if (!d.raised[which]) {
+      INQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4, sub)));
+      d.raised[which] = true;
+    }
+    if (!d.per_sm[which][groups]) {
+      int n = 0;
+      INQ_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, shared));
+      d.per_sm[which][groups] = n > 0 ? n : 1;
+    }
+    resident = d.per_sm[which][groups];
   }
-  if (!per_sm[which][groups]) {
-    int n = 0;
-    INQ_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, shared));
-    per_sm[which][groups] = n > 0 ? n : 1;
-  }
-  const Plan plan = make_plan(total, (int)n_pairs, uniform, per_sm[which][groups]);
+  const Plan plan = make_plan(total, (int)n_pairs, uniform, resident);
   if (((long long)plan.n_ctas + n_pairs) * kRecordFloats > a->partials_floats) return INQ_ERR_CAPACITY;
   DecodeParams P;
   P.seqs = (const SeqDesc*)a->seqs_device;
@@ -1336,22 +1363,35 @@ extern "C" int inq_decode_attention_noalloc(const inq_decode_args_t* a, inq_stre
   if (n_pairs > kStaticPairs) return INQ_ERR_CAPACITY;
   // The array's name is a host-side stand-in, not a device address: resolve it once per device,
   // with that device current, and hand the resolved pointer to the kernel.
-  static void* resolved[64] = {};
-  int device = -1;
-  INQ_CUDA_CHECK(cudaGetDevice(&device));
-  if (device < 0 || device >= 64) return INQ_ERR_UNSUPPORTED;
-  if (!resolved[device]) {
-    void* ptr = nullptr;
-    INQ_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
-    // counters must start at zero (the kernel leaves them zero afterwards)
-    INQ_CUDA_CHECK(cudaMemsetAsync(ptr, 0, kStaticCounterBytes, (cudaStream_t)stream_));
-    resolved[device] = ptr;
+  const int device = current_device();
+  if (device < 0) return INQ_ERR_UNSUPPORTED;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> guard(g_devices_mutex);
+    DeviceState& d = g_devices[device];
+    if (!d.static_scratch || d.static_counters_stale) {
+      void* ptr = nullptr;
+      INQ_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
+      // The arrival counters must be zero when a launch starts.  Every launch that runs to its end
+      // leaves them zero, so they are cleared on the first call on a device and again after a call
+      // whose launch was refused by the runtime.  A launch that is cut short on the device (the
+      // context is torn down under it) ends the process's use of that context anyway.
+      INQ_CUDA_CHECK(cudaMemsetAsync(ptr, 0, kStaticCounterBytes, (cudaStream_t)stream_));
+      d.static_scratch = ptr;
+      d.static_counters_stale = false;
+    }
+    scratch = d.static_scratch;
   }
   inq_decode_args_t local = *a;
-  local.counters = (int32_t*)resolved[device];
-  local.partials = (float*)((unsigned char*)resolved[device] + kStaticCounterBytes);
+  local.counters = (int32_t*)scratch;
+  local.partials = (float*)((unsigned char*)scratch + kStaticCounterBytes);
   local.partials_floats = (int64_t)kStaticRecords * kRecordFloats;
-  return inq_decode_attention(&local, stream_);   // INQ_ERR_CAPACITY when the launch needs more records
+  const int rc = inq_decode_attention(&local, stream_);   // INQ_ERR_CAPACITY when the launch needs more records
+  if (rc == INQ_ERR_CUDA) {
+    std::lock_guard<std::mutex> guard(g_devices_mutex);
+    g_devices[device].static_counters_stale = true;
+  }
+  return rc;
 }
 
 
@@ -1389,8 +1429,3 @@ extern "C" int inq_merge_partials(const float* records, int32_t n_parts, int64_t
   return INQ_OK;
 }
 
-#ifdef INQ_DECODE_TIMING
-extern "C" int inq_debug_decode_phases(void* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, inq::g_phase, sizeof(inq::g_phase));
-}
-#endif

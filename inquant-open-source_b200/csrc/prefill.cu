@@ -548,12 +548,9 @@ extern "C" int inq_prefill_attention(const inq_prefill_args_t* a, inq_stream_t s
   {
     // cut every item into `splits` KV segments when that fills the SMs more evenly: rounds of
     // CTAs over the SMs, each round as long as one segment, a few per cent of overhead per cut
-    static int n_sm = 0;
-    if (!n_sm) {
-      int device = 0;
-      INQ_CUDA_CHECK(cudaGetDevice(&device));
-      INQ_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
-    }
+    int n_sm = 0, device = 0;   // asked per call: the answer belongs to the current device
+    INQ_CUDA_CHECK(cudaGetDevice(&device));
+    INQ_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
     const long long items = (long long)P.n_qpairs * a->q_heads;
     const int lightest = (int)((std::min<long long>(a->kv_tokens, (long long)a->kv_tokens - a->q_tokens + kPfRows) + kPfTile - 1) / kPfTile);
     // cost of a cut into sp segments, in KV-tile times: rounds of CTAs over the SMs, each as long

@@ -28,7 +28,8 @@ class Field(ctypes.Structure):
 class Input(ctypes.Structure):
     _fields_ = [("x", c_void_p), ("dtype", c_int32), ("n_outer", c_int64), ("n_inner", c_int64),
                 ("stride_outer", c_int64), ("stride_inner", c_int64), ("stride_token", c_int64),
-                ("tokens", c_int32), ("channels", c_int32), ("page_ids", c_void_p), ("page_ids_i64", c_int32)]
+                ("tokens", c_int32), ("channels", c_int32), ("page_ids", c_void_p), ("page_ids_i64", c_int32),
+                ("num_slots", c_int64)]
 
 
 class K4EncodeArgs(ctypes.Structure):
@@ -51,7 +52,8 @@ class DecodeSeq(ctypes.Structure):
                 ("tail_key_stride_h", c_int64), ("tail_key_stride_t", c_int64),
                 ("tail_value_stride_h", c_int64), ("tail_value_stride_t", c_int64),
                 ("n_blocks", c_int32), ("sink_tokens", c_int32), ("tail_tokens", c_int32),
-                ("first_visible", c_int32), ("tail_skip", c_int32), ("tail_tokens_device", c_void_p),
+                ("first_visible", c_int32), ("tail_skip", c_int32), ("pool_pages", c_int32),
+                ("tail_tokens_device", c_void_p),
                 ("partial_output", c_void_p)]
 
 
@@ -209,12 +211,15 @@ def status_word(device: torch.device) -> torch.Tensor:
     return word
 
 
-def take_status(device: torch.device) -> int:
-    """Read and clear the status word (synchronises the current stream)."""
+def take_status(device: torch.device, mask: int = -1) -> int:
+    """Read the status word and clear the bits of ``mask`` that were set (synchronises the current
+    stream).  Bits outside ``mask`` stay in the word for whoever asks for them: a wait that timed
+    out or a skipped index is not lost because an encoder checked its finite bit in between.
+    Returns the bits of ``mask`` that were set."""
     word = status_word(device)
-    value = int(word.item())
+    value = int(word.item()) & mask
     if value:
-        word.zero_()
+        word.bitwise_and_(~value)
     return value
 
 
@@ -240,7 +245,7 @@ def nonfinite_reported(device: torch.device) -> bool:
     status reads are deferred."""
     if _deferred_depth:
         return False
-    return bool(take_status(device) & STATUS_NONFINITE)
+    return bool(take_status(device, STATUS_NONFINITE))
 
 
 def pointer(tensor: torch.Tensor | None) -> c_void_p:
@@ -257,12 +262,14 @@ def compact_field(tensor: torch.Tensor | None, n_inner: int) -> Field:
     return Field(tensor.data_ptr(), row * n_inner, row)
 
 
-def make_input(x: torch.Tensor, page_ids: torch.Tensor | None = None) -> Input:
-    """``x`` is [outer, inner, tokens, channels] with unit channel stride (any other strides)."""
+def make_input(x: torch.Tensor, page_ids: torch.Tensor | None = None, num_slots: int = 0) -> Input:
+    """``x`` is [outer, inner, tokens, channels] with unit channel stride (any other strides).
+    ``num_slots`` is the number of rows of the destination that ``page_ids`` index (ids outside it
+    are skipped on the device and reported through the status word)."""
     assert x.ndim == 4 and x.stride(3) == 1
     return Input(x.data_ptr(), DTYPE_CODE[x.dtype], x.shape[0], x.shape[1], x.stride(0), x.stride(1), x.stride(2),
                  x.shape[2], x.shape[3], None if page_ids is None else page_ids.data_ptr(),
-                 0 if page_ids is None else int(page_ids.dtype == torch.int64))
+                 0 if page_ids is None else int(page_ids.dtype == torch.int64), int(num_slots))
 
 
 _counters: dict[tuple, torch.Tensor] = {}

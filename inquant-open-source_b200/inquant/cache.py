@@ -180,6 +180,15 @@ class InQuantCache(_HFCache):
         self._tracked_aux_bytes = 0
         self.peak_nbytes = 0
         self._seen_tokens = 0
+        self._pending_commit = None
+
+    def _flush_pending(self) -> None:
+        """A graphed decode step (``inquant.graph_decode``) advances the tails on the device and books
+        the tokens into the host-side counters later; it registers that booking here so that every
+        entry point of the cache sees current lengths."""
+        hook = self._pending_commit
+        if hook is not None:
+            hook()
 
     def __len__(self) -> int:
         return max(self._layers, default=-1) + 1
@@ -192,6 +201,7 @@ class InQuantCache(_HFCache):
             yield self.materialize(idx)
 
     def get_seq_length(self, layer_idx: int | None = 0) -> int:
+        self._flush_pending()
         layer = self._layers.get(0 if layer_idx is None else layer_idx)
         return 0 if layer is None else layer.seq_length
 
@@ -248,6 +258,7 @@ class InQuantCache(_HFCache):
             self._seen_tokens = layer.seq_length
 
     def _validate_update(self, key_states, value_states, layer_idx, cache_kwargs):
+        self._flush_pending()
         if not isinstance(layer_idx, int) or layer_idx < 0:
             raise ValueError("layer_idx must be a nonnegative integer")
         if key_states.ndim != 4 or value_states.shape != key_states.shape:
@@ -435,6 +446,7 @@ class InQuantCache(_HFCache):
     @torch.no_grad()
     def materialize(self, layer_idx: int = 0):
         """Reconstruct this layer; returned tensors are not retained (reference ``cache.py:328-345``)."""
+        self._flush_pending()
         if layer_idx not in self._layers:
             raise KeyError(f"No cached layer {layer_idx}")
         layer = self._layers[layer_idx]
@@ -469,6 +481,7 @@ class InQuantCache(_HFCache):
 
     @property
     def residual_nbytes(self) -> int:
+        self._flush_pending()
         return sum(_tensor_bytes(layer.residual_key) + _tensor_bytes(layer.residual_value) for layer in self._layers.values())
 
     @property
@@ -487,9 +500,11 @@ class InQuantCache(_HFCache):
 
     @property
     def bf16_nbytes(self) -> int:
+        self._flush_pending()
         return sum(2 * 2 * layer.shape[0] * layer.shape[1] * layer.seq_length * layer.shape[3] for layer in self._layers.values())
 
     def memory_stats(self) -> dict[str, int | float]:
+        self._flush_pending()
         total, baseline = self.nbytes, self.bf16_nbytes
         return {
             "nbytes": total,
@@ -505,6 +520,7 @@ class InQuantCache(_HFCache):
         }
 
     def reset(self) -> None:
+        self._pending_commit = None
         self._layers.clear()
         self._attention_states.clear()
         self._shared_decode_workspace = None

@@ -210,13 +210,13 @@ def _validate_input(x: torch.Tensor) -> None:
 
 
 def encode_into(x: torch.Tensor, config: CodecConfig, payload, scales, salient, donors, padding,
-                roles=None, page_ids=None) -> None:
+                roles=None, page_ids=None, num_slots: int = 0) -> None:
     """Launch the fused encoder on ``x`` = [outer, inner, tokens, channels] (unit channel
     stride); outputs are ``_native.Field`` descriptors.  No synchronisation."""
     channels = x.shape[-1]
     count = math.floor(channels * config.salient_fraction)
     args = N.K4EncodeArgs()
-    args.input = N.make_input(x, page_ids)
+    args.input = N.make_input(x, page_ids, num_slots)
     args.sample_stride = config.sample_stride
     args.count = count
     args.min_error = int(config.donor_policy == "min_error")

@@ -11,7 +11,12 @@ CUDA graph and replays it per token.  What makes the step replayable:
   (``DecodeBatch`` of one sequence), so the graph does not depend on the tail length;
 * token id and position are static device tensors updated in place;
 * the cache's host-side bookkeeping (tail length, sequence length) is applied afterwards by
-  ``commit``, which also runs automatically before anything else touches the cache.
+  ``commit``.  While a graph is attached the stepper registers ``commit`` with the cache
+  (``InQuantCache._pending_commit``), and every entry point of the cache that reads or changes its
+  lengths (``update``, ``extend``, ``append_for_attention``, ``materialize``, ``get_seq_length``,
+  ``memory_stats``) runs it first, so direct use of the cache between steps sees current state.
+  A forward of the patched model that does not come from this stepper (a plain ``model(...)`` or
+  ``generate`` call) commits, detaches the graph and takes the ordinary path.
 
 When a tail is about to reach the length at which the cache seals a block, the step is run
 eagerly once through the ordinary patched forward (which seals exactly as
@@ -49,19 +54,27 @@ class GraphedDecodeStep:
         self._takes_cache_position = "cache_position" in inspect.signature(model.forward).parameters
         self._graph: torch.cuda.CUDAGraph | None = None
         self._pending = 0          # replayed steps not yet booked into the cache
+        self._driving = False      # True while this stepper itself runs the model's forward
         self._room = 0             # replays left before a tail reaches its sealing length
         self.replays = self.eager_steps = self.captures = 0
 
     # ------------------------------------------------------------------ graph life cycle
     def _forward(self):
         extra = {"cache_position": self.position} if self._takes_cache_position else {}
-        out = self.model(input_ids=self.token, position_ids=self.position.view(1, 1), past_key_values=self.cache,
-                         use_cache=True, **extra)
+        previous, self._driving = self._driving, True
+        try:
+            out = self.model(input_ids=self.token, position_ids=self.position.view(1, 1), past_key_values=self.cache,
+                             use_cache=True, **extra)
+        finally:
+            self._driving = previous
         return out.logits
 
     def _detach(self) -> None:
         for module in self.modules:
             module._inquant_graph_batch = None
+            module._inquant_graph_owner = None
+        if self.cache._pending_commit == self.commit:
+            self.cache._pending_commit = None
         self._graph = None
 
     def _capture(self) -> None:
@@ -75,6 +88,7 @@ class GraphedDecodeStep:
             heads = module.config.num_attention_heads
             module._inquant_graph_batch = DecodeBatch([SequenceState.from_cache_layer(cache, index)], heads,
                                                       layer.dtype, scale=module.scaling)
+            module._inquant_graph_owner = self
             # the cache appends in place while tail + 1 stays below its capacity, then seals
             rooms.append(min(capacity, layer.tail_key_buffer.shape[2]) - 1 - layer.tail_count)
         self._room = min(rooms)
@@ -108,19 +122,21 @@ class GraphedDecodeStep:
             self._detach()
             raise RuntimeError("the captured forward did not reach the packed decode path in every layer")
         self.logits, self._graph = logits, graph
+        cache._pending_commit = self.commit
         self.captures += 1
 
     def commit(self) -> None:
         """Book the replayed steps into the cache (tail and sequence lengths)."""
-        if not self._pending:
+        pending, self._pending = self._pending, 0   # cleared first: the cache calls back into commit
+        if not pending:
             return
         for index in range(len(self.modules)):
             layer = self.cache._layers[index]
-            layer.tail_count += self._pending
-            layer.seq_length += self._pending
+            layer.tail_count += pending
+            layer.seq_length += pending
+        for index in range(len(self.modules)):
             self.cache.record_peak(index)
         self.cache._seen_tokens = self.cache._layers[0].seq_length
-        self._pending = 0
 
     def close(self) -> None:
         """Commit and hand the model back to the ordinary patched forward."""

@@ -30,23 +30,8 @@ from types import MethodType
 from typing import Any
 
 import torch
-import torch.nn.functional as F
 
-from .cache import InQuantCache, PackedAttentionView
-
-
-def _reference_decode(query: torch.Tensor, view: PackedAttentionView, scale: float) -> torch.Tensor:
-    """Materialising comparison path (reference ``qwen_fused.py:21-30``): concatenates the sink,
-    every dequantised block and the tail, then calls SDPA.  For tests and debugging only; the
-    fused forward never calls it."""
-    def restore(sink, blocks, tail):
-        pieces = [] if sink is None else [sink]
-        pieces.extend(block.dequantize(dtype=query.dtype) for block in blocks)
-        pieces.append(tail)
-        return torch.cat(pieces, dim=2)
-    key = restore(view.sink_key, view.key_blocks, view.residual_key)
-    value = restore(view.sink_value, view.value_blocks, view.residual_value)
-    return F.scaled_dot_product_attention(query, key, value, scale=scale, enable_gqa=True)
+from .cache import InQuantCache
 
 
 @dataclass
@@ -204,6 +189,15 @@ def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False,
         cos, sin = position_embeddings
         query, key = apply_rotary_pos_emb(query, key, cos, sin)
         graph_batch = attention._inquant_graph_batch
+        owner = getattr(attention, "_inquant_graph_owner", None)
+        if graph_batch is not None and not (owner is not None and owner._driving):
+            # a forward that does not come from the graphed stepper: book its replayed tokens into
+            # the cache, drop the graph and decode through the ordinary path
+            if owner is not None:
+                owner.close()
+            else:
+                attention._inquant_graph_batch = None
+            graph_batch = None
         if graph_batch is not None:
             # graph-safe step (inquant.graph_decode): the tail length lives in a device counter and
             # the cache's host bookkeeping is applied afterwards, so nothing here depends on the step
@@ -248,6 +242,7 @@ def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False,
         module._inquant_cpu_reference_calls = 0
         module._inquant_fused_prefill_calls = 0
         module._inquant_graph_batch = None
+        module._inquant_graph_owner = None
         module.forward = MethodType(forward, module)
     return FusedQwen2Handle(originals)
 

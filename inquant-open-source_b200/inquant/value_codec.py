@@ -110,10 +110,10 @@ class ArenaPackedValues(PackedValues):
         return sum(_logical_bytes(t) // t.shape[0] for t in arena.tensors.values())
 
 
-def encode_values_into(x, bits, group_size, payload, scales, offsets, page_ids=None):
+def encode_values_into(x, bits, group_size, payload, scales, offsets, page_ids=None, num_slots: int = 0):
     """Launch the value encoder on ``x`` = [outer, inner, tokens, channels]; no synchronisation."""
     args = N.VEncodeArgs()
-    args.input = N.make_input(x, page_ids)
+    args.input = N.make_input(x, page_ids, num_slots)
     args.bits, args.group = bits, group_size
     args.payload, args.scales, args.offsets = payload, scales, offsets
     rc = N.library().inq_v_encode(N.ctypes.byref(args), N.pointer(N.status_word(x.device)),

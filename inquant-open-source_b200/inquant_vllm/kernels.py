@@ -16,6 +16,7 @@ def fill_paged_sequence(seq, query, output, cache, blocks, dense, num_pages, tai
     plane = dense.stride(0)
     seq.query, seq.output, seq.query_head_stride = query.data_ptr(), output.data_ptr(), 128
     seq.pool, seq.page_table, seq.n_blocks = cache.data_ptr(), blocks.data_ptr(), num_pages
+    seq.pool_pages = cache.shape[0]   # page ids are checked on the device against the pool size
     seq.sink_key, seq.sink_value = dense.data_ptr(), dense.data_ptr() + plane * es
     seq.tail_key = dense.data_ptr() + 4 * dense.stride(2) * es
     seq.tail_value = seq.tail_key + plane * es

@@ -83,11 +83,16 @@ def _seal(keys, values, layout, pool, page_ids):
     if values.stride(-1) != 1:
         values = values.contiguous()
     config = CodecConfig(donor_policy="min_error")
+    slots = 0 if page_ids is None else pool.shape[0]   # ids are checked on the device against the pool size
     encode_into(keys, config, layout.field(pool, "key_payload"), layout.field(pool, "key_scales"), None, None,
-                layout.field(pool, "key_padding"), roles=(layout.field(pool, "key_map"), 2), page_ids=page_ids)
+                layout.field(pool, "key_padding"), roles=(layout.field(pool, "key_map"), 2), page_ids=page_ids,
+                num_slots=slots)
     encode_values_into(values, 2, 64, layout.field(pool, "value_payload"), layout.field(pool, "value_scales"),
-                       layout.field(pool, "value_offsets"), page_ids=page_ids)
-    if N.take_status(keys.device) & N.STATUS_NONFINITE:
+                       layout.field(pool, "value_offsets"), page_ids=page_ids, num_slots=slots)
+    status = N.take_status(keys.device, N.STATUS_NONFINITE | N.STATUS_BAD_INDEX)
+    if status & N.STATUS_BAD_INDEX:
+        raise IndexError("a physical page id lies outside the page pool; that page was not written")
+    if status & N.STATUS_NONFINITE:
         raise ValueError("K/V pages must contain finite values with finite FP16 value parameters")
 
 

@@ -46,6 +46,33 @@ def test_struct_mirrors_have_the_sizes_the_header_implies():
     assert ctypes.sizeof(N.ExchangeRank) == 48 and ctypes.sizeof(N.ExchangeArgs) == 32
 
 
+def test_struct_mirrors_match_the_header_as_a_c_compiler_lays_it_out(tmp_path):
+    """sizeof and the offsets of the bounds fields (pool_pages, num_slots), taken from the header
+    by gcc, equal those of the ctypes mirrors."""
+    import subprocess
+    from inquant import _native as N
+    structs = [("inq_field_t", N.Field), ("inq_input_t", N.Input), ("inq_k4_encode_args_t", N.K4EncodeArgs),
+               ("inq_v_encode_args_t", N.VEncodeArgs), ("inq_decode_seq_t", N.DecodeSeq),
+               ("inq_decode_args_t", N.DecodeArgs), ("inq_append_args_t", N.AppendArgs),
+               ("inq_decode_generic_args_t", N.GenericDecodeArgs), ("inq_prefill_args_t", N.PrefillArgs),
+               ("inq_exchange_rank_t", N.ExchangeRank), ("inq_exchange_args_t", N.ExchangeArgs)]
+    offsets = [("inq_input_t", "num_slots", N.Input.num_slots.offset),
+               ("inq_decode_seq_t", "pool_pages", N.DecodeSeq.pool_pages.offset),
+               ("inq_decode_seq_t", "tail_tokens_device", N.DecodeSeq.tail_tokens_device.offset),
+               ("inq_decode_seq_t", "partial_output", N.DecodeSeq.partial_output.offset)]
+    lines = ["#include <stdio.h>", "#include <stddef.h>", f'#include "{HEADER}"', "int main(void) {"]
+    lines += [f'  printf("%zu\\n", sizeof({name}));' for name, _ in structs]
+    lines += [f'  printf("%zu\\n", offsetof({name}, {field}));' for name, field, _ in offsets]
+    lines += ["  return 0;", "}"]
+    source = tmp_path / "sizes.c"
+    source.write_text("\n".join(lines))
+    binary = tmp_path / "sizes"
+    subprocess.run(["gcc", "-std=c11", str(source), "-o", str(binary)], check=True)
+    got = [int(x) for x in subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout.split()]
+    want = [ctypes.sizeof(mirror) for _, mirror in structs] + [offset for _, _, offset in offsets]
+    assert got == want
+
+
 def test_exchange_entry_points_check_their_arguments_without_a_gpu():
     from inquant import _native as N
     lib = N.library()

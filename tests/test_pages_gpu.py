@@ -143,3 +143,37 @@ def test_paged_decode_argument_validation():
                      SharedDecodeWorkspace(), 0.1)
     with pytest.raises(ValueError):
         PageLayout(48, 4)
+
+
+def test_out_of_range_page_ids_are_skipped_and_reported():
+    """A physical page id beyond the pool is never used as an address: the encoders leave that
+    page unwritten (every other page is sealed, the pool's remaining pages keep their fill byte)
+    and the call reports it; the decode kernel reads its first page instead and sets the status bit."""
+    from inquant import _native as N
+    from inquant.triton_attention import SharedDecodeWorkspace
+    from inquant_vllm.kernels import paged_decode
+    from inquant_vllm.layout import PageLayout, pack_pages, pack_pages_into
+    block, heads = 64, 4
+    layout = PageLayout(block, heads)
+    kt, vt = _pages_input(41, heads, 3, block)
+    k, v = to_device(kt), to_device(vt)
+    reference = pack_pages(k, v, layout)
+    for bad in (7, -1, 1 << 20):
+        pool = torch.full((7, layout.page_bytes), 173, device="cuda", dtype=torch.uint8)
+        ids = torch.tensor([5, bad, 3], device="cuda", dtype=torch.int64)
+        with pytest.raises(IndexError, match="outside the page pool"):
+            pack_pages_into(k, v, layout, pool, ids)
+        assert torch.equal(pool[5], reference[0]) and torch.equal(pool[3], reference[2])
+        assert (pool[torch.tensor([0, 1, 2, 4, 6], device="cuda")] == 173).all()
+    assert N.take_status(torch.device("cuda", 0)) == 0
+    # decode: a table entry beyond the pool
+    pool = torch.zeros((4, layout.page_bytes), device="cuda", dtype=torch.uint8)
+    pool[:3] = reference
+    dense = torch.zeros((2, heads, block + 4, 128), dtype=torch.bfloat16, device="cuda")
+    q = to_device(workloads.make_query(3, 28)).view(1, 28, 128)
+    table = torch.tensor([0, 9, 2], device="cuda", dtype=torch.int32)
+    out = paged_decode(q, pool, table, dense, 3, 1, 4, layout, SharedDecodeWorkspace(), 128 ** -0.5)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    assert N.take_status(torch.device("cuda", 0), N.STATUS_BAD_INDEX) == N.STATUS_BAD_INDEX
+    assert N.take_status(torch.device("cuda", 0)) == 0

@@ -48,7 +48,25 @@ def _noalloc_decode(N, state, query, sink_k, sink_v, tail_k, tail_v, scale):
     return output
 
 
-def test_noalloc_entry_point_matches_regular_entry_point_twice():
+def _oracle_view_output(view, q32):
+    """The oracle's attention over the blocks of a cache view (their device bytes), the exact sink
+    and the exact tail."""
+    def host(t):
+        return to_numpy(t.float() if t.dtype == torch.bfloat16 else t)
+    keys, values = [host(view.sink_key)[0]], [host(view.sink_value)[0]]
+    for kb, vb in zip(view.key_blocks, view.value_blocks):
+        pk = oracle.PackedK(host(kb.payload), host(kb.scales), host(kb.salient_channels), host(kb.donor_channels),
+                            host(kb.padding), tuple(kb.shape), "bfloat16")
+        pv = oracle.PackedV(host(vb.payload), scales=host(vb.scales), offsets=host(vb.offsets), shape=tuple(vb.shape),
+                            dtype="bfloat16", bits=2, group_size=64)
+        keys.append(oracle.dequantize_k4(pk)[0])
+        values.append(oracle.dequantize_values(pv)[0])
+    keys.append(host(view.residual_key)[0])
+    values.append(host(view.residual_value)[0])
+    return oracle.attention_decode(q32, np.concatenate(keys, 1), np.concatenate(values, 1), 128 ** -0.5)
+
+
+def test_noalloc_entry_point_matches_regular_entry_point_and_oracle_twice():
     from inquant import _native as N
     from inquant.cache import CacheConfig, InQuantCache
     from inquant.codec import CodecConfig
@@ -63,14 +81,62 @@ def test_noalloc_entry_point_matches_regular_entry_point_twice():
     state = PackedDecodeState(view.key_blocks, view.value_blocks)
     scale = 128 ** -0.5
     for call in range(2):   # two calls in a row share the fixed scratch
-        q = to_device(workloads.make_query(500 + call, q_heads)).view(1, q_heads, 1, 128)
+        q32 = workloads.make_query(500 + call, q_heads)
+        q = to_device(q32).view(1, q_heads, 1, 128)
         expected = state.decode(q, sink_key=view.sink_key, sink_value=view.sink_value,
                                 residual_key=view.residual_key, residual_value=view.residual_value, scale=scale)
         actual = _noalloc_decode(N, state, q, view.sink_key, view.sink_value, view.residual_key, view.residual_value, scale)
         torch.cuda.synchronize()
         attention_close(to_numpy(actual.float()).reshape(q_heads, 128), to_numpy(expected.float()).reshape(q_heads, 128))
         assert torch.equal(actual, expected)   # same kernel, same work split: identical bits
+        attention_close(to_numpy(actual.float()).reshape(q_heads, 128), _oracle_view_output(view, q32))
     assert N.take_status(q.device) == 0
+
+
+def test_noalloc_entry_point_serves_a_batch_close_to_its_pair_limit():
+    """63 sequences x 4 KV heads = 252 of the 256 pairs the fixed scratch holds, described by a
+    device array of sequence records, twice in a row; every output equals the ordinary entry
+    point's bit for bit and three of them are compared with the oracle."""
+    from inquant import _native as N
+    from inquant.batched import DecodeBatch, SequenceState
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    heads, q_heads, n_seq = 4, 28, 63
+    config = CacheConfig(CodecConfig(donor_policy="min_error"), block_size=64, residual_length=32, sink_tokens=4,
+                         value_bits=2, validate_positions=False)
+    caches, raw = [], []
+    for index in range(n_seq):
+        tokens = 140 + 37 * (index % 5)          # 1 to 3 sealed blocks
+        k, v = workloads.make_kv(900 + index, heads, tokens)
+        cache = InQuantCache(config)
+        cache.update(to_device(k), to_device(v), 0)
+        caches.append(cache)
+        raw.append((k, v))
+    batch = DecodeBatch([SequenceState.from_cache_layer(c, 0) for c in caches], q_heads, torch.bfloat16)
+    for call in range(2):
+        q32 = workloads.bf16_exact(np.random.default_rng(60 + call).standard_normal((n_seq, q_heads, 128), dtype=np.float32))
+        batch.queries.copy_(to_device(q32))
+        expected = batch.attend().clone()
+        args = N.DecodeArgs.from_buffer_copy(batch._decode_args)
+        args.partials, args.partials_floats, args.counters = None, 0, None   # the entry point must not need them
+        batch.outputs.zero_()
+        rc = N.library().inq_decode_attention_noalloc(ctypes.byref(args), N.stream_pointer(batch.device))
+        assert rc == N.OK, rc
+        torch.cuda.synchronize()
+        assert torch.equal(batch.outputs, expected)
+        for index in (0, 31, 62):
+            k, v = raw[index]
+            take, blocks, tail = oracle.seal_plan(0, 0, k.shape[2], sink_tokens=4, residual_length=32, block_size=64)
+            pieces_k, pieces_v = [k[0, :, :take]], [v[0, :, :take]]
+            for b in range(blocks):
+                sl = slice(take + b * 64, take + (b + 1) * 64)
+                pieces_k.append(oracle.dequantize_k4(oracle.quantize_k4(k[:, :, sl], donor_policy="min_error"))[0])
+                pieces_v.append(oracle.dequantize_values(oracle.quantize_values(v[:, :, sl]))[0])
+            pieces_k.append(k[0, :, take + blocks * 64:])
+            pieces_v.append(v[0, :, take + blocks * 64:])
+            want = oracle.attention_decode(q32[index], np.concatenate(pieces_k, 1), np.concatenate(pieces_v, 1), 128 ** -0.5)
+            attention_close(to_numpy(batch.outputs[index].float()), want)
+    assert N.take_status(batch.device) == 0
 
 
 def test_noalloc_entry_point_rejects_sizes_beyond_its_fixed_scratch():
