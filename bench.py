@@ -390,6 +390,132 @@ def encoder_kernels_us(torch, k, v):
     return e0.elapsed_time(e1) / 10 * 1e3
 
 
+def reference_gpu_leg(torch, device):
+    """One layer of config 1 through the UNMODIFIED reference on this GPU (installed under
+    oracle/_ref): its torch CUDA encoders against this library's encoders byte by byte, and its
+    Triton decode kernels (`PackedDecodeState.decode`: partials + reduce) timed in alternation with
+    this library's single-layer decode on the same packed layer, warm and with L2 flushed."""
+    import importlib
+    import workloads
+    ref = _reference_modules()
+    if ref is None:
+        return {"unavailable": "oracle/_ref is missing (the reference checkout was absent when the library was built)"}
+    try:
+        rta = importlib.import_module("inquant_reference.triton_attention")
+    except Exception as exc:
+        return {"unavailable": f"the reference's Triton module did not import: {exc}"}
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.triton_attention import PackedDecodeState
+    k, v = workloads.make_kv_torch(424242, KV_HEADS, CONTEXT, device)
+    rcodec, rcache = ref["codec"], ref["cache"]
+    theirs = rcache.InQuantCache(rcache.CacheConfig(rcodec.CodecConfig(donor_policy="min_error", donor_backend="torch"),
+                                                    block_size=BLOCK, residual_length=RESIDUAL, sink_tokens=SINK, value_bits=2,
+                                                    value_group_size=64, validate_positions=False))
+    ours = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=BLOCK, residual_length=RESIDUAL,
+                                    sink_tokens=SINK, value_bits=2, value_group_size=64, validate_positions=False))
+    theirs.update(k, v, 0)
+    ours.update(k, v, 0)
+    a, b = theirs._layers[0], ours._layers[0]
+    mismatch, total = {}, 0
+    for kind, fields in (("key", ("payload", "scales", "salient_channels", "donor_channels", "padding")),
+                         ("value", ("payload", "scales", "offsets"))):
+        for name in fields:
+            x = torch.cat([getattr(blk, name) for blk in getattr(a, kind + "_blocks")], 0).contiguous().view(torch.uint8)
+            y = torch.cat([getattr(blk, name) for blk in getattr(b, kind + "_blocks")], 0).contiguous().view(torch.uint8)
+            count = int((x != y).sum().item()) if x.shape == y.shape else -1
+            mismatch[f"{kind}_{name}"] = count
+            total += max(count, 0)
+    gen = torch.Generator(device=device).manual_seed(11)
+    new_k = torch.randn((1, KV_HEADS, 1, DIM), device=device, generator=gen).bfloat16()
+    new_v = torch.randn((1, KV_HEADS, 1, DIM), device=device, generator=gen).bfloat16()
+    q = torch.randn((1, Q_HEADS, 1, DIM), device=device, generator=gen).bfloat16()
+    view_a = theirs.append_for_attention(new_k, new_v, 0)
+    view_b = ours.append_for_attention(new_k, new_v, 0)
+    state_a = rta.PackedDecodeState(list(view_a.key_blocks), list(view_a.value_blocks))
+    state_b = PackedDecodeState(view_b.key_blocks, view_b.value_blocks)
+    dense_a = dict(sink_key=view_a.sink_key, sink_value=view_a.sink_value, residual_key=view_a.residual_key, residual_value=view_a.residual_value)
+    dense_b = dict(sink_key=view_b.sink_key, sink_value=view_b.sink_value, residual_key=view_b.residual_key, residual_value=view_b.residual_value)
+    out_a = state_a.decode(q, **dense_a)
+    out_b = state_b.decode(q, **dense_b)
+    torch.cuda.synchronize()
+    diff = float((out_a.float() - out_b.float()).abs().max().item())
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    result = {}
+    for label, do_flush in (("warm", False), ("l2_flushed", True)):
+        times_a, times_b = [], []
+        for _ in range(30):   # alternate the two kernels so both see the same clocks
+            for state, dense, bucket in ((state_a, dense_a, times_a), (state_b, dense_b, times_b)):
+                if do_flush:
+                    flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                state.decode(q, **dense)
+                e1.record()
+                torch.cuda.synchronize()
+                bucket.append(e0.elapsed_time(e1) * 1e3)
+        result[label] = {"reference_triton_us": round(sorted(times_a)[len(times_a) // 2], 2),
+                         "this_library_us": round(sorted(times_b)[len(times_b) // 2], 2)}
+    blocks, tail = len(view_b.key_blocks), view_b.residual_key.shape[2]
+    return {"workload": "config 1, ONE layer (32768 tokens, 4 KV heads, 28 query heads), single-layer launches timed in alternation",
+            "reference": "unmodified reference from oracle/_ref: torch CUDA encoders (donor_backend=torch), Triton partials + reduce kernels",
+            "encoder_bytes_differing_from_reference_cuda": mismatch, "encoder_bytes_differing_total": total,
+            "decode_max_abs_diff_vs_reference_triton": round(diff, 5), "layer_bytes": layer_bytes(blocks, tail), **result}
+
+
+def append_sequence_leg(torch, device, cache, steps=136):
+    """Config 1's incremental appends on ONE cache through the public per-layer API: every step
+    appends one token to all 28 layers (`append_for_attention`) and attends (`PackedDecodeState.decode`).
+    From a 32768-token prefill the tail holds 252 tokens, so 131 appends fit the tail and append 132
+    seals a block in every layer (reference `cache.py:271-306`); the run crosses that seal and ends
+    with a comparison of one layer's output, new block included, with the oracle."""
+    import numpy as np
+    from inquant.triton_attention import PackedDecodeState, SharedDecodeWorkspace
+    oracle = _oracle()
+    layers = sorted(cache._layers)
+    pool = SharedDecodeWorkspace()
+    states = [PackedDecodeState(cache._layers[i].key_blocks, cache._layers[i].value_blocks, workspace_pool=pool) for i in layers]
+    blocks_before = len(states[0].key_blocks)
+    gen = torch.Generator(device=device).manual_seed(2718)
+    feed = torch.randn((steps, len(layers), Q_HEADS + 2 * KV_HEADS, DIM), device=device, generator=gen).bfloat16()
+    times, seal_steps = [], []
+    out = view = None
+    for step in range(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for slot, index in enumerate(layers):
+            row = feed[step, slot]
+            q = row[:Q_HEADS].view(1, Q_HEADS, 1, DIM)
+            new_k = row[Q_HEADS:Q_HEADS + KV_HEADS].view(1, KV_HEADS, 1, DIM)
+            new_v = row[Q_HEADS + KV_HEADS:].view(1, KV_HEADS, 1, DIM)
+            view = cache.append_for_attention(new_k, new_v, index)
+            if len(view.key_blocks) != len(states[slot].key_blocks):
+                states[slot].extend(view.key_blocks, view.value_blocks)
+            out = states[slot].decode(q, sink_key=view.sink_key, sink_value=view.sink_value,
+                                      residual_key=view.residual_key, residual_value=view.residual_value)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+        if len(cache._layers[layers[0]].key_blocks) != blocks_before + len(seal_steps):
+            seal_steps.append(step + 1)
+    # the last layer's last output against the oracle (its view holds the block sealed on the way)
+    pk, pv = oracle_packed(oracle, list(view.key_blocks), list(view.value_blocks))
+    sink = (_host(view.sink_key)[0], _host(view.sink_value)[0])
+    tail = (_host(view.residual_key)[0], _host(view.residual_value)[0])
+    keys, vals = oracle_dense_history(oracle, pk, pv, sink, tail)
+    want = oracle.attention_decode(_host(feed[steps - 1, len(layers) - 1, :Q_HEADS]), keys, vals, DIM ** -0.5)
+    err, cos, finite = _closeness(_host(out).reshape(Q_HEADS, DIM), want)
+    if not finite or err >= PARITY_MAX_ABS or cos < PARITY_MIN_COS:
+        raise ParityError(f"config 1 append sequence, last step: max abs {err:.3e}, min cosine {cos:.6f}")
+    plain = [t for i, t in enumerate(times) if i + 1 not in seal_steps and i >= 3]
+    return {"what": "per-layer public API: append_for_attention + PackedDecodeState.decode for each of the layers, one token per step",
+            "steps": steps, "us_per_step_median_without_seal": round(float(np.median(plain)), 1),
+            "first_128_steps_ms": round(sum(times[:128]) / 1e3, 3),
+            "seal_at_append": seal_steps, "us_of_sealing_steps": [round(times[i - 1], 1) for i in seal_steps],
+            "blocks_per_layer_before_after": [blocks_before, len(cache._layers[layers[0]].key_blocks)],
+            "parity_last_step": {"max_abs": round(err, 6), "min_cos": round(cos, 7), "blocks": len(view.key_blocks)}}
+
+
 def sustained_leg(torch, batch, run_step, device_index, seconds):
     """The same step replayed back to back for `seconds` of device time: on this pool the SM clock
     settles well below its boost value under seconds of load, and a kernel that is bound by
@@ -587,6 +713,9 @@ def run_cuda(args):
         burst_mhz = line["clocks"]["sm_mhz"] or line["clocks"]["sm_max_mhz"]
         sustained["burst_us_times_mhz"] = round(ms_per_step * 1e3 * burst_mhz, 0) if burst_mhz else None
         line["sustained"] = sustained
+    if not args.no_append_sequence:
+        # DecodeBatch advanced the tails on the device only: the cache's own counters still describe the prefill
+        line["append_sequence"] = append_sequence_leg(torch, device, cache)
     if args.split_context:
         del batch, cache
         torch.cuda.empty_cache()
@@ -604,6 +733,12 @@ def run_cuda(args):
     if world == 1 and args.model_step:
         torch.cuda.empty_cache()
         line["model_step"] = run_model_step(args, torch, device)
+    if rank == 0 and world == 1 and not args.no_reference_gpu:
+        torch.cuda.empty_cache()
+        try:
+            line["reference_gpu"] = reference_gpu_leg(torch, device)
+        except Exception as exc:   # the reference's kernels are JIT-compiled on the spot: report, do not fail the run
+            line["reference_gpu"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sample_layers=1)
     if rank == 0:
@@ -910,11 +1045,13 @@ def run_split_kv(args, torch, dist, device, world, rank):
             "steps": steps, "parity": parity, **extra}
 
 
-# DRAM bytes (read + write) of one decode_kernel launch: 151.77 MB measured by ncu on the 10-layer
-# capture case (143.9 MB algorithmic), scaled to the layers of this run because traffic grows in
-# proportion to the units processed (profiles/decode_kernel_cfg1_10layers.md).
-DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 151.77 / 143.89
-DECODE_TRAFFIC_BYTES = None
+# DRAM bytes (read + write) of one decode_kernel launch per algorithmic byte, from one ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum) of a 10-layer case of the same kernel, scaled to the
+# layers of this run because traffic grows in proportion to the units processed.  The source string
+# names the capture; set the ratio to None when the kernel changes and no new capture exists.
+DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 150.32 / 143.89
+DECODE_TRAFFIC_SOURCE = ("ncu capture of the 10-layer case (145.96 MB read + 4.36 MB written against 143.89 MB algorithmic), "
+                         "decode kernel with two salient codes per gather accumulator, scaled by units")
 
 
 # --------------------------------------------------------------------------- CPU arm (oracle port)
@@ -1024,11 +1161,89 @@ def cpu_baseline(sample_layers=1, repeats=3):
     return base
 
 
+def _reference_modules():
+    """The unmodified reference packages installed under oracle/_ref by oracle/build_ref.py, imported
+    under another name (this repository's mirror is also called `inquant`); None when absent."""
+    import importlib
+    path = os.path.join(ROOT, "oracle")
+    if path not in sys.path:
+        sys.path.insert(0, path)
+    try:
+        import build_ref
+        if not build_ref.available():
+            return None
+        build_ref.load_reference()
+        names = ("codec", "value_codec", "cache", "qwen_fused")
+        return {name: importlib.import_module(f"inquant_reference.{name}") for name in names}
+    except Exception:
+        return None
+
+
+def run_reference_torch(args, ref, world):
+    """The reference's own torch CPU implementation of the path, unmodified, on all host cores:
+    `InQuantCache.update` seals one layer of config 1 (32768 tokens, 4 KV heads); a step is that
+    layer's decode as the reference's oracle does it -- `append_for_attention`, then
+    `_reference_decode` (dequantise every block, SDPA with grouped queries)."""
+    import torch
+    import workloads
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(cores)
+    codec, cache_mod, fused = ref["codec"], ref["cache"], ref["qwen_fused"]
+    k32, v32 = workloads.make_kv(0, KV_HEADS, CONTEXT, outliers=6, adjacent=3)
+    k, v = torch.from_numpy(k32).to(torch.bfloat16), torch.from_numpy(v32).to(torch.bfloat16)
+    config = cache_mod.CacheConfig(codec.CodecConfig(donor_policy="min_error"), block_size=BLOCK, residual_length=RESIDUAL,
+                                   sink_tokens=SINK, value_bits=2, value_group_size=64, validate_positions=False)
+    cache = cache_mod.InQuantCache(config)
+    t0 = time.perf_counter()
+    cache.update(k, v, 0)
+    encode_s = time.perf_counter() - t0
+    gen = torch.Generator().manual_seed(3)
+    q = torch.from_numpy(workloads.make_query(0, Q_HEADS)).to(torch.bfloat16).view(1, Q_HEADS, 1, DIM)
+    scale = DIM ** -0.5
+
+    def step():
+        new_k = torch.randn((1, KV_HEADS, 1, DIM), generator=gen).to(torch.bfloat16)
+        new_v = torch.randn((1, KV_HEADS, 1, DIM), generator=gen).to(torch.bfloat16)
+        view = cache.append_for_attention(new_k, new_v, 0)
+        return fused._reference_decode(q, view, scale), view
+
+    t0 = time.perf_counter()
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    once = (time.perf_counter() - t0) / max(1, min(args.warmup, 2))
+    # a bounded sample: about a minute of host time, and no block seal inside the timed steps
+    steps = max(1, min(args.steps, int(60.0 / max(once, 1e-3)), 100))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        _, view = step()
+    per = (time.perf_counter() - t0) / steps
+    blocks, tail = len(view.key_blocks), view.residual_key.shape[2]
+    nbytes = layer_bytes(blocks, tail)
+    value = round(nbytes / per / 1e9, 4)
+    sample = (f"each step = ONE of the 28 layers (32768 tokens, 4 KV heads) through the reference's own torch CPU path "
+              f"(append_for_attention + _reference_decode: dequantise {blocks} blocks, SDPA), {cores} torch threads, "
+              f"{steps} timed steps of {per * 1e3:.0f} ms; GB/s is per byte, so not scaled")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
+        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(per * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 dequantised K/V, torch CPU SDPA", "data": "synthetic",
+        "config": {"workload": "config 1 (one layer per step on the host cores)"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "reference", "sample": sample,
+                         "torch_threads": torch.get_num_threads(), "host_cpus": os.cpu_count()},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "encode_tokens_per_s": round(CONTEXT / (encode_s * LAYERS), 1),
+        "encode_ms_one_layer": round(encode_s * 1e3, 1),
+    }))
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
+    ref = None if args.reference_port else _reference_modules()
+    if ref is not None:
+        return run_reference_torch(args, ref, world)
     import workloads
     oracle, pk, pv, dense, blocks, encode_s = cpu_layer(0)
     q = workloads.make_query(0, Q_HEADS)
@@ -1082,6 +1297,12 @@ def main():
     parser.add_argument("--skip-e2e", action="store_true", help="profiler captures: skip the host-buffer leg")
     parser.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill leg (config 2, one layer)")
     parser.add_argument("--no-paged-batch", action="store_true", help="skip the batched paged decode leg (config 3)")
+    parser.add_argument("--reference-port", action="store_true",
+                        help="--impl reference: time the numpy port of the reference even when oracle/_ref holds the reference itself")
+    parser.add_argument("--no-append-sequence", action="store_true",
+                        help="skip the 136-step append sequence that crosses a block seal (config 1)")
+    parser.add_argument("--no-reference-gpu", action="store_true",
+                        help="skip the leg that runs the reference's Triton decode kernel beside this library's")
     parser.add_argument("--sustained-seconds", type=float, default=2.5,
                         help="length of the sustained-clock leg (0 = skip)")
     parser.add_argument("--model-step", action="store_true",

@@ -136,6 +136,28 @@ int inq_v_dequantize(const uint8_t* payload, const void* scales, const void* off
 int inq_build_roles(const void* salient, const void* donors, int32_t descriptor_i32, int64_t rows,
                     int32_t channels, int32_t count, void* roles, int32_t role_bytes, inq_stream_t stream);
 
+/* Scatter of already-encoded codec output (compact tensors [pages, kv_heads, ...] as inq_k4_encode /
+ * inq_v_encode write them, 16 salient channels, V2 in groups of 64) into the physical pages
+ * page_ids[p] of a pool in the serving layout (layout.py:18-42), building each page's int16 role
+ * map on the way; one launch.  page_offsets as in inq_decode_args_t.  Every pointer, page_bytes and
+ * every offset must be a multiple of 16.  A page id outside [0, num_slots) is not written and sets
+ * INQ_STATUS_BAD_INDEX (num_slots 0: ids are not checked).
+ * Replaces: inquant_vllm/packing.py:7-55 `_write_pages` / `write_codec_pages`. */
+typedef struct {
+  const uint8_t* key_payload; const float* key_scales; const uint8_t* salient; const uint8_t* donors;
+  const float* key_padding; const uint8_t* value_payload; const void* value_scales; const void* value_offsets;
+  int64_t pages;
+  int32_t heads, block_tokens, count;
+  uint8_t* pool;
+  int64_t page_bytes;
+  int64_t page_offsets[6];
+  const void* page_ids;
+  int32_t page_ids_i64;
+  int64_t num_slots;
+  int32_t* status;
+} inq_write_pages_args_t;
+int inq_write_codec_pages(const inq_write_pages_args_t* args /* host */, inq_stream_t stream);
+
 /* ---------------------------------------------------------------- decode attention
  * One decode step of single-query grouped-query attention over packed K4/V2 history plus
  * the exact sink and recent tail, for one sequence (a layer of a request) or a batch of

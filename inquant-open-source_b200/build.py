@@ -20,6 +20,7 @@ SOURCES = {
     "prefill.cu": [],
     "decode_generic.cu": [],
     "exchange.cu": [],
+    "pages.cu": [],
 }
 
 

@@ -608,7 +608,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
 
     int cur_block = (int)(pa / spb), cur_slice = (int)(pa % spb);
     bool need_weights = true;
-    float alpha[2] = {0.f, 0.f}, beta[2] = {0.f, 0.f};
+    float alpha[2] = {0.f, 0.f}, beta[2] = {0.f, 0.f}, bm[2] = {0.f, 0.f};   // bm = beta - m_run
     const unsigned vsel = (r & 1) ? 0x7632u : 0x5410u;
     // ldmatrix row address of this lane inside a stage's V area: lanes 0-7 / 8-15 name tokens 0-7 /
     // 8-15 of value group 0, lanes 16-31 the same tokens of group 1 (halves of tokens 4..7 swapped)
@@ -706,7 +706,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
             const int idx = sidx[i];
             wsrc[idx] = (unsigned char)(4 * lane + i);
             wdon[idx] = (unsigned char)role[i];
-            wssc[idx] = scv[i];
+            // in the units of the score accumulator (see the salient query entries below); the second
+            // code of a gather column carries a factor 1/512
+            wssc[idx] = scv[i] * (down * ((idx & 8) ? 0.125f : (1.f / 4096.f)));
           }
         }
         __syncwarp();
@@ -728,17 +730,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           wcell[v] = (unsigned short)cell;
         }
         __syncwarp();
-        // query at the salient channels, as B fragments of the salient step: the staged copy,
-        // scaled back by its power of two, converts to the model dtype exactly
+        // query at the salient channels, as B fragments of the salient step.  The step adds straight
+        // into the score accumulator, whose unit is alpha = qinv * 2^(24 + ex_f): the staged query
+        // times 2^-12 and the salient value times 2^-(12 + ex_f) give exactly that unit, and both
+        // factors are powers of two, so the rounding to the model dtype is the reference's
         {
-          const float back = qunscale[r];
           for (int gsel = 0; gsel < groups; ++gsel) {
             unsigned short qv[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               const int i = gsel * 16 + 2 * j + (k & 1) + (k >> 1) * 8;
               const int c = wsrc[min(i, 63)];
-              const QT qt = from_float<QT>(qs[(r * 4 + (c >> 5)) * kQChunk + (c & 31)] * back);
+              const QT qt = from_float<QT>(qs[(r * 4 + (c >> 5)) * kQChunk + (c & 31)] * (1.f / 4096.f));
               qv[k] = i < P.n_pad ? *(const unsigned short*)&qt : (unsigned short)0;
             }
             *(uint2*)(wqsal + (gsel * 32 + lane) * 8) = make_uint2((unsigned)qv[0] | ((unsigned)qv[1] << 16),
@@ -774,6 +777,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         alpha[1] = __shfl_sync(0xffffffffu, inv, (2 * j + 1) * 4);
         beta[0] = __shfl_sync(0xffffffffu, cpart, (2 * j) * 4);
         beta[1] = __shfl_sync(0xffffffffu, cpart, (2 * j + 1) * 4);
+        bm[0] = beta[0] - m_run[0];
+        bm[1] = beta[1] - m_run[1];
         need_weights = false;
         if (issue_late) {
           __syncwarp();   // every lane has read the per-channel terms: the staging area is free
@@ -786,7 +791,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       if (++stage_index == kStages) stage_index = 0;
       // ---- scores of two 16-token sub-slices (tokens 0..15 and 16..31 of the stage): K nibbles
       //      times the folded query, plus the exactly rebuilt salient channels
-      float S[2][4], S2[2][4];
+      float S[2][4];
       {
         // C[sub-slice][frag]: column n of the gather holds the codes of salient n and n + 8 of the
         // group as (code'_n - 128) + (code'_{n+8} - 128) / 512, in units of 2^-13
@@ -832,10 +837,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
 #undef INQ_KMMA
 #undef INQ_KSTEP
         if (SAL) {
-#pragma unroll
-          for (int u = 0; u < kSub; ++u)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) S2[u][k] = 0.f;
           for (int gsel = 0; gsel < groups; ++gsel) {
             if (gsel) {
               // further groups of 16 salient channels (salient fractions above 1/8)
@@ -866,9 +867,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
             // adding 1.5 * 2^23 rounds to the integer part (the fraction stays within 1/4), the rest
             // is the second code over 512.
             const float2 sc0 = *(const float2*)(wssc + gsel * 16 + 2 * j);
-            float2 sc1 = *(const float2*)(wssc + gsel * 16 + 8 + 2 * j);
-            sc1.x *= 512.f;
-            sc1.y *= 512.f;
+            const float2 sc1 = *(const float2*)(wssc + gsel * 16 + 8 + 2 * j);
             const uint2 qb = *(const uint2*)(wqsal + (gsel * 32 + lane) * 8);
 #pragma unroll
             for (int u = 0; u < kSub; ++u) {
@@ -882,7 +881,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
               const unsigned a1 = pack_qt2<QT>(hi[2] * sc0.x, hi[3] * sc0.y);
               const unsigned a2 = pack_qt2<QT>(lo[0] * sc1.x, lo[1] * sc1.y);
               const unsigned a3 = pack_qt2<QT>(lo[2] * sc1.x, lo[3] * sc1.y);
-              mma_qt<QT>(S2[u], a0, a1, a2, a3, qb.x, qb.y);
+              mma_qt<QT>(S[u], a0, a1, a2, a3, qb.x, qb.y);
             }
           }
         }
@@ -891,14 +890,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       float s2[2][4];
 #pragma unroll
       for (int u = 0; u < kSub; ++u) {
-        s2[u][0] = fmaf(S[u][0], alpha[0], beta[0]);
-        s2[u][1] = fmaf(S[u][1], alpha[1], beta[1]);
-        s2[u][2] = fmaf(S[u][2], alpha[0], beta[0]);
-        s2[u][3] = fmaf(S[u][3], alpha[1], beta[1]);
-        if (SAL) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k) s2[u][k] = fmaf(S2[u][k], P.scale_log2e, s2[u][k]);
-        }
+        // relative to the running reference maximum: bm = beta - m_run
+        s2[u][0] = fmaf(S[u][0], alpha[0], bm[0]);
+        s2[u][1] = fmaf(S[u][1], alpha[1], bm[1]);
+        s2[u][2] = fmaf(S[u][2], alpha[0], bm[0]);
+        s2[u][3] = fmaf(S[u][3], alpha[1], bm[1]);
       }
       {
         const int tok0 = cur_slice * kSliceTokens;
@@ -914,14 +910,31 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       }
       // ---- online softmax (base 2) over the 32 tokens.  The reference maximum is raised only when
       //      a score exceeds it by more than the slack, so the accumulators are rescaled rarely and
-      //      probabilities stay below 2^slack; the common case costs one vote
+      //      probabilities stay below 2^slack; the common case costs one vote and the scores arrive
+      //      already relative to the reference
       {
         float mx0 = fmaxf(s2[0][0], s2[0][2]), mx1 = fmaxf(s2[0][1], s2[0][3]);
         if (kSub > 1) {
           mx0 = fmaxf(mx0, fmaxf(s2[kSub - 1][0], s2[kSub - 1][2]));
           mx1 = fmaxf(mx1, fmaxf(s2[kSub - 1][1], s2[kSub - 1][3]));
         }
-        if (__any_sync(0xffffffffu, mx0 > m_run[0] + kRescaleSlack || mx1 > m_run[1] + kRescaleSlack)) {
+        if (__any_sync(0xffffffffu, mx0 > kRescaleSlack || mx1 > kRescaleSlack)) {
+          // rare: recompute the absolute scores (the first slice of a warp meets a reference of
+          // -1e30, against which the relative form has no precision left), raise the reference
+          float ab[2][4];
+#pragma unroll
+          for (int u = 0; u < kSub; ++u) {
+            ab[u][0] = s2[u][0] == -INFINITY ? -INFINITY : fmaf(S[u][0], alpha[0], beta[0]);
+            ab[u][1] = s2[u][1] == -INFINITY ? -INFINITY : fmaf(S[u][1], alpha[1], beta[1]);
+            ab[u][2] = s2[u][2] == -INFINITY ? -INFINITY : fmaf(S[u][2], alpha[0], beta[0]);
+            ab[u][3] = s2[u][3] == -INFINITY ? -INFINITY : fmaf(S[u][3], alpha[1], beta[1]);
+          }
+          mx0 = fmaxf(ab[0][0], ab[0][2]);
+          mx1 = fmaxf(ab[0][1], ab[0][3]);
+          if (kSub > 1) {
+            mx0 = fmaxf(mx0, fmaxf(ab[kSub - 1][0], ab[kSub - 1][2]));
+            mx1 = fmaxf(mx1, fmaxf(ab[kSub - 1][1], ab[kSub - 1][3]));
+          }
 #pragma unroll
           for (int off = 4; off < 32; off <<= 1) {
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
@@ -939,15 +952,22 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           }
           m_run[0] = mn0;
           m_run[1] = mn1;
+          bm[0] = beta[0] - mn0;
+          bm[1] = beta[1] - mn1;
+#pragma unroll
+          for (int u = 0; u < kSub; ++u) {
+            s2[u][0] = ab[u][0] - mn0; s2[u][1] = ab[u][1] - mn1;
+            s2[u][2] = ab[u][2] - mn0; s2[u][3] = ab[u][3] - mn1;
+          }
         }
       }
       float pr[2][4];
 #pragma unroll
       for (int u = 0; u < kSub; ++u) {
-        pr[u][0] = fast_exp2(s2[u][0] - m_run[0]);
-        pr[u][1] = fast_exp2(s2[u][1] - m_run[1]);
-        pr[u][2] = fast_exp2(s2[u][2] - m_run[0]);
-        pr[u][3] = fast_exp2(s2[u][3] - m_run[1]);
+        pr[u][0] = fast_exp2(s2[u][0]);
+        pr[u][1] = fast_exp2(s2[u][1]);
+        pr[u][2] = fast_exp2(s2[u][2]);
+        pr[u][3] = fast_exp2(s2[u][3]);
         l_run[0] += pr[u][0] + pr[u][2];
         l_run[1] += pr[u][1] + pr[u][3];
       }
@@ -1275,7 +1295,6 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   // blocks of at most 16 tokens (16-token pages) take the 16-token-slice kernel: one slice per
   // block either way, so the work list does not depend on the choice
   const int sub = a->block_tokens <= 16 ? 1 : 2;
-  const int shared = smem_bytes(groups, sub);
   typedef void (*kernel_t)(const DecodeParams);
   static const kernel_t kernels[16] = {
       decode_kernel<0, __half, false, 2>, decode_kernel<0, __half, true, 2>,
@@ -1288,6 +1307,8 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
       decode_kernel<1, __nv_bfloat16, false, 1>, decode_kernel<1, __nv_bfloat16, true, 1>};
   const int which = (sub == 1 ? 8 : 0) + a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);
   const kernel_t kernel = kernels[which];
+  const int shared = smem_bytes(groups, sub);
+  const int shared_limit = smem_bytes(4, sub);
   const int device = current_device();
   if (device < 0) return INQ_ERR_UNSUPPORTED;   // device ordinals above 63 are not tracked
   int resident = 0;
@@ -1295,7 +1316,7 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
     std::lock_guard<std::mutex> guard(g_devices_mutex);
     DeviceState& d = g_devices[device];
     if (!d.raised[which]) {
-      INQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(4, sub)));
+      INQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_limit));
       d.raised[which] = true;
     }
     if (!d.per_sm[which][groups]) {

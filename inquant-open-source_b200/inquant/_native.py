@@ -66,6 +66,14 @@ class DecodeArgs(ctypes.Structure):
                 ("partials", c_void_p), ("partials_floats", c_int64), ("counters", c_void_p), ("status", c_void_p)]
 
 
+class WritePagesArgs(ctypes.Structure):
+    _fields_ = [("key_payload", c_void_p), ("key_scales", c_void_p), ("salient", c_void_p), ("donors", c_void_p),
+                ("key_padding", c_void_p), ("value_payload", c_void_p), ("value_scales", c_void_p), ("value_offsets", c_void_p),
+                ("pages", c_int64), ("heads", c_int32), ("block_tokens", c_int32), ("count", c_int32),
+                ("pool", c_void_p), ("page_bytes", c_int64), ("page_offsets", c_int64 * 6),
+                ("page_ids", c_void_p), ("page_ids_i64", c_int32), ("num_slots", c_int64), ("status", c_void_p)]
+
+
 class AppendArgs(ctypes.Structure):
     _fields_ = [("key", c_void_p), ("value", c_void_p), ("src_stride_h", c_int64),
                 ("tail_key", c_void_p), ("tail_value", c_void_p), ("tail_stride_h", c_int64), ("tail_stride_t", c_int64),
@@ -145,7 +153,7 @@ def library() -> ctypes.CDLL:
 # Every symbol declared in include/inquant_b200.h.
 EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
-    "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles",
+    "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles", "inq_write_codec_pages",
     "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
     "inq_prefill_attention", "inq_decode_generic", "inq_decode_generic_workspace_floats",
     "inq_prefill_workspace_bytes",
@@ -164,6 +172,7 @@ SIGNATURES = {
     "inq_v_dequantize": [_P, _P, _P, _L, _I, _I, _I, _I, _P, _I, _P],
     "inq_build_roles": [_P, _P, _I, _L, _I, _I, _P, _I, _P],
     "inq_decode_attention": [_P, _P],
+    "inq_write_codec_pages": [_P, _P],
     "inq_decode_attention_noalloc": [_P, _P],
     "inq_merge_partials": [_P, _I, _L, _P, _I, _P],
     "inq_prefill_attention": [_P, _P],

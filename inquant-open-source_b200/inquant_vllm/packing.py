@@ -1,4 +1,5 @@
-"""Write already-encoded codec output into physical pages (reference ``inquant_vllm/packing.py``).
+"""Write already-encoded codec output into physical pages (reference ``inquant_vllm/packing.py``):
+one launch of ``inq_write_codec_pages`` scatters every field and builds the pages' role maps.
 The fused path (``pack_pages_into``) never materialises codec tensors; this function exists
 for callers that hold ``PackedTensor`` / ``PackedValues`` objects."""
 import torch
@@ -14,15 +15,13 @@ def write_codec_pages(keys, values, layout, pool, page_ids):
         raise ValueError('One integer physical page ID is required per input page')
     if page_ids.device != pool.device or keys.payload.device != pool.device or values.payload.device != pool.device:
         raise ValueError('Codec tensors, page IDs and pool must share a CUDA device')
-    pages, heads = keys.shape[0], layout.heads
-    roles = torch.empty((pages, heads, 128), dtype=torch.int16, device=pool.device)
-    rc = N.library().inq_build_roles(N.pointer(keys.salient_channels.contiguous()), N.pointer(keys.donor_channels.contiguous()),
-                                     0, pages * heads, 128, keys.salient_channels.shape[-1], N.pointer(roles), 2,
-                                     N.stream_pointer(pool.device))
-    N.check(rc, "inq_build_roles")
-    fields = layout.views(pool)
-    index = page_ids.long()
-    for name, tensor in (("key_payload", keys.payload), ("key_scales", keys.scales), ("key_map", roles),
-                         ("key_padding", keys.padding), ("value_payload", values.payload),
-                         ("value_scales", values.scales), ("value_offsets", values.offsets)):
-        fields[name][index] = tensor.reshape(fields[name][index].shape)
+    if keys.salient_channels.shape[-1] != 16 or keys.salient_channels.dtype != torch.uint8:
+        raise ValueError('The page layout holds 16 salient channels per head')
+    from .kernels import page_offsets_array
+    tensors = [t.contiguous() for t in (keys.payload, keys.scales, keys.salient_channels, keys.donor_channels, keys.padding,
+                                        values.payload, values.scales, values.offsets)]
+    ids = page_ids.contiguous()
+    args = N.WritePagesArgs(*(t.data_ptr() for t in tensors), keys.shape[0], layout.heads, layout.block_size, 16,
+                            pool.data_ptr(), layout.page_bytes, page_offsets_array(layout), ids.data_ptr(),
+                            int(ids.dtype == torch.int64), pool.shape[0], N.status_word(pool.device).data_ptr())
+    N.check(N.library().inq_write_codec_pages(N.ctypes.byref(args), N.stream_pointer(pool.device)), "inq_write_codec_pages")
