@@ -113,6 +113,14 @@ int inq_k4_statistics(const inq_input_t* in /* host */, int32_t sample_stride, f
 int inq_k4_dequantize(const uint8_t* payload, const float* scales, const void* salient, const void* donors,
                       int32_t descriptor_i32, const float* padding, int64_t rows, int32_t tokens,
                       int32_t channels, int32_t count, void* out, int32_t out_dtype, inq_stream_t stream);
+/* The same with rows (outer, inner) written at out + outer * out_stride_outer + inner *
+ * out_stride_inner (elements; a row's tokens stay contiguous): the blocks of one encoder launch,
+ * [blocks, heads, T, C], land directly in a [heads, tokens, C] history at their token positions.
+ * Replaces: the per-block dequantize + torch.cat of cache.py:328-345 `materialize`. */
+int inq_k4_dequantize_strided(const uint8_t* payload, const float* scales, const void* salient, const void* donors,
+                              int32_t descriptor_i32, const float* padding, int64_t rows_outer, int32_t rows_inner,
+                              int32_t tokens, int32_t channels, int32_t count, void* out, int64_t out_stride_outer,
+                              int64_t out_stride_inner, int32_t out_dtype, inq_stream_t stream);
 
 /* ---------------------------------------------------------------- V encoder
  * Per-token, per-group affine INT2/INT4 with fp16 scale and minimum.
@@ -130,6 +138,10 @@ int inq_v_encode(const inq_v_encode_args_t* args /* host */, int32_t* status, in
 int inq_v_dequantize(const uint8_t* payload, const void* scales, const void* offsets, int64_t rows,
                      int32_t tokens, int32_t channels, int32_t bits, int32_t group, void* out,
                      int32_t out_dtype, inq_stream_t stream);
+/* Strided destination as in inq_k4_dequantize_strided. */
+int inq_v_dequantize_strided(const uint8_t* payload, const void* scales, const void* offsets, int64_t rows_outer,
+                             int32_t rows_inner, int32_t tokens, int32_t channels, int32_t bits, int32_t group, void* out,
+                             int64_t out_stride_outer, int64_t out_stride_inner, int32_t out_dtype, inq_stream_t stream);
 
 /* Role maps from descriptor lists.  Replaces: triton_attention.py:301-309 `_write_maps`
  * and the map construction inside packing.py:24-29.  lists [rows,count] u8 or i32. */
@@ -199,6 +211,17 @@ typedef struct {
                            * un-normalised record (acc[128], m in base-2 units, l) of each query
                            * head is stored instead -- the reference's partial format
                            * (triton_attention.py:162-165) -- for a cross-GPU merge */
+  /* The step's new token, used only by launches with `fused_append` set (else ignored): rows
+   * [kv_heads][128] of the query dtype, 16-byte aligned, `new_stride_h` elements apart.  The launch
+   * attends to the token as position tail_tokens of the tail (tail_tokens counts the tokens BEFORE
+   * it), stores it at that position of tail_key / tail_value (position >= tail_capacity: not
+   * stored, INQ_STATUS_BAD_INDEX) and, once every CTA has read the length, adds one to
+   * *tail_tokens_device.  Replaces the separate inq_append_token_batch launch of a decode step
+   * (cache.py:256-259, 271-299; backend.py:158-163). */
+  const void* new_key; const void* new_value;
+  int64_t new_stride_h;
+  int32_t tail_capacity;
+  int32_t reserved;
 } inq_decode_seq_t;
 
 typedef struct {
@@ -221,8 +244,9 @@ typedef struct {
   int32_t uniform_blocks;
   float* partials;          /* scratch, contents undefined on entry and exit */
   int64_t partials_floats;  /* its size: at least inq_decode_workspace_floats(n_pairs, total_units) */
-  int32_t* counters;        /* scratch: n_pairs ints, ZERO on entry, left zero on exit */
+  int32_t* counters;        /* scratch: n_pairs + 1 ints, ZERO on entry, left zero on exit */
   int32_t* status;          /* device status word */
+  int32_t fused_append;     /* 1: every sequence's new_key / new_value token is appended by this launch */
 } inq_decode_args_t;
 int inq_decode_attention(const inq_decode_args_t* args /* host */, inq_stream_t stream);
 /* The same decode step for callers that cannot allocate device memory (a serving engine that

@@ -944,7 +944,7 @@ __global__ void __launch_bounds__(1024) select_kernel(const float* saliency, con
 template <typename T>
 __global__ void k4_dequantize_kernel(const unsigned char* payload, const float* scales, const void* salient,
                                      const void* donors, int descriptor_i32, const float* padding, int tokens,
-                                     int channels, int count, T* out) {
+                                     int channels, int count, T* out, int rows_inner, long long out_so, long long out_si) {
   extern __shared__ __align__(16) unsigned char raw[];
   int* role = (int*)raw;  // >=0 partner slot of a salient channel, -1 normal, <=-2 donor
   float* scale = (float*)(role + channels);
@@ -965,7 +965,8 @@ __global__ void k4_dequantize_kernel(const unsigned char* payload, const float* 
   }
   __syncthreads();
   const unsigned char* bytes = payload + row * (long long)tokens * (channels / 2);
-  T* dst = out + row * (long long)tokens * channels;
+  // row (outer, inner) lands at out + outer * out_so + inner * out_si (elements); its tokens are contiguous
+  T* dst = out + (row / rows_inner) * out_so + (row % rows_inner) * out_si;
   const int t_begin = blockIdx.y * 16, t_end = min(tokens, t_begin + 16);
   for (int idx = t_begin * channels + threadIdx.x; idx < t_end * channels; idx += blockDim.x) {
     int t = idx / channels, c = idx % channels;
@@ -1147,7 +1148,8 @@ __global__ void __launch_bounds__(256) v_encode128_kernel(VParams p) {
 
 template <typename T>
 __global__ void v_dequantize_kernel(const unsigned char* payload, const __half* scales, const __half* offsets,
-                                    long long total, int channels, int bits, int group, T* out) {
+                                    long long total, int channels, int bits, int group, T* out, int tokens, int rows_inner,
+                                    long long out_so, long long out_si) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   long long token = idx / channels;
@@ -1158,7 +1160,9 @@ __global__ void v_dequantize_kernel(const unsigned char* payload, const __half* 
   long long param = token * (channels / group) + c / group;
   float value = code * __half2float(scales[param]);
   value = value + __half2float(offsets[param]);
-  out[idx] = from_float<T>(value);
+  // row (outer, inner) lands at out + outer * out_so + inner * out_si (elements); its tokens are contiguous
+  const long long row = token / tokens;
+  out[(row / rows_inner) * out_so + (row % rows_inner) * out_si + (token % tokens) * channels + c] = from_float<T>(value);
 }
 
 __global__ void build_roles_kernel(const void* salient, const void* donors, int descriptor_i32, int channels, int count,
@@ -1301,11 +1305,13 @@ extern "C" int inq_select_donors(const float* saliency, const float* donor_error
   return INQ_OK;
 }
 
-extern "C" int inq_k4_dequantize(const uint8_t* payload, const float* scales, const void* salient, const void* donors,
-                                 int32_t descriptor_i32, const float* padding, int64_t rows, int32_t tokens,
-                                 int32_t channels, int32_t count, void* out, int32_t out_dtype, inq_stream_t stream_) {
-  if (!payload || !scales || !out || rows < 1 || tokens < 1 || channels < 2 || channels % 2 || count < 0 ||
-      !valid_dtype(out_dtype) || rows >= (1ll << 31))
+extern "C" int inq_k4_dequantize_strided(const uint8_t* payload, const float* scales, const void* salient, const void* donors,
+                                         int32_t descriptor_i32, const float* padding, int64_t rows_outer, int32_t rows_inner,
+                                         int32_t tokens, int32_t channels, int32_t count, void* out, int64_t out_stride_outer,
+                                         int64_t out_stride_inner, int32_t out_dtype, inq_stream_t stream_) {
+  const long long rows = rows_outer * (long long)rows_inner;
+  if (!payload || !scales || !out || rows_outer < 1 || rows_inner < 1 || tokens < 1 || channels < 2 || channels % 2 || count < 0 ||
+      !valid_dtype(out_dtype) || rows >= (1ll << 31) || out_stride_outer < 0 || out_stride_inner < 0)
     return INQ_ERR_ARGUMENT;
   if (count && (!salient || !donors || !padding)) return INQ_ERR_ARGUMENT;
   if (channels > 4096) return INQ_ERR_UNSUPPORTED;
@@ -1314,17 +1320,24 @@ extern "C" int inq_k4_dequantize(const uint8_t* payload, const float* scales, co
   cudaStream_t stream = (cudaStream_t)stream_;
   switch (out_dtype) {
     case INQ_F32:
-      k4_dequantize_kernel<float><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (float*)out);
+      k4_dequantize_kernel<float><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (float*)out, rows_inner, out_stride_outer, out_stride_inner);
       break;
     case INQ_F16:
-      k4_dequantize_kernel<__half><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (__half*)out);
+      k4_dequantize_kernel<__half><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (__half*)out, rows_inner, out_stride_outer, out_stride_inner);
       break;
     default:
-      k4_dequantize_kernel<__nv_bfloat16><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (__nv_bfloat16*)out);
+      k4_dequantize_kernel<__nv_bfloat16><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (__nv_bfloat16*)out, rows_inner, out_stride_outer, out_stride_inner);
       break;
   }
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
+}
+
+extern "C" int inq_k4_dequantize(const uint8_t* payload, const float* scales, const void* salient, const void* donors,
+                                 int32_t descriptor_i32, const float* padding, int64_t rows, int32_t tokens,
+                                 int32_t channels, int32_t count, void* out, int32_t out_dtype, inq_stream_t stream_) {
+  return inq_k4_dequantize_strided(payload, scales, salient, donors, descriptor_i32, padding, rows, 1, tokens, channels, count, out,
+                                   (int64_t)tokens * channels, 0, out_dtype, stream_);
 }
 
 template <typename T>
@@ -1392,28 +1405,36 @@ extern "C" int inq_v_encode(const inq_v_encode_args_t* a, int32_t* status, inq_s
   return INQ_OK;
 }
 
-extern "C" int inq_v_dequantize(const uint8_t* payload, const void* scales, const void* offsets, int64_t rows,
-                                int32_t tokens, int32_t channels, int32_t bits, int32_t group, void* out,
-                                int32_t out_dtype, inq_stream_t stream_) {
-  if (!payload || !scales || !offsets || !out || rows < 1 || tokens < 1 || (bits != 2 && bits != 4) ||
-      (group != 32 && group != 64 && group != 128) || channels % group || !valid_dtype(out_dtype))
+extern "C" int inq_v_dequantize_strided(const uint8_t* payload, const void* scales, const void* offsets, int64_t rows_outer,
+                                        int32_t rows_inner, int32_t tokens, int32_t channels, int32_t bits, int32_t group, void* out,
+                                        int64_t out_stride_outer, int64_t out_stride_inner, int32_t out_dtype, inq_stream_t stream_) {
+  if (!payload || !scales || !offsets || !out || rows_outer < 1 || rows_inner < 1 || tokens < 1 || (bits != 2 && bits != 4) ||
+      (group != 32 && group != 64 && group != 128) || channels % group || !valid_dtype(out_dtype) || out_stride_outer < 0 ||
+      out_stride_inner < 0)
     return INQ_ERR_ARGUMENT;
-  long long total = rows * (long long)tokens * channels;
+  long long total = rows_outer * (long long)rows_inner * tokens * channels;
   unsigned blocks = (unsigned)((total + 255) / 256);
   cudaStream_t stream = (cudaStream_t)stream_;
   switch (out_dtype) {
     case INQ_F32:
-      v_dequantize_kernel<float><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (float*)out);
+      v_dequantize_kernel<float><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (float*)out, tokens, rows_inner, out_stride_outer, out_stride_inner);
       break;
     case INQ_F16:
-      v_dequantize_kernel<__half><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (__half*)out);
+      v_dequantize_kernel<__half><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (__half*)out, tokens, rows_inner, out_stride_outer, out_stride_inner);
       break;
     default:
-      v_dequantize_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (__nv_bfloat16*)out);
+      v_dequantize_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (__nv_bfloat16*)out, tokens, rows_inner, out_stride_outer, out_stride_inner);
       break;
   }
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
+}
+
+extern "C" int inq_v_dequantize(const uint8_t* payload, const void* scales, const void* offsets, int64_t rows,
+                                int32_t tokens, int32_t channels, int32_t bits, int32_t group, void* out,
+                                int32_t out_dtype, inq_stream_t stream_) {
+  return inq_v_dequantize_strided(payload, scales, offsets, rows, 1, tokens, channels, bits, group, out,
+                                  (int64_t)tokens * channels, 0, out_dtype, stream_);
 }
 
 extern "C" int inq_build_roles(const void* salient, const void* donors, int32_t descriptor_i32, int64_t rows,

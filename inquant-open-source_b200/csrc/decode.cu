@@ -86,6 +86,9 @@ struct SeqDesc {
   int pool_pages;
   const int* tail_tokens_dev;
   float* partial_out;            // optional: un-normalised (acc[128], m, l) per query head instead of `out`
+  const void* new_k; const void* new_v;   // the step's new token (launches with fused_append)
+  long long new_sh;
+  int tail_capacity, reserved;
 };
 static_assert(sizeof(SeqDesc) == sizeof(inq_decode_seq_t), "SeqDesc must mirror inq_decode_seq_t");
 
@@ -103,6 +106,7 @@ struct DecodeParams {
   float* partials;
   int* counters;
   int* status;
+  int fused_append;
 };
 
 struct BlockPtrs {
@@ -438,7 +442,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   const int n_workers = n_cta_pair * kWarps, worker = ((int)blockIdx.x - first_cta) * kWarps + warp;
   const long long pa = min(n_packed, seg_lo + (seg_hi - seg_lo) * warp / kWarps);
   const long long pb = min(n_packed, seg_lo + (seg_hi - seg_lo) * (warp + 1) / kWarps);
-  const int n_dense = sink_slices + tail_slices;
+  // with a fused append the step's new token is one more dense slice: it is read from the caller's
+  // rows (tail_tokens counts the tokens before it) and stored behind the tail for the next steps
+  const bool has_new = P.fused_append && SEQ(new_k) != nullptr;
+  const int n_dense = sink_slices + tail_slices + (has_new ? 1 : 0);
 
   float m_run[2] = {kNegBig, kNegBig}, l_run[2] = {0.f, 0.f};
   float acc[8][4];
@@ -464,12 +471,26 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     }
     for (int ds = worker; ds < n_dense; ds += n_workers) {
       const bool is_sink = ds < sink_slices;
-      const int tok0 = (is_sink ? ds : ds - sink_slices) * 16;
-      const int count = is_sink ? sink_tokens : tail_tokens;
-      const int skip = is_sink ? 0 : SEQ(tail_skip);
-      const QT* kb = (const QT*)(is_sink ? SEQ(sink_k) : SEQ(tail_k)) + (long long)h * (is_sink ? SEQ(sink_k_sh) : SEQ(tail_k_sh));
-      const QT* vb = (const QT*)(is_sink ? SEQ(sink_v) : SEQ(tail_v)) + (long long)h * (is_sink ? SEQ(sink_v_sh) : SEQ(tail_v_sh));
-      const long long kst = is_sink ? SEQ(sink_k_st) : SEQ(tail_k_st), vst = is_sink ? SEQ(sink_v_st) : SEQ(tail_v_st);
+      const bool is_new = ds >= sink_slices + tail_slices;   // the step's new token: a slice of one row
+      const int tok0 = is_new ? 0 : (is_sink ? ds : ds - sink_slices) * 16;
+      const int count = is_new ? 1 : is_sink ? sink_tokens : tail_tokens;
+      const int skip = is_sink || is_new ? 0 : SEQ(tail_skip);
+      const QT* kb = is_new ? (const QT*)SEQ(new_k) + (long long)h * SEQ(new_sh)
+                            : (const QT*)(is_sink ? SEQ(sink_k) : SEQ(tail_k)) + (long long)h * (is_sink ? SEQ(sink_k_sh) : SEQ(tail_k_sh));
+      const QT* vb = is_new ? (const QT*)SEQ(new_v) + (long long)h * SEQ(new_sh)
+                            : (const QT*)(is_sink ? SEQ(sink_v) : SEQ(tail_v)) + (long long)h * (is_sink ? SEQ(sink_v_sh) : SEQ(tail_v_sh));
+      const long long kst = is_new ? 0 : is_sink ? SEQ(sink_k_st) : SEQ(tail_k_st), vst = is_new ? 0 : is_sink ? SEQ(sink_v_st) : SEQ(tail_v_st);
+      if (is_new && gt == 0) {
+        // one warp per (sequence, KV head) stores the token behind the tail; this launch reads it
+        // from the caller's rows only, so the store races with nothing
+        if (tail_tokens < SEQ(tail_capacity)) {
+          QT* dst = (QT*)(lane < 16 ? SEQ(tail_k) : SEQ(tail_v)) + (long long)h * (lane < 16 ? SEQ(tail_k_sh) : SEQ(tail_v_sh)) +
+                    (long long)tail_tokens * (lane < 16 ? SEQ(tail_k_st) : SEQ(tail_v_st));
+          *((uint4*)dst + (lane & 15)) = *((const uint4*)(lane < 16 ? kb : vb) + (lane & 15));
+        } else if (lane == 0) {
+          atomicOr(P.status, INQ_STATUS_BAD_INDEX);
+        }
+      }
       const int last = count - 1;
       float S[4] = {0.f, 0.f, 0.f, 0.f};
       // the value rows are requested together with the key rows: one exposed latency, not two
@@ -1177,6 +1198,25 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   }
   __syncthreads();   // shared scratch is reused by the next pair of this CTA
   }  // pairs of this CTA
+  if (P.fused_append) {
+    // Every CTA has read the tail lengths of the pairs it visited by the time it arrives here; the
+    // last one to arrive advances the device-side lengths for the next step.
+    __shared__ int s_grid_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const int old = atomicAdd(P.counters + P.n_pairs, 1);
+      s_grid_last = old == (int)gridDim.x - 1;
+      if (s_grid_last) P.counters[P.n_pairs] = 0;
+    }
+    __syncthreads();
+    if (s_grid_last) {
+      for (int s = threadIdx.x; s < P.n_seq; s += kThreads) {
+        const SeqDesc* d = P.seqs ? P.seqs + s : &P.one;
+        if (d->new_k && d->tail_tokens_dev) atomicAdd((int*)d->tail_tokens_dev, 1);
+      }
+    }
+  }
 }
 
 #undef SEQ
@@ -1354,6 +1394,7 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   P.partials = a->partials;
   P.counters = a->counters;
   P.status = a->status;
+  P.fused_append = a->fused_append ? 1 : 0;
   kernel<<<(unsigned)plan.n_ctas, kThreads, shared, (cudaStream_t)stream_>>>(P);
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
@@ -1372,7 +1413,7 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
 namespace inq {
 constexpr int kStaticRecords = 1024;   // (resident CTAs + pairs) of one launch must fit
 constexpr int kStaticPairs = 256;      // (sequence, KV head, head tile) pairs of one launch
-constexpr size_t kStaticCounterBytes = kStaticPairs * sizeof(int);
+constexpr size_t kStaticCounterBytes = 2 * kStaticPairs * sizeof(int);   // pair counters, the grid counter, padding
 constexpr size_t kStaticBytes = kStaticCounterBytes + (size_t)kStaticRecords * kRecordFloats * sizeof(float);
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticBytes];
 }  // namespace inq

@@ -54,7 +54,8 @@ class DecodeSeq(ctypes.Structure):
                 ("n_blocks", c_int32), ("sink_tokens", c_int32), ("tail_tokens", c_int32),
                 ("first_visible", c_int32), ("tail_skip", c_int32), ("pool_pages", c_int32),
                 ("tail_tokens_device", c_void_p),
-                ("partial_output", c_void_p)]
+                ("partial_output", c_void_p), ("new_key", c_void_p), ("new_value", c_void_p),
+                ("new_stride_h", c_int64), ("tail_capacity", c_int32), ("reserved", c_int32)]
 
 
 class DecodeArgs(ctypes.Structure):
@@ -63,7 +64,8 @@ class DecodeArgs(ctypes.Structure):
                 ("layout", c_int32), ("dtype", c_int32), ("scale", ctypes.c_float),
                 ("page_bytes", c_int64), ("page_offsets", c_int64 * 6),
                 ("pair_starts", c_void_p), ("total_units", c_int64), ("uniform_blocks", c_int32),
-                ("partials", c_void_p), ("partials_floats", c_int64), ("counters", c_void_p), ("status", c_void_p)]
+                ("partials", c_void_p), ("partials_floats", c_int64), ("counters", c_void_p), ("status", c_void_p),
+                ("fused_append", c_int32)]
 
 
 class WritePagesArgs(ctypes.Structure):
@@ -153,7 +155,8 @@ def library() -> ctypes.CDLL:
 # Every symbol declared in include/inquant_b200.h.
 EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
-    "inq_k4_dequantize", "inq_v_encode", "inq_v_dequantize", "inq_build_roles", "inq_write_codec_pages",
+    "inq_k4_dequantize", "inq_k4_dequantize_strided", "inq_v_encode", "inq_v_dequantize", "inq_v_dequantize_strided",
+    "inq_build_roles", "inq_write_codec_pages",
     "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
     "inq_prefill_attention", "inq_decode_generic", "inq_decode_generic_workspace_floats",
     "inq_prefill_workspace_bytes",
@@ -168,6 +171,8 @@ SIGNATURES = {
     "inq_select_donors": [_P, _P, _L, _I, _I, _P, _P, _P],
     "inq_k4_statistics": [_P, _I, _P, _P, _P, _P, _P],
     "inq_k4_dequantize": [_P, _P, _P, _P, _I, _P, _L, _I, _I, _I, _P, _I, _P],
+    "inq_k4_dequantize_strided": [_P, _P, _P, _P, _I, _P, _L, _I, _I, _I, _I, _P, _L, _L, _I, _P],
+    "inq_v_dequantize_strided": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _P, _L, _L, _I, _P],
     "inq_v_encode": [_P, _P, _P],
     "inq_v_dequantize": [_P, _P, _P, _L, _I, _I, _I, _I, _P, _I, _P],
     "inq_build_roles": [_P, _P, _I, _L, _I, _I, _P, _I, _P],
@@ -289,8 +294,8 @@ def decode_counters(device: torch.device, count: int) -> torch.Tensor:
     (device, stream); the kernel leaves them zero, so they are reused launch after launch."""
     key = (device, torch.cuda.current_stream(device).cuda_stream)
     tensor = _counters.get(key)
-    if tensor is None or tensor.numel() < count:
-        tensor = torch.zeros(max(count, 1024), dtype=torch.int32, device=device)
+    if tensor is None or tensor.numel() < count + 1:   # one more: the launch-wide arrival counter of a fused append
+        tensor = torch.zeros(max(count + 1, 1024), dtype=torch.int32, device=device)
         _counters[key] = tensor
     return tensor
 

@@ -5,8 +5,12 @@ layer.  A layer of a 32K-token request is only ~14 MB of packed cache, i.e. ~2 m
 of HBM time on a B200, so per-layer launches are latency-bound.  ``DecodeBatch`` keeps a
 device-resident array of sequence descriptors (C ABI ``inq_decode_seq_t``) and runs
 
-    step():  1 launch  inq_append_token_batch   (new K/V token of every sequence -> its tail)
-             1 launch  inq_decode_attention     (all sequences, fused split-KV merge)
+    step():  1 launch  inq_decode_attention with `fused_append`: the new K/V token of every sequence
+             is attended to from the staging rows, stored behind its tail, and the device-side tail
+             lengths advance when the launch ends (all sequences, fused split-KV merge)
+
+(`append()` and `attend()` remain as two separate launches, inq_append_token_batch and
+inq_decode_attention.)
 
 with tail lengths held in device counters, so a decode loop makes no host round trip and
 can be captured in a CUDA graph.  Sequences are independent: this is also the collective-
@@ -132,7 +136,7 @@ class DecodeBatch:
         self.total_units = int(starts[-1])
         self.pair_starts = starts.to(self.device)
         self.partials = torch.empty(workspace_floats(n_pairs, self.total_units), dtype=torch.float32, device=self.device)
-        self.counters = torch.zeros(n_pairs, dtype=torch.int32, device=self.device)
+        self.counters = torch.zeros(n_pairs + 1, dtype=torch.int32, device=self.device)   # + the launch-wide arrival counter
         self.launches = 0
         self._initial_counters = self.tail_counters.clone()
         self._prepare_launch_arguments()
@@ -168,6 +172,12 @@ class DecodeBatch:
         self._finish_descriptors(seqs, apps)
 
     def _finish_descriptors(self, seqs, apps) -> None:
+        es = self.queries.element_size()
+        for i, s in enumerate(self.sequences):
+            # the step's new token, read by launches with fused_append
+            seqs[i].new_key, seqs[i].new_value = self.new_keys[i].data_ptr(), self.new_values[i].data_ptr()
+            seqs[i].new_stride_h = self.new_keys.stride(1)
+            seqs[i].tail_capacity = self._tail_capacity_of(s)
         if self.partial_records is not None:
             for i in range(len(self.sequences)):
                 seqs[i].partial_output = self.partial_records[i].data_ptr()
@@ -243,6 +253,9 @@ class DecodeBatch:
         args.status = N.status_word(self.device).data_ptr()
         self._decode_args = args
         self._decode_args_ref = ctypes.byref(args)
+        self._step_args = N.DecodeArgs.from_buffer_copy(args)
+        self._step_args.fused_append = 1
+        self._step_args_ref = ctypes.byref(self._step_args)
         self._status_pointer = N.status_word(self.device).data_ptr()
         self._graph = None
 
@@ -254,6 +267,11 @@ class DecodeBatch:
 
     def _launch_attend(self) -> None:
         rc = N.library().inq_decode_attention(self._decode_args_ref, N.stream_pointer(self.device))
+        if rc:
+            N.check(rc, "inq_decode_attention")
+
+    def _launch_step(self) -> None:
+        rc = N.library().inq_decode_attention(self._step_args_ref, N.stream_pointer(self.device))
         if rc:
             N.check(rc, "inq_decode_attention")
 
@@ -272,18 +290,22 @@ class DecodeBatch:
         return self.outputs
 
     def step(self) -> torch.Tensor:
-        """One decode step: append the new token of every sequence, then attend."""
-        self.append()
-        return self.attend()
+        """One decode step in one launch: attend to history plus the new token of every sequence
+        and append that token to its tail."""
+        if self.capacity_left < 1:
+            raise RuntimeError("a tail buffer is full: seal a block before appending")
+        self._launch_step()
+        self._appended += 1
+        self.launches += 1
+        return self.outputs
 
     def capture(self) -> None:
-        """Record append + attend into a CUDA graph; ``replay`` then costs one graph launch.
+        """Record the fused step into a CUDA graph; ``replay`` then costs one graph launch.
         Run at least one eager ``step`` first (the first launch sets kernel attributes)."""
         graph = torch.cuda.CUDAGraph()
         counters = self.tail_counters.clone()
         with torch.cuda.graph(graph):
-            self._launch_append()
-            self._launch_attend()
+            self._launch_step()
         self.tail_counters.copy_(counters)  # capture does not execute, but keep the state explicit
         self._graph = graph
 
@@ -294,7 +316,7 @@ class DecodeBatch:
             raise RuntimeError("a tail buffer is full: seal a block before appending")
         self._graph.replay()
         self._appended += 1
-        self.launches += 2
+        self.launches += 1
         return self.outputs
 
     def rewind(self, appended: int = 0) -> None:

@@ -131,6 +131,36 @@ def _quantize_temporal_blocks(tensor, block_count, block_size, config):
     return ArenaPackedTensor.split(packed, block_count, shape, tensor.dtype)
 
 
+def _dequantize_arena_into(arena, out: torch.Tensor, position: int) -> bool:
+    """Dequantise the blocks of one encoder arena ([blocks, heads, T, C] fields) straight into ``out``
+    [1, heads, tokens, C] from token ``position`` on (C ABI ``inq_k4_dequantize_strided`` /
+    ``inq_v_dequantize_strided``); False when the layouts do not allow it."""
+    from .value_codec import PackedValues
+    run, heads, tokens, channels = arena.shape
+    if out.stride(3) != 1 or out.stride(2) != channels or out.dtype not in N.DTYPE_CODE or not arena.payload.is_contiguous():
+        return False
+    base = out.data_ptr() + position * out.stride(2) * out.element_size()
+    lib, stream = N.library(), N.stream_pointer(out.device)
+    if isinstance(arena, PackedValues):
+        if not (arena.scales.is_contiguous() and arena.offsets.is_contiguous()):
+            return False
+        rc = lib.inq_v_dequantize_strided(N.pointer(arena.payload), N.pointer(arena.scales), N.pointer(arena.offsets), run, heads,
+                                          tokens, channels, arena.bits, arena.group_size, base, tokens * out.stride(2),
+                                          out.stride(1), N.DTYPE_CODE[out.dtype], stream)
+        N.check(rc, "inq_v_dequantize_strided")
+        return True
+    fields = (arena.scales, arena.salient_channels, arena.donor_channels, arena.padding)
+    if not all(t.is_contiguous() for t in fields):
+        return False
+    count = arena.salient_channels.shape[-1]
+    rc = lib.inq_k4_dequantize_strided(N.pointer(arena.payload), N.pointer(arena.scales), N.pointer(arena.salient_channels),
+                                       N.pointer(arena.donor_channels), int(arena.salient_channels.dtype == torch.int32),
+                                       N.pointer(arena.padding), run, heads, tokens, channels, count, base,
+                                       tokens * out.stride(2), out.stride(1), N.DTYPE_CODE[out.dtype], stream)
+    N.check(rc, "inq_k4_dequantize_strided")
+    return True
+
+
 def restore_blocks(blocks, out: torch.Tensor, position: int) -> int:
     """Dequantise ``blocks`` into ``out`` [1, H, tokens, C] from token ``position`` on; returns the
     position after the last block.  Blocks sealed by one call share an encoder arena: each arena is
@@ -147,7 +177,9 @@ def restore_blocks(blocks, out: torch.Tensor, position: int) -> int:
                     break
                 run += 1
         tokens = blocks[index].shape[2]
-        if run > 1 and run == arena[0].shape[0]:
+        if run > 1 and run == arena[0].shape[0] and _dequantize_arena_into(arena[0], out, position):
+            pass   # one launch wrote every block of the arena at its token position
+        elif run > 1 and run == arena[0].shape[0]:
             dense = arena[0].dequantize(dtype=out.dtype)            # [run, heads, tokens, channels]
             out[0, :, position:position + run * tokens].view(heads, run, tokens, channels).copy_(
                 dense.permute(1, 0, 2, 3))

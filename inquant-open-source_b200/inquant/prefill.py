@@ -79,23 +79,33 @@ class PrefillHistory:
     contents are undefined after that; reset it).  ``defer_checks=False`` keeps the reference's
     behaviour of raising inside the call, at one stream synchronisation per sealed tensor.
 
-    The price is memory: 2 * layers * H * tokens * C elements of the model dtype while the prompt
-    is being prefilled (1.9 GB for 32768 tokens of a 28-layer, 4-KV-head model); ``release`` frees
-    it.  Tensors grow geometrically unless ``capacity_tokens`` covers the prompt.
+    The price of keeping it is memory: 2 * layers * H * tokens * C elements of the model dtype while
+    the prompt is being prefilled (1.9 GB for 32768 tokens of a 28-layer, 4-KV-head model) -- the
+    dense cache the packed one exists to avoid.  ``persistent=False`` (the default) therefore keeps
+    NO per-layer copy: one scratch pair serves every layer, and a layer's history is rebuilt into it
+    from the packed cache for each of its chunks (sink and tail copied, every sealed block
+    dequantised by this library's kernels: a few per cent of the chunk's attention time).  That is
+    the reference's own semantics (``update`` materialises per call) at 2 * H * tokens * C elements
+    in total (71 MB for the same prompt).  ``persistent=True`` keeps the per-layer copies and
+    dequantises every block once.  ``release`` frees either.  Tensors grow geometrically unless
+    ``capacity_tokens`` covers the prompt.
     """
 
-    def __init__(self, cache, capacity_tokens: int = 4096, defer_checks: bool = True):
+    def __init__(self, cache, capacity_tokens: int = 4096, defer_checks: bool = True, persistent: bool = False):
         if capacity_tokens < 1:
             raise ValueError("capacity_tokens must be positive")
         self.cache, self.capacity_tokens, self.defer_checks = cache, int(capacity_tokens), bool(defer_checks)
+        self.persistent = bool(persistent)
         self._layers: dict[int, list] = {}    # layer -> [key, value, tokens, restored blocks]
+        self._scratch: list = [None, None, 0, 0]   # the shared pair of the non-persistent mode
 
     def release(self) -> None:
         self._layers.clear()
+        self._scratch = [None, None, 0, 0]
 
     def check(self) -> None:
         """Raise for failures recorded while checks were deferred (synchronises the stream)."""
-        devices = {state[0].device for state in self._layers.values() if state[0] is not None}
+        devices = {state[0].device for state in list(self._layers.values()) + [self._scratch] if state[0] is not None}
         for device in devices:
             status = N.take_status(device)
             if status & N.STATUS_NONFINITE:
@@ -105,7 +115,7 @@ class PrefillHistory:
 
     @property
     def nbytes(self) -> int:
-        return sum(s[0].numel() * s[0].element_size() * 2 for s in self._layers.values())
+        return sum(s[0].numel() * s[0].element_size() * 2 for s in list(self._layers.values()) + [self._scratch] if s[0] is not None)
 
     def _room(self, state: list, tokens: int, like: torch.Tensor) -> None:
         key = state[0]
@@ -125,6 +135,8 @@ class PrefillHistory:
         """Attention of the chunk over history + chunk, then append and seal; see ``prefill_chunk``."""
         from .cache import restore_blocks
         cache = self.cache
+        if not self.persistent:
+            return self._chunk_from_packed(query, key, value, layer_idx, scale, cache_kwargs)
         state = self._layers.setdefault(layer_idx, [None, None, 0, 0])
         seen = cache.get_seq_length(layer_idx) if layer_idx in cache._layers else 0
         if state[2] != seen and state[2] != 0:
@@ -155,6 +167,39 @@ class PrefillHistory:
             restore_blocks(layer.value_blocks[state[3]:], state[1], position)
             state[3] = len(layer.key_blocks)
         state[2] = seen + tokens
+        return out
+
+
+    def _chunk_from_packed(self, query, key, value, layer_idx, scale, cache_kwargs) -> torch.Tensor:
+        """One chunk with the layer's history rebuilt from the packed cache into the shared scratch."""
+        from .cache import restore_blocks
+        cache, scratch = self.cache, self._scratch
+        seen = cache.get_seq_length(layer_idx) if layer_idx in cache._layers else 0
+        cache._validate_update(key, value, layer_idx, cache_kwargs)
+        tokens = key.shape[2]
+        scratch[2] = 0          # nothing of another layer's contents is kept
+        if scratch[0] is not None and (scratch[0].dtype != key.dtype or scratch[0].device != key.device
+                                       or scratch[0].shape[1] != key.shape[1] or scratch[0].shape[3] != key.shape[3]):
+            scratch[0] = scratch[1] = None
+        self._room(scratch, seen + tokens, key)
+        if seen:
+            layer = cache._layers[layer_idx]
+            for out, sink, blocks, tail in ((scratch[0], layer.sink_key, layer.key_blocks, layer.residual_key),
+                                            (scratch[1], layer.sink_value, layer.value_blocks, layer.residual_value)):
+                position = 0 if sink is None else sink.shape[2]
+                if position:
+                    out[:, :, :position].copy_(sink)
+                position = restore_blocks(blocks, out, position)
+                if tail is not None and tail.shape[2]:
+                    out[:, :, position:position + tail.shape[2]].copy_(tail)
+        scratch[0][:, :, seen:seen + tokens].copy_(key)
+        scratch[1][:, :, seen:seen + tokens].copy_(value)
+        out = prefill_attention(query, scratch[0][:, :, :seen + tokens], scratch[1][:, :, :seen + tokens], scale)
+        if self.defer_checks:
+            with N.deferred_status():
+                cache.extend(key, value, layer_idx, cache_kwargs)
+        else:
+            cache.extend(key, value, layer_idx, cache_kwargs)
         return out
 
 

@@ -204,8 +204,7 @@ def enable_fused_attention(model: Any, *, allow_cpu_reference: bool = False,
             graph_batch.queries[0].copy_(query[0, :, 0])
             graph_batch.new_keys[0].copy_(key[0, :, 0])
             graph_batch.new_values[0].copy_(value[0, :, 0])
-            graph_batch._launch_append()
-            graph_batch._launch_attend()
+            graph_batch._launch_step()   # attention over history + the new token, which is appended by the same launch
             attention._inquant_fused_decode_calls += 1
             return attention.o_proj(graph_batch.outputs.reshape(*input_shape, -1)), None
         view = cache.append_for_attention(

@@ -190,21 +190,23 @@ class SplitKVDecode:
         """One decode step; ``inputs`` must hold the same queries on every rank (and the new
         token's K/V on the rank that owns the tail)."""
         if append and self.owns_tail:
-            self.batch.append()
-        self.batch.attend()
+            self.batch.step()        # one launch: attends to the new token and appends it
+        else:
+            self.batch.attend()
         self._exchange_and_merge()
         return self.outputs
 
     def capture(self) -> None:
-        """Record one step (append on the tail owner, local decode, exchange, merge) into a CUDA
+        """Record one step (local decode, with the fused append on the tail owner, exchange, merge) into a CUDA
         graph; ``replay`` then costs one graph launch per step.  Run eager steps first: the first
         launches set kernel attributes and NCCL builds its communicator outside a capture."""
         graph = torch.cuda.CUDAGraph()
         counters = self.batch.tail_counters.clone()
         with torch.cuda.graph(graph):
             if self.owns_tail:
-                self.batch._launch_append()
-            self.batch._launch_attend()
+                self.batch._launch_step()
+            else:
+                self.batch._launch_attend()
             self._exchange_and_merge()
         self.batch.tail_counters.copy_(counters)
         self._graph = graph

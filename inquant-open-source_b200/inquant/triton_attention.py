@@ -106,15 +106,24 @@ class PackedDecodeState:
         self._kv_heads = first.shape[1]
         self._packed_tokens = first.shape[2]
         self._salient = first.salient_channels.shape[-1]
-        for block in key_blocks:
-            if not isinstance(block, PackedTensor) or block.shape != first.shape or block.salient_channels.shape[-1] != self._salient:
+        # Only the new suffix is checked: the prefix was checked when it was added and is immutable.
+        # Blocks of an encoder arena are judged by the arena's tensors, so that none of their field
+        # views has to be created here (a 32K-token layer holds over a thousand of them).
+        def parts(block):
+            arena = block.__dict__.get("_arena") if hasattr(block, "__dict__") else None
+            return arena[0] if arena is not None else block
+
+        new_keys, new_values = key_blocks[old_count:], value_blocks[old_count:]
+        for block in new_keys:
+            if not isinstance(block, PackedTensor) or block.shape != first.shape \
+                    or parts(block).salient_channels.shape[-1] != self._salient:
                 raise ValueError("All packed K/V blocks must share shape and salient-channel count")
         # the preset (2-bit values in groups of 64) runs the streaming kernel; every other value
         # codec the reference accepts runs the general kernel
         self._inquant_values = isinstance(value_blocks[0], PackedTensor)
         if self._inquant_values:
             self._value_bits, self._value_group = 0, 64
-            self._value_salient = value_blocks[0].salient_channels.shape[-1]
+            self._value_salient = parts(value_blocks[0]).salient_channels.shape[-1]
         elif isinstance(value_blocks[0], PackedValues):
             self._value_bits = value_blocks[0].bits
             self._value_group = value_blocks[0].group_size
@@ -122,18 +131,22 @@ class PackedDecodeState:
         else:
             raise ValueError("Value blocks must be PackedValues or PackedTensor")
         self._preset = not self._inquant_values and (self._value_bits, self._value_group) == (2, 64)
-        for block in value_blocks:
+        for block in new_values:
             if block.shape != first.shape:
                 raise ValueError("All packed blocks must share shape")
             if self._inquant_values:
-                if not isinstance(block, PackedTensor) or block.salient_channels.shape[-1] != self._value_salient:
+                if not isinstance(block, PackedTensor) or parts(block).salient_channels.shape[-1] != self._value_salient:
                     raise ValueError("All V blocks must share the same quantizer")
             elif not isinstance(block, PackedValues) or (block.bits, block.group_size) != (self._value_bits, self._value_group):
                 raise ValueError("All V blocks must share the same quantizer")
-        for block in (*key_blocks, *value_blocks):
-            if any(t.device != self._device for t in block.tensors.values()):
+        checked = set()
+        for block in (*new_keys, *new_values):
+            owner = parts(block)
+            if id(owner) in checked:
+                continue
+            checked.add(id(owner))
+            if any(t.device != self._device for t in owner.tensors.values()):
                 raise ValueError("All packed tensors must share the same CUDA device")
-        new_keys, new_values = key_blocks[old_count:], value_blocks[old_count:]
         last_field = "padding" if self._inquant_values else "offsets"
         pointers = []
         for k, v in zip(new_keys, new_values):

@@ -102,7 +102,7 @@ def test_prefill_history_holds_exactly_what_update_would_return(value_bits, chun
     cfg = CacheConfig(CodecConfig(donor_policy="min_error"), block_size=64, residual_length=16, sink_tokens=4,
                       value_bits=value_bits, value_group_size=64)
     cache, shadow, plain = InQuantCache(cfg), InQuantCache(cfg), InQuantCache(cfg)
-    history = PrefillHistory(cache, capacity_tokens=128)      # forces the tensors to grow
+    history = PrefillHistory(cache, capacity_tokens=128, persistent=True)      # forces the tensors to grow
     scale, seen = 128 ** -0.5, 0
     for tokens in chunk_sizes:
         q = torch.randn((1, q_heads, tokens, 128), device="cuda", generator=gen).bfloat16()
@@ -122,7 +122,7 @@ def test_prefill_history_holds_exactly_what_update_would_return(value_bits, chun
         assert torch.equal(a, b)
     assert history.nbytes > 0
     # a history first used on a filled layer takes the dense state over from the cache
-    late = PrefillHistory(plain)
+    late = PrefillHistory(plain, persistent=True)
     q = torch.randn((1, q_heads, 50, 128), device="cuda", generator=gen).bfloat16()
     k = torch.randn((1, heads, 50, 128), device="cuda", generator=gen).bfloat16()
     assert torch.equal(prefill_chunk(plain, q, k, k, 0, scale, history=late), prefill_chunk(cache, q, k, k, 0, scale, history=history))
@@ -158,3 +158,34 @@ def test_prefill_history_reports_non_finite_input_at_check_or_at_once():
     strict = InQuantCache(cfg)
     with pytest.raises(ValueError, match="finite"):
         prefill_chunk(strict, q, bad, k, 0, history=PrefillHistory(strict, defer_checks=False))
+
+
+def test_prefill_history_without_a_dense_copy_rebuilds_from_the_packed_cache():
+    """The default history keeps no per-layer dense tensors: every chunk's history comes out of the
+    packed cache into one scratch pair shared by the layers.  Outputs and cache contents equal the
+    materialising form chunk by chunk, for two layers that alternate."""
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.prefill import PrefillHistory, prefill_chunk
+    gen = torch.Generator(device="cuda").manual_seed(29)
+    heads, q_heads = 2, 14
+    cfg = CacheConfig(CodecConfig(donor_policy="min_error"), block_size=64, residual_length=16, sink_tokens=4, value_bits=2)
+    cache, plain = InQuantCache(cfg), InQuantCache(cfg)
+    history = PrefillHistory(cache, capacity_tokens=64)
+    assert not history.persistent
+    scale = 128 ** -0.5
+    for tokens in (3, 200, 130, 70):
+        for layer in (0, 1):
+            q = torch.randn((1, q_heads, tokens, 128), device="cuda", generator=gen).bfloat16()
+            k = torch.randn((1, heads, tokens, 128), device="cuda", generator=gen).bfloat16()
+            v = torch.randn((1, heads, tokens, 128), device="cuda", generator=gen).bfloat16()
+            out = prefill_chunk(cache, q, k, v, layer, scale, history=history)
+            assert torch.equal(out, prefill_chunk(plain, q, k, v, layer, scale))
+    history.check()
+    for layer in (0, 1):
+        for a, b in zip(cache.materialize(layer), plain.materialize(layer)):
+            assert torch.equal(a, b)
+    assert not history._layers
+    assert 0 < history.nbytes <= 2 * heads * 1024 * 128 * 2     # one pair for both layers, grown geometrically
+    history.release()
+    assert history.nbytes == 0

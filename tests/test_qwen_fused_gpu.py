@@ -98,7 +98,7 @@ def test_chunked_prefill_through_the_tensor_core_kernel_matches_the_stock_forwar
         expected_cache, packed = InQuantCache(config), InQuantCache(config)
         if keep_history:   # the dense history is kept across chunks instead of rebuilt per chunk
             from inquant.prefill import PrefillHistory
-            packed._prefill_history = PrefillHistory(packed)
+            packed._prefill_history = PrefillHistory(packed, persistent=True)
         for start in range(0, 300, 100):
             chunk = tokens[:, start:start + 100]
             expected = twin(chunk, past_key_values=expected_cache).logits
