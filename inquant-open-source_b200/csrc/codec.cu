@@ -5,6 +5,8 @@
 // reference's bit for bit, and the reference performs separate IEEE multiplies, adds and
 // divisions.  The only fused operations are the explicit fma() calls of the division-by-
 // integer below, which is proven to return the correctly rounded quotient.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace inq {
@@ -941,6 +943,64 @@ __global__ void __launch_bounds__(1024) select_kernel(const float* saliency, con
 }
 
 // ------------------------------------------------------------------------------------------
+// 128-channel rows, 16-bit output: a thread owns 8 consecutive channels of one token (4 payload bytes
+// in, 16 bytes out); 16 threads cover a token, a CTA of 256 threads covers 16 tokens per step.
+template <typename T>
+__global__ void __launch_bounds__(256) k4_dequantize128_kernel(const unsigned char* payload, const float* scales, const void* salient,
+                                                               const void* donors, const float* padding, int tokens, int count, T* out,
+                                                               int rows_inner, long long out_so, long long out_si) {
+  __shared__ int role[128];
+  __shared__ float scale[128], pad[128];
+  const long long row = blockIdx.x;
+  if (threadIdx.x < 128) {
+    role[threadIdx.x] = -1;
+    scale[threadIdx.x] = scales[row * 128 + threadIdx.x];
+    pad[threadIdx.x] = 0.f;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < count) {
+    const int i = threadIdx.x;
+    const int s = ((const unsigned char*)salient)[row * count + i], d = ((const unsigned char*)donors)[row * count + i];
+    role[s] = d;
+    role[d] = -2 - i;
+    pad[d] = padding[row * count + i];
+  }
+  __syncthreads();
+  const unsigned char* bytes = payload + row * (long long)tokens * 64;
+  T* dst = out + (row / rows_inner) * out_so + (row % rows_inner) * out_si;
+  const int c0 = (threadIdx.x & 15) * 8;
+  int r[8];
+  float sc[8], pd[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    r[k] = role[c0 + k];
+    sc[k] = scale[c0 + k];
+    pd[k] = pad[c0 + k];
+  }
+  const int per_cta = (tokens + gridDim.y - 1) / gridDim.y;
+  const int t_begin = blockIdx.y * per_cta, t_end = min(tokens, t_begin + per_cta);
+  for (int t = t_begin + (threadIdx.x >> 4); t < t_end; t += 16) {
+    const unsigned char* line = bytes + (long long)t * 64;
+    const unsigned word = *(const unsigned*)(line + (c0 >> 1));
+    T vals[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int slot = (word >> (4 * k)) & 15;
+      float value;
+      if (r[k] >= 0) {
+        const int partner = (line[r[k] >> 1] >> ((r[k] & 1) * 4)) & 15;
+        value = (float)(((slot << 4) | partner) - 128) * sc[k];
+      } else if (r[k] == -1) {
+        value = (float)(slot - 8) * sc[k];
+      } else {
+        value = pd[k];
+      }
+      vals[k] = from_float<T>(value);
+    }
+    *(uint4*)(dst + (long long)t * 128 + c0) = *(const uint4*)vals;
+  }
+}
+
 template <typename T>
 __global__ void k4_dequantize_kernel(const unsigned char* payload, const float* scales, const void* salient,
                                      const void* donors, int descriptor_i32, const float* padding, int tokens,
@@ -1165,6 +1225,36 @@ __global__ void v_dequantize_kernel(const unsigned char* payload, const __half* 
   out[(row / rows_inner) * out_so + (row % rows_inner) * out_si + (token % tokens) * channels + c] = from_float<T>(value);
 }
 
+// 128 channels, 16-bit output: a thread owns 8 consecutive channels of one token (they share a group)
+template <typename T, int BITS>
+__global__ void __launch_bounds__(256) v_dequantize128_kernel(const unsigned char* payload, const __half* scales, const __half* offsets,
+                                                              long long total_tokens, int tokens, int group, T* out, int rows_inner,
+                                                              long long out_so, long long out_si) {
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // (token, chunk of 8 channels)
+  const long long token = item >> 4;
+  if (token >= total_tokens) return;
+  const int c0 = (int)(item & 15) * 8;
+  constexpr int kBytes = BITS;   // 8 channels x BITS bits
+  const unsigned char* src = payload + token * (128 * BITS / 8) + (c0 * BITS / 8);
+  unsigned word = 0;
+#pragma unroll
+  for (int b = 0; b < kBytes; ++b) word |= (unsigned)src[b] << (8 * b);
+  const int groups = 128 / group;
+  const long long param = token * groups + c0 / group;
+  const float sc = __half2float(scales[param]), of = __half2float(offsets[param]);
+  T vals[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float code = (float)((word >> (BITS * k)) & ((1u << BITS) - 1u));
+    float value = code * sc;
+    value = value + of;
+    vals[k] = from_float<T>(value);
+  }
+  const long long row = token / tokens;
+  T* dst = out + (row / rows_inner) * out_so + (row % rows_inner) * out_si + (token % tokens) * 128 + c0;
+  *(uint4*)dst = *(const uint4*)vals;
+}
+
 __global__ void build_roles_kernel(const void* salient, const void* donors, int descriptor_i32, int channels, int count,
                                    void* roles, int role_bytes) {
   const long long row = blockIdx.x;
@@ -1315,9 +1405,21 @@ extern "C" int inq_k4_dequantize_strided(const uint8_t* payload, const float* sc
     return INQ_ERR_ARGUMENT;
   if (count && (!salient || !donors || !padding)) return INQ_ERR_ARGUMENT;
   if (channels > 4096) return INQ_ERR_UNSUPPORTED;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (channels == 128 && !descriptor_i32 && count <= 64 && out_dtype != INQ_F32 && ((uintptr_t)out % 16) == 0 &&
+      out_stride_outer % 8 == 0 && out_stride_inner % 8 == 0 && ((uintptr_t)payload % 4) == 0) {
+    // enough CTAs per row to fill the device, at least 64 tokens each
+    int split = (int)std::min<long long>((tokens + 63) / 64, std::max<long long>(1, 2048 / rows));
+    dim3 fast((unsigned)rows, (unsigned)split);
+    if (out_dtype == INQ_F16)
+      k4_dequantize128_kernel<__half><<<fast, 256, 0, stream>>>(payload, scales, salient, donors, padding, tokens, count, (__half*)out, rows_inner, out_stride_outer, out_stride_inner);
+    else
+      k4_dequantize128_kernel<__nv_bfloat16><<<fast, 256, 0, stream>>>(payload, scales, salient, donors, padding, tokens, count, (__nv_bfloat16*)out, rows_inner, out_stride_outer, out_stride_inner);
+    INQ_CUDA_CHECK(cudaGetLastError());
+    return INQ_OK;
+  }
   dim3 grid((unsigned)rows, (unsigned)((tokens + 15) / 16));
   size_t shared = (size_t)channels * 12;
-  cudaStream_t stream = (cudaStream_t)stream_;
   switch (out_dtype) {
     case INQ_F32:
       k4_dequantize_kernel<float><<<grid, 256, shared, stream>>>(payload, scales, salient, donors, descriptor_i32, padding, tokens, channels, count, (float*)out, rows_inner, out_stride_outer, out_stride_inner);
@@ -1415,6 +1517,22 @@ extern "C" int inq_v_dequantize_strided(const uint8_t* payload, const void* scal
   long long total = rows_outer * (long long)rows_inner * tokens * channels;
   unsigned blocks = (unsigned)((total + 255) / 256);
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (channels == 128 && out_dtype != INQ_F32 && ((uintptr_t)out % 16) == 0 && out_stride_outer % 8 == 0 && out_stride_inner % 8 == 0) {
+    const long long total_tokens = rows_outer * (long long)rows_inner * tokens;
+    const unsigned fast = (unsigned)((total_tokens * 16 + 255) / 256);
+    const __half* sc = (const __half*)scales;
+    const __half* of = (const __half*)offsets;
+    if (out_dtype == INQ_F16 && bits == 2)
+      v_dequantize128_kernel<__half, 2><<<fast, 256, 0, stream>>>(payload, sc, of, total_tokens, tokens, group, (__half*)out, rows_inner, out_stride_outer, out_stride_inner);
+    else if (out_dtype == INQ_F16)
+      v_dequantize128_kernel<__half, 4><<<fast, 256, 0, stream>>>(payload, sc, of, total_tokens, tokens, group, (__half*)out, rows_inner, out_stride_outer, out_stride_inner);
+    else if (bits == 2)
+      v_dequantize128_kernel<__nv_bfloat16, 2><<<fast, 256, 0, stream>>>(payload, sc, of, total_tokens, tokens, group, (__nv_bfloat16*)out, rows_inner, out_stride_outer, out_stride_inner);
+    else
+      v_dequantize128_kernel<__nv_bfloat16, 4><<<fast, 256, 0, stream>>>(payload, sc, of, total_tokens, tokens, group, (__nv_bfloat16*)out, rows_inner, out_stride_outer, out_stride_inner);
+    INQ_CUDA_CHECK(cudaGetLastError());
+    return INQ_OK;
+  }
   switch (out_dtype) {
     case INQ_F32:
       v_dequantize_kernel<float><<<blocks, 256, 0, stream>>>(payload, (const __half*)scales, (const __half*)offsets, total, channels, bits, group, (float*)out, tokens, rows_inner, out_stride_outer, out_stride_inner);
