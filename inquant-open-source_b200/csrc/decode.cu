@@ -309,7 +309,11 @@ __device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned
 }
 
 // ------------------------------------------------------------------------------------------ the kernel
-template <int MODE, typename QT, bool SAL, int SUB>
+// FAST: blocks of whole 32-token slices, at least four per block, exactly one group of 16 salient
+// channels (the preset and the 128/256-token pages): the copies of a slice then are eight
+// asynchronous copies from per-lane pointers that advance by constants, a block's metadata is
+// requested as soon as the prefetch cursor enters the block, and nothing ragged is handled.
+template <int MODE, typename QT, bool SAL, int SUB, bool FAST>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const DecodeParams P) {
   constexpr int kSub = SUB;
   constexpr int kSliceTokens = SliceCfg<SUB>::kSliceTokens;
@@ -324,7 +328,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   unsigned char* warp_base = smem + kQBytes;
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
-  const int groups = (P.n_pad + 15) >> 4;                               // salient channels in groups of 16
+  const int n_pad = FAST ? 16 : P.n_pad;                                // salient channels per head
+  const int groups = FAST ? 1 : (n_pad + 15) >> 4;                      // ... in groups of 16
   const int warp_bytes = warp_smem_bytes(groups, kStageBytes);
   unsigned char* const wb = warp_base + warp * warp_bytes;
   // folded-query B fragments of the 8 K steps ([step][lane] x 8 bytes); while a block's weights
@@ -582,9 +587,58 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     auto stage_meta = [&](const BlockPtrs& bp, unsigned char* dst) {
       cp_async16(dst + lane * 16, bp.ks + lane * 16);
       if (lane < (MODE == 0 ? 8 : 16)) cp_async16(dst + 512 + lane * 16, bp.kr + lane * 16);
-      for (int i = lane; i < P.n_pad; i += 32) cp_async4(dst + 768 + i * 4, bp.kpad + i * 4);
+      for (int i = lane; i < n_pad; i += 32) cp_async4(dst + 768 + i * 4, bp.kpad + i * 4);
     };
+    // FAST: this lane's source pointers of the next slice to request (K rows, V rows, V scale and
+    // offset pairs), the shared-memory address of the stage it goes to, slices left in its block
+    const unsigned char* fk = pf_ptrs.kp + pf_slice * 2048 + lane * 16;
+    const unsigned char* fv = pf_ptrs.vp + pf_slice * 1024 + lane * 16;
+    const unsigned char* fs = pf_ptrs.vs + pf_slice * 128 + lane * 4;
+    const unsigned char* fo = pf_ptrs.vo + pf_slice * 128 + lane * 4;
+    const unsigned ring_lo = smem_addr(ring), ring_hi = ring_lo + kStages * kStageBytes;
+    unsigned issue_addr = ring_lo;
+    int pf_left = spb - pf_slice;
+    const unsigned fast_v_dst = (unsigned)(kStageK + (((lane >> 1) * 2 + ((lane & 1) ^ ((lane >> 3) & 1))) << 4));
+    if (FAST) {
+      stage_meta(pf_ptrs, wmeta);   // the first block's metadata rides with its first slice
+      meta_block = pf_block;
+    }
     auto issue = [&]() {
+      if (FAST) {
+        if (to_issue > 0) {
+          const unsigned dk = issue_addr + lane * 16, dv = issue_addr + fast_v_dst, dp = issue_addr + kStageK + kStageV + lane * 4;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dk), "l"(fk));
+          asm volatile("cp.async.cg.shared.global [%0+512], [%1+512], 16;" ::"r"(dk), "l"(fk));
+          asm volatile("cp.async.cg.shared.global [%0+1024], [%1+1024], 16;" ::"r"(dk), "l"(fk));
+          asm volatile("cp.async.cg.shared.global [%0+1536], [%1+1536], 16;" ::"r"(dk), "l"(fk));
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dv), "l"(fv));
+          asm volatile("cp.async.cg.shared.global [%0+512], [%1+512], 16;" ::"r"(dv), "l"(fv));
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dp), "l"(fs));
+          asm volatile("cp.async.ca.shared.global [%0+128], [%1], 4;" ::"r"(dp), "l"(fo));
+          fk += 2048; fv += 1024; fs += 128; fo += 128;
+          --to_issue;
+          issue_addr += kStageBytes;
+          if (issue_addr == ring_hi) issue_addr = ring_lo;
+          if (--pf_left == 0) {
+            pf_left = spb;
+            ++pf_block;
+            if (to_issue > 0) {
+              // the cursor enters a new block: its rows, and its metadata at once when the staging
+              // area is free, i.e. the block whose metadata it holds has been folded (always the case
+              // except for a warp whose range begins in the last slices of a block; the fold then
+              // fetches the metadata itself)
+              pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h);
+              fk = pf_ptrs.kp + lane * 16; fv = pf_ptrs.vp + lane * 16; fs = pf_ptrs.vs + lane * 4; fo = pf_ptrs.vo + lane * 4;
+              if (folded_block == meta_block) {
+                stage_meta(pf_ptrs, wmeta);
+                meta_block = pf_block;
+              }
+            }
+          }
+        }
+        cp_async_commit();
+        return;
+      }
       if (to_issue > 0) {
         unsigned char* const stage_ptr = ring + issue_stage * kStageBytes;
         if (kMetaInStage) {
@@ -638,6 +692,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     const unsigned ring_addr = smem_addr(ring), lane16 = lane * 16;
     const unsigned ww_addr = smem_addr(wW) + lane * 8, sel_addr = smem_addr(wsel) + lane * 8;
     int stage_index = 0;
+    unsigned consume_addr = ring_lo;
 
     for (int it = 0; it < n_my; ++it) {
       cp_async_wait<kStages - 2>();
@@ -645,7 +700,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       // With fewer than three slices per block the next block's metadata can only be staged once
       // this block's fold has released the staging area: there the copies are issued after the
       // fold.  Otherwise they go out first.
-      const bool issue_late = !kMetaInStage && spb < 3 && need_weights;
+      // FAST: a request that enters a new block also requests that block's metadata into the one
+      // staging area, so the fold of this slice's block (it reads that area) comes first
+      const bool issue_late = FAST ? need_weights : (!kMetaInStage && spb < 3 && need_weights);
       if (!issue_late) issue();
 
       if (need_weights) {
@@ -693,7 +750,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         bool bad = false;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          if (role[i] > 127 || role[i] < -1 - P.n_pad) {
+          if (role[i] > 127 || role[i] < -1 - n_pad) {
             bad = true;
             role[i] = -1;
           }
@@ -707,7 +764,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
             fv[i] = 0.f;
             kv[i] = 0.f;
             const int idx = -(MODE == 0 ? (int)((const signed char*)meta_roles)[role[i]] : (int)((const short*)meta_roles)[role[i]]) - 2;
-            if (idx >= 0 && idx < P.n_pad) sidx[i] = idx; else bad = true;
+            if (idx >= 0 && idx < n_pad) sidx[i] = idx; else bad = true;
           } else if (role[i] < -1) {
             // donor: its slot holds the low nibble of a salient code; the reference stores the
             // sampled mean as the channel's own value and rounds it to the model dtype
@@ -717,7 +774,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         }
         if (bad) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
         // the selection cells of the last block are cleared through their recorded offsets
-        for (int v = lane; v < 2 * P.n_pad; v += 32) *(unsigned short*)(wsel + wcell[v]) = 0;
+        for (int v = lane; v < 2 * n_pad; v += 32) *(unsigned short*)(wsel + wcell[v]) = 0;
         __syncwarp();   // the staged metadata has been read: its area now takes the per-channel terms
         *(float4*)(ff + 4 * lane) = make_float4(fv[0], fv[1], fv[2], fv[3]);
         *(float4*)(fk0 + 4 * lane) = make_float4(kv[0], kv[1], kv[2], kv[3]);
@@ -738,7 +795,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         // salient idx with weight 2^-13 when idx & 8 is clear and with weight 2^-22 when it is set;
         // every entry and every partial sum is exact.  One cell per lane: entry v is the source
         // (even v) or the donor slot (odd v) of salient v / 2.
-        for (int v = lane; v < 2 * P.n_pad; v += 32) {
+        for (int v = lane; v < 2 * n_pad; v += 32) {
           const int idx = v >> 1, which = v & 1;
           const int c = (which ? wdon[idx] : wsrc[idx]) & 127;
           const int jj = c >> 5, u = c & 31;
@@ -763,7 +820,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
               const int i = gsel * 16 + 2 * j + (k & 1) + (k >> 1) * 8;
               const int c = wsrc[min(i, 63)];
               const QT qt = from_float<QT>(qs[(r * 4 + (c >> 5)) * kQChunk + (c & 31)] * (1.f / 4096.f));
-              qv[k] = i < P.n_pad ? *(const unsigned short*)&qt : (unsigned short)0;
+              qv[k] = i < n_pad ? *(const unsigned short*)&qt : (unsigned short)0;
             }
             *(uint2*)(wqsal + (gsel * 32 + lane) * 8) = make_uint2((unsigned)qv[0] | ((unsigned)qv[1] << 16),
                                                                    (unsigned)qv[2] | ((unsigned)qv[3] << 16));
@@ -807,9 +864,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         }
       }
 
-      const unsigned stage = launder(ring_addr + stage_index * kStageBytes);
+      const unsigned stage = launder(FAST ? consume_addr : ring_addr + stage_index * kStageBytes);
       const unsigned ww_it = launder(ww_addr), sel_it = launder(sel_addr);
-      if (++stage_index == kStages) stage_index = 0;
+      if (FAST) {
+        consume_addr += kStageBytes;
+        if (consume_addr == ring_hi) consume_addr = ring_lo;
+      } else if (++stage_index == kStages) {
+        stage_index = 0;
+      }
       // ---- scores of two 16-token sub-slices (tokens 0..15 and 16..31 of the stage): K nibbles
       //      times the folded query, plus the exactly rebuilt salient channels
       float S[2][4];
@@ -917,7 +979,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         s2[u][2] = fmaf(S[u][2], alpha[0], bm[0]);
         s2[u][3] = fmaf(S[u][3], alpha[1], bm[1]);
       }
-      {
+      if (FAST) {
+        // whole slices only: the one mask left is the packed copy of the tokens the exact sink holds
+        const int g0 = cur_block * T + cur_slice * kSliceTokens;
+        if (g0 < first_visible) {
+#pragma unroll
+          for (int u = 0; u < kSub; ++u) {
+            if (g0 + 16 * u + r < first_visible) s2[u][0] = s2[u][1] = -INFINITY;
+            if (g0 + 16 * u + r + 8 < first_visible) s2[u][2] = s2[u][3] = -INFINITY;
+          }
+        }
+      } else {
         const int tok0 = cur_slice * kSliceTokens;
         const long long g0 = (long long)cur_block * T + tok0;
         if (tok0 + kSliceTokens > T || g0 < first_visible) {
@@ -1232,7 +1304,7 @@ using namespace inq;
 // device, not to the process: a process that drives several GPUs (or several host threads) gets
 // one record per device ordinal, filled under a mutex on first use.
 constexpr int kMaxDevices = 64;
-constexpr int kKernelVariants = 16;
+constexpr int kKernelVariants = 20;   // 16 general instances, 4 of the whole-slice fast path
 struct DeviceState {
   int sm_count = 0;
   bool raised[kKernelVariants] = {};
@@ -1336,16 +1408,21 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   // block either way, so the work list does not depend on the choice
   const int sub = a->block_tokens <= 16 ? 1 : 2;
   typedef void (*kernel_t)(const DecodeParams);
-  static const kernel_t kernels[16] = {
-      decode_kernel<0, __half, false, 2>, decode_kernel<0, __half, true, 2>,
-      decode_kernel<0, __nv_bfloat16, false, 2>, decode_kernel<0, __nv_bfloat16, true, 2>,
-      decode_kernel<1, __half, false, 2>, decode_kernel<1, __half, true, 2>,
-      decode_kernel<1, __nv_bfloat16, false, 2>, decode_kernel<1, __nv_bfloat16, true, 2>,
-      decode_kernel<0, __half, false, 1>, decode_kernel<0, __half, true, 1>,
-      decode_kernel<0, __nv_bfloat16, false, 1>, decode_kernel<0, __nv_bfloat16, true, 1>,
-      decode_kernel<1, __half, false, 1>, decode_kernel<1, __half, true, 1>,
-      decode_kernel<1, __nv_bfloat16, false, 1>, decode_kernel<1, __nv_bfloat16, true, 1>};
-  const int which = (sub == 1 ? 8 : 0) + a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);
+  static const kernel_t kernels[20] = {
+      decode_kernel<0, __half, false, 2, false>, decode_kernel<0, __half, true, 2, false>,
+      decode_kernel<0, __nv_bfloat16, false, 2, false>, decode_kernel<0, __nv_bfloat16, true, 2, false>,
+      decode_kernel<1, __half, false, 2, false>, decode_kernel<1, __half, true, 2, false>,
+      decode_kernel<1, __nv_bfloat16, false, 2, false>, decode_kernel<1, __nv_bfloat16, true, 2, false>,
+      decode_kernel<0, __half, false, 1, false>, decode_kernel<0, __half, true, 1, false>,
+      decode_kernel<0, __nv_bfloat16, false, 1, false>, decode_kernel<0, __nv_bfloat16, true, 1, false>,
+      decode_kernel<1, __half, false, 1, false>, decode_kernel<1, __half, true, 1, false>,
+      decode_kernel<1, __nv_bfloat16, false, 1, false>, decode_kernel<1, __nv_bfloat16, true, 1, false>,
+      // whole slices, at least four per block, one salient group
+      decode_kernel<0, __half, true, 2, true>, decode_kernel<0, __nv_bfloat16, true, 2, true>,
+      decode_kernel<1, __half, true, 2, true>, decode_kernel<1, __nv_bfloat16, true, 2, true>};
+  const bool fast = a->n_pad == 16 && a->block_tokens % 32 == 0 && a->block_tokens >= 128;
+  const int which = fast ? 16 + a->layout * 2 + (a->dtype == INQ_F16 ? 0 : 1)
+                         : (sub == 1 ? 8 : 0) + a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);
   const kernel_t kernel = kernels[which];
   const int shared = smem_bytes(groups, sub);
   const int shared_limit = smem_bytes(4, sub);
