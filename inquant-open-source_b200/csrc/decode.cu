@@ -58,9 +58,10 @@ constexpr int kCtasPerSm = 3;                       // register budget: 168 per 
 constexpr int kRecordStride = 132;                  // floats per query head: acc[128], m, l, pad
 constexpr int kRecordFloats = 8 * kRecordStride;    // one partial record (8 query heads)
 constexpr int kQChunk = 36;                         // padded 32-float chunk of the staged query
-constexpr int kQBytes = 8 * 4 * kQChunk * 4 + 64;   // staged query and two factors per head
+constexpr int kQFragBytes = 8 * 32 * 8;              // the staged query as fp16 B fragments of the 8 K steps
+constexpr int kQBytes = 8 * 4 * kQChunk * 4 + 64 + kQFragBytes;   // staged query, two factors per head, fragments
 constexpr float kNegBig = -1.0e30f;
-constexpr int kWarpFixed = 2048 + 256 + 64 + 64 + 1024;  // per-warp scratch before the per-group parts
+constexpr int kWarpFixed = 2048 + 256 + 64 + 64 + 1024 + 256;  // per-warp scratch before the per-group parts
 constexpr float kRescaleSlack = 4.f;   // the running reference maximum may lag the true one by 2^4
 // start value of a gather accumulator: -(128 + 128/512) in units of 2^-13, so that it ends as
 // (code'_n - 128) + (code'_{n+8} - 128) / 512 (the fraction stays within +-1/4 even for a column
@@ -325,6 +326,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   float* qs = (float*)smem;                                             // 8 heads x 4 chunks x kQChunk
   float* qinv = qs + 8 * 4 * kQChunk;   // per head: softmax scale * log2(e) * 2^(exponent of max|q| - 12)
   float* qunscale = qinv + 8;           // per head: the power of two that restores the staged query
+  // the staged query once more as fp16 pairs in B-fragment order: entry [K step][lane (head r, chunk j)]
+  // holds channels (c, c+4 | c+1, c+5), c = 32j + 8 (step / 2) + 2 (step % 2), of query head r
+  unsigned char* qfrag = (unsigned char*)(qunscale + 8);
   unsigned char* warp_base = smem + kQBytes;
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
@@ -339,6 +343,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   unsigned char* wsrc = (unsigned char*)(wssc + 64);                    // channel of salient i
   unsigned char* wdon = wsrc + 64;                                      // its donor slot
   unsigned char* wmeta = wdon + 64;       // staged block metadata: K scales 512 B | role map 256 B | padding 256 B
+  unsigned char* wfrag = wmeta + 1024;    // a block's channel weights as fp16 pairs in B-fragment order: [K step][chunk] x 8 B
   unsigned char* wqsal = wb + kWarpFixed;                               // B fragments: query at salient channels
   unsigned char* wsel = wqsal + groups * 256;                           // B fragments: nibble selection
   unsigned short* wcell = (unsigned short*)(wsel + groups * 2048);      // selection cells written by the last fold (offsets into wsel)
@@ -387,6 +392,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   const int* const d_pages = SEQ(page_table);
   const int d_pool_pages = SEQ(pool_pages);
   const int first_visible = SEQ(first_visible);
+  // (loaded here, ahead of the barriers of the query staging, so that their latency overlaps it)
+  const int T = P.T;
+  const int spb = (T + kSliceTokens - 1) / kSliceTokens;   // packed slices per block
+  const int n_blocks = SEQ(n_blocks);
+  const int sink_tokens = SEQ(sink_tokens);
+  const int* const tail_dev = SEQ(tail_tokens_dev);
+  const int tail_tokens = tail_dev ? *tail_dev : SEQ(tail_tokens);
   const int g_valid = min(8, P.G - gt * 8);
   const long long q_head0 = (long long)h * P.G + gt * 8;
   const QT* qptr = (const QT*)SEQ(q);
@@ -434,12 +446,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     }
   }
   __syncthreads();
-  const int T = P.T;
-  const int spb = (T + kSliceTokens - 1) / kSliceTokens;   // packed slices per block
-  const int n_blocks = SEQ(n_blocks);
-  const int sink_tokens = SEQ(sink_tokens);
-  const int* const tail_dev = SEQ(tail_tokens_dev);
-  const int tail_tokens = tail_dev ? *tail_dev : SEQ(tail_tokens);
+  for (int e = threadIdx.x; e < 8 * 32; e += kThreads) {
+    const int ks = e >> 5, fr = (e & 31) >> 2, fj = e & 3;
+    const float* src = qs + (fr * 4 + fj) * kQChunk + 8 * (ks >> 1) + 2 * (ks & 1);
+    *(uint2*)(qfrag + e * 8) = make_uint2(pack_half2(src[0], src[4]), pack_half2(src[1], src[5]));
+  }
+  __syncthreads();
   const long long n_packed = (long long)n_blocks * spb;
   const int sink_slices = (sink_tokens + 15) >> 4, tail_slices = (tail_tokens + 15) >> 4;
   // packed slices are cut evenly over all warps of this (sequence, KV head); the few dense
@@ -721,25 +733,27 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           __syncwarp();
         }
         folded_block = cur_block;
-        float* const ff = (float*)meta;     // during a fold: slot weight per channel, over the staged K scales
-        float* const fk0 = ff + 128;        // during a fold: additive constant per channel, over role map and padding
-        // step 1: this lane owns channels 4*lane .. 4*lane+3
+        // step 1: this lane owns the four channels c0, c0+1, c0+4, c0+5 (c0 = 8 (lane / 2) + 2 (lane % 2)):
+        // exactly the channels of one B-fragment entry (K step 2 ((lane / 2) % 4) + lane % 2, chunk lane / 8)
         const unsigned char* meta_roles = meta + 512;
+        const int c0 = 8 * (lane >> 1) + 2 * (lane & 1);
         int role[4], sidx[4];
-        float scv[4], fv[4], kv[4];
+        float scv[4], fv[4];
         {
-          const float4 sc = *(const float4*)(meta + lane * 16);
-          scv[0] = sc.x; scv[1] = sc.y; scv[2] = sc.z; scv[3] = sc.w;
+          const float2 sa = *(const float2*)(meta + c0 * 4), sb = *(const float2*)(meta + c0 * 4 + 16);
+          scv[0] = sa.x; scv[1] = sa.y; scv[2] = sb.x; scv[3] = sb.y;
           if (MODE == 0) {
-            const unsigned bits = *(const unsigned*)(meta_roles + lane * 4);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) role[i] = (int)(signed char)((bits >> (8 * i)) & 0xff);
+            const unsigned ba = *(const unsigned short*)(meta_roles + c0), bb = *(const unsigned short*)(meta_roles + c0 + 4);
+            role[0] = (int)(signed char)(ba & 0xff);
+            role[1] = (int)(signed char)(ba >> 8);
+            role[2] = (int)(signed char)(bb & 0xff);
+            role[3] = (int)(signed char)(bb >> 8);
           } else {
-            const uint2 bits = *(const uint2*)(meta_roles + lane * 8);
-            role[0] = (int)(short)(bits.x & 0xffff);
-            role[1] = (int)(short)(bits.x >> 16);
-            role[2] = (int)(short)(bits.y & 0xffff);
-            role[3] = (int)(short)(bits.y >> 16);
+            const unsigned ba = *(const unsigned*)(meta_roles + c0 * 2), bb = *(const unsigned*)(meta_roles + c0 * 2 + 8);
+            role[0] = (int)(short)(ba & 0xffff);
+            role[1] = (int)(short)(ba >> 16);
+            role[2] = (int)(short)(bb & 0xffff);
+            role[3] = (int)(short)(bb >> 16);
           }
         }
         // the block's scales are brought into [0, 2) by a power of two
@@ -748,6 +762,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         const int ex_f = max(-60, min(60, (int)(top >> 23) - 127));
         const float down = __uint_as_float((unsigned)(127 - ex_f) << 23);
         bool bad = false;
+        float* const pads = (float*)(meta + 768);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           if (role[i] > 127 || role[i] < -1 - n_pad) {
@@ -757,32 +772,30 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           sidx[i] = -1;
           // the odd channel of a byte is its high nibble: 16 times the code as an fp16 subnormal
           fv[i] = scv[i] * ((i & 1) ? 0.0625f * down : down);
-          kv[i] = -8.f * scv[i];
           if (role[i] >= 0) {
             // salient: both of its slots leave the linear fold (its exact, dtype-rounded value is
             // rebuilt per token); its index in the padding list is recorded in its donor's role
             fv[i] = 0.f;
-            kv[i] = 0.f;
             const int idx = -(MODE == 0 ? (int)((const signed char*)meta_roles)[role[i]] : (int)((const short*)meta_roles)[role[i]]) - 2;
             if (idx >= 0 && idx < n_pad) sidx[i] = idx; else bad = true;
           } else if (role[i] < -1) {
             // donor: its slot holds the low nibble of a salient code; the reference stores the
-            // sampled mean as the channel's own value and rounds it to the model dtype
+            // sampled mean as the channel's own value and rounds it to the model dtype (in place:
+            // one donor per list entry)
             fv[i] = 0.f;
-            kv[i] = to_float<QT>(from_float<QT>(((const float*)(meta + 768))[-role[i] - 2]));
+            pads[-role[i] - 2] = to_float<QT>(from_float<QT>(pads[-role[i] - 2]));
           }
         }
         if (bad) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
+        *(uint2*)(wfrag + ((2 * ((lane >> 1) & 3) + (lane & 1)) * 4 + (lane >> 3)) * 8) =
+            make_uint2(pack_half2(fv[0], fv[2]), pack_half2(fv[1], fv[3]));
         // the selection cells of the last block are cleared through their recorded offsets
         for (int v = lane; v < 2 * n_pad; v += 32) *(unsigned short*)(wsel + wcell[v]) = 0;
-        __syncwarp();   // the staged metadata has been read: its area now takes the per-channel terms
-        *(float4*)(ff + 4 * lane) = make_float4(fv[0], fv[1], fv[2], fv[3]);
-        *(float4*)(fk0 + 4 * lane) = make_float4(kv[0], kv[1], kv[2], kv[3]);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           if (sidx[i] >= 0) {
             const int idx = sidx[i];
-            wsrc[idx] = (unsigned char)(4 * lane + i);
+            wsrc[idx] = (unsigned char)(c0 + (i & 1) + 4 * (i >> 1));
             wdon[idx] = (unsigned char)role[i];
             // in the units of the score accumulator (see the salient query entries below); the second
             // code of a gather column carries a factor 1/512
@@ -807,7 +820,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           *(unsigned short*)(wsel + cell) = (unsigned short)(0x7800 - (which + half) * 0x1000 - ((idx >> 3) & 1) * 0x2400);
           wcell[v] = (unsigned short)cell;
         }
-        __syncwarp();
         // query at the salient channels, as B fragments of the salient step.  The step adds straight
         // into the score accumulator, whose unit is alpha = qinv * 2^(24 + ex_f): the staged query
         // times 2^-12 and the salient value times 2^-(12 + ex_f) give exactly that unit, and both
@@ -826,35 +838,48 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
                                                                    (unsigned)qv[2] | ((unsigned)qv[3] << 16));
           }
         }
-        // step 2: thread (head r, chunk j) owns the 32 channels 32j..32j+31 of query head r
-        const float* qown = qs + (r * 4 + j) * kQChunk;
-        const float* fown = ff + 32 * j;
-        const float* kown = fk0 + 32 * j;
-        float cp0 = 0.f, cp1 = 0.f, cp2 = 0.f, cp3 = 0.f;
-#pragma unroll
-        for (int k8 = 0; k8 < 4; ++k8) {
-          const float4 fa4 = *(const float4*)(fown + 8 * k8), fb4 = *(const float4*)(fown + 8 * k8 + 4);
-          const float4 ka4 = *(const float4*)(kown + 8 * k8), kb4 = *(const float4*)(kown + 8 * k8 + 4);
-          const float4 qa4 = *(const float4*)(qown + 8 * k8), qb4 = *(const float4*)(qown + 8 * k8 + 4);
-          cp0 = fmaf(qa4.x, ka4.x, cp0); cp1 = fmaf(qa4.y, ka4.y, cp1); cp2 = fmaf(qa4.z, ka4.z, cp2); cp3 = fmaf(qa4.w, ka4.w, cp3);
-          cp0 = fmaf(qb4.x, kb4.x, cp0); cp1 = fmaf(qb4.y, kb4.y, cp1); cp2 = fmaf(qb4.z, kb4.z, cp2); cp3 = fmaf(qb4.w, kb4.w, cp3);
-          // K steps 2*k8 and 2*k8+1: channels (0,4 | 1,5) and (2,6 | 3,7) of this group of eight
-          *(uint2*)(wW + ((2 * k8) * 32 + lane) * 8) = make_uint2(pack_half2(qa4.x * fa4.x, qb4.x * fb4.x), pack_half2(qa4.y * fa4.y, qb4.y * fb4.y));
-          *(uint2*)(wW + ((2 * k8 + 1) * 32 + lane) * 8) = make_uint2(pack_half2(qa4.z * fa4.z, qb4.z * fb4.z), pack_half2(qa4.w * fa4.w, qb4.w * fb4.w));
+        // the donors' constant values times the query: lane (r, j) sums the list entries r, r + 8, ...
+        // for query heads 2j and 2j+1, the eight rows are then added up
+        float dterm0 = 0.f, dterm1 = 0.f;
+        for (int i = r; i < n_pad; i += 8) {
+          const int c = wdon[i] & 127;
+          const float pad = pads[i];
+          const float* qd = qs + (2 * j * 4 + (c >> 5)) * kQChunk + (c & 31);
+          dterm0 = fmaf(qd[0], pad, dterm0);
+          dterm1 = fmaf(qd[4 * kQChunk], pad, dterm1);
         }
-        float cpart = (cp0 + cp1) + (cp2 + cp3);
-        cpart += __shfl_xor_sync(0xffffffffu, cpart, 1);
-        cpart += __shfl_xor_sync(0xffffffffu, cpart, 2);
-        // raw score -> base-2 score of head r: undo 2^-24 (subnormal nibbles), the scale exponent
-        // and the query factor
-        const float qf = qinv[r];
-        const float inv = qf * __uint_as_float((unsigned)(127 + 24 + ex_f) << 23);
-        cpart *= qf;
-        // score columns of this thread are query heads 2j and 2j+1
-        alpha[0] = __shfl_sync(0xffffffffu, inv, (2 * j) * 4);
-        alpha[1] = __shfl_sync(0xffffffffu, inv, (2 * j + 1) * 4);
-        beta[0] = __shfl_sync(0xffffffffu, cpart, (2 * j) * 4);
-        beta[1] = __shfl_sync(0xffffffffu, cpart, (2 * j + 1) * 4);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+          dterm0 += __shfl_xor_sync(0xffffffffu, dterm0, off);
+          dterm1 += __shfl_xor_sync(0xffffffffu, dterm1, off);
+        }
+        // step 2: the B fragments of the eight K steps are the staged query (fp16 pairs in fragment
+        // order) times the block's channel weights, one HMUL2 per register; the same fragments
+        // against an A operand of ones (1 for a low nibble, 16 for a high one) give the sum of the
+        // weights per query head, i.e. the contribution of the codes' zero point 8
+        float wsum[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          const unsigned qf_addr = launder(smem_addr(qfrag) + lane * 8), ff_addr = launder(smem_addr(wfrag) + j * 8);
+#define INQ_FOLD(KS)                                                                                       \
+  {                                                                                                        \
+    const uint2 qq = lds64<(KS) * 256>(qf_addr), ff2 = lds64<(KS) * 32>(ff_addr);                          \
+    const uint2 ww = make_uint2(hmul2_bits(qq.x, ff2.x), hmul2_bits(qq.y, ff2.y));                         \
+    *(uint2*)(wW + ((KS) * 32 + lane) * 8) = ww;                                                           \
+    mma_f16(wsum, 0x00010001u, 0x00010001u, 0x00100010u, 0x00100010u, ww.x, ww.y);                         \
+  }
+          INQ_FOLD(0) INQ_FOLD(1) INQ_FOLD(2) INQ_FOLD(3) INQ_FOLD(4) INQ_FOLD(5) INQ_FOLD(6) INQ_FOLD(7)
+#undef INQ_FOLD
+        }
+        // raw score -> base-2 score: undo 2^-24 (subnormal nibbles), the scale exponent and the query
+        // factor; score columns of this thread are query heads 2j and 2j+1
+        {
+          const float2 qf = *(const float2*)(qinv + 2 * j);
+          const float up = __uint_as_float((unsigned)(127 + 24 + ex_f) << 23);
+          alpha[0] = qf.x * up;
+          alpha[1] = qf.y * up;
+          beta[0] = fmaf(-8.f * alpha[0], wsum[0], qf.x * dterm0);
+          beta[1] = fmaf(-8.f * alpha[1], wsum[1], qf.y * dterm1);
+        }
         bm[0] = beta[0] - m_run[0];
         bm[1] = beta[1] - m_run[1];
         need_weights = false;
