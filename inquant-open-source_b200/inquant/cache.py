@@ -79,6 +79,7 @@ class _Layer:
     key_blocks: list = field(default_factory=list)
     value_blocks: list = field(default_factory=list)
     packed_nbytes: int = 0
+    retired_tail: tuple | None = None               # the tail buffers replaced by the last seal
 
     @property
     def sink_key(self):
@@ -109,6 +110,21 @@ class PackedAttentionView:
     residual_key: torch.Tensor
     residual_value: torch.Tensor
     seq_length: int
+
+
+_storage_use_count = getattr(torch._C, "_storage_Use_Count", None)
+
+
+def _use_count(tensor: torch.Tensor) -> int:
+    return _storage_use_count(tensor.untyped_storage()._cdata)
+
+
+_SOLE_USE_COUNT = _use_count(torch.empty(1)) if _storage_use_count is not None else -1
+
+
+def _sole_owner(tensor: torch.Tensor) -> bool:
+    """True when no other tensor (a view handed out earlier, a decode state) shares the storage."""
+    return _storage_use_count is not None and tensor._base is None and _use_count(tensor) <= _SOLE_USE_COUNT
 
 
 def _tensor_bytes(tensor: torch.Tensor | None) -> int:
@@ -352,6 +368,15 @@ class InQuantCache(_HFCache):
         return (torch.empty(shape, dtype=layer.dtype, device=layer.device),
                 torch.empty(shape, dtype=layer.dtype, device=layer.device))
 
+    def _tail_buffers_for(self, layer: _Layer, tokens: int):
+        """Tail buffers for the tokens left over by a seal: the pair retired by the previous seal when
+        it has the size and no tensor but the layer's own refers to its storage, else a new pair."""
+        retired, layer.retired_tail = layer.retired_tail, None
+        if retired is not None and retired[0] is not None and retired[0].shape[2] == tokens and all(
+                _sole_owner(t) for t in retired):
+            return retired
+        return self._new_buffers(layer, tokens)
+
     def _write_token(self, layer: _Layer, keys, values, sink_position: int) -> bool:
         """One-kernel write of a single token into the tail (and the sink); False when the
         layout does not meet the kernel's 16-byte alignment rules."""
@@ -410,18 +435,27 @@ class InQuantCache(_HFCache):
             layer.seq_length += 1
             return tail
 
-        # general path: build new storage first so that a failing codec call leaves the layer intact
         tail = None
-        if want_tail:
+        pending_key = pending_value = None
+        if (new_tokens == 1 and blocks == 1 and not take_sink and layer.tail_key_buffer is not None
+                and layer.tail_count == layer.tail_key_buffer.shape[2] - 1 and self._write_token(layer, keys, values, -1)):
+            # decode step that seals a block: the token completes the tail buffer in place (views
+            # handed out earlier end before it), so old tail + new token is the buffer itself
+            pending_key, pending_value = layer.tail_key_buffer, layer.tail_value_buffer
+            if want_tail:
+                tail = (pending_key, pending_value)
+        # general path: build new storage first so that a failing codec call leaves the layer intact
+        elif want_tail:
             tail = ((keys, values) if not layer.tail_count else
                     (torch.cat((layer.residual_key, keys), dim=2), torch.cat((layer.residual_value, values), dim=2)))
-        pending_key, pending_value = keys[:, :, take_sink:], values[:, :, take_sink:]
-        if layer.tail_count:
-            if want_tail and not take_sink:
-                pending_key, pending_value = tail
-            else:
-                pending_key = torch.cat((layer.residual_key, pending_key), dim=2)
-                pending_value = torch.cat((layer.residual_value, pending_value), dim=2)
+        if pending_key is None:
+            pending_key, pending_value = keys[:, :, take_sink:], values[:, :, take_sink:]
+            if layer.tail_count:
+                if want_tail and not take_sink:
+                    pending_key, pending_value = tail
+                else:
+                    pending_key = torch.cat((layer.residual_key, pending_key), dim=2)
+                    pending_value = torch.cat((layer.residual_value, pending_value), dim=2)
         # Both encoders are launched before either finite check is read: the key and value kernels
         # run back to back while the host builds the block views and the new tail, and one read of
         # the status word (one synchronisation instead of two) decides before any state changes.
@@ -435,8 +469,9 @@ class InQuantCache(_HFCache):
                                                    cfg.value_group_size)
         offset = blocks * cfg.block_size
         remainder = pending_key.shape[2] - offset
-        # a new tail buffer: views handed out earlier keep the old one alive and unchanged
-        tail_key_buffer, tail_value_buffer = self._new_buffers(layer, max(capacity, remainder))
+        # a new tail buffer: views handed out earlier keep the old one alive and unchanged.  The
+        # buffer retired by the previous seal is taken again when nothing else refers to it any more.
+        tail_key_buffer, tail_value_buffer = self._tail_buffers_for(layer, max(capacity, remainder))
         if remainder:
             tail_key_buffer[:, :, :remainder].copy_(pending_key[:, :, offset:])
             tail_value_buffer[:, :, :remainder].copy_(pending_value[:, :, offset:])
@@ -451,6 +486,10 @@ class InQuantCache(_HFCache):
             layer.sink_key_buffer[:, :, layer.sink_count:layer.sink_count + take_sink].copy_(keys[:, :, :take_sink])
             layer.sink_value_buffer[:, :, layer.sink_count:layer.sink_count + take_sink].copy_(values[:, :, :take_sink])
         layer.sink_count += take_sink
+        # the next seal takes the retired pair; a first call (prefill) provides one, so that no decode
+        # step has to wait for the allocator
+        layer.retired_tail = ((layer.tail_key_buffer, layer.tail_value_buffer) if layer.tail_key_buffer is not None
+                              else self._new_buffers(layer, capacity))
         layer.tail_key_buffer, layer.tail_value_buffer, layer.tail_count = tail_key_buffer, tail_value_buffer, remainder
         layer.key_blocks.extend(new_keys)
         layer.value_blocks.extend(new_values)

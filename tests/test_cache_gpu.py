@@ -117,6 +117,35 @@ def test_append_snapshot_matches_update_across_block_boundary():
                                       ['payload_nbytes', 'metadata_nbytes', 'sink_nbytes', 'residual_nbytes', 'auxiliary_nbytes'])
 
 
+def test_tail_views_survive_later_seals():
+    """A sealing decode step completes the tail buffer in place and takes over the buffer retired by
+    the seal before it, but only when no view handed out earlier still refers to that buffer."""
+    CacheConfig, InQuantCache, CodecConfig, _ = _mods()
+    cfg = CacheConfig(CodecConfig(salient_fraction=.125), block_size=8, residual_length=4, sink_tokens=2, value_bits=2)
+    key, value = to_device(_randn(31, (1, 2, 70, 128))), to_device(_randn(32, (1, 2, 70, 128)))
+    for hold in (True, False):
+        cache = InQuantCache(cfg)
+        cache.update(key[:, :, :9], value[:, :, :9], 0)
+        kept, buffers = [], set()
+        for token in range(9, 70):
+            view = cache.append_for_attention(key[:, :, token:token + 1], value[:, :, token:token + 1], 0)
+            # sink | dequantised blocks | tail of every view is the history up to and including the token
+            tail_start = token + 1 - view.residual_key.shape[2]
+            assert torch.equal(view.residual_key, key[:, :, tail_start:token + 1])
+            assert torch.equal(view.residual_value, value[:, :, tail_start:token + 1])
+            buffers.add(cache._layers[0].tail_key_buffer.data_ptr())
+            if hold:
+                kept.append((tail_start, token + 1, view.residual_key, view.residual_value))
+        for start, stop, k, v in kept:
+            assert torch.equal(k, key[:, :, start:stop]) and torch.equal(v, value[:, :, start:stop])
+        seals = len(cache._layers[0].key_blocks)
+        assert seals >= 6
+        # held views pin every retired buffer; without them two buffers alternate
+        assert len(buffers) == (seals + 1 if hold else 2) or not hold and len(buffers) <= 3
+        expected, _ = _oracle_materialize(to_numpy(key), 2, 8, 4, .125, "neighbors")
+        assert np.array_equal(to_numpy(cache.materialize(0)[0]), expected)
+
+
 def test_append_while_sink_is_still_filling():
     CacheConfig, InQuantCache, CodecConfig, _ = _mods()
     cfg = CacheConfig(sink_tokens=4, block_size=8, residual_length=2)
