@@ -1060,10 +1060,25 @@ def run_split_kv(args, torch, dist, device, world, rank):
             return float(worst[0]), float(total[1]), split.exchange
         return ms, float(local_bytes), split.exchange
 
-    ms, total_bytes, exchange = time_split("auto", check=True)
     record_bytes = LAYERS * Q_HEADS * 130 * 4
     extra = {}
-    if exchange == "p2p":
+    launch = "CUDA graph of decode (append fused in on the tail owner) + exchange + merge" if use_graph else "eager"
+    exchange = None
+    if world > 1:
+        try:
+            ms, total_bytes, exchange = time_split("fused", check=True)
+        except RuntimeError:
+            # every rank raises alike (the mappings are agreed on collectively), so all fall back together
+            exchange = None
+    if exchange is None:
+        ms, total_bytes, exchange = time_split("auto", check=True)
+    if exchange == "fused":
+        how = (f"inside the decode launch: the CTA that merges a (layer, KV head) pair stores its records ({record_bytes} B per rank "
+               "and step in all) into every peer's inbox over NVLink peer memory, signals, waits (bounded) and merges all ranks' records")
+        launch = "CUDA graph of ONE launch per rank (decode with the append fused in on the tail owner and the exchange in its merge)" if use_graph else "eager, one launch"
+        extra["us_per_step_separate_exchange_kernel"] = round(time_split("p2p")[0] * 1e3, 2)
+        extra["us_per_step_nccl_all_gather"] = round(time_split("nccl")[0] * 1e3, 2)
+    elif exchange == "p2p":
         how = (f"peer memory: one kernel per rank stores its {record_bytes} B of records into every peer's inbox over "
                "NVLink, signals, waits (bounded) and merges")
         extra["us_per_step_nccl_all_gather"] = round(time_split("nccl")[0] * 1e3, 2)
@@ -1075,7 +1090,7 @@ def run_split_kv(args, torch, dist, device, world, rank):
     return {"context": context, "blocks_per_rank": end - start, "us_per_step": round(ms * 1e3, 2),
             "aggregate_gbs": round(total_bytes / (ms * 1e-3) / 1e9, 1),
             "per_gpu_hbm_frac": round(total_bytes / world / (ms * 1e-3) / 1e9 / peak, 4),
-            "exchange": how, "launch": "CUDA graph of decode (append fused in on the tail owner) + exchange + merge" if use_graph else "eager",
+            "exchange": how, "launch": launch,
             "steps": steps, "parity": parity, **extra}
 
 

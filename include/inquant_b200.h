@@ -224,6 +224,27 @@ typedef struct {
   int32_t reserved;
 } inq_decode_seq_t;
 
+/* Split-KV across the GPUs of one node inside the decode launch itself (no counterpart in the
+ * reference, which is single-GPU): the CTA that merges this rank's parts of a pair
+ * (sequence, KV head, tile of 8 query heads) stores the pair's un-normalised record straight into
+ * every peer's inbox over NVLink peer memory, publishes it with a release store after a
+ * system-scope fence, waits for the peers' records of the same pair in its own inbox -- a bounded
+ * wait: after `spin_limit` polls it sets INQ_STATUS_WAIT_TIMEOUT and writes zero rows -- and merges
+ * all records in rank order (the cross-rank form of triton_attention.py:168-181), so every rank
+ * writes the same `output`.  The inboxes are those of inq_exchange_merge (inq_exchange_inbox_bytes,
+ * inq_peer_buffer_create / _open); an inbox serves either that entry point or this one, not both,
+ * and here a flag word stands for a pair: at most 512 pairs per launch.  Every rank launches the
+ * same steps in the same order; the launch needs all its CTAs resident (it always sizes its grid
+ * so) and other work on the GPU only delays the wait.  The struct lives in DEVICE memory. */
+typedef struct {
+  void* inboxes[8];       /* inbox of every rank as mapped into this process; [rank] is the own one */
+  int32_t* epoch;         /* device, zero before the first step: [0] = steps completed, advanced by the launch */
+  int64_t n_rows;         /* n_seq * kv_heads * q_per_kv, the same on every rank */
+  int32_t world, rank;
+  int32_t spin_limit;     /* polls of >= 100 ns before a wait gives up; 0 = default (a fraction of a second) */
+  int32_t reserved;
+} inq_decode_exchange_t;
+
 typedef struct {
   int32_t n_seq;
   const inq_decode_seq_t* seqs_device; /* [n_seq] in device memory, or NULL when n_seq == 1 */
@@ -247,6 +268,9 @@ typedef struct {
   int32_t* counters;        /* scratch: n_pairs + 1 ints, ZERO on entry, left zero on exit */
   int32_t* status;          /* device status word */
   int32_t fused_append;     /* 1: every sequence's new_key / new_value token is appended by this launch */
+  const inq_decode_exchange_t* exchange_device; /* optional, DEVICE memory: exchange and merge the records of
+                                                 * every pair with the peer GPUs inside this launch;
+                                                 * `partial_output` of the sequences is then ignored */
 } inq_decode_args_t;
 int inq_decode_attention(const inq_decode_args_t* args /* host */, inq_stream_t stream);
 /* The same decode step for callers that cannot allocate device memory (a serving engine that

@@ -37,6 +37,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "exchange.cuh"
 
 namespace inq {
 
@@ -108,7 +109,17 @@ struct DecodeParams {
   int* counters;
   int* status;
   int fused_append;
+  const struct ExchangeView* exchange;   // device memory; set when the launch exchanges its records with the peer GPUs
 };
+
+// mirrors inq_decode_exchange_t
+struct ExchangeView {
+  unsigned char* inbox[kExMaxWorld];
+  int* epoch;
+  long long n_rows;
+  int world, rank, spin_limit, reserved;
+};
+static_assert(sizeof(ExchangeView) == sizeof(inq_decode_exchange_t), "ExchangeView must mirror inq_decode_exchange_t");
 
 struct BlockPtrs {
   const unsigned char *kp, *ks, *kr, *kpad, *vp, *vs, *vo;
@@ -308,6 +319,94 @@ __device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned
     }
   }
 }
+
+// ------------------------------------------------------------------------------------------ exchange of a pair
+// Split-KV across GPUs, run by the CTA that has just merged this rank's parts of a pair: the
+// pair's un-normalised record (eight channels per thread in `oa`, `ob`; `top`, `l` of the row) is
+// stored into every peer's inbox over NVLink peer memory, published per pair with a release store
+// after a system-scope fence, the peers' records of the same pair are awaited in this rank's own
+// inbox (bounded: a wait that runs out raises INQ_STATUS_WAIT_TIMEOUT and zeroes the rows) and
+// all records are merged in rank order, so every rank writes bit-identical output rows.
+// All threads of the CTA call it; `active` marks those that hold a row.  The flag word of a pair
+// is indexed by the pair, the step number comes from the epoch word that the launch advances
+// when its last CTA leaves.
+template <typename QT>
+__device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long long row, int c8, bool active,
+                                           float4 oa, float4 ob, float top, float l, QT* out, int* status) {
+  __shared__ int s_failed;
+  const int tid = threadIdx.x;
+  const int world = X->world, me = X->rank;
+  const long long n_rows = X->n_rows;
+  const int step = X->epoch[0] + 1;
+  const int parity = step & 1;
+  unsigned char* const own = X->inbox[me];
+  if (tid == 0) s_failed = 0;
+  if (active) {
+    for (int p = 0; p < world; ++p) {
+      if (p == me) continue;
+      float* const dst = ex_data(X->inbox[p], parity, me, world, n_rows) + row * kExRowFloats;
+      *(float2*)(dst + c8) = make_float2(oa.x, oa.y);
+      *(float2*)(dst + c8 + 2) = make_float2(oa.z, oa.w);
+      *(float2*)(dst + c8 + 4) = make_float2(ob.x, ob.y);
+      *(float2*)(dst + c8 + 6) = make_float2(ob.z, ob.w);
+      if (c8 == 0) *(float2*)(dst + 128) = make_float2(top, l);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < world && tid != me) {
+    st_release_sys(ex_flag(X->inbox[tid], parity, me, pair), step);
+    const int* const flag = ex_flag(own, parity, tid, pair);
+    const int limit = X->spin_limit > 0 ? X->spin_limit : kExDefaultSpin;
+    int polls = 0;
+    while (ld_acquire_sys(flag) - step < 0) {
+      if (++polls > limit) {
+        atomicOr(&s_failed, 1);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+  const bool failed = s_failed != 0;
+  if (failed && tid == 0) atomicOr(status, INQ_STATUS_WAIT_TIMEOUT);
+  if (active) {
+    float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, norm = 1.f;
+    if (!failed) {
+      float2 ml[kExMaxWorld];
+      float all_top = top;
+#pragma unroll
+      for (int p = 0; p < kExMaxWorld; ++p) {
+        if (p < world && p != me) {
+          ml[p] = __ldcg((const float2*)(ex_data(own, parity, p, world, n_rows) + row * kExRowFloats + 128));
+          all_top = fmaxf(all_top, ml[p].x);
+        }
+      }
+      norm = 0.f;
+#pragma unroll
+      for (int p = 0; p < kExMaxWorld; ++p) {
+        if (p >= world) continue;
+        if (p == me) {
+          const float w = fast_exp2(top - all_top);
+          norm = fmaf(l, w, norm);
+          o[0] = fmaf(oa.x, w, o[0]); o[1] = fmaf(oa.y, w, o[1]); o[2] = fmaf(oa.z, w, o[2]); o[3] = fmaf(oa.w, w, o[3]);
+          o[4] = fmaf(ob.x, w, o[4]); o[5] = fmaf(ob.y, w, o[5]); o[6] = fmaf(ob.z, w, o[6]); o[7] = fmaf(ob.w, w, o[7]);
+        } else {
+          const float* rec = ex_data(own, parity, p, world, n_rows) + row * kExRowFloats + c8;
+          const float w = fast_exp2(ml[p].x - all_top);
+          const float2 a = __ldcg((const float2*)rec), b = __ldcg((const float2*)rec + 1);
+          const float2 c = __ldcg((const float2*)rec + 2), d = __ldcg((const float2*)rec + 3);
+          norm = fmaf(ml[p].y, w, norm);
+          o[0] = fmaf(a.x, w, o[0]); o[1] = fmaf(a.y, w, o[1]); o[2] = fmaf(b.x, w, o[2]); o[3] = fmaf(b.y, w, o[3]);
+          o[4] = fmaf(c.x, w, o[4]); o[5] = fmaf(c.y, w, o[5]); o[6] = fmaf(d.x, w, o[6]); o[7] = fmaf(d.y, w, o[7]);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) out[k] = from_float<QT>(failed ? 0.f : o[k] / norm);
+  }
+}
+
 
 // ------------------------------------------------------------------------------------------ the kernel
 // FAST: blocks of whole 32-token slices, at least four per block, exactly one group of 16 salient
@@ -1248,6 +1347,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     }
     __syncthreads();
     const int g = threadIdx.x >> 4, c8 = (threadIdx.x & 15) * 8;   // kThreads = 128: 8 heads x 16 threads
+    float4 ex_a = make_float4(0.f, 0.f, 0.f, 0.f), ex_b = ex_a;
     if (g < g_valid) {
       float o[8];
 #pragma unroll
@@ -1276,7 +1376,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         o[0] = fmaf(va.x, wt, o[0]); o[1] = fmaf(va.y, wt, o[1]); o[2] = fmaf(va.z, wt, o[2]); o[3] = fmaf(va.w, wt, o[3]);
         o[4] = fmaf(vb.x, wt, o[4]); o[5] = fmaf(vb.y, wt, o[5]); o[6] = fmaf(vb.z, wt, o[6]); o[7] = fmaf(vb.w, wt, o[7]);
       }
-      if (partial) {
+      if (P.exchange) {
+        // handed to the exchange below (every thread of the CTA takes part in it)
+        ex_a = make_float4(o[0], o[1], o[2], o[3]);
+        ex_b = make_float4(o[4], o[5], o[6], o[7]);
+      } else if (partial) {
         // this rank's share of a sequence split across GPUs: keep the record un-normalised
         float* rec_out = partial + (q_head0 + g) * 130;
 #pragma unroll
@@ -1292,12 +1396,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         for (int k = 0; k < 8; ++k) out[k] = from_float<QT>(o[k] / inv);
       }
     }
+    if (P.exchange) {
+      const bool active = g < g_valid;
+      exchange_pair<QT>(P.exchange, pair, (long long)seq * P.H * P.G + q_head0 + g, c8, active, ex_a, ex_b,
+                        active ? mtop[g] : 0.f, active ? norm[g] : 1.f, (QT*)SEQ(out) + (q_head0 + g) * 128 + c8, P.status);
+    }
   }
   __syncthreads();   // shared scratch is reused by the next pair of this CTA
   }  // pairs of this CTA
-  if (P.fused_append) {
-    // Every CTA has read the tail lengths of the pairs it visited by the time it arrives here; the
-    // last one to arrive advances the device-side lengths for the next step.
+  if (P.fused_append || P.exchange) {
+    // Every CTA has read the tail lengths of the pairs it visited (and the step number of the
+    // exchange) by the time it arrives here; the last one to arrive advances them for the next step.
     __shared__ int s_grid_last;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -1308,10 +1417,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     }
     __syncthreads();
     if (s_grid_last) {
-      for (int s = threadIdx.x; s < P.n_seq; s += kThreads) {
-        const SeqDesc* d = P.seqs ? P.seqs + s : &P.one;
-        if (d->new_k && d->tail_tokens_dev) atomicAdd((int*)d->tail_tokens_dev, 1);
+      if (P.fused_append) {
+        for (int s = threadIdx.x; s < P.n_seq; s += kThreads) {
+          const SeqDesc* d = P.seqs ? P.seqs + s : &P.one;
+          if (d->new_k && d->tail_tokens_dev) atomicAdd((int*)d->tail_tokens_dev, 1);
+        }
       }
+      if (P.exchange && threadIdx.x == 0) P.exchange->epoch[0] += 1;
     }
   }
 }
@@ -1497,6 +1609,8 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   P.counters = a->counters;
   P.status = a->status;
   P.fused_append = a->fused_append ? 1 : 0;
+  P.exchange = (const ExchangeView*)a->exchange_device;
+  if (P.exchange && plan.n_pairs > kExMaxChunks) return INQ_ERR_CAPACITY;   // one flag word per pair
   kernel<<<(unsigned)plan.n_ctas, kThreads, shared, (cudaStream_t)stream_>>>(P);
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;

@@ -23,16 +23,12 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "exchange.cuh"
 
 namespace inq {
 
-constexpr int kExMaxWorld = 8;
 constexpr int kExThreads = 256;
-constexpr int kExMaxChunks = 512;                 // CTAs per rank; all must be resident at once
-constexpr int kExRowFloats = 130;                 // acc[128], m (base-2 units), l
 constexpr int kExRowPairs = kExRowFloats / 2;     // a row as 8-byte pairs
-constexpr long long kExFlagBytes = 2ll * kExMaxWorld * kExMaxChunks * 4;   // [parity][src][chunk]
-constexpr int kExDefaultSpin = 1 << 21;           // polls of >= 100 ns: gives up after a fraction of a second
 
 struct ExchangeRank {
   const float* local;
@@ -48,26 +44,11 @@ struct ExchangeParams {
   long long n_rows;
 };
 
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ float ex_exp2(float x) {   // the approximation inq_merge_partials uses
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ int* ex_flag(unsigned char* inbox, int parity, int src, int chunk) {
-  return (int*)inbox + ((long long)parity * kExMaxWorld + src) * kExMaxChunks + chunk;
-}
-__device__ __forceinline__ float* ex_data(unsigned char* inbox, int parity, int src, int world, long long n_rows) {
-  return (float*)(inbox + kExFlagBytes) + ((long long)parity * world + src) * n_rows * kExRowFloats;
-}
-
 template <typename QT>
 __global__ void __launch_bounds__(kExThreads, 4) exchange_merge_kernel(const __grid_constant__ ExchangeParams P) {
   const ExchangeRank& R = P.ranks[blockIdx.y];

@@ -65,7 +65,13 @@ class DecodeArgs(ctypes.Structure):
                 ("page_bytes", c_int64), ("page_offsets", c_int64 * 6),
                 ("pair_starts", c_void_p), ("total_units", c_int64), ("uniform_blocks", c_int32),
                 ("partials", c_void_p), ("partials_floats", c_int64), ("counters", c_void_p), ("status", c_void_p),
-                ("fused_append", c_int32)]
+                ("fused_append", c_int32), ("exchange_device", c_void_p)]
+
+
+class DecodeExchange(ctypes.Structure):
+    """``inq_decode_exchange_t``; the kernel reads it from device memory."""
+    _fields_ = [("inboxes", c_void_p * 8), ("epoch", c_void_p), ("n_rows", c_int64),
+                ("world", c_int32), ("rank", c_int32), ("spin_limit", c_int32), ("reserved", c_int32)]
 
 
 class WritePagesArgs(ctypes.Structure):

@@ -259,6 +259,15 @@ class DecodeBatch:
         self._status_pointer = N.status_word(self.device).data_ptr()
         self._graph = None
 
+    def use_exchange(self, view: torch.Tensor | None) -> None:
+        """Exchange and merge every pair's record with the peer GPUs inside the decode launch
+        (``inq_decode_exchange_t`` in device memory, e.g. ``PeerExchange.decode_view()``); ``None``
+        switches it off.  ``outputs`` then holds the rows merged over all ranks."""
+        self._exchange_view = view
+        pointer = None if view is None else view.data_ptr()
+        self._decode_args.exchange_device = pointer
+        self._step_args.exchange_device = pointer
+
     def _launch_append(self) -> None:
         rc = N.library().inq_append_token_batch(self._append_records.data_ptr(), len(self.sequences),
                                                 self._status_pointer, N.stream_pointer(self.device))

@@ -13,6 +13,10 @@ log-sum-exp rule (the cross-rank form of ``triton_attention.py:168-181``).  Two 
             waits (bounded) for the peers' chunks and merges them (``inq_exchange_merge``);
 ``"nccl"``  one ``all_gather`` followed by the merge kernel ``inq_merge_partials``.
 
+``"fused"`` no launch of its own: the decode kernel's merging CTA of every (layer, KV head, head tile)
+            stores that pair's record into the peers' inboxes, awaits theirs (bounded) and merges them
+            (``inq_decode_exchange_t``), so a step is ONE launch per rank;
+
 ``"auto"`` takes the first when every rank sits on the same host and the mappings can be made,
 else the second.  Nothing else is exchanged: encode and append are block-local.  The reference
 has no multi-GPU path; this module is new.
@@ -119,6 +123,18 @@ class PeerExchange:
         self._inboxes = (ctypes.c_void_p * self.world)(*pointers)
         self._epoch = torch.zeros(2, dtype=torch.int32, device=device)
 
+    def decode_view(self) -> torch.Tensor:
+        """This exchange as the decode kernel reads it (``inq_decode_exchange_t`` in device memory): the
+        kernel then pushes, awaits and merges the records pair by pair itself.  An exchange serves
+        either ``run`` or the decode kernel, not both: they number their flag words differently."""
+        view = N.DecodeExchange()
+        for peer in range(self.world):
+            view.inboxes[peer] = self._inboxes[peer]
+        view.epoch, view.n_rows = self._epoch.data_ptr(), self.n_rows
+        view.world, view.rank, view.spin_limit = self.world, self.rank, self.spin_limit
+        self._view = torch.frombuffer(bytearray(bytes(view)), dtype=torch.uint8).to(self.device)
+        return self._view
+
     def run(self, local: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """``local`` [n_rows, 130] fp32 (this rank's records) -> ``out`` [n_rows, 128] fp16/bf16, merged
         over all ranks."""
@@ -152,26 +168,36 @@ class SplitKVDecode:
 
     def __init__(self, sequences: list[SequenceState], q_heads: int, group=None, dtype=torch.bfloat16,
                  owns_tail: bool | None = None, exchange: str = "auto"):
-        if exchange not in ("auto", "p2p", "nccl"):
-            raise ValueError("exchange must be 'auto', 'p2p' or 'nccl'")
+        if exchange not in ("auto", "p2p", "nccl", "fused"):
+            raise ValueError("exchange must be 'auto', 'p2p', 'nccl' or 'fused'")
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.owns_tail = (self.rank == self.world - 1) if owns_tail is None else owns_tail
-        self.batch = DecodeBatch(sequences, q_heads, dtype, partials_only=True)
+        self.fused = exchange == "fused" and self.world > 1
+        self.batch = DecodeBatch(sequences, q_heads, dtype, partials_only=not self.fused)
         n = len(sequences)
-        self.gathered = torch.empty((self.world, n * q_heads, 130), dtype=torch.float32, device=self.batch.device)
-        self.outputs = torch.empty((n, q_heads, 128), dtype=dtype, device=self.batch.device)
         self.peers = None
         if self.world > 1 and exchange != "nccl":
             try:
                 self.peers = PeerExchange(n * q_heads, self.batch.device, group)
             except RuntimeError:
-                if exchange == "p2p":
+                if exchange in ("p2p", "fused"):
                     raise
+        if self.fused:
+            # ONE launch per step: the decode kernel stores every pair's record into the peers'
+            # inboxes, awaits theirs (bounded) and merges them itself
+            self.batch.use_exchange(self.peers.decode_view())
+            self.outputs = self.batch.outputs
+            self.exchange = "fused"
+            return
+        self.gathered = torch.empty((self.world, n * q_heads, 130), dtype=torch.float32, device=self.batch.device)
+        self.outputs = torch.empty((n, q_heads, 128), dtype=dtype, device=self.batch.device)
         self.exchange = "p2p" if self.peers is not None else "nccl"
 
     def _exchange_and_merge(self) -> None:
+        if self.fused:
+            return
         local = self.batch.partial_records.view(-1, 130)
         if self.peers is not None:
             self.peers.run(local, self.outputs.view(-1, 128))

@@ -1,6 +1,7 @@
 """Worker of tests/test_split_kv_multigpu.py: run under torch.distributed.run with one process
 per GPU.  One request is sharded by sequence over the ranks; the split decode must reproduce the
-unsplit decode with both exchanges (peer memory and all-gather), eagerly and from a CUDA graph."""
+unsplit decode with every exchange (all-gather, peer memory, peer memory inside the decode launch),
+eagerly and from a CUDA graph."""
 import os
 import sys
 
@@ -41,7 +42,7 @@ def main() -> None:
         full.queries.copy_(q)
         expected.append(full.attend().clone())
     results = {}
-    for exchange in ("nccl", "p2p"):
+    for exchange in ("nccl", "p2p", "fused"):
         split = SplitKVDecode([shard_layer(cache, i, world, rank) for i in range(layers)], q_heads,
                               owns_tail=False, exchange=exchange)
         assert split.exchange == exchange
@@ -59,8 +60,8 @@ def main() -> None:
         for got, want in zip(outs, expected):
             # the merge order differs from the unsplit kernel's: one bf16 ulp (2^-7 relative) of slack
             assert torch.allclose(got.float(), want.float(), atol=4e-3, rtol=2.0 ** -7), exchange
-    for a, b in zip(results["nccl"], results["p2p"]):
-        assert torch.equal(a, b)
+    for a, b, c in zip(results["nccl"], results["p2p"], results["fused"]):
+        assert torch.equal(a, b) and torch.equal(a, c)
     dist.barrier()
     split.peers.close()
     dist.destroy_process_group()

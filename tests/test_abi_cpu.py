@@ -55,11 +55,14 @@ def test_struct_mirrors_match_the_header_as_a_c_compiler_lays_it_out(tmp_path):
                ("inq_v_encode_args_t", N.VEncodeArgs), ("inq_decode_seq_t", N.DecodeSeq),
                ("inq_decode_args_t", N.DecodeArgs), ("inq_append_args_t", N.AppendArgs),
                ("inq_decode_generic_args_t", N.GenericDecodeArgs), ("inq_prefill_args_t", N.PrefillArgs),
-               ("inq_exchange_rank_t", N.ExchangeRank), ("inq_exchange_args_t", N.ExchangeArgs)]
+               ("inq_exchange_rank_t", N.ExchangeRank), ("inq_exchange_args_t", N.ExchangeArgs),
+               ("inq_decode_exchange_t", N.DecodeExchange)]
     offsets = [("inq_input_t", "num_slots", N.Input.num_slots.offset),
                ("inq_decode_seq_t", "pool_pages", N.DecodeSeq.pool_pages.offset),
                ("inq_decode_seq_t", "tail_tokens_device", N.DecodeSeq.tail_tokens_device.offset),
-               ("inq_decode_seq_t", "partial_output", N.DecodeSeq.partial_output.offset)]
+               ("inq_decode_seq_t", "partial_output", N.DecodeSeq.partial_output.offset),
+               ("inq_decode_args_t", "exchange_device", N.DecodeArgs.exchange_device.offset),
+               ("inq_decode_exchange_t", "n_rows", N.DecodeExchange.n_rows.offset)]
     lines = ["#include <stdio.h>", "#include <stddef.h>", f'#include "{HEADER}"', "int main(void) {"]
     lines += [f'  printf("%zu\\n", sizeof({name}));' for name, _ in structs]
     lines += [f'  printf("%zu\\n", offsetof({name}, {field}));' for name, field, _ in offsets]

@@ -128,3 +128,105 @@ def test_peer_exchange_wait_gives_up_and_reports_when_a_peer_never_signals():
     assert N.take_status(torch.device("cuda", 0)) == N.STATUS_WAIT_TIMEOUT
     assert int(epochs[0, 0]) == 1
     assert torch.count_nonzero(outs[0]) == 0
+
+
+def _fused_rank(cache, layers, q_heads, world, rank, q, peer_records=None, spin_limit=0, steps=1):
+    """One rank of a split whose decode launch exchanges its records itself.  The peers do not
+    run: their inboxes are buffers of this process that soak up the pushes, and ``peer_records``
+    ([world, rows, 130], both parities filled) stand in this rank's inbox with their flags set
+    for ``steps`` steps, as if the peers had been faster."""
+    import ctypes
+    from inquant import _native as N
+    from inquant.batched import DecodeBatch
+    from inquant.split_kv import shard_layer
+    lib = N.library()
+    device = torch.device("cuda", 0)
+    rows = layers * q_heads
+    size = lib.inq_exchange_inbox_bytes(world, rows)
+    flag_bytes = 2 * 8 * 512 * 4
+    inboxes = [torch.zeros(size, dtype=torch.uint8, device=device) for _ in range(world)]
+    if peer_records is not None:
+        flags = inboxes[rank][:flag_bytes].view(torch.int32).view(2, 8, 512)
+        data = inboxes[rank][flag_bytes:].view(torch.float32).view(2, world, rows, 130)
+        for src in range(world):
+            if src != rank:
+                data[:, src] = peer_records[src]
+                flags[:, src] = steps        # "published up to step `steps`": enough for every step run here
+    epoch = torch.zeros(2, dtype=torch.int32, device=device)
+    view = N.DecodeExchange()
+    for peer in range(world):
+        view.inboxes[peer] = inboxes[peer].data_ptr()
+    view.epoch, view.n_rows, view.world, view.rank, view.spin_limit = epoch.data_ptr(), rows, world, rank, spin_limit
+    view_device = torch.frombuffer(bytearray(bytes(view)), dtype=torch.uint8).to(device)
+    batch = DecodeBatch([shard_layer(cache, i, world, rank) for i in range(layers)], q_heads, torch.bfloat16)
+    batch.use_exchange(view_device)
+    batch.queries.copy_(q)
+    outs = []
+    for _ in range(steps):
+        outs.append(batch.attend().clone())
+    torch.cuda.synchronize()
+    return outs, epoch, inboxes
+
+
+def _split_fixture(layers=3, heads=4, tokens=1000):
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=64, residual_length=32,
+                                     sink_tokens=4, value_bits=2, validate_positions=False))
+    for layer in range(layers):
+        k, v = workloads.make_kv(140 + layer, heads, tokens)
+        cache.update(to_device(k), to_device(v), layer)
+    return cache
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_decode_launch_that_exchanges_its_records_matches_the_gathered_merge(world):
+    """The exchange inside the decode launch (inq_decode_exchange_t): every rank, run alone with the
+    peers' records already in its inbox, must write exactly the rows that all-gather +
+    inq_merge_partials give, must leave its own records in the peers' inboxes, and must advance the
+    step number; two steps use both halves of the double-buffered inbox."""
+    from inquant import _native as N
+    from inquant.batched import DecodeBatch
+    from inquant.split_kv import merge_records, shard_layer
+    layers, q_heads = 3, 28
+    cache = _split_fixture(layers)
+    q = to_device(np.stack([workloads.make_query(160 + i, q_heads) for i in range(layers)]))
+    records = []
+    for rank in range(world):
+        part = DecodeBatch([shard_layer(cache, i, world, rank) for i in range(layers)], q_heads, torch.bfloat16,
+                           partials_only=True)
+        part.queries.copy_(q)
+        part.attend()
+        records.append(part.partial_records.view(-1, 130).clone())
+    records = torch.stack(records).contiguous()
+    expected = merge_records(records, torch.empty((layers * q_heads, 128), dtype=torch.bfloat16, device="cuda"))
+    flag_bytes = 2 * 8 * 512 * 4
+    for rank in range(world):
+        outs, epoch, inboxes = _fused_rank(cache, layers, q_heads, world, rank, q, peer_records=records, steps=2)
+        assert N.take_status(torch.device("cuda", 0)) == 0
+        assert int(epoch[0]) == 2
+        for out in outs:
+            assert torch.equal(out.view(-1, 128), expected)
+        for peer in range(world):
+            if peer == rank:
+                continue
+            pushed = inboxes[peer][flag_bytes:].view(torch.float32).view(2, world, layers * q_heads, 130)
+            flags = inboxes[peer][:flag_bytes].view(torch.int32).view(2, 8, 512)
+            # 7 query heads per KV head: one tile of 8 per (layer, KV head), i.e. layers * 4 pairs
+            assert torch.equal(pushed[0, rank], records[rank]) and torch.equal(pushed[1, rank], records[rank])
+            assert flags[1, rank, :layers * 4].tolist() == [1] * (layers * 4) and flags[0, rank, :layers * 4].tolist() == [2] * (layers * 4)
+            assert int(flags[:, rank, layers * 4:].abs().sum()) == 0
+
+
+def test_decode_launch_exchange_gives_up_when_a_peer_never_publishes():
+    """Rank 0 of two, alone: rank 1's flags never arrive, the bounded wait of every pair runs out,
+    the status word carries the timeout bit, the rows are zero and the context stays usable."""
+    from inquant import _native as N
+    layers, q_heads = 2, 28
+    cache = _split_fixture(layers)
+    q = to_device(np.stack([workloads.make_query(170 + i, q_heads) for i in range(layers)]))
+    outs, epoch, _ = _fused_rank(cache, layers, q_heads, 2, 0, q, peer_records=None, spin_limit=100)
+    assert N.take_status(torch.device("cuda", 0)) == N.STATUS_WAIT_TIMEOUT
+    assert int(epoch[0]) == 1 and torch.count_nonzero(outs[0]) == 0
+    again, _, _ = _fused_rank(cache, layers, q_heads, 1, 0, q)
+    assert N.take_status(torch.device("cuda", 0)) == 0 and torch.count_nonzero(again[0]) > 0
