@@ -1049,7 +1049,7 @@ def run_split_kv(args, torch, dist, device, world, rank):
         torch.cuda.synchronize()
         ms = t0.elapsed_time(t1) / steps
         if check:
-            parity.update(check_split_parity(torch, dist, split, cache, run_step, inputs[0], world, rank, first, last))
+            parity[exchange] = check_split_parity(torch, dist, split, cache, run_step, inputs[0], world, rank, first, last)
         local_bytes = split.batch.algorithmic_bytes()["total"]
         stats = torch.tensor([ms, float(local_bytes)], device=device, dtype=torch.float64)
         if world > 1:
@@ -1061,29 +1061,32 @@ def run_split_kv(args, torch, dist, device, world, rank):
         return ms, float(local_bytes), split.exchange
 
     record_bytes = LAYERS * Q_HEADS * 130 * 4
-    extra = {}
-    launch = "CUDA graph of decode (append fused in on the tail owner) + exchange + merge" if use_graph else "eager"
-    exchange = None
+    describe = {
+        "fused": (f"inside the decode launch: the CTA that merges a (layer, KV head) pair stores its records ({record_bytes} B per rank "
+                  "and step in all) into every peer's inbox over NVLink peer memory, signals, waits (bounded) and merges all ranks' records",
+                  "CUDA graph of ONE launch per rank (decode with the append fused in on the tail owner and the exchange in its merge)"),
+        "p2p": (f"peer memory: one kernel per rank stores its {record_bytes} B of records into every peer's inbox over "
+                "NVLink, signals, waits (bounded) and merges",
+                "CUDA graph of decode (append fused in on the tail owner) + one exchange-and-merge kernel"),
+        "nccl": (f"one all-gather of {record_bytes} B per rank per step, then a local log-sum-exp merge",
+                 "CUDA graph of decode (append fused in on the tail owner) + all-gather + merge"),
+    }
+    # every exchange this node offers is timed (each with its own parity check); the fastest is the
+    # leg's figure and the others are reported beside it
+    timed = {}
     if world > 1:
-        try:
-            ms, total_bytes, exchange = time_split("fused", check=True)
-        except RuntimeError:
-            # every rank raises alike (the mappings are agreed on collectively), so all fall back together
-            exchange = None
-    if exchange is None:
-        ms, total_bytes, exchange = time_split("auto", check=True)
-    if exchange == "fused":
-        how = (f"inside the decode launch: the CTA that merges a (layer, KV head) pair stores its records ({record_bytes} B per rank "
-               "and step in all) into every peer's inbox over NVLink peer memory, signals, waits (bounded) and merges all ranks' records")
-        launch = "CUDA graph of ONE launch per rank (decode with the append fused in on the tail owner and the exchange in its merge)" if use_graph else "eager, one launch"
-        extra["us_per_step_separate_exchange_kernel"] = round(time_split("p2p")[0] * 1e3, 2)
-        extra["us_per_step_nccl_all_gather"] = round(time_split("nccl")[0] * 1e3, 2)
-    elif exchange == "p2p":
-        how = (f"peer memory: one kernel per rank stores its {record_bytes} B of records into every peer's inbox over "
-               "NVLink, signals, waits (bounded) and merges")
-        extra["us_per_step_nccl_all_gather"] = round(time_split("nccl")[0] * 1e3, 2)
-    else:
-        how = f"one all-gather of {record_bytes} B per rank per step, then a local log-sum-exp merge"
+        for name in ("fused", "p2p"):
+            try:
+                timed[name] = time_split(name, check=True)
+            except RuntimeError:
+                pass   # every rank raises alike: the peer mappings are agreed on collectively
+    timed["nccl"] = time_split("nccl", check=True)
+    best = min(timed, key=lambda name: timed[name][0])
+    ms, total_bytes, exchange = timed[best]
+    how, launch = describe[best]
+    if not use_graph:
+        launch = "eager"
+    extra = {"us_per_step_by_exchange": {name: round(t[0] * 1e3, 2) for name, t in timed.items()}}
     if N.take_status(device):
         raise RuntimeError("a split-KV kernel reported a failure in the status word")
     peak, _ = measured_peak_gbs()
@@ -1091,7 +1094,7 @@ def run_split_kv(args, torch, dist, device, world, rank):
             "aggregate_gbs": round(total_bytes / (ms * 1e-3) / 1e9, 1),
             "per_gpu_hbm_frac": round(total_bytes / world / (ms * 1e-3) / 1e9 / peak, 4),
             "exchange": how, "launch": launch,
-            "steps": steps, "parity": parity, **extra}
+            "steps": steps, "parity": dict(parity[best], exchanges_checked=sorted(parity)), **extra}
 
 
 # DRAM bytes (read + write) of one decode_kernel launch per algorithmic byte, from one ncu capture

@@ -331,25 +331,38 @@ __device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned
 // is indexed by the pair, the step number comes from the epoch word that the launch advances
 // when its last CTA leaves.
 template <typename QT>
-__device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long long row, int c8, bool active,
-                                           float4 oa, float4 ob, float top, float l, QT* out, int* status) {
+__device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long long row0, int g, int g_valid, int c8,
+                                           float4 oa, float4 ob, float top, float l, QT* out, int* status,
+                                           float* scratch) {
   __shared__ int s_failed;
   const int tid = threadIdx.x;
+  const bool active = g < g_valid;
+  const long long row = row0 + g;
   const int world = X->world, me = X->rank;
   const long long n_rows = X->n_rows;
   const int step = X->epoch[0] + 1;
   const int parity = step & 1;
   unsigned char* const own = X->inbox[me];
   if (tid == 0) s_failed = 0;
+  // the pair's rows are adjacent in an inbox: staged in shared memory, they leave as consecutive
+  // 8-byte stores of consecutive threads (whole 128-byte lines over NVLink, not scattered sectors)
   if (active) {
-    for (int p = 0; p < world; ++p) {
-      if (p == me) continue;
-      float* const dst = ex_data(X->inbox[p], parity, me, world, n_rows) + row * kExRowFloats;
-      *(float2*)(dst + c8) = make_float2(oa.x, oa.y);
-      *(float2*)(dst + c8 + 2) = make_float2(oa.z, oa.w);
-      *(float2*)(dst + c8 + 4) = make_float2(ob.x, ob.y);
-      *(float2*)(dst + c8 + 6) = make_float2(ob.z, ob.w);
-      if (c8 == 0) *(float2*)(dst + 128) = make_float2(top, l);
+    float* const rec = scratch + g * kExRowFloats;
+    *(float2*)(rec + c8) = make_float2(oa.x, oa.y);
+    *(float2*)(rec + c8 + 2) = make_float2(oa.z, oa.w);
+    *(float2*)(rec + c8 + 4) = make_float2(ob.x, ob.y);
+    *(float2*)(rec + c8 + 6) = make_float2(ob.z, ob.w);
+    if (c8 == 0) *(float2*)(rec + 128) = make_float2(top, l);
+  }
+  __syncthreads();
+  {
+    const int n_pairs8 = g_valid * (kExRowFloats / 2);
+    const float2* const src = (const float2*)scratch;
+    // every rank starts with the peer after itself, so that no inbox is everybody's first target
+    for (int hop = 1; hop < world; ++hop) {
+      const int p = me + hop < world ? me + hop : me + hop - world;
+      float2* const dst = (float2*)(ex_data(X->inbox[p], parity, me, world, n_rows) + row0 * kExRowFloats);
+      for (int i = tid; i < n_pairs8; i += kThreads) dst[i] = src[i];
     }
   }
   __threadfence_system();
@@ -359,13 +372,15 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
     const int* const flag = ex_flag(own, parity, tid, pair);
     const int limit = X->spin_limit > 0 ? X->spin_limit : kExDefaultSpin;
     int polls = 0;
-    while (ld_acquire_sys(flag) - step < 0) {
+    // relaxed polls, one acquire once the flag is there
+    while (*(volatile const int*)flag - step < 0) {
       if (++polls > limit) {
         atomicOr(&s_failed, 1);
         break;
       }
-      __nanosleep(100);
+      __nanosleep(40);
     }
+    (void)ld_acquire_sys(flag);
   }
   __syncthreads();
   const bool failed = s_failed != 0;
@@ -1398,8 +1413,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     }
     if (P.exchange) {
       const bool active = g < g_valid;
-      exchange_pair<QT>(P.exchange, pair, (long long)seq * P.H * P.G + q_head0 + g, c8, active, ex_a, ex_b,
-                        active ? mtop[g] : 0.f, active ? norm[g] : 1.f, (QT*)SEQ(out) + (q_head0 + g) * 128 + c8, P.status);
+      const float top = active ? mtop[g] : 0.f, l = active ? norm[g] : 1.f;
+      __syncthreads();   // the merge is done with its shared scratch: it now stages the pair's record
+      exchange_pair<QT>(P.exchange, pair, (long long)seq * P.H * P.G + q_head0, g, g_valid, c8, ex_a, ex_b, top, l,
+                        (QT*)SEQ(out) + (q_head0 + g) * 128 + c8, P.status, (float*)warp_base);
     }
   }
   __syncthreads();   // shared scratch is reused by the next pair of this CTA

@@ -17,8 +17,9 @@ log-sum-exp rule (the cross-rank form of ``triton_attention.py:168-181``).  Two 
             stores that pair's record into the peers' inboxes, awaits theirs (bounded) and merges them
             (``inq_decode_exchange_t``), so a step is ONE launch per rank;
 
-``"auto"`` takes the first when every rank sits on the same host and the mappings can be made,
-else the second.  Nothing else is exchanged: encode and append are block-local.  The reference
+``"auto"`` takes peer memory when every rank sits on the same host and the mappings can be made
+(inside the decode launch between two ranks, the separate kernel from four ranks on: the faster one
+of each case as measured), else the all-gather.  Nothing else is exchanged: encode and append are block-local.  The reference
 has no multi-GPU path; this module is new.
 """
 from __future__ import annotations
@@ -174,9 +175,17 @@ class SplitKVDecode:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.owns_tail = (self.rank == self.world - 1) if owns_tail is None else owns_tail
-        self.fused = exchange == "fused" and self.world > 1
+        # measured on B200s: inside the decode launch the exchange is the faster one between two ranks,
+        # the separate kernel from four ranks on
+        self.fused = self.world > 1 and (exchange == "fused" or (exchange == "auto" and self.world == 2))
         self.batch = DecodeBatch(sequences, q_heads, dtype, partials_only=not self.fused)
         n = len(sequences)
+        pairs = n * self.batch.kv_heads * ((self.batch.q_per_kv + 7) // 8)
+        if self.fused and pairs > 512:   # one flag word per pair in an inbox
+            if exchange == "fused":
+                raise ValueError("the exchange inside the decode launch serves at most 512 (sequence, KV head, head tile) pairs")
+            self.fused = False
+            self.batch = DecodeBatch(sequences, q_heads, dtype, partials_only=True)
         self.peers = None
         if self.world > 1 and exchange != "nccl":
             try:
@@ -184,6 +193,8 @@ class SplitKVDecode:
             except RuntimeError:
                 if exchange in ("p2p", "fused"):
                     raise
+                self.fused = False
+                self.batch = DecodeBatch(sequences, q_heads, dtype, partials_only=True)
         if self.fused:
             # ONE launch per step: the decode kernel stores every pair's record into the peers'
             # inboxes, awaits theirs (bounded) and merges them itself
