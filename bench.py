@@ -1101,10 +1101,9 @@ def run_split_kv(args, torch, dist, device, world, rank):
 # (dram__bytes_read.sum + dram__bytes_write.sum) of a 10-layer case of the same kernel, scaled to the
 # layers of this run because traffic grows in proportion to the units processed.  The source string
 # names the capture; set the ratio to None when the kernel changes and no new capture exists.
-DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 149.49 / 143.89
-DECODE_TRAFFIC_SOURCE = ("ncu capture of the 10-layer case (145.55 MB read + 3.94 MB written against 143.89 MB algorithmic) of "
-                         "the decode kernel as it stands (packed salient gather, scores relative to the running maximum, fused "
-                         "append), scaled by units")
+DECODE_TRAFFIC_PER_ALGORITHMIC_BYTE = 150.17 / 143.72
+DECODE_TRAFFIC_SOURCE = ("ncu capture of the 10-layer case (145.49 MB read + 4.68 MB written against 143.72 MB algorithmic) of "
+                         "the decode kernel as it stands (whole-slice fast path, fragment-product fold, fused append), scaled by units")
 
 
 # --------------------------------------------------------------------------- CPU arm (oracle port)
