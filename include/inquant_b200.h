@@ -222,6 +222,8 @@ typedef struct {
   int64_t new_stride_h;
   int32_t tail_capacity;
   int32_t reserved;
+  const int8_t* value_roles;  /* layout 0 with value_kind 1: role map of the value blocks, int8
+                               * [n_blocks][kv_heads][128], as `roles` is for the keys */
 } inq_decode_seq_t;
 
 /* Split-KV across the GPUs of one node inside the decode launch itself (no counterpart in the
@@ -271,6 +273,14 @@ typedef struct {
   const inq_decode_exchange_t* exchange_device; /* optional, DEVICE memory: exchange and merge the records of
                                                  * every pair with the peer GPUs inside this launch;
                                                  * `partial_output` of the sequences is then ignored */
+  int32_t value_kind;       /* 0: values as 2-bit codes in groups of 64 channels (value_codec.py);
+                             * 1: values stored as InQuant packed tensors like the keys (the reference's
+                             *    CacheConfig default, value_bits=None): table columns 3..5 then hold the
+                             *    value payload [kv_heads][tokens][64], scales fp32 [kv_heads][128] and
+                             *    padding fp32 [kv_heads][16]; served for layout 0, n_pad 16 on both sides
+                             *    and blocks of a multiple of 32 tokens (>= 128), else INQ_ERR_UNSUPPORTED
+                             *    (inq_decode_generic serves the rest) */
+  int32_t reserved;
 } inq_decode_args_t;
 int inq_decode_attention(const inq_decode_args_t* args /* host */, inq_stream_t stream);
 /* The same decode step for callers that cannot allocate device memory (a serving engine that

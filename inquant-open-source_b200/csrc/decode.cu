@@ -47,10 +47,12 @@ constexpr int kStages = 3;
 // Tokens per loop iteration are a template parameter of the kernel: SUB = 2 (32 tokens) for
 // blocks above 16 tokens, SUB = 1 (16 tokens) for smaller blocks (16-token pages), where every
 // slice is a whole block and its metadata rides inside the slice's own ring stage.
-template <int SUB>
+// VK = 1: values stored as InQuant packed tensors like the keys (64 bytes of nibbles per token,
+// per-channel scales per block, no per-token parameters).
+template <int SUB, int VK = 0>
 struct SliceCfg {
   static constexpr int kSliceTokens = 16 * SUB;       // tokens staged and processed per loop iteration
-  static constexpr int kStageK = 1024 * SUB, kStageV = 512 * SUB, kStageP = 128 * SUB;
+  static constexpr int kStageK = 1024 * SUB, kStageV = (VK ? 1024 : 512) * SUB, kStageP = VK ? 0 : 128 * SUB;
   static constexpr int kStageMeta = SUB == 1 ? 1024 : 0;   // K scales 512 B | role map 256 B | padding 256 B
   static constexpr int kStageBytes = kStageK + kStageV + kStageP + kStageMeta;
 };
@@ -69,8 +71,13 @@ constexpr float kRescaleSlack = 4.f;   // the running reference maximum may lag 
 // whose second salient channel does not exist)
 constexpr float kGatherInit = -128.25f / 8192.f;
 
-__host__ __device__ constexpr int warp_smem_bytes(int groups, int stage_bytes) {
-  return kWarpFixed + groups * (256 + 2048 + 64) + kStages * stage_bytes;
+// per-warp scratch of the InQuant-coded value side: staged block metadata (scales 512 B | role map
+// 128 B | padding 64 B, padded to 768), per-lane flush tables (weight and constant of the lane's 16
+// channels, their kinds) and the exchange area of the donor slots' sums
+constexpr int kValueMeta = 768, kValueTables = 32 * (64 + 64 + 16), kValueXchg = 16 * 8 * 4;
+constexpr int kValueScratch = kValueMeta + kValueTables + kValueXchg;
+__host__ __device__ constexpr int warp_smem_bytes(int groups, int stage_bytes, int vk = 0) {
+  return kWarpFixed + groups * (256 + 2048 + 64) + (vk ? kValueScratch : 0) + kStages * stage_bytes;
 }
 
 struct SeqDesc {
@@ -91,6 +98,7 @@ struct SeqDesc {
   const void* new_k; const void* new_v;   // the step's new token (launches with fused_append)
   long long new_sh;
   int tail_capacity, reserved;
+  const signed char* value_roles;   // table layout, InQuant-coded values: int8 [n_blocks][H][128]
 };
 static_assert(sizeof(SeqDesc) == sizeof(inq_decode_seq_t), "SeqDesc must mirror inq_decode_seq_t");
 
@@ -122,7 +130,7 @@ struct ExchangeView {
 static_assert(sizeof(ExchangeView) == sizeof(inq_decode_exchange_t), "ExchangeView must mirror inq_decode_exchange_t");
 
 struct BlockPtrs {
-  const unsigned char *kp, *ks, *kr, *kpad, *vp, *vs, *vo;
+  const unsigned char *kp, *ks, *kr, *kpad, *vp, *vs, *vo, *vr;
 };
 
 // ------------------------------------------------------------------------------------------ PTX helpers
@@ -238,20 +246,30 @@ __device__ __forceinline__ float2 half2_bits_to_float2(unsigned bits) {
 }
 
 // ------------------------------------------------------------------------------------------ block lookup
-template <int MODE>
+template <int MODE, int VK = 0>
 __device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const long long* table,
                                                   const signed char* roles, const unsigned char* pool,
-                                                  const int* page_table, int pool_pages, int b, int h) {
+                                                  const int* page_table, int pool_pages, int b, int h,
+                                                  const signed char* value_roles = nullptr) {
   BlockPtrs out;
+  out.vr = nullptr;
   if (MODE == 0) {
     const long long* row = table + (long long)b * 6;
     const long long T = P.T;
     out.kp = (const unsigned char*)row[0] + (long long)h * T * 64;
     out.ks = (const unsigned char*)row[1] + (long long)h * 512;
     out.kpad = (const unsigned char*)row[2] + (long long)h * P.n_pad * 4;
-    out.vp = (const unsigned char*)row[3] + (long long)h * T * 32;
-    out.vs = (const unsigned char*)row[4] + (long long)h * T * 4;
-    out.vo = (const unsigned char*)row[5] + (long long)h * T * 4;
+    if (VK) {
+      // values coded like the keys: payload, per-channel scales, padding list, role map
+      out.vp = (const unsigned char*)row[3] + (long long)h * T * 64;
+      out.vs = (const unsigned char*)row[4] + (long long)h * 512;
+      out.vo = (const unsigned char*)row[5] + (long long)h * 64;
+      out.vr = (const unsigned char*)value_roles + ((long long)b * P.H + h) * 128;
+    } else {
+      out.vp = (const unsigned char*)row[3] + (long long)h * T * 32;
+      out.vs = (const unsigned char*)row[4] + (long long)h * T * 4;
+      out.vo = (const unsigned char*)row[5] + (long long)h * T * 4;
+    }
     out.kr = (const unsigned char*)roles + ((long long)b * P.H + h) * 128;
   } else {
     int id = page_table[b];
@@ -428,13 +446,20 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
 // channels (the preset and the 128/256-token pages): the copies of a slice then are eight
 // asynchronous copies from per-lane pointers that advance by constants, a block's metadata is
 // requested as soon as the prefetch cursor enters the block, and nothing ragged is handled.
-template <int MODE, typename QT, bool SAL, int SUB, bool FAST>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const DecodeParams P) {
+// VK = 1 (with FAST, table layout): the values are InQuant packed tensors like the keys.  Their
+// nibbles go through the value MMAs as fp16 subnormals into accumulators of the current block
+// alone; when the block ends these are folded into the running output with the block's
+// per-channel scales (regular channel: s (sum p code - 8 sum p); salient: s (16 sum p hi + sum p lo
+// - 128 sum p), the low-nibble sum fetched from the lane that owns the donor slot; donor: its
+// constant times sum p).  The second accumulator set needs the registers of two CTAs per SM.
+template <int MODE, typename QT, bool SAL, int SUB, bool FAST, int VK = 0>
+__global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(const DecodeParams P) {
+  static_assert(!VK || (FAST && MODE == 0 && SAL && SUB == 2), "InQuant-coded values: whole-slice path of the table layout only");
   constexpr int kSub = SUB;
-  constexpr int kSliceTokens = SliceCfg<SUB>::kSliceTokens;
-  constexpr int kStageK = SliceCfg<SUB>::kStageK, kStageV = SliceCfg<SUB>::kStageV, kStageP = SliceCfg<SUB>::kStageP;
-  constexpr int kStageBytes = SliceCfg<SUB>::kStageBytes;
-  constexpr bool kMetaInStage = SliceCfg<SUB>::kStageMeta > 0;   // host guarantees one slice per block
+  constexpr int kSliceTokens = SliceCfg<SUB, VK>::kSliceTokens;
+  constexpr int kStageK = SliceCfg<SUB, VK>::kStageK, kStageV = SliceCfg<SUB, VK>::kStageV, kStageP = SliceCfg<SUB, VK>::kStageP;
+  constexpr int kStageBytes = SliceCfg<SUB, VK>::kStageBytes;
+  constexpr bool kMetaInStage = SliceCfg<SUB, VK>::kStageMeta > 0;   // host guarantees one slice per block
   constexpr int kMetaOffset = kStageK + kStageV + kStageP;
   extern __shared__ __align__(16) unsigned char smem[];
   float* qs = (float*)smem;                                             // 8 heads x 4 chunks x kQChunk
@@ -448,7 +473,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   const int r = lane >> 2, j = lane & 3;
   const int n_pad = FAST ? 16 : P.n_pad;                                // salient channels per head
   const int groups = FAST ? 1 : (n_pad + 15) >> 4;                      // ... in groups of 16
-  const int warp_bytes = warp_smem_bytes(groups, kStageBytes);
+  const int warp_bytes = warp_smem_bytes(groups, kStageBytes, VK);
   unsigned char* const wb = warp_base + warp * warp_bytes;
   // folded-query B fragments of the 8 K steps ([step][lane] x 8 bytes); while a block's weights
   // are being derived the same 2 KB hold the per-channel slot weights and additive constants
@@ -461,7 +486,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   unsigned char* wqsal = wb + kWarpFixed;                               // B fragments: query at salient channels
   unsigned char* wsel = wqsal + groups * 256;                           // B fragments: nibble selection
   unsigned short* wcell = (unsigned short*)(wsel + groups * 2048);      // selection cells written by the last fold (offsets into wsel)
-  unsigned char* ring = (unsigned char*)wcell + groups * 64;
+  // InQuant-coded values: staged value metadata of a block, the lane's flush tables, the donor sums
+  unsigned char* wvmeta = (unsigned char*)wcell + groups * 64;
+  float* wvw = (float*)(wvmeta + kValueMeta);                           // [lane][16] weight of the block sum
+  float* wvk = wvw + 32 * 16;                                           // [lane][16] factor of sum p
+  signed char* wvkind = (signed char*)(wvk + 32 * 16);                  // [lane][16] -1 regular, idx salient, 16 + idx donor
+  float* wvx = (float*)(wvkind + 32 * 16);                              // [16 list entries][8 heads] low-nibble sums
+  unsigned char* ring = (unsigned char*)wcell + groups * 64 + (VK ? kValueScratch : 0);
   __shared__ int s_is_last;
 
   // Flat decomposition: the packed slices of all (sequence, KV head, head tile) pairs form one
@@ -505,6 +536,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   const unsigned char* const d_pool = SEQ(pool);
   const int* const d_pages = SEQ(page_table);
   const int d_pool_pages = SEQ(pool_pages);
+  const signed char* const d_vroles = VK ? SEQ(value_roles) : nullptr;
   const int first_visible = SEQ(first_visible);
   // (loaded here, ahead of the barriers of the query staging, so that their latency overlaps it)
   const int T = P.T;
@@ -630,6 +662,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       const QT* vC = vb + (long long)min(tok0 + 2 * j + 8, last) * vst;
       const QT* vD = vb + (long long)min(tok0 + 2 * j + 9, last) * vst;
       uint4 vrow[2][4];
+      uint2 vrow2[4][4];   // coded values: this lane's channels are 32 wg + 4 r .. + 3 (see the value MMAs below)
       {
         const QT* k_lo = kb + (long long)min(tok0 + r, last) * kst;
         const QT* k_hi = kb + (long long)min(tok0 + r + 8, last) * kst;
@@ -639,13 +672,24 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           x[m] = *(const uint4*)(k_lo + (4 * m + j) * 8);
           y[m] = *(const uint4*)(k_hi + (4 * m + j) * 8);
         }
+        if (VK) {
 #pragma unroll
-        for (int gr = 0; gr < 2; ++gr) {
-          const int ch = 64 * gr + 8 * r;
-          vrow[gr][0] = *(const uint4*)(vA + ch);
-          vrow[gr][1] = *(const uint4*)(vB + ch);
-          vrow[gr][2] = *(const uint4*)(vC + ch);
-          vrow[gr][3] = *(const uint4*)(vD + ch);
+          for (int wg = 0; wg < 4; ++wg) {
+            const int ch = 32 * wg + 4 * r;
+            vrow2[wg][0] = *(const uint2*)(vA + ch);
+            vrow2[wg][1] = *(const uint2*)(vB + ch);
+            vrow2[wg][2] = *(const uint2*)(vC + ch);
+            vrow2[wg][3] = *(const uint2*)(vD + ch);
+          }
+        } else {
+#pragma unroll
+          for (int gr = 0; gr < 2; ++gr) {
+            const int ch = 64 * gr + 8 * r;
+            vrow[gr][0] = *(const uint4*)(vA + ch);
+            vrow[gr][1] = *(const uint4*)(vB + ch);
+            vrow[gr][2] = *(const uint4*)(vC + ch);
+            vrow[gr][3] = *(const uint4*)(vD + ch);
+          }
         }
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
@@ -686,6 +730,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       l_run[1] += p1 + p3;
       const unsigned b0 = movmatrix_trans(pack_qt2<QT>(p0, p1));
       const unsigned b1 = movmatrix_trans(pack_qt2<QT>(p2, p3));
+      if (VK) {
+#pragma unroll
+        for (int wg = 0; wg < 4; ++wg) {
+          const uint2 A = vrow2[wg][0], Bv = vrow2[wg][1], C = vrow2[wg][2], Dv = vrow2[wg][3];
+          const unsigned av[2] = {A.x, A.y}, bv[2] = {Bv.x, Bv.y}, cv[2] = {C.x, C.y}, dv[2] = {Dv.x, Dv.y};
+#pragma unroll
+          for (int pp = 0; pp < 2; ++pp) {
+            mma_qt<QT>(acc[wg * 2 + pp], __byte_perm(av[pp], bv[pp], 0x5410u), __byte_perm(av[pp], bv[pp], 0x7632u),
+                       __byte_perm(cv[pp], dv[pp], 0x5410u), __byte_perm(cv[pp], dv[pp], 0x7632u), b0, b1);
+          }
+        }
+      } else {
 #pragma unroll
       for (int gr = 0; gr < 2; ++gr) {
         const uint4 A = vrow[gr][0], Bv = vrow[gr][1], C = vrow[gr][2], Dv = vrow[gr][3];
@@ -697,6 +753,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
                      __byte_perm(cv[q], dv[q], 0x5410u), __byte_perm(cv[q], dv[q], 0x7632u), b0, b1);
         }
       }
+      }
     }
   }
 
@@ -706,7 +763,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
   if (pb > pa) {
     const int n_my = (int)(pb - pa);
     int pf_block = (int)(pa / spb), pf_slice = (int)(pa % spb);   // prefetch cursor
-    BlockPtrs pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h);
+    BlockPtrs pf_ptrs = locate_block<MODE, VK>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
     int to_issue = n_my, issue_stage = 0;
     int meta_block = -1;        // block whose metadata is staged (or in flight) in wmeta
     int folded_block = -2;      // last block whose weights were derived from wmeta
@@ -714,17 +771,26 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       cp_async16(dst + lane * 16, bp.ks + lane * 16);
       if (lane < (MODE == 0 ? 8 : 16)) cp_async16(dst + 512 + lane * 16, bp.kr + lane * 16);
       for (int i = lane; i < n_pad; i += 32) cp_async4(dst + 768 + i * 4, bp.kpad + i * 4);
+      if (VK) {
+        cp_async16(wvmeta + lane * 16, bp.vs + lane * 16);
+        if (lane < 8) cp_async16(wvmeta + 512 + lane * 16, bp.vr + lane * 16);
+        if (lane < 16) cp_async4(wvmeta + 640 + lane * 4, bp.vo + lane * 4);
+      }
     };
     // FAST: this lane's source pointers of the next slice to request (K rows, V rows, V scale and
     // offset pairs), the shared-memory address of the stage it goes to, slices left in its block
     const unsigned char* fk = pf_ptrs.kp + pf_slice * 2048 + lane * 16;
-    const unsigned char* fv = pf_ptrs.vp + pf_slice * 1024 + lane * 16;
+    const unsigned char* fv = pf_ptrs.vp + pf_slice * (VK ? 2048 : 1024) + lane * 16;
     const unsigned char* fs = pf_ptrs.vs + pf_slice * 128 + lane * 4;
     const unsigned char* fo = pf_ptrs.vo + pf_slice * 128 + lane * 4;
     const unsigned ring_lo = smem_addr(ring), ring_hi = ring_lo + kStages * kStageBytes;
     unsigned issue_addr = ring_lo;
     int pf_left = spb - pf_slice;
-    const unsigned fast_v_dst = (unsigned)(kStageK + (((lane >> 1) * 2 + ((lane & 1) ^ ((lane >> 3) & 1))) << 4));
+    // value rows in a stage.  2-bit values: 32 B per token, the halves of tokens 4..7 (mod 8) swapped.
+    // Coded values: 64 B per token like the keys, the 16-byte chunks XORed with (token / 2) % 4 so that
+    // the later ldmatrix reads of eight tokens' chunks fall into distinct banks.
+    const unsigned fast_v_dst = VK ? (unsigned)(kStageK + (lane >> 2) * 64 + (((lane & 3) ^ ((lane >> 3) & 3)) << 4))
+                                   : (unsigned)(kStageK + (((lane >> 1) * 2 + ((lane & 1) ^ ((lane >> 3) & 1))) << 4));
     if (FAST) {
       stage_meta(pf_ptrs, wmeta);   // the first block's metadata rides with its first slice
       meta_block = pf_block;
@@ -739,9 +805,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           asm volatile("cp.async.cg.shared.global [%0+1536], [%1+1536], 16;" ::"r"(dk), "l"(fk));
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dv), "l"(fv));
           asm volatile("cp.async.cg.shared.global [%0+512], [%1+512], 16;" ::"r"(dv), "l"(fv));
-          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dp), "l"(fs));
-          asm volatile("cp.async.ca.shared.global [%0+128], [%1], 4;" ::"r"(dp), "l"(fo));
-          fk += 2048; fv += 1024; fs += 128; fo += 128;
+          if (VK) {
+            asm volatile("cp.async.cg.shared.global [%0+1024], [%1+1024], 16;" ::"r"(dv), "l"(fv));
+            asm volatile("cp.async.cg.shared.global [%0+1536], [%1+1536], 16;" ::"r"(dv), "l"(fv));
+          } else {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dp), "l"(fs));
+            asm volatile("cp.async.ca.shared.global [%0+128], [%1], 4;" ::"r"(dp), "l"(fo));
+          }
+          fk += 2048; fv += VK ? 2048 : 1024; fs += 128; fo += 128;
           --to_issue;
           issue_addr += kStageBytes;
           if (issue_addr == ring_hi) issue_addr = ring_lo;
@@ -753,7 +824,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
               // area is free, i.e. the block whose metadata it holds has been folded (always the case
               // except for a warp whose range begins in the last slices of a block; the fold then
               // fetches the metadata itself)
-              pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h);
+              pf_ptrs = locate_block<MODE, VK>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
               fk = pf_ptrs.kp + lane * 16; fv = pf_ptrs.vp + lane * 16; fs = pf_ptrs.vs + lane * 4; fo = pf_ptrs.vo + lane * 4;
               if (folded_block == meta_block) {
                 stage_meta(pf_ptrs, wmeta);
@@ -785,7 +856,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         if (++pf_slice == spb) {
           pf_slice = 0;
           ++pf_block;
-          if (to_issue > 0) pf_ptrs = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h);
+          if (to_issue > 0) pf_ptrs = locate_block<MODE, VK>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
         }
       }
       cp_async_commit();
@@ -795,7 +866,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     // the dense slices of this warp hide behind the DRAM latency of the first packed slices;
     // their contribution is brought into the packed loop's per-row units (powers of two)
     dense_part();
-    {
+    if (!VK) {
       const float ix[4] = {1.f / 16777216.f, 1.f / 1048576.f, 1.f / 65536.f, 1.f / 4194304.f};
       const float iy[4] = {1.f / 4194304.f, 1.f / 262144.f, 1.f / 16777216.f, 1.f / 1048576.f};
 #pragma unroll
@@ -819,6 +890,66 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
     const unsigned ww_addr = smem_addr(wW) + lane * 8, sel_addr = smem_addr(wsel) + lane * 8;
     int stage_index = 0;
     unsigned consume_addr = ring_lo;
+    // coded values: sums of the current block alone (in subnormal units) and of its probabilities
+    float bacc[8][4], l_blk[2] = {0.f, 0.f};
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) bacc[mt][k] = 0.f;
+    // ldmatrix row addresses inside a stage's value area: lanes 0-7 / 8-15 name tokens 0-7 / 8-15 of
+    // the first 16-byte chunk (words 0-7: channels 0-31), lanes 16-31 the same tokens of the second;
+    // the other address serves chunks 2 and 3.  Chunks are stored XORed with (token / 2) % 4.
+    const int vk_tok = (lane & 7) + 8 * ((lane >> 3) & 1), vk_sw = (vk_tok >> 1) & 3;
+    const unsigned vk_ldsm_a = (unsigned)(vk_tok * 64 + (((lane >> 4) ^ vk_sw) << 4));
+    const unsigned vk_ldsm_b = (unsigned)(vk_tok * 64 + ((((lane >> 4) + 2) ^ vk_sw) << 4));
+    // End of a block (or of this warp's range): the block's sums enter the running output with the
+    // block's per-channel scales.  Entry i of a lane's tables is channel 32 (i / 4) + 4 r + i % 4.
+    auto flush_values = [&]() {
+      float lb0 = l_blk[0], lb1 = l_blk[1];
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        lb0 += __shfl_xor_sync(0xffffffffu, lb0, off);
+        lb1 += __shfl_xor_sync(0xffffffffu, lb1, off);
+      }
+      const int4 kinds4 = *(const int4*)(wvkind + r * 16);
+      const int kinds[4] = {kinds4.x, kinds4.y, kinds4.z, kinds4.w};
+      // donor slots hold the low nibbles of salient codes: their sums go to the lanes of those channels
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int kind = (int)(signed char)((kinds[i >> 2] >> (8 * (i & 3))) & 0xff);
+        const int mt = 2 * (i >> 2) + ((i >> 1) & 1), x = i & 1;
+        if (kind >= 16) {
+          const float unit = x ? 1048576.f : 16777216.f;
+          *(float2*)(wvx + (kind - 16) * 8 + 2 * j) = make_float2(bacc[mt][2 * x] * unit, bacc[mt][2 * x + 1] * unit);
+        }
+      }
+      __syncwarp();
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 w4 = *(const float4*)(wvw + r * 16 + 4 * q4), k4 = *(const float4*)(wvk + r * 16 + 4 * q4);
+        const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, kv[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+        for (int ii = 0; ii < 4; ++ii) {
+          const int i = 4 * q4 + ii;
+          const int kind = (int)(signed char)((kinds[q4] >> (8 * ii)) & 0xff);
+          const int mt = 2 * q4 + (ii >> 1), x = ii & 1;
+          float add0 = fmaf(wv[ii], bacc[mt][2 * x], kv[ii] * lb0), add1 = fmaf(wv[ii], bacc[mt][2 * x + 1], kv[ii] * lb1);
+          if (kind >= 0 && kind < 16) {
+            const float2 low = *(const float2*)(wvx + kind * 8 + 2 * j);
+            const float s_src = kv[ii] * (-1.f / 128.f);
+            add0 = fmaf(s_src, low.x, add0);
+            add1 = fmaf(s_src, low.y, add1);
+          }
+          acc[mt][2 * x] += add0;
+          acc[mt][2 * x + 1] += add1;
+          bacc[mt][2 * x] = 0.f;
+          bacc[mt][2 * x + 1] = 0.f;
+          (void)i;
+        }
+      }
+      l_blk[0] = l_blk[1] = 0.f;
+      __syncwarp();
+    };
 
     for (int it = 0; it < n_my; ++it) {
       cp_async_wait<kStages - 2>();
@@ -838,7 +969,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           meta = ring + stage_index * kStageBytes + kMetaOffset;
         } else if (meta_block != cur_block) {
           // not prefetched (very short blocks): fetch now and wait for it alone
-          BlockPtrs cb = locate_block<MODE>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, cur_block, h);
+          BlockPtrs cb = locate_block<MODE, VK>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, cur_block, h, d_vroles);
           __syncwarp();
           stage_meta(cb, wmeta);
           cp_async_commit();
@@ -996,6 +1127,44 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
         }
         bm[0] = beta[0] - m_run[0];
         bm[1] = beta[1] - m_run[1];
+        if (VK) {
+          // flush tables of the value block: lane (r, j) derives entries 4j .. 4j+3 of row r
+          const float* const vscale = (const float*)wvmeta;
+          const signed char* const vroles = (const signed char*)(wvmeta + 512);
+          const float* const vpads = (const float*)(wvmeta + 640);
+          bool vbad = false;
+#pragma unroll
+          for (int ii = 0; ii < 4; ++ii) {
+            const int c = 32 * j + 4 * r + ii;
+            const float sc = vscale[c];
+            const float unit = (ii & 1) ? 1048576.f : 16777216.f;
+            int role = vroles[c];
+            float w = sc * unit, k = -8.f * sc;
+            int kind = -1;
+            if (role > 127 || role < -17) {
+              vbad = true;
+              w = 0.f; k = 0.f;
+            } else if (role >= 0) {
+              const int idx = -(int)vroles[role] - 2;
+              if (idx >= 0 && idx < 16) {
+                kind = idx;
+                w = 16.f * sc * unit;
+                k = -128.f * sc;
+              } else {
+                vbad = true;
+                w = 0.f; k = 0.f;
+              }
+            } else if (role < -1) {
+              kind = 16 + (-role - 2);
+              w = 0.f;
+              k = to_float<QT>(from_float<QT>(vpads[-role - 2]));
+            }
+            wvw[r * 16 + 4 * j + ii] = w;
+            wvk[r * 16 + 4 * j + ii] = k;
+            wvkind[r * 16 + 4 * j + ii] = (signed char)kind;
+          }
+          if (vbad) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
+        }
         need_weights = false;
         if (issue_late) {
           __syncwarp();   // every lane has read the per-channel terms: the staging area is free
@@ -1182,6 +1351,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
           for (int mt = 0; mt < 8; ++mt) {
             acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
           }
+          if (VK) {
+            l_blk[0] *= a0;
+            l_blk[1] *= a1;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+              bacc[mt][0] *= a0; bacc[mt][1] *= a1; bacc[mt][2] *= a0; bacc[mt][3] *= a1;
+            }
+          }
           m_run[0] = mn0;
           m_run[1] = mn1;
           bm[0] = beta[0] - mn0;
@@ -1227,21 +1404,49 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
       mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1); \
     }                                                                                                      \
   }
+#define INQ_PVK(BASE, LO, HI)                                                                              \
+  {                                                                                                        \
+    mma_f16(bacc[BASE], (LO) & 0x000F000Fu, (LO) & 0x00F000F0u, (HI) & 0x000F000Fu, (HI) & 0x00F000F0u, t0, t1); \
+    const unsigned lo8 = (LO) >> 8, hi8 = (HI) >> 8;                                                       \
+    mma_f16(bacc[BASE + 1], lo8 & 0x000F000Fu, lo8 & 0x00F000F0u, hi8 & 0x000F000Fu, hi8 & 0x00F000F0u, t0, t1); \
+  }
+      if (VK) {
+        // coded values: 16 tokens x 32 words of four nibbles each; word w of a token holds channels
+        // 4w .. 4w+3, so row r of the MMAs of chunk wg is word 8 wg + r: channels 32 wg + 4 r + (0 | 1)
+        // for the nibbles at bit 0 | 4 and, after a shift by 8, + (2 | 3)
+#pragma unroll
+        for (int u = 0; u < kSub; ++u) {
+          const unsigned t0 = movmatrix_trans(pack_half2(pr[u][0], pr[u][1]));
+          const unsigned t1 = movmatrix_trans(pack_half2(pr[u][2], pr[u][3]));
+          const uint4 Ma = u ? ldsm4_trans<kStageK + 1024>(stage + vk_ldsm_a) : ldsm4_trans<kStageK>(stage + vk_ldsm_a);
+          const uint4 Mb = u ? ldsm4_trans<kStageK + 1024>(stage + vk_ldsm_b) : ldsm4_trans<kStageK>(stage + vk_ldsm_b);
+          INQ_PVK(0, Ma.x, Ma.y)
+          INQ_PVK(2, Ma.z, Ma.w)
+          INQ_PVK(4, Mb.x, Mb.y)
+          INQ_PVK(6, Mb.z, Mb.w)
+          l_blk[0] += pr[u][0] + pr[u][2];
+          l_blk[1] += pr[u][1] + pr[u][3];
+        }
+      } else {
       INQ_PV(0)
       if (kSub > 1) INQ_PV(1)
+      }
 #undef INQ_PV
+#undef INQ_PVK
       if (++cur_slice == spb) {
         cur_slice = 0;
         ++cur_block;
         need_weights = true;
+        if (VK) flush_values();
       }
     }
+    if (VK && cur_slice != 0) flush_values();   // this warp's range ended inside a block
     cp_async_wait<0>();
     // a code at bit offset o of its 16-bit lane was multiplied as code * 2^(o-24)
     const float fx[4] = {16777216.f, 1048576.f, 65536.f, 4194304.f};   // offsets 0, 4, 8, 2
     const float fy[4] = {4194304.f, 262144.f, 16777216.f, 1048576.f};  // offsets 2, 6, 0, 4
 #pragma unroll
-    for (int mt = 0; mt < 8; ++mt) {
+    for (int mt = 0; mt < (VK ? 0 : 8); ++mt) {
       acc[mt][0] *= fx[mt & 3];
       acc[mt][1] *= fx[mt & 3];
       acc[mt][2] *= fy[mt & 3];
@@ -1269,7 +1474,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
     const int gr = mt >> 2, q = mt & 3;
-    const int ch = 64 * gr + 8 * r + 2 * q;
+    const int ch = VK ? 32 * (mt >> 1) + 4 * r + 2 * (mt & 1) : 64 * gr + 8 * r + 2 * q;
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int g = 2 * j + e;
@@ -1446,8 +1651,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const Deco
 }
 
 #undef SEQ
-static int smem_bytes(int groups, int sub) {
-  return kQBytes + kWarps * warp_smem_bytes(groups, sub == 1 ? SliceCfg<1>::kStageBytes : SliceCfg<2>::kStageBytes);
+static int smem_bytes(int groups, int sub, int vk = 0) {
+  const int stage = vk ? SliceCfg<2, 1>::kStageBytes : (sub == 1 ? SliceCfg<1>::kStageBytes : SliceCfg<2>::kStageBytes);
+  return kQBytes + kWarps * warp_smem_bytes(groups, stage, vk);
 }
 
 }  // namespace inq
@@ -1458,7 +1664,7 @@ using namespace inq;
 // device, not to the process: a process that drives several GPUs (or several host threads) gets
 // one record per device ordinal, filled under a mutex on first use.
 constexpr int kMaxDevices = 64;
-constexpr int kKernelVariants = 20;   // 16 general instances, 4 of the whole-slice fast path
+constexpr int kKernelVariants = 22;   // 16 general instances, 4 of the whole-slice fast path, 2 with coded values
 struct DeviceState {
   int sm_count = 0;
   bool raised[kKernelVariants] = {};
@@ -1562,7 +1768,7 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   // block either way, so the work list does not depend on the choice
   const int sub = a->block_tokens <= 16 ? 1 : 2;
   typedef void (*kernel_t)(const DecodeParams);
-  static const kernel_t kernels[20] = {
+  static const kernel_t kernels[kKernelVariants] = {
       decode_kernel<0, __half, false, 2, false>, decode_kernel<0, __half, true, 2, false>,
       decode_kernel<0, __nv_bfloat16, false, 2, false>, decode_kernel<0, __nv_bfloat16, true, 2, false>,
       decode_kernel<1, __half, false, 2, false>, decode_kernel<1, __half, true, 2, false>,
@@ -1573,13 +1779,21 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
       decode_kernel<1, __nv_bfloat16, false, 1, false>, decode_kernel<1, __nv_bfloat16, true, 1, false>,
       // whole slices, at least four per block, one salient group
       decode_kernel<0, __half, true, 2, true>, decode_kernel<0, __nv_bfloat16, true, 2, true>,
-      decode_kernel<1, __half, true, 2, true>, decode_kernel<1, __nv_bfloat16, true, 2, true>};
+      decode_kernel<1, __half, true, 2, true>, decode_kernel<1, __nv_bfloat16, true, 2, true>,
+      // the same with the values stored as InQuant packed tensors (table layout)
+      decode_kernel<0, __half, true, 2, true, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 1>};
   const bool fast = a->n_pad == 16 && a->block_tokens % 32 == 0 && a->block_tokens >= 128;
-  const int which = fast ? 16 + a->layout * 2 + (a->dtype == INQ_F16 ? 0 : 1)
+  const int vk = a->value_kind;
+  if (vk != 0 && vk != 1) return INQ_ERR_ARGUMENT;
+  // coded values are served for the whole-slice geometry of the table layout with 16 salient channels
+  // on either side; every other combination is inq_decode_generic's
+  if (vk && !(fast && a->layout == 0)) return INQ_ERR_UNSUPPORTED;
+  const int which = vk ? 20 + (a->dtype == INQ_F16 ? 0 : 1)
+                  : fast ? 16 + a->layout * 2 + (a->dtype == INQ_F16 ? 0 : 1)
                          : (sub == 1 ? 8 : 0) + a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);
   const kernel_t kernel = kernels[which];
-  const int shared = smem_bytes(groups, sub);
-  const int shared_limit = smem_bytes(4, sub);
+  const int shared = smem_bytes(groups, sub, vk);
+  const int shared_limit = smem_bytes(vk ? 1 : 4, sub, vk);
   const int device = current_device();
   if (device < 0) return INQ_ERR_UNSUPPORTED;   // device ordinals above 63 are not tracked
   int resident = 0;

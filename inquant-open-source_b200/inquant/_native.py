@@ -55,7 +55,8 @@ class DecodeSeq(ctypes.Structure):
                 ("first_visible", c_int32), ("tail_skip", c_int32), ("pool_pages", c_int32),
                 ("tail_tokens_device", c_void_p),
                 ("partial_output", c_void_p), ("new_key", c_void_p), ("new_value", c_void_p),
-                ("new_stride_h", c_int64), ("tail_capacity", c_int32), ("reserved", c_int32)]
+                ("new_stride_h", c_int64), ("tail_capacity", c_int32), ("reserved", c_int32),
+                ("value_roles", c_void_p)]
 
 
 class DecodeArgs(ctypes.Structure):
@@ -65,7 +66,7 @@ class DecodeArgs(ctypes.Structure):
                 ("page_bytes", c_int64), ("page_offsets", c_int64 * 6),
                 ("pair_starts", c_void_p), ("total_units", c_int64), ("uniform_blocks", c_int32),
                 ("partials", c_void_p), ("partials_floats", c_int64), ("counters", c_void_p), ("status", c_void_p),
-                ("fused_append", c_int32), ("exchange_device", c_void_p)]
+                ("fused_append", c_int32), ("exchange_device", c_void_p), ("value_kind", c_int32), ("reserved", c_int32)]
 
 
 class DecodeExchange(ctypes.Structure):

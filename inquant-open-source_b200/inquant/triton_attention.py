@@ -244,7 +244,11 @@ class PackedDecodeState:
         if self._stream_identity is not None and self._stream_identity != identity:
             raise RuntimeError("Packed decode state requires one CUDA stream per state")
         q_per_kv = query.shape[1] // kv_heads
-        if query.dtype == torch.float32 or (n_blocks and not self._preset):
+        # values stored as InQuant packed tensors (the reference's default) run the streaming kernel too
+        # when both sides have 16 salient channels and the blocks are whole 32-token slices
+        coded_values = bool(n_blocks) and self._inquant_values and self._salient == 16 and self._value_salient == 16 \
+            and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128
+        if query.dtype == torch.float32 or (n_blocks and not self._preset and not coded_values):
             return self._decode_general(query, kv_heads, q_per_kv, n_blocks, sink_key, sink_value, sink_t,
                                         residual_key, residual_value, residual_t, scale)
         tiles = (q_per_kv + 7) // 8
@@ -269,6 +273,7 @@ class PackedDecodeState:
         seq.query, seq.output, seq.query_head_stride = query.data_ptr(), output.data_ptr(), query.stride(1)
         seq.table = self._tables.data_ptr() if n_blocks else None
         seq.roles = self._key_map.data_ptr() if n_blocks else None
+        seq.value_roles = self._value_map.data_ptr() if coded_values else None
         if sink_t:
             seq.sink_key, seq.sink_value = sink_key.data_ptr(), sink_value.data_ptr()
             seq.sink_key_stride_h, seq.sink_key_stride_t = sink_key.stride(1), sink_key.stride(2)
@@ -283,6 +288,7 @@ class PackedDecodeState:
         args.kv_heads, args.q_per_kv = kv_heads, q_per_kv
         args.block_tokens, args.n_pad = self._packed_tokens, self._salient
         args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[query.dtype], scale
+        args.value_kind = int(coded_values)
         args.partials, args.partials_floats = workspace.data_ptr(), workspace.numel()
         args.counters = N.decode_counters(query.device, kv_heads * tiles).data_ptr()
         args.status = N.status_word(query.device).data_ptr()

@@ -40,7 +40,7 @@ def test_python_binding_lists_the_same_symbols():
 
 def test_struct_mirrors_have_the_sizes_the_header_implies():
     from inquant import _native as N
-    assert ctypes.sizeof(N.DecodeSeq) == 224
+    assert ctypes.sizeof(N.DecodeSeq) == 232
     assert ctypes.sizeof(N.PrefillArgs) == 4 * 8 + 8 * 8 + 4 * 4 + 4 + 4 + 8 + 8 + 8
     assert ctypes.sizeof(N.GenericDecodeArgs) % 8 == 0
     assert ctypes.sizeof(N.ExchangeRank) == 48 and ctypes.sizeof(N.ExchangeArgs) == 32
