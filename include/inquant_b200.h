@@ -279,8 +279,12 @@ typedef struct {
                              *    value payload [kv_heads][tokens][64], scales fp32 [kv_heads][128] and
                              *    padding fp32 [kv_heads][16]; served for layout 0, n_pad 16 on both sides
                              *    and blocks of a multiple of 32 tokens (>= 128), else INQ_ERR_UNSUPPORTED
-                             *    (inq_decode_generic serves the rest) */
-  int32_t reserved;
+                             *    (inq_decode_generic serves the rest);
+                             * 2: values as 4-bit codes with fp16 scale and offset per token and group of
+                             *    128 / value_groups channels (value_codec.py with bits=4): table columns 3..5
+                             *    hold payload [kv_heads][tokens][64], scales and offsets
+                             *    [kv_heads][tokens][value_groups]; same geometry limits as kind 1 */
+  int32_t value_groups;     /* kind 2: 1, 2 or 4 (groups of 128, 64 or 32 channels) */
 } inq_decode_args_t;
 int inq_decode_attention(const inq_decode_args_t* args /* host */, inq_stream_t stream);
 /* The same decode step for callers that cannot allocate device memory (a serving engine that

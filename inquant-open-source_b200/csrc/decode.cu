@@ -49,10 +49,12 @@ constexpr int kStages = 3;
 // slice is a whole block and its metadata rides inside the slice's own ring stage.
 // VK = 1: values stored as InQuant packed tensors like the keys (64 bytes of nibbles per token,
 // per-channel scales per block, no per-token parameters).
-template <int SUB, int VK = 0>
+// VK = 2: values as 4-bit codes with per-token scales and offsets for VG groups of 128 / VG channels.
+template <int SUB, int VK = 0, int VG = 2>
 struct SliceCfg {
   static constexpr int kSliceTokens = 16 * SUB;       // tokens staged and processed per loop iteration
-  static constexpr int kStageK = 1024 * SUB, kStageV = (VK ? 1024 : 512) * SUB, kStageP = VK ? 0 : 128 * SUB;
+  static constexpr int kStageK = 1024 * SUB, kStageV = (VK ? 1024 : 512) * SUB;
+  static constexpr int kStageP = VK == 1 ? 0 : 16 * SUB * VG * 4;   // fp16 scale and offset per token and group
   static constexpr int kStageMeta = SUB == 1 ? 1024 : 0;   // K scales 512 B | role map 256 B | padding 256 B
   static constexpr int kStageBytes = kStageK + kStageV + kStageP + kStageMeta;
 };
@@ -246,7 +248,7 @@ __device__ __forceinline__ float2 half2_bits_to_float2(unsigned bits) {
 }
 
 // ------------------------------------------------------------------------------------------ block lookup
-template <int MODE, int VK = 0>
+template <int MODE, int VK = 0, int VG = 2>
 __device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const long long* table,
                                                   const signed char* roles, const unsigned char* pool,
                                                   const int* page_table, int pool_pages, int b, int h,
@@ -259,12 +261,16 @@ __device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const l
     out.kp = (const unsigned char*)row[0] + (long long)h * T * 64;
     out.ks = (const unsigned char*)row[1] + (long long)h * 512;
     out.kpad = (const unsigned char*)row[2] + (long long)h * P.n_pad * 4;
-    if (VK) {
+    if (VK == 1) {
       // values coded like the keys: payload, per-channel scales, padding list, role map
       out.vp = (const unsigned char*)row[3] + (long long)h * T * 64;
       out.vs = (const unsigned char*)row[4] + (long long)h * 512;
       out.vo = (const unsigned char*)row[5] + (long long)h * 64;
       out.vr = (const unsigned char*)value_roles + ((long long)b * P.H + h) * 128;
+    } else if (VK == 2) {
+      out.vp = (const unsigned char*)row[3] + (long long)h * T * 64;
+      out.vs = (const unsigned char*)row[4] + (long long)h * T * (2 * VG);
+      out.vo = (const unsigned char*)row[5] + (long long)h * T * (2 * VG);
     } else {
       out.vp = (const unsigned char*)row[3] + (long long)h * T * 32;
       out.vs = (const unsigned char*)row[4] + (long long)h * T * 4;
@@ -452,14 +458,20 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
 // per-channel scales (regular channel: s (sum p code - 8 sum p); salient: s (16 sum p hi + sum p lo
 // - 128 sum p), the low-nibble sum fetched from the lane that owns the donor slot; donor: its
 // constant times sum p).  The second accumulator set needs the registers of two CTAs per SM.
-template <int MODE, typename QT, bool SAL, int SUB, bool FAST, int VK = 0>
+// VK = 2 (same geometry): 4-bit values with per-token scales and offsets for VG = 4, 2 or 1 groups
+// of 32, 64 or 128 channels.  The nibbles take the value MMAs of the coded values, the group scale is
+// multiplied into the probabilities and the offsets are contracted by one more MMA as for the 2-bit
+// values; a 16-byte chunk of a value row (8 words of four nibbles) is 32 channels, so every MMA lies
+// inside one group.  Their stages are 4.1 to 4.5 KB, so two CTAs fit an SM here as well.
+template <int MODE, typename QT, bool SAL, int SUB, bool FAST, int VK = 0, int VG = 2>
 __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(const DecodeParams P) {
-  static_assert(!VK || (FAST && MODE == 0 && SAL && SUB == 2), "InQuant-coded values: whole-slice path of the table layout only");
+  static_assert(!VK || (FAST && MODE == 0 && SAL && SUB == 2), "coded and 4-bit values: whole-slice path of the table layout only");
+  static_assert(VK == 2 ? (VG == 1 || VG == 2 || VG == 4) : VG == 2, "groups of 32, 64 or 128 channels");
   constexpr int kSub = SUB;
-  constexpr int kSliceTokens = SliceCfg<SUB, VK>::kSliceTokens;
-  constexpr int kStageK = SliceCfg<SUB, VK>::kStageK, kStageV = SliceCfg<SUB, VK>::kStageV, kStageP = SliceCfg<SUB, VK>::kStageP;
-  constexpr int kStageBytes = SliceCfg<SUB, VK>::kStageBytes;
-  constexpr bool kMetaInStage = SliceCfg<SUB, VK>::kStageMeta > 0;   // host guarantees one slice per block
+  constexpr int kSliceTokens = SliceCfg<SUB, VK, VG>::kSliceTokens;
+  constexpr int kStageK = SliceCfg<SUB, VK, VG>::kStageK, kStageV = SliceCfg<SUB, VK, VG>::kStageV, kStageP = SliceCfg<SUB, VK, VG>::kStageP;
+  constexpr int kStageBytes = SliceCfg<SUB, VK, VG>::kStageBytes;
+  constexpr bool kMetaInStage = SliceCfg<SUB, VK, VG>::kStageMeta > 0;   // host guarantees one slice per block
   constexpr int kMetaOffset = kStageK + kStageV + kStageP;
   extern __shared__ __align__(16) unsigned char smem[];
   float* qs = (float*)smem;                                             // 8 heads x 4 chunks x kQChunk
@@ -473,7 +485,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
   const int r = lane >> 2, j = lane & 3;
   const int n_pad = FAST ? 16 : P.n_pad;                                // salient channels per head
   const int groups = FAST ? 1 : (n_pad + 15) >> 4;                      // ... in groups of 16
-  const int warp_bytes = warp_smem_bytes(groups, kStageBytes, VK);
+  const int warp_bytes = warp_smem_bytes(groups, kStageBytes, VK == 1);
   unsigned char* const wb = warp_base + warp * warp_bytes;
   // folded-query B fragments of the 8 K steps ([step][lane] x 8 bytes); while a block's weights
   // are being derived the same 2 KB hold the per-channel slot weights and additive constants
@@ -492,7 +504,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
   float* wvk = wvw + 32 * 16;                                           // [lane][16] factor of sum p
   signed char* wvkind = (signed char*)(wvk + 32 * 16);                  // [lane][16] -1 regular, idx salient, 16 + idx donor
   float* wvx = (float*)(wvkind + 32 * 16);                              // [16 list entries][8 heads] low-nibble sums
-  unsigned char* ring = (unsigned char*)wcell + groups * 64 + (VK ? kValueScratch : 0);
+  unsigned char* ring = (unsigned char*)wcell + groups * 64 + (VK == 1 ? kValueScratch : 0);
   __shared__ int s_is_last;
 
   // Flat decomposition: the packed slices of all (sequence, KV head, head tile) pairs form one
@@ -536,7 +548,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
   const unsigned char* const d_pool = SEQ(pool);
   const int* const d_pages = SEQ(page_table);
   const int d_pool_pages = SEQ(pool_pages);
-  const signed char* const d_vroles = VK ? SEQ(value_roles) : nullptr;
+  const signed char* const d_vroles = VK == 1 ? SEQ(value_roles) : nullptr;
   const int first_visible = SEQ(first_visible);
   // (loaded here, ahead of the barriers of the query staging, so that their latency overlaps it)
   const int T = P.T;
@@ -763,7 +775,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
   if (pb > pa) {
     const int n_my = (int)(pb - pa);
     int pf_block = (int)(pa / spb), pf_slice = (int)(pa % spb);   // prefetch cursor
-    BlockPtrs pf_ptrs = locate_block<MODE, VK>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
+    BlockPtrs pf_ptrs = locate_block<MODE, VK, VG>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
     int to_issue = n_my, issue_stage = 0;
     int meta_block = -1;        // block whose metadata is staged (or in flight) in wmeta
     int folded_block = -2;      // last block whose weights were derived from wmeta
@@ -771,7 +783,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
       cp_async16(dst + lane * 16, bp.ks + lane * 16);
       if (lane < (MODE == 0 ? 8 : 16)) cp_async16(dst + 512 + lane * 16, bp.kr + lane * 16);
       for (int i = lane; i < n_pad; i += 32) cp_async4(dst + 768 + i * 4, bp.kpad + i * 4);
-      if (VK) {
+      if (VK == 1) {
         cp_async16(wvmeta + lane * 16, bp.vs + lane * 16);
         if (lane < 8) cp_async16(wvmeta + 512 + lane * 16, bp.vr + lane * 16);
         if (lane < 16) cp_async4(wvmeta + 640 + lane * 4, bp.vo + lane * 4);
@@ -781,8 +793,9 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
     // offset pairs), the shared-memory address of the stage it goes to, slices left in its block
     const unsigned char* fk = pf_ptrs.kp + pf_slice * 2048 + lane * 16;
     const unsigned char* fv = pf_ptrs.vp + pf_slice * (VK ? 2048 : 1024) + lane * 16;
-    const unsigned char* fs = pf_ptrs.vs + pf_slice * 128 + lane * 4;
-    const unsigned char* fo = pf_ptrs.vo + pf_slice * 128 + lane * 4;
+    constexpr int kParamLane = VK == 2 && VG == 4 ? 8 : 4;   // bytes of a parameter array one lane copies per slice
+    const unsigned char* fs = pf_ptrs.vs + pf_slice * (kStageP / 2) + lane * kParamLane;
+    const unsigned char* fo = pf_ptrs.vo + pf_slice * (kStageP / 2) + lane * kParamLane;
     const unsigned ring_lo = smem_addr(ring), ring_hi = ring_lo + kStages * kStageBytes;
     unsigned issue_addr = ring_lo;
     int pf_left = spb - pf_slice;
@@ -798,7 +811,8 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
     auto issue = [&]() {
       if (FAST) {
         if (to_issue > 0) {
-          const unsigned dk = issue_addr + lane * 16, dv = issue_addr + fast_v_dst, dp = issue_addr + kStageK + kStageV + lane * 4;
+          const unsigned dk = issue_addr + lane * 16, dv = issue_addr + fast_v_dst;
+          const unsigned dp = issue_addr + kStageK + kStageV + lane * (VK == 2 && VG == 4 ? 8 : 4);
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dk), "l"(fk));
           asm volatile("cp.async.cg.shared.global [%0+512], [%1+512], 16;" ::"r"(dk), "l"(fk));
           asm volatile("cp.async.cg.shared.global [%0+1024], [%1+1024], 16;" ::"r"(dk), "l"(fk));
@@ -808,11 +822,20 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
           if (VK) {
             asm volatile("cp.async.cg.shared.global [%0+1024], [%1+1024], 16;" ::"r"(dv), "l"(fv));
             asm volatile("cp.async.cg.shared.global [%0+1536], [%1+1536], 16;" ::"r"(dv), "l"(fv));
-          } else {
+          }
+          if (VK == 2 && VG == 4) {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dp), "l"(fs));
+            asm volatile("cp.async.ca.shared.global [%0+256], [%1], 8;" ::"r"(dp), "l"(fo));
+          } else if (VK == 2 && VG == 1) {
+            if (lane < 16) {
+              asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dp), "l"(fs));
+              asm volatile("cp.async.ca.shared.global [%0+64], [%1], 4;" ::"r"(dp), "l"(fo));
+            }
+          } else if (VK != 1) {
             asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dp), "l"(fs));
             asm volatile("cp.async.ca.shared.global [%0+128], [%1], 4;" ::"r"(dp), "l"(fo));
           }
-          fk += 2048; fv += VK ? 2048 : 1024; fs += 128; fo += 128;
+          fk += 2048; fv += VK ? 2048 : 1024; fs += kStageP / 2; fo += kStageP / 2;
           --to_issue;
           issue_addr += kStageBytes;
           if (issue_addr == ring_hi) issue_addr = ring_lo;
@@ -824,8 +847,8 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
               // area is free, i.e. the block whose metadata it holds has been folded (always the case
               // except for a warp whose range begins in the last slices of a block; the fold then
               // fetches the metadata itself)
-              pf_ptrs = locate_block<MODE, VK>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
-              fk = pf_ptrs.kp + lane * 16; fv = pf_ptrs.vp + lane * 16; fs = pf_ptrs.vs + lane * 4; fo = pf_ptrs.vo + lane * 4;
+              pf_ptrs = locate_block<MODE, VK, VG>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
+              fk = pf_ptrs.kp + lane * 16; fv = pf_ptrs.vp + lane * 16; fs = pf_ptrs.vs + lane * kParamLane; fo = pf_ptrs.vo + lane * kParamLane;
               if (folded_block == meta_block) {
                 stage_meta(pf_ptrs, wmeta);
                 meta_block = pf_block;
@@ -856,7 +879,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
         if (++pf_slice == spb) {
           pf_slice = 0;
           ++pf_block;
-          if (to_issue > 0) pf_ptrs = locate_block<MODE, VK>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
+          if (to_issue > 0) pf_ptrs = locate_block<MODE, VK, VG>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
         }
       }
       cp_async_commit();
@@ -866,6 +889,16 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
     // the dense slices of this warp hide behind the DRAM latency of the first packed slices;
     // their contribution is brought into the packed loop's per-row units (powers of two)
     dense_part();
+    if (VK == 2) {
+      // 4-bit values: rows r carry nibbles at bit 0 (2^-24), rows r + 8 nibbles at bit 4 (2^-20)
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        acc[mt][0] *= 1.f / 16777216.f;
+        acc[mt][1] *= 1.f / 16777216.f;
+        acc[mt][2] *= 1.f / 1048576.f;
+        acc[mt][3] *= 1.f / 1048576.f;
+      }
+    }
     if (!VK) {
       const float ix[4] = {1.f / 16777216.f, 1.f / 1048576.f, 1.f / 65536.f, 1.f / 4194304.f};
       const float iy[4] = {1.f / 4194304.f, 1.f / 262144.f, 1.f / 16777216.f, 1.f / 1048576.f};
@@ -969,7 +1002,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
           meta = ring + stage_index * kStageBytes + kMetaOffset;
         } else if (meta_block != cur_block) {
           // not prefetched (very short blocks): fetch now and wait for it alone
-          BlockPtrs cb = locate_block<MODE, VK>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, cur_block, h, d_vroles);
+          BlockPtrs cb = locate_block<MODE, VK, VG>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, cur_block, h, d_vroles);
           __syncwarp();
           stage_meta(cb, wmeta);
           cp_async_commit();
@@ -1127,7 +1160,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
         }
         bm[0] = beta[0] - m_run[0];
         bm[1] = beta[1] - m_run[1];
-        if (VK) {
+        if (VK == 1) {
           // flush tables of the value block: lane (r, j) derives entries 4j .. 4j+3 of row r
           const float* const vscale = (const float*)wvmeta;
           const signed char* const vroles = (const signed char*)(wvmeta + 512);
@@ -1351,7 +1384,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
           for (int mt = 0; mt < 8; ++mt) {
             acc[mt][0] *= a0; acc[mt][1] *= a1; acc[mt][2] *= a0; acc[mt][3] *= a1;
           }
-          if (VK) {
+          if (VK == 1) {
             l_blk[0] *= a0;
             l_blk[1] *= a1;
 #pragma unroll
@@ -1410,7 +1443,56 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
     const unsigned lo8 = (LO) >> 8, hi8 = (HI) >> 8;                                                       \
     mma_f16(bacc[BASE + 1], lo8 & 0x000F000Fu, lo8 & 0x00F000F0u, hi8 & 0x000F000Fu, hi8 & 0x00F000F0u, t0, t1); \
   }
-      if (VK) {
+      if (VK == 2) {
+        // 4-bit values in VG groups: the value MMAs of the coded values with the group's per-token
+        // scale multiplied into the probabilities; offsets of group r in row r of one more MMA
+        constexpr int kPairBytes = 4 * VG;          // parameters of a token pair: 2 tokens x VG groups x fp16
+#pragma unroll
+        for (int u = 0; u < kSub; ++u) {
+          const unsigned t0 = movmatrix_trans(pack_half2(pr[u][0], pr[u][1]));
+          const unsigned t1 = movmatrix_trans(pack_half2(pr[u][2], pr[u][3]));
+          const unsigned sp = stage + kStageK + kStageV + kPairBytes * j + (u ? 8 * kPairBytes : 0);
+          unsigned sc_lo[VG], sc_hi[VG], of_lo, of_hi;   // half2 (token 2j, token 2j+1) and (2j+8, 2j+9) per group
+          if (VG == 1) {
+            sc_lo[0] = lds32<0>(sp); sc_hi[0] = lds32<4 * kPairBytes>(sp);
+            of_lo = lds32<kStageP / 2>(sp); of_hi = lds32<kStageP / 2 + 4 * kPairBytes>(sp);
+          } else if (VG == 2) {
+            const uint2 a = lds64<0>(sp), b = lds64<4 * kPairBytes>(sp);
+            const uint2 c = lds64<kStageP / 2>(sp), d = lds64<kStageP / 2 + 4 * kPairBytes>(sp);
+#pragma unroll
+            for (int g = 0; g < VG; ++g) {
+              sc_lo[g] = __byte_perm(a.x, a.y, g ? 0x7632u : 0x5410u);
+              sc_hi[g] = __byte_perm(b.x, b.y, g ? 0x7632u : 0x5410u);
+            }
+            of_lo = __byte_perm(c.x, c.y, vsel);
+            of_hi = __byte_perm(d.x, d.y, vsel);
+          } else {
+            const uint4 a = lds128<0>(sp), b = lds128<4 * kPairBytes>(sp);
+            const uint4 c = lds128<kStageP / 2>(sp), d = lds128<kStageP / 2 + 4 * kPairBytes>(sp);
+            const unsigned aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int g = 0; g < VG; ++g) {
+              sc_lo[g] = __byte_perm(aw[g >> 1], aw[2 + (g >> 1)], (g & 1) ? 0x7632u : 0x5410u);
+              sc_hi[g] = __byte_perm(bw[g >> 1], bw[2 + (g >> 1)], (g & 1) ? 0x7632u : 0x5410u);
+            }
+            const bool upper = (r & 2) != 0;
+            of_lo = __byte_perm(upper ? c.y : c.x, upper ? c.w : c.z, vsel);
+            of_hi = __byte_perm(upper ? d.y : d.x, upper ? d.w : d.z, vsel);
+          }
+          mma_f16(oacc, of_lo, 0u, of_hi, 0u, t0, t1);
+          const uint4 Ma = u ? ldsm4_trans<kStageK + 1024>(stage + vk_ldsm_a) : ldsm4_trans<kStageK>(stage + vk_ldsm_a);
+          const uint4 Mb = u ? ldsm4_trans<kStageK + 1024>(stage + vk_ldsm_b) : ldsm4_trans<kStageK>(stage + vk_ldsm_b);
+          const unsigned lo[4] = {Ma.x, Ma.z, Mb.x, Mb.z}, hi[4] = {Ma.y, Ma.w, Mb.y, Mb.w};
+#pragma unroll
+          for (int wg = 0; wg < 4; ++wg) {
+            const int g = wg * VG / 4;
+            const unsigned b0 = hmul2_bits(t0, sc_lo[g]), b1 = hmul2_bits(t1, sc_hi[g]);
+            mma_f16(acc[2 * wg], lo[wg] & 0x000F000Fu, lo[wg] & 0x00F000F0u, hi[wg] & 0x000F000Fu, hi[wg] & 0x00F000F0u, b0, b1);
+            const unsigned lo8 = lo[wg] >> 8, hi8 = hi[wg] >> 8;
+            mma_f16(acc[2 * wg + 1], lo8 & 0x000F000Fu, lo8 & 0x00F000F0u, hi8 & 0x000F000Fu, hi8 & 0x00F000F0u, b0, b1);
+          }
+        }
+      } else if (VK) {
         // coded values: 16 tokens x 32 words of four nibbles each; word w of a token holds channels
         // 4w .. 4w+3, so row r of the MMAs of chunk wg is word 8 wg + r: channels 32 wg + 4 r + (0 | 1)
         // for the nibbles at bit 0 | 4 and, after a shift by 8, + (2 | 3)
@@ -1437,14 +1519,23 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
         cur_slice = 0;
         ++cur_block;
         need_weights = true;
-        if (VK) flush_values();
+        if (VK == 1) flush_values();
       }
     }
-    if (VK && cur_slice != 0) flush_values();   // this warp's range ended inside a block
+    if (VK == 1 && cur_slice != 0) flush_values();   // this warp's range ended inside a block
     cp_async_wait<0>();
     // a code at bit offset o of its 16-bit lane was multiplied as code * 2^(o-24)
     const float fx[4] = {16777216.f, 1048576.f, 65536.f, 4194304.f};   // offsets 0, 4, 8, 2
     const float fy[4] = {4194304.f, 262144.f, 16777216.f, 1048576.f};  // offsets 2, 6, 0, 4
+    if (VK == 2) {
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        acc[mt][0] *= 16777216.f;
+        acc[mt][1] *= 16777216.f;
+        acc[mt][2] *= 1048576.f;
+        acc[mt][3] *= 1048576.f;
+      }
+    }
 #pragma unroll
     for (int mt = 0; mt < (VK ? 0 : 8); ++mt) {
       acc[mt][0] *= fx[mt & 3];
@@ -1463,9 +1554,10 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], off);
   }
   // the offset sums of value group gr, heads 2j and 2j+1, sit in lane (r = gr, j)
-  float osum[2][2];
+  constexpr int kOffsetGroups = VK == 2 ? VG : 2;
+  float osum[kOffsetGroups][2];
 #pragma unroll
-  for (int gr = 0; gr < 2; ++gr) {
+  for (int gr = 0; gr < kOffsetGroups; ++gr) {
     osum[gr][0] = __shfl_sync(0xffffffffu, oacc[0], gr * 4 + j);
     osum[gr][1] = __shfl_sync(0xffffffffu, oacc[1], gr * 4 + j);
   }
@@ -1473,7 +1565,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
   float* wout = (float*)ring;   // [8][132]
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
-    const int gr = mt >> 2, q = mt & 3;
+    const int gr = VK == 2 ? (mt >> 1) * VG / 4 : mt >> 2, q = mt & 3;   // value group of the accumulator
     const int ch = VK ? 32 * (mt >> 1) + 4 * r + 2 * (mt & 1) : 64 * gr + 8 * r + 2 * q;
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -1651,9 +1743,10 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
 }
 
 #undef SEQ
-static int smem_bytes(int groups, int sub, int vk = 0) {
-  const int stage = vk ? SliceCfg<2, 1>::kStageBytes : (sub == 1 ? SliceCfg<1>::kStageBytes : SliceCfg<2>::kStageBytes);
-  return kQBytes + kWarps * warp_smem_bytes(groups, stage, vk);
+static int smem_bytes(int groups, int sub, int vk = 0, int vg = 2) {
+  const int stage = vk == 2 ? (vg == 1 ? SliceCfg<2, 2, 1>::kStageBytes : vg == 2 ? SliceCfg<2, 2, 2>::kStageBytes : SliceCfg<2, 2, 4>::kStageBytes)
+                  : vk ? SliceCfg<2, 1>::kStageBytes : (sub == 1 ? SliceCfg<1>::kStageBytes : SliceCfg<2>::kStageBytes);
+  return kQBytes + kWarps * warp_smem_bytes(groups, stage, vk == 1);
 }
 
 }  // namespace inq
@@ -1664,7 +1757,7 @@ using namespace inq;
 // device, not to the process: a process that drives several GPUs (or several host threads) gets
 // one record per device ordinal, filled under a mutex on first use.
 constexpr int kMaxDevices = 64;
-constexpr int kKernelVariants = 22;   // 16 general instances, 4 of the whole-slice fast path, 2 with coded values
+constexpr int kKernelVariants = 28;   // 16 general instances, 4 of the whole-slice fast path, 2 with coded values, 6 with 4-bit values
 struct DeviceState {
   int sm_count = 0;
   bool raised[kKernelVariants] = {};
@@ -1781,19 +1874,24 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
       decode_kernel<0, __half, true, 2, true>, decode_kernel<0, __nv_bfloat16, true, 2, true>,
       decode_kernel<1, __half, true, 2, true>, decode_kernel<1, __nv_bfloat16, true, 2, true>,
       // the same with the values stored as InQuant packed tensors (table layout)
-      decode_kernel<0, __half, true, 2, true, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 1>};
+      decode_kernel<0, __half, true, 2, true, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 1>,
+      // 4-bit values in 1, 2 or 4 groups
+      decode_kernel<0, __half, true, 2, true, 2, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 1>,
+      decode_kernel<0, __half, true, 2, true, 2, 2>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 2>,
+      decode_kernel<0, __half, true, 2, true, 2, 4>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 4>};
   const bool fast = a->n_pad == 16 && a->block_tokens % 32 == 0 && a->block_tokens >= 128;
-  const int vk = a->value_kind;
-  if (vk != 0 && vk != 1) return INQ_ERR_ARGUMENT;
+  const int vk = a->value_kind, vg = a->value_groups;
+  if (vk < 0 || vk > 2 || (vk == 2 && vg != 1 && vg != 2 && vg != 4)) return INQ_ERR_ARGUMENT;
   // coded values are served for the whole-slice geometry of the table layout with 16 salient channels
   // on either side; every other combination is inq_decode_generic's
   if (vk && !(fast && a->layout == 0)) return INQ_ERR_UNSUPPORTED;
-  const int which = vk ? 20 + (a->dtype == INQ_F16 ? 0 : 1)
+  const int which = vk == 2 ? 22 + (vg == 1 ? 0 : vg == 2 ? 2 : 4) + (a->dtype == INQ_F16 ? 0 : 1)
+                  : vk ? 20 + (a->dtype == INQ_F16 ? 0 : 1)
                   : fast ? 16 + a->layout * 2 + (a->dtype == INQ_F16 ? 0 : 1)
                          : (sub == 1 ? 8 : 0) + a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);
   const kernel_t kernel = kernels[which];
-  const int shared = smem_bytes(groups, sub, vk);
-  const int shared_limit = smem_bytes(vk ? 1 : 4, sub, vk);
+  const int shared = smem_bytes(groups, sub, vk, vg);
+  const int shared_limit = smem_bytes(vk ? 1 : 4, sub, vk, vg);
   const int device = current_device();
   if (device < 0) return INQ_ERR_UNSUPPORTED;   // device ordinals above 63 are not tracked
   int resident = 0;

@@ -66,7 +66,7 @@ class DecodeArgs(ctypes.Structure):
                 ("page_bytes", c_int64), ("page_offsets", c_int64 * 6),
                 ("pair_starts", c_void_p), ("total_units", c_int64), ("uniform_blocks", c_int32),
                 ("partials", c_void_p), ("partials_floats", c_int64), ("counters", c_void_p), ("status", c_void_p),
-                ("fused_append", c_int32), ("exchange_device", c_void_p), ("value_kind", c_int32), ("reserved", c_int32)]
+                ("fused_append", c_int32), ("exchange_device", c_void_p), ("value_kind", c_int32), ("value_groups", c_int32)]
 
 
 class DecodeExchange(ctypes.Structure):

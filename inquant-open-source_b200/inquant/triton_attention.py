@@ -248,7 +248,10 @@ class PackedDecodeState:
         # when both sides have 16 salient channels and the blocks are whole 32-token slices
         coded_values = bool(n_blocks) and self._inquant_values and self._salient == 16 and self._value_salient == 16 \
             and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128
-        if query.dtype == torch.float32 or (n_blocks and not self._preset and not coded_values):
+        # ... and so do 4-bit values in groups of 32, 64 or 128 channels
+        wide_values = bool(n_blocks) and not self._inquant_values and self._value_bits == 4 and self._salient == 16 \
+            and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128
+        if query.dtype == torch.float32 or (n_blocks and not self._preset and not coded_values and not wide_values):
             return self._decode_general(query, kv_heads, q_per_kv, n_blocks, sink_key, sink_value, sink_t,
                                         residual_key, residual_value, residual_t, scale)
         tiles = (q_per_kv + 7) // 8
@@ -288,7 +291,8 @@ class PackedDecodeState:
         args.kv_heads, args.q_per_kv = kv_heads, q_per_kv
         args.block_tokens, args.n_pad = self._packed_tokens, self._salient
         args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[query.dtype], scale
-        args.value_kind = int(coded_values)
+        args.value_kind = 1 if coded_values else 2 if wide_values else 0
+        args.value_groups = 128 // self._value_group if wide_values else 0
         args.partials, args.partials_floats = workspace.data_ptr(), workspace.numel()
         args.counters = N.decode_counters(query.device, kv_heads * tiles).data_ptr()
         args.status = N.status_word(query.device).data_ptr()
