@@ -273,8 +273,8 @@ __device__ __forceinline__ BlockPtrs locate_block(const DecodeParams& P, const l
       out.vo = (const unsigned char*)row[5] + (long long)h * T * (2 * VG);
     } else {
       out.vp = (const unsigned char*)row[3] + (long long)h * T * 32;
-      out.vs = (const unsigned char*)row[4] + (long long)h * T * 4;
-      out.vo = (const unsigned char*)row[5] + (long long)h * T * 4;
+      out.vs = (const unsigned char*)row[4] + (long long)h * T * (2 * VG);
+      out.vo = (const unsigned char*)row[5] + (long long)h * T * (2 * VG);
     }
     out.kr = (const unsigned char*)roles + ((long long)b * P.H + h) * 128;
   } else {
@@ -466,7 +466,8 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
 template <int MODE, typename QT, bool SAL, int SUB, bool FAST, int VK = 0, int VG = 2>
 __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(const DecodeParams P) {
   static_assert(!VK || (FAST && MODE == 0 && SAL && SUB == 2), "coded and 4-bit values: whole-slice path of the table layout only");
-  static_assert(VK == 2 ? (VG == 1 || VG == 2 || VG == 4) : VG == 2, "groups of 32, 64 or 128 channels");
+  static_assert(VK == 2 ? (VG == 1 || VG == 2 || VG == 4) : VK == 0 ? (VG == 2 || (VG == 1 && FAST && MODE == 0)) : VG == 2,
+                "4-bit values: groups of 32, 64 or 128 channels; 2-bit values: 64, or 128 on the whole-slice path");
   constexpr int kSub = SUB;
   constexpr int kSliceTokens = SliceCfg<SUB, VK, VG>::kSliceTokens;
   constexpr int kStageK = SliceCfg<SUB, VK, VG>::kStageK, kStageV = SliceCfg<SUB, VK, VG>::kStageV, kStageP = SliceCfg<SUB, VK, VG>::kStageP;
@@ -826,7 +827,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
           if (VK == 2 && VG == 4) {
             asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dp), "l"(fs));
             asm volatile("cp.async.ca.shared.global [%0+256], [%1], 8;" ::"r"(dp), "l"(fo));
-          } else if (VK == 2 && VG == 1) {
+          } else if (VK != 1 && VG == 1) {
             if (lane < 16) {
               asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dp), "l"(fs));
               asm volatile("cp.async.ca.shared.global [%0+64], [%1], 4;" ::"r"(dp), "l"(fo));
@@ -1437,6 +1438,24 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
       mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1); \
     }                                                                                                      \
   }
+/* 2-bit values with ONE group of 128 channels: a token pair's scales (offsets) are one 32-bit word */     \
+#define INQ_PV1(U)                                                                                         \
+  {                                                                                                        \
+    const unsigned t0 = movmatrix_trans(pack_half2(pr[U][0], pr[U][1]));                                   \
+    const unsigned t1 = movmatrix_trans(pack_half2(pr[U][2], pr[U][3]));                                   \
+    const unsigned sp = stage + kStageK + kStageV + 4 * j;                                                 \
+    const unsigned b0 = hmul2_bits(t0, lds32<32 * (U)>(sp)), b1 = hmul2_bits(t1, lds32<32 * (U) + 16>(sp)); \
+    mma_f16(oacc, lds32<kStageP / 2 + 32 * (U)>(sp), 0u, lds32<kStageP / 2 + 32 * (U) + 16>(sp), 0u, t0, t1); \
+    const uint4 M = ldsm4_trans<kStageK + 512 * (U)>(stage + v_ldsm);                                      \
+    _Pragma("unroll") for (int gr = 0; gr < 2; ++gr) {                                                     \
+      const unsigned M0 = gr ? M.z : M.x, M1 = gr ? M.w : M.y;                                             \
+      const unsigned N0 = M0 >> 10, N1 = M1 >> 10;                                                         \
+      mma_f16(acc[gr * 4 + 0], M0 & 0x00030003u, M0 & 0x000C000Cu, M1 & 0x00030003u, M1 & 0x000C000Cu, b0, b1); \
+      mma_f16(acc[gr * 4 + 1], M0 & 0x00300030u, M0 & 0x00C000C0u, M1 & 0x00300030u, M1 & 0x00C000C0u, b0, b1); \
+      mma_f16(acc[gr * 4 + 2], M0 & 0x03000300u, N0 & 0x00030003u, M1 & 0x03000300u, N1 & 0x00030003u, b0, b1); \
+      mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1); \
+    }                                                                                                      \
+  }
 #define INQ_PVK(BASE, LO, HI)                                                                              \
   {                                                                                                        \
     mma_f16(bacc[BASE], (LO) & 0x000F000Fu, (LO) & 0x00F000F0u, (HI) & 0x000F000Fu, (HI) & 0x00F000F0u, t0, t1); \
@@ -1509,11 +1528,15 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
           l_blk[0] += pr[u][0] + pr[u][2];
           l_blk[1] += pr[u][1] + pr[u][3];
         }
+      } else if (VG == 1) {
+        INQ_PV1(0)
+        INQ_PV1(1)
       } else {
       INQ_PV(0)
       if (kSub > 1) INQ_PV(1)
       }
 #undef INQ_PV
+#undef INQ_PV1
 #undef INQ_PVK
       if (++cur_slice == spb) {
         cur_slice = 0;
@@ -1565,8 +1588,8 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
   float* wout = (float*)ring;   // [8][132]
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
-    const int gr = VK == 2 ? (mt >> 1) * VG / 4 : mt >> 2, q = mt & 3;   // value group of the accumulator
-    const int ch = VK ? 32 * (mt >> 1) + 4 * r + 2 * (mt & 1) : 64 * gr + 8 * r + 2 * q;
+    const int gr = VK == 2 ? (mt >> 1) * VG / 4 : VG == 1 ? 0 : mt >> 2, q = mt & 3;   // value group of the accumulator
+    const int ch = VK ? 32 * (mt >> 1) + 4 * r + 2 * (mt & 1) : 64 * (mt >> 2) + 8 * r + 2 * q;
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int g = 2 * j + e;
@@ -1744,7 +1767,8 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
 
 #undef SEQ
 static int smem_bytes(int groups, int sub, int vk = 0, int vg = 2) {
-  const int stage = vk == 2 ? (vg == 1 ? SliceCfg<2, 2, 1>::kStageBytes : vg == 2 ? SliceCfg<2, 2, 2>::kStageBytes : SliceCfg<2, 2, 4>::kStageBytes)
+  const int stage = vk == 0 && vg == 1 ? SliceCfg<2, 0, 1>::kStageBytes
+                  : vk == 2 ? (vg == 1 ? SliceCfg<2, 2, 1>::kStageBytes : vg == 2 ? SliceCfg<2, 2, 2>::kStageBytes : SliceCfg<2, 2, 4>::kStageBytes)
                   : vk ? SliceCfg<2, 1>::kStageBytes : (sub == 1 ? SliceCfg<1>::kStageBytes : SliceCfg<2>::kStageBytes);
   return kQBytes + kWarps * warp_smem_bytes(groups, stage, vk == 1);
 }
@@ -1757,7 +1781,7 @@ using namespace inq;
 // device, not to the process: a process that drives several GPUs (or several host threads) gets
 // one record per device ordinal, filled under a mutex on first use.
 constexpr int kMaxDevices = 64;
-constexpr int kKernelVariants = 28;   // 16 general instances, 4 of the whole-slice fast path, 2 with coded values, 6 with 4-bit values
+constexpr int kKernelVariants = 30;   // 16 general, 4 whole-slice, 2 coded values, 6 4-bit values, 2 2-bit values in one group
 struct DeviceState {
   int sm_count = 0;
   bool raised[kKernelVariants] = {};
@@ -1878,14 +1902,20 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
       // 4-bit values in 1, 2 or 4 groups
       decode_kernel<0, __half, true, 2, true, 2, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 1>,
       decode_kernel<0, __half, true, 2, true, 2, 2>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 2>,
-      decode_kernel<0, __half, true, 2, true, 2, 4>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 4>};
+      decode_kernel<0, __half, true, 2, true, 2, 4>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 4>,
+      // 2-bit values in one group of 128 channels
+      decode_kernel<0, __half, true, 2, true, 0, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 0, 1>};
   const bool fast = a->n_pad == 16 && a->block_tokens % 32 == 0 && a->block_tokens >= 128;
   const int vk = a->value_kind, vg = a->value_groups;
-  if (vk < 0 || vk > 2 || (vk == 2 && vg != 1 && vg != 2 && vg != 4)) return INQ_ERR_ARGUMENT;
+  if (vk < 0 || vk > 2 || (vk == 2 && vg != 1 && vg != 2 && vg != 4) || (vk == 0 && vg != 0 && vg != 1 && vg != 2))
+    return INQ_ERR_ARGUMENT;
+  const bool one_group = vk == 0 && vg == 1;   // 2-bit values, one group of 128 channels
+  if (one_group && !(fast && a->layout == 0)) return INQ_ERR_UNSUPPORTED;
   // coded values are served for the whole-slice geometry of the table layout with 16 salient channels
   // on either side; every other combination is inq_decode_generic's
   if (vk && !(fast && a->layout == 0)) return INQ_ERR_UNSUPPORTED;
-  const int which = vk == 2 ? 22 + (vg == 1 ? 0 : vg == 2 ? 2 : 4) + (a->dtype == INQ_F16 ? 0 : 1)
+  const int which = one_group ? 28 + (a->dtype == INQ_F16 ? 0 : 1)
+                  : vk == 2 ? 22 + (vg == 1 ? 0 : vg == 2 ? 2 : 4) + (a->dtype == INQ_F16 ? 0 : 1)
                   : vk ? 20 + (a->dtype == INQ_F16 ? 0 : 1)
                   : fast ? 16 + a->layout * 2 + (a->dtype == INQ_F16 ? 0 : 1)
                          : (sub == 1 ? 8 : 0) + a->layout * 4 + (a->dtype == INQ_F16 ? 0 : 2) + (groups > 0 ? 1 : 0);

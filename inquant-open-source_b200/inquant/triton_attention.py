@@ -251,7 +251,10 @@ class PackedDecodeState:
         # ... and so do 4-bit values in groups of 32, 64 or 128 channels
         wide_values = bool(n_blocks) and not self._inquant_values and self._value_bits == 4 and self._salient == 16 \
             and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128
-        if query.dtype == torch.float32 or (n_blocks and not self._preset and not coded_values and not wide_values):
+        whole_slices = bool(n_blocks) and self._salient == 16 and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128
+        one_group = whole_slices and not self._inquant_values and (self._value_bits, self._value_group) == (2, 128)
+        if query.dtype == torch.float32 or (n_blocks and not self._preset and not coded_values and not wide_values
+                                            and not one_group):
             return self._decode_general(query, kv_heads, q_per_kv, n_blocks, sink_key, sink_value, sink_t,
                                         residual_key, residual_value, residual_t, scale)
         tiles = (q_per_kv + 7) // 8
@@ -292,7 +295,7 @@ class PackedDecodeState:
         args.block_tokens, args.n_pad = self._packed_tokens, self._salient
         args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[query.dtype], scale
         args.value_kind = 1 if coded_values else 2 if wide_values else 0
-        args.value_groups = 128 // self._value_group if wide_values else 0
+        args.value_groups = 128 // self._value_group if wide_values else 1 if one_group else 0
         args.partials, args.partials_floats = workspace.data_ptr(), workspace.numel()
         args.counters = N.decode_counters(query.device, kv_heads * tiles).data_ptr()
         args.status = N.status_word(query.device).data_ptr()

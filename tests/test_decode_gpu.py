@@ -308,21 +308,22 @@ def test_values_stored_as_inquant_tensors_run_the_streaming_kernel(dtype, q_head
     assert N.take_status(torch.device("cuda", 0)) == 0
 
 
-@pytest.mark.parametrize("group,dtype,q_heads,heads,block,blocks,tail", [
-    (64, "bfloat16", 28, 4, 256, 3, 281), (32, "float16", 14, 2, 256, 5, 17), (128, "bfloat16", 8, 2, 128, 7, 0),
-    (32, "bfloat16", 12, 1, 256, 40, 300)])
-def test_four_bit_values_run_the_streaming_kernel(group, dtype, q_heads, heads, block, blocks, tail):
-    """4-bit values in groups of 32, 64 or 128 channels (value_codec.py with bits=4) on the one-launch
-    kernel: checked against the oracle's dequantised values and the general kernel's output."""
+@pytest.mark.parametrize("bits,group,dtype,q_heads,heads,block,blocks,tail", [
+    (4, 64, "bfloat16", 28, 4, 256, 3, 281), (4, 32, "float16", 14, 2, 256, 5, 17), (4, 128, "bfloat16", 8, 2, 128, 7, 0),
+    (4, 32, "bfloat16", 12, 1, 256, 40, 300), (2, 128, "bfloat16", 28, 4, 256, 3, 281), (2, 128, "float16", 8, 2, 128, 9, 5)])
+def test_four_bit_values_run_the_streaming_kernel(bits, group, dtype, q_heads, heads, block, blocks, tail):
+    """4-bit values in groups of 32, 64 or 128 channels and 2-bit values in one group of 128
+    (value_codec.py) on the one-launch kernel: checked against the oracle's dequantised values and
+    the general kernel's output."""
     CodecConfig, quantize, quantize_values, PackedDecodeState, _, _ = _mods()
     cfg = CodecConfig(salient_fraction=0.125, donor_policy="min_error")
     boost_k = np.where((np.arange(128) >= 5) & (np.arange(128) < 8), 12, 1).astype(np.float32)
     ks = [oracle.round_to_dtype(_random(700 + i, (1, heads, block, 128), dtype) * boost_k, dtype) for i in range(blocks)]
     vs = [oracle.round_to_dtype(_random(800 + i, (1, heads, block, 128), dtype) + 0.5, dtype) for i in range(blocks)]
     keys = [quantize(to_device(k, dtype), cfg) for k in ks]
-    values = [quantize_values(to_device(v, dtype), 4, group) for v in vs]
+    values = [quantize_values(to_device(v, dtype), bits, group) for v in vs]
     dense_k = [oracle.dequantize_k4(oracle.quantize_k4(k, dtype, 8, 0.125, "min_error"))[0] for k in ks]
-    dense_v = [oracle.dequantize_values(oracle.quantize_values(v, dtype, 4, group))[0] for v in vs]
+    dense_v = [oracle.dequantize_values(oracle.quantize_values(v, dtype, bits, group))[0] for v in vs]
     sink_k, sink_v = _random(1, (1, heads, 4, 128), dtype), _random(2, (1, heads, 4, 128), dtype)
     q = _random(5, (q_heads, 128), dtype)
     args = dict(sink_key=to_device(sink_k, dtype), sink_value=to_device(sink_v, dtype))
