@@ -99,10 +99,14 @@ class DecodeBatch:
             self.layout = sequences[0].layout
             self.device = sequences[0].pool.device
             self.kv_heads = self.layout.heads
+            self.value_kind, self.value_groups = 0, 0
         else:
             with_blocks = [s.decode_state for s in sequences if s.decode_state.key_blocks]
-            if any(not state._preset for state in with_blocks):
-                raise NotImplementedError("batched decode runs the K4/V2 preset (2-bit values in groups of 64) only")
+            kinds = {state.streaming_value_kind() for state in with_blocks}
+            if None in kinds or len(kinds) > 1:
+                raise NotImplementedError("batched decode needs one value codec that the streaming kernel serves "
+                                          "(PackedDecodeState.streaming_value_kind)")
+            self.value_kind, self.value_groups = kinds.pop() if kinds else (0, 0)
             first = with_blocks[0] if with_blocks else sequences[0].decode_state
             self.device = sequences[0].tail_key_buffer.device
             self.kv_heads = sequences[0].tail_key_buffer.shape[1]
@@ -202,6 +206,7 @@ class DecodeBatch:
             n_blocks = len(st.key_blocks)
             d.table = st._tables.data_ptr() if n_blocks else None
             d.roles = st._key_map.data_ptr() if n_blocks else None
+            d.value_roles = st._value_map.data_ptr() if n_blocks and self.value_kind == 1 else None
             d.n_blocks = n_blocks
             if s.sink_key is not None and s.sink_key.shape[2]:
                 for t in (s.sink_key, s.sink_value):
@@ -244,6 +249,7 @@ class DecodeBatch:
         args.kv_heads, args.q_per_kv = self.kv_heads, self.q_per_kv
         args.block_tokens, args.n_pad = self.block_tokens, self.n_pad
         args.layout, args.dtype, args.scale = int(self.paged), N.DTYPE_CODE[self.dtype], self.scale
+        args.value_kind, args.value_groups = self.value_kind, self.value_groups
         if self.paged:
             from inquant_vllm.kernels import page_offsets_array
             args.page_bytes, args.page_offsets = self.layout.page_bytes, page_offsets_array(self.layout)
@@ -346,8 +352,14 @@ class DecodeBatch:
         packed = meta = dense = 0
         for s in self.sequences:
             nb = self._blocks_of(s)
-            packed += h * nb * t * (64 + 32 + 8)
-            meta += h * nb * (832 if self.paged else 512 + self.n_pad * 2 + self.n_pad * 4)
+            if self.value_kind == 1:       # values coded like the keys
+                value_row, value_meta = 64, 512 + 16 * 2 + 16 * 4
+            elif self.value_kind == 2:     # 4-bit codes, fp16 scale and offset per token and group
+                value_row, value_meta = 64 + 4 * self.value_groups, 0
+            else:                          # 2-bit codes in two groups (or one)
+                value_row, value_meta = 32 + 4 * (self.value_groups or 2), 0
+            packed += h * nb * t * (64 + value_row)
+            meta += h * nb * ((832 if self.paged else 512 + self.n_pad * 2 + self.n_pad * 4) + value_meta)
             sink = s.sink_count if self.paged else (0 if s.sink_key is None else s.sink_key.shape[2])
             dense += (sink + s.tail_count + self._appended) * h * 128 * es * 2
         qo = len(self.sequences) * self.q_heads * 128 * es * 2

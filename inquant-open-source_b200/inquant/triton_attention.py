@@ -197,6 +197,24 @@ class PackedDecodeState:
         return sum(t.numel() * t.element_size() for t in
                    (self._tables, self._key_map, self._value_map, self._workspace) if t is not None)
 
+    def streaming_value_kind(self):
+        """``(value_kind, value_groups)`` of ``inq_decode_attention`` for this state's value codec, or
+        ``None`` when only the general kernel serves it.  The preset (2-bit values in groups of 64) runs
+        every geometry; values stored as InQuant packed tensors (the reference's default), 4-bit values in
+        groups of 32 / 64 / 128 and 2-bit values in one group of 128 run it when both sides have 16
+        salient channels and the blocks are whole 32-token slices (at least four)."""
+        if self._preset:
+            return 0, 0
+        if not (self._salient == 16 and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128):
+            return None
+        if self._inquant_values:
+            return (1, 0) if self._value_salient == 16 else None
+        if self._value_bits == 4:
+            return 2, 128 // self._value_group
+        if (self._value_bits, self._value_group) == (2, 128):
+            return 0, 1
+        return None
+
     @torch.no_grad()
     def decode(self, query, *, sink_key=None, sink_value=None, residual_key=None, residual_value=None, scale=None):
         if query.ndim != 4 or query.shape[0] != 1 or query.shape[1] < 1 or query.shape[-2:] != (1, 128):
@@ -244,17 +262,8 @@ class PackedDecodeState:
         if self._stream_identity is not None and self._stream_identity != identity:
             raise RuntimeError("Packed decode state requires one CUDA stream per state")
         q_per_kv = query.shape[1] // kv_heads
-        # values stored as InQuant packed tensors (the reference's default) run the streaming kernel too
-        # when both sides have 16 salient channels and the blocks are whole 32-token slices
-        coded_values = bool(n_blocks) and self._inquant_values and self._salient == 16 and self._value_salient == 16 \
-            and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128
-        # ... and so do 4-bit values in groups of 32, 64 or 128 channels
-        wide_values = bool(n_blocks) and not self._inquant_values and self._value_bits == 4 and self._salient == 16 \
-            and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128
-        whole_slices = bool(n_blocks) and self._salient == 16 and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128
-        one_group = whole_slices and not self._inquant_values and (self._value_bits, self._value_group) == (2, 128)
-        if query.dtype == torch.float32 or (n_blocks and not self._preset and not coded_values and not wide_values
-                                            and not one_group):
+        kind = self.streaming_value_kind() if n_blocks else (0, 0)
+        if query.dtype == torch.float32 or kind is None:
             return self._decode_general(query, kv_heads, q_per_kv, n_blocks, sink_key, sink_value, sink_t,
                                         residual_key, residual_value, residual_t, scale)
         tiles = (q_per_kv + 7) // 8
@@ -279,7 +288,7 @@ class PackedDecodeState:
         seq.query, seq.output, seq.query_head_stride = query.data_ptr(), output.data_ptr(), query.stride(1)
         seq.table = self._tables.data_ptr() if n_blocks else None
         seq.roles = self._key_map.data_ptr() if n_blocks else None
-        seq.value_roles = self._value_map.data_ptr() if coded_values else None
+        seq.value_roles = self._value_map.data_ptr() if kind[0] == 1 else None
         if sink_t:
             seq.sink_key, seq.sink_value = sink_key.data_ptr(), sink_value.data_ptr()
             seq.sink_key_stride_h, seq.sink_key_stride_t = sink_key.stride(1), sink_key.stride(2)
@@ -294,8 +303,7 @@ class PackedDecodeState:
         args.kv_heads, args.q_per_kv = kv_heads, q_per_kv
         args.block_tokens, args.n_pad = self._packed_tokens, self._salient
         args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[query.dtype], scale
-        args.value_kind = 1 if coded_values else 2 if wide_values else 0
-        args.value_groups = 128 // self._value_group if wide_values else 1 if one_group else 0
+        args.value_kind, args.value_groups = kind
         args.partials, args.partials_floats = workspace.data_ptr(), workspace.numel()
         args.counters = N.decode_counters(query.device, kv_heads * tiles).data_ptr()
         args.status = N.status_word(query.device).data_ptr()

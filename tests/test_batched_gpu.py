@@ -82,6 +82,45 @@ def test_table_batch_matches_per_sequence_decode_oracle_and_graph_replay():
             batch.step()
 
 
+@pytest.mark.parametrize("value_bits,group", [(None, 64), (4, 32), (4, 128), (2, 128)])
+def test_table_batch_of_other_value_codecs_matches_per_sequence_decode(value_bits, group):
+    """Values stored as InQuant packed tensors (the reference's default), 4-bit values and 2-bit values in one
+    group: the batched one-launch step (new token appended by the launch, CUDA-graph replay) equals the
+    per-sequence decode over the same caches, which the decode tests check against the oracle."""
+    from inquant.batched import DecodeBatch, SequenceState
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.triton_attention import PackedDecodeState
+    from inquant import _native as N
+    lengths = (900, 1300, 2100)
+    caches = []
+    for i, tokens in enumerate(lengths):
+        k, v = workloads.make_kv(30 + i, 4, tokens)
+        cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=128, residual_length=64,
+                                         sink_tokens=4, value_bits=value_bits, value_group_size=group, validate_positions=False))
+        cache.update(to_device(k), to_device(v), 0)
+        caches.append(cache)
+    seqs = [SequenceState.from_cache_layer(c, 0) for c in caches]
+    batch = DecodeBatch(seqs, 28, torch.bfloat16)
+    assert (batch.value_kind, batch.value_groups) == {None: (1, 0), 4: (2, 128 // group), 2: (0, 1)}[value_bits]
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    steps = torch.randn((4, len(lengths), 28 + 8, 128), device="cuda", generator=gen).bfloat16()
+    for step in range(4):
+        batch.inputs.copy_(steps[step])
+        if step == 2:
+            batch.capture()
+        out = batch.replay() if step >= 2 else batch.step()
+        torch.cuda.synchronize()
+        for i, cache in enumerate(caches):
+            layer = cache._layers[0]
+            n = batch.tail_tokens[i]
+            single = PackedDecodeState(layer.key_blocks, layer.value_blocks).decode(
+                batch.queries[i].unsqueeze(0).unsqueeze(2).contiguous(), sink_key=layer.sink_key, sink_value=layer.sink_value,
+                residual_key=layer.tail_key_buffer[:, :, :n], residual_value=layer.tail_value_buffer[:, :, :n])
+            attention_close(to_numpy(single.float()).reshape(28, 128), to_numpy(out[i].float()), max_abs=8e-3, cosine=0.99999)
+    assert N.take_status(batch.device) == 0
+
+
 @pytest.mark.parametrize("block,heads,q_heads", [(16, 8, 32), (64, 4, 28)])
 def test_paged_batch_of_requests_with_different_lengths(block, heads, q_heads):
     """Batched paged decode: requests of seeded lengths, shuffled physical pages, one launch."""
