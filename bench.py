@@ -390,6 +390,66 @@ def encoder_kernels_us(torch, k, v):
     return e0.elapsed_time(e1) / 10 * 1e3
 
 
+def value_codecs_leg(torch, device):
+    """One layer of config 1 under every value codec the one-launch kernel serves: the preset (2-bit,
+    groups of 64), values stored as InQuant packed tensors (the reference's `CacheConfig` default),
+    4-bit values in groups of 64 and 32, 2-bit values in one group of 128.  Ten decodes per CUDA-graph
+    replay, device time per launch; each output is compared with the general kernel's for the same state
+    (the tests hold both against the oracle)."""
+    import workloads
+    from inquant.cache import CacheConfig, InQuantCache
+    from inquant.codec import CodecConfig
+    from inquant.triton_attention import PackedDecodeState
+    k, v = workloads.make_kv_torch(77, KV_HEADS, CONTEXT, device)
+    gen = torch.Generator(device=device).manual_seed(78)
+    q = torch.randn((1, Q_HEADS, 1, DIM), device=device, generator=gen).bfloat16()
+    out = {}
+    codecs = (("k4_v2_g64", dict(value_bits=2, value_group_size=64)), ("k4_values_as_inquant_tensors", dict(value_bits=None)),
+              ("k4_v4_g64", dict(value_bits=4, value_group_size=64)), ("k4_v4_g32", dict(value_bits=4, value_group_size=32)),
+              ("k4_v2_g128", dict(value_bits=2, value_group_size=128)))
+    for name, kw in codecs:
+        cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=BLOCK, residual_length=RESIDUAL,
+                                         sink_tokens=SINK, validate_positions=False, **kw))
+        cache.update(k, v, 0)
+        layer = cache._layers[0]
+        dense = dict(sink_key=layer.sink_key, sink_value=layer.sink_value, residual_key=layer.residual_key,
+                     residual_value=layer.residual_value)
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            state = PackedDecodeState(layer.key_blocks, layer.value_blocks)
+            for _ in range(3):
+                result = state.decode(q, **dense)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(10):
+                    result = state.decode(q, **dense)
+            graph.replay()
+            side.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            for _ in range(5):
+                graph.replay()
+            e1.record(side)
+            side.synchronize()
+            general = state._decode_general(q, KV_HEADS, Q_HEADS // KV_HEADS, len(layer.key_blocks), layer.sink_key, layer.sink_value,
+                                            layer.sink_key.shape[2], layer.residual_key, layer.residual_value,
+                                            layer.residual_key.shape[2], DIM ** -0.5)
+            side.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / 50
+        nbytes = sum(b.nbytes for b in layer.key_blocks) + sum(b.nbytes for b in layer.value_blocks)
+        diff = float((result.float() - general.float()).abs().max())
+        if not diff < PARITY_MAX_ABS:
+            raise ParityError(f"value codec {name}: one-launch kernel and general kernel differ by {diff:.3e}")
+        out[name] = {"us_per_layer": round(us, 2), "packed_mb": round(nbytes / 1e6, 2), "packed_gbs": round(nbytes / us / 1e3, 1),
+                     "streaming_value_kind": list(state.streaming_value_kind()), "max_abs_vs_general_kernel": round(diff, 6)}
+        del cache, state, graph
+    out["note"] = ("one layer (14-19 MB) stays in the 126 MB L2 between the replays: these are L2-warm times, to be compared "
+                   "with one another and with reference_gpu.warm, not with the 28-layer figures")
+    return out
+
+
 def reference_gpu_leg(torch, device):
     """One layer of config 1 through the UNMODIFIED reference on this GPU (installed under
     oracle/_ref): its torch CUDA encoders against this library's encoders byte by byte, and its
@@ -757,6 +817,9 @@ def run_cuda(args):
     if world == 1 and args.model_step:
         torch.cuda.empty_cache()
         line["model_step"] = run_model_step(args, torch, device)
+    if rank == 0 and world == 1 and not args.no_value_codecs:
+        torch.cuda.empty_cache()
+        line["value_codecs"] = value_codecs_leg(torch, device)
     if rank == 0 and world == 1 and not args.no_reference_gpu:
         torch.cuda.empty_cache()
         try:
@@ -1353,6 +1416,7 @@ def main():
                         help="--impl reference: time the numpy port of the reference even when oracle/_ref holds the reference itself")
     parser.add_argument("--no-append-sequence", action="store_true",
                         help="skip the 136-step append sequence that crosses a block seal (config 1)")
+    parser.add_argument("--no-value-codecs", action="store_true", help="skip the one-layer leg over the other value codecs")
     parser.add_argument("--no-reference-gpu", action="store_true",
                         help="skip the leg that runs the reference's Triton decode kernel beside this library's")
     parser.add_argument("--sustained-seconds", type=float, default=2.5,

@@ -21,7 +21,8 @@ CUDA graph and replays it per token.  What makes the step replayable:
 When a tail is about to reach the length at which the cache seals a block, the step is run
 eagerly once through the ordinary patched forward (which seals exactly as
 ``InQuantCache.append_for_attention`` does) and the graph is recorded again over the new block
-list.  K4/V2 preset caches, batch 1, fp16/bf16 models.
+list.  Caches whose value codec the one-launch kernel serves (``PackedDecodeState.streaming_value_kind``),
+batch 1, fp16/bf16 models.
 """
 from __future__ import annotations
 
