@@ -549,7 +549,13 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
   const unsigned char* const d_pool = SEQ(pool);
   const int* const d_pages = SEQ(page_table);
   const int d_pool_pages = SEQ(pool_pages);
-  const signed char* const d_vroles = VK == 1 ? SEQ(value_roles) : nullptr;
+  // coded values without their role map: never dereferenced, the key map stands in and the caller
+  // learns of it from the status word
+  const signed char* d_vroles = VK == 1 ? SEQ(value_roles) : nullptr;
+  if (VK == 1 && d_vroles == nullptr) {
+    if (threadIdx.x == 0) atomicOr(P.status, INQ_STATUS_BAD_INDEX);
+    d_vroles = d_roles;
+  }
   const int first_visible = SEQ(first_visible);
   // (loaded here, ahead of the barriers of the query staging, so that their latency overlaps it)
   const int T = P.T;
@@ -1914,6 +1920,8 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   // coded values are served for the whole-slice geometry of the table layout with 16 salient channels
   // on either side; every other combination is inq_decode_generic's
   if (vk && !(fast && a->layout == 0)) return INQ_ERR_UNSUPPORTED;
+  if (vk == 1 && !a->seqs_device && ((const SeqDesc*)a->seq_host)->n_blocks > 0 && !((const SeqDesc*)a->seq_host)->value_roles)
+    return INQ_ERR_ARGUMENT;
   const int which = one_group ? 28 + (a->dtype == INQ_F16 ? 0 : 1)
                   : vk == 2 ? 22 + (vg == 1 ? 0 : vg == 2 ? 2 : 4) + (a->dtype == INQ_F16 ? 0 : 1)
                   : vk ? 20 + (a->dtype == INQ_F16 ? 0 : 1)

@@ -11,15 +11,15 @@ from helpers import attention_close, to_device, to_numpy
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("world", [1, 2, 3, 8])
-def test_emulated_ranks_merge_to_the_unsplit_result(world):
+@pytest.mark.parametrize("world,value_bits,block", [(1, 2, 64), (2, 2, 64), (3, 2, 64), (8, 2, 64), (3, None, 128), (2, 4, 128)])
+def test_emulated_ranks_merge_to_the_unsplit_result(world, value_bits, block):
     from inquant.batched import DecodeBatch, SequenceState
     from inquant.cache import CacheConfig, InQuantCache
     from inquant.codec import CodecConfig
     from inquant.split_kv import merge_records, shard_layer
     heads, q_heads, layers = 4, 28, 3
-    cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=64, residual_length=32,
-                                     sink_tokens=4, value_bits=2, validate_positions=False))
+    cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=block, residual_length=32,
+                                     sink_tokens=4, value_bits=value_bits, validate_positions=False))
     for layer, tokens in enumerate((1000, 1000, 1000)):
         k, v = workloads.make_kv(40 + layer, heads, tokens)
         cache.update(to_device(k), to_device(v), layer)
