@@ -393,7 +393,7 @@ def encoder_kernels_us(torch, k, v):
 def value_codecs_leg(torch, device):
     """One layer of config 1 under every value codec the one-launch kernel serves: the preset (2-bit,
     groups of 64), values stored as InQuant packed tensors (the reference's `CacheConfig` default),
-    4-bit values in groups of 64 and 32, 2-bit values in one group of 128.  Ten decodes per CUDA-graph
+    4-bit values in groups of 64 and 32, 2-bit values in groups of 128 and 32.  Ten decodes per CUDA-graph
     replay, device time per launch; each output is compared with the general kernel's for the same state
     (the tests hold both against the oracle)."""
     import workloads
@@ -406,7 +406,7 @@ def value_codecs_leg(torch, device):
     out = {}
     codecs = (("k4_v2_g64", dict(value_bits=2, value_group_size=64)), ("k4_values_as_inquant_tensors", dict(value_bits=None)),
               ("k4_v4_g64", dict(value_bits=4, value_group_size=64)), ("k4_v4_g32", dict(value_bits=4, value_group_size=32)),
-              ("k4_v2_g128", dict(value_bits=2, value_group_size=128)))
+              ("k4_v2_g128", dict(value_bits=2, value_group_size=128)), ("k4_v2_g32", dict(value_bits=2, value_group_size=32)))
     for name, kw in codecs:
         cache = InQuantCache(CacheConfig(CodecConfig(donor_policy="min_error"), block_size=BLOCK, residual_length=RESIDUAL,
                                          sink_tokens=SINK, validate_positions=False, **kw))

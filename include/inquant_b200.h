@@ -285,7 +285,8 @@ typedef struct {
                              *    hold payload [kv_heads][tokens][64], scales and offsets
                              *    [kv_heads][tokens][value_groups]; same geometry limits as kind 1 */
   int32_t value_groups;     /* kind 2: 1, 2 or 4 (groups of 128, 64 or 32 channels); kind 0: 0 or 2 for the
-                             * groups of 64 channels, 1 for one group of 128 (geometry limits of kind 1) */
+                             * groups of 64 channels, 1 for one group of 128, 4 for groups of 32 (geometry limits
+                             * of kind 1) */
 } inq_decode_args_t;
 int inq_decode_attention(const inq_decode_args_t* args /* host */, inq_stream_t stream);
 /* The same decode step for callers that cannot allocate device memory (a serving engine that

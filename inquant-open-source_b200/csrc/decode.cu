@@ -466,8 +466,8 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
 template <int MODE, typename QT, bool SAL, int SUB, bool FAST, int VK = 0, int VG = 2>
 __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(const DecodeParams P) {
   static_assert(!VK || (FAST && MODE == 0 && SAL && SUB == 2), "coded and 4-bit values: whole-slice path of the table layout only");
-  static_assert(VK == 2 ? (VG == 1 || VG == 2 || VG == 4) : VK == 0 ? (VG == 2 || (VG == 1 && FAST && MODE == 0)) : VG == 2,
-                "4-bit values: groups of 32, 64 or 128 channels; 2-bit values: 64, or 128 on the whole-slice path");
+  static_assert(VK == 2 ? (VG == 1 || VG == 2 || VG == 4) : VK == 0 ? (VG == 2 || ((VG == 1 || VG == 4) && FAST && MODE == 0)) : VG == 2,
+                "4-bit values: groups of 32, 64 or 128 channels; 2-bit values: 64, or 32 and 128 on the whole-slice path");
   constexpr int kSub = SUB;
   constexpr int kSliceTokens = SliceCfg<SUB, VK, VG>::kSliceTokens;
   constexpr int kStageK = SliceCfg<SUB, VK, VG>::kStageK, kStageV = SliceCfg<SUB, VK, VG>::kStageV, kStageP = SliceCfg<SUB, VK, VG>::kStageP;
@@ -800,7 +800,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
     // offset pairs), the shared-memory address of the stage it goes to, slices left in its block
     const unsigned char* fk = pf_ptrs.kp + pf_slice * 2048 + lane * 16;
     const unsigned char* fv = pf_ptrs.vp + pf_slice * (VK ? 2048 : 1024) + lane * 16;
-    constexpr int kParamLane = VK == 2 && VG == 4 ? 8 : 4;   // bytes of a parameter array one lane copies per slice
+    constexpr int kParamLane = VK != 1 && VG == 4 ? 8 : 4;   // bytes of a parameter array one lane copies per slice
     const unsigned char* fs = pf_ptrs.vs + pf_slice * (kStageP / 2) + lane * kParamLane;
     const unsigned char* fo = pf_ptrs.vo + pf_slice * (kStageP / 2) + lane * kParamLane;
     const unsigned ring_lo = smem_addr(ring), ring_hi = ring_lo + kStages * kStageBytes;
@@ -819,7 +819,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
       if (FAST) {
         if (to_issue > 0) {
           const unsigned dk = issue_addr + lane * 16, dv = issue_addr + fast_v_dst;
-          const unsigned dp = issue_addr + kStageK + kStageV + lane * (VK == 2 && VG == 4 ? 8 : 4);
+          const unsigned dp = issue_addr + kStageK + kStageV + lane * (VK != 1 && VG == 4 ? 8 : 4);
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dk), "l"(fk));
           asm volatile("cp.async.cg.shared.global [%0+512], [%1+512], 16;" ::"r"(dk), "l"(fk));
           asm volatile("cp.async.cg.shared.global [%0+1024], [%1+1024], 16;" ::"r"(dk), "l"(fk));
@@ -830,7 +830,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
             asm volatile("cp.async.cg.shared.global [%0+1024], [%1+1024], 16;" ::"r"(dv), "l"(fv));
             asm volatile("cp.async.cg.shared.global [%0+1536], [%1+1536], 16;" ::"r"(dv), "l"(fv));
           }
-          if (VK == 2 && VG == 4) {
+          if (VK != 1 && VG == 4) {
             asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dp), "l"(fs));
             asm volatile("cp.async.ca.shared.global [%0+256], [%1], 8;" ::"r"(dp), "l"(fo));
           } else if (VK != 1 && VG == 1) {
@@ -1462,6 +1462,36 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
       mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1); \
     }                                                                                                      \
   }
+/* 2-bit values in FOUR groups of 32 channels: a group is four of the eight 16-bit words of a value MMA's     \
+   rows, so every MMA is issued twice, once with rows r < 4 (the others zeroed) against the probabilities     \
+   scaled for the lower group and once with rows r >= 4 against those of the upper group */                  \
+#define INQ_PV4(U)                                                                                         \
+  {                                                                                                        \
+    const unsigned t0 = movmatrix_trans(pack_half2(pr[U][0], pr[U][1]));                                   \
+    const unsigned t1 = movmatrix_trans(pack_half2(pr[U][2], pr[U][3]));                                   \
+    const unsigned sp = stage + kStageK + kStageV + 16 * j;                                                \
+    const uint4 sa = lds128<128 * (U)>(sp), sb = lds128<128 * (U) + 64>(sp);                               \
+    const uint4 oa = lds128<kStageP / 2 + 128 * (U)>(sp), ob = lds128<kStageP / 2 + 128 * (U) + 64>(sp);   \
+    const bool upper = (r & 2) != 0, low_rows = r < 4;                                                     \
+    mma_f16(oacc, __byte_perm(upper ? oa.y : oa.x, upper ? oa.w : oa.z, vsel), 0u,                          \
+            __byte_perm(upper ? ob.y : ob.x, upper ? ob.w : ob.z, vsel), 0u, t0, t1);                      \
+    const uint4 M = ldsm4_trans<kStageK + 512 * (U)>(stage + v_ldsm);                                      \
+    _Pragma("unroll") for (int gr = 0; gr < 2; ++gr) {                                                     \
+      const unsigned w0 = gr ? sa.y : sa.x, w1 = gr ? sa.w : sa.z, w2 = gr ? sb.y : sb.x, w3 = gr ? sb.w : sb.z; \
+      _Pragma("unroll") for (int half = 0; half < 2; ++half) {                                             \
+        const unsigned gsel2 = half ? 0x7632u : 0x5410u;                                                   \
+        const unsigned b0 = hmul2_bits(t0, __byte_perm(w0, w1, gsel2));                                    \
+        const unsigned b1 = hmul2_bits(t1, __byte_perm(w2, w3, gsel2));                                    \
+        const bool mine = half ? !low_rows : low_rows;                                                     \
+        const unsigned M0 = mine ? (gr ? M.z : M.x) : 0u, M1 = mine ? (gr ? M.w : M.y) : 0u;               \
+        const unsigned N0 = M0 >> 10, N1 = M1 >> 10;                                                       \
+        mma_f16(acc[gr * 4 + 0], M0 & 0x00030003u, M0 & 0x000C000Cu, M1 & 0x00030003u, M1 & 0x000C000Cu, b0, b1); \
+        mma_f16(acc[gr * 4 + 1], M0 & 0x00300030u, M0 & 0x00C000C0u, M1 & 0x00300030u, M1 & 0x00C000C0u, b0, b1); \
+        mma_f16(acc[gr * 4 + 2], M0 & 0x03000300u, N0 & 0x00030003u, M1 & 0x03000300u, N1 & 0x00030003u, b0, b1); \
+        mma_f16(acc[gr * 4 + 3], N0 & 0x000C000Cu, N0 & 0x00300030u, N1 & 0x000C000Cu, N1 & 0x00300030u, b0, b1); \
+      }                                                                                                    \
+    }                                                                                                      \
+  }
 #define INQ_PVK(BASE, LO, HI)                                                                              \
   {                                                                                                        \
     mma_f16(bacc[BASE], (LO) & 0x000F000Fu, (LO) & 0x00F000F0u, (HI) & 0x000F000Fu, (HI) & 0x00F000F0u, t0, t1); \
@@ -1537,12 +1567,16 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
       } else if (VG == 1) {
         INQ_PV1(0)
         INQ_PV1(1)
+      } else if (VG == 4) {
+        INQ_PV4(0)
+        INQ_PV4(1)
       } else {
       INQ_PV(0)
       if (kSub > 1) INQ_PV(1)
       }
 #undef INQ_PV
 #undef INQ_PV1
+#undef INQ_PV4
 #undef INQ_PVK
       if (++cur_slice == spb) {
         cur_slice = 0;
@@ -1583,7 +1617,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], off);
   }
   // the offset sums of value group gr, heads 2j and 2j+1, sit in lane (r = gr, j)
-  constexpr int kOffsetGroups = VK == 2 ? VG : 2;
+  constexpr int kOffsetGroups = VK == 2 || VG == 4 ? VG : 2;
   float osum[kOffsetGroups][2];
 #pragma unroll
   for (int gr = 0; gr < kOffsetGroups; ++gr) {
@@ -1594,7 +1628,8 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
   float* wout = (float*)ring;   // [8][132]
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
-    const int gr = VK == 2 ? (mt >> 1) * VG / 4 : VG == 1 ? 0 : mt >> 2, q = mt & 3;   // value group of the accumulator
+    const int q = mt & 3;
+    const int gr = VK == 2 ? (mt >> 1) * VG / 4 : VG == 1 ? 0 : VG == 4 ? 2 * (mt >> 2) + (r >> 2) : mt >> 2;   // value group of the accumulator
     const int ch = VK ? 32 * (mt >> 1) + 4 * r + 2 * (mt & 1) : 64 * (mt >> 2) + 8 * r + 2 * q;
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -1774,6 +1809,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
 #undef SEQ
 static int smem_bytes(int groups, int sub, int vk = 0, int vg = 2) {
   const int stage = vk == 0 && vg == 1 ? SliceCfg<2, 0, 1>::kStageBytes
+                  : vk == 0 && vg == 4 ? SliceCfg<2, 0, 4>::kStageBytes
                   : vk == 2 ? (vg == 1 ? SliceCfg<2, 2, 1>::kStageBytes : vg == 2 ? SliceCfg<2, 2, 2>::kStageBytes : SliceCfg<2, 2, 4>::kStageBytes)
                   : vk ? SliceCfg<2, 1>::kStageBytes : (sub == 1 ? SliceCfg<1>::kStageBytes : SliceCfg<2>::kStageBytes);
   return kQBytes + kWarps * warp_smem_bytes(groups, stage, vk == 1);
@@ -1787,7 +1823,7 @@ using namespace inq;
 // device, not to the process: a process that drives several GPUs (or several host threads) gets
 // one record per device ordinal, filled under a mutex on first use.
 constexpr int kMaxDevices = 64;
-constexpr int kKernelVariants = 30;   // 16 general, 4 whole-slice, 2 coded values, 6 4-bit values, 2 2-bit values in one group
+constexpr int kKernelVariants = 32;   // 16 general, 4 whole-slice, 2 coded values, 6 4-bit values, 4 2-bit values in one or four groups
 struct DeviceState {
   int sm_count = 0;
   bool raised[kKernelVariants] = {};
@@ -1909,20 +1945,21 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
       decode_kernel<0, __half, true, 2, true, 2, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 1>,
       decode_kernel<0, __half, true, 2, true, 2, 2>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 2>,
       decode_kernel<0, __half, true, 2, true, 2, 4>, decode_kernel<0, __nv_bfloat16, true, 2, true, 2, 4>,
-      // 2-bit values in one group of 128 channels
-      decode_kernel<0, __half, true, 2, true, 0, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 0, 1>};
+      // 2-bit values in one group of 128 channels, in four groups of 32
+      decode_kernel<0, __half, true, 2, true, 0, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 0, 1>,
+      decode_kernel<0, __half, true, 2, true, 0, 4>, decode_kernel<0, __nv_bfloat16, true, 2, true, 0, 4>};
   const bool fast = a->n_pad == 16 && a->block_tokens % 32 == 0 && a->block_tokens >= 128;
   const int vk = a->value_kind, vg = a->value_groups;
-  if (vk < 0 || vk > 2 || (vk == 2 && vg != 1 && vg != 2 && vg != 4) || (vk == 0 && vg != 0 && vg != 1 && vg != 2))
+  if (vk < 0 || vk > 2 || (vk == 2 && vg != 1 && vg != 2 && vg != 4) || (vk == 0 && vg != 0 && vg != 1 && vg != 2 && vg != 4))
     return INQ_ERR_ARGUMENT;
-  const bool one_group = vk == 0 && vg == 1;   // 2-bit values, one group of 128 channels
+  const bool one_group = vk == 0 && (vg == 1 || vg == 4);   // 2-bit values in one group of 128 channels or four of 32
   if (one_group && !(fast && a->layout == 0)) return INQ_ERR_UNSUPPORTED;
   // coded values are served for the whole-slice geometry of the table layout with 16 salient channels
   // on either side; every other combination is inq_decode_generic's
   if (vk && !(fast && a->layout == 0)) return INQ_ERR_UNSUPPORTED;
   if (vk == 1 && !a->seqs_device && ((const SeqDesc*)a->seq_host)->n_blocks > 0 && !((const SeqDesc*)a->seq_host)->value_roles)
     return INQ_ERR_ARGUMENT;
-  const int which = one_group ? 28 + (a->dtype == INQ_F16 ? 0 : 1)
+  const int which = one_group ? (vg == 1 ? 28 : 30) + (a->dtype == INQ_F16 ? 0 : 1)
                   : vk == 2 ? 22 + (vg == 1 ? 0 : vg == 2 ? 2 : 4) + (a->dtype == INQ_F16 ? 0 : 1)
                   : vk ? 20 + (a->dtype == INQ_F16 ? 0 : 1)
                   : fast ? 16 + a->layout * 2 + (a->dtype == INQ_F16 ? 0 : 1)

@@ -201,7 +201,7 @@ class PackedDecodeState:
         """``(value_kind, value_groups)`` of ``inq_decode_attention`` for this state's value codec, or
         ``None`` when only the general kernel serves it.  The preset (2-bit values in groups of 64) runs
         every geometry; values stored as InQuant packed tensors (the reference's default), 4-bit values in
-        groups of 32 / 64 / 128 and 2-bit values in one group of 128 run it when both sides have 16
+        groups of 32 / 64 / 128 and 2-bit values in groups of 32 or 128 run it when both sides have 16
         salient channels and the blocks are whole 32-token slices (at least four)."""
         if self._preset:
             return 0, 0
@@ -211,8 +211,8 @@ class PackedDecodeState:
             return (1, 0) if self._value_salient == 16 else None
         if self._value_bits == 4:
             return 2, 128 // self._value_group
-        if (self._value_bits, self._value_group) == (2, 128):
-            return 0, 1
+        if self._value_bits == 2:
+            return 0, 128 // self._value_group
         return None
 
     @torch.no_grad()

@@ -82,7 +82,7 @@ def test_table_batch_matches_per_sequence_decode_oracle_and_graph_replay():
             batch.step()
 
 
-@pytest.mark.parametrize("value_bits,group", [(None, 64), (4, 32), (4, 128), (2, 128)])
+@pytest.mark.parametrize("value_bits,group", [(None, 64), (4, 32), (4, 128), (2, 128), (2, 32)])
 def test_table_batch_of_other_value_codecs_matches_per_sequence_decode(value_bits, group):
     """Values stored as InQuant packed tensors (the reference's default), 4-bit values and 2-bit values in one
     group: the batched one-launch step (new token appended by the launch, CUDA-graph replay) equals the
@@ -102,7 +102,7 @@ def test_table_batch_of_other_value_codecs_matches_per_sequence_decode(value_bit
         caches.append(cache)
     seqs = [SequenceState.from_cache_layer(c, 0) for c in caches]
     batch = DecodeBatch(seqs, 28, torch.bfloat16)
-    assert (batch.value_kind, batch.value_groups) == {None: (1, 0), 4: (2, 128 // group), 2: (0, 1)}[value_bits]
+    assert (batch.value_kind, batch.value_groups) == {None: (1, 0), 4: (2, 128 // group), 2: (0, 128 // group)}[value_bits]
     gen = torch.Generator(device="cuda").manual_seed(11)
     steps = torch.randn((4, len(lengths), 28 + 8, 128), device="cuda", generator=gen).bfloat16()
     for step in range(4):

@@ -310,7 +310,8 @@ def test_values_stored_as_inquant_tensors_run_the_streaming_kernel(dtype, q_head
 
 @pytest.mark.parametrize("bits,group,dtype,q_heads,heads,block,blocks,tail", [
     (4, 64, "bfloat16", 28, 4, 256, 3, 281), (4, 32, "float16", 14, 2, 256, 5, 17), (4, 128, "bfloat16", 8, 2, 128, 7, 0),
-    (4, 32, "bfloat16", 12, 1, 256, 40, 300), (2, 128, "bfloat16", 28, 4, 256, 3, 281), (2, 128, "float16", 8, 2, 128, 9, 5)])
+    (4, 32, "bfloat16", 12, 1, 256, 40, 300), (2, 128, "bfloat16", 28, 4, 256, 3, 281), (2, 128, "float16", 8, 2, 128, 9, 5),
+    (2, 32, "bfloat16", 28, 4, 256, 3, 281), (2, 32, "float16", 14, 2, 128, 11, 40)])
 def test_four_bit_values_run_the_streaming_kernel(bits, group, dtype, q_heads, heads, block, blocks, tail):
     """4-bit values in groups of 32, 64 or 128 channels and 2-bit values in one group of 128
     (value_codec.py) on the one-launch kernel: checked against the oracle's dequantised values and
