@@ -1137,16 +1137,20 @@ def run_split_kv(args, torch, dist, device, world, rank):
     # every exchange this node offers is timed (each with its own parity check); the fastest is the
     # leg's figure and the others are reported beside it
     timed = {}
-    if world > 1:
-        for name in ("fused", "p2p"):
-            try:
-                timed[name] = time_split(name, check=True)
-            except RuntimeError:
-                pass   # every rank raises alike: the peer mappings are agreed on collectively
-    timed["nccl"] = time_split("nccl", check=True)
+    for name in args.split_exchanges.split(","):
+        if name == "nccl" or world == 1:
+            if "nccl" not in timed:
+                timed["nccl"] = time_split("nccl", check=True)
+            continue
+        try:
+            result = time_split(name, check=name not in parity)
+        except RuntimeError:
+            continue   # every rank raises alike: the peer mappings are agreed on collectively
+        # an exchange named twice is timed twice (the order of the legs is then visible in the figures)
+        timed[name if name not in timed else name + "_again"] = result
     best = min(timed, key=lambda name: timed[name][0])
     ms, total_bytes, exchange = timed[best]
-    how, launch = describe[best]
+    how, launch = describe[best.replace("_again", "")]
     if not use_graph:
         launch = "eager"
     extra = {"us_per_step_by_exchange": {name: round(t[0] * 1e3, 2) for name, t in timed.items()}}
@@ -1157,7 +1161,7 @@ def run_split_kv(args, torch, dist, device, world, rank):
             "aggregate_gbs": round(total_bytes / (ms * 1e-3) / 1e9, 1),
             "per_gpu_hbm_frac": round(total_bytes / world / (ms * 1e-3) / 1e9 / peak, 4),
             "exchange": how, "launch": launch,
-            "steps": steps, "parity": dict(parity[best], exchanges_checked=sorted(parity)), **extra}
+            "steps": steps, "parity": dict(parity[best.replace("_again", "")], exchanges_checked=sorted(parity)), **extra}
 
 
 # DRAM bytes (read + write) of one decode_kernel launch per algorithmic byte, from one ncu capture
@@ -1416,6 +1420,8 @@ def main():
                         help="--impl reference: time the numpy port of the reference even when oracle/_ref holds the reference itself")
     parser.add_argument("--no-append-sequence", action="store_true",
                         help="skip the 136-step append sequence that crosses a block seal (config 1)")
+    parser.add_argument("--split-exchanges", default="fused,p2p,nccl",
+                        help="exchanges of the split-KV leg to time, in this order (fused, p2p, nccl; several GPUs only)")
     parser.add_argument("--no-value-codecs", action="store_true", help="skip the one-layer leg over the other value codecs")
     parser.add_argument("--no-reference-gpu", action="store_true",
                         help="skip the leg that runs the reference's Triton decode kernel beside this library's")
