@@ -278,7 +278,7 @@ typedef struct {
                              *    CacheConfig default, value_bits=None): table columns 3..5 then hold the
                              *    value payload [kv_heads][tokens][64], scales fp32 [kv_heads][128] and
                              *    padding fp32 [kv_heads][16]; served for layout 0, n_pad 16 on both sides
-                             *    and blocks of a multiple of 32 tokens (>= 128), else INQ_ERR_UNSUPPORTED
+                             *    and blocks of a multiple of 32 tokens (>= 64), else INQ_ERR_UNSUPPORTED
                              *    (inq_decode_generic serves the rest);
                              * 2: values as 4-bit codes with fp16 scale and offset per token and group of
                              *    128 / value_groups channels (value_codec.py with bits=4): table columns 3..5

@@ -66,7 +66,7 @@ constexpr int kQChunk = 36;                         // padded 32-float chunk of 
 constexpr int kQFragBytes = 8 * 32 * 8;              // the staged query as fp16 B fragments of the 8 K steps
 constexpr int kQBytes = 8 * 4 * kQChunk * 4 + 64 + kQFragBytes;   // staged query, two factors per head, fragments
 constexpr float kNegBig = -1.0e30f;
-constexpr int kWarpFixed = 2048 + 256 + 64 + 64 + 1024 + 256;  // per-warp scratch before the per-group parts
+constexpr int kWarpFixed = 2048 + 256 + 64 + 64 + 2048 + 256;  // per-warp scratch before the per-group parts
 constexpr float kRescaleSlack = 4.f;   // the running reference maximum may lag the true one by 2^4
 // start value of a gather accumulator: -(128 + 128/512) in units of 2^-13, so that it ends as
 // (code'_n - 128) + (code'_{n+8} - 128) / 512 (the fraction stays within +-1/4 even for a column
@@ -77,7 +77,7 @@ constexpr float kGatherInit = -128.25f / 8192.f;
 // 128 B | padding 64 B, padded to 768), per-lane flush tables (weight and constant of the lane's 16
 // channels, their kinds) and the exchange area of the donor slots' sums
 constexpr int kValueMeta = 768, kValueTables = 32 * (64 + 64 + 16), kValueXchg = 16 * 8 * 4;
-constexpr int kValueScratch = kValueMeta + kValueTables + kValueXchg;
+constexpr int kValueScratch = 2 * kValueMeta + kValueTables + kValueXchg;   // two metadata slots, as for the keys
 __host__ __device__ constexpr int warp_smem_bytes(int groups, int stage_bytes, int vk = 0) {
   return kWarpFixed + groups * (256 + 2048 + 64) + (vk ? kValueScratch : 0) + kStages * stage_bytes;
 }
@@ -448,7 +448,7 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
 
 
 // ------------------------------------------------------------------------------------------ the kernel
-// FAST: blocks of whole 32-token slices, at least four per block, exactly one group of 16 salient
+// FAST: blocks of whole 32-token slices, at least two per block, exactly one group of 16 salient
 // channels (the preset and the 128/256-token pages): the copies of a slice then are eight
 // asynchronous copies from per-lane pointers that advance by constants, a block's metadata is
 // requested as soon as the prefetch cursor enters the block, and nothing ragged is handled.
@@ -494,14 +494,17 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
   float* wssc = (float*)(wb + 2048);                                    // scale of salient channel i
   unsigned char* wsrc = (unsigned char*)(wssc + 64);                    // channel of salient i
   unsigned char* wdon = wsrc + 64;                                      // its donor slot
-  unsigned char* wmeta = wdon + 64;       // staged block metadata: K scales 512 B | role map 256 B | padding 256 B
-  unsigned char* wfrag = wmeta + 1024;    // a block's channel weights as fp16 pairs in B-fragment order: [K step][chunk] x 8 B
+  // staged block metadata: K scales 512 B | role map 256 B | padding 256 B.  Two slots: the whole-slice
+  // path stages block b into slot b % 2, so the block after the one being consumed can be requested
+  // while this one's slot is still to be read
+  unsigned char* wmeta = wdon + 64;
+  unsigned char* wfrag = wmeta + 2048;    // a block's channel weights as fp16 pairs in B-fragment order: [K step][chunk] x 8 B
   unsigned char* wqsal = wb + kWarpFixed;                               // B fragments: query at salient channels
   unsigned char* wsel = wqsal + groups * 256;                           // B fragments: nibble selection
   unsigned short* wcell = (unsigned short*)(wsel + groups * 2048);      // selection cells written by the last fold (offsets into wsel)
   // InQuant-coded values: staged value metadata of a block, the lane's flush tables, the donor sums
   unsigned char* wvmeta = (unsigned char*)wcell + groups * 64;
-  float* wvw = (float*)(wvmeta + kValueMeta);                           // [lane][16] weight of the block sum
+  float* wvw = (float*)(wvmeta + 2 * kValueMeta);                       // [lane][16] weight of the block sum
   float* wvk = wvw + 32 * 16;                                           // [lane][16] factor of sum p
   signed char* wvkind = (signed char*)(wvk + 32 * 16);                  // [lane][16] -1 regular, idx salient, 16 + idx donor
   float* wvx = (float*)(wvkind + 32 * 16);                              // [16 list entries][8 heads] low-nibble sums
@@ -786,14 +789,15 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
     int to_issue = n_my, issue_stage = 0;
     int meta_block = -1;        // block whose metadata is staged (or in flight) in wmeta
     int folded_block = -2;      // last block whose weights were derived from wmeta
-    auto stage_meta = [&](const BlockPtrs& bp, unsigned char* dst) {
+    auto stage_meta = [&](const BlockPtrs& bp, unsigned char* dst, int slot = 0) {
       cp_async16(dst + lane * 16, bp.ks + lane * 16);
       if (lane < (MODE == 0 ? 8 : 16)) cp_async16(dst + 512 + lane * 16, bp.kr + lane * 16);
       for (int i = lane; i < n_pad; i += 32) cp_async4(dst + 768 + i * 4, bp.kpad + i * 4);
       if (VK == 1) {
-        cp_async16(wvmeta + lane * 16, bp.vs + lane * 16);
-        if (lane < 8) cp_async16(wvmeta + 512 + lane * 16, bp.vr + lane * 16);
-        if (lane < 16) cp_async4(wvmeta + 640 + lane * 4, bp.vo + lane * 4);
+        unsigned char* const vdst = wvmeta + slot * kValueMeta;
+        cp_async16(vdst + lane * 16, bp.vs + lane * 16);
+        if (lane < 8) cp_async16(vdst + 512 + lane * 16, bp.vr + lane * 16);
+        if (lane < 16) cp_async4(vdst + 640 + lane * 4, bp.vo + lane * 4);
       }
     };
     // FAST: this lane's source pointers of the next slice to request (K rows, V rows, V scale and
@@ -811,10 +815,7 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
     // the later ldmatrix reads of eight tokens' chunks fall into distinct banks.
     const unsigned fast_v_dst = VK ? (unsigned)(kStageK + (lane >> 2) * 64 + (((lane & 3) ^ ((lane >> 3) & 3)) << 4))
                                    : (unsigned)(kStageK + (((lane >> 1) * 2 + ((lane & 1) ^ ((lane >> 3) & 1))) << 4));
-    if (FAST) {
-      stage_meta(pf_ptrs, wmeta);   // the first block's metadata rides with its first slice
-      meta_block = pf_block;
-    }
+    if (FAST) stage_meta(pf_ptrs, wmeta + (pf_block & 1) * 1024, pf_block & 1);   // the first block's metadata rides with its first slice
     auto issue = [&]() {
       if (FAST) {
         if (to_issue > 0) {
@@ -850,16 +851,13 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
             pf_left = spb;
             ++pf_block;
             if (to_issue > 0) {
-              // the cursor enters a new block: its rows, and its metadata at once when the staging
-              // area is free, i.e. the block whose metadata it holds has been folded (always the case
-              // except for a warp whose range begins in the last slices of a block; the fold then
-              // fetches the metadata itself)
+              // the cursor enters a new block: its rows, and its metadata at once into slot block % 2.
+              // The cursor runs at most three slices ahead of the slice being consumed and a block has
+              // at least two, so the slot's previous block lies behind the consumed one or is the
+              // consumed one, whose fold precedes this request (the copies are issued after it).
               pf_ptrs = locate_block<MODE, VK, VG>(P, d_table, d_roles, d_pool, d_pages, d_pool_pages, pf_block, h, d_vroles);
               fk = pf_ptrs.kp + lane * 16; fv = pf_ptrs.vp + lane * 16; fs = pf_ptrs.vs + lane * kParamLane; fo = pf_ptrs.vo + lane * kParamLane;
-              if (folded_block == meta_block) {
-                stage_meta(pf_ptrs, wmeta);
-                meta_block = pf_block;
-              }
+              stage_meta(pf_ptrs, wmeta + (pf_block & 1) * 1024, pf_block & 1);
             }
           }
         }
@@ -997,15 +995,17 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
       // With fewer than three slices per block the next block's metadata can only be staged once
       // this block's fold has released the staging area: there the copies are issued after the
       // fold.  Otherwise they go out first.
-      // FAST: a request that enters a new block also requests that block's metadata into the one
-      // staging area, so the fold of this slice's block (it reads that area) comes first
+      // FAST: a request that enters a new block also requests that block's metadata, possibly into
+      // the slot of this slice's block, so the fold of this block (it reads that slot) comes first
       const bool issue_late = FAST ? need_weights : (!kMetaInStage && spb < 3 && need_weights);
       if (!issue_late) issue();
 
       if (need_weights) {
         // ---- fold this block's descriptor, scales and padding into the query
         unsigned char* meta = wmeta;
-        if (kMetaInStage) {
+        if (FAST) {
+          meta = wmeta + (cur_block & 1) * 1024;
+        } else if (kMetaInStage) {
           meta = ring + stage_index * kStageBytes + kMetaOffset;
         } else if (meta_block != cur_block) {
           // not prefetched (very short blocks): fetch now and wait for it alone
@@ -1169,9 +1169,10 @@ __global__ void __launch_bounds__(kThreads, VK ? 2 : kCtasPerSm) decode_kernel(c
         bm[1] = beta[1] - m_run[1];
         if (VK == 1) {
           // flush tables of the value block: lane (r, j) derives entries 4j .. 4j+3 of row r
-          const float* const vscale = (const float*)wvmeta;
-          const signed char* const vroles = (const signed char*)(wvmeta + 512);
-          const float* const vpads = (const float*)(wvmeta + 640);
+          const unsigned char* const vmeta = wvmeta + (cur_block & 1) * kValueMeta;
+          const float* const vscale = (const float*)vmeta;
+          const signed char* const vroles = (const signed char*)(vmeta + 512);
+          const float* const vpads = (const float*)(vmeta + 640);
           bool vbad = false;
 #pragma unroll
           for (int ii = 0; ii < 4; ++ii) {
@@ -1936,7 +1937,7 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
       decode_kernel<0, __nv_bfloat16, false, 1, false>, decode_kernel<0, __nv_bfloat16, true, 1, false>,
       decode_kernel<1, __half, false, 1, false>, decode_kernel<1, __half, true, 1, false>,
       decode_kernel<1, __nv_bfloat16, false, 1, false>, decode_kernel<1, __nv_bfloat16, true, 1, false>,
-      // whole slices, at least four per block, one salient group
+      // whole slices, at least two per block, one salient group
       decode_kernel<0, __half, true, 2, true>, decode_kernel<0, __nv_bfloat16, true, 2, true>,
       decode_kernel<1, __half, true, 2, true>, decode_kernel<1, __nv_bfloat16, true, 2, true>,
       // the same with the values stored as InQuant packed tensors (table layout)
@@ -1948,7 +1949,7 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
       // 2-bit values in one group of 128 channels, in four groups of 32
       decode_kernel<0, __half, true, 2, true, 0, 1>, decode_kernel<0, __nv_bfloat16, true, 2, true, 0, 1>,
       decode_kernel<0, __half, true, 2, true, 0, 4>, decode_kernel<0, __nv_bfloat16, true, 2, true, 0, 4>};
-  const bool fast = a->n_pad == 16 && a->block_tokens % 32 == 0 && a->block_tokens >= 128;
+  const bool fast = a->n_pad == 16 && a->block_tokens % 32 == 0 && a->block_tokens >= 64;
   const int vk = a->value_kind, vg = a->value_groups;
   if (vk < 0 || vk > 2 || (vk == 2 && vg != 1 && vg != 2 && vg != 4) || (vk == 0 && vg != 0 && vg != 1 && vg != 2 && vg != 4))
     return INQ_ERR_ARGUMENT;

@@ -202,10 +202,10 @@ class PackedDecodeState:
         ``None`` when only the general kernel serves it.  The preset (2-bit values in groups of 64) runs
         every geometry; values stored as InQuant packed tensors (the reference's default), 4-bit values in
         groups of 32 / 64 / 128 and 2-bit values in groups of 32 or 128 run it when both sides have 16
-        salient channels and the blocks are whole 32-token slices (at least four)."""
+        salient channels and the blocks are whole 32-token slices (at least two)."""
         if self._preset:
             return 0, 0
-        if not (self._salient == 16 and self._packed_tokens % 32 == 0 and self._packed_tokens >= 128):
+        if not (self._salient == 16 and self._packed_tokens % 32 == 0 and self._packed_tokens >= 64):
             return None
         if self._inquant_values:
             return (1, 0) if self._value_salient == 16 else None
