@@ -31,19 +31,21 @@ def _model(model_type="qwen2", layers=2, heads=4, kv_heads=2):
 # layer both paths see identical cache contents and differ by at most two such steps.  With two
 # layers the second layer's K/V inherit that difference, so once a block seals the two caches
 # may hold different codes; the longer case therefore only bounds the drift.
-@pytest.mark.parametrize("model_type,layers,prefill_tokens,heads,kv_heads,steps,atol,value_bits", [
-    ("qwen2", 1, 3, 4, 2, 40, .016, 2), ("qwen2", 1, 98, 4, 2, 40, .016, 2), ("qwen2", 1, 300, 14, 2, 7, .016, 2),
-    ("mistral", 1, 98, 8, 2, 7, .016, 2), ("qwen2", 2, 98, 4, 2, 40, .04, 2),
-    # the reference's default cache stores values as InQuant packed tensors too (general kernel)
-    ("qwen2", 1, 98, 4, 2, 40, .016, None), ("qwen2", 1, 98, 4, 2, 7, .016, 4)])
-def test_fused_decode_matches_materialising_forward(model_type, layers, prefill_tokens, heads, kv_heads, steps, atol, value_bits):
+@pytest.mark.parametrize("model_type,layers,prefill_tokens,heads,kv_heads,steps,atol,value_bits,block", [
+    ("qwen2", 1, 3, 4, 2, 40, .016, 2, 32), ("qwen2", 1, 98, 4, 2, 40, .016, 2, 32), ("qwen2", 1, 300, 14, 2, 7, .016, 2, 32),
+    ("mistral", 1, 98, 8, 2, 7, .016, 2, 32), ("qwen2", 2, 98, 4, 2, 40, .04, 2, 32),
+    # the reference's default cache stores values as InQuant packed tensors too: the general kernel with
+    # 32-token blocks, the one-launch kernel with blocks of whole slices (at least two)
+    ("qwen2", 1, 98, 4, 2, 40, .016, None, 32), ("qwen2", 1, 98, 4, 2, 7, .016, 4, 32),
+    ("qwen2", 1, 200, 4, 2, 70, .016, None, 64), ("qwen2", 1, 200, 4, 2, 70, .016, 4, 64), ("mistral", 1, 200, 8, 2, 70, .016, 2, 64)])
+def test_fused_decode_matches_materialising_forward(model_type, layers, prefill_tokens, heads, kv_heads, steps, atol, value_bits, block):
     from inquant.cache import CacheConfig, InQuantCache
     from inquant.codec import CodecConfig
     from inquant.qwen_fused import enable_fused_attention
     torch.manual_seed(37)
     model = _model(model_type, layers=layers, heads=heads, kv_heads=kv_heads)
     twin = copy.deepcopy(model)
-    config = CacheConfig(CodecConfig(salient_fraction=.125), block_size=32, residual_length=4, sink_tokens=2,
+    config = CacheConfig(CodecConfig(salient_fraction=.125), block_size=block, residual_length=4, sink_tokens=2,
                          value_bits=value_bits)
     with enable_fused_attention(model) as handle, torch.no_grad():
         expected_cache, packed = InQuantCache(config), InQuantCache(config)
