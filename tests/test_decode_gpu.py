@@ -347,6 +347,54 @@ def test_four_bit_values_run_the_streaming_kernel(bits, group, dtype, q_heads, h
     assert N.take_status(torch.device("cuda", 0)) == 0
 
 
+def test_streaming_and_general_kernel_agree_on_random_shapes_and_value_codecs():
+    """Forty seeded random configurations (value codec, block length 64/128/256, KV heads, query heads per KV
+    head up to 16, 1..40 blocks, sink and tail lengths, dtype, donor policy): the one-launch kernel and the
+    general kernel are two independent implementations of the same contract and must agree."""
+    CodecConfig, quantize, quantize_values, PackedDecodeState, _, _ = _mods()
+    from inquant import _native as N
+    rng = np.random.default_rng(20240)
+    dev = torch.device("cuda", 0)
+    codecs = {"preset": (2, 64), "v4g32": (4, 32), "v4g64": (4, 64), "v4g128": (4, 128), "v2g128": (2, 128), "v2g32": (2, 32)}
+    for case in range(40):
+        kind = str(rng.choice(["coded", *codecs]))
+        block, heads = int(rng.choice([64, 128, 256])), int(rng.choice([1, 2, 4, 8]))
+        group = int(rng.choice([1, 2, 4, 7, 8, 9, 16]))
+        blocks = int(rng.integers(1, 40 if heads <= 2 else 16))
+        tail, sink = int(rng.choice([0, 1, 15, 16, 17, 100, 300])), int(rng.choice([0, 2, 4]))
+        dtype = torch.bfloat16 if rng.random() < 0.6 else torch.float16
+        cfg = CodecConfig(salient_fraction=0.125, donor_policy="min_error" if rng.random() < 0.5 else "neighbors")
+        gen = torch.Generator(device=dev).manual_seed(5000 + case)
+        boost = torch.ones(128, device=dev)
+        boost[torch.from_numpy(rng.integers(0, 128, size=3)).to(dev)] = 8.0
+
+        def randn(*shape):
+            return torch.randn(shape, device=dev, generator=gen)
+
+        keys = [quantize((randn(1, heads, block, 128) * boost).to(dtype), cfg) for _ in range(blocks)]
+        if kind == "coded":
+            values = [quantize((randn(1, heads, block, 128) * boost + 0.3).to(dtype), cfg) for _ in range(blocks)]
+        else:
+            values = [quantize_values((randn(1, heads, block, 128) + 0.3).to(dtype), *codecs[kind]) for _ in range(blocks)]
+        query = randn(1, heads * group, 1, 128).to(dtype)
+        dense = {}
+        if sink:
+            dense.update(sink_key=randn(1, heads, sink, 128).to(dtype), sink_value=randn(1, heads, sink, 128).to(dtype))
+        if tail:
+            dense.update(residual_key=randn(1, heads, tail, 128).to(dtype), residual_value=randn(1, heads, tail, 128).to(dtype))
+        state = PackedDecodeState(keys, values)
+        assert state.streaming_value_kind() is not None
+        fast = state.decode(query, **dense).float().reshape(heads * group, 128)
+        general = state._decode_general(query, heads, group, blocks, dense.get("sink_key"), dense.get("sink_value"), sink,
+                                        dense.get("residual_key"), dense.get("residual_value"), tail, 128 ** -0.5)
+        general = general.float().reshape(heads * group, 128)
+        label = (case, kind, block, heads, group, blocks, tail, sink, dtype)
+        assert torch.isfinite(fast).all(), label
+        assert (fast - general).abs().max().item() < 2e-2 + 8e-3 * general.abs().max().item(), label
+        assert torch.nn.functional.cosine_similarity(fast, general, dim=1).min().item() > 0.9999, label
+        assert N.take_status(dev) == 0, label
+
+
 def test_general_kernel_dense_only_fp32():
     _, _, _, _, _, packed_decode = _mods()
     k, v, q = _random(7, (1, 2, 150, 128), "float32"), _random(8, (1, 2, 150, 128), "float32"), _random(9, (6, 128), "float32")
