@@ -229,15 +229,17 @@ typedef struct {
 /* Split-KV across the GPUs of one node inside the decode launch itself (no counterpart in the
  * reference, which is single-GPU): the CTA that merges this rank's parts of a pair
  * (sequence, KV head, tile of 8 query heads) stores the pair's un-normalised record straight into
- * every peer's inbox over NVLink peer memory, publishes it with a release store after a
- * system-scope fence, waits for the peers' records of the same pair in its own inbox -- a bounded
- * wait: after `spin_limit` polls it sets INQ_STATUS_WAIT_TIMEOUT and writes zero rows -- and merges
- * all records in rank order (the cross-rank form of triton_attention.py:168-181), so every rank
- * writes the same `output`.  The inboxes are those of inq_exchange_merge (inq_exchange_inbox_bytes,
- * inq_peer_buffer_create / _open); an inbox serves either that entry point or this one, not both,
- * and here a flag word stands for a pair: at most 512 pairs per launch.  Every rank launches the
- * same steps in the same order; the launch needs all its CTAs resident (it always sizes its grid
- * so) and other work on the GPU only delays the wait.  The struct lives in DEVICE memory. */
+ * every peer's inbox over NVLink peer memory, waits for the peers' records of the same pair in its
+ * own inbox -- a bounded wait: after `spin_limit` polls it sets INQ_STATUS_WAIT_TIMEOUT and writes
+ * zero rows -- and merges all records in rank order (the cross-rank form of
+ * triton_attention.py:168-181), so every rank writes the same `output`.  Every 32-bit word of a
+ * record travels as one indivisible 8-byte store {word, step number}; a reader takes a word when its
+ * step number is the current one, so the launch needs neither a system-scope fence nor flag words.
+ * An inbox holds inq_decode_exchange_inbox_bytes(world, n_rows) bytes, zeroed before the first step
+ * (inq_peer_buffer_create / _open); one inbox serves either inq_exchange_merge or this form, not
+ * both.  Every rank launches the same steps in the same order; the launch needs all its CTAs
+ * resident (it always sizes its grid so) and other work on the GPU only delays the wait.  The struct
+ * lives in DEVICE memory. */
 typedef struct {
   void* inboxes[8];       /* inbox of every rank as mapped into this process; [rank] is the own one */
   int32_t* epoch;         /* device, zero before the first step: [0] = steps completed, advanced by the launch */
@@ -338,6 +340,7 @@ typedef struct {
 } inq_exchange_args_t;
 int inq_exchange_merge(const inq_exchange_args_t* args /* host */, inq_stream_t stream);
 int64_t inq_exchange_inbox_bytes(int32_t world, int64_t n_rows);
+int64_t inq_decode_exchange_inbox_bytes(int32_t world, int64_t n_rows);   /* inbox of inq_decode_exchange_t */
 /* Device memory other processes of the node can map: create = cudaMalloc + zero fill + a 64-byte
  * CUDA IPC handle to send to the peers; open maps a peer's buffer (enabling peer access);
  * close / destroy undo open / create.  These four calls synchronise with the device. */

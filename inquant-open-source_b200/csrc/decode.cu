@@ -346,14 +346,26 @@ __device__ __forceinline__ void stage_slice(unsigned char* stage, const unsigned
 
 // ------------------------------------------------------------------------------------------ exchange of a pair
 // Split-KV across GPUs, run by the CTA that has just merged this rank's parts of a pair: the
-// pair's un-normalised record (eight channels per thread in `oa`, `ob`; `top`, `l` of the row) is
-// stored into every peer's inbox over NVLink peer memory, published per pair with a release store
-// after a system-scope fence, the peers' records of the same pair are awaited in this rank's own
-// inbox (bounded: a wait that runs out raises INQ_STATUS_WAIT_TIMEOUT and zeroes the rows) and
-// all records are merged in rank order, so every rank writes bit-identical output rows.
-// All threads of the CTA call it; `active` marks those that hold a row.  The flag word of a pair
-// is indexed by the pair, the step number comes from the epoch word that the launch advances
-// when its last CTA leaves.
+// pair's un-normalised record (eight channels per thread in `oa`, `ob`; `top`, `l` of the row) goes
+// into every peer's inbox over NVLink peer memory, the peers' records of the same pair are awaited
+// in this rank's own inbox and all records are merged in rank order, so every rank writes
+// bit-identical output rows.
+// Every 32-bit word of a record travels as ONE 8-byte store {word, step number}: such a store is
+// indivisible, so a word whose tag equals the current step is the word of this step and neither a
+// fence nor a separate flag is needed (a system-scope fence inside this kernel was measured at 9 us:
+// it queues behind the copies the other CTAs of the SM still have in flight).  A reader polls the
+// words it needs until their tags match -- bounded: a wait that runs out raises
+// INQ_STATUS_WAIT_TIMEOUT and zeroes the rows.  The inbox is double buffered by step parity.
+// All threads of the CTA call it; those with g < g_valid hold a row.  The step number comes from
+// the epoch word that the launch advances when its last CTA leaves.
+__device__ __forceinline__ void st_tagged(uint2* p, unsigned word, unsigned tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(word), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint4 ld_tagged2(const uint2* p) {   // two tagged words
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 template <typename QT>
 __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long long row0, int g, int g_valid, int c8,
                                            float4 oa, float4 ob, float top, float l, QT* out, int* status,
@@ -364,8 +376,8 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
   const long long row = row0 + g;
   const int world = X->world, me = X->rank;
   const long long n_rows = X->n_rows;
-  const int step = X->epoch[0] + 1;
-  const int parity = step & 1;
+  const unsigned step = (unsigned)(X->epoch[0] + 1);
+  const int parity = (int)(step & 1u);
   unsigned char* const own = X->inbox[me];
   if (tid == 0) s_failed = 0;
   // the pair's rows are adjacent in an inbox: staged in shared memory, they leave as consecutive
@@ -380,31 +392,47 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
   }
   __syncthreads();
   {
-    const int n_pairs8 = g_valid * (kExRowFloats / 2);
-    const float2* const src = (const float2*)scratch;
+    const int n_words = g_valid * kExRowFloats;
+    const unsigned* const src = (const unsigned*)scratch;
     // every rank starts with the peer after itself, so that no inbox is everybody's first target
     for (int hop = 1; hop < world; ++hop) {
       const int p = me + hop < world ? me + hop : me + hop - world;
-      float2* const dst = (float2*)(ex_data(X->inbox[p], parity, me, world, n_rows) + row0 * kExRowFloats);
-      for (int i = tid; i < n_pairs8; i += kThreads) dst[i] = src[i];
+      uint2* const dst = ex_tagged(X->inbox[p], parity, me, world, n_rows) + row0 * kExRowFloats;
+      for (int i = tid; i < n_words; i += kThreads) st_tagged(dst + i, src[i], step);
     }
   }
-  __threadfence_system();
-  __syncthreads();
-  if (tid < world && tid != me) {
-    st_release_sys(ex_flag(X->inbox[tid], parity, me, pair), step);
-    const int* const flag = ex_flag(own, parity, tid, pair);
+  (void)pair;
+  // this thread's words of every peer's record (channels c8 .. c8+7 and (m, l) of its row) are awaited
+  // first; only (m, l) are kept, the channels are read again when the records are summed in rank order
+  float peer_m[kExMaxWorld], peer_l[kExMaxWorld];
+  bool failed_here = false;
+  if (active) {
     const int limit = X->spin_limit > 0 ? X->spin_limit : kExDefaultSpin;
-    int polls = 0;
-    // relaxed polls, one acquire once the flag is there
-    while (*(volatile const int*)flag - step < 0) {
-      if (++polls > limit) {
-        atomicOr(&s_failed, 1);
-        break;
+#pragma unroll
+    for (int p = 0; p < kExMaxWorld; ++p) {
+      peer_m[p] = 0.f;
+      peer_l[p] = 0.f;
+      if (p >= world || p == me || failed_here) continue;
+      const uint2* const rec = ex_tagged(own, parity, p, world, n_rows) + row * kExRowFloats;
+      int polls = 0;
+      while (true) {
+        const uint4 w0 = ld_tagged2(rec + c8), w1 = ld_tagged2(rec + c8 + 2), w2 = ld_tagged2(rec + c8 + 4);
+        const uint4 w3 = ld_tagged2(rec + c8 + 6), w4 = ld_tagged2(rec + 128);
+        const bool here = w0.y == step && w0.w == step && w1.y == step && w1.w == step && w2.y == step && w2.w == step &&
+                          w3.y == step && w3.w == step && w4.y == step && w4.w == step;
+        if (here) {
+          peer_m[p] = __uint_as_float(w4.x);
+          peer_l[p] = __uint_as_float(w4.z);
+          break;
+        }
+        if (++polls > limit) {
+          failed_here = true;
+          break;
+        }
+        __nanosleep(40);
       }
-      __nanosleep(40);
     }
-    (void)ld_acquire_sys(flag);
+    if (failed_here) atomicOr(&s_failed, 1);
   }
   __syncthreads();
   const bool failed = s_failed != 0;
@@ -412,15 +440,10 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
   if (active) {
     float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, norm = 1.f;
     if (!failed) {
-      float2 ml[kExMaxWorld];
       float all_top = top;
 #pragma unroll
-      for (int p = 0; p < kExMaxWorld; ++p) {
-        if (p < world && p != me) {
-          ml[p] = __ldcg((const float2*)(ex_data(own, parity, p, world, n_rows) + row * kExRowFloats + 128));
-          all_top = fmaxf(all_top, ml[p].x);
-        }
-      }
+      for (int p = 0; p < kExMaxWorld; ++p)
+        if (p < world && p != me) all_top = fmaxf(all_top, peer_m[p]);
       norm = 0.f;
 #pragma unroll
       for (int p = 0; p < kExMaxWorld; ++p) {
@@ -431,13 +454,14 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
           o[0] = fmaf(oa.x, w, o[0]); o[1] = fmaf(oa.y, w, o[1]); o[2] = fmaf(oa.z, w, o[2]); o[3] = fmaf(oa.w, w, o[3]);
           o[4] = fmaf(ob.x, w, o[4]); o[5] = fmaf(ob.y, w, o[5]); o[6] = fmaf(ob.z, w, o[6]); o[7] = fmaf(ob.w, w, o[7]);
         } else {
-          const float* rec = ex_data(own, parity, p, world, n_rows) + row * kExRowFloats + c8;
-          const float w = fast_exp2(ml[p].x - all_top);
-          const float2 a = __ldcg((const float2*)rec), b = __ldcg((const float2*)rec + 1);
-          const float2 c = __ldcg((const float2*)rec + 2), d = __ldcg((const float2*)rec + 3);
-          norm = fmaf(ml[p].y, w, norm);
-          o[0] = fmaf(a.x, w, o[0]); o[1] = fmaf(a.y, w, o[1]); o[2] = fmaf(b.x, w, o[2]); o[3] = fmaf(b.y, w, o[3]);
-          o[4] = fmaf(c.x, w, o[4]); o[5] = fmaf(c.y, w, o[5]); o[6] = fmaf(d.x, w, o[6]); o[7] = fmaf(d.y, w, o[7]);
+          const uint2* const rec = ex_tagged(own, parity, p, world, n_rows) + row * kExRowFloats + c8;
+          const uint4 w0 = ld_tagged2(rec), w1 = ld_tagged2(rec + 2), w2 = ld_tagged2(rec + 4), w3 = ld_tagged2(rec + 6);
+          const float w = fast_exp2(peer_m[p] - all_top);
+          norm = fmaf(peer_l[p], w, norm);
+          o[0] = fmaf(__uint_as_float(w0.x), w, o[0]); o[1] = fmaf(__uint_as_float(w0.z), w, o[1]);
+          o[2] = fmaf(__uint_as_float(w1.x), w, o[2]); o[3] = fmaf(__uint_as_float(w1.z), w, o[3]);
+          o[4] = fmaf(__uint_as_float(w2.x), w, o[4]); o[5] = fmaf(__uint_as_float(w2.z), w, o[5]);
+          o[6] = fmaf(__uint_as_float(w3.x), w, o[6]); o[7] = fmaf(__uint_as_float(w3.z), w, o[7]);
         }
       }
     }
@@ -445,7 +469,6 @@ __device__ __noinline__ void exchange_pair(const ExchangeView* X, int pair, long
     for (int k = 0; k < 8; ++k) out[k] = from_float<QT>(failed ? 0.f : o[k] / norm);
   }
 }
-
 
 // ------------------------------------------------------------------------------------------ the kernel
 // FAST: blocks of whole 32-token slices, at least two per block, exactly one group of 16 salient
@@ -2015,7 +2038,6 @@ extern "C" int inq_decode_attention(const inq_decode_args_t* a, inq_stream_t str
   P.status = a->status;
   P.fused_append = a->fused_append ? 1 : 0;
   P.exchange = (const ExchangeView*)a->exchange_device;
-  if (P.exchange && plan.n_pairs > kExMaxChunks) return INQ_ERR_CAPACITY;   // one flag word per pair
   kernel<<<(unsigned)plan.n_ctas, kThreads, shared, (cudaStream_t)stream_>>>(P);
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;

@@ -144,6 +144,11 @@ extern "C" int64_t inq_exchange_inbox_bytes(int32_t world, int64_t n_rows) {
   return inq::kExFlagBytes + 2ll * world * n_rows * inq::kExRowFloats * 4;
 }
 
+extern "C" int64_t inq_decode_exchange_inbox_bytes(int32_t world, int64_t n_rows) {
+  if (world < 1 || world > inq::kExMaxWorld || n_rows < 1) return 0;
+  return inq::kExFlagBytes + 2ll * world * n_rows * inq::kExRowFloats * 8;   // every word with its step number
+}
+
 extern "C" int inq_exchange_merge(const inq_exchange_args_t* a, inq_stream_t stream_) {
   using namespace inq;
   if (!a || !a->ranks || a->world < 1 || a->world > kExMaxWorld || a->n_rows < 1 || a->n_rows >= (1ll << 31))

@@ -29,5 +29,10 @@ __device__ __forceinline__ int* ex_flag(unsigned char* inbox, int parity, int sr
 __device__ __forceinline__ float* ex_data(unsigned char* inbox, int parity, int src, int world, long long n_rows) {
   return (float*)(inbox + kExFlagBytes) + ((long long)parity * world + src) * n_rows * kExRowFloats;
 }
+// The decode kernel's own exchange keeps the same record grid but every 32-bit word of a record is
+// an 8-byte pair {word, step number it belongs to}; it uses no flag words.
+__device__ __forceinline__ uint2* ex_tagged(unsigned char* inbox, int parity, int src, int world, long long n_rows) {
+  return (uint2*)(inbox + kExFlagBytes) + ((long long)parity * world + src) * n_rows * kExRowFloats;
+}
 
 }  // namespace inq

@@ -148,6 +148,8 @@ def library() -> ctypes.CDLL:
         lib.inq_prefill_workspace_bytes.argtypes = [c_int32, c_int32]
         lib.inq_exchange_inbox_bytes.restype = c_int64
         lib.inq_exchange_inbox_bytes.argtypes = [c_int32, c_int64]
+        lib.inq_decode_exchange_inbox_bytes.restype = c_int64
+        lib.inq_decode_exchange_inbox_bytes.argtypes = [c_int32, c_int64]
         lib.inq_decode_units.restype = c_int64
         lib.inq_decode_units.argtypes = [c_int32, c_int32]
         for name in EXPORTS:
@@ -167,7 +169,7 @@ EXPORTS = (
     "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
     "inq_prefill_attention", "inq_decode_generic", "inq_decode_generic_workspace_floats",
     "inq_prefill_workspace_bytes",
-    "inq_exchange_merge", "inq_exchange_inbox_bytes", "inq_peer_buffer_create", "inq_peer_buffer_open",
+    "inq_exchange_merge", "inq_exchange_inbox_bytes", "inq_decode_exchange_inbox_bytes", "inq_peer_buffer_create", "inq_peer_buffer_open",
     "inq_peer_buffer_close", "inq_peer_buffer_destroy",
 )
 

@@ -14,8 +14,9 @@ log-sum-exp rule (the cross-rank form of ``triton_attention.py:168-181``).  Two 
 ``"nccl"``  one ``all_gather`` followed by the merge kernel ``inq_merge_partials``.
 
 ``"fused"`` no launch of its own: the decode kernel's merging CTA of every (layer, KV head, head tile)
-            stores that pair's record into the peers' inboxes, awaits theirs (bounded) and merges them
-            (``inq_decode_exchange_t``), so a step is ONE launch per rank;
+            stores that pair's record into the peers' inboxes (every word with its step number: no
+            fence, no flags), awaits theirs (bounded) and merges them (``inq_decode_exchange_t``), so a step
+            is ONE launch per rank;
 
 ``"auto"`` takes peer memory when every rank sits on the same host and the mappings can be made
 (inside the decode launch between two ranks, the separate kernel from four ranks on: the faster one
@@ -93,7 +94,9 @@ class PeerExchange:
         error = None
         with torch.cuda.device(device):
             try:
-                N.check(lib.inq_peer_buffer_create(lib.inq_exchange_inbox_bytes(self.world, self.n_rows),
+                # sized for either form of the exchange (the decode launch's own tags every word: twice the bytes)
+                N.check(lib.inq_peer_buffer_create(max(lib.inq_exchange_inbox_bytes(self.world, self.n_rows),
+                                                       lib.inq_decode_exchange_inbox_bytes(self.world, self.n_rows)),
                                                    ctypes.byref(self._own), handle), "inq_peer_buffer_create")
             except (RuntimeError, ValueError) as exc:
                 error = str(exc)
@@ -127,7 +130,7 @@ class PeerExchange:
     def decode_view(self) -> torch.Tensor:
         """This exchange as the decode kernel reads it (``inq_decode_exchange_t`` in device memory): the
         kernel then pushes, awaits and merges the records pair by pair itself.  An exchange serves
-        either ``run`` or the decode kernel, not both: they number their flag words differently."""
+        either ``run`` or the decode kernel, not both: they lay the records out differently."""
         view = N.DecodeExchange()
         for peer in range(self.world):
             view.inboxes[peer] = self._inboxes[peer]
@@ -180,12 +183,6 @@ class SplitKVDecode:
         self.fused = self.world > 1 and (exchange == "fused" or (exchange == "auto" and self.world == 2))
         self.batch = DecodeBatch(sequences, q_heads, dtype, partials_only=not self.fused)
         n = len(sequences)
-        pairs = n * self.batch.kv_heads * ((self.batch.q_per_kv + 7) // 8)
-        if self.fused and pairs > 512:   # one flag word per pair in an inbox
-            if exchange == "fused":
-                raise ValueError("the exchange inside the decode launch serves at most 512 (sequence, KV head, head tile) pairs")
-            self.fused = False
-            self.batch = DecodeBatch(sequences, q_heads, dtype, partials_only=True)
         self.peers = None
         if self.world > 1 and exchange != "nccl":
             try:

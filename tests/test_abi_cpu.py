@@ -81,6 +81,8 @@ def test_exchange_entry_points_check_their_arguments_without_a_gpu():
     lib = N.library()
     assert lib.inq_exchange_inbox_bytes(9, 10) == 0 and lib.inq_exchange_inbox_bytes(2, 0) == 0
     assert lib.inq_exchange_inbox_bytes(2, 10) == 2 * 8 * 512 * 4 + 2 * 2 * 10 * 520
+    assert lib.inq_decode_exchange_inbox_bytes(2, 10) == 2 * 8 * 512 * 4 + 2 * 2 * 10 * 1040
+    assert lib.inq_decode_exchange_inbox_bytes(0, 10) == 0
     args = N.ExchangeArgs(None, 1, 2, 10, 2, 0)
     assert lib.inq_exchange_merge(ctypes.byref(args), None) == N.ERR_ARGUMENT
     assert lib.inq_peer_buffer_create(0, None, None) == N.ERR_ARGUMENT

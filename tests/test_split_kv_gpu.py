@@ -133,8 +133,8 @@ def test_peer_exchange_wait_gives_up_and_reports_when_a_peer_never_signals():
 def _fused_rank(cache, layers, q_heads, world, rank, q, peer_records=None, spin_limit=0, steps=1):
     """One rank of a split whose decode launch exchanges its records itself.  The peers do not
     run: their inboxes are buffers of this process that soak up the pushes, and ``peer_records``
-    ([world, rows, 130], both parities filled) stand in this rank's inbox with their flags set
-    for ``steps`` steps, as if the peers had been faster."""
+    ([world, rows, 130]) stand in this rank's inbox as the peers would have stored them for the steps
+    run here (every word tagged with its step number: step 1 in the odd half, step 2 in the even one)."""
     import ctypes
     from inquant import _native as N
     from inquant.batched import DecodeBatch
@@ -142,16 +142,16 @@ def _fused_rank(cache, layers, q_heads, world, rank, q, peer_records=None, spin_
     lib = N.library()
     device = torch.device("cuda", 0)
     rows = layers * q_heads
-    size = lib.inq_exchange_inbox_bytes(world, rows)
+    size = lib.inq_decode_exchange_inbox_bytes(world, rows)
     flag_bytes = 2 * 8 * 512 * 4
     inboxes = [torch.zeros(size, dtype=torch.uint8, device=device) for _ in range(world)]
     if peer_records is not None:
-        flags = inboxes[rank][:flag_bytes].view(torch.int32).view(2, 8, 512)
-        data = inboxes[rank][flag_bytes:].view(torch.float32).view(2, world, rows, 130)
+        words = inboxes[rank][flag_bytes:].view(torch.int32).view(2, world, rows, 130, 2)
         for src in range(world):
             if src != rank:
-                data[:, src] = peer_records[src]
-                flags[:, src] = steps        # "published up to step `steps`": enough for every step run here
+                words[:, src, :, :, 0] = peer_records[src].view(torch.int32)
+                words[1, src, :, :, 1] = 1     # step 1 uses the odd half of the double buffer
+                words[0, src, :, :, 1] = 2     # step 2 the even one
     epoch = torch.zeros(2, dtype=torch.int32, device=device)
     view = N.DecodeExchange()
     for peer in range(world):
@@ -183,8 +183,9 @@ def _split_fixture(layers=3, heads=4, tokens=1000):
 def test_decode_launch_that_exchanges_its_records_matches_the_gathered_merge(world):
     """The exchange inside the decode launch (inq_decode_exchange_t): every rank, run alone with the
     peers' records already in its inbox, must write exactly the rows that all-gather +
-    inq_merge_partials give, must leave its own records in the peers' inboxes, and must advance the
-    step number; two steps use both halves of the double-buffered inbox."""
+    inq_merge_partials give, must leave its own records (every word tagged with the step) in the
+    peers' inboxes, and must advance the step number; two steps use both halves of the double-buffered
+    inbox."""
     from inquant import _native as N
     from inquant.batched import DecodeBatch
     from inquant.split_kv import merge_records, shard_layer
@@ -210,16 +211,16 @@ def test_decode_launch_that_exchanges_its_records_matches_the_gathered_merge(wor
         for peer in range(world):
             if peer == rank:
                 continue
-            pushed = inboxes[peer][flag_bytes:].view(torch.float32).view(2, world, layers * q_heads, 130)
-            flags = inboxes[peer][:flag_bytes].view(torch.int32).view(2, 8, 512)
-            # 7 query heads per KV head: one tile of 8 per (layer, KV head), i.e. layers * 4 pairs
-            assert torch.equal(pushed[0, rank], records[rank]) and torch.equal(pushed[1, rank], records[rank])
-            assert flags[1, rank, :layers * 4].tolist() == [1] * (layers * 4) and flags[0, rank, :layers * 4].tolist() == [2] * (layers * 4)
-            assert int(flags[:, rank, layers * 4:].abs().sum()) == 0
+            pushed = inboxes[peer][flag_bytes:].view(torch.int32).view(2, world, layers * q_heads, 130, 2)
+            want = records[rank].view(torch.int32)
+            assert torch.equal(pushed[0, rank, :, :, 0], want) and torch.equal(pushed[1, rank, :, :, 0], want)
+            assert bool((pushed[1, rank, :, :, 1] == 1).all()) and bool((pushed[0, rank, :, :, 1] == 2).all())
+            others = [src for src in range(world) if src != rank]
+            assert int(pushed[:, others].abs().sum()) == 0 and int(inboxes[peer][:flag_bytes].sum()) == 0
 
 
 def test_decode_launch_exchange_gives_up_when_a_peer_never_publishes():
-    """Rank 0 of two, alone: rank 1's flags never arrive, the bounded wait of every pair runs out,
+    """Rank 0 of two, alone: rank 1's words never arrive, the bounded wait of every pair runs out,
     the status word carries the timeout bit, the rows are zero and the context stays usable."""
     from inquant import _native as N
     layers, q_heads = 2, 28
