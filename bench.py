@@ -1126,7 +1126,8 @@ def run_split_kv(args, torch, dist, device, world, rank):
     record_bytes = LAYERS * Q_HEADS * 130 * 4
     describe = {
         "fused": (f"inside the decode launch: the CTA that merges a (layer, KV head) pair stores its records ({record_bytes} B per rank "
-                  "and step in all) into every peer's inbox over NVLink peer memory, signals, waits (bounded) and merges all ranks' records",
+                  "and step in all) into every peer's inbox over NVLink peer memory, every word as one 8-byte store tagged with the "
+                  "step number (no fence, no flags), polls the peers' words (bounded) and merges all ranks' records",
                   "CUDA graph of ONE launch per rank (decode with the append fused in on the tail owner and the exchange in its merge)"),
         "p2p": (f"peer memory: one kernel per rank stores its {record_bytes} B of records into every peer's inbox over "
                 "NVLink, signals, waits (bounded) and merges",

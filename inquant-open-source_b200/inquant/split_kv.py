@@ -18,9 +18,8 @@ log-sum-exp rule (the cross-rank form of ``triton_attention.py:168-181``).  Two 
             fence, no flags), awaits theirs (bounded) and merges them (``inq_decode_exchange_t``), so a step
             is ONE launch per rank;
 
-``"auto"`` takes peer memory when every rank sits on the same host and the mappings can be made
-(inside the decode launch between two ranks, the separate kernel from four ranks on: the faster one
-of each case as measured), else the all-gather.  Nothing else is exchanged: encode and append are block-local.  The reference
+``"auto"`` takes peer memory inside the decode launch when every rank sits on the same host and the
+mappings can be made (the fastest of the three as measured on 2, 4 and 8 GPUs), else the all-gather.  Nothing else is exchanged: encode and append are block-local.  The reference
 has no multi-GPU path; this module is new.
 """
 from __future__ import annotations
@@ -178,9 +177,8 @@ class SplitKVDecode:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.owns_tail = (self.rank == self.world - 1) if owns_tail is None else owns_tail
-        # measured on B200s: inside the decode launch the exchange is the faster one between two ranks,
-        # the separate kernel from four ranks on
-        self.fused = self.world > 1 and (exchange == "fused" or (exchange == "auto" and self.world == 2))
+        # measured on 2, 4 and 8 B200s: the exchange inside the decode launch is the fastest of the three
+        self.fused = self.world > 1 and exchange in ("fused", "auto")
         self.batch = DecodeBatch(sequences, q_heads, dtype, partials_only=not self.fused)
         n = len(sequences)
         self.peers = None
