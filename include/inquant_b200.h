@@ -309,6 +309,17 @@ int inq_decode_attention_noalloc(const inq_decode_args_t* args /* host */, inq_s
  * across ranks after an all-gather. */
 int inq_merge_partials(const float* records, int32_t n_parts, int64_t n_rows, void* out, int32_t out_dtype,
                        inq_stream_t stream);
+/* Every sealed block of one cached layer back into dense key and value histories in ONE launch, addressed
+ * through the layer's decode descriptors (the 6-pointer block table and the int8 role map of
+ * inq_decode_seq_t, layout 0): what InQuantCache.materialize (cache.py:328-345) does block by block
+ * with PackedTensor.dequantize (codec.py:112-134) and PackedValues.dequantize (value_codec.py:43-48),
+ * same arithmetic, same rounding.  K4 keys with `count` salient channels and 2-bit values in groups of
+ * 64, 128 channels; rows of head h land at out + h * stride_h + (position + block * tokens + t) * 128
+ * elements of out_dtype (fp16 / bf16); out pointers 16-byte aligned, stride_h a multiple of 8. */
+int inq_restore_blocks_table(const int64_t* table, const int8_t* roles, int32_t n_blocks, int32_t heads, int32_t tokens,
+                             int32_t count, void* out_key, void* out_value, int64_t stride_h, int64_t position,
+                             int32_t out_dtype, inq_stream_t stream);
+
 /* Split-KV across the GPUs of ONE node without a library collective: exchange of the partial
  * records over NVLink peer memory fused with their merge, one launch per rank and decode step.
  * Every rank owns an inbox (inq_peer_buffer_create, inq_exchange_inbox_bytes bytes, zeroed) that

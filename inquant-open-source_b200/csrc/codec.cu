@@ -1255,6 +1255,76 @@ __global__ void __launch_bounds__(256) v_dequantize128_kernel(const unsigned cha
   *(uint4*)dst = *(const uint4*)vals;
 }
 
+// All sealed blocks of one cached layer back into a dense history in ONE launch, addressed through the
+// decode descriptors of that layer: the 6-pointer table (key payload, key scales, key padding, value
+// payload, value scales, value offsets per block) and the int8 role map.  CTA (block-head row, token
+// part): keys exactly as k4_dequantize128_kernel, 2-bit values in groups of 64 channels exactly as
+// v_dequantize128_kernel; a thread owns 8 consecutive channels of a token.  Rows land at
+// out + head * stride_h + (position + block * tokens + t) * 128.
+template <typename T>
+__global__ void __launch_bounds__(256) restore_table_kernel(const long long* table, const signed char* roles, int heads, int tokens,
+                                                            int count, T* out_k, T* out_v, long long stride_h, long long position) {
+  __shared__ int role[128];
+  __shared__ float scale[128], pad[128];
+  const int b = blockIdx.x / heads, h = blockIdx.x % heads;
+  const long long* row = table + (long long)b * 6;
+  const unsigned char* kp = (const unsigned char*)row[0] + (long long)h * tokens * 64;
+  const float* ks = (const float*)row[1] + h * 128;
+  const float* kpad = (const float*)row[2] + h * count;
+  const unsigned char* vp = (const unsigned char*)row[3] + (long long)h * tokens * 32;
+  const __half* vs = (const __half*)row[4] + (long long)h * tokens * 2;
+  const __half* vo = (const __half*)row[5] + (long long)h * tokens * 2;
+  if (threadIdx.x < 128) {
+    const int r = roles[((long long)b * heads + h) * 128 + threadIdx.x];
+    role[threadIdx.x] = r;
+    scale[threadIdx.x] = ks[threadIdx.x];
+    pad[threadIdx.x] = (r <= -2 && -r - 2 < count) ? kpad[-r - 2] : 0.f;
+  }
+  __syncthreads();
+  const int c0 = (threadIdx.x & 15) * 8;
+  int r[8];
+  float sc[8], pd[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    r[k] = role[c0 + k];
+    sc[k] = scale[c0 + k];
+    pd[k] = pad[c0 + k];
+  }
+  const long long base = (long long)h * stride_h + (position + (long long)b * tokens) * 128;
+  const int per_cta = (tokens + gridDim.y - 1) / gridDim.y;
+  const int t_begin = blockIdx.y * per_cta, t_end = min(tokens, t_begin + per_cta);
+  for (int t = t_begin + (threadIdx.x >> 4); t < t_end; t += 16) {
+    const unsigned char* line = kp + (long long)t * 64;
+    const unsigned word = *(const unsigned*)(line + (c0 >> 1));
+    T vals[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int slot = (word >> (4 * k)) & 15;
+      float value;
+      if (r[k] >= 0) {
+        const int partner = (line[r[k] >> 1] >> ((r[k] & 1) * 4)) & 15;
+        value = (float)(((slot << 4) | partner) - 128) * sc[k];
+      } else if (r[k] == -1) {
+        value = (float)(slot - 8) * sc[k];
+      } else {
+        value = pd[k];
+      }
+      vals[k] = from_float<T>(value);
+    }
+    *(uint4*)(out_k + base + (long long)t * 128 + c0) = *(const uint4*)vals;
+    // values: 8 channels are two bytes of 2-bit codes and share a group of 64
+    const unsigned short codes = *(const unsigned short*)(vp + (long long)t * 32 + (c0 >> 2));
+    const float vsc = __half2float(vs[t * 2 + (c0 >> 6)]), vof = __half2float(vo[t * 2 + (c0 >> 6)]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float value = (float)((codes >> (2 * k)) & 3u) * vsc;
+      value = value + vof;
+      vals[k] = from_float<T>(value);
+    }
+    *(uint4*)(out_v + base + (long long)t * 128 + c0) = *(const uint4*)vals;
+  }
+}
+
 __global__ void build_roles_kernel(const void* salient, const void* donors, int descriptor_i32, int channels, int count,
                                    void* roles, int role_bytes) {
   const long long row = blockIdx.x;
@@ -1562,6 +1632,31 @@ extern "C" int inq_build_roles(const void* salient, const void* donors, int32_t 
   if (count && (!salient || !donors)) return INQ_ERR_ARGUMENT;
   if (rows == 0) return INQ_OK;
   build_roles_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream_>>>(salient, donors, descriptor_i32, channels, count, roles, role_bytes);
+  INQ_CUDA_CHECK(cudaGetLastError());
+  return INQ_OK;
+}
+
+extern "C" int inq_restore_blocks_table(const int64_t* table, const int8_t* roles, int32_t n_blocks, int32_t heads, int32_t tokens,
+                                        int32_t count, void* out_key, void* out_value, int64_t stride_h, int64_t position,
+                                        int32_t out_dtype, inq_stream_t stream_) {
+  if (!table || !roles || !out_key || !out_value || n_blocks < 0 || heads < 1 || tokens < 1 || count < 0 || count > 64)
+    return INQ_ERR_ARGUMENT;
+  if (out_dtype != INQ_F16 && out_dtype != INQ_BF16) return INQ_ERR_UNSUPPORTED;
+  if ((((uintptr_t)out_key | (uintptr_t)out_value) & 15) != 0 || stride_h % 8 != 0 || position < 0) return INQ_ERR_ARGUMENT;
+  if (n_blocks == 0) return INQ_OK;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  // enough CTAs to fill the device when the layer holds few blocks
+  const long long rows = (long long)n_blocks * heads;
+  int split = 1;
+  while (split < 8 && rows * split < 592 && tokens / (split * 2) >= 16) split *= 2;
+  const dim3 grid((unsigned)rows, (unsigned)split);
+  if (out_dtype == INQ_F16)
+    restore_table_kernel<__half><<<grid, 256, 0, stream>>>((const long long*)table, (const signed char*)roles, heads, tokens, count,
+                                                          (__half*)out_key, (__half*)out_value, stride_h, position);
+  else
+    restore_table_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const long long*)table, (const signed char*)roles, heads, tokens,
+                                                                 count, (__nv_bfloat16*)out_key, (__nv_bfloat16*)out_value, stride_h,
+                                                                 position);
   INQ_CUDA_CHECK(cudaGetLastError());
   return INQ_OK;
 }

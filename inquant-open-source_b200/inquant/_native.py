@@ -169,7 +169,7 @@ EXPORTS = (
     "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
     "inq_prefill_attention", "inq_decode_generic", "inq_decode_generic_workspace_floats",
     "inq_prefill_workspace_bytes",
-    "inq_exchange_merge", "inq_exchange_inbox_bytes", "inq_decode_exchange_inbox_bytes", "inq_peer_buffer_create", "inq_peer_buffer_open",
+    "inq_exchange_merge", "inq_exchange_inbox_bytes", "inq_decode_exchange_inbox_bytes", "inq_restore_blocks_table", "inq_peer_buffer_create", "inq_peer_buffer_open",
     "inq_peer_buffer_close", "inq_peer_buffer_destroy",
 )
 
@@ -185,6 +185,7 @@ SIGNATURES = {
     "inq_v_encode": [_P, _P, _P],
     "inq_v_dequantize": [_P, _P, _P, _L, _I, _I, _I, _I, _P, _I, _P],
     "inq_build_roles": [_P, _P, _I, _L, _I, _I, _P, _I, _P],
+    "inq_restore_blocks_table": [_P, _P, _I, _I, _I, _I, _P, _P, _L, _L, _I, _P],
     "inq_decode_attention": [_P, _P],
     "inq_write_codec_pages": [_P, _P],
     "inq_decode_attention_noalloc": [_P, _P],

@@ -84,7 +84,8 @@ class PrefillHistory:
     dense cache the packed one exists to avoid.  ``persistent=False`` (the default) therefore keeps
     NO per-layer copy: one scratch pair serves every layer, and a layer's history is rebuilt into it
     from the packed cache for each of its chunks (sink and tail copied, every sealed block
-    dequantised by this library's kernels: a few per cent of the chunk's attention time).  That is
+    dequantised by ONE launch addressed through the layer's decode descriptors,
+    ``inq_restore_blocks_table``: a few per cent of the chunk's attention time).  That is
     the reference's own semantics (``update`` materialises per call) at 2 * H * tokens * C elements
     in total (71 MB for the same prompt).  ``persistent=True`` keeps the per-layer copies and
     dequantises every block once.  ``release`` frees either.  Tensors grow geometrically unless
@@ -98,10 +99,41 @@ class PrefillHistory:
         self.persistent = bool(persistent)
         self._layers: dict[int, list] = {}    # layer -> [key, value, tokens, restored blocks]
         self._scratch: list = [None, None, 0, 0]   # the shared pair of the non-persistent mode
+        self._descriptors: dict[int, object] = {}  # layer -> decode descriptors of its sealed blocks (block table, role map)
 
     def release(self) -> None:
         self._layers.clear()
+        self._descriptors.clear()
         self._scratch = [None, None, 0, 0]
+
+    def _restore_all(self, layer_idx: int, layer, out_key: torch.Tensor, out_value: torch.Tensor, position: int) -> int | None:
+        """Every sealed block of the layer into the two histories by ONE launch, addressed through the
+        layer's decode descriptors (kept here and extended by the blocks each chunk seals); None when the
+        layout is not the one that launch serves (then the blocks are restored arena by arena)."""
+        from .triton_attention import PackedDecodeState
+        blocks = len(layer.key_blocks)
+        if not blocks:
+            return position
+        state = self._descriptors.get(layer_idx)
+        try:
+            if state is None or len(state.key_blocks) > blocks:
+                state = self._descriptors[layer_idx] = PackedDecodeState(layer.key_blocks, layer.value_blocks)
+            elif len(state.key_blocks) < blocks:
+                state.extend(layer.key_blocks, layer.value_blocks)
+        except (ValueError, RuntimeError):
+            self._descriptors.pop(layer_idx, None)
+            return None
+        channels = out_key.shape[3]
+        if not state._preset or channels != 128 or out_key.dtype not in (torch.float16, torch.bfloat16) \
+                or out_key.stride(3) != 1 or out_key.stride(2) != channels or out_value.stride() != out_key.stride():
+            return None
+        tokens = state._packed_tokens
+        rc = N.library().inq_restore_blocks_table(state._tables.data_ptr(), state._key_map.data_ptr(), blocks, out_key.shape[1],
+                                                  tokens, state._salient, out_key.data_ptr(), out_value.data_ptr(),
+                                                  out_key.stride(1), position, N.DTYPE_CODE[out_key.dtype],
+                                                  N.stream_pointer(out_key.device))
+        N.check(rc, "inq_restore_blocks_table")
+        return position + blocks * tokens
 
     def check(self) -> None:
         """Raise for failures recorded while checks were deferred (synchronises the stream)."""
@@ -184,12 +216,14 @@ class PrefillHistory:
         self._room(scratch, seen + tokens, key)
         if seen:
             layer = cache._layers[layer_idx]
+            sink_tokens = 0 if layer.sink_key is None else layer.sink_key.shape[2]
+            after_blocks = self._restore_all(layer_idx, layer, scratch[0], scratch[1], sink_tokens)
             for out, sink, blocks, tail in ((scratch[0], layer.sink_key, layer.key_blocks, layer.residual_key),
                                             (scratch[1], layer.sink_value, layer.value_blocks, layer.residual_value)):
-                position = 0 if sink is None else sink.shape[2]
+                position = sink_tokens
                 if position:
                     out[:, :, :position].copy_(sink)
-                position = restore_blocks(blocks, out, position)
+                position = restore_blocks(blocks, out, position) if after_blocks is None else after_blocks
                 if tail is not None and tail.shape[2]:
                     out[:, :, position:position + tail.shape[2]].copy_(tail)
         scratch[0][:, :, seen:seen + tokens].copy_(key)

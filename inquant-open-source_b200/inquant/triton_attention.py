@@ -69,6 +69,7 @@ class PackedDecodeState:
         self._workspace = None
         self._workspace_pool = workspace_pool
         self._tables = None
+        self._host_tables = None     # pinned mirror of the table: new rows reach the device without a synchronisation
         self._key_map = None
         self._value_map = None
         self._device = None
@@ -167,6 +168,10 @@ class PackedDecodeState:
             key_map = torch.empty((capacity, self._kv_heads, 128), dtype=torch.int8, device=self._device)
             value_map = torch.empty((capacity, self._kv_heads, 128) if self._inquant_values else (0,),
                                     dtype=torch.int8, device=self._device)
+            host_tables = torch.empty((capacity, 6), dtype=torch.int64, pin_memory=True)
+            if old_count:
+                host_tables[:old_count].copy_(self._host_tables[:old_count])
+            self._host_tables = host_tables
             if old_count:
                 tables[:old_count].copy_(self._tables[:old_count])
                 key_map[:old_count].copy_(self._key_map[:old_count])
@@ -174,7 +179,9 @@ class PackedDecodeState:
                     value_map[:old_count].copy_(self._value_map[:old_count])
             self._tables, self._key_map, self._value_map = tables, key_map, value_map
             self._capacity = capacity
-        self._tables[old_count:count].copy_(torch.tensor(pointers, dtype=torch.int64).to(self._device, non_blocking=False))
+        # rows of the pinned mirror are written once and never again, so the asynchronous copy needs no fence
+        self._host_tables[old_count:count].copy_(torch.tensor(pointers, dtype=torch.int64))
+        self._tables[old_count:count].copy_(self._host_tables[old_count:count], non_blocking=True)
         self._write_maps(self._key_map[old_count:count], new_keys, self._salient)
         if self._inquant_values:
             self._write_maps(self._value_map[old_count:count], new_values, self._value_salient)
