@@ -219,8 +219,26 @@ def require_cuda(tensor: torch.Tensor, what: str) -> None:
         raise RuntimeError(f"{what} requires CUDA tensors: the B200 build has no CPU path")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def stream_handle(device: torch.device) -> int:
+    """The current CUDA stream of ``device`` as an integer handle (no stream object is built: this runs
+    several times per decode call)."""
+    if _raw_stream is not None:
+        index = device.index
+        return _raw_stream(torch.cuda.current_device() if index is None else index)
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def stream_identity(device: torch.device) -> tuple:
+    """(device, stream handle) of the current stream, comparable across calls."""
+    index = device.index
+    return (torch.cuda.current_device() if index is None else index, stream_handle(device))
+
+
 def stream_pointer(device: torch.device) -> c_void_p:
-    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    return c_void_p(stream_handle(device))
 
 
 _status_words: dict[torch.device, torch.Tensor] = {}
@@ -302,7 +320,7 @@ _counters: dict[tuple, torch.Tensor] = {}
 def decode_counters(device: torch.device, count: int) -> torch.Tensor:
     """Zero-initialised arrival counters of the fused split-KV merge, one array per
     (device, stream); the kernel leaves them zero, so they are reused launch after launch."""
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    key = (device, stream_handle(device))
     tensor = _counters.get(key)
     if tensor is None or tensor.numel() < count + 1:   # one more: the launch-wide arrival counter of a fused append
         tensor = torch.zeros(max(count + 1, 1024), dtype=torch.int32, device=device)

@@ -36,8 +36,7 @@ class SharedDecodeWorkspace:
         return 0 if self.tensor is None else self.tensor.numel() * self.tensor.element_size()
 
     def acquire(self, shape, device):
-        stream = torch.cuda.current_stream(device)
-        identity = (stream.device, stream.cuda_stream)
+        identity = N.stream_identity(device)
         if self._stream_identity is not None and identity != self._stream_identity:
             raise RuntimeError("Shared decode workspace requires one CUDA stream per cache")
         self._stream_identity = identity
@@ -98,8 +97,7 @@ class PackedDecodeState:
         first = key_blocks[0]
         if first.shape[0] != 1 or first.shape[-1] != 128 or first.payload.device.type != "cuda":
             raise ValueError("Packed decode requires CUDA blocks with batch=1 and head_dim=128")
-        stream = torch.cuda.current_stream(first.payload.device)
-        identity = (stream.device, stream.cuda_stream)
+        identity = N.stream_identity(first.payload.device)
         if self._stream_identity is not None and self._stream_identity != identity:
             raise RuntimeError("Descriptor updates require one CUDA stream per state")
         self._stream_identity = identity
@@ -264,8 +262,7 @@ class PackedDecodeState:
             scale = 128 ** -0.5
         if not math.isfinite(scale) or scale <= 0:
             raise ValueError("attention scale must be positive and finite")
-        stream = torch.cuda.current_stream(query.device)
-        identity = (stream.device, stream.cuda_stream)
+        identity = N.stream_identity(query.device)
         if self._stream_identity is not None and self._stream_identity != identity:
             raise RuntimeError("Packed decode state requires one CUDA stream per state")
         q_per_kv = query.shape[1] // kv_heads
