@@ -80,6 +80,7 @@ class _Layer:
     value_blocks: list = field(default_factory=list)
     packed_nbytes: int = 0
     retired_tail: tuple | None = None               # the tail buffers replaced by the last seal
+    append_args: tuple | None = None                # launch structure of the one-token append, per tail buffer pair
 
     @property
     def sink_key(self):
@@ -380,27 +381,34 @@ class InQuantCache(_HFCache):
     def _write_token(self, layer: _Layer, keys, values, sink_position: int) -> bool:
         """One-kernel write of a single token into the tail (and the sink); False when the
         layout does not meet the kernel's 16-byte alignment rules."""
-        row_bytes = layer.shape[3] * keys.element_size()
-        tensors = (keys, values, layer.tail_key_buffer, layer.tail_value_buffer)
-        if row_bytes % 16 or any(t.data_ptr() % 16 or t.stride(-1) != 1 for t in tensors):
-            return False
         es = keys.element_size()
-        if (keys.stride(1) * es) % 16 or (values.stride(1) * es) % 16 or keys.stride(1) != values.stride(1):
+        row_bytes = layer.shape[3] * es
+        if row_bytes % 16 or keys.data_ptr() % 16 or values.data_ptr() % 16 or keys.stride(-1) != 1 or values.stride(-1) != 1:
             return False
-        args = N.AppendArgs()
-        args.key, args.value, args.src_stride_h = keys.data_ptr(), values.data_ptr(), keys.stride(1) * es
+        if (keys.stride(1) * es) % 16 or keys.stride(1) != values.stride(1):
+            return False
         tk, tv = layer.tail_key_buffer, layer.tail_value_buffer
-        args.tail_key, args.tail_value = tk.data_ptr(), tv.data_ptr()
-        args.tail_stride_h, args.tail_stride_t = tk.stride(1) * es, tk.stride(2) * es
-        args.tail_position, args.tail_capacity = layer.tail_count, tk.shape[2]
+        cached = layer.append_args
+        if cached is None or cached[0] != tk.data_ptr() or cached[1] != tv.data_ptr():
+            # what only changes when the tail buffers are replaced (a seal) is filled once
+            if tk.data_ptr() % 16 or tv.data_ptr() % 16 or tk.stride(-1) != 1 or tv.stride(-1) != 1:
+                return False
+            args = N.AppendArgs()
+            args.tail_key, args.tail_value = tk.data_ptr(), tv.data_ptr()
+            args.tail_stride_h, args.tail_stride_t = tk.stride(1) * es, tk.stride(2) * es
+            args.tail_capacity = tk.shape[2]
+            args.heads, args.row_bytes = layer.shape[1], row_bytes
+            args.status = N.status_word(layer.device).data_ptr()
+            cached = layer.append_args = (tk.data_ptr(), tv.data_ptr(), args, N.ctypes.byref(args))
+        args = cached[2]
+        args.key, args.value, args.src_stride_h = keys.data_ptr(), values.data_ptr(), keys.stride(1) * es
+        args.tail_position = layer.tail_count
         args.sink_position = sink_position
         if sink_position >= 0:
             sk, sv = layer.sink_key_buffer, layer.sink_value_buffer
             args.sink_key, args.sink_value = sk.data_ptr(), sv.data_ptr()
             args.sink_stride_h, args.sink_stride_t = sk.stride(1) * es, sk.stride(2) * es
-        args.heads, args.row_bytes = layer.shape[1], row_bytes
-        args.status = N.status_word(layer.device).data_ptr()
-        N.check(N.library().inq_append_token(N.ctypes.byref(args), N.stream_pointer(layer.device)), "inq_append_token")
+        N.check(N.library().inq_append_token(cached[3], N.stream_pointer(layer.device)), "inq_append_token")
         return True
 
     def _append(self, layer: _Layer, keys, values, want_tail: bool = False):

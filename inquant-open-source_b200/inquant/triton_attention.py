@@ -82,6 +82,10 @@ class PackedDecodeState:
         self._preset = True
         self._capacity = 0
         self._stream_identity = None
+        self._record_counts = {}
+        self._seq_struct = N.DecodeSeq()
+        self._args_struct = N.DecodeArgs()
+        self._args_struct.seq_host = N.ctypes.pointer(self._seq_struct)
         self.extend(key_blocks, value_blocks)
 
     def extend(self, key_blocks, value_blocks):
@@ -272,7 +276,10 @@ class PackedDecodeState:
                                         residual_key, residual_value, residual_t, scale)
         tiles = (q_per_kv + 7) // 8
         pairs = kv_heads * tiles
-        records = workspace_floats(pairs, pairs * pair_units(n_blocks, self._packed_tokens)) // N.RECORD_FLOATS
+        records = self._record_counts.get((pairs, n_blocks))
+        if records is None:
+            records = workspace_floats(pairs, pairs * pair_units(n_blocks, self._packed_tokens)) // N.RECORD_FLOATS
+            self._record_counts = {(pairs, n_blocks): records}     # one entry: the count changes when a block is sealed
         workspace_shape = (records, N.RECORD_FLOATS)
         if self._workspace_pool is not None:
             workspace = self._workspace_pool.acquire(workspace_shape, query.device)
@@ -280,7 +287,7 @@ class PackedDecodeState:
             if self._workspace is None or self._workspace.shape != workspace_shape or self._workspace.device != query.device:
                 self._workspace = torch.empty(workspace_shape, dtype=torch.float32, device=query.device)
             workspace = self._workspace
-        if not N.dense_rows_aligned(query.squeeze(2).unsqueeze(0)):
+        if query.data_ptr() % 16 or query.stride(1) % 8:     # rows of a head: 16-byte aligned (unit channel stride was checked)
             query = query.contiguous()
         output = torch.empty(query.shape, dtype=query.dtype, device=query.device)
         if self._tables is None:
@@ -288,7 +295,7 @@ class PackedDecodeState:
             self._key_map = torch.empty((0, kv_heads, 128), dtype=torch.int8, device=query.device)
             self._value_map = torch.empty((0,), dtype=torch.int8, device=query.device)
             self._device = query.device
-        seq = N.DecodeSeq()
+        seq = self._seq_struct        # reused from call to call: every field a call may leave unset is reset below
         seq.query, seq.output, seq.query_head_stride = query.data_ptr(), output.data_ptr(), query.stride(1)
         seq.table = self._tables.data_ptr() if n_blocks else None
         seq.roles = self._key_map.data_ptr() if n_blocks else None
@@ -297,13 +304,17 @@ class PackedDecodeState:
             seq.sink_key, seq.sink_value = sink_key.data_ptr(), sink_value.data_ptr()
             seq.sink_key_stride_h, seq.sink_key_stride_t = sink_key.stride(1), sink_key.stride(2)
             seq.sink_value_stride_h, seq.sink_value_stride_t = sink_value.stride(1), sink_value.stride(2)
+        else:
+            seq.sink_key = seq.sink_value = None
         if residual_t:
             seq.tail_key, seq.tail_value = residual_key.data_ptr(), residual_value.data_ptr()
             seq.tail_key_stride_h, seq.tail_key_stride_t = residual_key.stride(1), residual_key.stride(2)
             seq.tail_value_stride_h, seq.tail_value_stride_t = residual_value.stride(1), residual_value.stride(2)
+        else:
+            seq.tail_key = seq.tail_value = None
         seq.n_blocks, seq.sink_tokens, seq.tail_tokens = n_blocks, sink_t, residual_t
-        args = N.DecodeArgs()
-        args.n_seq, args.seq_host = 1, N.ctypes.pointer(seq)
+        args = self._args_struct
+        args.n_seq = 1
         args.kv_heads, args.q_per_kv = kv_heads, q_per_kv
         args.block_tokens, args.n_pad = self._packed_tokens, self._salient
         args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[query.dtype], scale
