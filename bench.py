@@ -319,9 +319,9 @@ def build_request(torch, device, seed_base):
 
 def measure_append_and_seal(torch, batch, device):
     """The append kernel alone (one launch writes the new token of all 28 layers into tail, and
-    sink while it fills) and the sealing of one 256-token block of one layer through the codec
-    API (K4 + V2 encoders on [1, 4, 256, 128], including the finite-check read-back): a block is
-    sealed once per 256 decoded tokens and layer."""
+    sink while it fills) and the sealing of one 256-token block of one layer (K4 + V2 encoders on
+    [1, 4, 256, 128], including the finite-check read-back) through the cache and through the two
+    codec calls: a block is sealed once per 256 decoded tokens and layer."""
     from inquant.codec import CodecConfig, quantize
     from inquant.value_codec import quantize_values
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -347,9 +347,31 @@ def measure_append_and_seal(torch, batch, device):
         quantize(block_k, cfg), quantize_values(block_v, 2, 64)
     e1.record()
     torch.cuda.synchronize()
+    codec_us = e0.elapsed_time(e1) / reps * 1e3
+    # the same block sealed the way the cache does it: one `extend` (`update` without the dense history it returns) of BLOCK tokens on a layer whose
+    # tail is full seals exactly one block (both encoders and the tail copy from one host call, one
+    # read of the status word)
+    from inquant.cache import CacheConfig, InQuantCache
+    cache = InQuantCache(CacheConfig(cfg, block_size=BLOCK, residual_length=RESIDUAL, sink_tokens=SINK, value_bits=2,
+                                     value_group_size=64, validate_positions=False))
+    first = torch.randn((1, KV_HEADS, SINK + RESIDUAL, DIM), device=device, generator=gen).bfloat16()
+    cache.extend(first, first, 0)
+    for _ in range(3):
+        cache.extend(block_k, block_v, 0)
+    torch.cuda.synchronize()
+    before = len(cache._layers[0].key_blocks)
+    e0.record()
+    for _ in range(reps):
+        cache.extend(block_k, block_v, 0)
+    e1.record()
+    torch.cuda.synchronize()
+    assert len(cache._layers[0].key_blocks) == before + reps
     seal_us = e0.elapsed_time(e1) / reps * 1e3
     return {"append_us_all_layers": round(append_us, 2), "seal_us_per_block_and_layer": round(seal_us, 1),
-            "seal_us_per_token_amortised_all_layers": round(seal_us * LAYERS / BLOCK, 2)}
+            "seal_us_per_token_amortised_all_layers": round(seal_us * LAYERS / BLOCK, 2),
+            "codec_calls_us_per_block": round(codec_us, 1),
+            "what": "seal: InQuantCache.extend of one 256-token chunk on one layer (K4 + V2 encoders, tail copy, "
+                    "finite-check read-back); codec_calls: quantize + quantize_values of the same block, each with its own read-back"}
 
 
 def encoder_kernels_us(torch, k, v):

@@ -444,6 +444,30 @@ int inq_append_token(const inq_append_args_t* args /* host */, inq_stream_t stre
 int inq_append_token_batch(const inq_append_args_t* records_device, int32_t count, int32_t* status,
                            inq_stream_t stream);
 
+/* ---------------------------------------------------------------- sealing blocks in one call
+ * Everything a cache update that seals blocks does on the device, issued by ONE host call on one
+ * stream: the key encoder, the value encoder (`value_k4` when values are stored as InQuant tensors,
+ * `value` for the affine 2/4-bit codec; either may be NULL) and up to four dense row-range copies
+ * (the tokens the attention sink takes, the remainder that becomes the new exact tail; source and
+ * destination are [heads, tokens, row_bytes] with the byte strides given, all multiples of 16, and
+ * must not overlap).  All arguments are checked before the first launch.
+ * Replaces: cache.py:271-306 (`_append`: cat, one codec call per temporal block through
+ * cache.py:89-119 / value_codec.py:75-88, cloned sink and tail) as one host call. */
+typedef struct {
+  const void* src; void* dst;
+  int64_t src_stride_h, src_stride_t, dst_stride_h, dst_stride_t;   /* bytes */
+  int32_t tokens;       /* rows per head; 0: entry unused */
+  int32_t reserved;
+} inq_row_copy_t;
+typedef struct {
+  const inq_k4_encode_args_t* key;        /* NULL: no key encoder launch */
+  const inq_k4_encode_args_t* value_k4;   /* NULL: values are not InQuant tensors */
+  const inq_v_encode_args_t* value;       /* NULL: no affine value encoder launch */
+  inq_row_copy_t copies[4];
+  int32_t n_copies, heads, row_bytes, reserved;
+} inq_seal_args_t;
+int inq_seal_blocks(const inq_seal_args_t* args /* host */, int32_t* status, inq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

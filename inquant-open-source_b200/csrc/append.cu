@@ -2,6 +2,8 @@
 // while it is still filling, the attention sink.
 #include "common.cuh"
 
+#include <algorithm>
+
 namespace inq {
 
 struct AppendParams {
@@ -75,9 +77,72 @@ __global__ void __launch_bounds__(256) append_batch_kernel(const inq_append_args
   append_one(p);
 }
 
+// Row ranges that a sealing update moves (tokens taken by the sink, the remainder that becomes the
+// new tail): blockIdx.y picks the copy, the x dimension strides over its 16-byte vectors.
+struct RowCopies {
+  const uint4* src[4];
+  uint4* dst[4];
+  long long src_stride_h[4], src_stride_t[4], dst_stride_h[4], dst_stride_t[4];   // 16-byte units
+  int tokens[4];
+  int heads, row_vectors;
+};
+
+__global__ void __launch_bounds__(256) copy_rows_kernel(RowCopies c) {
+  const int which = blockIdx.y;
+  const int tokens = c.tokens[which];
+  const long long total = (long long)c.heads * tokens * c.row_vectors;
+  const uint4* src = c.src[which];
+  uint4* dst = c.dst[which];
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % c.row_vectors);
+    const long long row = i / c.row_vectors;
+    const int t = (int)(row % tokens), h = (int)(row / tokens);
+    dst[h * c.dst_stride_h[which] + t * c.dst_stride_t[which] + v] = src[h * c.src_stride_h[which] + t * c.src_stride_t[which] + v];
+  }
+}
+
 }  // namespace inq
 
 using namespace inq;
+
+extern "C" int inq_seal_blocks(const inq_seal_args_t* a, int32_t* status, inq_stream_t stream) {
+  if (!a || !status || a->n_copies < 0 || a->n_copies > 4) return INQ_ERR_ARGUMENT;
+  RowCopies c;
+  int n = 0;
+  long long most = 0;
+  if (a->n_copies) {
+    if (a->heads < 1 || a->row_bytes < 16 || a->row_bytes % 16) return INQ_ERR_ARGUMENT;
+    for (int i = 0; i < a->n_copies; ++i) {
+      const inq_row_copy_t& r = a->copies[i];
+      if (r.tokens < 0) return INQ_ERR_ARGUMENT;
+      if (!r.tokens) continue;
+      if (!r.src || !r.dst || (uintptr_t)r.src % 16 || (uintptr_t)r.dst % 16) return INQ_ERR_ARGUMENT;
+      if (r.src_stride_h % 16 || r.src_stride_t % 16 || r.dst_stride_h % 16 || r.dst_stride_t % 16) return INQ_ERR_ARGUMENT;
+      c.src[n] = (const uint4*)r.src;
+      c.dst[n] = (uint4*)r.dst;
+      c.src_stride_h[n] = r.src_stride_h / 16;
+      c.src_stride_t[n] = r.src_stride_t / 16;
+      c.dst_stride_h[n] = r.dst_stride_h / 16;
+      c.dst_stride_t[n] = r.dst_stride_t / 16;
+      c.tokens[n] = r.tokens;
+      most = std::max(most, (long long)a->heads * r.tokens * (a->row_bytes / 16));
+      ++n;
+    }
+    c.heads = a->heads;
+    c.row_vectors = a->row_bytes / 16;
+  }
+  // every argument is checked before the first launch: a refused call has launched nothing
+  int rc;
+  if (a->key && (rc = inq_k4_encode(a->key, status, stream)) != INQ_OK) return rc;
+  if (a->value_k4 && (rc = inq_k4_encode(a->value_k4, status, stream)) != INQ_OK) return rc;
+  if (a->value && (rc = inq_v_encode(a->value, status, stream)) != INQ_OK) return rc;
+  if (n) {
+    const unsigned blocks = (unsigned)std::min<long long>((most + 255) / 256, 1184);
+    copy_rows_kernel<<<dim3(blocks, (unsigned)n), 256, 0, (cudaStream_t)stream>>>(c);
+    INQ_CUDA_CHECK(cudaGetLastError());
+  }
+  return INQ_OK;
+}
 
 extern "C" int inq_append_token(const inq_append_args_t* a, inq_stream_t stream) {
   if (!a || !a->key || !a->value || !a->tail_key || !a->tail_value || !a->status) return INQ_ERR_ARGUMENT;

@@ -91,6 +91,17 @@ class AppendArgs(ctypes.Structure):
                 ("sink_position", c_int32), ("heads", c_int32), ("row_bytes", c_int32), ("status", c_void_p)]
 
 
+class RowCopy(ctypes.Structure):
+    _fields_ = [("src", c_void_p), ("dst", c_void_p), ("src_stride_h", c_int64), ("src_stride_t", c_int64),
+                ("dst_stride_h", c_int64), ("dst_stride_t", c_int64), ("tokens", c_int32), ("reserved", c_int32)]
+
+
+class SealArgs(ctypes.Structure):
+    _fields_ = [("key", ctypes.POINTER(K4EncodeArgs)), ("value_k4", ctypes.POINTER(K4EncodeArgs)),
+                ("value", ctypes.POINTER(VEncodeArgs)), ("copies", RowCopy * 4),
+                ("n_copies", c_int32), ("heads", c_int32), ("row_bytes", c_int32), ("reserved", c_int32)]
+
+
 class GenericDecodeArgs(ctypes.Structure):
     _fields_ = [("q", c_void_p), ("out", c_void_p), ("q_stride_h", c_int64), ("table", c_void_p),
                 ("key_roles", c_void_p), ("value_roles", c_void_p),
@@ -166,7 +177,7 @@ EXPORTS = (
     "inq_last_error", "inq_version", "inq_k4_encode", "inq_select_donors", "inq_k4_statistics",
     "inq_k4_dequantize", "inq_k4_dequantize_strided", "inq_v_encode", "inq_v_dequantize", "inq_v_dequantize_strided",
     "inq_build_roles", "inq_write_codec_pages",
-    "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch",
+    "inq_decode_attention", "inq_decode_attention_noalloc", "inq_decode_units", "inq_merge_partials", "inq_decode_workspace_floats", "inq_append_token", "inq_append_token_batch", "inq_seal_blocks",
     "inq_prefill_attention", "inq_decode_generic", "inq_decode_generic_workspace_floats",
     "inq_prefill_workspace_bytes",
     "inq_exchange_merge", "inq_exchange_inbox_bytes", "inq_decode_exchange_inbox_bytes", "inq_restore_blocks_table", "inq_peer_buffer_create", "inq_peer_buffer_open",
@@ -199,6 +210,7 @@ SIGNATURES = {
     "inq_peer_buffer_destroy": [_P],
     "inq_append_token": [_P, _P],
     "inq_append_token_batch": [_P, _I, _P, _P],
+    "inq_seal_blocks": [_P, _P, _P],
 }
 
 

@@ -16,6 +16,7 @@ Only batch-one, append-only inference on CUDA tensors is supported.
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 from typing import Any, Iterator
 
@@ -378,6 +379,105 @@ class InQuantCache(_HFCache):
             return retired
         return self._new_buffers(layer, tokens)
 
+    def _seal_in_one_call(self, layer: _Layer, pending_key, pending_value, blocks: int, copies):
+        """Seal ``blocks`` temporal blocks of 16-bit 128-channel keys and values and move the row
+        ranges of ``copies`` (source tensor, first source token, destination tensor, first destination
+        token, tokens) with ONE host call (C ABI ``inq_seal_blocks``): encoder outputs are allocated,
+        the descriptors computed from the strides of the pending tensors (the block axis becomes the
+        batch axis of the launch through strides alone, reference ``cache.py:89-119``) and nothing is
+        read back.  Returns the new key and value blocks, or None when the layout is outside what
+        this path covers (the general path then does the same work call by call)."""
+        cfg = self.config
+        codec = cfg.codec
+        batch, heads, _, channels = pending_key.shape
+        dtype = pending_key.dtype
+        if (batch != 1 or channels != 128 or dtype not in (torch.float16, torch.bfloat16) or pending_value.dtype != dtype
+                or pending_value.shape != pending_key.shape or not pending_key.is_cuda):
+            return None
+        if cfg.value_bits is not None and channels % cfg.value_group_size:
+            return None
+        tokens = cfg.block_size
+        sources = (pending_key, pending_value)
+        for tensor in sources:
+            if tensor.stride(3) != 1 or tensor.data_ptr() % 16 or tensor.stride(1) % 8 or tensor.stride(2) % 8:
+                return None
+        seal = N.SealArgs()
+        seal.heads, seal.row_bytes = heads, channels * 2
+        n = 0
+        for source, first, target, start, count in copies:
+            if not count:
+                continue
+            if (source.stride(3) != 1 or target.stride(3) != 1 or source.data_ptr() % 16 or target.data_ptr() % 16
+                    or source.stride(1) % 8 or source.stride(2) % 8 or target.stride(1) % 8 or target.stride(2) % 8):
+                return None
+            entry = seal.copies[n]
+            entry.src = source.data_ptr() + first * source.stride(2) * 2
+            entry.dst = target.data_ptr() + start * target.stride(2) * 2
+            entry.src_stride_h, entry.src_stride_t = source.stride(1) * 2, source.stride(2) * 2
+            entry.dst_stride_h, entry.dst_stride_t = target.stride(1) * 2, target.stride(2) * 2
+            entry.tokens = count
+            n += 1
+        seal.n_copies = n
+        device = pending_key.device
+        code = N.DTYPE_CODE[dtype]
+
+        def rows(tensor):
+            return N.Input(tensor.data_ptr(), code, blocks, heads, tokens * tensor.stride(2), tensor.stride(1),
+                           tensor.stride(2), tokens, channels, None, 0, 0)
+
+        def field(tensor, row_bytes):
+            return N.Field(tensor.data_ptr(), row_bytes * heads, row_bytes)
+
+        none = N.Field(None, 0, 0)
+
+        def k4_launch(tensor):
+            count = math.floor(channels * codec.salient_fraction)
+            payload = torch.empty((blocks, heads, tokens, channels // 2), dtype=torch.uint8, device=device)
+            scales = torch.empty((blocks, heads, channels), dtype=torch.float32, device=device)
+            salient = torch.empty((blocks, heads, count), dtype=torch.uint8, device=device)
+            donors = torch.empty((blocks, heads, count), dtype=torch.uint8, device=device)
+            padding = torch.empty((blocks, heads, count), dtype=torch.float32, device=device)
+            args = N.K4EncodeArgs()
+            args.input = rows(tensor)
+            args.sample_stride, args.count = codec.sample_stride, count
+            args.min_error = int(codec.donor_policy == "min_error")
+            args.payload, args.scales = field(payload, tokens * channels // 2), field(scales, channels * 4)
+            args.padding = field(padding, count * 4) if count else none
+            args.salient = field(salient, count) if count else none
+            args.donors = field(donors, count) if count else none
+            args.roles, args.role_bytes, args.descriptor_i32 = none, 0, 0
+            packed = PackedTensor(payload, scales, salient, donors, padding, (blocks, heads, tokens, channels), dtype)
+            return args, packed
+
+        key_args, packed_keys = k4_launch(pending_key)
+        seal.key = N.ctypes.pointer(key_args)
+        if cfg.value_bits is None:
+            value_args, packed_values = k4_launch(pending_value)
+            seal.value_k4 = N.ctypes.pointer(value_args)
+        else:
+            from .value_codec import ArenaPackedValues, PackedValues
+            bits, group = cfg.value_bits, cfg.value_group_size
+            payload = torch.empty((blocks, heads, tokens, channels * bits // 8), dtype=torch.uint8, device=device)
+            scales = torch.empty((blocks, heads, tokens, channels // group), dtype=torch.float16, device=device)
+            offsets = torch.empty((blocks, heads, tokens, channels // group), dtype=torch.float16, device=device)
+            value_args = N.VEncodeArgs()
+            value_args.input = rows(pending_value)
+            value_args.bits, value_args.group = bits, group
+            value_args.payload = field(payload, tokens * channels * bits // 8)
+            value_args.scales = field(scales, tokens * (channels // group) * 2)
+            value_args.offsets = field(offsets, tokens * (channels // group) * 2)
+            seal.value = N.ctypes.pointer(value_args)
+            packed_values = PackedValues(payload, scales, offsets, (blocks, heads, tokens, channels), dtype, bits, group)
+        N.check(N.library().inq_seal_blocks(N.ctypes.byref(seal), N.status_word(device).data_ptr(), N.stream_pointer(device)),
+                "inq_seal_blocks")
+        if blocks == 1:
+            return [packed_keys], [packed_values]
+        shape = (1, heads, tokens, channels)
+        new_keys = ArenaPackedTensor.split(packed_keys, blocks, shape, dtype)
+        if cfg.value_bits is None:
+            return new_keys, ArenaPackedTensor.split(packed_values, blocks, shape, dtype)
+        return new_keys, ArenaPackedValues.split(packed_values, blocks, shape, dtype)
+
     def _write_token(self, layer: _Layer, keys, values, sink_position: int) -> bool:
         """One-kernel write of a single token into the tail (and the sink); False when the
         layout does not meet the kernel's 16-byte alignment rules."""
@@ -464,25 +564,37 @@ class InQuantCache(_HFCache):
                 else:
                     pending_key = torch.cat((layer.residual_key, pending_key), dim=2)
                     pending_value = torch.cat((layer.residual_value, pending_value), dim=2)
-        # Both encoders are launched before either finite check is read: the key and value kernels
-        # run back to back while the host builds the block views and the new tail, and one read of
-        # the status word (one synchronisation instead of two) decides before any state changes.
-        with N.deferred_status():
-            new_keys = _quantize_temporal_blocks(pending_key, blocks, cfg.block_size, cfg.codec)
-            if cfg.value_bits is None:
-                new_values = _quantize_temporal_blocks(pending_value, blocks, cfg.block_size, cfg.codec)
-            else:
-                from .value_codec import quantize_value_blocks
-                new_values = quantize_value_blocks(pending_value, blocks, cfg.block_size, cfg.value_bits,
-                                                   cfg.value_group_size)
         offset = blocks * cfg.block_size
         remainder = pending_key.shape[2] - offset
         # a new tail buffer: views handed out earlier keep the old one alive and unchanged.  The
         # buffer retired by the previous seal is taken again when nothing else refers to it any more.
         tail_key_buffer, tail_value_buffer = self._tail_buffers_for(layer, max(capacity, remainder))
-        if remainder:
-            tail_key_buffer[:, :, :remainder].copy_(pending_key[:, :, offset:])
-            tail_value_buffer[:, :, :remainder].copy_(pending_value[:, :, offset:])
+        # Both encoders are launched before either finite check is read: the key and value kernels
+        # run back to back while the host builds the block views, and one read of the status word
+        # (one synchronisation instead of two) decides before any state changes.  Where the layout
+        # allows, the encoders and the copies into the new tail and the sink are one host call; rows
+        # that the copies write lie beyond what the layer's counters expose until the check passed.
+        sealed = None
+        if blocks:
+            sealed = self._seal_in_one_call(layer, pending_key, pending_value, blocks, (
+                (pending_key, offset, tail_key_buffer, 0, remainder),
+                (pending_value, offset, tail_value_buffer, 0, remainder),
+                (keys, 0, layer.sink_key_buffer, layer.sink_count, take_sink),
+                (values, 0, layer.sink_value_buffer, layer.sink_count, take_sink)))
+        if sealed is not None:
+            new_keys, new_values = sealed
+        else:
+            with N.deferred_status():
+                new_keys = _quantize_temporal_blocks(pending_key, blocks, cfg.block_size, cfg.codec)
+                if cfg.value_bits is None:
+                    new_values = _quantize_temporal_blocks(pending_value, blocks, cfg.block_size, cfg.codec)
+                else:
+                    from .value_codec import quantize_value_blocks
+                    new_values = quantize_value_blocks(pending_value, blocks, cfg.block_size, cfg.value_bits,
+                                                       cfg.value_group_size)
+            if remainder:
+                tail_key_buffer[:, :, :remainder].copy_(pending_key[:, :, offset:])
+                tail_value_buffer[:, :, :remainder].copy_(pending_value[:, :, offset:])
         if blocks and N.nonfinite_reported(layer.device):
             # the failure path alone works out which tensor it was (same messages as the codecs)
             if not bool(torch.isfinite(pending_key[:, :, :offset]).all()):
@@ -490,7 +602,7 @@ class InQuantCache(_HFCache):
             if cfg.value_bits is None:
                 raise ValueError("x must contain finite values representable in float32")
             raise ValueError("Values and stored FP16 quantization parameters must be finite")
-        if take_sink:
+        if take_sink and sealed is None:
             layer.sink_key_buffer[:, :, layer.sink_count:layer.sink_count + take_sink].copy_(keys[:, :, :take_sink])
             layer.sink_value_buffer[:, :, layer.sink_count:layer.sink_count + take_sink].copy_(values[:, :, :take_sink])
         layer.sink_count += take_sink

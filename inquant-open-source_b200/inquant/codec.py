@@ -9,7 +9,9 @@ inputs.  Tensors must live on a CUDA device.
 from __future__ import annotations
 
 import math
+from collections import deque
 from dataclasses import dataclass
+from itertools import repeat
 
 import torch
 
@@ -121,53 +123,55 @@ class PackedTensor:
 
 
 class ArenaPackedTensor(PackedTensor):
-    """One block of a batch that a single encoder launch sealed.  Its field tensors are views of
-    that launch's output arena and are created on first access: a 32K-token prefill seals 127
-    blocks per layer, and building 5 views for each costs more host time than the launch."""
+    """One block of a batch that a single encoder launch sealed.  An instance holds nothing but
+    ``(arena, index)`` in a slot: its field tensors are views of that launch's output arena, created
+    on first access, and its shape and dtype are read off the arena -- a 32K-token prefill seals 127
+    blocks per layer, and building views (or even instance dictionaries) for each costs more host
+    time than the launch."""
 
+    __slots__ = ("_arena",)
     _FIELDS = ("payload", "scales", "salient_channels", "donor_channels", "padding")
 
-    def __init__(self, arena: PackedTensor, index: int, shape, original_dtype) -> None:
+    def __init__(self, arena: PackedTensor, index: int, shape=None, original_dtype=None) -> None:
         object.__setattr__(self, "_arena", (arena, index))
-        object.__setattr__(self, "shape", shape)
-        object.__setattr__(self, "original_dtype", original_dtype)
 
     @classmethod
-    def split(cls, arena: PackedTensor, count: int, shape, original_dtype) -> list:
-        """The ``count`` blocks of ``arena`` as a list.  Attributes go straight into the instance
-        dictionaries: a frozen dataclass' constructor costs four times as much per block."""
-        new, blocks = object.__new__, []
-        for index in range(count):
-            block = new(cls)
-            fields = block.__dict__
-            fields["_arena"] = (arena, index)
-            fields["shape"] = shape
-            fields["original_dtype"] = original_dtype
-            blocks.append(block)
+    def split(cls, arena: PackedTensor, count: int, shape=None, original_dtype=None) -> list:
+        """The ``count`` blocks of ``arena`` as a list, built without running Python code per block
+        (the slot's descriptor is applied by ``map``)."""
+        blocks = list(map(object.__new__, repeat(cls, count)))
+        deque(map(cls.__dict__["_arena"].__set__, blocks, zip(repeat(arena), range(count))), maxlen=0)
         return blocks
 
-    def __getattr__(self, name):   # reached only while a field has not been materialised yet
+    def __getattr__(self, name):   # reached only while an attribute has not been materialised yet
+        if name == "_arena":
+            raise AttributeError(name)
+        arena, index = self._arena
         if name in ArenaPackedTensor._FIELDS:
-            arena, index = self.__dict__["_arena"]
-            view = getattr(arena, name)[index:index + 1]
-            object.__setattr__(self, name, view)
-            return view
-        raise AttributeError(name)
+            value = getattr(arena, name)[index:index + 1]
+        elif name == "shape":
+            value = (1, *arena.shape[1:])
+        elif name == "original_dtype":
+            value = arena.original_dtype
+        else:
+            raise AttributeError(name)
+        object.__setattr__(self, name, value)
+        return value
 
     def field_pointer(self, name: str) -> int:
         """Device address of a field without creating its view."""
-        arena, index = self.__dict__["_arena"]
+        arena, index = self._arena
         tensor = getattr(arena, name)
         return tensor.data_ptr() + index * tensor.stride(0) * tensor.element_size()
 
     @property
     def payload_nbytes(self) -> int:
-        arena, _ = self.__dict__["_arena"]
+        arena, _ = self._arena
         return _logical_bytes(arena.payload) // arena.payload.shape[0]
 
     @property
     def nbytes(self) -> int:
-        arena, _ = self.__dict__["_arena"]
+        arena, _ = self._arena
         return sum(_logical_bytes(t) // t.shape[0] for t in arena.tensors.values())
 
 

@@ -56,6 +56,28 @@ def pair_units(n_blocks: int, block_tokens: int) -> int:
     return int(N.library().inq_decode_units(n_blocks, block_tokens))
 
 
+def _stacked_field(blocks, name: str) -> torch.Tensor:
+    """``torch.cat`` of one field over ``blocks`` along the block axis, contiguous.  Consecutive
+    blocks of one encoder arena are taken as ONE slice of the arena's tensor, so that a layer sealed
+    by a single launch needs neither a view per block nor a copy."""
+    pieces, run = [], None      # run: [arena, first index, one past the last index]
+    for block in blocks:
+        arena = getattr(block, "_arena", None)
+        if arena is not None and run is not None and run[0] is arena[0] and run[2] == arena[1]:
+            run[2] += 1
+            continue
+        if run is not None:
+            pieces.append(getattr(run[0], name)[run[1]:run[2]])
+            run = None
+        if arena is not None:
+            run = [arena[0], arena[1], arena[1] + 1]
+        else:
+            pieces.append(getattr(block, name))
+    if run is not None:
+        pieces.append(getattr(run[0], name)[run[1]:run[2]])
+    return (pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=0)).contiguous()
+
+
 class PackedDecodeState:
     """Reusable descriptors for immutable blocks; exact tails are per-call inputs
     (reference ``triton_attention.py:211-388``)."""
@@ -113,7 +135,7 @@ class PackedDecodeState:
         # Blocks of an encoder arena are judged by the arena's tensors, so that none of their field
         # views has to be created here (a 32K-token layer holds over a thousand of them).
         def parts(block):
-            arena = block.__dict__.get("_arena") if hasattr(block, "__dict__") else None
+            arena = getattr(block, "_arena", None)
             return arena[0] if arena is not None else block
 
         new_keys, new_values = key_blocks[old_count:], value_blocks[old_count:]
@@ -152,11 +174,25 @@ class PackedDecodeState:
                 raise ValueError("All packed tensors must share the same CUDA device")
         last_field = "padding" if self._inquant_values else "offsets"
         pointers = []
+        bases = {}     # per encoder arena: (address, bytes per block) of the three fields the kernel reads
+
+        def located(block, names):
+            arena = getattr(block, "_arena", None)
+            if arena is None:
+                return None
+            owner, index = arena
+            entry = bases.get(id(owner))
+            if entry is None:
+                entry = bases[id(owner)] = [(t.data_ptr(), t.stride(0) * t.element_size())
+                                            for t in (getattr(owner, name) for name in names)]
+            return [base + index * step for base, step in entry]
+
+        key_fields, value_fields = ("payload", "scales", "padding"), ("payload", "scales", last_field)
         for k, v in zip(new_keys, new_values):
-            if hasattr(k, "field_pointer") and hasattr(v, "field_pointer"):
-                # blocks of one encoder launch: contiguous slices of its arena, addressed directly
-                pointers.append([k.field_pointer("payload"), k.field_pointer("scales"), k.field_pointer("padding"),
-                                 v.field_pointer("payload"), v.field_pointer("scales"), v.field_pointer(last_field)])
+            # blocks of one encoder launch: contiguous slices of its arena, addressed directly
+            at_k, at_v = located(k, key_fields), located(v, value_fields)
+            if at_k is not None and at_v is not None:
+                pointers.append(at_k + at_v)
                 continue
             for t in (*k.tensors.values(), *v.tensors.values()):
                 if not t.is_contiguous():
@@ -165,7 +201,10 @@ class PackedDecodeState:
                              v.payload.data_ptr(), v.scales.data_ptr(), getattr(v, last_field).data_ptr()])
         count = len(key_blocks)
         if count > self._capacity:
-            capacity = count if not self._capacity else max(count, min(self._capacity * 2, count + 7))
+            # a few rows to spare from the first allocation on: the seal that follows a prefill (and
+            # seven more) then extends the tables in place instead of reallocating them and their
+            # pinned mirror in the middle of a decode step
+            capacity = count + 8 if not self._capacity else max(count + 8, min(self._capacity * 2, count + 64))
             tables = torch.empty((capacity, 6), dtype=torch.int64, device=self._device)
             key_map = torch.empty((capacity, self._kv_heads, 128), dtype=torch.int8, device=self._device)
             value_map = torch.empty((capacity, self._kv_heads, 128) if self._inquant_values else (0,),
@@ -192,8 +231,8 @@ class PackedDecodeState:
     def _write_maps(self, result, blocks, count):
         """Roles: donor channel 0..127 for a salient channel, -1 normal, -2-i for the i-th donor
         (C ABI ``inq_build_roles``; reference ``triton_attention.py:301-309``)."""
-        sources = torch.cat([block.salient_channels for block in blocks], dim=0).contiguous()
-        donors = torch.cat([block.donor_channels for block in blocks], dim=0).contiguous()
+        sources = _stacked_field(blocks, "salient_channels")
+        donors = _stacked_field(blocks, "donor_channels")
         rows = len(blocks) * self._kv_heads
         rc = N.library().inq_build_roles(N.pointer(sources), N.pointer(donors), 0, rows, 128, count,
                                          N.pointer(result), 1, N.stream_pointer(self._device))

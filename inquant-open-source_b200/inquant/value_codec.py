@@ -1,6 +1,8 @@
 """Per-token affine INT2/INT4 value codec: same interface as the reference
 ``inquant/value_codec.py``, computed by the sm_100a kernel behind ``inq_v_encode``."""
+from collections import deque
 from dataclasses import dataclass
+from itertools import repeat
 
 import torch
 
@@ -58,55 +60,50 @@ class PackedValues:
 
 
 class ArenaPackedValues(PackedValues):
-    """One block of a batch sealed by a single value-encoder launch; field views are created on
-    first access (see ``codec.ArenaPackedTensor``)."""
+    """One block of a batch sealed by a single value-encoder launch: ``(arena, index)`` in a slot,
+    everything else read off the arena on first access (see ``codec.ArenaPackedTensor``)."""
 
+    __slots__ = ("_arena",)
     _FIELDS = ("payload", "scales", "offsets")
 
-    def __init__(self, arena: PackedValues, index: int, shape, original_dtype) -> None:
+    def __init__(self, arena: PackedValues, index: int, shape=None, original_dtype=None) -> None:
         object.__setattr__(self, "_arena", (arena, index))
-        object.__setattr__(self, "shape", shape)
-        object.__setattr__(self, "original_dtype", original_dtype)
-        object.__setattr__(self, "bits", arena.bits)
-        object.__setattr__(self, "group_size", arena.group_size)
 
     @classmethod
-    def split(cls, arena: PackedValues, count: int, shape, original_dtype) -> list:
+    def split(cls, arena: PackedValues, count: int, shape=None, original_dtype=None) -> list:
         """The ``count`` blocks of ``arena`` as a list (see ``codec.ArenaPackedTensor.split``)."""
-        new, blocks = object.__new__, []
-        bits, group_size = arena.bits, arena.group_size
-        for index in range(count):
-            block = new(cls)
-            fields = block.__dict__
-            fields["_arena"] = (arena, index)
-            fields["shape"] = shape
-            fields["original_dtype"] = original_dtype
-            fields["bits"] = bits
-            fields["group_size"] = group_size
-            blocks.append(block)
+        blocks = list(map(object.__new__, repeat(cls, count)))
+        deque(map(cls.__dict__["_arena"].__set__, blocks, zip(repeat(arena), range(count))), maxlen=0)
         return blocks
 
     def __getattr__(self, name):
+        if name == "_arena":
+            raise AttributeError(name)
+        arena, index = self._arena
         if name in ArenaPackedValues._FIELDS:
-            arena, index = self.__dict__["_arena"]
-            view = getattr(arena, name)[index:index + 1]
-            object.__setattr__(self, name, view)
-            return view
-        raise AttributeError(name)
+            value = getattr(arena, name)[index:index + 1]
+        elif name == "shape":
+            value = (1, *arena.shape[1:])
+        elif name in ("original_dtype", "bits", "group_size"):
+            value = getattr(arena, name)
+        else:
+            raise AttributeError(name)
+        object.__setattr__(self, name, value)
+        return value
 
     def field_pointer(self, name: str) -> int:
-        arena, index = self.__dict__["_arena"]
+        arena, index = self._arena
         tensor = getattr(arena, name)
         return tensor.data_ptr() + index * tensor.stride(0) * tensor.element_size()
 
     @property
     def payload_nbytes(self):
-        arena, _ = self.__dict__["_arena"]
+        arena, _ = self._arena
         return _logical_bytes(arena.payload) // arena.payload.shape[0]
 
     @property
     def nbytes(self):
-        arena, _ = self.__dict__["_arena"]
+        arena, _ = self._arena
         return sum(_logical_bytes(t) // t.shape[0] for t in arena.tensors.values())
 
 

@@ -56,13 +56,15 @@ def test_struct_mirrors_match_the_header_as_a_c_compiler_lays_it_out(tmp_path):
                ("inq_decode_args_t", N.DecodeArgs), ("inq_append_args_t", N.AppendArgs),
                ("inq_decode_generic_args_t", N.GenericDecodeArgs), ("inq_prefill_args_t", N.PrefillArgs),
                ("inq_exchange_rank_t", N.ExchangeRank), ("inq_exchange_args_t", N.ExchangeArgs),
-               ("inq_decode_exchange_t", N.DecodeExchange)]
+               ("inq_decode_exchange_t", N.DecodeExchange), ("inq_row_copy_t", N.RowCopy),
+               ("inq_seal_args_t", N.SealArgs)]
     offsets = [("inq_input_t", "num_slots", N.Input.num_slots.offset),
                ("inq_decode_seq_t", "pool_pages", N.DecodeSeq.pool_pages.offset),
                ("inq_decode_seq_t", "tail_tokens_device", N.DecodeSeq.tail_tokens_device.offset),
                ("inq_decode_seq_t", "partial_output", N.DecodeSeq.partial_output.offset),
                ("inq_decode_args_t", "exchange_device", N.DecodeArgs.exchange_device.offset),
-               ("inq_decode_exchange_t", "n_rows", N.DecodeExchange.n_rows.offset)]
+               ("inq_decode_exchange_t", "n_rows", N.DecodeExchange.n_rows.offset),
+               ("inq_seal_args_t", "n_copies", N.SealArgs.n_copies.offset)]
     lines = ["#include <stdio.h>", "#include <stddef.h>", f'#include "{HEADER}"', "int main(void) {"]
     lines += [f'  printf("%zu\\n", sizeof({name}));' for name, _ in structs]
     lines += [f'  printf("%zu\\n", offsetof({name}, {field}));' for name, field, _ in offsets]
@@ -88,3 +90,25 @@ def test_exchange_entry_points_check_their_arguments_without_a_gpu():
     assert lib.inq_peer_buffer_create(0, None, None) == N.ERR_ARGUMENT
     assert lib.inq_peer_buffer_open(None, None) == N.ERR_ARGUMENT
     assert lib.inq_peer_buffer_close(None) == N.ERR_ARGUMENT and lib.inq_peer_buffer_destroy(None) == N.ERR_ARGUMENT
+
+
+def test_seal_entry_point_refuses_bad_row_copies_before_any_launch():
+    """`inq_seal_blocks` checks every argument before its first launch, so a refused call needs no GPU."""
+    from inquant import _native as N
+    lib = N.library()
+    word = ctypes.c_int32(0)
+    status = ctypes.cast(ctypes.pointer(word), ctypes.c_void_p)
+    assert lib.inq_seal_blocks(None, status, None) == N.ERR_ARGUMENT
+    args = N.SealArgs()
+    assert lib.inq_seal_blocks(ctypes.byref(args), None, None) == N.ERR_ARGUMENT
+    args.n_copies = 5
+    assert lib.inq_seal_blocks(ctypes.byref(args), status, None) == N.ERR_ARGUMENT
+    args.n_copies, args.heads, args.row_bytes = 1, 4, 250          # rows are not whole 16-byte vectors
+    assert lib.inq_seal_blocks(ctypes.byref(args), status, None) == N.ERR_ARGUMENT
+    args.row_bytes = 256
+    args.copies[0].src, args.copies[0].dst, args.copies[0].tokens = 4096, 8200, 3   # destination not 16-byte aligned
+    assert lib.inq_seal_blocks(ctypes.byref(args), status, None) == N.ERR_ARGUMENT
+    args.copies[0].dst, args.copies[0].src_stride_t = 8192, 250
+    assert lib.inq_seal_blocks(ctypes.byref(args), status, None) == N.ERR_ARGUMENT
+    # nothing to encode and nothing to copy is a valid call that launches nothing
+    assert lib.inq_seal_blocks(ctypes.byref(N.SealArgs()), status, None) == N.OK

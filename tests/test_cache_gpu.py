@@ -189,6 +189,56 @@ def test_batched_prefill_matches_serial_blocks():
     assert cache.nbytes == expected_bytes + cache.sink_nbytes + cache.residual_nbytes
 
 
+@pytest.mark.parametrize("value_bits", [None, 2, 4])
+def test_one_call_sealing_equals_the_call_by_call_path(value_bits, monkeypatch):
+    """Sealing through ``inq_seal_blocks`` (encoders and the sink / tail copies from one host call)
+    leaves byte for byte what the general path leaves: every packed field, the sink and the tail,
+    over a prefill of several blocks, chunks that cross block boundaries, sink tokens arriving in
+    the same call as sealed blocks, and decode steps that seal."""
+    CacheConfig, InQuantCache, CodecConfig, _ = _mods()
+    cfg = CacheConfig(CodecConfig(donor_policy="min_error"), block_size=32, residual_length=16, sink_tokens=4,
+                      value_bits=value_bits, value_group_size=64, validate_positions=False)
+    key, value = to_device(_randn(61, (1, 2, 400, 128))), to_device(_randn(62, (1, 2, 400, 128)))
+    # heads-major memory as a model hands it over: [1, tokens, heads, 128] transposed
+    strided_key = key.transpose(1, 2).contiguous().transpose(1, 2)
+    chunks = [(0, 3), (3, 150), (150, 151), (151, 290), (290, 291)] + [(t, t + 1) for t in range(291, 400)]
+
+    def run(one_call, k):
+        calls = []
+        if one_call:
+            original = InQuantCache._seal_in_one_call
+
+            def counted(self, *args):
+                result = original(self, *args)
+                calls.append(result is not None)
+                return result
+            monkeypatch.setattr(InQuantCache, "_seal_in_one_call", counted)
+        else:
+            monkeypatch.setattr(InQuantCache, "_seal_in_one_call", lambda self, *args: None)
+        cache = InQuantCache(cfg)
+        for start, stop in chunks:
+            if stop - start == 1 and start > 150:
+                cache.append_for_attention(k[:, :, start:stop], value[:, :, start:stop], 0)
+            else:
+                cache.extend(k[:, :, start:stop], value[:, :, start:stop], 0)
+        monkeypatch.undo()
+        return cache._layers[0], calls
+
+    general, _ = run(False, key)
+    for k in (key, strided_key):
+        fast, calls = run(True, k)
+        assert calls and all(calls)
+        assert len(fast.key_blocks) == len(general.key_blocks) == (400 - 4 - 16) // 32
+        assert fast.sink_count == general.sink_count == 4 and fast.tail_count == general.tail_count
+        for mine, theirs in zip(fast.key_blocks + fast.value_blocks, general.key_blocks + general.value_blocks):
+            assert type(mine).__mro__[-2] is type(theirs).__mro__[-2] and mine.shape == theirs.shape
+            for name, tensor in theirs.tensors.items():
+                assert torch.equal(mine.tensors[name], tensor), name
+        for a, b in ((fast.sink_key, general.sink_key), (fast.sink_value, general.sink_value),
+                     (fast.residual_key, general.residual_key), (fast.residual_value, general.residual_value)):
+            assert torch.equal(a, b)
+
+
 def test_positions_layers_reset_and_unsupported_operations():
     CacheConfig, InQuantCache, CodecConfig, _ = _mods()
     from unittest.mock import patch
