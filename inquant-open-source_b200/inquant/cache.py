@@ -379,14 +379,17 @@ class InQuantCache(_HFCache):
             return retired
         return self._new_buffers(layer, tokens)
 
-    def _seal_in_one_call(self, layer: _Layer, pending_key, pending_value, blocks: int, copies):
-        """Seal ``blocks`` temporal blocks of 16-bit 128-channel keys and values and move the row
-        ranges of ``copies`` (source tensor, first source token, destination tensor, first destination
-        token, tokens) with ONE host call (C ABI ``inq_seal_blocks``): encoder outputs are allocated,
-        the descriptors computed from the strides of the pending tensors (the block axis becomes the
-        batch axis of the launch through strides alone, reference ``cache.py:89-119``) and nothing is
-        read back.  Returns the new key and value blocks, or None when the layout is outside what
-        this path covers (the general path then does the same work call by call)."""
+    def _seal_direct(self, layer: _Layer, pending_key, pending_value, blocks: int, copy_sources, copies):
+        """Seal ``blocks`` temporal blocks of 16-bit 128-channel keys and values with descriptors
+        computed from the strides of the pending tensors (the block axis becomes the batch axis of
+        a launch through strides alone, reference ``cache.py:89-119``) and nothing read back.  The
+        key encoder -- the longest kernel of a seal -- is launched first (``inq_k4_encode``), so
+        that it runs while the host allocates the rest; the value encoder and the row ranges
+        ``copies()`` names (source tensor, first source token, destination tensor, first
+        destination token, tokens; destinations are the layer's own contiguous buffers) follow in
+        ONE host call (``inq_seal_blocks``).  Returns the new key and value blocks, or None -- before
+        anything is launched -- when the layout is outside what this path covers (the general path
+        then does the same work call by call)."""
         cfg = self.config
         codec = cfg.codec
         batch, heads, _, channels = pending_key.shape
@@ -396,41 +399,26 @@ class InQuantCache(_HFCache):
             return None
         if cfg.value_bits is not None and channels % cfg.value_group_size:
             return None
+        for tensor in (pending_key, pending_value, *copy_sources):
+            strides = tensor.stride()
+            if strides[3] != 1 or tensor.data_ptr() % 16 or strides[1] % 8 or strides[2] % 8:
+                return None
         tokens = cfg.block_size
-        sources = (pending_key, pending_value)
-        for tensor in sources:
-            if tensor.stride(3) != 1 or tensor.data_ptr() % 16 or tensor.stride(1) % 8 or tensor.stride(2) % 8:
-                return None
-        seal = N.SealArgs()
-        seal.heads, seal.row_bytes = heads, channels * 2
-        n = 0
-        for source, first, target, start, count in copies:
-            if not count:
-                continue
-            if (source.stride(3) != 1 or target.stride(3) != 1 or source.data_ptr() % 16 or target.data_ptr() % 16
-                    or source.stride(1) % 8 or source.stride(2) % 8 or target.stride(1) % 8 or target.stride(2) % 8):
-                return None
-            entry = seal.copies[n]
-            entry.src = source.data_ptr() + first * source.stride(2) * 2
-            entry.dst = target.data_ptr() + start * target.stride(2) * 2
-            entry.src_stride_h, entry.src_stride_t = source.stride(1) * 2, source.stride(2) * 2
-            entry.dst_stride_h, entry.dst_stride_t = target.stride(1) * 2, target.stride(2) * 2
-            entry.tokens = count
-            n += 1
-        seal.n_copies = n
         device = pending_key.device
         code = N.DTYPE_CODE[dtype]
+        status = N.status_word(device).data_ptr()
+        lib = N.library()
+        none = N.Field(None, 0, 0)
 
         def rows(tensor):
-            return N.Input(tensor.data_ptr(), code, blocks, heads, tokens * tensor.stride(2), tensor.stride(1),
-                           tensor.stride(2), tokens, channels, None, 0, 0)
+            _, stride_h, stride_t, _ = tensor.stride()
+            return N.Input(tensor.data_ptr(), code, blocks, heads, tokens * stride_t, stride_h, stride_t, tokens, channels,
+                           None, 0, 0)
 
         def field(tensor, row_bytes):
             return N.Field(tensor.data_ptr(), row_bytes * heads, row_bytes)
 
-        none = N.Field(None, 0, 0)
-
-        def k4_launch(tensor):
+        def k4_arguments(tensor):
             count = math.floor(channels * codec.salient_fraction)
             payload = torch.empty((blocks, heads, tokens, channels // 2), dtype=torch.uint8, device=device)
             scales = torch.empty((blocks, heads, channels), dtype=torch.float32, device=device)
@@ -445,15 +433,33 @@ class InQuantCache(_HFCache):
             args.padding = field(padding, count * 4) if count else none
             args.salient = field(salient, count) if count else none
             args.donors = field(donors, count) if count else none
-            args.roles, args.role_bytes, args.descriptor_i32 = none, 0, 0
-            packed = PackedTensor(payload, scales, salient, donors, padding, (blocks, heads, tokens, channels), dtype)
-            return args, packed
+            return args, (payload, scales, salient, donors, padding)
 
-        key_args, packed_keys = k4_launch(pending_key)
-        seal.key = N.ctypes.pointer(key_args)
+        shape = (blocks, heads, tokens, channels)
+        key_args, key_fields = k4_arguments(pending_key)
+        N.check(lib.inq_k4_encode(N.ctypes.byref(key_args), status, N.stream_pointer(device)), "inq_k4_encode")
+        packed_keys = PackedTensor(*key_fields, shape, dtype)
+
+        seal = N.SealArgs()
+        seal.heads, seal.row_bytes = heads, channels * 2
+        n = 0
+        for source, first, target, start, count in copies():
+            if not count:
+                continue
+            entry = seal.copies[n]
+            _, source_h, source_t, _ = source.stride()
+            _, target_h, target_t, _ = target.stride()
+            entry.src = source.data_ptr() + first * source_t * 2
+            entry.dst = target.data_ptr() + start * target_t * 2
+            entry.src_stride_h, entry.src_stride_t = source_h * 2, source_t * 2
+            entry.dst_stride_h, entry.dst_stride_t = target_h * 2, target_t * 2
+            entry.tokens = count
+            n += 1
+        seal.n_copies = n
         if cfg.value_bits is None:
-            value_args, packed_values = k4_launch(pending_value)
+            value_args, value_fields = k4_arguments(pending_value)
             seal.value_k4 = N.ctypes.pointer(value_args)
+            packed_values = PackedTensor(*value_fields, shape, dtype)
         else:
             from .value_codec import ArenaPackedValues, PackedValues
             bits, group = cfg.value_bits, cfg.value_group_size
@@ -467,16 +473,14 @@ class InQuantCache(_HFCache):
             value_args.scales = field(scales, tokens * (channels // group) * 2)
             value_args.offsets = field(offsets, tokens * (channels // group) * 2)
             seal.value = N.ctypes.pointer(value_args)
-            packed_values = PackedValues(payload, scales, offsets, (blocks, heads, tokens, channels), dtype, bits, group)
-        N.check(N.library().inq_seal_blocks(N.ctypes.byref(seal), N.status_word(device).data_ptr(), N.stream_pointer(device)),
-                "inq_seal_blocks")
+            packed_values = PackedValues(payload, scales, offsets, shape, dtype, bits, group)
+        N.check(lib.inq_seal_blocks(N.ctypes.byref(seal), status, N.stream_pointer(device)), "inq_seal_blocks")
         if blocks == 1:
             return [packed_keys], [packed_values]
-        shape = (1, heads, tokens, channels)
-        new_keys = ArenaPackedTensor.split(packed_keys, blocks, shape, dtype)
+        new_keys = ArenaPackedTensor.split(packed_keys, blocks)
         if cfg.value_bits is None:
-            return new_keys, ArenaPackedTensor.split(packed_values, blocks, shape, dtype)
-        return new_keys, ArenaPackedValues.split(packed_values, blocks, shape, dtype)
+            return new_keys, ArenaPackedTensor.split(packed_values, blocks)
+        return new_keys, ArenaPackedValues.split(packed_values, blocks)
 
     def _write_token(self, layer: _Layer, keys, values, sink_position: int) -> bool:
         """One-kernel write of a single token into the tail (and the sink); False when the
@@ -566,21 +570,33 @@ class InQuantCache(_HFCache):
                     pending_value = torch.cat((layer.residual_value, pending_value), dim=2)
         offset = blocks * cfg.block_size
         remainder = pending_key.shape[2] - offset
-        # a new tail buffer: views handed out earlier keep the old one alive and unchanged.  The
-        # buffer retired by the previous seal is taken again when nothing else refers to it any more.
-        tail_key_buffer, tail_value_buffer = self._tail_buffers_for(layer, max(capacity, remainder))
+        tail_buffers = []
+
+        def new_tail():
+            # a new tail buffer: views handed out earlier keep the old one alive and unchanged.  The
+            # buffer retired by the previous seal is taken again when nothing else refers to it any more.
+            if not tail_buffers:
+                tail_buffers.extend(self._tail_buffers_for(layer, max(capacity, remainder)))
+            return tail_buffers
+
+        def row_copies():
+            tail_key_buffer, tail_value_buffer = new_tail()
+            return ((pending_key, offset, tail_key_buffer, 0, remainder),
+                    (pending_value, offset, tail_value_buffer, 0, remainder),
+                    (keys, 0, layer.sink_key_buffer, layer.sink_count, take_sink),
+                    (values, 0, layer.sink_value_buffer, layer.sink_count, take_sink))
+
         # Both encoders are launched before either finite check is read: the key and value kernels
         # run back to back while the host builds the block views, and one read of the status word
         # (one synchronisation instead of two) decides before any state changes.  Where the layout
-        # allows, the encoders and the copies into the new tail and the sink are one host call; rows
-        # that the copies write lie beyond what the layer's counters expose until the check passed.
+        # allows, the key encoder starts before the new tail is even allocated, and the value encoder
+        # and the copies into the new tail and the sink are one host call; rows that the copies write
+        # lie beyond what the layer's counters expose until the check passed.
         sealed = None
         if blocks:
-            sealed = self._seal_in_one_call(layer, pending_key, pending_value, blocks, (
-                (pending_key, offset, tail_key_buffer, 0, remainder),
-                (pending_value, offset, tail_value_buffer, 0, remainder),
-                (keys, 0, layer.sink_key_buffer, layer.sink_count, take_sink),
-                (values, 0, layer.sink_value_buffer, layer.sink_count, take_sink)))
+            sealed = self._seal_direct(layer, pending_key, pending_value, blocks,
+                                       (keys, values) if take_sink else (), row_copies)
+        tail_key_buffer, tail_value_buffer = new_tail()
         if sealed is not None:
             new_keys, new_values = sealed
         else:

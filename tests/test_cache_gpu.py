@@ -190,8 +190,9 @@ def test_batched_prefill_matches_serial_blocks():
 
 
 @pytest.mark.parametrize("value_bits", [None, 2, 4])
-def test_one_call_sealing_equals_the_call_by_call_path(value_bits, monkeypatch):
-    """Sealing through ``inq_seal_blocks`` (encoders and the sink / tail copies from one host call)
+def test_direct_sealing_equals_the_call_by_call_path(value_bits, monkeypatch):
+    """Sealing with computed descriptors (key encoder first, then ``inq_seal_blocks``: value
+    encoder and the sink / tail copies from one host call)
     leaves byte for byte what the general path leaves: every packed field, the sink and the tail,
     over a prefill of several blocks, chunks that cross block boundaries, sink tokens arriving in
     the same call as sealed blocks, and decode steps that seal."""
@@ -206,15 +207,15 @@ def test_one_call_sealing_equals_the_call_by_call_path(value_bits, monkeypatch):
     def run(one_call, k):
         calls = []
         if one_call:
-            original = InQuantCache._seal_in_one_call
+            original = InQuantCache._seal_direct
 
             def counted(self, *args):
                 result = original(self, *args)
                 calls.append(result is not None)
                 return result
-            monkeypatch.setattr(InQuantCache, "_seal_in_one_call", counted)
+            monkeypatch.setattr(InQuantCache, "_seal_direct", counted)
         else:
-            monkeypatch.setattr(InQuantCache, "_seal_in_one_call", lambda self, *args: None)
+            monkeypatch.setattr(InQuantCache, "_seal_direct", lambda self, *args: None)
         cache = InQuantCache(cfg)
         for start, stop in chunks:
             if stop - start == 1 and start > 150:
