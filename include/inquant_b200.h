@@ -293,13 +293,13 @@ typedef struct {
 int inq_decode_attention(const inq_decode_args_t* args /* host */, inq_stream_t stream);
 /* The same decode step for callers that cannot allocate device memory (a serving engine that
  * has committed the whole device to its own page pool, a host runtime that owns all device
- * memory, code inside a CUDA-graph capture).  It has no counterpart in the reference.  The
+ * memory).  It has no counterpart in the reference.  The
  * partial records and arrival counters live in a fixed array inside the library (about 4.2 MB
  * per device, held until the process exits), so `partials`, `partials_floats` and `counters` of
  * the arguments are ignored.  Limits: at most 256 pairs (n_seq * kv_heads * ceil(q_per_kv/8))
  * and at most 1024 partial records (resident CTAs + pairs) per launch; larger launches return
  * INQ_ERR_CAPACITY.  It calls no cudaMalloc/cudaFree.  The first call on a device resolves the
- * array's address and zeroes its counters on `stream`: make that call before any stream capture.
+ * array's address and zeroes its counters on `stream`.
  * All calls on a device share the array: launches that may overlap on the GPU (different
  * streams) race on it; calls on one stream do not. */
 int inq_decode_attention_noalloc(const inq_decode_args_t* args /* host */, inq_stream_t stream);

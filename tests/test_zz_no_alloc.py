@@ -1,8 +1,8 @@
 """The allocation-free decode entry point (`inq_decode_attention_noalloc`).
 
 Some callers of this library cannot allocate device memory when they decode: a serving engine
-that gave the whole device to its page pool at start-up, a host runtime that owns all device
-memory itself, or code that runs inside a CUDA-graph capture.  For them the library keeps the
+that gave the whole device to its page pool at start-up, or a host runtime that owns all device
+memory itself.  For them the library keeps the
 split-KV scratch in a fixed device array.  This test drives that entry point directly through
 the C ABI and checks it against the ordinary entry point (which uses caller-provided scratch)
 on two consecutive calls, because the fixed array keeps the previous call's contents.
