@@ -83,13 +83,25 @@ class _Layer:
     retired_tail: tuple | None = None               # the tail buffers replaced by the last seal
     append_args: tuple | None = None                # launch structure of the one-token append, per tail buffer pair
 
+    sink_views: tuple | None = None                 # (count, key view, value view) handed out last
+
+    def _sink_pair(self):
+        """The sink views for the current count: the same two tensor objects until the count changes
+        (a full sink never changes again, so every decode step of a layer gets the pair it got
+        before and whoever checked it once need not check it again)."""
+        cached = self.sink_views
+        if cached is None or cached[0] != self.sink_count:
+            cached = self.sink_views = (self.sink_count, self.sink_key_buffer[:, :, :self.sink_count],
+                                        self.sink_value_buffer[:, :, :self.sink_count])
+        return cached
+
     @property
     def sink_key(self):
-        return None if not self.sink_count else self.sink_key_buffer[:, :, :self.sink_count]
+        return None if not self.sink_count else self._sink_pair()[1]
 
     @property
     def sink_value(self):
-        return None if not self.sink_count else self.sink_value_buffer[:, :, :self.sink_count]
+        return None if not self.sink_count else self._sink_pair()[2]
 
     @property
     def residual_key(self):
