@@ -45,6 +45,19 @@ class SharedDecodeWorkspace:
             self.tensor = torch.empty(required, dtype=torch.float32, device=device)
         return self.tensor[:required].view(shape)
 
+    def acquire_address(self, floats: int, device, identity=None) -> int:
+        """``acquire`` for a caller that only needs the device address of ``floats`` scratch floats
+        (no view tensors are built); ``identity`` is the caller's current-stream identity when it
+        already has it."""
+        if identity is None:
+            identity = N.stream_identity(device)
+        if self._stream_identity is not None and identity != self._stream_identity:
+            raise RuntimeError("Shared decode workspace requires one CUDA stream per cache")
+        self._stream_identity = identity
+        if self.tensor is None or self.tensor.numel() < floats:
+            self.tensor = torch.empty(floats, dtype=torch.float32, device=device)
+        return self.tensor.data_ptr()
+
 
 def workspace_floats(n_pairs: int, total_units: int) -> int:
     """Scratch floats for the split-KV partial records of ``n_pairs`` (sequence, KV head,
@@ -331,12 +344,13 @@ class PackedDecodeState:
             records = workspace_floats(pairs, pairs * pair_units(n_blocks, self._packed_tokens)) // N.RECORD_FLOATS
             self._record_counts = {(pairs, n_blocks): records}     # one entry: the count changes when a block is sealed
         workspace_shape = (records, N.RECORD_FLOATS)
+        workspace_floats_needed = records * N.RECORD_FLOATS
         if self._workspace_pool is not None:
-            workspace = self._workspace_pool.acquire(workspace_shape, query.device)
+            workspace_address = self._workspace_pool.acquire_address(workspace_floats_needed, query.device, identity)
         else:
             if self._workspace is None or self._workspace.shape != workspace_shape or self._workspace.device != query.device:
                 self._workspace = torch.empty(workspace_shape, dtype=torch.float32, device=query.device)
-            workspace = self._workspace
+            workspace_address = self._workspace.data_ptr()
         if query.data_ptr() % 16 or query.stride(1) % 8:     # rows of a head: 16-byte aligned (unit channel stride was checked)
             query = query.contiguous()
         output = torch.empty(query.shape, dtype=query.dtype, device=query.device)
@@ -369,7 +383,7 @@ class PackedDecodeState:
         args.block_tokens, args.n_pad = self._packed_tokens, self._salient
         args.layout, args.dtype, args.scale = 0, N.DTYPE_CODE[query.dtype], scale
         args.value_kind, args.value_groups = kind
-        args.partials, args.partials_floats = workspace.data_ptr(), workspace.numel()
+        args.partials, args.partials_floats = workspace_address, workspace_floats_needed
         args.counters = N.decode_counters(query.device, kv_heads * tiles).data_ptr()
         args.status = N.status_word(query.device).data_ptr()
         rc = N.library().inq_decode_attention(N.ctypes.byref(args), N.stream_pointer(query.device))
