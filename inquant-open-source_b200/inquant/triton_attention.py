@@ -134,53 +134,64 @@ class PackedDecodeState:
             raise ValueError("PackedDecodeState.extend requires an immutable append-only prefix")
         if len(key_blocks) == old_count:
             return
-        first = key_blocks[0]
-        if first.shape[0] != 1 or first.shape[-1] != 128 or first.payload.device.type != "cuda":
+        # Blocks of an encoder arena are judged by the arena's tensors, each arena once: none of
+        # their field views (nor their instance dictionaries) has to be created here -- a 32K-token
+        # layer holds over a thousand fields in 254 blocks.
+        def owners(blocks):
+            """(tensors' owner, shape of one block) per plain block and per run of one arena's blocks."""
+            last = None
+            for block in blocks:
+                arena = getattr(block, "_arena", None)
+                if arena is None:
+                    last = None
+                    yield block, block.shape
+                elif arena[0] is not last:
+                    last = arena[0]
+                    yield last, (1, *last.shape[1:])
+
+        first, first_shape = next(owners(key_blocks[:1]))
+        first_device = first.payload.device
+        if first_shape[0] != 1 or first_shape[-1] != 128 or first_device.type != "cuda":
             raise ValueError("Packed decode requires CUDA blocks with batch=1 and head_dim=128")
-        identity = N.stream_identity(first.payload.device)
+        identity = N.stream_identity(first_device)
         if self._stream_identity is not None and self._stream_identity != identity:
             raise RuntimeError("Descriptor updates require one CUDA stream per state")
         self._stream_identity = identity
-        self._device = first.payload.device
-        self._kv_heads = first.shape[1]
-        self._packed_tokens = first.shape[2]
+        self._device = first_device
+        self._kv_heads = first_shape[1]
+        self._packed_tokens = first_shape[2]
         self._salient = first.salient_channels.shape[-1]
         # Only the new suffix is checked: the prefix was checked when it was added and is immutable.
-        # Blocks of an encoder arena are judged by the arena's tensors, so that none of their field
-        # views has to be created here (a 32K-token layer holds over a thousand of them).
-        def parts(block):
-            arena = getattr(block, "_arena", None)
-            return arena[0] if arena is not None else block
-
         new_keys, new_values = key_blocks[old_count:], value_blocks[old_count:]
-        for block in new_keys:
-            if not isinstance(block, PackedTensor) or block.shape != first.shape \
-                    or parts(block).salient_channels.shape[-1] != self._salient:
+        key_owners, value_owners = list(owners(new_keys)), list(owners(new_values))
+        for owner, shape in key_owners:
+            if not isinstance(owner, PackedTensor) or shape != first_shape \
+                    or owner.salient_channels.shape[-1] != self._salient:
                 raise ValueError("All packed K/V blocks must share shape and salient-channel count")
         # the preset (2-bit values in groups of 64) runs the streaming kernel; every other value
         # codec the reference accepts runs the general kernel
-        self._inquant_values = isinstance(value_blocks[0], PackedTensor)
+        first_value = next(owners(value_blocks[:1]))[0]
+        self._inquant_values = isinstance(first_value, PackedTensor)
         if self._inquant_values:
             self._value_bits, self._value_group = 0, 64
-            self._value_salient = parts(value_blocks[0]).salient_channels.shape[-1]
-        elif isinstance(value_blocks[0], PackedValues):
-            self._value_bits = value_blocks[0].bits
-            self._value_group = value_blocks[0].group_size
+            self._value_salient = first_value.salient_channels.shape[-1]
+        elif isinstance(first_value, PackedValues):
+            self._value_bits = first_value.bits
+            self._value_group = first_value.group_size
             self._value_salient = 0
         else:
             raise ValueError("Value blocks must be PackedValues or PackedTensor")
         self._preset = not self._inquant_values and (self._value_bits, self._value_group) == (2, 64)
-        for block in new_values:
-            if block.shape != first.shape:
+        for owner, shape in value_owners:
+            if shape != first_shape:
                 raise ValueError("All packed blocks must share shape")
             if self._inquant_values:
-                if not isinstance(block, PackedTensor) or parts(block).salient_channels.shape[-1] != self._value_salient:
+                if not isinstance(owner, PackedTensor) or owner.salient_channels.shape[-1] != self._value_salient:
                     raise ValueError("All V blocks must share the same quantizer")
-            elif not isinstance(block, PackedValues) or (block.bits, block.group_size) != (self._value_bits, self._value_group):
+            elif not isinstance(owner, PackedValues) or (owner.bits, owner.group_size) != (self._value_bits, self._value_group):
                 raise ValueError("All V blocks must share the same quantizer")
         checked = set()
-        for block in (*new_keys, *new_values):
-            owner = parts(block)
+        for owner, _ in (*key_owners, *value_owners):
             if id(owner) in checked:
                 continue
             checked.add(id(owner))

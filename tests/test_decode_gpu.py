@@ -200,6 +200,48 @@ def test_argument_validation():
         PackedDecodeState([quantize(kv), quantize(kv)], [quantize(kv), quantize_values(kv)])
 
 
+def test_extend_judges_the_blocks_of_an_encoder_launch_by_their_arena():
+    """Blocks sealed by one launch are checked and addressed through their arena: none of their
+    field views is created, a plain block sealed later joins them, and blocks of another geometry
+    or codec are refused with the reference's messages."""
+    from inquant.cache import CacheConfig, InQuantCache
+    CodecConfig, quantize, quantize_values, PackedDecodeState, _, _ = _mods()
+
+    def cache_with(block, tokens, value_bits=2, seed=5):
+        cache = InQuantCache(CacheConfig(CodecConfig(), block_size=block, residual_length=8, sink_tokens=4,
+                                         value_bits=value_bits, validate_positions=False))
+        x = to_device(_random(seed, (1, 2, tokens, 128), "bfloat16"))
+        cache.extend(x, x, 0)
+        return cache, x
+
+    cache, x = cache_with(32, 4 + 5 * 32 + 8 + 31)
+    layer = cache._layers[0]
+    assert len(layer.key_blocks) == 5 and all(hasattr(b, "_arena") for b in layer.key_blocks)
+    state = PackedDecodeState(layer.key_blocks, layer.value_blocks)
+    assert all(not vars(b) for b in layer.key_blocks + layer.value_blocks)      # nothing was materialised
+    q = to_device(_random(6, (1, 4, 1, 128), "bfloat16"))
+    before = state.decode(q, sink_key=layer.sink_key, sink_value=layer.sink_value,
+                          residual_key=layer.residual_key, residual_value=layer.residual_value)
+    cache.extend(x[:, :, :1], x[:, :, :1], 0)                                  # completes a block: a plain one
+    assert len(layer.key_blocks) == 6 and not hasattr(layer.key_blocks[5], "_arena")
+    state.extend(layer.key_blocks, layer.value_blocks)
+    after = state.decode(q, sink_key=layer.sink_key, sink_value=layer.sink_value,
+                         residual_key=layer.residual_key, residual_value=layer.residual_value)
+    dense_k, dense_v = cache.materialize(0)
+    want = oracle.attention_decode(to_numpy(q.float())[0, :, 0], to_numpy(dense_k.float())[0], to_numpy(dense_v.float())[0],
+                                   128 ** -0.5)
+    attention_close(to_numpy(after.float()).reshape(want.shape), want)
+    assert before.shape == after.shape
+
+    other, _ = cache_with(64, 4 + 3 * 64 + 8)
+    with pytest.raises(ValueError, match="share shape"):
+        PackedDecodeState(layer.key_blocks + other._layers[0].key_blocks, layer.value_blocks + other._layers[0].value_blocks)
+    four_bit, _ = cache_with(32, 4 + 2 * 32 + 8, value_bits=4)
+    with pytest.raises(ValueError, match="same quantizer"):
+        PackedDecodeState(layer.key_blocks + four_bit._layers[0].key_blocks,
+                          layer.value_blocks + four_bit._layers[0].value_blocks)
+
+
 @pytest.mark.parametrize("name", sorted(DECODE_CASES))
 def test_single_layer_roundtrip_matches_reference_output(golden, name):
     """Config 0 of the benchmark definition (and a short-block variant): encode on the GPU,
