@@ -38,6 +38,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     objects = []
     build_dir = os.path.join(HERE, "build")
     os.makedirs(build_dir, exist_ok=True)
+    running = []
     for name, extra in SOURCES.items():
         src = os.path.join(CSRC, name)
         obj = os.path.join(build_dir, name.replace(".cu", ".o"))
@@ -45,8 +46,13 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
             cmd = [nvcc, *ARCH, *COMMON, *extra, "-c", src, "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
-            subprocess.run(cmd, check=True)
+            # the translation units are independent: all stale ones compile at the same time (the
+            # decode kernels alone take minutes), which bounds a build from scratch by the longest file
+            running.append((cmd, subprocess.Popen(cmd)))
         objects.append(obj)
+    failed = [cmd for cmd, process in running if process.wait() != 0]
+    if failed:
+        raise subprocess.CalledProcessError(1, failed[0])
     if force or _stale(LIB, objects):
         subprocess.run([nvcc, *ARCH, "-shared", "-o", LIB, *objects, "-cudart", "static"], check=True)
     return LIB
