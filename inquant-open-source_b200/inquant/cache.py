@@ -8,7 +8,9 @@ values) and an exact recent tail.  Differences from the reference implementation
   by a single small kernel (C ABI ``inq_append_token``) instead of ``torch.cat`` + ``clone``
   of the whole tail, and ``residual_key`` / ``sink_key`` are views of those buffers;
 * all blocks sealed by one call come out of ONE fused encoder launch per tensor and are
-  exposed as views of its output arena (no per-block clones);
+  exposed as views of its output arena (no per-block clones); the launches take their
+  descriptors from the strides of the pending tensors, the key encoder goes first and the value
+  encoder and the sink / tail row copies follow in one host call (C ABI ``inq_seal_blocks``);
 * byte accounting is logical (``numel * itemsize``), which equals the storage sizes the
   reference reports for its compact clones.
 
